@@ -1,0 +1,467 @@
+// Bandwidth-bound kernels: RMSNorm (+residual add), per-head QK-RMSNorm fused with RoPE, SwiGLU.
+//
+// All of them read and write bf16 with fp32 math, use 16-byte vector accesses and size their
+// grids from the row count. They take the place of the reference's Triton kernels
+// src/kohakuwullm/kernels/elementwise/rmsnorm.py:20-128, swiglu.py:49-119 and
+// src/kohakuwullm/kernels/attention/rope.py:27-89.
+#include "common.cuh"
+
+namespace kwu {
+
+// --------------------------------------------------------------------------- RMSNorm
+// One warp per row. y = x * rstd * w   (w fp32, optional; `one_plus` selects the Gemma (1+w) form)
+// Optional fused residual: h = x + res is formed first, written to `h_out`, and normalised.
+template <bool HAS_RES>
+__global__ void __launch_bounds__(256)
+rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+                   const float* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                   __nv_bfloat16* __restrict__ h_out, float* __restrict__ rstd_out, int rows,
+                   int cols, float eps, int one_plus) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int nvec = cols >> 3;  // cols % 8 == 0 (checked on the host)
+  for (int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows;
+       row += gridDim.x * warps_per_block) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * cols);
+    const uint4* rr = HAS_RES ? reinterpret_cast<const uint4*>(res + static_cast<size_t>(row) * cols) : nullptr;
+    uint4* hr = HAS_RES ? reinterpret_cast<uint4*>(h_out + static_cast<size_t>(row) * cols) : nullptr;
+    float ss = 0.f;
+    for (int v = lane; v < nvec; v += 32) {
+      uint4 a = xr[v];
+      float2 f0 = unpack_bf16(a.x), f1 = unpack_bf16(a.y), f2 = unpack_bf16(a.z), f3 = unpack_bf16(a.w);
+      if (HAS_RES) {
+        const uint4 b = rr[v];
+        const float2 g0 = unpack_bf16(b.x), g1 = unpack_bf16(b.y), g2 = unpack_bf16(b.z), g3 = unpack_bf16(b.w);
+        a.x = pack_bf16(f0.x + g0.x, f0.y + g0.y);
+        a.y = pack_bf16(f1.x + g1.x, f1.y + g1.y);
+        a.z = pack_bf16(f2.x + g2.x, f2.y + g2.y);
+        a.w = pack_bf16(f3.x + g3.x, f3.y + g3.y);
+        hr[v] = a;
+        // normalise the value that was stored (bf16-rounded), so backward sees the same h
+        f0 = unpack_bf16(a.x); f1 = unpack_bf16(a.y); f2 = unpack_bf16(a.z); f3 = unpack_bf16(a.w);
+      }
+      ss += f0.x * f0.x + f0.y * f0.y + f1.x * f1.x + f1.y * f1.y + f2.x * f2.x + f2.y * f2.y +
+            f3.x * f3.x + f3.y * f3.y;
+    }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / static_cast<float>(cols) + eps);
+    if (lane == 0 && rstd_out) rstd_out[row] = rstd;
+    if (HAS_RES) __syncwarp();
+    const uint4* src = HAS_RES ? reinterpret_cast<const uint4*>(hr) : xr;
+    uint4* yr = reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * cols);
+    for (int v = lane; v < nvec; v += 32) {
+      const uint4 a = src[v];
+      float f[8];
+      float2 t;
+      t = unpack_bf16(a.x); f[0] = t.x; f[1] = t.y;
+      t = unpack_bf16(a.y); f[2] = t.x; f[3] = t.y;
+      t = unpack_bf16(a.z); f[4] = t.x; f[5] = t.y;
+      t = unpack_bf16(a.w); f[6] = t.x; f[7] = t.y;
+      if (w) {
+        const float4 w0 = reinterpret_cast<const float4*>(w)[2 * v];
+        const float4 w1 = reinterpret_cast<const float4*>(w)[2 * v + 1];
+        const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] = f[e] * rstd * (one_plus ? 1.f + ww[e] : ww[e]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] *= rstd;
+      }
+      uint4 o;
+      o.x = pack_bf16(f[0], f[1]); o.y = pack_bf16(f[2], f[3]);
+      o.z = pack_bf16(f[4], f[5]); o.w = pack_bf16(f[6], f[7]);
+      yr[v] = o;
+    }
+  }
+}
+
+// Backward. dx = rstd * (g - xhat * mean(g * xhat)),  g = dy * w_eff,  xhat = x * rstd.
+// Optional `dres` is added into dx (gradient arriving on the residual path), which fuses the
+// residual-add backward. Each block accumulates a dW partial over its rows in shared memory and
+// writes it to dw_partial[block, cols]; a second kernel sums the partials.
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
+                   const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dy,
+                   const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
+                   float* __restrict__ dw_partial, int rows, int cols, int one_plus) {
+  extern __shared__ float s_dw[];  // cols floats
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int nvec = cols >> 3;
+  if (dw_partial)
+    for (int i = threadIdx.x; i < cols; i += blockDim.x) s_dw[i] = 0.f;
+  __syncthreads();
+  for (int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows;
+       row += gridDim.x * warps_per_block) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * cols);
+    const uint4* gr = reinterpret_cast<const uint4*>(dy + static_cast<size_t>(row) * cols);
+    const float rstd = rstd_in[row];
+    float dot = 0.f;
+    for (int v = lane; v < nvec; v += 32) {
+      const uint4 a = xr[v], g = gr[v];
+      float xf[8], gf[8];
+      float2 t;
+      t = unpack_bf16(a.x); xf[0] = t.x; xf[1] = t.y; t = unpack_bf16(a.y); xf[2] = t.x; xf[3] = t.y;
+      t = unpack_bf16(a.z); xf[4] = t.x; xf[5] = t.y; t = unpack_bf16(a.w); xf[6] = t.x; xf[7] = t.y;
+      t = unpack_bf16(g.x); gf[0] = t.x; gf[1] = t.y; t = unpack_bf16(g.y); gf[2] = t.x; gf[3] = t.y;
+      t = unpack_bf16(g.z); gf[4] = t.x; gf[5] = t.y; t = unpack_bf16(g.w); gf[6] = t.x; gf[7] = t.y;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        float we = 1.f;
+        if (w) we = one_plus ? 1.f + w[8 * v + e] : w[8 * v + e];
+        dot += gf[e] * we * xf[e] * rstd;
+      }
+    }
+    dot = warp_sum(dot) / static_cast<float>(cols);
+    const uint4* rr = dres ? reinterpret_cast<const uint4*>(dres + static_cast<size_t>(row) * cols) : nullptr;
+    uint4* dxr = reinterpret_cast<uint4*>(dx + static_cast<size_t>(row) * cols);
+    for (int v = lane; v < nvec; v += 32) {
+      const uint4 a = xr[v], g = gr[v];
+      float xf[8], gf[8], rf[8];
+      float2 t;
+      t = unpack_bf16(a.x); xf[0] = t.x; xf[1] = t.y; t = unpack_bf16(a.y); xf[2] = t.x; xf[3] = t.y;
+      t = unpack_bf16(a.z); xf[4] = t.x; xf[5] = t.y; t = unpack_bf16(a.w); xf[6] = t.x; xf[7] = t.y;
+      t = unpack_bf16(g.x); gf[0] = t.x; gf[1] = t.y; t = unpack_bf16(g.y); gf[2] = t.x; gf[3] = t.y;
+      t = unpack_bf16(g.z); gf[4] = t.x; gf[5] = t.y; t = unpack_bf16(g.w); gf[6] = t.x; gf[7] = t.y;
+      if (rr) {
+        const uint4 r = rr[v];
+        t = unpack_bf16(r.x); rf[0] = t.x; rf[1] = t.y; t = unpack_bf16(r.y); rf[2] = t.x; rf[3] = t.y;
+        t = unpack_bf16(r.z); rf[4] = t.x; rf[5] = t.y; t = unpack_bf16(r.w); rf[6] = t.x; rf[7] = t.y;
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) rf[e] = 0.f;
+      }
+      float o[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        float we = 1.f;
+        if (w) we = one_plus ? 1.f + w[8 * v + e] : w[8 * v + e];
+        const float xhat = xf[e] * rstd;
+        o[e] = rstd * (gf[e] * we - xhat * dot) + rf[e];
+        if (dw_partial) atomicAdd(&s_dw[8 * v + e], gf[e] * xhat);
+      }
+      uint4 ov;
+      ov.x = pack_bf16(o[0], o[1]); ov.y = pack_bf16(o[2], o[3]);
+      ov.z = pack_bf16(o[4], o[5]); ov.w = pack_bf16(o[6], o[7]);
+      dxr[v] = ov;
+    }
+  }
+  if (dw_partial) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < cols; i += blockDim.x)
+      dw_partial[static_cast<size_t>(blockIdx.x) * cols + i] = s_dw[i];
+  }
+}
+
+// dw[c] (+)= sum_b partial[b, c]
+__global__ void colsum_partials_kernel(const float* __restrict__ partial, float* __restrict__ dw,
+                                       int nblocks, int cols, int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float s = 0.f;
+  for (int b = 0; b < nblocks; ++b) s += partial[static_cast<size_t>(b) * cols + c];
+  dw[c] = accumulate ? dw[c] + s : s;
+}
+
+// --------------------------------------------------------------------------- QK-norm + RoPE
+// One warp per (token, head) row of HEAD_DIM = 64: lane i owns elements i and i+32, which are
+// exactly the rotate-half partners. Reads rows from a strided source (the fused qkv projection
+// output), applies RMSNorm over the head (optional fp32 weight[64]) and then rotary embedding
+// with per-token cos/sin half tables (T, rot/2) fp32; elements beyond `rot` pass through.
+//   forward : dst = rope(norm(src))
+//   backward: dsrc = norm_bwd(rope_bwd(ddst)); dweight partials accumulated with atomics.
+__global__ void __launch_bounds__(256)
+qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ src, int src_ld,
+                       __nv_bfloat16* __restrict__ dst, int dst_ld,
+                       const float* __restrict__ weight, const float* __restrict__ cos_t,
+                       const float* __restrict__ sin_t, int tokens, int heads, int rot_half,
+                       float eps, int do_norm) {
+  const int lane = threadIdx.x & 31;
+  const long total = static_cast<long>(tokens) * heads;
+  const int wpb = blockDim.x >> 5;
+  for (long r = static_cast<long>(blockIdx.x) * wpb + (threadIdx.x >> 5); r < total;
+       r += static_cast<long>(gridDim.x) * wpb) {
+    const int t = static_cast<int>(r / heads);
+    const int h = static_cast<int>(r % heads);
+    const __nv_bfloat16* s = src + static_cast<size_t>(t) * src_ld + h * 64;
+    float a = __bfloat162float(s[lane]);
+    float b = __bfloat162float(s[lane + 32]);
+    if (do_norm) {
+      const float ss = warp_sum(a * a + b * b);
+      const float rstd = rsqrtf(ss * (1.f / 64.f) + eps);
+      a *= rstd;
+      b *= rstd;
+      if (weight) {
+        a *= weight[lane];
+        b *= weight[lane + 32];
+      }
+      // the reference rounds the normalised value to the storage dtype before rotating
+      a = __bfloat162float(__float2bfloat16(a));
+      b = __bfloat162float(__float2bfloat16(b));
+    }
+    float oa = a, ob = b;
+    if (rot_half == 32) {
+      const float c = cos_t[static_cast<size_t>(t) * 32 + lane];
+      const float sn = sin_t[static_cast<size_t>(t) * 32 + lane];
+      oa = a * c - b * sn;
+      ob = b * c + a * sn;
+    } else if (rot_half > 0) {
+      // partial rotary: element j < rot_half pairs with j + rot_half; the tail passes through
+      const float other_a = __shfl_sync(0xffffffffu, a, (lane + rot_half) & 31);
+      const float other_b = __shfl_sync(0xffffffffu, a, (lane - rot_half) & 31);
+      if (lane < rot_half) {
+        const float c = cos_t[static_cast<size_t>(t) * rot_half + lane];
+        const float sn = sin_t[static_cast<size_t>(t) * rot_half + lane];
+        oa = a * c - other_a * sn;
+      } else if (lane < 2 * rot_half) {
+        const float c = cos_t[static_cast<size_t>(t) * rot_half + lane - rot_half];
+        const float sn = sin_t[static_cast<size_t>(t) * rot_half + lane - rot_half];
+        oa = a * c + other_b * sn;
+      }
+    }
+    __nv_bfloat16* d = dst + static_cast<size_t>(t) * dst_ld + h * 64;
+    d[lane] = __float2bfloat16(oa);
+    d[lane + 32] = __float2bfloat16(ob);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ src, int src_ld,
+                       const __nv_bfloat16* __restrict__ dout, int dout_ld,
+                       __nv_bfloat16* __restrict__ dsrc, int dsrc_ld,
+                       const float* __restrict__ weight, float* __restrict__ dweight,
+                       const float* __restrict__ cos_t, const float* __restrict__ sin_t, int tokens,
+                       int heads, int rot_half, float eps, int do_norm) {
+  __shared__ float s_dw[64];
+  if (threadIdx.x < 64) s_dw[threadIdx.x] = 0.f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const long total = static_cast<long>(tokens) * heads;
+  const int wpb = blockDim.x >> 5;
+  float dwa = 0.f, dwb = 0.f;
+  for (long r = static_cast<long>(blockIdx.x) * wpb + (threadIdx.x >> 5); r < total;
+       r += static_cast<long>(gridDim.x) * wpb) {
+    const int t = static_cast<int>(r / heads);
+    const int h = static_cast<int>(r % heads);
+    const __nv_bfloat16* g = dout + static_cast<size_t>(t) * dout_ld + h * 64;
+    float ga = __bfloat162float(g[lane]);
+    float gb = __bfloat162float(g[lane + 32]);
+    // rotary backward = rotation by the negated angle
+    float da = ga, db = gb;
+    if (rot_half == 32) {
+      const float c = cos_t[static_cast<size_t>(t) * 32 + lane];
+      const float sn = sin_t[static_cast<size_t>(t) * 32 + lane];
+      da = ga * c + gb * sn;
+      db = gb * c - ga * sn;
+    } else if (rot_half > 0) {
+      const float other_a = __shfl_sync(0xffffffffu, ga, (lane + rot_half) & 31);
+      const float other_b = __shfl_sync(0xffffffffu, ga, (lane - rot_half) & 31);
+      if (lane < rot_half) {
+        const float c = cos_t[static_cast<size_t>(t) * rot_half + lane];
+        const float sn = sin_t[static_cast<size_t>(t) * rot_half + lane];
+        da = ga * c + other_a * sn;
+      } else if (lane < 2 * rot_half) {
+        const float c = cos_t[static_cast<size_t>(t) * rot_half + lane - rot_half];
+        const float sn = sin_t[static_cast<size_t>(t) * rot_half + lane - rot_half];
+        da = ga * c - other_b * sn;
+      }
+    }
+    if (do_norm) {
+      const __nv_bfloat16* s = src + static_cast<size_t>(t) * src_ld + h * 64;
+      const float xa = __bfloat162float(s[lane]);
+      const float xb = __bfloat162float(s[lane + 32]);
+      const float ss = warp_sum(xa * xa + xb * xb);
+      const float rstd = rsqrtf(ss * (1.f / 64.f) + eps);
+      const float ha = xa * rstd, hb = xb * rstd;
+      const float wa = weight ? weight[lane] : 1.f, wb = weight ? weight[lane + 32] : 1.f;
+      if (dweight) {
+        dwa += da * ha;
+        dwb += db * hb;
+      }
+      const float g1 = da * wa, g2 = db * wb;
+      const float dot = warp_sum(g1 * ha + g2 * hb) * (1.f / 64.f);
+      da = rstd * (g1 - ha * dot);
+      db = rstd * (g2 - hb * dot);
+    }
+    __nv_bfloat16* d = dsrc + static_cast<size_t>(t) * dsrc_ld + h * 64;
+    d[lane] = __float2bfloat16(da);
+    d[lane + 32] = __float2bfloat16(db);
+  }
+  if (dweight) {
+    atomicAdd(&s_dw[lane], dwa);
+    atomicAdd(&s_dw[lane + 32], dwb);
+    __syncthreads();
+    if (threadIdx.x < 64) atomicAdd(&dweight[threadIdx.x], s_dw[threadIdx.x]);
+  }
+}
+
+// --------------------------------------------------------------------------- SwiGLU
+// in: (rows, 2H) with the gate in columns [0,H) and the value in [H,2H); out (rows, H).
+__global__ void __launch_bounds__(256)
+swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ in, int in_ld, __nv_bfloat16* __restrict__ out,
+                  int out_ld, int rows, int H) {
+  const int nvec = H >> 3;
+  const long total = static_cast<long>(rows) * nvec;
+  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const int r = static_cast<int>(i / nvec);
+    const int v = static_cast<int>(i % nvec);
+    const uint4 g = *reinterpret_cast<const uint4*>(in + static_cast<size_t>(r) * in_ld + 8 * v);
+    const uint4 u = *reinterpret_cast<const uint4*>(in + static_cast<size_t>(r) * in_ld + H + 8 * v);
+    const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+    uint32_t ow[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 gf = unpack_bf16(gw[e]), uf = unpack_bf16(uw[e]);
+      const float s0 = gf.x / (1.f + __expf(-gf.x)), s1 = gf.y / (1.f + __expf(-gf.y));
+      ow[e] = pack_bf16(s0 * uf.x, s1 * uf.y);
+    }
+    *reinterpret_cast<uint4*>(out + static_cast<size_t>(r) * out_ld + 8 * v) =
+        make_uint4(ow[0], ow[1], ow[2], ow[3]);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ in, int in_ld,
+                  const __nv_bfloat16* __restrict__ dout, int dout_ld,
+                  __nv_bfloat16* __restrict__ din, int din_ld, int rows, int H) {
+  const int nvec = H >> 3;
+  const long total = static_cast<long>(rows) * nvec;
+  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const int r = static_cast<int>(i / nvec);
+    const int v = static_cast<int>(i % nvec);
+    const uint4 g = *reinterpret_cast<const uint4*>(in + static_cast<size_t>(r) * in_ld + 8 * v);
+    const uint4 u = *reinterpret_cast<const uint4*>(in + static_cast<size_t>(r) * in_ld + H + 8 * v);
+    const uint4 d = *reinterpret_cast<const uint4*>(dout + static_cast<size_t>(r) * dout_ld + 8 * v);
+    const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w},
+                   dw[4] = {d.x, d.y, d.z, d.w};
+    uint32_t og[4], ou[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 gf = unpack_bf16(gw[e]), uf = unpack_bf16(uw[e]), df = unpack_bf16(dw[e]);
+      const float sg0 = 1.f / (1.f + __expf(-gf.x)), sg1 = 1.f / (1.f + __expf(-gf.y));
+      const float si0 = gf.x * sg0, si1 = gf.y * sg1;
+      const float dg0 = df.x * uf.x * (sg0 * (1.f + gf.x * (1.f - sg0)));
+      const float dg1 = df.y * uf.y * (sg1 * (1.f + gf.y * (1.f - sg1)));
+      og[e] = pack_bf16(dg0, dg1);
+      ou[e] = pack_bf16(df.x * si0, df.y * si1);
+    }
+    *reinterpret_cast<uint4*>(din + static_cast<size_t>(r) * din_ld + 8 * v) =
+        make_uint4(og[0], og[1], og[2], og[3]);
+    *reinterpret_cast<uint4*>(din + static_cast<size_t>(r) * din_ld + H + 8 * v) =
+        make_uint4(ou[0], ou[1], ou[2], ou[3]);
+  }
+}
+
+static inline int grid_for(long work_items, int per_block, int cap = 148 * 8) {
+  long g = (work_items + per_block - 1) / per_block;
+  if (g < 1) g = 1;
+  if (g > cap) g = cap;
+  return static_cast<int>(g);
+}
+
+static inline int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_last_error("%s launch: %s", what, cudaGetErrorString(e));
+    return 11;
+  }
+  return 0;
+}
+
+}  // namespace kwu
+
+using namespace kwu;
+
+KWU_API int kwu_rmsnorm_fwd(const void* x, const void* res, const float* w, void* y, void* h_out,
+                            float* rstd, int rows, int cols, float eps, int one_plus, void* stream) {
+  if (cols % 8) { set_last_error("rmsnorm: cols must be a multiple of 8"); return 7; }
+  if (rows <= 0) return 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int grid = grid_for(rows, 8);
+  if (res)
+    rmsnorm_fwd_kernel<true><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)res, w,
+                                                  (__nv_bfloat16*)y, (__nv_bfloat16*)h_out, rstd, rows,
+                                                  cols, eps, one_plus);
+  else
+    rmsnorm_fwd_kernel<false><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, nullptr, w, (__nv_bfloat16*)y,
+                                                   nullptr, rstd, rows, cols, eps, one_plus);
+  return check_launch("rmsnorm_fwd");
+}
+
+// dw_partial: scratch of `kwu_rmsnorm_bwd_blocks(rows)` x cols floats (may be null when w is null).
+KWU_API int kwu_rmsnorm_bwd_blocks(int rows) { return grid_for(rows, 8, 296); }
+
+KWU_API int kwu_rmsnorm_bwd(const void* x, const float* w, const float* rstd, const void* dy,
+                            const void* dres, void* dx, float* dw, float* dw_partial, int rows,
+                            int cols, int one_plus, int accumulate_dw, void* stream) {
+  if (cols % 8) { set_last_error("rmsnorm: cols must be a multiple of 8"); return 7; }
+  if (rows <= 0) return 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int grid = grid_for(rows, 8, 296);
+  const bool want_dw = (w != nullptr && dw != nullptr && dw_partial != nullptr);
+  rmsnorm_bwd_kernel<<<grid, 256, want_dw ? cols * sizeof(float) : 0, st>>>(
+      (const __nv_bfloat16*)x, w, rstd, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)dres,
+      (__nv_bfloat16*)dx, want_dw ? dw_partial : nullptr, rows, cols, one_plus);
+  if (int rc = check_launch("rmsnorm_bwd")) return rc;
+  if (want_dw) {
+    colsum_partials_kernel<<<(cols + 255) / 256, 256, 0, st>>>(dw_partial, dw, grid, cols, accumulate_dw);
+    return check_launch("rmsnorm_dw");
+  }
+  return 0;
+}
+
+KWU_API int kwu_qknorm_rope_fwd(const void* src, int src_ld, void* dst, int dst_ld, const float* weight,
+                                const float* cos_t, const float* sin_t, int tokens, int heads,
+                                int head_dim, int rot_half, float eps, int do_norm, void* stream) {
+  if (head_dim != 64) { set_last_error("qknorm_rope: head_dim must be 64"); return 7; }
+  if (rot_half != 32 && rot_half != 16 && rot_half != 8 && rot_half != 0) {
+    set_last_error("qknorm_rope: rotary half must be 0, 8, 16 or 32");
+    return 7;
+  }
+  if (tokens <= 0) return 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int grid = grid_for(static_cast<long>(tokens) * heads, 8, 148 * 16);
+  qknorm_rope_fwd_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)src, src_ld, (__nv_bfloat16*)dst,
+                                              dst_ld, weight, cos_t, sin_t, tokens, heads, rot_half,
+                                              eps, do_norm);
+  return check_launch("qknorm_rope_fwd");
+}
+
+KWU_API int kwu_qknorm_rope_bwd(const void* src, int src_ld, const void* dout, int dout_ld, void* dsrc,
+                                int dsrc_ld, const float* weight, float* dweight, const float* cos_t,
+                                const float* sin_t, int tokens, int heads, int head_dim, int rot_half,
+                                float eps, int do_norm, void* stream) {
+  if (head_dim != 64) { set_last_error("qknorm_rope: head_dim must be 64"); return 7; }
+  if (tokens <= 0) return 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int grid = grid_for(static_cast<long>(tokens) * heads, 8, 148 * 4);
+  qknorm_rope_bwd_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)src, src_ld,
+                                              (const __nv_bfloat16*)dout, dout_ld, (__nv_bfloat16*)dsrc,
+                                              dsrc_ld, weight, dweight, cos_t, sin_t, tokens, heads,
+                                              rot_half, eps, do_norm);
+  return check_launch("qknorm_rope_bwd");
+}
+
+KWU_API int kwu_swiglu_fwd(const void* in, int in_ld, void* out, int out_ld, int rows, int H,
+                           void* stream) {
+  if (H % 8 || in_ld % 8 || out_ld % 8) { set_last_error("swiglu: H and pitches must be multiples of 8"); return 7; }
+  if (rows <= 0) return 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int grid = grid_for(static_cast<long>(rows) * (H / 8), 256);
+  swiglu_fwd_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)in, in_ld, (__nv_bfloat16*)out, out_ld,
+                                         rows, H);
+  return check_launch("swiglu_fwd");
+}
+
+KWU_API int kwu_swiglu_bwd(const void* in, int in_ld, const void* dout, int dout_ld, void* din,
+                           int din_ld, int rows, int H, void* stream) {
+  if (H % 8 || in_ld % 8 || dout_ld % 8 || din_ld % 8) { set_last_error("swiglu: H and pitches must be multiples of 8"); return 7; }
+  if (rows <= 0) return 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int grid = grid_for(static_cast<long>(rows) * (H / 8), 256);
+  swiglu_bwd_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)in, in_ld, (const __nv_bfloat16*)dout,
+                                         dout_ld, (__nv_bfloat16*)din, din_ld, rows, H);
+  return check_launch("swiglu_bwd");
+}

@@ -1,0 +1,400 @@
+// Persistent, warp-specialised bf16 GEMM on the 5th-generation tensor cores.
+//
+//   C[M,N] (+)= A * B      fp32 accumulation in TMEM, bf16 or fp32 output
+//
+// Operand storage (each operand independently):
+//   A "K-major":  A stored [M,K] row-major.      A "MN-major": A stored [K,M] row-major.
+//   B "K-major":  B stored [N,K] row-major.      B "MN-major": B stored [K,N] row-major.
+// so y = x W^T, dx = dy W and dW = dy^T x all run without a transpose pass.
+//
+// Structure of one CTA (192 threads, one CTA per SM, static round-robin tile schedule):
+//   warp 0      TMA producer: cp.async.bulk.tensor tiles into a 128B-swizzled smem ring
+//   warp 1      allocates TMEM; one lane issues tcgen05.mma and tcgen05.commit
+//   warps 2..5  epilogue: tcgen05.ld the finished accumulator, convert, store to global
+// Two TMEM accumulators let the epilogue of tile i overlap the main loop of tile i+1.
+// Takes the role of the cuBLAS calls behind nn.Linear in the reference
+// (src/kohakuwullm/models/components/attention.py:77-89, mlp.py:15-126).
+#include "common.cuh"
+
+#include <cstdio>
+#include <mutex>
+#include <unordered_map>
+
+namespace kwu {
+
+constexpr int GEMM_BM = 128;
+constexpr int GEMM_BK = 64;   // 64 bf16 = one 128-byte swizzle row
+constexpr int GEMM_THREADS = 192;
+
+struct GemmParams {
+  int M, N, K;
+  int ldc;
+  int out_fp32;     // 0: bf16 output, 1: fp32 output
+  int accumulate;   // 1: C += A*B (read-modify-write in the epilogue)
+  float alpha;      // scale applied to the product
+  // descriptor constants, computed on the host
+  uint32_t a_lbo, a_sbo, a_kadv;
+  uint32_t b_lbo, b_sbo, b_kadv;
+  uint32_t idesc;
+  int tiles_m, tiles_n;
+  int* status;
+};
+
+template <int BN>
+struct GemmSmem {
+  static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
+  static constexpr int B_BYTES = BN * GEMM_BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN >= 256) ? 4 : ((BN >= 192) ? 5 : 6);
+  static constexpr int BAR_BYTES = 1024;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // +1024 alignment slack
+};
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 void* __restrict__ Cout, const GemmParams p) {
+  using S = GemmSmem<BN>;
+  constexpr int STAGES = S::STAGES;
+  constexpr uint32_t TMEM_COLS = (2 * BN <= 256) ? 256 : 512;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* bar_area = smem + STAGES * S::STAGE_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_area);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* acc_full = empty_bar + STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int num_kb = (p.K + GEMM_BK - 1) / GEMM_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&acc_full[s], 1);
+      mbar_init(&acc_empty[s], 128);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile / p.tiles_n) * GEMM_BM;
+        const int n0 = (tile % p.tiles_n) * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * S::STAGE_BYTES;
+          uint8_t* sb = sa + S::A_BYTES;
+          mbar_expect_tx(&full_bar[stage], S::STAGE_BYTES);
+          const int k0 = kb * GEMM_BK;
+          if (!A_MN) {
+            tma_load_2d(sa, &tmA, &full_bar[stage], k0, m0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < GEMM_BM / 64; ++c)
+              tma_load_2d(sa + c * 8192, &tmA, &full_bar[stage], m0 + c * 64, k0);
+          }
+          if (!B_MN) {
+            tma_load_2d(sb, &tmB, &full_bar[stage], k0, n0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(sb + c * 8192, &tmB, &full_bar[stage], n0 + c * 64, k0);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+        const int as = it & 1;
+        const uint32_t aphase = (it >> 1) & 1;
+        if (!mbar_wait(&acc_empty[as], aphase ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_EMPTY)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + as * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * S::STAGE_BYTES);
+          const uint32_t sb = sa + S::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < GEMM_BK / 16; ++k) {
+            const uint64_t ad = make_smem_desc(sa + k * p.a_kadv, p.a_lbo, p.a_sbo, SWZ_128B);
+            const uint64_t bd = make_smem_desc(sb + k * p.b_kadv, p.b_lbo, p.b_sbo, SWZ_128B);
+            mma_f16_ss(d_tmem, ad, bd, p.idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(&empty_bar[stage]);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) tc_commit(&acc_full[as]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+    int it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+      const int as = it & 1;
+      const uint32_t aphase = (it >> 1) & 1;
+      const int m0 = (tile / p.tiles_n) * GEMM_BM;
+      const int n0 = (tile % p.tiles_n) * BN;
+      ok = mbar_wait(&acc_full[as], aphase, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_FULL);
+      ok = __all_sync(0xffffffffu, ok);  // the TMEM loads below are warp-collective
+      if (!ok) break;
+      tc_fence_after();
+      const int row = m0 + quarter * 32 + lane;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + as * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_x32(t_row + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (row < p.M && col0 < p.N) {
+          const bool full = (col0 + 32 <= p.N);
+          if (p.out_fp32) {
+            float* dst = reinterpret_cast<float*>(Cout) + static_cast<size_t>(row) * p.ldc + col0;
+            if (full) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                float4 v;
+                v.x = __uint_as_float(r[4 * j + 0]) * p.alpha;
+                v.y = __uint_as_float(r[4 * j + 1]) * p.alpha;
+                v.z = __uint_as_float(r[4 * j + 2]) * p.alpha;
+                v.w = __uint_as_float(r[4 * j + 3]) * p.alpha;
+                float4* d4 = reinterpret_cast<float4*>(dst) + j;
+                if (p.accumulate) {
+                  const float4 o = *d4;
+                  v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                }
+                *d4 = v;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                if (col0 + j < p.N) {
+                  float v = __uint_as_float(r[j]) * p.alpha;
+                  if (p.accumulate) v += dst[j];
+                  dst[j] = v;
+                }
+              }
+            }
+          } else {
+            __nv_bfloat16* dst =
+                reinterpret_cast<__nv_bfloat16*>(Cout) + static_cast<size_t>(row) * p.ldc + col0;
+            if (full) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float f[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[8 * j + e]) * p.alpha;
+                uint4* d4 = reinterpret_cast<uint4*>(dst) + j;
+                if (p.accumulate) {
+                  const uint4 o = *d4;
+                  const float2 o0 = unpack_bf16(o.x), o1 = unpack_bf16(o.y), o2 = unpack_bf16(o.z),
+                               o3 = unpack_bf16(o.w);
+                  f[0] += o0.x; f[1] += o0.y; f[2] += o1.x; f[3] += o1.y;
+                  f[4] += o2.x; f[5] += o2.y; f[6] += o3.x; f[7] += o3.y;
+                }
+                uint4 v;
+                v.x = pack_bf16(f[0], f[1]);
+                v.y = pack_bf16(f[2], f[3]);
+                v.z = pack_bf16(f[4], f[5]);
+                v.w = pack_bf16(f[6], f[7]);
+                *d4 = v;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                if (col0 + j < p.N) {
+                  float v = __uint_as_float(r[j]) * p.alpha;
+                  if (p.accumulate) v += __bfloat162float(dst[j]);
+                  dst[j] = __float2bfloat16(v);
+                }
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&acc_empty[as]);
+    }
+  }
+
+  // ---------------------------------------------------------------- tear-down
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // give copies that are still in flight time to land before the CTA's smem goes away
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------ host launcher
+static int g_num_sms = 0;
+static int num_sms() {
+  if (!g_num_sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (g_num_sms <= 0) g_num_sms = 148;
+  }
+  return g_num_sms;
+}
+
+struct DescOverride {
+  int active = 0;
+  uint32_t a_lbo, a_sbo, a_kadv, b_lbo, b_sbo, b_kadv;
+};
+static DescOverride g_override;
+
+template <int BN, bool A_MN, bool B_MN>
+static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb,
+                       int ldc, int out_fp32, int accumulate, float alpha, int max_ctas,
+                       cudaStream_t stream, int* status) {
+  using S = GemmSmem<BN>;
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!A_MN)
+    rc = encode_tmap_2d(&tmA, A, ELEM_BF16, M, K, lda, GEMM_BM, GEMM_BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  else
+    rc = encode_tmap_2d(&tmA, A, ELEM_BF16, K, M, lda, GEMM_BK, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return rc;
+  if (!B_MN)
+    rc = encode_tmap_2d(&tmB, B, ELEM_BF16, N, K, ldb, BN, GEMM_BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  else
+    rc = encode_tmap_2d(&tmB, B, ELEM_BF16, K, N, ldb, GEMM_BK, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return rc;
+
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc;
+  p.out_fp32 = out_fp32; p.accumulate = accumulate; p.alpha = alpha;
+  // K-major, 128B swizzle: rows are 128 B, 8-row groups 1024 B apart, K advances 32 B per MMA.
+  // MN-major, 128B swizzle: 64-element chunks along MN are whole 8 KB boxes, 8-row K groups are
+  // 1024 B apart, K advances 16 rows = 2048 B per MMA.
+  p.a_lbo = A_MN ? 8192 : 16; p.a_sbo = 1024; p.a_kadv = A_MN ? 2048 : 32;
+  p.b_lbo = B_MN ? 8192 : 16; p.b_sbo = 1024; p.b_kadv = B_MN ? 2048 : 32;
+  if (g_override.active) {
+    if (A_MN) { p.a_lbo = g_override.a_lbo; p.a_sbo = g_override.a_sbo; p.a_kadv = g_override.a_kadv; }
+    if (B_MN) { p.b_lbo = g_override.b_lbo; p.b_sbo = g_override.b_sbo; p.b_kadv = g_override.b_kadv; }
+  }
+  p.idesc = make_idesc_f16(GEMM_BM, BN, 1, A_MN ? 1 : 0, B_MN ? 1 : 0);
+  p.tiles_m = (M + GEMM_BM - 1) / GEMM_BM;
+  p.tiles_n = (N + BN - 1) / BN;
+  p.status = status;
+
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    if (e != cudaSuccess) {
+      set_last_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+      return 10;
+    }
+    attr_set = true;
+  }
+  int grid = p.tiles_m * p.tiles_n;
+  int cap = num_sms();
+  if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;
+  if (grid > cap) grid = cap;
+  kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, C, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_last_error("gemm launch: %s", cudaGetErrorString(e));
+    return 11;
+  }
+  return 0;
+}
+
+static int pick_bn(int M, int N, int forced) {
+  if (forced == 128 || forced == 256) return forced;
+  const int sms = num_sms();
+  const int tm = (M + GEMM_BM - 1) / GEMM_BM;
+  const long t256 = static_cast<long>(tm) * ((N + 255) / 256);
+  const long t128 = static_cast<long>(tm) * ((N + 127) / 128);
+  const long c256 = ((t256 + sms - 1) / sms) * 256;
+  const long c128 = ((t128 + sms - 1) / sms) * 128;
+  // a wide tile re-reads A half as often; prefer it unless the narrow one saves a real wave
+  return (c128 * 100 < c256 * 92) ? 128 : 256;
+}
+
+}  // namespace kwu
+
+// C[M,N] (+)= alpha * op(A) op(B). a_mn / b_mn select the storage described at the top of the file.
+// lda/ldb/ldc are row pitches in elements of the STORED matrices. bn: 0 = choose, 128 or 256.
+KWU_API int kwu_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb,
+                          int ldc, int a_mn, int b_mn, int out_fp32, int accumulate, float alpha,
+                          int bn, int max_ctas, void* stream, int* status) {
+  using namespace kwu;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int BN = pick_bn(M, N, bn);
+#define KWU_GEMM_CASE(bnv, amn, bmn)                                                              \
+  if (BN == bnv && a_mn == amn && b_mn == bmn)                                                    \
+    return launch_gemm<bnv, amn != 0, bmn != 0>(A, B, C, M, N, K, lda, ldb, ldc, out_fp32,        \
+                                                accumulate, alpha, max_ctas, st, status);
+  KWU_GEMM_CASE(128, 0, 0) KWU_GEMM_CASE(128, 0, 1) KWU_GEMM_CASE(128, 1, 0) KWU_GEMM_CASE(128, 1, 1)
+  KWU_GEMM_CASE(256, 0, 0) KWU_GEMM_CASE(256, 0, 1) KWU_GEMM_CASE(256, 1, 0) KWU_GEMM_CASE(256, 1, 1)
+#undef KWU_GEMM_CASE
+  set_last_error("kwu_gemm_bf16: unsupported variant");
+  return 20;
+}
+
+// Test hook: override the MN-major descriptor constants (used once to pin the layout rules).
+KWU_API void kwu_gemm_debug_override(int active, unsigned a_lbo, unsigned a_sbo, unsigned a_kadv,
+                                     unsigned b_lbo, unsigned b_sbo, unsigned b_kadv) {
+  kwu::g_override.active = active;
+  kwu::g_override.a_lbo = a_lbo; kwu::g_override.a_sbo = a_sbo; kwu::g_override.a_kadv = a_kadv;
+  kwu::g_override.b_lbo = b_lbo; kwu::g_override.b_sbo = b_sbo; kwu::g_override.b_kadv = b_kadv;
+}
