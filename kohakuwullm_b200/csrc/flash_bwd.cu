@@ -1,0 +1,487 @@
+// Varlen causal / sliding-window flash attention backward for head_dim 64, bf16, on tcgen05.
+//
+// Three launches, no atomics, deterministic:
+//   1. delta[h,t] = sum_d out[t,h,d] * dout[t,h,d]
+//   2. dK/dV kernel: one CTA per (128-key tile, kv head). Scores are formed TRANSPOSED
+//      (S^T = K Q^T, dP^T = V dO^T, keys on the TMEM lanes) so that P^T and dS^T are directly the
+//      A operands of dV += P^T dO and dK += dS^T Q. The CTA loops over every query head of its GQA
+//      group and every 64-query tile that can see the key tile, accumulating in TMEM.
+//   3. dQ kernel: one CTA per (128-query tile, query head), loops over 64-key tiles:
+//      S = Q K^T, dP = dO V^T, dS = P o (dP - delta) * scale written to TMEM as bf16,
+//      dQ += dS K accumulated in TMEM.
+// The stored lse already contains the sink term, so P = exp(S*scale - lse) is the sink-aware
+// probability and nothing else changes (sink columns carry a zero value).
+// Replaces src/kohakuwullm/kernels/attention/flash_attn_bwd.py:16-348 of the reference (which
+// accumulates GQA groups with fp32 atomics).
+#include "common.cuh"
+
+namespace kwu {
+
+constexpr int FB_D = 64;
+constexpr int FB_THREADS = 192;
+constexpr float FB_LOG2E = 1.4426950408889634f;
+
+// ------------------------------------------------------------------------------------ delta
+__global__ void __launch_bounds__(256)
+flash_delta_kernel(const __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ dout,
+                   float* __restrict__ delta, int T, int Hq) {
+  // one warp per (t, h) row of 64: two elements per lane
+  const int lane = threadIdx.x & 31;
+  const long total = static_cast<long>(T) * Hq;
+  const int wpb = blockDim.x >> 5;
+  for (long r = static_cast<long>(blockIdx.x) * wpb + (threadIdx.x >> 5); r < total;
+       r += static_cast<long>(gridDim.x) * wpb) {
+    const uint32_t a = reinterpret_cast<const uint32_t*>(out + r * 64)[lane];
+    const uint32_t b = reinterpret_cast<const uint32_t*>(dout + r * 64)[lane];
+    const float2 fa = unpack_bf16(a), fb = unpack_bf16(b);
+    const float s = warp_sum(fa.x * fb.x + fa.y * fb.y);
+    if (lane == 0) {
+      const int t = static_cast<int>(r / Hq), h = static_cast<int>(r % Hq);
+      delta[static_cast<size_t>(h) * T + t] = s;
+    }
+  }
+}
+
+struct FlashBwdParams {
+  const float* lse;     // (Hq, T), natural log, sink term included
+  const float* delta;   // (Hq, T)
+  __nv_bfloat16* dq;    // (T, Hq, 64)
+  __nv_bfloat16* dk;    // (T, Hkv, 64)
+  __nv_bfloat16* dv;    // (T, Hkv, 64)
+  const int4* plan;
+  int T, Hq, Hkv, window;
+  float scale;
+  int* status;
+};
+
+// ------------------------------------------------------------------------------------ dK / dV
+// smem: K tile 16 KB, V tile 16 KB, 2 stages x (Q 8 KB + dO 8 KB).
+constexpr int FBK_SMEM = 2 * 16384 + 2 * 16384 + 1024 + 1024;
+
+__global__ void __launch_bounds__(FB_THREADS, 2)
+flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_constant__ CUtensorMap tmDO64,
+                      const __grid_constant__ CUtensorMap tmK128, const __grid_constant__ CUtensorMap tmV128,
+                      const FlashBwdParams p) {
+  const int4 job = p.plan[blockIdx.x];
+  if (!job.w) return;
+  const int kv0 = job.x, de = job.z;
+  const int hk = blockIdx.y;
+  const int group = p.Hq / p.Hkv;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = smem + 16384;
+  uint8_t* sQ = smem + 32768;           // 2 stages x 8 KB
+  uint8_t* sDO = smem + 32768 + 16384;  // 2 stages x 8 KB
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 65536);
+  uint64_t* kv_full = bars + 0;
+  uint64_t* qd_full = bars + 1;   // [2]
+  uint64_t* qd_empty = bars + 3;  // [2]
+  uint64_t* sdp_full = bars + 5;
+  uint64_t* p_ready = bars + 6;
+  uint64_t* acc_done = bars + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int q_begin = kv0;
+  int q_end = de;
+  if (p.window > 0) q_end = min(de, kv0 + 127 + p.window);
+  const int n_q = (q_end - q_begin + 63) / 64;
+  const int n_it = n_q * group;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&qd_full[s], 1);
+      mbar_init(&qd_empty[s], 1);
+    }
+    mbar_init(sdp_full, 1);
+    mbar_init(p_ready, 128);
+    mbar_init(acc_done, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base, tDP = tmem_base + 64, tDV = tmem_base + 128, tDK = tmem_base + 192;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      mbar_expect_tx(kv_full, 32768);
+      tma_load_2d(sK, &tmK128, kv_full, hk * FB_D, kv0);
+      tma_load_2d(sV, &tmV128, kv_full, hk * FB_D, kv0);
+      for (int it = 0; it < n_it; ++it) {
+        const int s = it & 1;
+        const uint32_t ph = (it >> 1) & 1;
+        const int h = hk * group + it / n_q;
+        const int q_lo = q_begin + (it % n_q) * 64;
+        if (!mbar_wait(&qd_empty[s], ph ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_EMPTY)) break;
+        mbar_expect_tx(&qd_full[s], 16384);
+        tma_load_2d(sQ + s * 8192, &tmQ64, &qd_full[s], h * FB_D, q_lo);
+        tma_load_2d(sDO + s * 8192, &tmDO64, &qd_full[s], h * FB_D, q_lo);
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc_f16(128, 64, 1, 0, 0);   // S^T, dP^T: N = 64 queries
+      const uint32_t idesc_a = make_idesc_f16(128, 64, 1, 0, 1);   // dV, dK: B is MN-major
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV);
+      bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int s = it & 1;
+        const uint32_t ph = (it >> 1) & 1;
+        ok = mbar_wait(&qd_full[s], ph, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t bQ = smem_u32(sQ + s * 8192), bDO = smem_u32(sDO + s * 8192);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          mma_f16_ss(tS, make_smem_desc(aK + k * 32, 16, 1024, SWZ_128B),
+                     make_smem_desc(bQ + k * 32, 16, 1024, SWZ_128B), idesc_s, k > 0 ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          mma_f16_ss(tDP, make_smem_desc(aV + k * 32, 16, 1024, SWZ_128B),
+                     make_smem_desc(bDO + k * 32, 16, 1024, SWZ_128B), idesc_s, k > 0 ? 1u : 0u);
+        tc_commit(sdp_full);
+        ok = mbar_wait(p_ready, it & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_MISC);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          mma_f16_ts(tDV, tS + k * 8, make_smem_desc(bDO + k * 2048, 8192, 1024, SWZ_128B), idesc_a,
+                     (it > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          mma_f16_ts(tDK, tDP + k * 8, make_smem_desc(bQ + k * 2048, 8192, 1024, SWZ_128B), idesc_a,
+                     (it > 0 || k > 0) ? 1u : 0u);
+        tc_commit(&qd_empty[s]);
+      }
+      if (ok) tc_commit(acc_done);
+    }
+  } else {
+    const int row = warp * 32 + lane;
+    const int kj = kv0 + row;
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    const float c_log2 = p.scale * FB_LOG2E;
+    bool ok = true;
+    for (int it = 0; it < n_it; ++it) {
+      const int h = hk * group + it / n_q;
+      const int q_lo = q_begin + (it % n_q) * 64;
+      const float* lse_h = p.lse + static_cast<size_t>(h) * p.T;
+      const float* dl_h = p.delta + static_cast<size_t>(h) * p.T;
+      ok = mbar_wait(sdp_full, it & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_FULL);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t sv[32], dp[32], pp[16], dd[16];
+        tmem_ld_x32(tS + lane_addr + c * 32, sv);
+        tmem_ld_x32(tDP + lane_addr + c * 32, dp);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float pr[2], dsv[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int qi = q_lo + c * 32 + e + u;
+            const bool valid = (qi < q_end) && (kj <= qi) && (kj < de) &&
+                               (p.window <= 0 || qi - kj < p.window);
+            const int qc = min(qi, p.T - 1);
+            const float lse_q = lse_h[qc] * FB_LOG2E;
+            const float dl_q = dl_h[qc];
+            const float pv = valid ? exp2f(__uint_as_float(sv[e + u]) * c_log2 - lse_q) : 0.f;
+            pr[u] = pv;
+            dsv[u] = pv * (__uint_as_float(dp[e + u]) - dl_q) * p.scale;
+          }
+          pp[e / 2] = pack_bf16(pr[0], pr[1]);
+          dd[e / 2] = pack_bf16(dsv[0], dsv[1]);
+        }
+        // P^T / dS^T as bf16 overwrite the first half of the columns that were just read
+        tmem_st_x16(tS + lane_addr + c * 16, pp);
+        tmem_st_x16(tDP + lane_addr + c * 16, dd);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(p_ready);
+    }
+    if (ok) {
+      ok = mbar_wait(acc_done, 0, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_FULL);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after();
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        uint32_t o[64];
+        const uint32_t src = (which == 0 ? tDV : tDK) + lane_addr;
+        tmem_ld_x32(src, o);
+        tmem_ld_x32(src + 32, o + 32);
+        tmem_ld_wait();
+        if (kj < de) {
+          __nv_bfloat16* base = (which == 0 ? p.dv : p.dk) + (static_cast<size_t>(kj) * p.Hkv + hk) * FB_D;
+          uint4* dst = reinterpret_cast<uint4*>(base);
+#pragma unroll
+          for (int v = 0; v < 8; ++v) {
+            uint4 w;
+            w.x = pack_bf16(__uint_as_float(o[8 * v + 0]), __uint_as_float(o[8 * v + 1]));
+            w.y = pack_bf16(__uint_as_float(o[8 * v + 2]), __uint_as_float(o[8 * v + 3]));
+            w.z = pack_bf16(__uint_as_float(o[8 * v + 4]), __uint_as_float(o[8 * v + 5]));
+            w.w = pack_bf16(__uint_as_float(o[8 * v + 6]), __uint_as_float(o[8 * v + 7]));
+            dst[v] = w;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag)
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 256);
+  }
+}
+
+// ------------------------------------------------------------------------------------ dQ
+// smem: Q 16 KB, dO 16 KB, 2 stages x (K 8 KB + V 8 KB).
+constexpr int FBQ_SMEM = 2 * 16384 + 2 * 16384 + 1024 + 1024;
+
+__global__ void __launch_bounds__(FB_THREADS, 2)
+flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_constant__ CUtensorMap tmDO128,
+                    const __grid_constant__ CUtensorMap tmK64, const __grid_constant__ CUtensorMap tmV64,
+                    const FlashBwdParams p) {
+  const int4 job = p.plan[blockIdx.x];
+  if (!job.w) return;
+  const int q0 = job.x, ds = job.y, de = job.z;
+  const int h = blockIdx.y;
+  const int hk = h / (p.Hq / p.Hkv);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sDO = smem + 16384;
+  uint8_t* sK = smem + 32768;           // 2 stages x 8 KB
+  uint8_t* sV = smem + 32768 + 16384;   // 2 stages x 8 KB
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 65536);
+  uint64_t* q_full = bars + 0;
+  uint64_t* kv_full = bars + 1;   // [2]
+  uint64_t* kv_empty = bars + 3;  // [2]
+  uint64_t* sdp_full = bars + 5;
+  uint64_t* p_ready = bars + 6;
+  uint64_t* acc_done = bars + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int q_hi = min(q0 + 128, de);
+  int lo = ds;
+  if (p.window > 0) lo = max(ds, q0 - p.window + 1);
+  const int n_kv = (q_hi - lo + 63) / 64;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    mbar_init(sdp_full, 1);
+    mbar_init(p_ready, 128);
+    mbar_init(acc_done, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base, tDP = tmem_base + 64, tDQ = tmem_base + 128;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, 32768);
+      tma_load_2d(sQ, &tmQ128, q_full, h * FB_D, q0);
+      tma_load_2d(sDO, &tmDO128, q_full, h * FB_D, q0);
+      for (int j = 0; j < n_kv; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&kv_empty[s], ph ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_EMPTY)) break;
+        mbar_expect_tx(&kv_full[s], 16384);
+        tma_load_2d(sK + s * 8192, &tmK64, &kv_full[s], hk * FB_D, lo + j * 64);
+        tma_load_2d(sV + s * 8192, &tmV64, &kv_full[s], hk * FB_D, lo + j * 64);
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc_f16(128, 64, 1, 0, 0);
+      const uint32_t idesc_q = make_idesc_f16(128, 64, 1, 0, 1);
+      const uint32_t aQ = smem_u32(sQ), aDO = smem_u32(sDO);
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        ok = mbar_wait(&kv_full[s], ph, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t bK = smem_u32(sK + s * 8192), bV = smem_u32(sV + s * 8192);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          mma_f16_ss(tS, make_smem_desc(aQ + k * 32, 16, 1024, SWZ_128B),
+                     make_smem_desc(bK + k * 32, 16, 1024, SWZ_128B), idesc_s, k > 0 ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          mma_f16_ss(tDP, make_smem_desc(aDO + k * 32, 16, 1024, SWZ_128B),
+                     make_smem_desc(bV + k * 32, 16, 1024, SWZ_128B), idesc_s, k > 0 ? 1u : 0u);
+        tc_commit(sdp_full);
+        ok = mbar_wait(p_ready, j & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_MISC);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          mma_f16_ts(tDQ, tS + k * 8, make_smem_desc(bK + k * 2048, 8192, 1024, SWZ_128B), idesc_q,
+                     (j > 0 || k > 0) ? 1u : 0u);
+        tc_commit(&kv_empty[s]);
+      }
+      if (ok) tc_commit(acc_done);
+    }
+  } else {
+    const int row = warp * 32 + lane;
+    const int qi = q0 + row;
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    const float c_log2 = p.scale * FB_LOG2E;
+    const int qc = min(qi, p.T - 1);
+    const float lse_q = p.lse[static_cast<size_t>(h) * p.T + qc] * FB_LOG2E;
+    const float dl_q = p.delta[static_cast<size_t>(h) * p.T + qc];
+    bool ok = true;
+    for (int j = 0; j < n_kv; ++j) {
+      const int kv0 = lo + j * 64;
+      ok = mbar_wait(sdp_full, j & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_FULL);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t sv[32], dp[32], dd[16];
+        tmem_ld_x32(tS + lane_addr + c * 32, sv);
+        tmem_ld_x32(tDP + lane_addr + c * 32, dp);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float dsv[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int kj = kv0 + c * 32 + e + u;
+            const bool valid = (qi < q_hi) && (kj <= qi) && (p.window <= 0 || qi - kj < p.window);
+            const float pv = valid ? exp2f(__uint_as_float(sv[e + u]) * c_log2 - lse_q) : 0.f;
+            dsv[u] = pv * (__uint_as_float(dp[e + u]) - dl_q) * p.scale;
+          }
+          dd[e / 2] = pack_bf16(dsv[0], dsv[1]);
+        }
+        tmem_st_x16(tS + lane_addr + c * 16, dd);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(p_ready);
+    }
+    if (ok) {
+      ok = mbar_wait(acc_done, 0, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_FULL);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      tc_fence_after();
+      uint32_t o[64];
+      tmem_ld_x32(tDQ + lane_addr, o);
+      tmem_ld_x32(tDQ + lane_addr + 32, o + 32);
+      tmem_ld_wait();
+      if (qi < q_hi) {
+        uint4* dst = reinterpret_cast<uint4*>(p.dq + (static_cast<size_t>(qi) * p.Hq + h) * FB_D);
+#pragma unroll
+        for (int v = 0; v < 8; ++v) {
+          uint4 w;
+          w.x = pack_bf16(__uint_as_float(o[8 * v + 0]), __uint_as_float(o[8 * v + 1]));
+          w.y = pack_bf16(__uint_as_float(o[8 * v + 2]), __uint_as_float(o[8 * v + 3]));
+          w.z = pack_bf16(__uint_as_float(o[8 * v + 4]), __uint_as_float(o[8 * v + 5]));
+          w.w = pack_bf16(__uint_as_float(o[8 * v + 6]), __uint_as_float(o[8 * v + 7]));
+          dst[v] = w;
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag)
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 256);
+  }
+}
+
+}  // namespace kwu
+
+using namespace kwu;
+
+KWU_API int kwu_flash_bwd(const void* q, int q_ld, const void* k, int k_ld, const void* v, int v_ld,
+                          const void* out, const void* dout, const float* lse, float* delta,
+                          void* dq, void* dk, void* dv, const void* plan,
+                          int n_tiles, int T, int Hq, int Hkv, int window, float scale, void* stream,
+                          int* status) {
+  if (T <= 0 || n_tiles <= 0) return 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  {
+    long rows = static_cast<long>(T) * Hq;
+    long g = (rows + 7) / 8;
+    if (g > 148 * 16) g = 148 * 16;
+    flash_delta_kernel<<<static_cast<int>(g), 256, 0, st>>>((const __nv_bfloat16*)out,
+                                                          (const __nv_bfloat16*)dout, delta, T, Hq);
+  }
+  CUtensorMap tmQ64, tmDO64, tmK128, tmV128, tmQ128, tmDO128, tmK64, tmV64;
+  int rc;
+  const uint64_t wq = (uint64_t)Hq * FB_D, wk = (uint64_t)Hkv * FB_D;
+  const int SW = CU_TENSOR_MAP_SWIZZLE_128B;
+  if ((rc = encode_tmap_2d(&tmQ64, q, ELEM_BF16, T, wq, q_ld, 64, 64, SW))) return rc;
+  if ((rc = encode_tmap_2d(&tmDO64, dout, ELEM_BF16, T, wq, wq, 64, 64, SW))) return rc;
+  if ((rc = encode_tmap_2d(&tmK128, k, ELEM_BF16, T, wk, k_ld, 128, 64, SW))) return rc;
+  if ((rc = encode_tmap_2d(&tmV128, v, ELEM_BF16, T, wk, v_ld, 128, 64, SW))) return rc;
+  if ((rc = encode_tmap_2d(&tmQ128, q, ELEM_BF16, T, wq, q_ld, 128, 64, SW))) return rc;
+  if ((rc = encode_tmap_2d(&tmDO128, dout, ELEM_BF16, T, wq, wq, 128, 64, SW))) return rc;
+  if ((rc = encode_tmap_2d(&tmK64, k, ELEM_BF16, T, wk, k_ld, 64, 64, SW))) return rc;
+  if ((rc = encode_tmap_2d(&tmV64, v, ELEM_BF16, T, wk, v_ld, 64, 64, SW))) return rc;
+  static bool attr = false;
+  if (!attr) {
+    cudaError_t e1 = cudaFuncSetAttribute(flash_bwd_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FBK_SMEM);
+    cudaError_t e2 = cudaFuncSetAttribute(flash_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FBQ_SMEM);
+    if (e1 != cudaSuccess || e2 != cudaSuccess) { set_last_error("flash_bwd attr failed"); return 10; }
+    attr = true;
+  }
+  FlashBwdParams p;
+  p.lse = lse; p.delta = delta;
+  p.dq = (__nv_bfloat16*)dq; p.dk = (__nv_bfloat16*)dk; p.dv = (__nv_bfloat16*)dv;
+  p.plan = reinterpret_cast<const int4*>(plan);
+  p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.window = window; p.scale = scale; p.status = status;
+  flash_bwd_dkdv_kernel<<<dim3(n_tiles, Hkv), FB_THREADS, FBK_SMEM, st>>>(tmQ64, tmDO64, tmK128, tmV128, p);
+  flash_bwd_dq_kernel<<<dim3(n_tiles, Hq), FB_THREADS, FBQ_SMEM, st>>>(tmQ128, tmDO128, tmK64, tmV64, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { set_last_error("flash_bwd launch: %s", cudaGetErrorString(e)); return 11; }
+  return 0;
+}

@@ -1,0 +1,370 @@
+// Varlen causal / sliding-window flash attention forward for head_dim 64, bf16, on tcgen05.
+//
+// One CTA per (128-row query tile, query head). Roles:
+//   warps 0..3  softmax: thread r owns query row r; reads S from TMEM, online softmax in fp32,
+//               writes P (bf16) back to TMEM, rescales the O accumulator when the row max moves
+//   warp 4      TMA producer: Q once, then K and V tiles through two-stage rings
+//   warp 5      issues tcgen05.mma:  S = Q K^T (smem x smem)  and  O += P V (TMEM x smem)
+// TMEM columns: S [0,128) fp32, P [128,192) packed bf16, O [192,256) fp32. Two CTAs fit per SM, so
+// one CTA's softmax overlaps the other's tensor-core work.
+//
+// Documents never attend across their boundary: a tile's key range is clipped to its own document
+// and (with a window) to the last `window` positions. Sinks enter as sink_lse[h] = logsumexp of the
+// head's sink logits: the stored lse is logaddexp(lse, sink_lse) and the output is scaled to match.
+// Replaces src/kohakuwullm/kernels/attention/flash_attn_fwd.py:35-154 and the vendor FA2 call at
+// src/kohakuwullm/models/components/attention.py:170-188 of the reference.
+#include "common.cuh"
+
+namespace kwu {
+
+constexpr int FA_BM = 128;   // query rows per CTA
+constexpr int FA_BN = 128;   // keys per tile
+constexpr int FA_D = 64;
+constexpr int FA_THREADS = 192;
+constexpr int FA_TILE_BYTES = 128 * 64 * 2;  // 16 KB
+constexpr int FA_SMEM = 5 * FA_TILE_BYTES + 1024 + 1024;
+constexpr float FA_NEG = -1.0e30f;
+
+struct FlashFwdParams {
+  __nv_bfloat16* out;   // (T, Hq, 64)
+  float* lse;           // (Hq, T)
+  const int4* plan;     // (q0, doc_start, doc_end, valid)
+  int T, Hq, Hkv, window;
+  const float* sink_lse;  // (Hq) or null
+  float scale_log2;       // softmax scale * log2(e)
+  int* status;
+};
+
+// Tile list for packed batches: for every document, ceil(len/tile) entries.
+__global__ void attn_plan_kernel(const int* __restrict__ cu, int ndocs, int tile, int4* __restrict__ plan,
+                                 int max_tiles) {
+  // one block; thread t handles documents t, t+blockDim, ... after an exclusive scan of tile counts
+  extern __shared__ int s_off[];  // ndocs + 1
+  for (int d = threadIdx.x; d < ndocs; d += blockDim.x) {
+    const int len = cu[d + 1] - cu[d];
+    s_off[d + 1] = (len + tile - 1) / tile;
+  }
+  if (threadIdx.x == 0) s_off[0] = 0;
+  __syncthreads();
+  if (threadIdx.x == 0)
+    for (int d = 0; d < ndocs; ++d) s_off[d + 1] += s_off[d];
+  __syncthreads();
+  const int used = s_off[ndocs];
+  for (int d = threadIdx.x; d < ndocs; d += blockDim.x) {
+    const int s = cu[d], e = cu[d + 1];
+    int idx = s_off[d];
+    for (int q0 = s; q0 < e && idx < max_tiles; q0 += tile, ++idx) plan[idx] = make_int4(q0, s, e, 1);
+  }
+  for (int i = used + threadIdx.x; i < max_tiles; i += blockDim.x) plan[i] = make_int4(0, 0, 0, 0);
+}
+
+__global__ void __launch_bounds__(FA_THREADS, 2)
+flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const FlashFwdParams p) {
+  const int4 job = p.plan[blockIdx.x];
+  if (!job.w) return;
+  const int q0 = job.x, ds = job.y, de = job.z;
+  const int h = blockIdx.y;
+  const int hk = h / (p.Hq / p.Hkv);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = smem + FA_TILE_BYTES;       // 2 stages
+  uint8_t* sV = smem + 3 * FA_TILE_BYTES;   // 2 stages
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 5 * FA_TILE_BYTES);
+  uint64_t* q_full = bars + 0;
+  uint64_t* k_full = bars + 1;   // [2]
+  uint64_t* k_empty = bars + 3;  // [2]
+  uint64_t* v_full = bars + 5;   // [2]
+  uint64_t* v_empty = bars + 7;  // [2]
+  uint64_t* s_full = bars + 9;
+  uint64_t* p_full = bars + 10;
+  uint64_t* o_done = bars + 11;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // key range of this tile
+  const int q_hi = min(q0 + FA_BM, de);           // one past the last valid query row
+  int lo = ds;
+  if (p.window > 0) lo = max(ds, q0 - p.window + 1);
+  const int n_kv = (q_hi - lo + FA_BN - 1) / FA_BN;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 128);
+    mbar_init(o_done, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base, tP = tmem_base + 128, tO = tmem_base + 192;
+
+  if (warp == 4) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tmQ);
+      tma_prefetch_desc(&tmK);
+      tma_prefetch_desc(&tmV);
+      mbar_expect_tx(q_full, FA_TILE_BYTES);
+      tma_load_2d(sQ, &tmQ, q_full, h * FA_D, q0);
+      for (int j = 0; j < n_kv; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        const int kv0 = lo + j * FA_BN;
+        if (!mbar_wait(&k_empty[s], ph ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_EMPTY)) break;
+        mbar_expect_tx(&k_full[s], FA_TILE_BYTES);
+        tma_load_2d(sK + s * FA_TILE_BYTES, &tmK, &k_full[s], hk * FA_D, kv0);
+        if (!mbar_wait(&v_empty[s], ph ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_EMPTY)) break;
+        mbar_expect_tx(&v_full[s], FA_TILE_BYTES);
+        tma_load_2d(sV + s * FA_TILE_BYTES, &tmV, &v_full[s], hk * FA_D, kv0);
+      }
+    }
+  } else if (warp == 5) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc_f16(128, 128, 1, 0, 0);
+      const uint32_t idesc_o = make_idesc_f16(128, 64, 1, 0, 1);
+      const uint32_t aQ = smem_u32(sQ);
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
+      auto issue_s = [&](int j) {
+        const int s = j & 1;
+        const uint32_t bK = smem_u32(sK + s * FA_TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < FA_D / 16; ++k)
+          mma_f16_ss(tS, make_smem_desc(aQ + k * 32, 16, 1024, SWZ_128B),
+                     make_smem_desc(bK + k * 32, 16, 1024, SWZ_128B), idesc_s, k > 0 ? 1u : 0u);
+        tc_commit(s_full);
+        tc_commit(&k_empty[s]);
+      };
+      if (ok) ok = mbar_wait(&k_full[0], 0, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0);
+      }
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (j + 1 < n_kv) {
+          ok = mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
+          if (!ok) break;
+        }
+        // P_j written (and S_j fully read) by the softmax warps
+        ok = mbar_wait(p_full, j & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_MISC);
+        if (!ok) break;
+        tc_fence_after();
+        if (j + 1 < n_kv) issue_s(j + 1);
+        ok = mbar_wait(&v_full[s], ph, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t bV = smem_u32(sV + s * FA_TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < FA_BN / 16; ++k)
+          mma_f16_ts(tO, tP + k * 8, make_smem_desc(bV + k * 2048, 8192, 1024, SWZ_128B), idesc_o,
+                     (j > 0 || k > 0) ? 1u : 0u);
+        tc_commit(o_done);
+        tc_commit(&v_empty[s]);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax (warps 0..3)
+    const int row = warp * 32 + lane;        // query row inside the tile == TMEM lane
+    const int qi = q0 + row;
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    float m = FA_NEG, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_kv; ++j) {
+      const int kv0 = lo + j * FA_BN;
+      ok = mbar_wait(s_full, j & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_FULL);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const bool need_mask = (kv0 + FA_BN - 1 > q0) || (p.window > 0 && (q0 + FA_BM - 1 - kv0) >= p.window);
+      // pass 1: row maximum
+      float mx = m;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_x32(tS + lane_addr + c * 32, r);
+        tmem_ld_wait();
+        if (need_mask) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const int kj = kv0 + c * 32 + e;
+            const bool valid = (kj <= qi) && (p.window <= 0 || qi - kj < p.window);
+            const float sv = valid ? __uint_as_float(r[e]) * p.scale_log2 : FA_NEG;
+            mx = fmaxf(mx, sv);
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(r[e]) * p.scale_log2);
+        }
+      }
+      const float alpha = exp2f(m - mx);
+      m = mx;
+      // pass 2: probabilities, packed to bf16
+      uint32_t pk[64];
+      float sum = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_x32(tS + lane_addr + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float s0 = __uint_as_float(r[e]) * p.scale_log2;
+          float s1 = __uint_as_float(r[e + 1]) * p.scale_log2;
+          if (need_mask) {
+            const int kj = kv0 + c * 32 + e;
+            const bool v0 = (kj <= qi) && (p.window <= 0 || qi - kj < p.window);
+            const bool v1 = (kj + 1 <= qi) && (p.window <= 0 || qi - kj - 1 < p.window);
+            s0 = v0 ? s0 : FA_NEG;
+            s1 = v1 ? s1 : FA_NEG;
+          }
+          const float p0 = exp2f(s0 - m), p1 = exp2f(s1 - m);
+          sum += p0 + p1;
+          pk[c * 16 + e / 2] = pack_bf16(p0, p1);
+        }
+      }
+      l = l * alpha + sum;
+      // the previous P V product must be complete before P is overwritten and O is touched
+      if (j > 0) {
+        ok = mbar_wait(o_done, (j - 1) & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_EMPTY);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            uint32_t o[32];
+            tmem_ld_x32(tO + lane_addr + c * 32, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+            tmem_st_x32(tO + lane_addr + c * 32, o);
+          }
+        }
+      }
+      tmem_st_x32(tP + lane_addr, pk);
+      tmem_st_x32(tP + lane_addr + 32, pk + 32);
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(p_full);
+    }
+    // ---------------------------------------------------------------- epilogue
+    if (ok && n_kv > 0) {
+      ok = mbar_wait(o_done, (n_kv - 1) & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_FULL);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok && n_kv > 0) {
+      tc_fence_after();
+      float lse = (m + log2f(l)) * 0.6931471805599453f;  // natural log
+      float inv = 1.f / l;
+      if (p.sink_lse) {
+        const float sl = p.sink_lse[h];
+        const float tot = fmaxf(lse, sl) + log1pf(__expf(-fabsf(lse - sl)));
+        inv *= __expf(lse - tot);
+        lse = tot;
+      }
+      uint32_t o[64];
+      tmem_ld_x32(tO + lane_addr, o);
+      tmem_ld_x32(tO + lane_addr + 32, o + 32);
+      tmem_ld_wait();
+      if (qi < q_hi) {
+        uint4* dst = reinterpret_cast<uint4*>(p.out + (static_cast<size_t>(qi) * p.Hq + h) * FA_D);
+#pragma unroll
+        for (int v = 0; v < 8; ++v) {
+          uint4 w;
+          w.x = pack_bf16(__uint_as_float(o[8 * v + 0]) * inv, __uint_as_float(o[8 * v + 1]) * inv);
+          w.y = pack_bf16(__uint_as_float(o[8 * v + 2]) * inv, __uint_as_float(o[8 * v + 3]) * inv);
+          w.z = pack_bf16(__uint_as_float(o[8 * v + 4]) * inv, __uint_as_float(o[8 * v + 5]) * inv);
+          w.w = pack_bf16(__uint_as_float(o[8 * v + 6]) * inv, __uint_as_float(o[8 * v + 7]) * inv);
+          dst[v] = w;
+        }
+        p.lse[static_cast<size_t>(h) * p.T + qi] = lse;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag)
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 256);
+  }
+}
+
+}  // namespace kwu
+
+using namespace kwu;
+
+KWU_API int kwu_attn_plan(const int* cu_seqlens, int ndocs, int tile, void* plan, int max_tiles,
+                          void* stream) {
+  if (ndocs <= 0 || max_tiles <= 0) return 0;
+  if ((ndocs + 1) * sizeof(int) > 96 * 1024) {
+    set_last_error("attn_plan: too many documents (%d)", ndocs);
+    return 7;
+  }
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  static bool attr = false;
+  const size_t smem = (ndocs + 1) * sizeof(int);
+  if (!attr && smem > 48 * 1024) {
+    cudaFuncSetAttribute(attn_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    attr = true;
+  }
+  attn_plan_kernel<<<1, 256, smem, st>>>(cu_seqlens, ndocs, tile, reinterpret_cast<int4*>(plan), max_tiles);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { set_last_error("attn_plan launch: %s", cudaGetErrorString(e)); return 11; }
+  return 0;
+}
+
+KWU_API int kwu_flash_fwd(const void* q, int q_ld, const void* k, int k_ld, const void* v, int v_ld,
+                          void* out, float* lse, const void* plan, int n_tiles, int T, int Hq, int Hkv,
+                          int window, const float* sink_lse, float scale, void* stream, int* status) {
+  if (T <= 0 || n_tiles <= 0) return 0;
+  if (Hq % Hkv) { set_last_error("flash_fwd: Hq must be a multiple of Hkv"); return 7; }
+  CUtensorMap tmQ, tmK, tmV;
+  int rc;
+  if ((rc = encode_tmap_2d(&tmQ, q, ELEM_BF16, T, (uint64_t)Hq * FA_D, q_ld, FA_BM, FA_D, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  if ((rc = encode_tmap_2d(&tmK, k, ELEM_BF16, T, (uint64_t)Hkv * FA_D, k_ld, FA_BN, FA_D, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  if ((rc = encode_tmap_2d(&tmV, v, ELEM_BF16, T, (uint64_t)Hkv * FA_D, v_ld, FA_BN, FA_D, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  static bool attr = false;
+  if (!attr) {
+    cudaError_t e = cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FA_SMEM);
+    if (e != cudaSuccess) { set_last_error("flash_fwd attr: %s", cudaGetErrorString(e)); return 10; }
+    attr = true;
+  }
+  FlashFwdParams p;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  p.lse = lse;
+  p.plan = reinterpret_cast<const int4*>(plan);
+  p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.window = window;
+  p.sink_lse = sink_lse;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = status;
+  dim3 grid(n_tiles, Hq);
+  flash_fwd_kernel<<<grid, FA_THREADS, FA_SMEM, reinterpret_cast<cudaStream_t>(stream)>>>(tmQ, tmK, tmV, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { set_last_error("flash_fwd launch: %s", cudaGetErrorString(e)); return 11; }
+  return 0;
+}

@@ -1,0 +1,157 @@
+"""Packed variable-length causal / sliding-window attention with attention sinks.
+
+Inputs are packed: ``q`` (T,Hq,D), ``k``/``v`` (T,Hkv,D), ``cu_seqlens`` (N+1,) int32. A query
+attends to keys of its own document only, never to later positions, and (with ``window=w``) only
+to the ``w`` most recent positions including itself. Attention sinks are extra softmax columns
+with a learned logit and a zero value: with ``sink_lse[h] = logsumexp(sinks[h, :])`` the result
+equals ``softmax-attention * sigmoid(lse - sink_lse)`` (one sink per head is the reference's
+``out * sigmoid(lse - sink)``, src/kohakuwullm/models/components/attention.py:91-100).
+
+``varlen_attention`` runs the tcgen05 flash kernels (``csrc/flash_fwd.cu`` / ``flash_bwd.cu``)
+for bf16 CUDA tensors with head_dim 64 and the fp32 PyTorch reference everywhere else.
+Reference kernels: src/kohakuwullm/kernels/attention/flash_attn_fwd.py:35-154,
+flash_attn_bwd.py:16-348.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from kohakuwullm_b200.ops import native
+
+c_int, c_float = ctypes.c_int, ctypes.c_float
+
+
+def _doc_ids(cu_seqlens: torch.Tensor, total: int) -> torch.Tensor:
+    idx = torch.arange(total, device=cu_seqlens.device)
+    return torch.searchsorted(cu_seqlens[1:].to(torch.long).contiguous(), idx, right=True)
+
+
+def attention_mask(cu_seqlens: torch.Tensor, total: int, window: int | None) -> torch.Tensor:
+    """(T,T) bool mask, true where query i may attend key j."""
+    doc = _doc_ids(cu_seqlens, total)
+    i = torch.arange(total, device=cu_seqlens.device)
+    allowed = (doc[:, None] == doc[None, :]) & (i[None, :] <= i[:, None])
+    if window is not None:
+        allowed &= (i[:, None] - i[None, :]) < window
+    return allowed
+
+
+def varlen_attention_reference(q, k, v, cu_seqlens, window=None, sink_lse=None, scale=None,
+                               return_lse=False):
+    """fp32 oracle. Works document by document so memory stays O(max_len^2)."""
+    T, Hq, D = q.shape
+    Hkv = k.shape[1]
+    group = Hq // Hkv
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    bounds = cu_seqlens.tolist()
+    outs, lses = [], []
+    for s, e in zip(bounds[:-1], bounds[1:]):
+        L = e - s
+        qf = q[s:e].float().transpose(0, 1)                              # (Hq, L, D)
+        kf = k[s:e].float().transpose(0, 1).repeat_interleave(group, 0)  # (Hq, L, D)
+        vf = v[s:e].float().transpose(0, 1).repeat_interleave(group, 0)
+        scores = torch.matmul(qf, kf.transpose(1, 2)) * scale           # (Hq, L, L)
+        i = torch.arange(L, device=q.device)
+        ok = i[None, :] <= i[:, None]
+        if window is not None:
+            ok &= (i[:, None] - i[None, :]) < window
+        scores = scores.masked_fill(~ok, float("-inf"))
+        lse = torch.logsumexp(scores, dim=-1)                             # (Hq, L)
+        if sink_lse is not None:
+            lse = torch.logaddexp(lse, sink_lse.float()[:, None])
+        p = torch.exp(scores - lse[..., None])
+        outs.append(torch.matmul(p, vf).transpose(0, 1))                  # (L, Hq, D)
+        lses.append(lse)
+    out = torch.cat(outs, 0).to(q.dtype) if outs else q.new_zeros(q.shape)
+    if return_lse:
+        return out, torch.cat(lses, 1)
+    return out
+
+
+# --------------------------------------------------------------------------------- native path
+def attention_plan(cu_seqlens: torch.Tensor, total_tokens: int, tile: int = 128) -> torch.Tensor:
+    """Device-side work list: one int4 ``(q0, doc_start, doc_end, valid)`` per 128-row query tile.
+
+    The list has the host-known length ``ceil(T/tile) + num_docs`` (an upper bound on the number
+    of tiles), so building and using it needs no host synchronisation and is graph-capturable.
+    """
+    L = native.require()
+    ndocs = cu_seqlens.numel() - 1
+    max_tiles = (total_tokens + tile - 1) // tile + ndocs
+    plan = torch.empty(max_tiles, 4, dtype=torch.int32, device=cu_seqlens.device)
+    rc = L.kwu_attn_plan(native.ptr(cu_seqlens), c_int(ndocs), c_int(tile), native.ptr(plan),
+                         c_int(max_tiles), native.stream_ptr())
+    native.check(rc, "attn_plan")
+    return plan
+
+
+class _FlashVarlen(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, cu_seqlens, plan, window, sink_lse, scale):
+        L = native.require()
+        T, Hq, D = q.shape
+        Hkv = k.shape[1]
+        out = torch.empty(T, Hq, D, dtype=q.dtype, device=q.device)
+        lse = torch.empty(Hq, T, dtype=torch.float32, device=q.device)
+        rc = L.kwu_flash_fwd(
+            native.ptr(q), c_int(q.stride(0)), native.ptr(k), c_int(k.stride(0)), native.ptr(v),
+            c_int(v.stride(0)), native.ptr(out), native.ptr(lse), native.ptr(plan),
+            c_int(plan.shape[0]), c_int(T), c_int(Hq), c_int(Hkv), c_int(window or 0),
+            native.ptr(sink_lse), c_float(scale), native.stream_ptr(), native.ptr(native.status_word()),
+        )
+        native.check(rc, "flash_fwd")
+        ctx.save_for_backward(q, k, v, out, lse, plan, sink_lse, cu_seqlens)
+        ctx.window, ctx.scale = window, scale
+        ctx.mark_non_differentiable(lse)
+        return out, lse
+
+    @staticmethod
+    def backward(ctx, dout, _dlse):
+        L = native.require()
+        q, k, v, out, lse, plan, sink_lse, cu_seqlens = ctx.saved_tensors
+        T, Hq, D = q.shape
+        Hkv = k.shape[1]
+        dout = dout.contiguous()
+        dq = torch.empty(T, Hq, D, dtype=q.dtype, device=q.device)
+        dk = torch.empty(T, Hkv, D, dtype=q.dtype, device=q.device)
+        dv = torch.empty(T, Hkv, D, dtype=q.dtype, device=q.device)
+        delta = torch.empty(Hq, T, dtype=torch.float32, device=q.device)
+        rc = L.kwu_flash_bwd(
+            native.ptr(q), c_int(q.stride(0)), native.ptr(k), c_int(k.stride(0)), native.ptr(v),
+            c_int(v.stride(0)), native.ptr(out), native.ptr(dout), native.ptr(lse), native.ptr(delta),
+            native.ptr(dq), native.ptr(dk), native.ptr(dv), native.ptr(plan),
+            c_int(plan.shape[0]), c_int(T), c_int(Hq), c_int(Hkv), c_int(ctx.window or 0),
+            c_float(ctx.scale), native.stream_ptr(), native.ptr(native.status_word()),
+        )
+        native.check(rc, "flash_bwd")
+        dsink = None
+        if sink_lse is not None and ctx.needs_input_grad[6]:
+            # sink columns carry a zero value, so dS_sink = -p_sink * delta summed over queries
+            dsink = -(torch.exp(sink_lse.float()[:, None] - lse) * delta).sum(1).to(sink_lse.dtype)
+        return dq, dk, dv, None, None, None, dsink, None
+
+
+def native_supported(q, k, v) -> bool:
+    return (
+        native.available() and q.is_cuda and q.dtype == torch.bfloat16 and k.dtype == q.dtype
+        and v.dtype == q.dtype and q.shape[-1] == 64 and q.stride(-1) == 1 and k.stride(-1) == 1
+        and v.stride(-1) == 1 and q.stride(1) == 64 and k.stride(1) == 64 and v.stride(1) == 64
+    )
+
+
+def varlen_attention(q, k, v, cu_seqlens, max_seqlen=None, window=None, sink_lse=None, scale=None,
+                     plan=None, return_lse=False):
+    """Packed causal attention; see the module docstring for the semantics."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    if native_supported(q, k, v):
+        if plan is None:
+            plan = attention_plan(cu_seqlens, q.shape[0])
+        if sink_lse is not None:
+            sink_lse = sink_lse.float()
+        out, lse = _FlashVarlen.apply(q, k, v, cu_seqlens, plan, window, sink_lse, float(scale))
+        return (out, lse) if return_lse else out
+    return varlen_attention_reference(q, k, v, cu_seqlens, window, sink_lse, scale, return_lse)
