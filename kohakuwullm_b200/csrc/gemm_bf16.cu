@@ -38,7 +38,18 @@ struct GemmParams {
   uint32_t idesc;
   int tiles_m, tiles_n;
   int* status;
+  // fused cross-entropy epilogues (EPI_LSE / EPI_DLOGITS)
+  const int* labels;     // (M) target column per row, negative = ignored row
+  float2* partial;       // EPI_LSE: (tiles_n, M) running (max, sum-exp) per row and column tile
+  float* target_logit;   // EPI_LSE: (M) logit of the target column
+  const float* lse;      // EPI_DLOGITS: (M) log-sum-exp of the full row
+  const float* coef_p;   // EPI_DLOGITS: (M) factor on the probabilities
+  const float* coef_y;   // EPI_DLOGITS: (M) factor on the one-hot target
 };
+
+constexpr int EPI_STORE = 0;    // C (+)= alpha * acc
+constexpr int EPI_LSE = 1;      // no C: per-row (max, sum-exp) partials and the target logit
+constexpr int EPI_DLOGITS = 2;  // C = coef_p * exp(acc - lse) - coef_y * onehot   (bf16)
 
 template <int BN>
 struct GemmSmem {
@@ -50,7 +61,7 @@ struct GemmSmem {
   static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // +1024 alignment slack
 };
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  void* __restrict__ Cout, const GemmParams p) {
@@ -191,13 +202,71 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_after();
       const int row = m0 + quarter * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + as * BN;
+      // per-row state of the cross-entropy epilogues
+      float run_max = -INFINITY, run_sum = 0.f, tgt = 0.f;
+      bool tgt_here = false;
+      int label = -1;
+      float row_lse = 0.f, row_cp = 0.f, row_cy = 0.f;
+      if (EPI != EPI_STORE && row < p.M) {
+        label = p.labels ? p.labels[row] : -1;
+        if (EPI == EPI_DLOGITS) {
+          row_lse = p.lse[row];
+          row_cp = p.coef_p[row];
+          row_cy = p.coef_y[row];
+        }
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
         tmem_ld_x32(t_row + c * 32, r);
         tmem_ld_wait();
         const int col0 = n0 + c * 32;
-        if (row < p.M && col0 < p.N) {
+        if (EPI == EPI_LSE) {
+          if (row < p.M && col0 < p.N) {
+            float cmax = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float v = (col0 + j < p.N) ? __uint_as_float(r[j]) * p.alpha : -INFINITY;
+              r[j] = __float_as_uint(v);
+              cmax = fmaxf(cmax, v);
+              if (col0 + j == label) { tgt = v; tgt_here = true; }
+            }
+            const float nm = fmaxf(run_max, cmax);
+            float cs = 0.f;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) cs += exp2f((__uint_as_float(r[j]) - nm) * 1.4426950408889634f);
+            run_sum = run_sum * exp2f((run_max - nm) * 1.4426950408889634f) + cs;
+            run_max = nm;
+          }
+        } else if (EPI == EPI_DLOGITS) {
+          if (row < p.M && col0 < p.N) {
+            __nv_bfloat16* dst =
+                reinterpret_cast<__nv_bfloat16*>(Cout) + static_cast<size_t>(row) * p.ldc + col0;
+            float f[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float v = __uint_as_float(r[j]) * p.alpha;
+              float g = row_cp * exp2f((v - row_lse) * 1.4426950408889634f);
+              if (col0 + j == label) g -= row_cy;
+              f[j] = g;
+            }
+            if (col0 + 32 <= p.N) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint4 v;
+                v.x = pack_bf16(f[8 * j + 0], f[8 * j + 1]);
+                v.y = pack_bf16(f[8 * j + 2], f[8 * j + 3]);
+                v.z = pack_bf16(f[8 * j + 4], f[8 * j + 5]);
+                v.w = pack_bf16(f[8 * j + 6], f[8 * j + 7]);
+                reinterpret_cast<uint4*>(dst)[j] = v;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) dst[j] = __float2bfloat16(f[j]);
+            }
+          }
+        } else if (row < p.M && col0 < p.N) {
           const bool full = (col0 + 32 <= p.N);
           if (p.out_fp32) {
             float* dst = reinterpret_cast<float*>(Cout) + static_cast<size_t>(row) * p.ldc + col0;
@@ -263,6 +332,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
         }
       }
+      if (EPI == EPI_LSE && row < p.M) {
+        p.partial[static_cast<size_t>(tile % p.tiles_n) * p.M + row] = make_float2(run_max, run_sum);
+        if (tgt_here) p.target_logit[row] = tgt;
+      }
       tc_fence_before();
       mbar_arrive(&acc_empty[as]);
     }
@@ -299,10 +372,19 @@ struct DescOverride {
 };
 static DescOverride g_override;
 
-template <int BN, bool A_MN, bool B_MN>
+struct EpiArgs {
+  const int* labels = nullptr;
+  float2* partial = nullptr;
+  float* target_logit = nullptr;
+  const float* lse = nullptr;
+  const float* coef_p = nullptr;
+  const float* coef_y = nullptr;
+};
+
+template <int BN, bool A_MN, bool B_MN, int EPI = EPI_STORE>
 static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb,
                        int ldc, int out_fp32, int accumulate, float alpha, int max_ctas,
-                       cudaStream_t stream, int* status) {
+                       cudaStream_t stream, int* status, const EpiArgs& ea = EpiArgs()) {
   using S = GemmSmem<BN>;
   CUtensorMap tmA, tmB;
   int rc;
@@ -333,8 +415,10 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
   p.tiles_m = (M + GEMM_BM - 1) / GEMM_BM;
   p.tiles_n = (N + BN - 1) / BN;
   p.status = status;
+  p.labels = ea.labels; p.partial = ea.partial; p.target_logit = ea.target_logit;
+  p.lse = ea.lse; p.coef_p = ea.coef_p; p.coef_y = ea.coef_y;
 
-  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, EPI>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
@@ -397,4 +481,66 @@ KWU_API void kwu_gemm_debug_override(int active, unsigned a_lbo, unsigned a_sbo,
   kwu::g_override.active = active;
   kwu::g_override.a_lbo = a_lbo; kwu::g_override.a_sbo = a_sbo; kwu::g_override.a_kadv = a_kadv;
   kwu::g_override.b_lbo = b_lbo; kwu::g_override.b_sbo = b_sbo; kwu::g_override.b_kadv = b_kadv;
+}
+
+
+// ------------------------------------------------------------------ fused linear cross-entropy
+// Forward: logits = alpha * h W^T are never written. Every (row, 256-column tile) leaves one
+// (max, sum-exp) pair in partial[tile, row]; the target logit of each row is captured on the way.
+// kwu_ce_combine then folds the partials into lse[row].
+KWU_API int kwu_ce_tiles_n(int V) { return (V + 255) / 256; }
+
+KWU_API int kwu_gemm_lse(const void* H, const void* W, int T, int V, int D, int ldh, int ldw,
+                         const int* labels, void* partial, float* target_logit, float alpha,
+                         void* stream, int* status) {
+  using namespace kwu;
+  if (T <= 0) return 0;
+  EpiArgs ea;
+  ea.labels = labels;
+  ea.partial = reinterpret_cast<float2*>(partial);
+  ea.target_logit = target_logit;
+  return launch_gemm<256, false, false, EPI_LSE>(H, W, nullptr, T, V, D, ldh, ldw, 0, 0, 0, alpha, 0,
+                                                 reinterpret_cast<cudaStream_t>(stream), status, ea);
+}
+
+// Backward recompute: dlogits[row, col] = coef_p[row] * exp(logit - lse[row]) - coef_y[row] * onehot,
+// written as bf16 with row pitch ldd.
+KWU_API int kwu_gemm_dlogits(const void* H, const void* W, void* dlogits, int T, int V, int D, int ldh,
+                             int ldw, int ldd, const int* labels, const float* lse,
+                             const float* coef_p, const float* coef_y, float alpha, void* stream,
+                             int* status) {
+  using namespace kwu;
+  if (T <= 0) return 0;
+  EpiArgs ea;
+  ea.labels = labels;
+  ea.lse = lse;
+  ea.coef_p = coef_p;
+  ea.coef_y = coef_y;
+  return launch_gemm<256, false, false, EPI_DLOGITS>(H, W, dlogits, T, V, D, ldh, ldw, ldd, 0, 0, alpha,
+                                                     0, reinterpret_cast<cudaStream_t>(stream), status, ea);
+}
+
+namespace kwu {
+__global__ void ce_combine_kernel(const float2* __restrict__ partial, int tiles_n, int M,
+                                  float* __restrict__ lse) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= M) return;
+  float m = -INFINITY, s = 0.f;
+  for (int t = 0; t < tiles_n; ++t) {
+    const float2 v = partial[static_cast<size_t>(t) * M + row];
+    const float nm = fmaxf(m, v.x);
+    s = s * __expf(m - nm) + v.y * __expf(v.x - nm);
+    m = nm;
+  }
+  lse[row] = m + __logf(s);
+}
+}  // namespace kwu
+
+KWU_API int kwu_ce_combine(const void* partial, int tiles_n, int M, float* lse, void* stream) {
+  if (M <= 0) return 0;
+  kwu::ce_combine_kernel<<<(M + 127) / 128, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const float2*>(partial), tiles_n, M, lse);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { kwu::set_last_error("ce_combine launch: %s", cudaGetErrorString(e)); return 11; }
+  return 0;
 }

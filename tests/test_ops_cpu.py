@@ -1,0 +1,83 @@
+"""CPU paths of the ops: they are the oracles of the GPU tests, so they are pinned against
+independent formulations here."""
+
+import math
+
+import torch
+
+from kohakuwullm_b200.models.seqinfo import SeqInfo
+from kohakuwullm_b200.ops.attention import attention_mask, varlen_attention, varlen_attention_reference
+from kohakuwullm_b200.ops.elementwise import qknorm_rope, rmsnorm, swiglu
+from kohakuwullm_b200.ops.gemm import linear, matmul
+from kohakuwullm_b200.ops.loss import linear_cross_entropy, linear_cross_entropy_reference
+
+
+def test_matmul_majors_on_cpu():
+    a, b = torch.randn(5, 7), torch.randn(3, 7)
+    ref = a @ b.t()
+    torch.testing.assert_close(matmul(a, b), ref)
+    torch.testing.assert_close(matmul(a.t().contiguous(), b, a_mn=True), ref)
+    torch.testing.assert_close(matmul(a, b.t().contiguous(), b_mn=True), ref)
+    out = torch.ones(5, 3)
+    matmul(a, b, out=out, accumulate=True, alpha=2.0)
+    torch.testing.assert_close(out, 1 + 2 * ref)
+    torch.testing.assert_close(linear(a, b), ref)
+
+
+def test_attention_reference_matches_dense_mask():
+    torch.manual_seed(0)
+    info = SeqInfo.from_lengths([5, 9, 3])
+    T = info.total_tokens
+    q, k, v = torch.randn(T, 4, 8), torch.randn(T, 2, 8), torch.randn(T, 2, 8)
+    for window in (None, 4):
+        out = varlen_attention(q, k, v, info.cu_seqlens, window=window)
+        mask = attention_mask(info.cu_seqlens, T, window)
+        kk, vv = k.repeat_interleave(2, 1), v.repeat_interleave(2, 1)
+        s = torch.einsum("thd,shd->hts", q, kk) / math.sqrt(8)
+        s = s.masked_fill(~mask[None], float("-inf"))
+        ref = torch.einsum("hts,shd->thd", s.softmax(-1), vv)
+        torch.testing.assert_close(out, ref, rtol=1e-4, atol=1e-5)
+
+
+def test_attention_sink_is_sigmoid_gate():
+    torch.manual_seed(1)
+    info = SeqInfo.from_lengths([6, 4])
+    T = info.total_tokens
+    q, k, v = torch.randn(T, 2, 8), torch.randn(T, 2, 8), torch.randn(T, 2, 8)
+    sink = torch.randn(2)
+    plain, lse = varlen_attention_reference(q, k, v, info.cu_seqlens, return_lse=True)
+    gated = varlen_attention_reference(q, k, v, info.cu_seqlens, sink_lse=sink)
+    gate = torch.sigmoid(lse - sink[:, None]).t()[..., None]
+    torch.testing.assert_close(gated, plain * gate, rtol=1e-4, atol=1e-5)
+
+
+def test_chunked_ce_matches_materialised():
+    torch.manual_seed(2)
+    h = torch.randn(50, 16, requires_grad=True)
+    w = torch.randn(40, 16, requires_grad=True)
+    labels = torch.randint(0, 40, (50,))
+    labels[::5] = -100
+    ce, lse = linear_cross_entropy(h, w, labels, chunk=16)
+    (ce.sum() + 0.1 * (lse ** 2).sum()).backward()
+    g1, g2 = h.grad.clone(), w.grad.clone()
+    h.grad = w.grad = None
+    ce_r, lse_r = linear_cross_entropy_reference(h, w, labels)
+    (ce_r.sum() + 0.1 * (lse_r ** 2).sum()).backward()
+    torch.testing.assert_close(ce, ce_r)
+    torch.testing.assert_close(g1, h.grad, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(g2, w.grad, rtol=1e-4, atol=1e-5)
+
+
+def test_elementwise_cpu_paths():
+    x = torch.randn(4, 16)
+    y = rmsnorm(x, torch.ones(16))
+    torch.testing.assert_close(y.pow(2).mean(-1), torch.ones(4), rtol=1e-3, atol=1e-3)
+    y2, h = rmsnorm(x, None, residual=x)
+    torch.testing.assert_close(h, 2 * x)
+    g = torch.randn(3, 8)
+    torch.testing.assert_close(swiglu(g), torch.nn.functional.silu(g[:, :4]) * g[:, 4:])
+    q = torch.randn(5, 2, 64)
+    ang = torch.rand(5, 32)
+    out = qknorm_rope(q, None, ang.cos(), ang.sin())
+    # rotation preserves the norm of the normalised vector
+    torch.testing.assert_close(out.pow(2).mean(-1), torch.ones(5, 2), rtol=1e-3, atol=1e-3)
