@@ -31,9 +31,10 @@ enum : int {
   KWU_ERR_BAD_ARG = 7,
 };
 
-// Wait limit in nanoseconds of %globaltimer (2 s by default; tests shorten it).
-#ifndef KWU_WAIT_LIMIT_NS
-#define KWU_WAIT_LIMIT_NS 2000000000ull
+// Wait limit in SM clock cycles (about 2 s at 2 GHz; tests shorten it). The clock is only read once
+// per 1024 failed polls, so a wait that succeeds quickly never pays for it.
+#ifndef KWU_WAIT_LIMIT_CYCLES
+#define KWU_WAIT_LIMIT_CYCLES 4000000000ll
 #endif
 
 __device__ __forceinline__ uint64_t global_timer_ns() {
@@ -91,20 +92,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Returns false when the wait was abandoned (own time-out or somebody else's abort).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int code) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
+  long long t0 = 0;
   uint32_t spins = 0;
-  while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
+  while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 0x3ff) == 0) {
       if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > KWU_WAIT_LIMIT_NS) {
+      const long long now = clock64();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > KWU_WAIT_LIMIT_CYCLES) {
         *abort_flag = 1;
         if (status) atomicCAS(status, 0, code);
         return false;
       }
     }
   }
+  return true;
 }
 
 // ------------------------------------------------------------------ TMA
@@ -328,9 +331,16 @@ __device__ __forceinline__ float warp_max(float v) {
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
   return v;
 }
+// 2^x on the special-function unit, no range fix-ups (inputs here are <= 0 or already bounded)
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&v);
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));  // low half = a, high half = b
+  return r;
 }
 __device__ __forceinline__ float2 unpack_bf16(uint32_t u) {
   __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162*>(&u);
@@ -351,5 +361,7 @@ int encode_tmap_2d(CUtensorMap* out, const void* base, int elem_kind, uint64_t r
                    uint64_t ld_elems, uint32_t box_rows, uint32_t box_cols, int swizzle);
 enum : int { ELEM_BF16 = 0, ELEM_F16 = 1, ELEM_U8 = 2, ELEM_F32 = 3 };
 const char* last_error();
+void count_launch(int n = 1);
+long long launch_total();  // bumps the library-wide kernel launch counter
 void set_last_error(const char* fmt, ...);
 }  // namespace kwu

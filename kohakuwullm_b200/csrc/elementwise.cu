@@ -380,13 +380,14 @@ KWU_API int kwu_rmsnorm_fwd(const void* x, const void* res, const float* w, void
   if (rows <= 0) return 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int grid = grid_for(rows, 8);
-  if (res)
+  if (res) {
     rmsnorm_fwd_kernel<true><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)res, w,
                                                   (__nv_bfloat16*)y, (__nv_bfloat16*)h_out, rstd, rows,
-                                                  cols, eps, one_plus);
-  else
+                                                  cols, eps, one_plus); kwu::count_launch();
+  } else {
     rmsnorm_fwd_kernel<false><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, nullptr, w, (__nv_bfloat16*)y,
-                                                   nullptr, rstd, rows, cols, eps, one_plus);
+                                                   nullptr, rstd, rows, cols, eps, one_plus); kwu::count_launch();
+  }
   return check_launch("rmsnorm_fwd");
 }
 
@@ -403,10 +404,10 @@ KWU_API int kwu_rmsnorm_bwd(const void* x, const float* w, const float* rstd, co
   const bool want_dw = (w != nullptr && dw != nullptr && dw_partial != nullptr);
   rmsnorm_bwd_kernel<<<grid, 256, want_dw ? cols * sizeof(float) : 0, st>>>(
       (const __nv_bfloat16*)x, w, rstd, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)dres,
-      (__nv_bfloat16*)dx, want_dw ? dw_partial : nullptr, rows, cols, one_plus);
+      (__nv_bfloat16*)dx, want_dw ? dw_partial : nullptr, rows, cols, one_plus); kwu::count_launch();
   if (int rc = check_launch("rmsnorm_bwd")) return rc;
   if (want_dw) {
-    colsum_partials_kernel<<<(cols + 255) / 256, 256, 0, st>>>(dw_partial, dw, grid, cols, accumulate_dw);
+    colsum_partials_kernel<<<(cols + 255) / 256, 256, 0, st>>>(dw_partial, dw, grid, cols, accumulate_dw); kwu::count_launch();
     return check_launch("rmsnorm_dw");
   }
   return 0;
@@ -425,7 +426,7 @@ KWU_API int kwu_qknorm_rope_fwd(const void* src, int src_ld, void* dst, int dst_
   const int grid = grid_for(static_cast<long>(tokens) * heads, 8, 148 * 16);
   qknorm_rope_fwd_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)src, src_ld, (__nv_bfloat16*)dst,
                                               dst_ld, weight, cos_t, sin_t, tokens, heads, rot_half,
-                                              eps, do_norm);
+                                              eps, do_norm); kwu::count_launch();
   return check_launch("qknorm_rope_fwd");
 }
 
@@ -440,7 +441,7 @@ KWU_API int kwu_qknorm_rope_bwd(const void* src, int src_ld, const void* dout, i
   qknorm_rope_bwd_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)src, src_ld,
                                               (const __nv_bfloat16*)dout, dout_ld, (__nv_bfloat16*)dsrc,
                                               dsrc_ld, weight, dweight, cos_t, sin_t, tokens, heads,
-                                              rot_half, eps, do_norm);
+                                              rot_half, eps, do_norm); kwu::count_launch();
   return check_launch("qknorm_rope_bwd");
 }
 
@@ -451,7 +452,7 @@ KWU_API int kwu_swiglu_fwd(const void* in, int in_ld, void* out, int out_ld, int
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int grid = grid_for(static_cast<long>(rows) * (H / 8), 256);
   swiglu_fwd_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)in, in_ld, (__nv_bfloat16*)out, out_ld,
-                                         rows, H);
+                                         rows, H); kwu::count_launch();
   return check_launch("swiglu_fwd");
 }
 
@@ -462,6 +463,6 @@ KWU_API int kwu_swiglu_bwd(const void* in, int in_ld, const void* dout, int dout
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int grid = grid_for(static_cast<long>(rows) * (H / 8), 256);
   swiglu_bwd_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)in, in_ld, (const __nv_bfloat16*)dout,
-                                         dout_ld, (__nv_bfloat16*)din, din_ld, rows, H);
+                                         dout_ld, (__nv_bfloat16*)din, din_ld, rows, H); kwu::count_launch();
   return check_launch("swiglu_bwd");
 }

@@ -48,7 +48,11 @@ struct FlashBwdParams {
   __nv_bfloat16* dq;    // (T, Hq, 64)
   __nv_bfloat16* dk;    // (T, Hkv, 64)
   __nv_bfloat16* dv;    // (T, Hkv, 64)
+  float* dk_part;       // (T, Hq, 64) per-query-head partials when Hq > Hkv, else null
+  float* dv_part;
   const int4* plan;
+  int n_tiles;
+  int dk_ld, dv_ld;     // row pitch (elements per token) of dk / dv, so they can land inside a fused dqkv buffer
   int T, Hq, Hkv, window;
   float scale;
   int* status;
@@ -56,7 +60,7 @@ struct FlashBwdParams {
 
 // ------------------------------------------------------------------------------------ dK / dV
 // smem: K tile 16 KB, V tile 16 KB, 2 stages x (Q 8 KB + dO 8 KB).
-constexpr int FBK_SMEM = 2 * 16384 + 2 * 16384 + 1024 + 1024;
+constexpr int FBK_SMEM = 2 * 16384 + 2 * 16384 + 1024 + 1024 + 1024;
 
 __global__ void __launch_bounds__(FB_THREADS, 2)
 flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_constant__ CUtensorMap tmDO64,
@@ -65,8 +69,8 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
   const int4 job = p.plan[blockIdx.x];
   if (!job.w) return;
   const int kv0 = job.x, de = job.z;
-  const int hk = blockIdx.y;
-  const int group = p.Hq / p.Hkv;
+  const int h = blockIdx.y;                 // one CTA per query head; GQA partials are summed afterwards
+  const int hk = h / (p.Hq / p.Hkv);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -75,7 +79,9 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
   uint8_t* sV = smem + 16384;
   uint8_t* sQ = smem + 32768;           // 2 stages x 8 KB
   uint8_t* sDO = smem + 32768 + 16384;  // 2 stages x 8 KB
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 65536);
+  float* sLse = reinterpret_cast<float*>(smem + 65536);        // 2 stages x 64, pre-scaled by log2(e)
+  float* sDelta = sLse + 128;                                  // 2 stages x 64
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 65536 + 1024);
   uint64_t* kv_full = bars + 0;
   uint64_t* qd_full = bars + 1;   // [2]
   uint64_t* qd_empty = bars + 3;  // [2]
@@ -92,7 +98,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
   int q_end = de;
   if (p.window > 0) q_end = min(de, kv0 + 127 + p.window);
   const int n_q = (q_end - q_begin + 63) / 64;
-  const int n_it = n_q * group;
+  const int n_it = n_q;
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
@@ -121,12 +127,26 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
       mbar_expect_tx(kv_full, 32768);
       tma_load_2d(sK, &tmK128, kv_full, hk * FB_D, kv0);
       tma_load_2d(sV, &tmV128, kv_full, hk * FB_D, kv0);
-      for (int it = 0; it < n_it; ++it) {
-        const int s = it & 1;
-        const uint32_t ph = (it >> 1) & 1;
-        const int h = hk * group + it / n_q;
-        const int q_lo = q_begin + (it % n_q) * 64;
-        if (!mbar_wait(&qd_empty[s], ph ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_EMPTY)) break;
+    }
+    const float* lse_h = p.lse + static_cast<size_t>(h) * p.T;
+    const float* dl_h = p.delta + static_cast<size_t>(h) * p.T;
+    for (int it = 0; it < n_it; ++it) {
+      const int s = it & 1;
+      const uint32_t ph = (it >> 1) & 1;
+      const int q_lo = q_begin + it * 64;
+      int ok = 1;
+      if (lane == 0) ok = mbar_wait(&qd_empty[s], ph ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_EMPTY) ? 1 : 0;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      // per-query softmax statistics of this tile, staged once for all 128 key rows
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int qc = min(q_lo + lane + 32 * u, p.T - 1);
+        sLse[s * 64 + lane + 32 * u] = lse_h[qc] * FB_LOG2E;
+        sDelta[s * 64 + lane + 32 * u] = dl_h[qc] * p.scale;
+      }
+      __syncwarp();
+      if (lane == 0) {
         mbar_expect_tx(&qd_full[s], 16384);
         tma_load_2d(sQ + s * 8192, &tmQ64, &qd_full[s], h * FB_D, q_lo);
         tma_load_2d(sDO + s * 8192, &tmDO64, &qd_full[s], h * FB_D, q_lo);
@@ -176,14 +196,20 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
     const float c_log2 = p.scale * FB_LOG2E;
     bool ok = true;
     for (int it = 0; it < n_it; ++it) {
-      const int h = hk * group + it / n_q;
-      const int q_lo = q_begin + (it % n_q) * 64;
-      const float* lse_h = p.lse + static_cast<size_t>(h) * p.T;
-      const float* dl_h = p.delta + static_cast<size_t>(h) * p.T;
-      ok = mbar_wait(sdp_full, it & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_FULL);
+      const int q_lo = q_begin + it * 64;
+      const float* lse_s = sLse + (it & 1) * 64;
+      const float* dl_s = sDelta + (it & 1) * 64;
+      // observe the producer's barrier directly so its smem writes are visible here
+      ok = mbar_wait(&qd_full[it & 1], (it >> 1) & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
+      if (ok) ok = mbar_wait(sdp_full, it & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_FULL);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
+      // query columns of this tile that key row kj may attend to: [c_lo, c_hi]
+      const int c_lo_q = kj - q_lo;                                           // causal: qi >= kj
+      int c_hi_q = min(q_end, p.window > 0 ? kj + p.window : q_end) - 1 - q_lo;  // window and document end
+      if (kj >= de) c_hi_q = -1;
+      const bool need_mask = (c_lo_q > 0) || (c_hi_q < 63);
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t sv[32], dp[32], pp[16], dd[16];
@@ -195,15 +221,11 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
           float pr[2], dsv[2];
 #pragma unroll
           for (int u = 0; u < 2; ++u) {
-            const int qi = q_lo + c * 32 + e + u;
-            const bool valid = (qi < q_end) && (kj <= qi) && (kj < de) &&
-                               (p.window <= 0 || qi - kj < p.window);
-            const int qc = min(qi, p.T - 1);
-            const float lse_q = lse_h[qc] * FB_LOG2E;
-            const float dl_q = dl_h[qc];
-            const float pv = valid ? exp2f(__uint_as_float(sv[e + u]) * c_log2 - lse_q) : 0.f;
+            const int col = c * 32 + e + u;
+            float pv = fast_exp2(fmaf(__uint_as_float(sv[e + u]), c_log2, -lse_s[col]));
+            if (need_mask) pv = (col >= c_lo_q && col <= c_hi_q) ? pv : 0.f;
             pr[u] = pv;
-            dsv[u] = pv * (__uint_as_float(dp[e + u]) - dl_q) * p.scale;
+            dsv[u] = pv * fmaf(__uint_as_float(dp[e + u]), p.scale, -dl_s[col]);
           }
           pp[e / 2] = pack_bf16(pr[0], pr[1]);
           dd[e / 2] = pack_bf16(dsv[0], dsv[1]);
@@ -230,16 +252,26 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
         tmem_ld_x32(src + 32, o + 32);
         tmem_ld_wait();
         if (kj < de) {
-          __nv_bfloat16* base = (which == 0 ? p.dv : p.dk) + (static_cast<size_t>(kj) * p.Hkv + hk) * FB_D;
-          uint4* dst = reinterpret_cast<uint4*>(base);
+          if (p.dk_part) {
+            float4* dst = reinterpret_cast<float4*>((which == 0 ? p.dv_part : p.dk_part) +
+                                                    (static_cast<size_t>(kj) * p.Hq + h) * FB_D);
 #pragma unroll
-          for (int v = 0; v < 8; ++v) {
-            uint4 w;
-            w.x = pack_bf16(__uint_as_float(o[8 * v + 0]), __uint_as_float(o[8 * v + 1]));
-            w.y = pack_bf16(__uint_as_float(o[8 * v + 2]), __uint_as_float(o[8 * v + 3]));
-            w.z = pack_bf16(__uint_as_float(o[8 * v + 4]), __uint_as_float(o[8 * v + 5]));
-            w.w = pack_bf16(__uint_as_float(o[8 * v + 6]), __uint_as_float(o[8 * v + 7]));
-            dst[v] = w;
+            for (int v = 0; v < 16; ++v)
+              dst[v] = make_float4(__uint_as_float(o[4 * v]), __uint_as_float(o[4 * v + 1]),
+                                   __uint_as_float(o[4 * v + 2]), __uint_as_float(o[4 * v + 3]));
+          } else {
+            __nv_bfloat16* base = (which == 0 ? p.dv + static_cast<size_t>(kj) * p.dv_ld
+                                              : p.dk + static_cast<size_t>(kj) * p.dk_ld) + hk * FB_D;
+            uint4* dst = reinterpret_cast<uint4*>(base);
+#pragma unroll
+            for (int v = 0; v < 8; ++v) {
+              uint4 w;
+              w.x = pack_bf16(__uint_as_float(o[8 * v + 0]), __uint_as_float(o[8 * v + 1]));
+              w.y = pack_bf16(__uint_as_float(o[8 * v + 2]), __uint_as_float(o[8 * v + 3]));
+              w.z = pack_bf16(__uint_as_float(o[8 * v + 4]), __uint_as_float(o[8 * v + 5]));
+              w.w = pack_bf16(__uint_as_float(o[8 * v + 6]), __uint_as_float(o[8 * v + 7]));
+              dst[v] = w;
+            }
           }
         }
       }
@@ -264,7 +296,8 @@ __global__ void __launch_bounds__(FB_THREADS, 2)
 flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_constant__ CUtensorMap tmDO128,
                     const __grid_constant__ CUtensorMap tmK64, const __grid_constant__ CUtensorMap tmV64,
                     const FlashBwdParams p) {
-  const int4 job = p.plan[blockIdx.x];
+  // later query tiles of a document see more keys: schedule them first
+  const int4 job = p.plan[p.n_tiles - 1 - blockIdx.x];
   if (!job.w) return;
   const int q0 = job.x, ds = job.y, de = job.z;
   const int h = blockIdx.y;
@@ -370,7 +403,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
     const float c_log2 = p.scale * FB_LOG2E;
     const int qc = min(qi, p.T - 1);
     const float lse_q = p.lse[static_cast<size_t>(h) * p.T + qc] * FB_LOG2E;
-    const float dl_q = p.delta[static_cast<size_t>(h) * p.T + qc];
+    const float dl_q = p.delta[static_cast<size_t>(h) * p.T + qc] * p.scale;
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
       const int kv0 = lo + j * 64;
@@ -378,6 +411,10 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
+      // key columns of this tile that query row qi may attend to: [c_lo, c_hi]
+      const int c_hi_k = (qi < q_hi) ? (qi - kv0) : -1;
+      const int c_lo_k = (p.window > 0) ? (qi - p.window + 1 - kv0) : 0;
+      const bool need_mask = (c_hi_k < 63) || (c_lo_k > 0);
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t sv[32], dp[32], dd[16];
@@ -389,10 +426,10 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
           float dsv[2];
 #pragma unroll
           for (int u = 0; u < 2; ++u) {
-            const int kj = kv0 + c * 32 + e + u;
-            const bool valid = (qi < q_hi) && (kj <= qi) && (p.window <= 0 || qi - kj < p.window);
-            const float pv = valid ? exp2f(__uint_as_float(sv[e + u]) * c_log2 - lse_q) : 0.f;
-            dsv[u] = pv * (__uint_as_float(dp[e + u]) - dl_q) * p.scale;
+            const int col = c * 32 + e + u;
+            float pv = fast_exp2(fmaf(__uint_as_float(sv[e + u]), c_log2, -lse_q));
+            if (need_mask) pv = (col >= c_lo_k && col <= c_hi_k) ? pv : 0.f;
+            dsv[u] = pv * fmaf(__uint_as_float(dp[e + u]), p.scale, -dl_q);
           }
           dd[e / 2] = pack_bf16(dsv[0], dsv[1]);
         }
@@ -437,13 +474,46 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
   }
 }
 
+// dk[t, hk, :] = sum over the query heads of group hk of part[t, h, :]   (same for dv)
+__global__ void __launch_bounds__(256)
+flash_group_reduce_kernel(const float* __restrict__ dk_part, const float* __restrict__ dv_part,
+                          __nv_bfloat16* __restrict__ dk, __nv_bfloat16* __restrict__ dv, int dk_ld,
+                          int dv_ld, int T, int Hq, int Hkv) {
+  const int group = Hq / Hkv;
+  const long total = static_cast<long>(T) * Hkv * 16;  // float4 lanes
+  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const int v = static_cast<int>(i & 15);
+    const long th = i >> 4;
+    const int hk = static_cast<int>(th % Hkv);
+    const long t = th / Hkv;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+    for (int g = 0; g < group; ++g) {
+      const size_t off = ((static_cast<size_t>(t) * Hq + hk * group + g) * 64) / 4 + v;
+      const float4 x = reinterpret_cast<const float4*>(dk_part)[off];
+      const float4 y = reinterpret_cast<const float4*>(dv_part)[off];
+      a.x += x.x; a.y += x.y; a.z += x.z; a.w += x.w;
+      b.x += y.x; b.y += y.y; b.z += y.z; b.w += y.w;
+    }
+    reinterpret_cast<uint2*>(dk + static_cast<size_t>(t) * dk_ld + hk * 64)[v] =
+        make_uint2(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w));
+    reinterpret_cast<uint2*>(dv + static_cast<size_t>(t) * dv_ld + hk * 64)[v] =
+        make_uint2(pack_bf16(b.x, b.y), pack_bf16(b.z, b.w));
+  }
+}
+
 }  // namespace kwu
 
 using namespace kwu;
 
+// Scratch for the GQA partial sums: 2 * T * Hq * 64 floats when Hq > Hkv (0 otherwise).
+KWU_API long long kwu_flash_bwd_scratch_floats(int T, int Hq, int Hkv) {
+  return Hq > Hkv ? 2ll * T * Hq * 64 : 0;
+}
+
 KWU_API int kwu_flash_bwd(const void* q, int q_ld, const void* k, int k_ld, const void* v, int v_ld,
                           const void* out, const void* dout, const float* lse, float* delta,
-                          void* dq, void* dk, void* dv, const void* plan,
+                          void* dq, void* dk, int dk_ld, void* dv, int dv_ld, float* scratch, const void* plan,
                           int n_tiles, int T, int Hq, int Hkv, int window, float scale, void* stream,
                           int* status) {
   if (T <= 0 || n_tiles <= 0) return 0;
@@ -453,7 +523,7 @@ KWU_API int kwu_flash_bwd(const void* q, int q_ld, const void* k, int k_ld, cons
     long g = (rows + 7) / 8;
     if (g > 148 * 16) g = 148 * 16;
     flash_delta_kernel<<<static_cast<int>(g), 256, 0, st>>>((const __nv_bfloat16*)out,
-                                                          (const __nv_bfloat16*)dout, delta, T, Hq);
+                                                          (const __nv_bfloat16*)dout, delta, T, Hq); kwu::count_launch();
   }
   CUtensorMap tmQ64, tmDO64, tmK128, tmV128, tmQ128, tmDO128, tmK64, tmV64;
   int rc;
@@ -478,9 +548,23 @@ KWU_API int kwu_flash_bwd(const void* q, int q_ld, const void* k, int k_ld, cons
   p.lse = lse; p.delta = delta;
   p.dq = (__nv_bfloat16*)dq; p.dk = (__nv_bfloat16*)dk; p.dv = (__nv_bfloat16*)dv;
   p.plan = reinterpret_cast<const int4*>(plan);
+  p.n_tiles = n_tiles;
+  p.dk_ld = dk_ld; p.dv_ld = dv_ld;
   p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.window = window; p.scale = scale; p.status = status;
-  flash_bwd_dkdv_kernel<<<dim3(n_tiles, Hkv), FB_THREADS, FBK_SMEM, st>>>(tmQ64, tmDO64, tmK128, tmV128, p);
-  flash_bwd_dq_kernel<<<dim3(n_tiles, Hq), FB_THREADS, FBQ_SMEM, st>>>(tmQ128, tmDO128, tmK64, tmV64, p);
+  if (Hq > Hkv) {
+    if (!scratch) { set_last_error("flash_bwd: GQA needs the scratch buffer"); return 7; }
+    p.dk_part = scratch;
+    p.dv_part = scratch + static_cast<size_t>(T) * Hq * 64;
+  } else {
+    p.dk_part = p.dv_part = nullptr;
+  }
+  flash_bwd_dkdv_kernel<<<dim3(n_tiles, Hq), FB_THREADS, FBK_SMEM, st>>>(tmQ64, tmDO64, tmK128, tmV128, p); kwu::count_launch();
+  if (Hq > Hkv) {
+    long g = (static_cast<long>(T) * Hkv * 16 + 255) / 256;
+    if (g > 148 * 16) g = 148 * 16;
+    flash_group_reduce_kernel<<<static_cast<int>(g), 256, 0, st>>>(p.dk_part, p.dv_part, p.dk, p.dv, dk_ld, dv_ld, T, Hq, Hkv); kwu::count_launch();
+  }
+  flash_bwd_dq_kernel<<<dim3(n_tiles, Hq), FB_THREADS, FBQ_SMEM, st>>>(tmQ128, tmDO128, tmK64, tmV64, p); kwu::count_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { set_last_error("flash_bwd launch: %s", cudaGetErrorString(e)); return 11; }
   return 0;

@@ -29,6 +29,7 @@ struct FlashFwdParams {
   __nv_bfloat16* out;   // (T, Hq, 64)
   float* lse;           // (Hq, T)
   const int4* plan;     // (q0, doc_start, doc_end, valid)
+  int n_tiles;
   int T, Hq, Hkv, window;
   const float* sink_lse;  // (Hq) or null
   float scale_log2;       // softmax scale * log2(e)
@@ -61,7 +62,8 @@ __global__ void attn_plan_kernel(const int* __restrict__ cu, int ndocs, int tile
 __global__ void __launch_bounds__(FA_THREADS, 2)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const FlashFwdParams p) {
-  const int4 job = p.plan[blockIdx.x];
+  // later query tiles of a document see more keys: schedule them first
+  const int4 job = p.plan[p.n_tiles - 1 - blockIdx.x];
   if (!job.w) return;
   const int q0 = job.x, ds = job.y, de = job.z;
   const int h = blockIdx.y;
@@ -198,8 +200,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (!ok) break;
       tc_fence_after();
       const bool need_mask = (kv0 + FA_BN - 1 > q0) || (p.window > 0 && (q0 + FA_BM - 1 - kv0) >= p.window);
-      // pass 1: row maximum
-      float mx = m;
+      // key columns this row may see inside the tile: [c_lo, c_hi]
+      int c_hi = qi - kv0;
+      int c_lo = (p.window > 0) ? (qi - p.window + 1 - kv0) : -1;
+      // pass 1: row maximum of the raw scores (the positive scale commutes with max)
+      float mx4[4] = {m, m, m, m};   // independent chains keep the max off the critical path
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t r[32];
@@ -208,21 +213,22 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (need_mask) {
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
-            const int kj = kv0 + c * 32 + e;
-            const bool valid = (kj <= qi) && (p.window <= 0 || qi - kj < p.window);
-            const float sv = valid ? __uint_as_float(r[e]) * p.scale_log2 : FA_NEG;
-            mx = fmaxf(mx, sv);
+            const int col = c * 32 + e;
+            const float sv = (col <= c_hi && col >= c_lo) ? __uint_as_float(r[e]) : FA_NEG;
+            mx4[e & 3] = fmaxf(mx4[e & 3], sv);
           }
         } else {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(r[e]) * p.scale_log2);
+          for (int e = 0; e < 32; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(r[e]));
         }
       }
-      const float alpha = exp2f(m - mx);
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      const float alpha = fast_exp2((m - mx) * p.scale_log2);
       m = mx;
-      // pass 2: probabilities, packed to bf16
+      const float neg_ms = -mx * p.scale_log2;
+      // pass 2: probabilities p = 2^(s*c - m*c), packed to bf16
       uint32_t pk[64];
-      float sum = 0.f;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t r[32];
@@ -230,21 +236,18 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tmem_ld_wait();
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
-          float s0 = __uint_as_float(r[e]) * p.scale_log2;
-          float s1 = __uint_as_float(r[e + 1]) * p.scale_log2;
+          float p0 = fast_exp2(fmaf(__uint_as_float(r[e]), p.scale_log2, neg_ms));
+          float p1 = fast_exp2(fmaf(__uint_as_float(r[e + 1]), p.scale_log2, neg_ms));
           if (need_mask) {
-            const int kj = kv0 + c * 32 + e;
-            const bool v0 = (kj <= qi) && (p.window <= 0 || qi - kj < p.window);
-            const bool v1 = (kj + 1 <= qi) && (p.window <= 0 || qi - kj - 1 < p.window);
-            s0 = v0 ? s0 : FA_NEG;
-            s1 = v1 ? s1 : FA_NEG;
+            const int col = c * 32 + e;
+            p0 = (col <= c_hi && col >= c_lo) ? p0 : 0.f;
+            p1 = (col + 1 <= c_hi && col + 1 >= c_lo) ? p1 : 0.f;
           }
-          const float p0 = exp2f(s0 - m), p1 = exp2f(s1 - m);
-          sum += p0 + p1;
+          sum4[(e >> 1) & 3] += p0 + p1;
           pk[c * 16 + e / 2] = pack_bf16(p0, p1);
         }
       }
-      l = l * alpha + sum;
+      l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
       // the previous P V product must be complete before P is overwritten and O is touched
       if (j > 0) {
         ok = mbar_wait(o_done, (j - 1) & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_EMPTY);
@@ -276,7 +279,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     if (ok && n_kv > 0) {
       tc_fence_after();
-      float lse = (m + log2f(l)) * 0.6931471805599453f;  // natural log
+      float lse = (m * p.scale_log2 + log2f(l)) * 0.6931471805599453f;  // natural log
       float inv = 1.f / l;
       if (p.sink_lse) {
         const float sl = p.sink_lse[h];
@@ -332,7 +335,7 @@ KWU_API int kwu_attn_plan(const int* cu_seqlens, int ndocs, int tile, void* plan
     cudaFuncSetAttribute(attn_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
     attr = true;
   }
-  attn_plan_kernel<<<1, 256, smem, st>>>(cu_seqlens, ndocs, tile, reinterpret_cast<int4*>(plan), max_tiles);
+  attn_plan_kernel<<<1, 256, smem, st>>>(cu_seqlens, ndocs, tile, reinterpret_cast<int4*>(plan), max_tiles); kwu::count_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { set_last_error("attn_plan launch: %s", cudaGetErrorString(e)); return 11; }
   return 0;
@@ -358,12 +361,13 @@ KWU_API int kwu_flash_fwd(const void* q, int q_ld, const void* k, int k_ld, cons
   p.out = reinterpret_cast<__nv_bfloat16*>(out);
   p.lse = lse;
   p.plan = reinterpret_cast<const int4*>(plan);
+  p.n_tiles = n_tiles;
   p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.window = window;
   p.sink_lse = sink_lse;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
   dim3 grid(n_tiles, Hq);
-  flash_fwd_kernel<<<grid, FA_THREADS, FA_SMEM, reinterpret_cast<cudaStream_t>(stream)>>>(tmQ, tmK, tmV, p);
+  flash_fwd_kernel<<<grid, FA_THREADS, FA_SMEM, reinterpret_cast<cudaStream_t>(stream)>>>(tmQ, tmK, tmV, p); kwu::count_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { set_last_error("flash_fwd launch: %s", cudaGetErrorString(e)); return 11; }
   return 0;

@@ -432,7 +432,7 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
   int cap = num_sms();
   if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;
   if (grid > cap) grid = cap;
-  kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, C, p);
+  kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, C, p); kwu::count_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_error("gemm launch: %s", cudaGetErrorString(e));
@@ -539,7 +539,7 @@ __global__ void ce_combine_kernel(const float2* __restrict__ partial, int tiles_
 KWU_API int kwu_ce_combine(const void* partial, int tiles_n, int M, float* lse, void* stream) {
   if (M <= 0) return 0;
   kwu::ce_combine_kernel<<<(M + 127) / 128, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<const float2*>(partial), tiles_n, M, lse);
+      reinterpret_cast<const float2*>(partial), tiles_n, M, lse); kwu::count_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { kwu::set_last_error("ce_combine launch: %s", cudaGetErrorString(e)); return 11; }
   return 0;

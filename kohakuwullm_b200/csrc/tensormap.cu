@@ -3,11 +3,15 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <atomic>
 #include <mutex>
 
 namespace kwu {
 
 static thread_local char g_err[512] = {0};
+static std::atomic<long long> g_launches{0};
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+long long launch_total() { return g_launches.load(); }
 const char* last_error() { return g_err; }
 void set_last_error(const char* fmt, ...) {
   va_list ap;
@@ -72,3 +76,6 @@ int encode_tmap_2d(CUtensorMap* out, const void* base, int elem_kind, uint64_t r
 }  // namespace kwu
 
 KWU_API const char* kwu_last_error() { return kwu::last_error(); }
+
+// Number of kernels this library has launched in this process (for launch accounting in benchmarks).
+KWU_API long long kwu_launch_count() { return kwu::launch_total(); }

@@ -1,0 +1,84 @@
+"""Dense feed-forward blocks.
+
+``GLUMLP`` keeps gate and value in ONE projection ``w_in`` (dim -> 2*hidden) so a single GEMM feeds
+the fused SwiGLU kernel, which reads the two halves in place. Reference:
+src/kohakuwullm/models/components/mlp.py:15-126.
+"""
+
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+from kohakuwullm_b200.ops.elementwise import swiglu
+from kohakuwullm_b200.ops.gemm import linear
+from kohakuwullm_b200.registry import MLP
+
+
+def resolve_hidden(dim: int, ratio: float = 4.0, hidden: int | None = None, multiple_of: int = 128,
+                   glu: bool = True) -> int:
+    """Hidden width: explicit value, else ``ratio * dim`` (times 2/3 for gated units), rounded UP."""
+    if hidden is not None:
+        return int(hidden)
+    h = dim * ratio * (2.0 / 3.0 if glu else 1.0)
+    return int(-(-h // multiple_of) * multiple_of)
+
+
+class Linear(nn.Module):
+    """Weight-only (optionally biased) linear layer running on the tcgen05 GEMM."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = False):
+        super().__init__()
+        self.in_features, self.out_features = in_features, out_features
+        self.weight = nn.Parameter(torch.empty(out_features, in_features))
+        self.bias = nn.Parameter(torch.zeros(out_features)) if bias else None
+
+    def forward(self, x):
+        return linear(x, self.weight, self.bias)
+
+    def extra_repr(self):
+        return f"{self.in_features} -> {self.out_features}, bias={self.bias is not None}"
+
+
+class GLUMLP(nn.Module):
+    activation = "silu"
+
+    def __init__(self, dim: int, hidden: int | None = None, ratio: float = 4.0, multiple_of: int = 128,
+                 bias: bool = False, **_unused):
+        super().__init__()
+        self.dim = dim
+        self.hidden = resolve_hidden(dim, ratio, hidden, multiple_of, glu=True)
+        self.w_in = Linear(dim, 2 * self.hidden, bias)
+        self.w_out = Linear(self.hidden, dim, bias)
+
+    def forward(self, x):
+        h = self.w_in(x)
+        if self.activation == "silu":
+            a = swiglu(h)
+        else:
+            g, v = h.chunk(2, dim=-1)
+            a = torch.nn.functional.gelu(g, approximate="tanh") * v
+        return self.w_out(a)
+
+
+class GeGLUMLP(GLUMLP):
+    activation = "gelu"
+
+
+class GELUMLP(nn.Module):
+    def __init__(self, dim: int, hidden: int | None = None, ratio: float = 4.0, multiple_of: int = 128,
+                 bias: bool = False, **_unused):
+        super().__init__()
+        self.hidden = resolve_hidden(dim, ratio, hidden, multiple_of, glu=False)
+        self.fc1 = Linear(dim, self.hidden, bias)
+        self.fc2 = Linear(self.hidden, dim, bias)
+
+    def forward(self, x):
+        return self.fc2(torch.nn.functional.gelu(self.fc1(x)))
+
+
+MLP.register("swiglu", GLUMLP)
+MLP.register("swiglu_native", GLUMLP)
+MLP.register("swiglu_triton", GLUMLP)  # name kept so reference configs load
+MLP.register("geglu", GeGLUMLP)
+MLP.register("gelu", GELUMLP)

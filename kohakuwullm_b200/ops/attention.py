@@ -120,10 +120,13 @@ class _FlashVarlen(torch.autograd.Function):
         dk = torch.empty(T, Hkv, D, dtype=q.dtype, device=q.device)
         dv = torch.empty(T, Hkv, D, dtype=q.dtype, device=q.device)
         delta = torch.empty(Hq, T, dtype=torch.float32, device=q.device)
+        n_scratch = L.kwu_flash_bwd_scratch_floats(c_int(T), c_int(Hq), c_int(Hkv))
+        scratch = torch.empty(n_scratch, dtype=torch.float32, device=q.device) if n_scratch else None
         rc = L.kwu_flash_bwd(
             native.ptr(q), c_int(q.stride(0)), native.ptr(k), c_int(k.stride(0)), native.ptr(v),
             c_int(v.stride(0)), native.ptr(out), native.ptr(dout), native.ptr(lse), native.ptr(delta),
-            native.ptr(dq), native.ptr(dk), native.ptr(dv), native.ptr(plan),
+            native.ptr(dq), native.ptr(dk), c_int(dk.stride(0)), native.ptr(dv), c_int(dv.stride(0)),
+            native.ptr(scratch), native.ptr(plan),
             c_int(plan.shape[0]), c_int(T), c_int(Hq), c_int(Hkv), c_int(ctx.window or 0),
             c_float(ctx.scale), native.stream_ptr(), native.ptr(native.status_word()),
         )
@@ -155,3 +158,100 @@ def varlen_attention(q, k, v, cu_seqlens, max_seqlen=None, window=None, sink_lse
         out, lse = _FlashVarlen.apply(q, k, v, cu_seqlens, plan, window, sink_lse, float(scale))
         return (out, lse) if return_lse else out
     return varlen_attention_reference(q, k, v, cu_seqlens, window, sink_lse, scale, return_lse)
+
+
+# --------------------------------------------------------------------------------- fused core
+class _AttentionCore(torch.autograd.Function):
+    """QK-norm + RoPE + flash attention over a fused ``qkv`` projection output, as ONE autograd node.
+
+    Forward reads q / k / v as strided slices of ``qkv`` (no split copies). Backward writes the three
+    gradient slices straight into one ``dqkv`` buffer: dv by the flash backward kernel, dq / dk by the
+    norm+rope backward kernel, so autograd never materialises zero-padded slice gradients.
+    """
+
+    @staticmethod
+    def forward(ctx, qkv, q_norm, k_norm, cos, sin, cu_seqlens, plan, sink_lse, Hq, Hkv, window, scale,
+                eps, do_norm):
+        from kohakuwullm_b200.ops.elementwise import c_float as cf, c_int as ci
+
+        L = native.require()
+        T = qkv.shape[0]
+        D = 64
+        ld = qkv.stride(0)
+        q_src = qkv[:, : Hq * D]
+        k_src = qkv[:, Hq * D:(Hq + Hkv) * D]
+        v = qkv[:, (Hq + Hkv) * D:].view(T, Hkv, D)
+        q = torch.empty(T, Hq, D, dtype=qkv.dtype, device=qkv.device)
+        k = torch.empty(T, Hkv, D, dtype=qkv.dtype, device=qkv.device)
+        rot_half = 0 if cos is None else cos.shape[-1]
+        for src, dst, w, H in ((q_src, q, q_norm, Hq), (k_src, k, k_norm, Hkv)):
+            rc = L.kwu_qknorm_rope_fwd(native.ptr(src), ci(ld), native.ptr(dst), ci(H * D), native.ptr(w),
+                                       native.ptr(cos), native.ptr(sin), ci(T), ci(H), ci(D), ci(rot_half),
+                                       cf(eps), ci(int(do_norm)), native.stream_ptr())
+            native.check(rc, "qknorm_rope_fwd")
+        out = torch.empty(T, Hq, D, dtype=qkv.dtype, device=qkv.device)
+        lse = torch.empty(Hq, T, dtype=torch.float32, device=qkv.device)
+        rc = L.kwu_flash_fwd(native.ptr(q), ci(Hq * D), native.ptr(k), ci(Hkv * D), native.ptr(v), ci(ld),
+                             native.ptr(out), native.ptr(lse), native.ptr(plan), ci(plan.shape[0]), ci(T),
+                             ci(Hq), ci(Hkv), ci(window or 0), native.ptr(sink_lse), cf(scale),
+                             native.stream_ptr(), native.ptr(native.status_word()))
+        native.check(rc, "flash_fwd")
+        ctx.save_for_backward(qkv, q, k, out, lse, plan, sink_lse, q_norm, k_norm, cos, sin)
+        ctx.cfg = (Hq, Hkv, window, scale, eps, do_norm)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        from kohakuwullm_b200.ops.elementwise import c_float as cf, c_int as ci
+
+        L = native.require()
+        qkv, q, k, out, lse, plan, sink_lse, q_norm, k_norm, cos, sin = ctx.saved_tensors
+        Hq, Hkv, window, scale, eps, do_norm = ctx.cfg
+        T, D = qkv.shape[0], 64
+        ld = qkv.stride(0)
+        dout = dout.contiguous()
+        dqkv = torch.empty_like(qkv)
+        dld = dqkv.stride(0)
+        dq = torch.empty(T, Hq, D, dtype=qkv.dtype, device=qkv.device)
+        dk = torch.empty(T, Hkv, D, dtype=qkv.dtype, device=qkv.device)
+        dv = dqkv[:, (Hq + Hkv) * D:]
+        v = qkv[:, (Hq + Hkv) * D:]
+        delta = torch.empty(Hq, T, dtype=torch.float32, device=qkv.device)
+        n_scratch = L.kwu_flash_bwd_scratch_floats(ci(T), ci(Hq), ci(Hkv))
+        scratch = torch.empty(n_scratch, dtype=torch.float32, device=qkv.device) if n_scratch else None
+        rc = L.kwu_flash_bwd(native.ptr(q), ci(Hq * D), native.ptr(k), ci(Hkv * D), native.ptr(v), ci(ld),
+                             native.ptr(out), native.ptr(dout), native.ptr(lse), native.ptr(delta),
+                             native.ptr(dq), native.ptr(dk), ci(Hkv * D), native.ptr(dv), ci(dld),
+                             native.ptr(scratch), native.ptr(plan), ci(plan.shape[0]), ci(T), ci(Hq), ci(Hkv),
+                             ci(window or 0), cf(scale), native.stream_ptr(), native.ptr(native.status_word()))
+        native.check(rc, "flash_bwd")
+        rot_half = 0 if cos is None else cos.shape[-1]
+        dws = []
+        for src, g, dst, w, H in ((qkv[:, : Hq * D], dq, dqkv[:, : Hq * D], q_norm, Hq),
+                                  (qkv[:, Hq * D:(Hq + Hkv) * D], dk, dqkv[:, Hq * D:(Hq + Hkv) * D], k_norm, Hkv)):
+            dw = torch.zeros(D, dtype=torch.float32, device=qkv.device) if w is not None else None
+            rc = L.kwu_qknorm_rope_bwd(native.ptr(src), ci(ld), native.ptr(g), ci(H * D), native.ptr(dst), ci(dld),
+                                       native.ptr(w), native.ptr(dw), native.ptr(cos), native.ptr(sin), ci(T),
+                                       ci(H), ci(D), ci(rot_half), cf(eps), ci(int(do_norm)), native.stream_ptr())
+            native.check(rc, "qknorm_rope_bwd")
+            dws.append(dw)
+        dsink = None
+        if sink_lse is not None and ctx.needs_input_grad[7]:
+            dsink = -(torch.exp(sink_lse.float()[:, None] - lse) * delta).sum(1).to(sink_lse.dtype)
+        return (dqkv, dws[0], dws[1], None, None, None, None, dsink, None, None, None, None, None, None)
+
+
+def attention_core_supported(qkv, head_dim, q_norm, k_norm, cos) -> bool:
+    return (native.available() and qkv.is_cuda and qkv.dtype == torch.bfloat16 and head_dim == 64
+            and qkv.stride(1) == 1 and (q_norm is None or q_norm.dtype == torch.float32)
+            and (cos is None or (cos.dtype == torch.float32 and cos.shape[-1] in (8, 16, 32))))
+
+
+def attention_core(qkv, q_norm, k_norm, cos, sin, cu_seqlens, plan, sink_lse, Hq, Hkv, window, scale, eps,
+                   do_norm):
+    if plan is None:
+        plan = attention_plan(cu_seqlens, qkv.shape[0])
+    if sink_lse is not None:
+        sink_lse = sink_lse.float()
+    return _AttentionCore.apply(qkv, q_norm, k_norm, cos, sin, cu_seqlens, plan, sink_lse, Hq, Hkv, window,
+                                float(scale), float(eps), bool(do_norm))

@@ -50,6 +50,9 @@ def lib() -> ctypes.CDLL:
             )
     handle = ctypes.CDLL(str(LIB_PATH))
     handle.kwu_last_error.restype = ctypes.c_char_p
+    handle.kwu_launch_count.restype = ctypes.c_longlong
+    if hasattr(handle, "kwu_flash_bwd_scratch_floats"):
+        handle.kwu_flash_bwd_scratch_floats.restype = ctypes.c_longlong
     return handle
 
 

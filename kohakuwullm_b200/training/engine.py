@@ -1,0 +1,251 @@
+"""``TrainEngine``: one optimizer step over packed micro-batches with token-exact accumulation.
+
+The step is free of host synchronisation:
+
+1. the trained-token count of the step is taken from the HOST copy of the labels, summed over the
+   data-parallel group on the device, and kept as a device scalar ``inv_tokens``;
+2. every micro-batch is copied host->device (pinned, non-blocking), run forward with
+   ``reduction="sum"`` and backward with unit scale, so ``main_grad`` accumulates plain sums;
+3. gradient buffers are summed across ranks, the global norm is taken on the device, and the clipping
+   coefficient times ``inv_tokens`` enters the fused AdamW kernel as its ``grad_scale``;
+4. MXFP8 weight copies are re-quantised and router biases updated.
+
+Loss and gradients are therefore identical (up to summation order) for any split of the same tokens
+into micro-batches and ranks. Reference semantics: src/kohakuwullm/training/loop/trainer.py:172-240.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Sequence
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+from kohakuwullm_b200.data.packing import PackedBatch
+from kohakuwullm_b200.ops import native
+from kohakuwullm_b200.parallel.ddp import GradSync
+from kohakuwullm_b200.parallel.flat import FlatParameters
+from kohakuwullm_b200.training.optim.fused_adamw import FlatAdamW
+from kohakuwullm_b200.training.optim.lowbit import cast_parameters_
+
+
+class GraphedMicroStep:
+    """Forward + backward of one packed micro-batch captured in a CUDA graph.
+
+    A 546M-parameter step is several thousand small launches per micro-batch; replaying them from a
+    graph removes the host from the critical path. Shapes are fixed by ``(tokens, max_docs)``:
+    ``cu_seqlens`` is padded with zero-length documents up to ``max_docs`` (they produce no attention
+    tiles), so packs with any number of documents replay the same graph. Inputs are copied straight
+    from (pinned) host memory into the graph's static buffers.
+    """
+
+    def __init__(self, engine: "TrainEngine", tokens: int, max_docs: int):
+        dev = engine.device
+        self.engine, self.tokens, self.max_docs = engine, tokens, max_docs
+        self.tok = torch.zeros(tokens, dtype=torch.long, device=dev)
+        self.lab = torch.full((tokens,), -100, dtype=torch.long, device=dev)
+        self.pos = torch.zeros(tokens, dtype=torch.long, device=dev)
+        self.cu = torch.full((max_docs + 1,), tokens, dtype=torch.int32, device=dev)
+        self.cu[0] = 0
+        self.ce = torch.zeros((), dtype=torch.float32, device=dev)
+        self.extra: dict[str, torch.Tensor] = {}
+        self.graph: torch.cuda.CUDAGraph | None = None
+
+    def _info(self):
+        from kohakuwullm_b200.models.seqinfo import SeqInfo
+
+        return SeqInfo(self.cu, self.pos, self.tokens, self.max_docs, None)
+
+    def load(self, mb: PackedBatch) -> None:
+        n_docs = mb.seq_info.num_seqs
+        if mb.num_tokens != self.tokens or n_docs > self.max_docs:
+            raise ValueError("micro-batch does not fit this graph")
+        self.tok.copy_(mb.tokens, non_blocking=True)
+        self.lab.copy_(mb.labels, non_blocking=True)
+        self.pos.copy_(mb.seq_info.position_ids, non_blocking=True)
+        self.cu[: n_docs + 1].copy_(mb.seq_info.cu_seqlens, non_blocking=True)
+        if n_docs < self.max_docs:
+            self.cu[n_docs + 1:].fill_(self.tokens)
+
+    def _run(self) -> None:
+        eng = self.engine
+        loss, logs = eng.model.loss(self.tok, self.lab, self._info(), reduction="sum",
+                                    router_scale=eng._router_scale)
+        loss.backward()
+        self.ce.copy_(logs["ce"])
+        for k in ("z_loss", "router_loss"):
+            if k in logs:
+                if k not in self.extra:
+                    self.extra[k] = torch.zeros((), dtype=torch.float32, device=eng.device)
+                self.extra[k].copy_(logs[k])
+
+    def capture(self, warmup: int = 2) -> None:
+        eng = self.engine
+        side = torch.cuda.Stream(device=eng.device)
+        side.wait_stream(torch.cuda.current_stream())
+        saved = [b.clone() for b in eng.flat.grad_buffers()]
+        with torch.cuda.stream(side):
+            for _ in range(warmup):
+                self._run()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        lib = native.lib()
+        before = lib.kwu_launch_count()
+        with torch.cuda.graph(self.graph):
+            self._run()
+        self.native_launches = int(lib.kwu_launch_count() - before)  # kernels of this library per replay
+        # warm-up and capture runs must not leak into the real gradients / router statistics
+        for b, s0 in zip(eng.flat.grad_buffers(), saved):
+            b.copy_(s0)
+
+    def replay(self) -> None:
+        self.graph.replay()
+        self.engine.replayed_native_launches += self.native_launches
+
+
+class TrainEngine:
+    def __init__(self, model: nn.Module, *, lr: float = 3e-4, betas=(0.9, 0.95), eps: float = 1e-8,
+                 weight_decay: float = 0.1, max_grad_norm: float = 1.0,
+                 param_dtype: torch.dtype | None = None, group=None, grad_sync: str = "nccl",
+                 device: torch.device | str | None = None, lr_schedule=None,
+                 cuda_graphs: bool | None = None, graph_max_docs: int | None = None):
+        self.model = model
+        if device is not None:
+            model.to(device)
+        self.device = next(model.parameters()).device
+        if param_dtype is not None and param_dtype != torch.float32:
+            cast_parameters_(model, param_dtype)
+        self.flat = FlatParameters(model)
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if self.world > 1 else 0
+        if grad_sync == "fused" and self.world > 1 and self.device.type == "cuda":
+            from kohakuwullm_b200.parallel.fused_ddp import FusedGradSync
+
+            self.sync = FusedGradSync(self.flat, group)
+        else:
+            self.sync = GradSync(self.flat, group)
+        self.optimizer = FlatAdamW(self.flat, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
+        self.max_grad_norm = max_grad_norm
+        self.lr_schedule = lr_schedule
+        self.global_step = 0
+        dev = self.device
+        self._sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
+        self._coef = torch.ones(1, dtype=torch.float32, device=dev)
+        self._norm = torch.zeros(1, dtype=torch.float32, device=dev)
+        self._partial = None
+        self.has_mxfp8 = hasattr(model, "refresh_mxfp8") and getattr(getattr(model, "config", None), "mxfp8", False)
+        self.has_router = hasattr(model, "update_router_bias")
+        self.last_router_stats: dict = {}
+        self.cuda_graphs = (self.device.type == "cuda" and native.available()) if cuda_graphs is None else cuda_graphs
+        self.graph_max_docs = graph_max_docs
+        self._graphs: dict[tuple[int, int], GraphedMicroStep] = {}
+        self.replayed_native_launches = 0
+        self._router_scale = torch.ones(1, dtype=torch.float32, device=dev)
+
+    def _graph_for(self, mb: PackedBatch) -> GraphedMicroStep | None:
+        """Graph matching this micro-batch's token count (captured on first use), or None."""
+        if not self.cuda_graphs:
+            return None
+        T = mb.num_tokens
+        max_docs = self.graph_max_docs or max(8, T // 32)
+        if mb.seq_info.num_seqs > max_docs:
+            return None
+        key = (T, max_docs)
+        g = self._graphs.get(key)
+        if g is None:
+            g = GraphedMicroStep(self, T, max_docs)
+            g.load(mb)
+            router_state = self._snapshot_router()
+            g.capture()
+            self._restore_router(router_state)
+            self._graphs[key] = g
+        return g
+
+    def native_launch_total(self) -> int:
+        """Kernels of the native library launched so far: direct launches plus graph replays."""
+        return int(native.lib().kwu_launch_count()) + self.replayed_native_launches
+
+    def _snapshot_router(self):
+        return [b.clone() for n, b in self.model.named_buffers() if n.endswith("load_accum")]
+
+    def _restore_router(self, saved):
+        bufs = [b for n, b in self.model.named_buffers() if n.endswith("load_accum")]
+        for b, s0 in zip(bufs, saved):
+            b.copy_(s0)
+
+    # ------------------------------------------------------------------
+    def _grad_norm_and_coef(self, inv_tokens: torch.Tensor) -> None:
+        bufs = self.flat.grad_buffers()
+        if self.device.type == "cuda" and native.available():
+            L = native.require()
+            if self._partial is None:
+                self._partial = torch.empty(L.kwu_sumsq_blocks(), dtype=torch.float32, device=self.device)
+            for i, b in enumerate(bufs):
+                rc = L.kwu_sumsq_flat(native.ptr(b), ctypes.c_longlong(b.numel()), native.ptr(self._partial),
+                                      native.ptr(self._sumsq), ctypes.c_int(int(i > 0)), native.stream_ptr())
+                native.check(rc, "sumsq_flat")
+            rc = L.kwu_clip_coef(native.ptr(self._sumsq), native.ptr(inv_tokens),
+                                 ctypes.c_float(self.max_grad_norm or 0.0), native.ptr(self._coef),
+                                 native.ptr(self._norm), native.stream_ptr())
+            native.check(rc, "clip_coef")
+        else:
+            sq = sum((b.double() ** 2).sum() for b in bufs).float()
+            norm = sq.sqrt() * inv_tokens
+            self._norm.copy_(norm.reshape(1))
+            coef = inv_tokens.clone().reshape(1)
+            if self.max_grad_norm:
+                coef = coef * torch.clamp(self.max_grad_norm / (norm + 1e-6), max=1.0)
+            self._coef.copy_(coef.reshape(1))
+
+    def step(self, micro_batches: Sequence[PackedBatch]) -> dict[str, torch.Tensor]:
+        model = self.model
+        model.train()
+        dev = self.device
+        local_tokens = sum(mb.trained_tokens() for mb in micro_batches)
+        tok = torch.tensor([float(local_tokens)], dtype=torch.float32).to(dev, non_blocking=True)
+        self.sync.all_reduce_scalar(tok)
+        inv_tokens = 1.0 / tok.clamp(min=1.0)
+        # router auxiliary terms are per-micro-batch means: weight them like one rank's share of tokens
+        self._router_scale.copy_(tok / (self.world * max(len(micro_batches), 1)))
+        ce_total = torch.zeros((), dtype=torch.float32, device=dev)
+        extra: dict[str, torch.Tensor] = {}
+        for mb in micro_batches:
+            graph = self._graph_for(mb)
+            if graph is not None:
+                graph.load(mb)
+                graph.replay()
+                ce_total = ce_total + graph.ce
+                for k, v in graph.extra.items():
+                    extra[k] = extra.get(k, 0) + v
+                continue
+            mb = mb.to(dev, non_blocking=True)
+            loss, logs = model.loss(mb.tokens, mb.labels, mb.seq_info, reduction="sum",
+                                    router_scale=self._router_scale)
+            loss.backward()
+            ce_total = ce_total + logs["ce"]
+            for k in ("z_loss", "router_loss"):
+                if k in logs:
+                    extra[k] = extra.get(k, 0) + logs[k]
+        self.sync.reduce()
+        self._grad_norm_and_coef(inv_tokens)
+        if self.lr_schedule is not None:
+            self.optimizer.param_groups[0]["lr"] = self.lr_schedule(self.global_step)
+        if local_tokens > 0 or self.world > 1:
+            self.optimizer.step(grad_scale=self._coef, zero_grad=True)
+            if self.has_mxfp8:
+                model.refresh_mxfp8()
+        else:
+            self.flat.zero_grad()  # an all-masked step updates nothing
+        if self.has_router:
+            self.last_router_stats = model.update_router_bias()
+        self.global_step += 1
+        ce_all = self.sync.all_reduce_scalar(ce_total.reshape(1).clone()) if self.world > 1 else ce_total.reshape(1)
+        out = {"loss": (ce_all * inv_tokens).reshape(()), "grad_norm": self._norm.reshape(()).clone(),
+               "tokens": tok.reshape(())}
+        for k, v in extra.items():
+            out[k] = v * inv_tokens.reshape(())
+        return out

@@ -83,3 +83,39 @@ def test_packed_attention_does_not_cross_documents():
     assert torch.equal(out1[:200], out2[:200])
     assert torch.equal(out1[500:], out2[500:])
     assert not torch.equal(out1[200:500], out2[200:500])
+
+
+def test_attention_layer_fused_core_matches_unfused():
+    """The fused QK-norm + RoPE + flash node must give the same output and gradients as the
+    composition of the separate ops (which are tested against fp32 references above)."""
+    from kohakuwullm_b200.models.components.attention import Attention, SDPAAttention
+    from kohakuwullm_b200.models.components.posenc import RoPE
+    from kohakuwullm_b200.models.seqinfo import SeqInfo
+
+    torch.manual_seed(0)
+    info = SeqInfo.from_lengths([300, 212], device="cuda")
+    T = info.total_tokens
+    kw = dict(dim=256, heads=4, kv_heads=2, head_dim=64, window=100, sink=True, num_sinks=2)
+    a = Attention(**kw).cuda()
+    b = SDPAAttention(**kw).cuda()
+    for p in a.parameters():
+        if p.dim() >= 2:
+            torch.nn.init.normal_(p, std=0.05)
+    b.load_state_dict(a.state_dict())
+    for m in (a, b):
+        for n, p in m.named_parameters():
+            if p.dim() >= 2 and "sink" not in n:
+                p.data = p.data.to(torch.bfloat16)
+    rope = RoPE(64).cuda().prepare(info.position_ids)
+    x = torch.randn(T, 256, device="cuda", dtype=torch.bfloat16)
+    dy = torch.randn(T, 256, device="cuda", dtype=torch.bfloat16)
+    outs = []
+    for m in (a, b):
+        xi = x.clone().requires_grad_()
+        y = m(xi, info, rope)
+        y.backward(dy)
+        outs.append((y, xi.grad, m.qkv_proj.weight.grad, m.sink.grad, m.q_norm.grad))
+    for got, want in zip(*outs):
+        err = (got.float() - want.float()).abs().max().item()
+        scale = max(want.float().abs().max().item(), 1e-6)
+        assert err <= 4e-2 * scale, f"err {err} scale {scale}"
