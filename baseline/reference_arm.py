@@ -2,7 +2,7 @@
 driven through its own public API and stock code path, for the same metric and config.
 
 The step mirrors what the reference's own end-to-end harness does
-(scripts/bench/e2e/step_throughput.py:100-195): ``LMBackbone(cfg)`` -> ``cast_parameters_`` ->
+(scripts/bench/e2e/step_throughput.py:100-195): ``LMBackbone(cfg)`` (fp32 parameters) ->
 ``swap_mxfp8`` -> ``build_optimizer("fused_adamw")`` -> per micro-batch ``loss(reduction="sum")`` under
 bf16 autocast, ``(loss/total).backward()``, DDP ``no_sync`` on all but the last micro-batch,
 ``opt.step()``, ``refresh_mxfp8_weights``. Synthetic packs come from the reference's own
@@ -90,8 +90,9 @@ def run_reference(args, micro_tokens, grad_accum, len_min, len_max, metric, Cloc
         # torch 2.11's varlen_attn has no ``enable_gqa`` argument, so the reference's default "varlen"
         # backend cannot run here; its own Triton flash-attention backend is selected instead.
         cfg = get_preset("Kohaku-500M", depth=24, mlp_hidden=3584, rope_theta=500000.0, attn=args.ref_attn)
+        # fp32 parameters under bf16 autocast with fused AdamW: the reference harness's default arm
+        # (its FusedAdamW refuses 16-bit parameters)
         model = LMBackbone(cfg).to(device=dev, dtype=torch.float32)
-        cast_parameters_(model, torch.bfloat16)
         expect_refresh = 0
         if use_mxfp8:
             report = swap_mxfp8(model)

@@ -1,0 +1,459 @@
+// MXFP8: e4m3 values with one UE8M0 (power-of-two) scale per 32 elements along the contraction axis.
+//
+//   kwu_mxfp8_quantize     (M,K) bf16 -> (M,K) e4m3 + scales, blocks along K (rows stay rows)
+//   kwu_mxfp8_quantize_t   (R,C) bf16 -> (C,R) e4m3 + scales, blocks along R: the transposed copy a
+//                          dgrad needs (dx = dy W contracts over the rows of W)
+//   kwu_gemm_mxfp8         C[M,N] (+)= A[M,K] B[N,K]^T with tcgen05.mma.kind::mxf8f6f4.block_scale
+//
+// Scale layout: the one the tensor core consumes from TMEM. For every 128-row x 128-column tile of
+// the matrix there is one 512-byte chunk; inside it the scale of row r, 32-block j sits at byte
+// (r % 32) * 16 + (r / 32) * 4 + j. Chunks are ordered [row_tile][k_chunk]. A chunk is moved
+// global -> shared by one bulk copy and shared -> TMEM by one tcgen05.cp.32x128b.warpx4.
+// Exponent rule: exp = max(ceil(log2(amax / 448)), -127) (round UP so nothing saturates), amax
+// clamped at 1e-30, stored as exp + 127; values are divided by 2^exp and rounded to e4m3 (satfinite).
+// Rows beyond M inside the last 128-row tile get the neutral scale byte 127 so that padded rows can
+// never inject a NaN scale. Reference: src/kohakuwullm/kernels/mxfp8/quantize.py:39-215 and the
+// cuBLASLt path behind src/kohakuwullm/kernels/mxfp8/linear.py:49-126.
+#include "common.cuh"
+
+namespace kwu {
+
+// ------------------------------------------------------------------------------------ quantise
+__device__ __forceinline__ uint32_t ue8m0_from_amax(float amax) {
+  amax = fmaxf(amax, 1e-30f);
+  const float v = amax * (1.0f / 448.0f);
+  const uint32_t bits = __float_as_uint(v);
+  uint32_t e = (bits >> 23) & 0xffu;
+  if (bits & 0x7fffffu) e += 1;  // ceil(log2(v))
+  return min(e, 254u);
+}
+__device__ __forceinline__ float inv_scale_from_ue8m0(uint32_t e) {
+  // 2^-(e-127) = 2^(127-e): biased exponent 254 - e (e = 254 would be a denormal; clamp)
+  const uint32_t be = (e >= 254u) ? 1u : (254u - e);
+  return __uint_as_float(be << 23);
+}
+__device__ __forceinline__ size_t sf_offset(int row, int kblock, int n_kchunks) {
+  const int rt = row >> 7, r = row & 127;
+  return (static_cast<size_t>(rt) * n_kchunks + (kblock >> 2)) * 512 + (r & 31) * 16 + (r >> 5) * 4 +
+         (kblock & 3);
+}
+
+// One thread = 8 consecutive elements; 4 threads = one 32-block; a warp covers 256 columns of a row.
+__global__ void __launch_bounds__(256)
+mxfp8_quantize_kernel(const __nv_bfloat16* __restrict__ x, int ldx, uint8_t* __restrict__ q, int ldq,
+                      uint8_t* __restrict__ sf, int M, int K, int M_pad) {
+  const int lane = threadIdx.x & 31;
+  const int n_kchunks = K >> 7;
+  const int segs = (K + 255) >> 8;  // 256-column segments per row
+  const long total = static_cast<long>(M_pad) * segs;
+  const int wpb = blockDim.x >> 5;
+  for (long w = static_cast<long>(blockIdx.x) * wpb + (threadIdx.x >> 5); w < total;
+       w += static_cast<long>(gridDim.x) * wpb) {
+    const int row = static_cast<int>(w / segs);
+    const int col = static_cast<int>(w % segs) * 256 + lane * 8;
+    const bool in_col = col < K;
+    float f[8];
+    if (row < M && in_col) {
+      const uint4 a = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * ldx + col);
+      float2 t;
+      t = unpack_bf16(a.x); f[0] = t.x; f[1] = t.y;
+      t = unpack_bf16(a.y); f[2] = t.x; f[3] = t.y;
+      t = unpack_bf16(a.z); f[4] = t.x; f[5] = t.y;
+      t = unpack_bf16(a.w); f[6] = t.x; f[7] = t.y;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = 0.f;
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    const uint32_t e8 = (row < M) ? ue8m0_from_amax(amax) : 127u;
+    if (in_col) {
+      if (row < M) {
+        const float inv = inv_scale_from_ue8m0(e8);
+        uint32_t lo = 0, hi = 0;
+#pragma unroll
+        for (int e = 0; e < 4; e += 2) {
+          const __nv_fp8x2_storage_t a2 = __nv_cvt_float2_to_fp8x2(make_float2(f[e] * inv, f[e + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+          const __nv_fp8x2_storage_t b2 = __nv_cvt_float2_to_fp8x2(make_float2(f[e + 4] * inv, f[e + 5] * inv), __NV_SATFINITE, __NV_E4M3);
+          lo |= static_cast<uint32_t>(a2) << (8 * e);
+          hi |= static_cast<uint32_t>(b2) << (8 * e);
+        }
+        *reinterpret_cast<uint2*>(q + static_cast<size_t>(row) * ldq + col) = make_uint2(lo, hi);
+      }
+      if ((lane & 3) == 0) sf[sf_offset(row, col >> 5, n_kchunks)] = static_cast<uint8_t>(e8);
+    }
+  }
+}
+
+// Transposed quantise: input (R, C) row-major, output qT (C, R) with blocks of 32 along R.
+// A block handles a 32 (rows) x 64 (cols) input tile: thread t < 64 owns column c0 + t.
+__global__ void __launch_bounds__(64)
+mxfp8_quantize_t_kernel(const __nv_bfloat16* __restrict__ x, int ldx, uint8_t* __restrict__ qT, int ldq,
+                        uint8_t* __restrict__ sf, int R, int C, int C_pad) {
+  const int r0 = blockIdx.y * 32;
+  const int c = blockIdx.x * 64 + threadIdx.x;
+  if (c >= C_pad) return;
+  const int n_kchunks = (R + 127) >> 7;  // contraction axis of the output is R
+  float v[32];
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const int r = r0 + i;
+    v[i] = (r < R && c < C) ? __bfloat162float(x[static_cast<size_t>(r) * ldx + c]) : 0.f;
+    amax = fmaxf(amax, fabsf(v[i]));
+  }
+  const uint32_t e8 = (c < C) ? ue8m0_from_amax(amax) : 127u;
+  if (r0 < R) sf[sf_offset(c, r0 >> 5, n_kchunks)] = static_cast<uint8_t>(e8);
+  if (c < C) {
+    const float inv = inv_scale_from_ue8m0(e8);
+    uint32_t w[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const __nv_fp8x2_storage_t a2 = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * j] * inv, v[4 * j + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+      const __nv_fp8x2_storage_t b2 = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * j + 2] * inv, v[4 * j + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+      w[j] = static_cast<uint32_t>(a2) | (static_cast<uint32_t>(b2) << 16);
+    }
+    uint4* dst = reinterpret_cast<uint4*>(qT + static_cast<size_t>(c) * ldq + r0);
+    if (r0 + 32 <= R) {
+      dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+      dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    } else {
+      uint8_t* d8 = qT + static_cast<size_t>(c) * ldq + r0;
+      for (int i = 0; i < 32 && r0 + i < R; ++i) d8[i] = static_cast<uint8_t>(w[i >> 2] >> (8 * (i & 3)));
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------ GEMM
+constexpr int MX_BM = 128;
+constexpr int MX_BK = 128;  // 128 e4m3 = one 128-byte swizzle row = four K=32 MMAs = one scale chunk
+constexpr int MX_THREADS = 192;
+
+struct MxGemmParams {
+  int M, N, K;
+  int ldc;
+  int out_fp32, accumulate;
+  float alpha;
+  const uint8_t* sfa;  // scale chunks of A: [ceil(M/128)][K/128][512]
+  const uint8_t* sfb;  // scale chunks of B: [ceil(N/128)][K/128][512]
+  int tiles_m, tiles_n;
+  int* status;
+};
+
+template <int BN>
+struct MxSmem {
+  static constexpr int A_BYTES = MX_BM * MX_BK;
+  static constexpr int B_BYTES = BN * MX_BK;
+  static constexpr int SFB_CHUNKS = (BN + 127) / 128;
+  static constexpr int SF_BYTES = 512 + SFB_CHUNKS * 512;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + 1024;  // data + scale area (padded to 1 KB)
+  static constexpr int STAGES = (BN > 192) ? 4 : ((BN > 128) ? 5 : 6);
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 + 1024;
+};
+
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      :
+      : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+
+template <int BN>
+__global__ void __launch_bounds__(MX_THREADS, 1)
+gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                  void* __restrict__ Cout, const MxGemmParams p) {
+  using S = MxSmem<BN>;
+  constexpr int STAGES = S::STAGES;
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t SFA_COL = 2 * BN;
+  constexpr uint32_t SFB_COL = 2 * BN + 4;
+  static_assert(2 * BN + 4 + 4 * S::SFB_CHUNKS <= 512, "accumulators + scales must fit in TMEM");
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* bar_area = smem + STAGES * S::STAGE_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_area);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* acc_full = empty_bar + STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int num_kb = p.K / MX_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&acc_full[s], 1);
+      mbar_init(&acc_empty[s], 128);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int tm = tile / p.tiles_n, tn = tile % p.tiles_n;
+        const int m0 = tm * MX_BM, n0 = tn * BN;
+        // scale chunks of this tile's rows: A rows [m0, m0+128) are row tile tm; B rows [n0, n0+BN)
+        // start at 128-row tile n0/128 (BN is a multiple of 16, n0 may start mid-chunk only when
+        // BN is not a multiple of 128: the chunk pair covering [n0, n0+BN) is loaded and the row
+        // offset inside it is applied through the TMEM lane/column arithmetic below).
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * S::STAGE_BYTES;
+          uint8_t* sb = sa + S::A_BYTES;
+          uint8_t* ssf = sb + S::B_BYTES;
+          mbar_expect_tx(&full_bar[stage], S::A_BYTES + S::B_BYTES + S::SF_BYTES);
+          tma_load_2d(sa, &tmA, &full_bar[stage], kb * MX_BK, m0);
+          tma_load_2d(sb, &tmB, &full_bar[stage], kb * MX_BK, n0);
+          bulk_load_1d(ssf, p.sfa + (static_cast<size_t>(tm) * num_kb + kb) * 512, 512, &full_bar[stage]);
+#pragma unroll
+          for (int c = 0; c < S::SFB_CHUNKS; ++c)
+            bulk_load_1d(ssf + 512 + c * 512,
+                         p.sfb + (static_cast<size_t>(n0 / 128 + c) * num_kb + kb) * 512, 512, &full_bar[stage]);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+        const int as = it & 1;
+        const uint32_t aphase = (it >> 1) & 1;
+        if (!mbar_wait(&acc_empty[as], aphase ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_EMPTY)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + as * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * S::STAGE_BYTES);
+          const uint32_t sb = sa + S::A_BYTES;
+          const uint32_t ssf = sb + S::B_BYTES;
+          // scale chunks: shared -> TMEM (32 rows x 16 B each, 8-row groups 128 B apart, no swizzle)
+          tc_cp_32x128b_warpx4(tmem_base + SFA_COL, make_smem_desc(ssf, 16, 128, SWZ_NONE));
+#pragma unroll
+          for (int c = 0; c < S::SFB_CHUNKS; ++c)
+            tc_cp_32x128b_warpx4(tmem_base + SFB_COL + 4 * c, make_smem_desc(ssf + 512 + 512 * c, 16, 128, SWZ_NONE));
+#pragma unroll
+          for (int k = 0; k < MX_BK / 32; ++k) {
+            const uint64_t ad = make_smem_desc(sa + k * 32, 16, 1024, SWZ_128B);
+            const uint64_t bd = make_smem_desc(sb + k * 32, 16, 1024, SWZ_128B);
+            mma_mxf8_ss(d_tmem, ad, bd, make_idesc_mxf8(MX_BM, BN, k, k), tmem_base + SFA_COL,
+                        tmem_base + SFB_COL, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(&empty_bar[stage]);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) tc_commit(&acc_full[as]);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    int it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+      const int as = it & 1;
+      const uint32_t aphase = (it >> 1) & 1;
+      const int m0 = (tile / p.tiles_n) * MX_BM;
+      const int n0 = (tile % p.tiles_n) * BN;
+      ok = mbar_wait(&acc_full[as], aphase, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_FULL);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int row = m0 + quarter * 32 + lane;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + as * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_x32(t_row + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (row < p.M && col0 < p.N) {
+          const bool full = (col0 + 32 <= p.N);
+          if (p.out_fp32) {
+            float* dst = reinterpret_cast<float*>(Cout) + static_cast<size_t>(row) * p.ldc + col0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (full || col0 + j < p.N) {
+                float v = __uint_as_float(r[j]) * p.alpha;
+                if (p.accumulate) v += dst[j];
+                dst[j] = v;
+              }
+            }
+          } else {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(Cout) + static_cast<size_t>(row) * p.ldc + col0;
+            if (full) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float f[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[8 * j + e]) * p.alpha;
+                uint4* d4 = reinterpret_cast<uint4*>(dst) + j;
+                if (p.accumulate) {
+                  const uint4 o = *d4;
+                  const float2 o0 = unpack_bf16(o.x), o1 = unpack_bf16(o.y), o2 = unpack_bf16(o.z), o3 = unpack_bf16(o.w);
+                  f[0] += o0.x; f[1] += o0.y; f[2] += o1.x; f[3] += o1.y;
+                  f[4] += o2.x; f[5] += o2.y; f[6] += o3.x; f[7] += o3.y;
+                }
+                *d4 = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                if (col0 + j < p.N) {
+                  float v = __uint_as_float(r[j]) * p.alpha;
+                  if (p.accumulate) v += __bfloat162float(dst[j]);
+                  dst[j] = __float2bfloat16(v);
+                }
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&acc_empty[as]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag)
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int BN>
+static int launch_mx(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                     const uint8_t* sfa, const uint8_t* sfb, int out_fp32, int accumulate, float alpha,
+                     cudaStream_t stream, int* status) {
+  using S = MxSmem<BN>;
+  CUtensorMap tmA, tmB;
+  int rc;
+  if ((rc = encode_tmap_2d(&tmA, A, ELEM_U8, M, K, lda, MX_BM, MX_BK, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  if ((rc = encode_tmap_2d(&tmB, B, ELEM_U8, N, K, ldb, BN, MX_BK, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  MxGemmParams p;
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.out_fp32 = out_fp32; p.accumulate = accumulate; p.alpha = alpha;
+  p.sfa = sfa; p.sfb = sfb;
+  p.tiles_m = (M + MX_BM - 1) / MX_BM;
+  p.tiles_n = (N + BN - 1) / BN;
+  p.status = status;
+  auto kern = gemm_mxfp8_kernel<BN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    if (e != cudaSuccess) { set_last_error("gemm_mxfp8 attr: %s", cudaGetErrorString(e)); return 10; }
+    attr_set = true;
+  }
+  int sms = 0, dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  int grid = p.tiles_m * p.tiles_n;
+  if (grid > sms) grid = sms;
+  kern<<<grid, MX_THREADS, S::TOTAL, stream>>>(tmA, tmB, C, p); kwu::count_launch();
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { set_last_error("gemm_mxfp8 launch: %s", cudaGetErrorString(e)); return 11; }
+  return 0;
+}
+
+// B's scale chunks are indexed by 128-row tiles, so a column tile must start on a 128 boundary:
+// BN is restricted to multiples of 128 unless a single tile covers all of N.
+static int pick_bn_mx(int M, int N, int forced) {
+  if (forced == 128) return 128;
+  // BN = 128 is the only width whose tiles always start on a scale-chunk boundary
+  return 128;
+}
+
+}  // namespace kwu
+
+using namespace kwu;
+
+// Bytes of the scale buffer of a (rows, K) operand.
+KWU_API long long kwu_mxfp8_sf_bytes(int rows, int K) {
+  return static_cast<long long>((rows + 127) / 128) * (K / 128) * 512;
+}
+
+KWU_API int kwu_mxfp8_quantize(const void* x, int ldx, void* q, int ldq, void* sf, int M, int K, void* stream) {
+  if (K % 128) { set_last_error("mxfp8_quantize: K must be a multiple of 128 (got %d)", K); return 7; }
+  if (M <= 0) return 0;
+  const int M_pad = (M + 127) / 128 * 128;
+  long warps = static_cast<long>(M_pad) * ((K + 255) / 256);
+  long grid = (warps + 7) / 8;
+  if (grid > 148 * 16) grid = 148 * 16;
+  mxfp8_quantize_kernel<<<static_cast<int>(grid), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      (const __nv_bfloat16*)x, ldx, (uint8_t*)q, ldq, (uint8_t*)sf, M, K, M_pad); kwu::count_launch();
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { set_last_error("mxfp8_quantize launch: %s", cudaGetErrorString(e)); return 11; }
+  return 0;
+}
+
+// x (R, C) -> qT (C, R) quantised along R; sf has kwu_mxfp8_sf_bytes(C, R) bytes. R % 128 == 0.
+KWU_API int kwu_mxfp8_quantize_t(const void* x, int ldx, void* qT, int ldq, void* sf, int R, int C, void* stream) {
+  if (R % 128) { set_last_error("mxfp8_quantize_t: R must be a multiple of 128 (got %d)", R); return 7; }
+  if (C <= 0) return 0;
+  const int C_pad = (C + 127) / 128 * 128;
+  dim3 grid((C_pad + 63) / 64, R / 32);
+  mxfp8_quantize_t_kernel<<<grid, 64, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      (const __nv_bfloat16*)x, ldx, (uint8_t*)qT, ldq, (uint8_t*)sf, R, C, C_pad); kwu::count_launch();
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { set_last_error("mxfp8_quantize_t launch: %s", cudaGetErrorString(e)); return 11; }
+  return 0;
+}
+
+KWU_API int kwu_gemm_mxfp8(const void* A, const void* sfa, const void* B, const void* sfb, void* C, int M,
+                           int N, int K, int lda, int ldb, int ldc, int out_fp32, int accumulate,
+                           float alpha, int bn, void* stream, int* status) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K % 128) { set_last_error("gemm_mxfp8: K must be a multiple of 128 (got %d)", K); return 7; }
+  const int BN = pick_bn_mx(M, N, bn);
+  (void)BN;
+  return launch_mx<128>(A, B, C, M, N, K, lda, ldb, ldc, (const uint8_t*)sfa, (const uint8_t*)sfb, out_fp32,
+                        accumulate, alpha, reinterpret_cast<cudaStream_t>(stream), status);
+}

@@ -39,6 +39,16 @@ static EncodeTiledFn get_encode() {
 
 int encode_tmap_2d(CUtensorMap* out, const void* base, int elem_kind, uint64_t rows, uint64_t cols,
                    uint64_t ld_elems, uint32_t box_rows, uint32_t box_cols, int swizzle) {
+  // The driver call needs a context bound to THIS thread (autograd runs backward on its own threads,
+  // which may not have touched the runtime yet): binding the current device's primary context is cheap.
+  static thread_local bool bound = false;
+  if (!bound) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaSetDevice(dev);
+    cudaFree(nullptr);
+    bound = true;
+  }
   EncodeTiledFn fn = get_encode();
   if (!fn) {
     set_last_error("cuTensorMapEncodeTiled entry point unavailable");

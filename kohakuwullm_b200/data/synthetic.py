@@ -30,7 +30,8 @@ def draw_lengths(total: int, len_min: int, len_max: int, gen: torch.Generator, l
         used += n
     # a trailing 1-token document has no target; merge it into its neighbour
     if len(lengths) > 1 and lengths[-1] == 1:
-        lengths[-2] += lengths.pop()
+        last = lengths.pop()
+        lengths[-1] += last
     return lengths
 
 

@@ -32,8 +32,35 @@ class Linear(nn.Module):
         self.in_features, self.out_features = in_features, out_features
         self.weight = nn.Parameter(torch.empty(out_features, in_features))
         self.bias = nn.Parameter(torch.zeros(out_features)) if bias else None
+        # set by swap_mxfp8: marks the layer as MXFP8; the quantised copies are built lazily on the
+        # weight's device and dropped whenever the module is moved or cast
+        self.mxfp8 = False
+        self._qweight = None
+
+    def _apply(self, fn, recurse=True):
+        self._qweight = None
+        return super()._apply(fn, recurse)
+
+    def quantized_weight(self):
+        from kohakuwullm_b200.ops.mxfp8 import QuantizedWeight
+
+        if self._qweight is None:
+            self._qweight = QuantizedWeight(self.weight.detach())
+        return self._qweight
+
+    def refresh_quantized_weight(self) -> bool:
+        """Re-quantise after an optimizer step. Returns True when this layer holds MXFP8 copies."""
+        if not self.mxfp8 or self._qweight is None:
+            return self.mxfp8
+        self._qweight.refresh(self.weight.detach())
+        return True
 
     def forward(self, x):
+        if self.mxfp8 and self.bias is None:
+            from kohakuwullm_b200.ops import mxfp8 as mx
+
+            if mx.supported(x, self.weight):
+                return mx.mxfp8_linear(x, self.weight, self.quantized_weight())
         return linear(x, self.weight, self.bias)
 
     def extra_repr(self):

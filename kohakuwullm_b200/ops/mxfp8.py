@@ -1,0 +1,178 @@
+"""MXFP8 (e4m3 + UE8M0 per-32 block scales) quantisation, block-scaled GEMM and the MXFP8 linear.
+
+Recipe of one linear layer ``y = x W^T`` (reference: src/kohakuwullm/kernels/mxfp8/linear.py:49-126):
+
+=========  =================================================  ==========================
+product    operands                                           precision
+=========  =================================================  ==========================
+FPROP      ``x`` quantised along K  x  ``W`` quantised along K   MXFP8, fp32 accumulate
+DGRAD      ``dy`` quantised along N x  ``W^T`` quantised along N  MXFP8, fp32 accumulate
+WGRAD      ``dy^T x`` in bf16, accumulated into ``main_grad``    bf16 inputs, fp32 accumulate
+=========  =================================================  ==========================
+
+The two weight copies (``W`` along K and the transposed copy ``W^T`` along N) are cached on the
+parameter and rebuilt by ``refresh_weight`` after every optimizer step. Activations are quantised on
+the fly. Quantisation rule: ``exp = max(ceil(log2(amax/448)), -127)``, value ``x / 2^exp`` rounded to
+e4m3 with saturation (src/kohakuwullm/kernels/mxfp8/quantize.py:39-56).
+
+``quantize_reference`` / ``dequantize`` restate the rule in PyTorch (bit-exact oracle of the kernel);
+scales are kept in the tensor-core layout described in ``csrc/mxfp8.cu`` and converted by
+``sf_to_natural`` for inspection.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from kohakuwullm_b200.ops import native
+from kohakuwullm_b200.ops.gemm import matmul
+
+c_int, c_float = ctypes.c_int, ctypes.c_float
+E4M3_MAX = 448.0
+
+
+# ------------------------------------------------------------------------------------ reference
+def quantize_reference(x: torch.Tensor):
+    """(M,K) -> (q float8_e4m3fn (M,K), exp uint8 (M,K/32)) with the exponent rule above."""
+    M, K = x.shape
+    xb = x.float().view(M, K // 32, 32)
+    amax = xb.abs().amax(-1).clamp(min=1e-30)
+    exp = torch.ceil(torch.log2(amax / E4M3_MAX)).clamp(min=-127, max=127)
+    # exact ceil(log2) from the float bits (log2 of a float can be off by one ulp near powers of two)
+    bits = (amax / E4M3_MAX).view(torch.int32)
+    e = ((bits >> 23) & 0xFF) + ((bits & 0x7FFFFF) != 0).to(torch.int32)
+    e = e.clamp(max=254)
+    del exp
+    inv = torch.where(e >= 254, torch.full_like(e, 1), 254 - e)
+    inv_scale = (inv << 23).view(torch.float32)
+    q = (xb * inv_scale[..., None]).clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn).view(M, K)
+    return q, e.to(torch.uint8)
+
+
+def dequantize(q: torch.Tensor, e_natural: torch.Tensor) -> torch.Tensor:
+    M, K = q.shape
+    scale = torch.pow(2.0, e_natural.float() - 127.0)
+    return (q.float().view(M, K // 32, 32) * scale[..., None]).view(M, K)
+
+
+def sf_to_natural(sf: torch.Tensor, rows: int, K: int) -> torch.Tensor:
+    """Tensor-core scale layout -> (rows, K/32) uint8."""
+    nk = K // 128
+    rt = (rows + 127) // 128
+    chunks = sf.view(rt, nk, 32, 4, 4)             # [row_tile][k_chunk][r%32][r/32][k_block]
+    nat = chunks.permute(0, 3, 2, 1, 4).reshape(rt * 128, nk * 4)
+    return nat[:rows].contiguous()
+
+
+# ------------------------------------------------------------------------------------ native ops
+def sf_bytes(rows: int, K: int) -> int:
+    return ((rows + 127) // 128) * (K // 128) * 512
+
+
+def quantize(x: torch.Tensor, out_q: torch.Tensor | None = None, out_sf: torch.Tensor | None = None):
+    """bf16 (M,K) -> (q uint8 (M,K), sf uint8 chunks); blocks along K."""
+    L = native.require()
+    M, K = x.shape
+    q = out_q if out_q is not None else torch.empty(M, K, dtype=torch.uint8, device=x.device)
+    sf = out_sf if out_sf is not None else torch.empty(sf_bytes(M, K), dtype=torch.uint8, device=x.device)
+    rc = L.kwu_mxfp8_quantize(native.ptr(x), c_int(x.stride(0)), native.ptr(q), c_int(q.stride(0)),
+                              native.ptr(sf), c_int(M), c_int(K), native.stream_ptr())
+    native.check(rc, "mxfp8_quantize")
+    return q, sf
+
+
+def quantize_transposed(x: torch.Tensor, out_q=None, out_sf=None):
+    """bf16 (R,C) -> (qT uint8 (C,R), sf chunks of a (C,R) operand); blocks along R."""
+    L = native.require()
+    R, C = x.shape
+    q = out_q if out_q is not None else torch.empty(C, R, dtype=torch.uint8, device=x.device)
+    sf = out_sf if out_sf is not None else torch.empty(sf_bytes(C, R), dtype=torch.uint8, device=x.device)
+    rc = L.kwu_mxfp8_quantize_t(native.ptr(x), c_int(x.stride(0)), native.ptr(q), c_int(q.stride(0)),
+                                native.ptr(sf), c_int(R), c_int(C), native.stream_ptr())
+    native.check(rc, "mxfp8_quantize_t")
+    return q, sf
+
+
+def gemm(a_q, a_sf, b_q, b_sf, out=None, out_dtype=torch.bfloat16, accumulate=False, alpha=1.0):
+    """``out (+)= alpha * A B^T`` with A (M,K), B (N,K) both e4m3 with per-32 scales along K."""
+    L = native.require()
+    M, K = a_q.shape
+    N = b_q.shape[0]
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype, device=a_q.device)
+    rc = L.kwu_gemm_mxfp8(native.ptr(a_q), native.ptr(a_sf), native.ptr(b_q), native.ptr(b_sf), native.ptr(out),
+                          c_int(M), c_int(N), c_int(K), c_int(a_q.stride(0)), c_int(b_q.stride(0)),
+                          c_int(out.stride(0)), c_int(int(out.dtype == torch.float32)), c_int(int(accumulate)),
+                          c_float(alpha), c_int(0), native.stream_ptr(), native.ptr(native.status_word()))
+    native.check(rc, "gemm_mxfp8")
+    return out
+
+
+# ------------------------------------------------------------------------------------ linear
+class QuantizedWeight:
+    """The two MXFP8 copies of one weight matrix (N,K): ``W`` along K and ``W^T`` along N."""
+
+    def __init__(self, weight: torch.Tensor):
+        N, K = weight.shape
+        dev = weight.device
+        self.q = torch.empty(N, K, dtype=torch.uint8, device=dev)
+        self.sf = torch.empty(sf_bytes(N, K), dtype=torch.uint8, device=dev)
+        self.qt = torch.empty(K, N, dtype=torch.uint8, device=dev)
+        self.sft = torch.empty(sf_bytes(K, N), dtype=torch.uint8, device=dev)
+        self.refresh(weight)
+
+    @torch.no_grad()
+    def refresh(self, weight: torch.Tensor) -> None:
+        quantize(weight, self.q, self.sf)
+        quantize_transposed(weight, self.qt, self.sft)
+
+
+class _MXFP8Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, qw: QuantizedWeight):
+        xq, xsf = quantize(x)
+        y = gemm(xq, xsf, qw.q, qw.sf, out_dtype=x.dtype)
+        ctx.save_for_backward(x, w)
+        ctx.qw = qw
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        qw = ctx.qw
+        dy = dy.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dyq, dysf = quantize(dy)
+            dx = gemm(dyq, dysf, qw.qt, qw.sft, out_dtype=x.dtype)
+        if ctx.needs_input_grad[1]:
+            main_grad = getattr(w, "main_grad", None)
+            if main_grad is not None:
+                matmul(dy, x, a_mn=True, b_mn=True, out=main_grad, accumulate=True)
+            else:
+                dw = matmul(dy, x, a_mn=True, b_mn=True, out_dtype=w.dtype)
+        return dx, dw, None
+
+
+def supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """MXFP8 needs bf16 CUDA operands with both feature dimensions multiples of 128."""
+    return (native.available() and x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and w.shape[0] % 128 == 0 and w.shape[1] % 128 == 0)
+
+
+def mxfp8_linear(x: torch.Tensor, w: torch.Tensor, qw: QuantizedWeight) -> torch.Tensor:
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    return _MXFP8Linear.apply(x2, w, qw).reshape(*lead, w.shape[0])
+
+
+def mxfp8_linear_reference(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """Quantise-dequantise emulation of the forward product in fp32 (oracle for tests and CPU)."""
+    xq, xe = quantize_reference(x.reshape(-1, x.shape[-1]))
+    wq, we = quantize_reference(w)
+    y = dequantize(xq, xe) @ dequantize(wq, we).t()
+    return y.to(x.dtype).reshape(*x.shape[:-1], w.shape[0])
