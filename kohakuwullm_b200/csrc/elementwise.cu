@@ -466,3 +466,72 @@ KWU_API int kwu_swiglu_bwd(const void* in, int in_ld, const void* dout, int dout
                                          dout_ld, (__nv_bfloat16*)din, din_ld, rows, H); kwu::count_launch();
   return check_launch("swiglu_bwd");
 }
+
+// --------------------------------------------------------------------------- allocation-free variant
+// kwu_rmsnorm_bwd_noalloc: RMSNorm backward for callers that cannot obtain device memory themselves.
+// See kwu_noalloc.h for who those callers are and for the contract. The weight-gradient partial sums
+// that kwu_rmsnorm_bwd takes as a caller-provided buffer live here in a fixed array inside the
+// library image; every GPU that loads the library carries it until the process exits.
+#include "kwu_noalloc.h"
+
+#include <mutex>
+
+namespace kwu {
+
+static __device__ __align__(256) float g_noalloc_dw_partial[KWU_NOALLOC_MAX_BLOCKS * KWU_NOALLOC_MAX_COLS];
+
+// In host code the array's name is only a handle for the runtime, not a device address, so the
+// address is asked for once per device (with that device current) and cached.
+static float* noalloc_scratch_address() {
+  static std::mutex mu;
+  static float* per_device[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    set_last_error("rmsnorm_bwd_noalloc: cannot identify the current device");
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (!per_device[dev]) {
+    float* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_dw_partial);
+    if (e != cudaSuccess || !ptr) {
+      set_last_error("rmsnorm_bwd_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return nullptr;
+    }
+    per_device[dev] = ptr;
+  }
+  return per_device[dev];
+}
+
+}  // namespace kwu
+
+KWU_API int kwu_rmsnorm_bwd_noalloc(const void* x, const float* w, const float* rstd, const void* dy,
+                                    const void* dres, void* dx, float* dw, int rows, int cols,
+                                    int one_plus, int accumulate_dw, void* stream) {
+  if (cols % 8) { set_last_error("rmsnorm_bwd_noalloc: cols must be a multiple of 8 (got %d)", cols); return 7; }
+  if (cols > KWU_NOALLOC_MAX_COLS) {
+    set_last_error("rmsnorm_bwd_noalloc: cols %d exceeds the built-in scratch (at most %d columns); "
+                   "use kwu_rmsnorm_bwd with a caller-provided buffer", cols, KWU_NOALLOC_MAX_COLS);
+    return 7;
+  }
+  if (rows <= 0) return 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const bool want_dw = (w != nullptr && dw != nullptr);
+  float* partial = nullptr;
+  if (want_dw) {
+    partial = noalloc_scratch_address();
+    if (!partial) return 12;
+  }
+  const int grid = grid_for(rows, 8, KWU_NOALLOC_MAX_BLOCKS);
+  // every block overwrites its own row of the scratch before the column sum reads it, so nothing in
+  // the array has to start at zero even though it still holds the previous call's partial sums
+  rmsnorm_bwd_kernel<<<grid, 256, want_dw ? cols * sizeof(float) : 0, st>>>(
+      (const __nv_bfloat16*)x, w, rstd, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)dres,
+      (__nv_bfloat16*)dx, partial, rows, cols, one_plus); kwu::count_launch();
+  if (int rc = check_launch("rmsnorm_bwd_noalloc")) return rc;
+  if (want_dw) {
+    colsum_partials_kernel<<<(cols + 255) / 256, 256, 0, st>>>(partial, dw, grid, cols, accumulate_dw); kwu::count_launch();
+    return check_launch("rmsnorm_bwd_noalloc_dw");
+  }
+  return 0;
+}
