@@ -1,0 +1,140 @@
+"""Whole-model checkpoints for pipeline (and data-parallel, and single-GPU) runs.
+
+File layout (Lightning-shaped so generic tooling can open it)::
+
+    {"state_dict": {whole-model name: tensor},
+     "optimizer_states": [{"named_optimizer_state": {whole-model name: {...}}, "step": n}],
+     "global_step": int, "epoch": int, "pytorch-lightning_version": "kohakuwupipe", **extra}
+
+Weights AND optimizer state are keyed by the parameter's name in the whole model (stage-local block
+index + the stage's first layer), never by rank or position, so a checkpoint written under one
+pipeline split loads under any other split, under DDP, or on one GPU. Every rank contributes its
+stage through ``all_gather_object``; rank 0 writes. Parameter groups are not stored: each rank rebuilds
+them from its own parameters. Reference: src/kohakuwupipe/io/checkpoint.py:18-210.
+"""
+
+from __future__ import annotations
+
+import os
+from typing import Mapping
+
+import torch
+import torch.distributed as dist
+
+FORMAT_TAG = "kohakuwupipe"
+
+
+def _world(group=None) -> int:
+    return dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+
+
+def _rank(group=None) -> int:
+    return dist.get_rank(group) if dist.is_available() and dist.is_initialized() else 0
+
+
+def local_state_dict(module: torch.nn.Module, names: Mapping[str, str] | None = None) -> dict[str, torch.Tensor]:
+    """CPU copy of a module's parameters and persistent buffers under whole-model names."""
+    names = names or {}
+    out = {}
+    for k, v in module.state_dict().items():
+        out[names.get(k, k)] = v.detach().to("cpu", copy=True)
+    return out
+
+
+def gather_state_dict(module: torch.nn.Module, names: Mapping[str, str] | None = None, group=None) -> dict:
+    """Union of every rank's ``local_state_dict`` (identical on all ranks)."""
+    mine = local_state_dict(module, names)
+    if _world(group) == 1:
+        return mine
+    parts: list = [None] * _world(group)
+    dist.all_gather_object(parts, mine, group=group)
+    merged: dict[str, torch.Tensor] = {}
+    for part in parts:
+        for k, v in part.items():
+            merged.setdefault(k, v)
+    return merged
+
+
+def gather_optimizer_state(optimizer, names: Mapping[str, str] | None = None, group=None) -> dict:
+    """Whole-model-named optimizer state. ``optimizer.state_dict()`` must expose
+    ``named_optimizer_state`` keyed by local parameter names (``FlatAdamW`` does)."""
+    names = names or {}
+    sd = optimizer.state_dict()
+    mine = {names.get(k, k): {kk: (vv.detach().to("cpu", copy=True) if torch.is_tensor(vv) else vv)
+                              for kk, vv in v.items()}
+            for k, v in sd["named_optimizer_state"].items()}
+    if _world(group) > 1:
+        parts: list = [None] * _world(group)
+        dist.all_gather_object(parts, mine, group=group)
+        merged: dict = {}
+        for part in parts:
+            for k, v in part.items():
+                if k not in merged:
+                    merged[k] = v
+                elif "range" in v and "range" in merged[k]:
+                    merged[k] = _merge_ranges(merged[k], v)
+        mine = merged
+    return {"named_optimizer_state": mine, "step": sd.get("step", 0), "hyper": sd.get("hyper", {})}
+
+
+def _merge_ranges(a: dict, b: dict) -> dict:
+    """Concatenate two partial (sharded) states of one parameter into one covering both ranges."""
+    first, second = (a, b) if a["range"][0] <= b["range"][0] else (b, a)
+    if first["range"][1] != second["range"][0]:
+        return first if (first["range"][1] - first["range"][0]) >= (second["range"][1] - second["range"][0]) else second
+    out = {"range": (first["range"][0], second["range"][1])}
+    for k in first:
+        if k != "range" and torch.is_tensor(first[k]):
+            out[k] = torch.cat([first[k].reshape(-1), second[k].reshape(-1)])
+    return out
+
+
+def save(path: str, module: torch.nn.Module, optimizer=None, *, names: Mapping[str, str] | None = None,
+         global_step: int = 0, epoch: int = 0, extra: dict | None = None, group=None) -> None:
+    state = gather_state_dict(module, names, group)
+    opt = gather_optimizer_state(optimizer, names, group) if optimizer is not None else None
+    if _rank(group) == 0:
+        payload = {"state_dict": state, "optimizer_states": [opt] if opt is not None else [],
+                   "global_step": int(global_step), "epoch": int(epoch),
+                   "pytorch-lightning_version": FORMAT_TAG}
+        payload.update(extra or {})
+        tmp = f"{path}.tmp"
+        os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+        torch.save(payload, tmp)
+        os.replace(tmp, path)
+    if _world(group) > 1:
+        dist.barrier(group=group)
+
+
+def load(path: str, module: torch.nn.Module, optimizer=None, *, names: Mapping[str, str] | None = None,
+         strict: bool = True, group=None) -> dict:
+    """Load the slice of a whole-model checkpoint that this module (stage) owns. Returns the payload
+    without the big tensors (progress, scheduler state, ...)."""
+    payload = torch.load(path, map_location="cpu", weights_only=False)
+    names = dict(names or {})
+    state = payload["state_dict"]
+    local = {}
+    missing = []
+    for k in module.state_dict().keys():
+        g = names.get(k, k)
+        if g in state:
+            local[k] = state[g]
+        else:
+            missing.append(g)
+    if missing and strict:
+        raise KeyError(f"checkpoint {path} lacks {len(missing)} tensors of this stage, e.g. {missing[:3]}")
+    module.load_state_dict(local, strict=False)
+    if optimizer is not None and payload.get("optimizer_states"):
+        opt = payload["optimizer_states"][0]
+        if "named_optimizer_state" not in opt:
+            world = _world(group)
+            per_rank = payload["optimizer_states"]
+            if len(per_rank) != world:
+                raise RuntimeError(f"legacy per-rank optimizer state of {len(per_rank)} ranks cannot be loaded "
+                                   f"at world size {world}")
+            optimizer.load_state_dict(per_rank[_rank(group)])
+        else:
+            inverse = {v: k for k, v in names.items()}
+            named = {inverse.get(g, g): v for g, v in opt["named_optimizer_state"].items()}
+            optimizer.load_state_dict({"named_optimizer_state": named, "step": opt.get("step", 0)})
+    return {k: v for k, v in payload.items() if k not in ("state_dict", "optimizer_states")}

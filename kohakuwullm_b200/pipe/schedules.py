@@ -1,0 +1,185 @@
+"""Pipeline schedules.
+
+Two executors share one interface (``step(first_stage_inputs, n_micro) -> list of losses``):
+
+* ``NativeSchedule`` — GPipe and 1F1B written directly on ``torch.distributed`` point-to-point ops.
+  Activations and their gradients cross a stage boundary as fixed-shape tensors (``boundary`` example
+  tensors give shape and dtype); a send towards one neighbour and the matching receive from it are
+  issued as ONE batched group so neither side can block the other, and on CUDA the transfers run on
+  NCCL's own stream, overlapping the next micro-batch's compute.
+* ``TorchSchedule`` — adapter over ``torch.distributed.pipelining`` for the multi-chunk schedules
+  (interleaved 1F1B, looped BFS, interleaved zero-bubble, ZB-V, DualPipe-V), always built with
+  ``scale_grads=False`` because the loss is already normalised by the step's token count.
+
+Reference: src/kohakuwupipe/training/trainer.py:37-63,143-160.
+"""
+
+from __future__ import annotations
+
+from typing import Callable, Sequence
+
+import torch
+import torch.distributed as dist
+
+SCHEDULES = ("gpipe", "1f1b", "interleaved-1f1b", "looped-bfs", "interleaved-zb", "zbv", "dualpipe-v")
+MULTI_CHUNK = ("interleaved-1f1b", "looped-bfs", "interleaved-zb", "zbv", "dualpipe-v")
+V_STYLE = ("zbv", "dualpipe-v")
+
+
+def _as_tuple(x):
+    return x if isinstance(x, (tuple, list)) else (x,)
+
+
+class NativeSchedule:
+    """GPipe / 1F1B over one stage per rank."""
+
+    def __init__(self, stage_fn: Callable, *, stage_index: int, num_stages: int, n_micro: int,
+                 loss_fn: Callable | None, boundary: Sequence[torch.Tensor],
+                 out_boundary: Sequence[torch.Tensor] | None = None, kind: str = "1f1b",
+                 group=None, prev_rank: int | None = None, next_rank: int | None = None):
+        if kind not in ("gpipe", "1f1b"):
+            raise ValueError(f"NativeSchedule runs gpipe or 1f1b, not {kind!r}")
+        self.stage_fn, self.loss_fn = stage_fn, loss_fn
+        self.s, self.S, self.M, self.kind = stage_index, num_stages, n_micro, kind
+        self.group = group
+        def describe(ts):
+            return [(tuple(t.shape), t.dtype, t.device, t.requires_grad or t.is_floating_point()) for t in ts]
+
+        # what arrives from the previous stage / what this stage sends on (gradients come back in that shape)
+        self.boundary = describe(boundary)
+        self.out_boundary = describe(out_boundary if out_boundary is not None else boundary)
+        rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.prev = prev_rank if prev_rank is not None else rank - 1
+        self.next = next_rank if next_rank is not None else rank + 1
+        self.first, self.last = stage_index == 0, stage_index == num_stages - 1
+        self._pending: list = []
+
+    # ------------------------------------------------------------------ communication
+    def _empty(self, spec):
+        return [torch.empty(shape, dtype=dtype, device=dev) for shape, dtype, dev, _ in spec]
+
+    def _exchange(self, send_to, send_tensors, recv_from, recv_grad: bool):
+        """One batched group: optional send towards ``send_to`` and optional receive from ``recv_from``."""
+        ops, recv_bufs = [], None
+        if send_tensors is not None:
+            for t in send_tensors:
+                ops.append(dist.P2POp(dist.isend, t.contiguous(), send_to, self.group))
+        if recv_from is not None:
+            # activations arrive from the previous stage, gradients from the next one
+            recv_bufs = self._empty(self.boundary if recv_grad else self.out_boundary)
+            for t in recv_bufs:
+                ops.append(dist.P2POp(dist.irecv, t, recv_from, self.group))
+        if ops:
+            for w in dist.batch_isend_irecv(ops):
+                w.wait()
+        if recv_bufs is not None and recv_grad:
+            recv_bufs = [t.requires_grad_() if t.is_floating_point() else t for t in recv_bufs]
+        return recv_bufs
+
+    # ------------------------------------------------------------------ compute
+    def _forward(self, mb: int, inputs, stash, losses):
+        out = self.stage_fn(mb, *inputs) if inputs is not None else self.stage_fn(mb)
+        outs = _as_tuple(out)
+        if self.last:
+            loss = self.loss_fn(outs if len(outs) > 1 else outs[0], mb)
+            losses.append(loss.detach())
+            stash[mb] = (inputs, (loss,))
+            return None
+        stash[mb] = (inputs, outs)
+        return [o.detach() for o in outs]
+
+    def _backward(self, mb: int, grads, stash):
+        inputs, outs = stash.pop(mb)
+        if self.last:
+            outs[0].backward()
+        else:
+            pairs = [(o, g) for o, g in zip(outs, grads) if o.requires_grad]
+            torch.autograd.backward([o for o, _ in pairs], [g for _, g in pairs])
+        if self.first or inputs is None:
+            return None
+        return [i.grad if i.grad is not None else torch.zeros_like(i) for i in inputs]
+
+    # ------------------------------------------------------------------ schedules
+    def step(self, n_micro: int | None = None) -> list[torch.Tensor]:
+        M = n_micro or self.M
+        stash: dict[int, tuple] = {}
+        losses: list[torch.Tensor] = []
+        warm = M if self.kind == "gpipe" else min(self.S - self.s - 1, M)
+        steady = M - warm
+        f = b = 0
+        inputs = None if self.first else self._exchange(None, None, self.prev, True)
+        # warm-up forwards
+        for _ in range(warm):
+            out = self._forward(f, inputs, stash, losses)
+            f += 1
+            more_f = f < M
+            inputs = self._exchange(None if self.last else self.next, out,
+                                    self.prev if (more_f and not self.first) else None, True)
+        # steady state: one forward, one backward
+        grads = None
+        for i in range(steady):
+            out = self._forward(f, inputs, stash, losses)
+            f += 1
+            grads = self._exchange(None if self.last else self.next, out,
+                                   None if self.last else self.next, False)
+            gin = self._backward(b, grads, stash)
+            b += 1
+            more_f = f < M
+            inputs = self._exchange(None if self.first else self.prev, gin,
+                                    self.prev if (more_f and not self.first) else None, True)
+        # cool-down backwards
+        while b < M:
+            grads = None if self.last else self._exchange(None, None, self.next, False)
+            gin = self._backward(b, grads, stash)
+            b += 1
+            self._exchange(None if self.first else self.prev, gin, None, False)
+        return losses
+
+
+class TorchSchedule:
+    """``torch.distributed.pipelining`` schedule over one or several local stage modules."""
+
+    def __init__(self, stage_modules: Sequence[torch.nn.Module], stage_indices: Sequence[int], *,
+                 num_stages: int, n_micro: int, loss_fn: Callable | None, kind: str, device,
+                 input_args: Sequence[tuple], group=None):
+        from torch.distributed import pipelining as pp
+
+        classes = {
+            "gpipe": pp.ScheduleGPipe, "1f1b": pp.Schedule1F1B,
+            "interleaved-1f1b": pp.ScheduleInterleaved1F1B, "looped-bfs": pp.ScheduleLoopedBFS,
+            "interleaved-zb": pp.ScheduleInterleavedZeroBubble, "zbv": pp.ScheduleZBVZeroBubble,
+            "dualpipe-v": pp.ScheduleDualPipeV,
+        }
+        if kind not in classes:
+            raise ValueError(f"unknown schedule {kind!r}; choose from {sorted(classes)}")
+        stages = [pp.PipelineStage(m, i, num_stages, device, input_args=a, group=group)
+                  for m, i, a in zip(stage_modules, stage_indices, input_args)]
+        cls = classes[kind]
+        single = kind in ("gpipe", "1f1b")
+        self.has_first = 0 in stage_indices
+        self.has_last = (num_stages - 1) in stage_indices
+        # the loss is normalised by the step's token count already: no 1/n_micro scaling
+        self.schedule = cls(stages[0] if single else stages, n_microbatches=n_micro, loss_fn=loss_fn,
+                            scale_grads=False)
+        self.n_micro = n_micro
+
+    def step(self, first_input: torch.Tensor | None = None, target: torch.Tensor | None = None):
+        losses: list[torch.Tensor] = []
+        kwargs = {}
+        if self.has_last:
+            kwargs = {"target": target, "losses": losses}
+        if self.has_first:
+            self.schedule.step(first_input, **kwargs)
+        else:
+            self.schedule.step(**kwargs)
+        return losses
+
+
+def local_stage_indices(rank: int, world: int, chunks: int, style: str = "loop") -> list[int]:
+    """Global stage indices held by ``rank`` with ``chunks`` stages per rank: looped (rank, rank+W, ...)
+    or folded in a V (rank and 2W-1-rank)."""
+    if style == "v":
+        if chunks != 2:
+            raise ValueError("V-style schedules hold exactly two chunks per rank")
+        return [rank, 2 * world - 1 - rank]
+    return [rank + c * world for c in range(chunks)]

@@ -50,6 +50,7 @@ class GraphedMicroStep:
         self.cu = torch.full((max_docs + 1,), tokens, dtype=torch.int32, device=dev)
         self.cu[0] = 0
         self.ce = torch.zeros((), dtype=torch.float32, device=dev)
+        self.total = torch.zeros((), dtype=torch.float32, device=dev)
         self.extra: dict[str, torch.Tensor] = {}
         self.graph: torch.cuda.CUDAGraph | None = None
 
@@ -75,6 +76,7 @@ class GraphedMicroStep:
                                     router_scale=eng._router_scale)
         loss.backward()
         self.ce.copy_(logs["ce"])
+        self.total.copy_(loss.detach())
         for k in ("z_loss", "router_loss"):
             if k in logs:
                 if k not in self.extra:
@@ -212,6 +214,7 @@ class TrainEngine:
         # router auxiliary terms are per-micro-batch means: weight them like one rank's share of tokens
         self._router_scale.copy_(tok / (self.world * max(len(micro_batches), 1)))
         ce_total = torch.zeros((), dtype=torch.float32, device=dev)
+        loss_total = torch.zeros((), dtype=torch.float32, device=dev)
         extra: dict[str, torch.Tensor] = {}
         for mb in micro_batches:
             graph = self._graph_for(mb)
@@ -219,6 +222,7 @@ class TrainEngine:
                 graph.load(mb)
                 graph.replay()
                 ce_total = ce_total + graph.ce
+                loss_total = loss_total + graph.total
                 for k, v in graph.extra.items():
                     extra[k] = extra.get(k, 0) + v
                 continue
@@ -227,6 +231,7 @@ class TrainEngine:
                                     router_scale=self._router_scale)
             loss.backward()
             ce_total = ce_total + logs["ce"]
+            loss_total = loss_total + loss.detach().float()
             for k in ("z_loss", "router_loss"):
                 if k in logs:
                     extra[k] = extra.get(k, 0) + logs[k]
@@ -243,9 +248,12 @@ class TrainEngine:
         if self.has_router:
             self.last_router_stats = model.update_router_bias()
         self.global_step += 1
-        ce_all = self.sync.all_reduce_scalar(ce_total.reshape(1).clone()) if self.world > 1 else ce_total.reshape(1)
-        out = {"loss": (ce_all * inv_tokens).reshape(()), "grad_norm": self._norm.reshape(()).clone(),
-               "tokens": tok.reshape(())}
+        sums = torch.stack([loss_total.reshape(()), ce_total.reshape(())])
+        if self.world > 1:
+            sums = self.sync.all_reduce_scalar(sums.clone())
+        # "loss" is the optimised objective (cross-entropy + z-loss + router terms) per trained token
+        out = {"loss": (sums[0] * inv_tokens).reshape(()), "ce": (sums[1] * inv_tokens).reshape(()),
+               "grad_norm": self._norm.reshape(()).clone(), "tokens": tok.reshape(())}
         for k, v in extra.items():
             out[k] = v * inv_tokens.reshape(())
         return out

@@ -1,0 +1,151 @@
+"""``LMPipelineModule``: the language-model adapter of the pipeline engine.
+
+Per stage it builds the backbone, slices it (``LMStage``), casts parameters to the training dtype
+(norm / router / rotary / sink / bias stay fp32), converts the stage's linears to MXFP8 and creates a
+flat-buffer fused AdamW over the stage's own parameters. Every rank receives the SAME step batch (a
+list of packed micro-batches); stage 0 uses the tokens, the last stage the labels, nothing else is
+moved. ``verify_same_batch`` compares a 4-number fp64 signature of the first batch across ranks.
+Reference: src/kohakuwullm/training/parallel/uwupipe.py:44-313.
+"""
+
+from __future__ import annotations
+
+from typing import Sequence
+
+import torch
+import torch.distributed as dist
+
+from kohakuwullm_b200.data.packing import PackedBatch
+from kohakuwullm_b200.models.backbone import LMBackbone
+from kohakuwullm_b200.models.presets import LMArchConfig
+from kohakuwullm_b200.parallel.flat import FlatParameters
+from kohakuwullm_b200.pipe.module import PipelineModule
+from kohakuwullm_b200.pipe.plan import StagePlan
+from kohakuwullm_b200.training.optim.fused_adamw import FlatAdamW
+from kohakuwullm_b200.training.optim.lowbit import cast_parameters_
+from kohakuwullm_b200.training.parallel.pipeline import LMStage, model_has_router_loss
+
+
+def batch_signature(batch: Sequence[PackedBatch]) -> torch.Tensor:
+    toks = torch.cat([b.tokens.reshape(-1).double().cpu() for b in batch])
+    labs = torch.cat([b.labels.reshape(-1).double().cpu() for b in batch])
+    idx = torch.arange(1, toks.numel() + 1, dtype=torch.float64)
+    return torch.stack([toks.sum(), (toks * idx).sum() / idx.sum(), labs.sum(), torch.tensor(float(toks.numel()), dtype=torch.float64)])
+
+
+def verify_same_batch(batch: Sequence[PackedBatch], device, group=None) -> None:
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+        return
+    sig = batch_signature(batch)
+    if dist.get_backend(group) == "nccl":
+        sig = sig.to(device)
+    parts = [torch.empty_like(sig) for _ in range(dist.get_world_size(group))]
+    dist.all_gather(parts, sig, group=group)
+    for r, other in enumerate(parts):
+        if not torch.equal(other.cpu(), parts[0].cpu()):
+            raise RuntimeError(f"rank {r} loaded a different batch than rank 0: pipeline ranks must iterate "
+                               f"identical data ({other.tolist()} vs {parts[0].tolist()})")
+
+
+class LMPipelineModule(PipelineModule):
+    def __init__(self, config: LMArchConfig, *, micro_tokens: int, lr: float = 3e-4, betas=(0.9, 0.95),
+                 weight_decay: float = 0.1, param_dtype: torch.dtype | None = torch.bfloat16,
+                 seed: int = 1234, lr_schedule=None, group=None):
+        super().__init__()
+        self.config, self.micro_tokens = config, micro_tokens
+        self.lr, self.betas, self.weight_decay = lr, betas, weight_decay
+        self.param_dtype, self.seed, self.lr_schedule, self.group = param_dtype, seed, lr_schedule, group
+        self._labels: list[torch.Tensor] = []
+        self._checked = False
+        self._router_scale = 1.0
+
+    # ------------------------------------------------------------------ construction
+    def configure_model(self, plan: StagePlan, rank: int, world: int, device) -> LMStage:
+        torch.manual_seed(self.seed)  # every rank builds the same whole model, then keeps its slice
+        cfg = self.config.replace(mxfp8=False)
+        backbone = LMBackbone(cfg)
+        stage = LMStage(backbone, plan, boundary_dtype=None)
+        del backbone
+        stage.to(device)
+        dtype = self.param_dtype if torch.device(device).type == "cuda" else None
+        if dtype is not None and dtype != torch.float32:
+            cast_parameters_(stage, dtype)
+        if self.config.mxfp8 and torch.device(device).type == "cuda":
+            from kohakuwullm_b200.models.mxfp8_swap import swap_mxfp8
+
+            report = swap_mxfp8(stage)
+            if report.blocking:
+                raise RuntimeError(f"MXFP8 conversion incomplete on stage {plan.index}: {report.blocking}")
+        return stage
+
+    def configure_optimizers(self):
+        params = self.stages[0] if len(self.stages) == 1 else torch.nn.ModuleList(self.stages)
+        self.flat = FlatParameters(params)
+        self._flat_names = {f"{i}.{k}": v for i, st in enumerate(self.stages) for k, v in st.global_names().items()}
+        opt = FlatAdamW(self.flat, lr=self.lr, betas=self.betas, weight_decay=self.weight_decay)
+        return opt
+
+    def boundary_example(self, plan: StagePlan):
+        dtype = next(p for p in self.stages[0].parameters() if p.dim() >= 2).dtype
+        hidden = torch.zeros(self.micro_tokens, self.config.dim, dtype=dtype, device=self.device)
+        if model_has_router_loss(self.config):
+            return (hidden, torch.zeros(1, dtype=torch.float32, device=self.device))
+        return (hidden,)
+
+    def first_input_example(self):
+        return (torch.zeros(self.micro_tokens, dtype=torch.long, device=self.device),)
+
+    def global_names(self) -> dict[str, str]:
+        if len(self.stages) == 1:
+            return self.stages[0].global_names()
+        return dict(self._flat_names)
+
+    # ------------------------------------------------------------------ per step
+    def set_batch(self, batch: Sequence[PackedBatch]) -> None:
+        if not self._checked:
+            verify_same_batch(batch, self.device, self.group)
+            self._checked = True
+        infos = [b.seq_info.to(self.device, non_blocking=True) for b in batch]
+        for stage in self.stages:
+            stage.set_seq_info(infos)
+            if stage.is_first:
+                stage.set_tokens([b.tokens.to(self.device, non_blocking=True) for b in batch])
+            if stage.is_last:
+                self._labels = [b.labels.to(self.device, non_blocking=True) for b in batch]
+        tokens = self.step_tokens(batch)
+        self._router_scale = tokens / max(len(batch), 1)
+
+    def num_microbatches(self, batch) -> int:
+        return len(batch)
+
+    def step_tokens(self, batch) -> int:
+        return sum(b.trained_tokens() for b in batch)
+
+    def loss(self, output, micro_index: int) -> torch.Tensor:
+        from kohakuwullm_b200.pipe import streams
+
+        last = next(s for s in self.stages if s.is_last)
+        hidden, aux = (output if isinstance(output, (tuple, list)) else (output, None))
+        loss, logs = last.head.loss(hidden, self._labels[micro_index], reduction="sum")
+        if aux is not None:
+            loss = loss + streams.reduce_accumulator(aux) * self._router_scale
+        self.log("ce_sum", logs["ce"])
+        return loss
+
+    def forward_backward(self, schedule, batch, n_micro: int):
+        from kohakuwullm_b200.pipe.schedules import NativeSchedule
+
+        if isinstance(schedule, NativeSchedule):
+            return schedule.step(n_micro)
+        first = next((s for s in self.stages if s.is_first), None)
+        tokens = torch.cat([b.tokens.to(self.device) for b in batch]) if first is not None else None
+        target = torch.arange(n_micro, device=self.device).reshape(n_micro, 1)
+        return schedule.step(tokens, target)
+
+    def post_step(self) -> None:
+        for stage in self.stages:
+            if self.config.mxfp8:
+                from kohakuwullm_b200.models.mxfp8_swap import refresh_mxfp8_weights
+
+                refresh_mxfp8_weights(stage)
+            stage.update_router_bias()
