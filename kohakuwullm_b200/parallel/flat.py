@@ -37,7 +37,10 @@ class FlatGroup:
 
 class FlatParameters:
     def __init__(self, module: nn.Module, align: int = 128, pad_total_to: int = 1024,
-                 install_hooks: bool = True):
+                 install_hooks: bool = True, allocator=None):
+        """``allocator(numel, dtype, device) -> 1-D tensor`` lets a caller place the buffers in special
+        memory (e.g. peer-mapped symmetric memory); the default is ordinary device memory."""
+        alloc = allocator or (lambda n, dt, dev: torch.zeros(n, dtype=dt, device=dev))
         self.module = module
         self.groups: dict[str, FlatGroup] = {}
         seen: set[int] = set()
@@ -57,8 +60,10 @@ class FlatParameters:
         for g in self.groups.values():
             g.total = -(-g.total // pad_total_to) * pad_total_to
             device = g.params[0].device
-            g.data = torch.zeros(g.total, dtype=g.dtype, device=device)
-            g.main_grad = torch.zeros(g.total, dtype=torch.float32, device=device)
+            g.data = alloc(g.total, g.dtype, device)
+            g.main_grad = alloc(g.total, torch.float32, device)
+            g.data.zero_()
+            g.main_grad.zero_()
             for i, p in enumerate(g.params):
                 s, e = g.span(i)
                 view = g.data[s:e].view(p.shape)

@@ -120,17 +120,23 @@ class TrainEngine:
         self.device = next(model.parameters()).device
         if param_dtype is not None and param_dtype != torch.float32:
             cast_parameters_(model, param_dtype)
-        self.flat = FlatParameters(model)
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if self.world > 1 else 0
-        if grad_sync == "fused" and self.world > 1 and self.device.type == "cuda":
+        self.fused_sync = grad_sync == "fused" and self.world > 1 and self.device.type == "cuda"
+        if self.fused_sync:
             from kohakuwullm_b200.parallel.fused_ddp import FusedGradSync
+            from kohakuwullm_b200.parallel.symm import SymmetricPool
 
-            self.sync = FusedGradSync(self.flat, group)
+            pool = SymmetricPool(group)
+            self.flat = FlatParameters(model, allocator=pool.empty)
+            self.sync = FusedGradSync(self.flat, pool, group)
+            shard = (self.rank, self.world)
         else:
+            self.flat = FlatParameters(model)
             self.sync = GradSync(self.flat, group)
-        self.optimizer = FlatAdamW(self.flat, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
+            shard = None
+        self.optimizer = FlatAdamW(self.flat, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, shard=shard)
         self.max_grad_norm = max_grad_norm
         self.lr_schedule = lr_schedule
         self.global_step = 0
@@ -235,11 +241,17 @@ class TrainEngine:
             for k in ("z_loss", "router_loss"):
                 if k in logs:
                     extra[k] = extra.get(k, 0) + logs[k]
-        self.sync.reduce()
-        self._grad_norm_and_coef(inv_tokens)
         if self.lr_schedule is not None:
             self.optimizer.param_groups[0]["lr"] = self.lr_schedule(self.global_step)
-        if local_tokens > 0 or self.world > 1:
+        if self.fused_sync:
+            # one fused pass: reduce-scatter + scaling + clipping + sharded AdamW + all-gather
+            self.sync.step(self.optimizer, inv_tokens.reshape(1), self.max_grad_norm)
+            self._norm = self.sync.norm
+            if self.has_mxfp8:
+                model.refresh_mxfp8()
+        elif local_tokens > 0 or self.world > 1:
+            self.sync.reduce()
+            self._grad_norm_and_coef(inv_tokens)
             self.optimizer.step(grad_scale=self._coef, zero_grad=True)
             if self.has_mxfp8:
                 model.refresh_mxfp8()

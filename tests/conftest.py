@@ -19,9 +19,11 @@ def pytest_configure(config):
 def pytest_collection_modifyitems(config, items):
     import torch
 
-    if torch.cuda.is_available():
-        return
+    n_gpus = torch.cuda.device_count() if torch.cuda.is_available() else 0
     skip = pytest.mark.skip(reason="no CUDA device")
+    skip_multi = pytest.mark.skip(reason="needs 2 or more CUDA devices")
     for item in items:
-        if "gpu" in item.keywords or "multigpu" in item.keywords:
+        if "multigpu" in item.keywords and n_gpus < 2:
+            item.add_marker(skip_multi)
+        elif "gpu" in item.keywords and n_gpus < 1:
             item.add_marker(skip)

@@ -1,0 +1,123 @@
+"""Data pipeline: permutation, packing, label shifting, loaders and exact resume."""
+
+import random
+
+import pytest
+import torch
+from hypothesis import given, settings, strategies as st
+
+from kohakuwullm_b200.data import (ByteTokenizer, FeistelPermutation, IterativePackLoader, MicroBatchedLoader,
+                                   ResumableLoader, ShardIndices, collate_packed, collate_padded, is_validation,
+                                   split_packed, split_padded)
+from kohakuwullm_b200.data.filters import ngram_repeat_ratio, passes_repeat_filter
+from kohakuwullm_b200.data.renderers.base import ChatMLRenderer, PlainRenderer, TIPORenderer
+from kohakuwullm_b200.data.sources.records import CorpusRecords, ListRecords
+
+
+@settings(max_examples=40, deadline=None)
+@given(st.integers(1, 3000), st.integers(0, 2 ** 40))
+def test_feistel_is_a_permutation(n, key):
+    perm = FeistelPermutation(n, key)
+    assert sorted(perm(i) for i in range(n)) == list(range(n))
+
+
+def test_shards_partition_every_epoch_and_epochs_differ():
+    n, shards = 103, 4
+    for epoch in (0, 1):
+        seen = []
+        for s in range(shards):
+            seen += [idx for _, idx in ShardIndices(n, s, shards, seed=5).iterate(epoch)]
+        assert sorted(seen) == list(range(n))
+    a = [i for _, i in ShardIndices(n, 0, 1, seed=5).iterate(0)]
+    b = [i for _, i in ShardIndices(n, 0, 1, seed=5).iterate(1)]
+    assert a != b
+
+
+def test_validation_split_is_stable():
+    flags = [is_validation(f"doc{i}", 0.1, seed=3) for i in range(2000)]
+    assert 120 < sum(flags) < 280
+    assert flags == [is_validation(f"doc{i}", 0.1, seed=3) for i in range(2000)]
+
+
+def test_labels_are_shifted_inside_each_document():
+    a, b = torch.tensor([1, 2, 3, 4]), torch.tensor([7, 8, 9])
+    batch = collate_packed([a, (b, torch.tensor([False, False, True])), torch.tensor([5])])
+    assert batch.tokens.tolist() == [1, 2, 3, 4, 7, 8, 9]
+    assert batch.labels.tolist() == [2, 3, 4, -100, -100, 9, -100]   # no target crosses a boundary
+    assert batch.seq_info.cu_seqlens.tolist() == [0, 4, 7]
+    assert batch.seq_info.position_ids.tolist() == [0, 1, 2, 3, 0, 1, 2]
+
+
+def test_split_packed_is_document_aligned_and_complete():
+    docs = [torch.arange(n) + 10 * n for n in (9, 3, 7, 5, 2, 8)]
+    whole = collate_packed(docs)
+    parts = split_packed(whole, 3)
+    assert sum(p.num_tokens for p in parts) == whole.num_tokens
+    assert sum(p.trained_tokens() for p in parts) == whole.trained_tokens()
+    sizes = sorted(p.num_tokens for p in parts)
+    assert sizes[-1] - sizes[0] <= 9
+
+
+def test_padded_twin():
+    batch = collate_padded([torch.arange(5), torch.arange(3)], pad_id=0)
+    assert batch.tokens.shape == (2, 5) and batch.labels[1].tolist() == [1, 2, -100, -100, -100]
+    assert [p.tokens.shape[0] for p in split_padded(batch, 2)] == [1, 1]
+
+
+def test_renderers_mark_trained_roles_only():
+    chat = ChatMLRenderer()
+    segs = chat({"messages": [{"role": "user", "content": "hi"}, {"role": "assistant", "content": "yo"}]})
+    assert [t for _, t in segs] == [False, False, False, True]
+    assert PlainRenderer()("abc") == [("abc", True)]
+    rec = {"tags": [f"t{i}" for i in range(12)], "caption": "A long caption. More.", "rating": "g"}
+    prompt, completion = TIPORenderer()(rec, random.Random(1))
+    assert prompt[1] is False and completion[1] is True
+
+
+def _loader(records, **kw):
+    tok = ByteTokenizer()
+    return IterativePackLoader(records, PlainRenderer(), tok.encode, k=64, m=16, bos=tok.bos_token_id,
+                               eos=tok.eos_token_id, seed=7, **kw)
+
+
+def test_iterative_loader_respects_budget_and_resumes_exactly():
+    records = ListRecords([{"text": "x" * n} for n in random.Random(0).choices(range(3, 50), k=200)])
+    full = []
+    it = iter(ResumableLoader(_loader(records)))
+    for _ in range(12):
+        full.append(next(it))
+    assert all(48 <= b.num_tokens <= 64 for b in full[:-1])
+    # stop after 5 batches, checkpoint, resume in a new loader: the stream continues identically
+    first = ResumableLoader(_loader(records))
+    it = iter(first)
+    head = [next(it) for _ in range(5)]
+    state = first.state_dict()
+    second = ResumableLoader(_loader(records))
+    second.load_state_dict(state)
+    it2 = iter(second)
+    tail = [next(it2) for _ in range(7)]
+    for a, b in zip(head + tail, full):
+        assert torch.equal(a.tokens, b.tokens) and torch.equal(a.labels, b.labels)
+    with pytest.raises(ValueError):
+        ResumableLoader(_loader(records, shard=1, shards=2)).load_state_dict(state)
+
+
+def test_pipeline_loader_emits_exact_microbatches():
+    tok = ByteTokenizer()
+    records = ListRecords([{"text": "y" * n} for n in random.Random(1).choices(range(3, 90), k=100)])
+    loader = MicroBatchedLoader(records, PlainRenderer(), tok.encode, k=64, num_microbatches=3, seed=1)
+    step, _ = next(iter(loader))
+    assert len(step) == 3 and all(m.num_tokens == 64 for m in step)
+
+
+def test_corpus_records_and_manifest(tmp_path):
+    (tmp_path / "a.jsonl").write_text('{"text": "one"}\n{"text": "two"}\n')
+    (tmp_path / "b.txt").write_text("three\n\nfour\n")
+    corpus = CorpusRecords(str(tmp_path))
+    assert len(corpus) == 4 and [corpus[i]["text"] for i in range(4)] == ["one", "two", "three", "four"]
+    assert (tmp_path / "manifest.json").exists()
+
+
+def test_repeat_filter():
+    assert ngram_repeat_ratio(list(range(100))) == 0.0
+    assert not passes_repeat_filter([1, 2, 3, 4] * 30)
