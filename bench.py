@@ -150,7 +150,18 @@ def run_ours(args):
     cfg = get_preset(PRESET, **overrides)
     with torch.device(dev):
         model = LMBackbone(cfg)
-    engine = TrainEngine(model, lr=1e-4, param_dtype=torch.bfloat16, grad_sync=args.grad_sync)
+    mode = args.grad_sync
+    if mode == "auto":
+        mode = "fused" if world > 1 else "nccl"
+    try:
+        engine = TrainEngine(model, lr=1e-4, param_dtype=torch.bfloat16, grad_sync=mode)
+    except Exception as exc:  # noqa: BLE001  symmetric memory unavailable: keep the run alive on NCCL
+        if mode != "fused" or args.grad_sync == "fused":
+            raise
+        print(f"[bench] fused gradient sync unavailable ({type(exc).__name__}: {exc}); using NCCL", file=sys.stderr)
+        mode = "nccl"
+        engine = TrainEngine(model, lr=1e-4, param_dtype=torch.bfloat16, grad_sync=mode)
+    args.grad_sync = mode
 
     host_packs = [p.pin_memory() for p in make_packs(GRAD_ACCUM, MICRO_TOKENS, LEN_MIN, LEN_MAX, cfg.vocab_size, seed=17 + rank)]
     dev_packs = [p.to(dev) for p in host_packs]
@@ -221,7 +232,8 @@ def main():
     ap.add_argument("--steps", type=int, default=8)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--grad-sync", default="nccl", choices=["nccl", "fused"])
+    ap.add_argument("--grad-sync", default="auto", choices=["auto", "nccl", "fused"],
+                    help="auto: fused NVLink peer-memory kernels when N>1 (NCCL all-reduce if they cannot be set up)")
     ap.add_argument("--ref-attn", default="triton", help="attention backend of the reference arm")
     ap.add_argument("--no-mxfp8", action="store_true", help="bf16 linears instead of MXFP8 (diagnostic only)")
     args = ap.parse_args()

@@ -193,6 +193,10 @@ ddp_adamw_allgather_kernel(const AdamArgs a) {
       float g[8], p[8], mm[8], vv[8];
       *reinterpret_cast<float4*>(g) = *reinterpret_cast<const float4*>(a.local_grad + gi);
       *reinterpret_cast<float4*>(g + 4) = *reinterpret_cast<const float4*>(a.local_grad + gi + 4);
+      if (a.zero_all_grads) {  // the owner clears its shard as it consumes it
+        *reinterpret_cast<float4*>(a.local_grad + gi) = make_float4(0.f, 0.f, 0.f, 0.f);
+        *reinterpret_cast<float4*>(a.local_grad + gi + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
       float* mst = a.master ? a.master + i : reinterpret_cast<float*>(a.peers.param[a.rank]) + gi;
       *reinterpret_cast<float4*>(p) = *reinterpret_cast<const float4*>(mst);
       *reinterpret_cast<float4*>(p + 4) = *reinterpret_cast<const float4*>(mst + 4);
@@ -237,7 +241,8 @@ ddp_adamw_allgather_kernel(const AdamArgs a) {
       // every peer has published its slot, i.e. has finished reading this rank's gradients
       const long long zs = static_cast<long long>(gridDim.x) * blockDim.x * 4;
       for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4; i < a.total; i += zs)
-        *reinterpret_cast<float4*>(a.local_grad + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < a.lo || i >= a.lo + a.n)  // the own shard is cleared element by element above
+          *reinterpret_cast<float4*>(a.local_grad + i) = make_float4(0.f, 0.f, 0.f, 0.f);
     }
   }
   __threadfence_system();  // this thread's peer stores are performed before anything that follows
