@@ -38,6 +38,17 @@ struct GemmParams {
   uint32_t idesc;
   int tiles_m, tiles_n;
   int* status;
+  // grouped (mixture-of-experts) modes
+  //   1: rows grouped by expert: row tile t reads group_tiles[t] = (m0, expert, valid); the expert picks
+  //      a block of `group_b_rows` rows of B (K-major: output rows; MN-major: contraction rows)
+  //   2: contraction grouped by expert (weight gradients): C[e] (+)= A[rows_e]^T B[rows_e] with
+  //      rows_e = [group_offsets[e], group_offsets[e+1]); C advances by c_group_stride elements per expert
+  int group_mode;
+  const int4* group_tiles;
+  const int* group_offsets;
+  int group_b_rows;
+  int num_groups;
+  long long c_group_stride;
   // fused cross-entropy epilogues (EPI_LSE / EPI_DLOGITS)
   const int* labels;     // (M) target column per row, negative = ignored row
   float2* partial;       // EPI_LSE: (tiles_n, M) running (max, sum-exp) per row and column tile
@@ -61,10 +72,43 @@ struct GemmSmem {
   static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // +1024 alignment slack
 };
 
+struct TileInfo {
+  int m0, n0;        // output tile origin
+  int b_row_off;     // added to B's row coordinate (expert selection)
+  int k_begin, nkb;  // contraction range in elements / 64-blocks
+  long long c_off;   // added to the output pointer (elements)
+};
+
+// Same decoding in every role of the CTA. Returns false for tiles that carry no work.
+template <int BN>
+__device__ __forceinline__ bool decode_tile(const GemmParams& p, int tile, int num_kb, TileInfo& t) {
+  t.b_row_off = 0; t.k_begin = 0; t.nkb = num_kb; t.c_off = 0;
+  if (p.group_mode == 2) {
+    const int per = p.tiles_m * p.tiles_n;
+    const int e = tile / per, r = tile % per;
+    t.m0 = (r / p.tiles_n) * GEMM_BM;
+    t.n0 = (r % p.tiles_n) * BN;
+    t.k_begin = p.group_offsets[e];
+    t.nkb = (p.group_offsets[e + 1] - t.k_begin) / GEMM_BK;
+    t.c_off = static_cast<long long>(e) * p.c_group_stride;
+    return t.nkb > 0;
+  }
+  const int tm = tile / p.tiles_n;
+  t.n0 = (tile % p.tiles_n) * BN;
+  if (p.group_mode == 1) {
+    const int4 g = p.group_tiles[tm];
+    t.m0 = g.x;
+    t.b_row_off = g.y * p.group_b_rows;
+    return g.z != 0;
+  }
+  t.m0 = tm * GEMM_BM;
+  return true;
+}
+
 template <int BN, bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 void* __restrict__ Cout, const GemmParams p) {
+                 void* __restrict__ Cbase, const GemmParams p) {
   using S = GemmSmem<BN>;
   constexpr int STAGES = S::STAGES;
   constexpr uint32_t TMEM_COLS = (2 * BN <= 256) ? 256 : 512;
@@ -82,7 +126,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int num_tiles = p.tiles_m * p.tiles_n * (p.group_mode == 2 ? p.num_groups : 1);
   const int num_kb = (p.K + GEMM_BK - 1) / GEMM_BK;
 
   if (threadIdx.x == 0) {
@@ -115,9 +159,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile / p.tiles_n) * GEMM_BM;
-        const int n0 = (tile % p.tiles_n) * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        TileInfo ti;
+        if (!decode_tile<BN>(p, tile, num_kb, ti)) continue;
+        const int m0 = ti.m0, n0 = ti.n0;
+        for (int kb = 0; kb < ti.nkb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_EMPTY)) {
             ok = false;
             break;
@@ -125,7 +170,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           uint8_t* sa = smem + stage * S::STAGE_BYTES;
           uint8_t* sb = sa + S::A_BYTES;
           mbar_expect_tx(&full_bar[stage], S::STAGE_BYTES);
-          const int k0 = kb * GEMM_BK;
+          const int k0 = ti.k_begin + kb * GEMM_BK;
           if (!A_MN) {
             tma_load_2d(sa, &tmA, &full_bar[stage], k0, m0);
           } else {
@@ -134,11 +179,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               tma_load_2d(sa + c * 8192, &tmA, &full_bar[stage], m0 + c * 64, k0);
           }
           if (!B_MN) {
-            tma_load_2d(sb, &tmB, &full_bar[stage], k0, n0);
+            tma_load_2d(sb, &tmB, &full_bar[stage], k0, n0 + ti.b_row_off);
           } else {
 #pragma unroll
             for (int c = 0; c < BN / 64; ++c)
-              tma_load_2d(sb + c * 8192, &tmB, &full_bar[stage], n0 + c * 64, k0);
+              tma_load_2d(sb + c * 8192, &tmB, &full_bar[stage], n0 + c * 64, k0 + ti.b_row_off);
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -154,16 +199,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        TileInfo ti;
+        if (!decode_tile<BN>(p, tile, num_kb, ti)) continue;
         const int as = it & 1;
         const uint32_t aphase = (it >> 1) & 1;
+        ++it;
         if (!mbar_wait(&acc_empty[as], aphase ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_EMPTY)) {
           ok = false;
           break;
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + as * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = 0; kb < ti.nkb; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL)) {
             ok = false;
             break;
@@ -191,11 +239,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int quarter = warp & 3;  // TMEM lane quarter this warp may read
     int it = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      TileInfo ti;
+      if (!decode_tile<BN>(p, tile, num_kb, ti)) continue;
       const int as = it & 1;
       const uint32_t aphase = (it >> 1) & 1;
-      const int m0 = (tile / p.tiles_n) * GEMM_BM;
-      const int n0 = (tile % p.tiles_n) * BN;
+      ++it;
+      const int m0 = ti.m0, n0 = ti.n0;
+      void* Cout = reinterpret_cast<uint8_t*>(Cbase) + ti.c_off * (p.out_fp32 ? 4 : 2);
       ok = mbar_wait(&acc_full[as], aphase, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_FULL);
       ok = __all_sync(0xffffffffu, ok);  // the TMEM loads below are warp-collective
       if (!ok) break;
@@ -333,7 +384,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
       }
       if (EPI == EPI_LSE && row < p.M) {
-        p.partial[static_cast<size_t>(tile % p.tiles_n) * p.M + row] = make_float2(run_max, run_sum);
+        p.partial[static_cast<size_t>(n0 / BN) * p.M + row] = make_float2(run_max, run_sum);
         if (tgt_here) p.target_logit[row] = tgt;
       }
       tc_fence_before();
@@ -372,6 +423,16 @@ struct DescOverride {
 };
 static DescOverride g_override;
 
+struct GroupArgs {
+  int mode = 0;
+  const int4* tiles = nullptr;
+  const int* offsets = nullptr;
+  int b_rows = 0;
+  int num_groups = 1;
+  long long c_stride = 0;
+  int row_tiles = 0;  // mode 1: number of entries in `tiles`
+};
+
 struct EpiArgs {
   const int* labels = nullptr;
   float2* partial = nullptr;
@@ -384,7 +445,8 @@ struct EpiArgs {
 template <int BN, bool A_MN, bool B_MN, int EPI = EPI_STORE>
 static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb,
                        int ldc, int out_fp32, int accumulate, float alpha, int max_ctas,
-                       cudaStream_t stream, int* status, const EpiArgs& ea = EpiArgs()) {
+                       cudaStream_t stream, int* status, const EpiArgs& ea = EpiArgs(),
+                       const GroupArgs& ga = GroupArgs(), int b_total_rows = 0) {
   using S = GemmSmem<BN>;
   CUtensorMap tmA, tmB;
   int rc;
@@ -393,10 +455,11 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
   else
     rc = encode_tmap_2d(&tmA, A, ELEM_BF16, K, M, lda, GEMM_BK, 64, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc) return rc;
+  // with expert groups B is the stack of all experts' matrices: b_total_rows rows in storage order
   if (!B_MN)
-    rc = encode_tmap_2d(&tmB, B, ELEM_BF16, N, K, ldb, BN, GEMM_BK, CU_TENSOR_MAP_SWIZZLE_128B);
+    rc = encode_tmap_2d(&tmB, B, ELEM_BF16, b_total_rows ? b_total_rows : N, K, ldb, BN, GEMM_BK, CU_TENSOR_MAP_SWIZZLE_128B);
   else
-    rc = encode_tmap_2d(&tmB, B, ELEM_BF16, K, N, ldb, GEMM_BK, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+    rc = encode_tmap_2d(&tmB, B, ELEM_BF16, b_total_rows ? b_total_rows : K, N, ldb, GEMM_BK, 64, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc) return rc;
 
   GemmParams p;
@@ -412,9 +475,11 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
     if (B_MN) { p.b_lbo = g_override.b_lbo; p.b_sbo = g_override.b_sbo; p.b_kadv = g_override.b_kadv; }
   }
   p.idesc = make_idesc_f16(GEMM_BM, BN, 1, A_MN ? 1 : 0, B_MN ? 1 : 0);
-  p.tiles_m = (M + GEMM_BM - 1) / GEMM_BM;
+  p.tiles_m = ga.mode == 1 ? ga.row_tiles : (M + GEMM_BM - 1) / GEMM_BM;
   p.tiles_n = (N + BN - 1) / BN;
   p.status = status;
+  p.group_mode = ga.mode; p.group_tiles = ga.tiles; p.group_offsets = ga.offsets;
+  p.group_b_rows = ga.b_rows; p.num_groups = ga.num_groups; p.c_group_stride = ga.c_stride;
   p.labels = ea.labels; p.partial = ea.partial; p.target_logit = ea.target_logit;
   p.lse = ea.lse; p.coef_p = ea.coef_p; p.coef_y = ea.coef_y;
 
@@ -428,7 +493,8 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
     }
     attr_set = true;
   }
-  int grid = p.tiles_m * p.tiles_n;
+  long grid_l = static_cast<long>(p.tiles_m) * p.tiles_n * (ga.mode == 2 ? ga.num_groups : 1);
+  int grid = grid_l > (1 << 30) ? (1 << 30) : static_cast<int>(grid_l);
   int cap = num_sms();
   if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;
   if (grid > cap) grid = cap;
@@ -543,4 +609,45 @@ KWU_API int kwu_ce_combine(const void* partial, int tiles_n, int M, float* lse, 
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { kwu::set_last_error("ce_combine launch: %s", cudaGetErrorString(e)); return 11; }
   return 0;
+}
+
+
+// ------------------------------------------------------------------ grouped (mixture-of-experts) GEMMs
+// Rows grouped by expert (forward and dgrad):  C[rows of tile] = A[rows of tile] * op(B[expert]).
+//   A (M_pad, K) K-major. b_mn = 0: B is (E*N, K), expert e owns rows [e*N, (e+1)*N)  -> y = x W_e^T
+//                         b_mn = 1: B is (E*Kc, N) with Kc = K,  expert e owns rows [e*K, (e+1)*K) -> dx = dy W_e
+//   tiles: (row_tiles, 4) int32 entries (m0, expert, valid, unused) built by kwu_moe_plan.
+KWU_API int kwu_gemm_bf16_grouped_rows(const void* A, const void* B, void* C, int M_pad, int N, int K, int lda,
+                                       int ldb, int ldc, int b_mn, int num_experts, const void* tiles,
+                                       int row_tiles, int out_fp32, void* stream, int* status) {
+  using namespace kwu;
+  if (M_pad <= 0 || row_tiles <= 0) return 0;
+  GroupArgs ga;
+  ga.mode = 1;
+  ga.tiles = reinterpret_cast<const int4*>(tiles);
+  ga.row_tiles = row_tiles;
+  ga.b_rows = b_mn ? K : N;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int total_rows = num_experts * ga.b_rows;
+  if (b_mn)
+    return launch_gemm<128, false, true>(A, B, C, M_pad, N, K, lda, ldb, ldc, out_fp32, 0, 1.f, 0, st, status,
+                                         EpiArgs(), ga, total_rows);
+  return launch_gemm<128, false, false>(A, B, C, M_pad, N, K, lda, ldb, ldc, out_fp32, 0, 1.f, 0, st, status,
+                                        EpiArgs(), ga, total_rows);
+}
+
+// Contraction grouped by expert (weight gradients): dW[e] (N_out, K_out) (+)= dY[rows_e]^T X[rows_e].
+//   dY (M_pad, N_out) and X (M_pad, K_out) row-major; offsets: (E+1) padded row offsets (multiples of 128).
+KWU_API int kwu_gemm_bf16_grouped_wgrad(const void* dY, const void* X, void* dW, int M_pad, int N_out, int K_out,
+                                        int lddy, int ldx, int num_experts, const int* offsets, int out_fp32,
+                                        int accumulate, void* stream, int* status) {
+  using namespace kwu;
+  if (M_pad <= 0) return 0;
+  GroupArgs ga;
+  ga.mode = 2;
+  ga.offsets = offsets;
+  ga.num_groups = num_experts;
+  ga.c_stride = static_cast<long long>(N_out) * K_out;
+  return launch_gemm<128, true, true>(dY, X, dW, N_out, K_out, M_pad, lddy, ldx, K_out, out_fp32, accumulate, 1.f,
+                                      0, reinterpret_cast<cudaStream_t>(stream), status, EpiArgs(), ga, 0);
 }

@@ -1,0 +1,326 @@
+// Mixture-of-experts routing and dispatch kernels.
+//
+//   moe_router_fwd   gate logits (fp32 SIMT tile GEMM) -> score (sigmoid | softmax | sqrt-softplus) ->
+//                    selection over score + bias (bias steers SELECTION only) -> top-k by repeated warp
+//                    arg-max -> gate weight from the UNBIASED score, optionally normalised over the k picks
+//                    and scaled -> per-call histogram `counts` and the running `load_accum`.
+//   moe_plan         counts -> expert row offsets padded to 128 rows, the grouped-GEMM tile table and
+//                    zeroed cursors (one block, no host synchronisation; list lengths are host bounds).
+//   moe_place        every (token, slot) pair takes a row inside its expert's padded range.
+//   moe_gather       expert-sorted activation rows (padding rows are zero).
+//   moe_combine      out[t] = sum_slot w[t,slot] * rows[pos(t,slot)]: a per-token gather-sum, so the result
+//                    does not depend on the order in which pairs were placed (no atomics on the output).
+//   moe_combine_bwd  d_rows[pos] = w * dout[t] (padding rows zero), d_w[t,slot] = <rows[pos], dout[t]>.
+// Reference: src/kohakuwullm/kernels/moe/router.py:76-194, moe_dispatch.py:14-130.
+#include "common.cuh"
+
+namespace kwu {
+
+constexpr int RT_BT = 32;     // tokens per block
+constexpr int RT_BD = 32;     // reduction chunk
+constexpr int RT_MAXE = 128;
+
+enum : int { SCORE_SIGMOID = 0, SCORE_SOFTMAX = 1, SCORE_SQRTSOFTPLUS = 2 };
+
+__global__ void __launch_bounds__(256)
+moe_router_fwd_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const float* __restrict__ W,
+                      const float* __restrict__ bias, float* __restrict__ logits_out, int* __restrict__ idx_out,
+                      float* __restrict__ weight_out, int* __restrict__ counts, float* __restrict__ load_accum,
+                      int T, int D, int E, int top_k, int score_fn, int norm_topk, float scaling) {
+  __shared__ float s_x[RT_BT][RT_BD + 1];
+  __shared__ float s_w[RT_MAXE][RT_BD + 1];
+  __shared__ float s_logit[RT_BT][RT_MAXE + 1];
+  const int t0 = blockIdx.x * RT_BT;
+  const int tid = threadIdx.x;
+  // thread -> (token ty, experts tx, tx + 8, ...): 256 threads = 32 tokens x 8 expert lanes
+  const int ty = tid >> 3, tx = tid & 7;
+  float acc[RT_MAXE / 8];
+#pragma unroll
+  for (int j = 0; j < RT_MAXE / 8; ++j) acc[j] = 0.f;
+  for (int d0 = 0; d0 < D; d0 += RT_BD) {
+    for (int i = tid; i < RT_BT * RT_BD; i += 256) {
+      const int r = i / RT_BD, c = i % RT_BD;
+      const int t = t0 + r;
+      s_x[r][c] = (t < T && d0 + c < D) ? __bfloat162float(x[static_cast<size_t>(t) * ldx + d0 + c]) : 0.f;
+    }
+    for (int i = tid; i < E * RT_BD; i += 256) {
+      const int r = i / RT_BD, c = i % RT_BD;
+      s_w[r][c] = (d0 + c < D) ? W[static_cast<size_t>(r) * D + d0 + c] : 0.f;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int c = 0; c < RT_BD; ++c) {
+      const float xv = s_x[ty][c];
+#pragma unroll
+      for (int j = 0; j < RT_MAXE / 8; ++j)
+        if (tx + 8 * j < E) acc[j] += xv * s_w[tx + 8 * j][c];
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int j = 0; j < RT_MAXE / 8; ++j)
+    if (tx + 8 * j < E) s_logit[ty][tx + 8 * j] = acc[j];
+  __syncthreads();
+
+  // top-k: one warp handles 4 tokens; lane l owns experts l, l+32, l+64, l+96
+  const int warp = tid >> 5, lane = tid & 31;
+  for (int r = warp * 4; r < warp * 4 + 4; ++r) {
+    const int t = t0 + r;
+    if (t >= T) continue;
+    float sc[4], sel[4];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int e = lane + 32 * j;
+      const float lg = e < E ? s_logit[r][e] : -INFINITY;
+      if (logits_out && e < E) logits_out[static_cast<size_t>(t) * E + e] = lg;
+      sc[j] = lg;
+      mx = fmaxf(mx, lg);
+    }
+    if (score_fn == SCORE_SOFTMAX) {
+      mx = warp_max(mx);
+      float sum = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        sc[j] = (lane + 32 * j < E) ? __expf(sc[j] - mx) : 0.f;
+        sum += sc[j];
+      }
+      sum = warp_sum(sum);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) sc[j] /= sum;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float lg = sc[j];
+        if (score_fn == SCORE_SIGMOID) sc[j] = 1.f / (1.f + __expf(-lg));
+        else sc[j] = sqrtf(lg > 20.f ? lg : log1pf(__expf(lg)));
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int e = lane + 32 * j;
+      sel[j] = e < E ? sc[j] + (bias ? bias[e] : 0.f) : -INFINITY;
+    }
+    float wsum = 0.f;
+    float my_w = 0.f;
+    int my_e = -1;
+    for (int k = 0; k < top_k; ++k) {
+      // warp arg-max over 4 candidates per lane; ties go to the lower expert index
+      float best = -INFINITY;
+      int be = RT_MAXE;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int e = lane + 32 * j;
+        if (sel[j] > best || (sel[j] == best && e < be)) { best = sel[j]; be = e; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+        if (ob > best || (ob == best && oe < be)) { best = ob; be = oe; }
+      }
+      // the owner lane reports the unbiased score and retires the expert
+      const int owner = be & 31, slot = be >> 5;
+      float score = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (j == slot) score = sc[j];
+      score = __shfl_sync(0xffffffffu, score, owner);
+      if (lane == owner) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (j == slot) sel[j] = -INFINITY;
+      }
+      if (lane == k) { my_w = score; my_e = be; }
+      wsum += score;
+    }
+    if (lane < top_k) {
+      float w = my_w;
+      if (norm_topk) w = w / (wsum + 1e-20f);
+      w *= scaling;
+      idx_out[static_cast<size_t>(t) * top_k + lane] = my_e;
+      weight_out[static_cast<size_t>(t) * top_k + lane] = w;
+      atomicAdd(&counts[my_e], 1);
+      if (load_accum) atomicAdd(&load_accum[my_e], 1.f);
+    }
+  }
+}
+
+// One block. offsets[e] = start row of expert e (multiples of 128), offsets[E] = rows in use.
+// tiles: (m0, expert, valid, 0) for every 128-row tile; entries past the used rows are invalid.
+__global__ void moe_plan_kernel(const int* __restrict__ counts, int E, int* __restrict__ offsets,
+                                int* __restrict__ cursors, int4* __restrict__ tiles, int max_tiles,
+                                int* __restrict__ pair_of, int max_rows) {
+  __shared__ int s_off[RT_MAXE + 1];
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int e = 0; e < E; ++e) {
+      s_off[e] = acc;
+      acc += (counts[e] + 127) / 128 * 128;
+    }
+    s_off[E] = acc;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) {
+    offsets[e] = s_off[e];
+    if (e < E) cursors[e] = 0;
+  }
+  for (int e = threadIdx.x; e < E; e += blockDim.x)
+    for (int m0 = s_off[e], i = s_off[e] / 128; m0 < s_off[e + 1] && i < max_tiles; m0 += 128, ++i)
+      tiles[i] = make_int4(m0, e, 1, 0);
+  for (int i = s_off[E] / 128 + threadIdx.x; i < max_tiles; i += blockDim.x) tiles[i] = make_int4(0, 0, 0, 0);
+  for (int i = threadIdx.x; i < max_rows; i += blockDim.x) pair_of[i] = -1;
+}
+
+__global__ void moe_place_kernel(const int* __restrict__ idx, int n_pairs, const int* __restrict__ offsets,
+                                 int* __restrict__ cursors, int* __restrict__ pos_of, int* __restrict__ pair_of) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_pairs) return;
+  const int e = idx[i];
+  const int pos = offsets[e] + atomicAdd(&cursors[e], 1);
+  pos_of[i] = pos;
+  pair_of[pos] = i;
+}
+
+// rows[pos] = x[pair_of[pos] / k] (zero when the row is padding). One warp per row.
+__global__ void __launch_bounds__(256)
+moe_gather_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const int* __restrict__ pair_of, int top_k,
+                  __nv_bfloat16* __restrict__ rows, int D, int max_rows, const int* __restrict__ offsets, int E) {
+  const int lane = threadIdx.x & 31;
+  const int wpb = blockDim.x >> 5;
+  const int used = offsets[E];
+  for (int r = blockIdx.x * wpb + (threadIdx.x >> 5); r < used; r += gridDim.x * wpb) {
+    const int pair = pair_of[r];
+    uint4* dst = reinterpret_cast<uint4*>(rows + static_cast<size_t>(r) * D);
+    if (pair < 0) {
+      for (int v = lane; v < D / 8; v += 32) dst[v] = make_uint4(0, 0, 0, 0);
+    } else {
+      const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(pair / top_k) * ldx);
+      for (int v = lane; v < D / 8; v += 32) dst[v] = src[v];
+    }
+  }
+}
+
+// out[t] = sum_slot w[t,slot] * rows[pos_of[t,slot]]  (w null: plain sum, used as the gather backward)
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const __nv_bfloat16* __restrict__ rows, const int* __restrict__ pos_of,
+                   const float* __restrict__ w, __nv_bfloat16* __restrict__ out, int ldo, int T, int top_k, int D) {
+  const int lane = threadIdx.x & 31;
+  const int wpb = blockDim.x >> 5;
+  for (int t = blockIdx.x * wpb + (threadIdx.x >> 5); t < T; t += gridDim.x * wpb) {
+    for (int v = lane; v < D / 8; v += 32) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int s = 0; s < top_k; ++s) {
+        const int pos = pos_of[t * top_k + s];
+        const float ws = w ? w[t * top_k + s] : 1.f;
+        const uint4 a = reinterpret_cast<const uint4*>(rows + static_cast<size_t>(pos) * D)[v];
+        float2 f;
+        f = unpack_bf16(a.x); acc[0] += ws * f.x; acc[1] += ws * f.y;
+        f = unpack_bf16(a.y); acc[2] += ws * f.x; acc[3] += ws * f.y;
+        f = unpack_bf16(a.z); acc[4] += ws * f.x; acc[5] += ws * f.y;
+        f = unpack_bf16(a.w); acc[6] += ws * f.x; acc[7] += ws * f.y;
+      }
+      reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * ldo)[v] =
+          make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]), pack_bf16(acc[4], acc[5]), pack_bf16(acc[6], acc[7]));
+    }
+  }
+}
+
+// d_rows[pos] = w[pair] * dout[token(pair)] (0 for padding); d_w[pair] = <rows[pos], dout[token]>
+__global__ void __launch_bounds__(256)
+moe_combine_bwd_kernel(const __nv_bfloat16* __restrict__ rows, const __nv_bfloat16* __restrict__ dout, int lddo,
+                       const int* __restrict__ pair_of, const float* __restrict__ w, __nv_bfloat16* __restrict__ d_rows,
+                       float* __restrict__ d_w, int top_k, int D, const int* __restrict__ offsets, int E) {
+  const int lane = threadIdx.x & 31;
+  const int wpb = blockDim.x >> 5;
+  const int used = offsets[E];
+  for (int r = blockIdx.x * wpb + (threadIdx.x >> 5); r < used; r += gridDim.x * wpb) {
+    const int pair = pair_of[r];
+    uint4* dst = reinterpret_cast<uint4*>(d_rows + static_cast<size_t>(r) * D);
+    if (pair < 0) {
+      for (int v = lane; v < D / 8; v += 32) dst[v] = make_uint4(0, 0, 0, 0);
+      continue;
+    }
+    const float ws = w[pair];
+    const uint4* g = reinterpret_cast<const uint4*>(dout + static_cast<size_t>(pair / top_k) * lddo);
+    const uint4* y = reinterpret_cast<const uint4*>(rows + static_cast<size_t>(r) * D);
+    float dot = 0.f;
+    for (int v = lane; v < D / 8; v += 32) {
+      const uint4 gv = g[v], yv = y[v];
+      const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, yw[4] = {yv.x, yv.y, yv.z, yv.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 gf = unpack_bf16(gw[e]), yf = unpack_bf16(yw[e]);
+        dot += gf.x * yf.x + gf.y * yf.y;
+        o[e] = pack_bf16(ws * gf.x, ws * gf.y);
+      }
+      dst[v] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+    dot = warp_sum(dot);
+    if (lane == 0 && d_w) d_w[pair] = dot;
+  }
+}
+
+static inline int moe_check(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { set_last_error("%s launch: %s", what, cudaGetErrorString(e)); return 11; }
+  return 0;
+}
+
+}  // namespace kwu
+
+using namespace kwu;
+
+KWU_API int kwu_moe_router_fwd(const void* x, int ldx, const float* W, const float* bias, float* logits,
+                               int* idx, float* weight, int* counts, float* load_accum, int T, int D, int E,
+                               int top_k, int score_fn, int norm_topk, float scaling, void* stream) {
+  if (E > RT_MAXE || E % 8 || top_k > 32 || top_k > E) { set_last_error("moe_router: need E <= 128, E %% 8 == 0, k <= 32"); return 7; }
+  if (T <= 0) return 0;
+  moe_router_fwd_kernel<<<(T + RT_BT - 1) / RT_BT, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      (const __nv_bfloat16*)x, ldx, W, bias, logits, idx, weight, counts, load_accum, T, D, E, top_k, score_fn,
+      norm_topk, scaling); kwu::count_launch();
+  return moe_check("moe_router_fwd");
+}
+
+// Host bounds used to size the buffers: rows = pairs + E*127 rounded up to 128; tiles = rows / 128.
+KWU_API int kwu_moe_max_rows(int n_pairs, int E) { return (n_pairs + E * 127 + 127) / 128 * 128; }
+
+KWU_API int kwu_moe_plan_and_place(const int* counts, const int* idx, int n_pairs, int E, int* offsets, int* cursors,
+                                   void* tiles, int max_tiles, int* pos_of, int* pair_of, int max_rows, void* stream) {
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (E > RT_MAXE) { set_last_error("moe_plan: E must be <= 128"); return 7; }
+  moe_plan_kernel<<<1, 1024, 0, st>>>(counts, E, offsets, cursors, reinterpret_cast<int4*>(tiles), max_tiles, pair_of, max_rows); kwu::count_launch();
+  if (n_pairs > 0) {
+    moe_place_kernel<<<(n_pairs + 255) / 256, 256, 0, st>>>(idx, n_pairs, offsets, cursors, pos_of, pair_of); kwu::count_launch();
+  }
+  return moe_check("moe_plan_and_place");
+}
+
+KWU_API int kwu_moe_gather(const void* x, int ldx, const int* pair_of, int top_k, void* rows, int D, int max_rows,
+                           const int* offsets, int E, void* stream) {
+  if (D % 8) { set_last_error("moe_gather: D must be a multiple of 8"); return 7; }
+  moe_gather_kernel<<<148 * 8, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      (const __nv_bfloat16*)x, ldx, pair_of, top_k, (__nv_bfloat16*)rows, D, max_rows, offsets, E); kwu::count_launch();
+  return moe_check("moe_gather");
+}
+
+KWU_API int kwu_moe_combine(const void* rows, const int* pos_of, const float* w, void* out, int ldo, int T, int top_k,
+                            int D, void* stream) {
+  if (D % 8) { set_last_error("moe_combine: D must be a multiple of 8"); return 7; }
+  if (T <= 0) return 0;
+  int grid = (T + 7) / 8;
+  if (grid > 148 * 8) grid = 148 * 8;
+  moe_combine_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      (const __nv_bfloat16*)rows, pos_of, w, (__nv_bfloat16*)out, ldo, T, top_k, D); kwu::count_launch();
+  return moe_check("moe_combine");
+}
+
+KWU_API int kwu_moe_combine_bwd(const void* rows, const void* dout, int lddo, const int* pair_of, const float* w,
+                                void* d_rows, float* d_w, int top_k, int D, const int* offsets, int E, void* stream) {
+  if (D % 8) { set_last_error("moe_combine_bwd: D must be a multiple of 8"); return 7; }
+  moe_combine_bwd_kernel<<<148 * 8, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      (const __nv_bfloat16*)rows, (const __nv_bfloat16*)dout, lddo, pair_of, w, (__nv_bfloat16*)d_rows, d_w, top_k, D,
+      offsets, E); kwu::count_launch();
+  return moe_check("moe_combine_bwd");
+}

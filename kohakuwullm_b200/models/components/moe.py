@@ -60,7 +60,14 @@ class TopKRouter(nn.Module):
         return torch.sqrt(torch.nn.functional.softplus(logits))
 
     def route(self, x: torch.Tensor):
-        """x (T, dim) -> idx (T,k) int64, weight (T,k) fp32, counts (E,) int32."""
+        """x (T, dim) -> idx (T,k), weight (T,k) fp32, counts (E,) int32."""
+        if moe_ops.router_supported(x, self.weight, self.num_groups):
+            idx, w, counts, logits = moe_ops.router_topk(
+                x, self.weight, self.expert_bias, self.load_accum if self.training else None, self.top_k,
+                self.score, self.norm_topk_prob, self.routed_scaling_factor)
+            self.aux_loss = self._aux(logits, self.scores(logits), counts) \
+                if (self.training and (self.aux_loss_weight or self.z_loss_weight)) else None
+            return idx, w, counts
         logits = torch.nn.functional.linear(x.float(), self.weight.float())
         s = self.scores(logits)
         biased = s + self.expert_bias.to(s.dtype)

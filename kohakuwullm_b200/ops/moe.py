@@ -1,17 +1,32 @@
-"""Routed-expert evaluation: counting-sort dispatch, per-expert SwiGLU MLP, weighted combine.
+"""Routed-expert evaluation: router top-k, counting-sort dispatch, grouped expert GEMMs, combine.
 
-``routed_experts_reference`` is the per-expert PyTorch loop (CPU path and test oracle; one host
-read of the expert offsets). ``routed_experts`` is the sync-free native path: a counting sort places
-every (token, slot) pair into an expert-sorted, 128-row-aligned buffer, two grouped tcgen05 GEMMs
-evaluate the experts and a deterministic segment sum combines the results.
-Reference: src/kohakuwullm/kernels/moe/moe_dispatch.py:14-130, grouped_gemm.py:22-362.
+``routed_experts_reference`` is the per-expert PyTorch loop (CPU path and test oracle; one host read of
+the expert offsets). ``routed_experts`` is the native, host-sync-free path:
+
+1. ``plan`` — from the router's per-expert ``counts`` build 128-row-aligned expert offsets, the tile table
+   of the grouped GEMMs and the placement of every (token, slot) pair (``csrc/moe.cu``);
+2. gather the token rows into expert order (padding rows are zero);
+3. ``h = rows @ w_in[e]^T`` — grouped tcgen05 GEMM, SwiGLU, ``y = a @ w_out[e]^T`` — grouped GEMM;
+4. combine: per-token gather-sum weighted by the gate (deterministic, no atomics on the output).
+
+Backward mirrors it: combine-bwd -> grouped dgrad / grouped wgrad (fp32, straight into ``main_grad``
+when the trainer provides it) -> SwiGLU-bwd -> gather-bwd (a per-token gather-sum again).
+Buffer sizes are host-known upper bounds (``pairs + E*127`` rows), so nothing waits on the device.
+Reference: src/kohakuwullm/kernels/moe/moe_dispatch.py:14-130, grouped_gemm.py:22-362, router.py:76-280.
 """
 
 from __future__ import annotations
 
+import ctypes
+from dataclasses import dataclass
+
 import torch
 
 from kohakuwullm_b200.ops import native
+from kohakuwullm_b200.ops.elementwise import swiglu
+
+c_int, c_float = ctypes.c_int, ctypes.c_float
+SCORE_IDS = {"sigmoid": 0, "softmax": 1, "sqrtsoftplus": 2}
 
 
 def routed_experts_reference(x, idx, weight, w_in, w_out):
@@ -19,7 +34,7 @@ def routed_experts_reference(x, idx, weight, w_in, w_out):
     T, dim = x.shape
     k = idx.shape[1]
     E = w_in.shape[0]
-    flat_expert = idx.reshape(-1)
+    flat_expert = idx.reshape(-1).long()
     order = torch.argsort(flat_expert, stable=True)          # pair index sorted by expert
     token_of = order // k
     counts = torch.bincount(flat_expert, minlength=E)
@@ -42,8 +57,207 @@ def routed_experts_reference(x, idx, weight, w_in, w_out):
 
 
 def native_supported(x, w_in) -> bool:
-    return False
+    return (native.available() and x.is_cuda and x.dtype == torch.bfloat16 and w_in.dtype == torch.bfloat16
+            and x.shape[-1] % 64 == 0 and w_in.shape[1] % 128 == 0 and w_in.shape[0] <= 128)
+
+
+# ------------------------------------------------------------------------------------ router
+class _RouterTopK(torch.autograd.Function):
+    """Fused gate GEMM + score + biased top-k + histogram. Backward re-derives the (tiny) score /
+    normalisation gradient from the saved logits with PyTorch ops and forms the two gate-matrix products
+    in fp32."""
+
+    @staticmethod
+    def forward(ctx, x, W, bias, load_accum, top_k, score, norm_topk, scaling):
+        L = native.require()
+        T, D = x.shape
+        E = W.shape[0]
+        logits = torch.empty(T, E, dtype=torch.float32, device=x.device)
+        idx = torch.empty(T, top_k, dtype=torch.int32, device=x.device)
+        weight = torch.empty(T, top_k, dtype=torch.float32, device=x.device)
+        counts = torch.zeros(E, dtype=torch.int32, device=x.device)
+        rc = L.kwu_moe_router_fwd(native.ptr(x), c_int(x.stride(0)), native.ptr(W), native.ptr(bias), native.ptr(logits),
+                                  native.ptr(idx), native.ptr(weight), native.ptr(counts), native.ptr(load_accum),
+                                  c_int(T), c_int(D), c_int(E), c_int(top_k), c_int(SCORE_IDS[score]),
+                                  c_int(int(norm_topk)), c_float(scaling), native.stream_ptr())
+        native.check(rc, "moe_router_fwd")
+        ctx.save_for_backward(x, W, logits, idx)
+        ctx.cfg = (score, norm_topk, scaling)
+        ctx.mark_non_differentiable(idx, counts)
+        return idx, weight, counts, logits
+
+    @staticmethod
+    def backward(ctx, _didx, dweight, _dcounts, dlogits_in):
+        x, W, logits, idx = ctx.saved_tensors
+        score, norm_topk, scaling = ctx.cfg
+        with torch.enable_grad():
+            lg = logits.detach().requires_grad_()
+            if score == "sigmoid":
+                s = torch.sigmoid(lg)
+            elif score == "softmax":
+                s = torch.softmax(lg, -1)
+            else:
+                s = torch.sqrt(torch.nn.functional.softplus(lg))
+            w = s.gather(1, idx.long())
+            if norm_topk:
+                w = w / (w.sum(-1, keepdim=True) + 1e-20)
+            w = w * scaling
+            (dl,) = torch.autograd.grad(w, lg, dweight)
+        if dlogits_in is not None:
+            dl = dl + dlogits_in
+        dx = (dl @ W.float()).to(x.dtype) if ctx.needs_input_grad[0] else None
+        dW = (dl.t() @ x.float()).to(W.dtype) if ctx.needs_input_grad[1] else None
+        return dx, dW, None, None, None, None, None, None
+
+
+def router_topk(x, W, bias, load_accum, top_k, score="sigmoid", norm_topk=True, scaling=1.0):
+    """Native router. Returns ``(idx int32 (T,k), weight fp32 (T,k), counts int32 (E,), logits fp32 (T,E))``."""
+    return _RouterTopK.apply(x, W, bias, load_accum, top_k, score, norm_topk, float(scaling))
+
+
+def router_supported(x, W, num_groups: int) -> bool:
+    return (native.available() and x.is_cuda and x.dtype == torch.bfloat16 and W.dtype == torch.float32
+            and W.shape[0] <= 128 and W.shape[0] % 8 == 0 and num_groups <= 1)
+
+
+# ------------------------------------------------------------------------------------ dispatch plan
+@dataclass
+class DispatchPlan:
+    offsets: torch.Tensor    # (E+1,) int32, 128-aligned expert row offsets; offsets[E] = rows in use
+    tiles: torch.Tensor      # (max_tiles, 4) int32: (m0, expert, valid, 0)
+    pos_of: torch.Tensor     # (T*k,) int32 row of every (token, slot) pair
+    pair_of: torch.Tensor    # (max_rows,) int32 pair of every row, -1 for padding
+    max_rows: int
+    top_k: int
+    num_experts: int
+
+
+def make_plan(idx: torch.Tensor, counts: torch.Tensor, num_experts: int) -> DispatchPlan:
+    L = native.require()
+    T, k = idx.shape
+    n_pairs = T * k
+    max_rows = L.kwu_moe_max_rows(c_int(n_pairs), c_int(num_experts))
+    max_tiles = max_rows // 128
+    dev = idx.device
+    offsets = torch.empty(num_experts + 1, dtype=torch.int32, device=dev)
+    cursors = torch.empty(num_experts, dtype=torch.int32, device=dev)
+    tiles = torch.empty(max_tiles, 4, dtype=torch.int32, device=dev)
+    pos_of = torch.empty(n_pairs, dtype=torch.int32, device=dev)
+    pair_of = torch.empty(max_rows, dtype=torch.int32, device=dev)
+    rc = L.kwu_moe_plan_and_place(native.ptr(counts), native.ptr(idx), c_int(n_pairs), c_int(num_experts),
+                                  native.ptr(offsets), native.ptr(cursors), native.ptr(tiles), c_int(max_tiles),
+                                  native.ptr(pos_of), native.ptr(pair_of), c_int(max_rows), native.stream_ptr())
+    native.check(rc, "moe_plan_and_place")
+    return DispatchPlan(offsets, tiles, pos_of, pair_of, max_rows, k, num_experts)
+
+
+class _Gather(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, plan: DispatchPlan):
+        L = native.require()
+        T, D = x.shape
+        rows = torch.empty(plan.max_rows, D, dtype=x.dtype, device=x.device)
+        rc = L.kwu_moe_gather(native.ptr(x), c_int(x.stride(0)), native.ptr(plan.pair_of), c_int(plan.top_k),
+                              native.ptr(rows), c_int(D), c_int(plan.max_rows), native.ptr(plan.offsets),
+                              c_int(plan.num_experts), native.stream_ptr())
+        native.check(rc, "moe_gather")
+        ctx.plan, ctx.T = plan, T
+        return rows
+
+    @staticmethod
+    def backward(ctx, drows):
+        L = native.require()
+        plan = ctx.plan
+        D = drows.shape[1]
+        dx = torch.empty(ctx.T, D, dtype=drows.dtype, device=drows.device)
+        rc = L.kwu_moe_combine(native.ptr(drows.contiguous()), native.ptr(plan.pos_of), native.ptr(None), native.ptr(dx),
+                               c_int(D), c_int(ctx.T), c_int(plan.top_k), c_int(D), native.stream_ptr())
+        native.check(rc, "moe_gather_bwd")
+        return dx, None
+
+
+class _GroupedLinear(torch.autograd.Function):
+    """``out[rows of expert e] = rows @ W[e]^T`` with W (E, N, K)."""
+
+    @staticmethod
+    def forward(ctx, rows, W, plan: DispatchPlan):
+        L = native.require()
+        E, N, K = W.shape
+        out = torch.empty(plan.max_rows, N, dtype=rows.dtype, device=rows.device)
+        rc = L.kwu_gemm_bf16_grouped_rows(native.ptr(rows), native.ptr(W), native.ptr(out), c_int(plan.max_rows), c_int(N),
+                                          c_int(K), c_int(rows.stride(0)), c_int(K), c_int(N), c_int(0), c_int(E),
+                                          native.ptr(plan.tiles), c_int(plan.tiles.shape[0]), c_int(0),
+                                          native.stream_ptr(), native.ptr(native.status_word()))
+        native.check(rc, "grouped_gemm_fwd")
+        ctx.save_for_backward(rows, W)
+        ctx.plan = plan
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        L = native.require()
+        rows, W = ctx.saved_tensors
+        plan = ctx.plan
+        E, N, K = W.shape
+        dout = dout.contiguous()
+        drows = dW = None
+        if ctx.needs_input_grad[0]:
+            drows = torch.empty(plan.max_rows, K, dtype=rows.dtype, device=rows.device)
+            # dx = dy W_e : B = W viewed as (E*N, K) stored [contraction N rows][K cols] per expert
+            rc = L.kwu_gemm_bf16_grouped_rows(native.ptr(dout), native.ptr(W), native.ptr(drows), c_int(plan.max_rows),
+                                              c_int(K), c_int(N), c_int(dout.stride(0)), c_int(K), c_int(K), c_int(1),
+                                              c_int(E), native.ptr(plan.tiles), c_int(plan.tiles.shape[0]), c_int(0),
+                                              native.stream_ptr(), native.ptr(native.status_word()))
+            native.check(rc, "grouped_gemm_dgrad")
+        if ctx.needs_input_grad[1]:
+            main_grad = getattr(W, "main_grad", None)
+            target = main_grad if main_grad is not None else torch.zeros(E, N, K, dtype=torch.float32, device=W.device)
+            rc = L.kwu_gemm_bf16_grouped_wgrad(native.ptr(dout), native.ptr(rows), native.ptr(target), c_int(plan.max_rows),
+                                               c_int(N), c_int(K), c_int(dout.stride(0)), c_int(rows.stride(0)), c_int(E),
+                                               native.ptr(plan.offsets), c_int(1), c_int(1), native.stream_ptr(),
+                                               native.ptr(native.status_word()))
+            native.check(rc, "grouped_gemm_wgrad")
+            if main_grad is None:
+                dW = target.to(W.dtype)
+        return drows, dW, None
+
+
+class _Combine(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, rows, weight, plan: DispatchPlan, T):
+        L = native.require()
+        D = rows.shape[1]
+        out = torch.empty(T, D, dtype=rows.dtype, device=rows.device)
+        w = weight.reshape(-1).float().contiguous()
+        rc = L.kwu_moe_combine(native.ptr(rows), native.ptr(plan.pos_of), native.ptr(w), native.ptr(out), c_int(D),
+                               c_int(T), c_int(plan.top_k), c_int(D), native.stream_ptr())
+        native.check(rc, "moe_combine")
+        ctx.save_for_backward(rows, w)
+        ctx.plan, ctx.wshape, ctx.wdtype = plan, weight.shape, weight.dtype
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        L = native.require()
+        rows, w = ctx.saved_tensors
+        plan = ctx.plan
+        D = rows.shape[1]
+        dout = dout.contiguous()
+        drows = torch.empty_like(rows)
+        dw = torch.zeros_like(w)
+        rc = L.kwu_moe_combine_bwd(native.ptr(rows), native.ptr(dout), c_int(dout.stride(0)), native.ptr(plan.pair_of),
+                                   native.ptr(w), native.ptr(drows), native.ptr(dw), c_int(plan.top_k), c_int(D),
+                                   native.ptr(plan.offsets), c_int(plan.num_experts), native.stream_ptr())
+        native.check(rc, "moe_combine_bwd")
+        return drows, dw.view(ctx.wshape).to(ctx.wdtype), None, None
 
 
 def routed_experts(x, idx, weight, counts, w_in, w_out):
-    raise native.NativeError("native routed experts are not built in this configuration")
+    """Native routed-expert MLP. ``idx`` (T,k) int32, ``weight`` (T,k), ``counts`` (E,) int32 from the router."""
+    T = x.shape[0]
+    plan = make_plan(idx.to(torch.int32).contiguous(), counts.to(torch.int32), w_in.shape[0])
+    rows = _Gather.apply(x.contiguous(), plan)
+    h = _GroupedLinear.apply(rows, w_in, plan)
+    a = swiglu(h)
+    y_rows = _GroupedLinear.apply(a, w_out, plan)
+    return _Combine.apply(y_rows, weight, plan, T)
