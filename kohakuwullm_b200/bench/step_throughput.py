@@ -1,0 +1,131 @@
+"""Step throughput of any preset at a fixed optimizer-step token budget.
+
+    python -m kohakuwullm_b200.bench.step_throughput --preset B200-moe-991M --micro-tokens 4096 --accum 4
+    torchrun --nproc-per-node 4 -m kohakuwullm_b200.bench.step_throughput --preset B200-moe-991M --pipeline
+
+Data-parallel mode runs ``TrainEngine`` (token-exact accumulation, fused gradient sync on N>1); with
+``--pipeline`` the ranks form a pipeline whose split is measured at start-up (``measure_costs`` on rank 0,
+broadcast, ``plan_for``) and driven by the 1F1B schedule. Packs are synthetic (documents uniform or
+log-uniform in ``[len-min, len-max]``, random ids). Timing: CUDA events around ``--steps`` steps after
+``--warmup`` steps, barrier + synchronize on both sides, max over ranks.
+Reference: scripts/bench/e2e/step_throughput.py:100-374.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import time
+
+import torch
+import torch.distributed as dist
+
+from kohakuwullm_b200.data.synthetic import make_packs
+from kohakuwullm_b200.models import LMBackbone, get_preset
+
+
+def _timed(fn, steps, world):
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(steps):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([s.elapsed_time(e)], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t[0])
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--preset", default="B200-dense-546M")
+    ap.add_argument("--micro-tokens", type=int, default=4096)
+    ap.add_argument("--accum", type=int, default=4)
+    ap.add_argument("--len-min", type=int, default=64)
+    ap.add_argument("--len-max", type=int, default=4096)
+    ap.add_argument("--log-uniform", action="store_true")
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--pipeline", action="store_true")
+    ap.add_argument("--schedule", default="1f1b")
+    ap.add_argument("--no-mxfp8", action="store_true")
+    ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--set", action="append", default=[], help="config override KEY=VALUE (python literal)")
+    args = ap.parse_args(argv)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        if args.pipeline:
+            dist.init_process_group("nccl")  # lazy: per-pair communicators for P2P
+        else:
+            dist.init_process_group("nccl", device_id=dev)
+    overrides = {}
+    for kv in args.set:
+        k, v = kv.split("=", 1)
+        try:
+            overrides[k] = eval(v, {}, {})  # noqa: S307  operator-supplied literals
+        except Exception:  # noqa: BLE001
+            overrides[k] = v
+    if args.no_mxfp8:
+        overrides["mxfp8"] = False
+    cfg = get_preset(args.preset, **overrides)
+    torch.manual_seed(1234)
+
+    if args.pipeline and world > 1:
+        from kohakuwullm_b200.pipe.trainer import PipelineTrainer
+        from kohakuwullm_b200.training.parallel.autotune import broadcast_costs, measure_costs
+        from kohakuwullm_b200.training.parallel.pipeline import plan_for
+        from kohakuwullm_b200.training.parallel.uwupipe import LMPipelineModule
+
+        costs = measure_costs(cfg, args.micro_tokens, dev) if rank == 0 else None
+        costs = broadcast_costs(costs, cfg.depth, dev)
+        plans = plan_for(cfg, world, args.micro_tokens, costs=costs)
+        module = LMPipelineModule(cfg, micro_tokens=args.micro_tokens, lr=1e-4)
+        trainer = PipelineTrainer(module, plans, rank=rank, world=world, device=dev, n_micro=args.accum,
+                                  schedule=args.schedule)
+        packs = make_packs(args.accum, args.micro_tokens, args.len_min, args.len_max, cfg.vocab_size, seed=17,
+                           log_uniform=args.log_uniform)
+        step = lambda: trainer.loop.step(packs)  # noqa: E731
+        split = [p.num_layers for p in plans]
+        tokens_per_step = args.micro_tokens * args.accum
+    else:
+        from kohakuwullm_b200.training.engine import TrainEngine
+
+        with torch.device(dev):
+            model = LMBackbone(cfg)
+        engine = TrainEngine(model, lr=1e-4, param_dtype=torch.bfloat16,
+                             grad_sync="fused" if world > 1 else "nccl", cuda_graphs=not args.no_graphs)
+        packs = [p.to(dev) for p in make_packs(args.accum, args.micro_tokens, args.len_min, args.len_max,
+                                               cfg.vocab_size, seed=17 + rank, log_uniform=args.log_uniform)]
+        step = lambda: engine.step(packs)  # noqa: E731
+        split = None
+        tokens_per_step = args.micro_tokens * args.accum * world
+
+    for _ in range(args.warmup):
+        out = step()
+    ms = _timed(step, args.steps, world)
+    from kohakuwullm_b200.ops import native
+
+    native.check_status()
+    if rank == 0:
+        loss = out["loss"] if isinstance(out, dict) else out.loss
+        print(json.dumps({"preset": args.preset, "n_gpus": world, "mode": "pipeline" if args.pipeline and world > 1 else "dp",
+                          "split": split, "tokens_per_step": tokens_per_step, "ms_per_step": ms / args.steps,
+                          "tokens_per_s": tokens_per_step * args.steps / (ms / 1e3), "loss": float(loss),
+                          "peak_mem_gib": torch.cuda.max_memory_allocated() / 2 ** 30}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
