@@ -123,8 +123,11 @@ class PipelineLoop:
         self.callbacks.on_fit_start(self)
         self.callbacks.on_train_start(self)
         try:
-            for batch in batches:
-                if self.global_step >= max_steps:
+            it = iter(batches)
+            while self.global_step < max_steps:  # test before pulling, so no fetched batch goes untrained
+                try:
+                    batch = next(it)
+                except StopIteration:
                     break
                 outs.append(self.step(batch))
         except BaseException as exc:  # noqa: BLE001  every rank's callbacks hear about it, then it propagates
