@@ -1,0 +1,8 @@
+"""DeepSeekMoE ~991M under pipeline parallelism: measured split, 1F1B, 16 micro-batches of 4096 tokens."""
+
+PRESET = "B200-moe-991M"
+MICRO_TOKENS = 4096
+NUM_MICROBATCHES = 16
+SCHEDULE = "1f1b"
+AUTOTUNE = True
+LR = 3e-4
