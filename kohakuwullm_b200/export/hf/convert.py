@@ -1,0 +1,58 @@
+"""Framework checkpoint / live model -> Hugging Face repository (config, weights, modeling code)."""
+
+from __future__ import annotations
+
+import os
+import shutil
+
+import torch
+
+
+def to_hf_config(cfg):
+    from kohakuwullm_b200.export.hf.configuration_kohaku import KohakuConfig
+
+    rk = cfg.moe_router_kwargs or {}
+    return KohakuConfig(
+        vocab_size=cfg.vocab_size, hidden_size=cfg.dim, num_hidden_layers=cfg.depth, num_attention_heads=cfg.heads,
+        num_key_value_heads=cfg.kv_heads, head_dim=cfg.head_dim,
+        intermediate_size=cfg.mlp_hidden or int(-(-cfg.dim * cfg.mlp_ratio * 2 / 3 // cfg.mlp_multiple_of) * cfg.mlp_multiple_of),
+        rms_norm_eps=cfg.norm_eps, kohaku_rope_theta=cfg.rope_theta, kohaku_rope_scaling=cfg.rope_scaling,
+        kohaku_rope_factor=cfg.rope_factor,
+        max_position_embeddings=cfg.max_position, qk_norm=cfg.qk_norm, windows=cfg.windows,
+        num_sinks=cfg.attn_num_sinks if cfg.attn_sink else 0, moe_layers=cfg.moe_layers,
+        moe_num_experts=cfg.moe_num_experts if any(cfg.moe_layers) else 0, moe_top_k=cfg.moe_top_k,
+        moe_num_shared=cfg.moe_num_shared, moe_intermediate_size=cfg.moe_hidden or 0, moe_score=rk.get("score", "sigmoid"),
+        moe_norm_topk_prob=rk.get("norm_topk_prob", True), moe_scaling=rk.get("routed_scaling_factor", 1.0),
+        tie_word_embeddings=cfg.tie_embeddings, embedding_scale=cfg.embedding_scale, logit_soft_cap=cfg.logit_soft_cap)
+
+
+def convert_state_dict(state: dict, cfg) -> dict:
+    out = {}
+    for k, v in state.items():
+        if k.endswith("load_accum"):
+            continue
+        k = k.replace("head.proj.weight", "lm_head.weight").replace(".mlp.router.weight", ".mlp.router.weight")
+        k = k.replace(".mlp.router.expert_bias", ".mlp.expert_bias")
+        k = k.replace(".mlp.shared.w_in.weight", ".mlp.shared.w_in.weight")
+        out[k] = v
+    if cfg.tie_embeddings:
+        out["lm_head.weight"] = out["embed.weight"]
+    return out
+
+
+def export_hf(backbone_or_state, cfg, out_dir: str, dtype=torch.bfloat16):
+    from kohakuwullm_b200.export.hf.modeling_kohaku import KohakuForCausalLM
+
+    state = backbone_or_state.state_dict() if hasattr(backbone_or_state, "state_dict") else backbone_or_state
+    hf_cfg = to_hf_config(cfg)
+    hf_cfg.auto_map = {"AutoConfig": "configuration_kohaku.KohakuConfig",
+                       "AutoModelForCausalLM": "modeling_kohaku.KohakuForCausalLM"}
+    model = KohakuForCausalLM(hf_cfg)
+    missing, unexpected = model.load_state_dict(convert_state_dict(state, cfg), strict=False)
+    if unexpected or [m for m in missing if "inv_freq" not in m]:
+        raise RuntimeError(f"export mismatch: missing {missing[:5]} unexpected {unexpected[:5]}")
+    model.to(dtype).save_pretrained(out_dir, safe_serialization=True)
+    here = os.path.dirname(__file__)
+    for f in ("configuration_kohaku.py", "modeling_kohaku.py"):
+        shutil.copy(os.path.join(here, f), os.path.join(out_dir, f))
+    return model
