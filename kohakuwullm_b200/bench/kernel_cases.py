@@ -1,0 +1,174 @@
+"""Per-kernel micro-benchmarks with roofline fractions against the measured peaks of this machine.
+
+    python -m kohakuwullm_b200.bench.kernel_cases                 # all cases, one JSON line each
+    python -m kohakuwullm_b200.bench.kernel_cases --only flash    # a single family (used under ncu)
+
+Every case is timed with CUDA events on the launching stream after warm-up, with an L2 flush before each
+sample (``bench_samples``). FLOP / byte counts are the algorithmic ones. Shapes are those of the dense
+546M benchmark config (4096-token packs, d 1280, FFN 3584, 20/4 heads of 64, vocab 65536).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+
+import torch
+
+from kohakuwullm_b200.bench.timing import bench_samples, module_metrics
+
+
+def _report(name, samples, **kw):
+    ms = statistics.median(samples)
+    out = {"case": name, **module_metrics(ms, **kw)}
+    print(json.dumps(out), flush=True)
+
+
+def case_gemm(reps):
+    from kohakuwullm_b200.ops.gemm import matmul
+
+    for (M, N, K, amn, bmn, tag) in [(8192, 8192, 8192, False, False, "square"), (4096, 1792, 1280, False, False, "qkv_fwd"),
+                                     (4096, 7168, 1280, False, False, "w_in_fwd"), (4096, 1280, 3584, False, False, "w_out_fwd"),
+                                     (4096, 1280, 7168, False, True, "w_in_dgrad"), (7168, 1280, 4096, True, True, "w_in_wgrad")]:
+        a = torch.randn((K, M) if amn else (M, K), device="cuda").to(torch.bfloat16)
+        b = torch.randn((K, N) if bmn else (N, K), device="cuda").to(torch.bfloat16)
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        s = bench_samples(lambda: matmul(a, b, a_mn=amn, b_mn=bmn, out=out), repeats=reps)
+        _report(f"gemm_bf16/{tag}_{M}x{N}x{K}", s, flops=2.0 * M * N * K, bytes_moved=2.0 * (M * K + N * K + M * N))
+
+
+def case_mxfp8(reps):
+    from kohakuwullm_b200.ops import mxfp8 as mx
+
+    for (M, N, K, tag) in [(8192, 8192, 8192, "square"), (4096, 1792, 1280, "qkv_fwd"), (4096, 7168, 1280, "w_in_fwd"),
+                           (4096, 1280, 3584, "w_out_fwd")]:
+        a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+        b = torch.randn(N, K, device="cuda").to(torch.bfloat16)
+        aq, asf = mx.quantize(a)
+        bq, bsf = mx.quantize(b)
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        s = bench_samples(lambda: mx.gemm(aq, asf, bq, bsf, out=out), repeats=reps)
+        _report(f"gemm_mxfp8/{tag}_{M}x{N}x{K}", s, flops=2.0 * M * N * K, bytes_moved=1.0 * (M * K + N * K) + 2.0 * M * N)
+    x = torch.randn(16384, 3584, device="cuda").to(torch.bfloat16)
+    q = torch.empty(16384, 3584, dtype=torch.uint8, device="cuda")
+    sf = torch.empty(mx.sf_bytes(16384, 3584), dtype=torch.uint8, device="cuda")
+    s = bench_samples(lambda: mx.quantize(x, q, sf), repeats=reps)
+    _report("mxfp8_quantize/16384x3584", s, bytes_moved=x.numel() * 3.0 + sf.numel())
+    w = torch.randn(7168, 1280, device="cuda").to(torch.bfloat16)
+    s = bench_samples(lambda: mx.quantize_transposed(w), repeats=reps)
+    _report("mxfp8_quantize_t/7168x1280", s, bytes_moved=w.numel() * 3.0)
+
+
+def case_flash(reps):
+    from kohakuwullm_b200.models.flops import attention_pairs
+    from kohakuwullm_b200.models.seqinfo import SeqInfo
+    from kohakuwullm_b200.ops.attention import attention_plan, varlen_attention
+
+    for lengths, window, tag in [([2500, 1596], None, "causal_4096"), ([16384], 1024, "window1024_16384"), ([16384], None, "causal_16384")]:
+        info = SeqInfo.from_lengths(lengths, device="cuda")
+        T, Hq, Hkv = info.total_tokens, 20, 4
+        q = torch.randn(T, Hq, 64, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+        k = torch.randn(T, Hkv, 64, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+        v = torch.randn(T, Hkv, 64, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+        do = torch.randn(T, Hq, 64, device="cuda", dtype=torch.bfloat16)
+        plan = attention_plan(info.cu_seqlens, T)
+        pairs = sum(attention_pairs(n, window) for n in lengths)
+        fwd_flops = 4.0 * Hq * 64 * pairs
+        with torch.no_grad():
+            s = bench_samples(lambda: varlen_attention(q, k, v, info.cu_seqlens, window=window, plan=plan), repeats=reps)
+        _report(f"flash_fwd/{tag}", s, flops=fwd_flops)
+        out = varlen_attention(q, k, v, info.cu_seqlens, window=window, plan=plan)
+
+        def bwd():
+            q.grad = k.grad = v.grad = None
+            out.backward(do, retain_graph=True)
+
+        s = bench_samples(bwd, repeats=reps)
+        _report(f"flash_bwd/{tag}", s, flops=2.5 * fwd_flops)
+
+
+def case_elementwise(reps):
+    from kohakuwullm_b200.ops.elementwise import qknorm_rope, rmsnorm, swiglu
+
+    rows, cols = 32768, 1280
+    x = torch.randn(rows, cols, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    res = torch.randn(rows, cols, device="cuda", dtype=torch.bfloat16)
+    w = torch.ones(cols, device="cuda", requires_grad=True)
+    with torch.no_grad():
+        s = bench_samples(lambda: rmsnorm(x, w, residual=res), repeats=reps)
+    _report(f"rmsnorm_add_fwd/{rows}x{cols}", s, bytes_moved=rows * cols * 2.0 * 4)
+    y, h = rmsnorm(x, w, residual=res)
+    dy = torch.randn_like(y)
+
+    def bwd():
+        x.grad = w.grad = None
+        torch.autograd.backward([y, h], [dy, dy], retain_graph=True)
+
+    s = bench_samples(bwd, repeats=reps)
+    _report(f"rmsnorm_add_bwd/{rows}x{cols}", s, bytes_moved=rows * cols * 2.0 * 4)
+    hh = torch.randn(16384, 2 * 3584, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    with torch.no_grad():
+        s = bench_samples(lambda: swiglu(hh), repeats=reps)
+    _report("swiglu_fwd/16384x3584", s, bytes_moved=16384 * 3584 * 2.0 * 3)
+    qkv = torch.randn(16384, 28 * 64, device="cuda", dtype=torch.bfloat16)
+    ang = torch.rand(16384, 32, device="cuda")
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    qw = torch.ones(64, device="cuda")
+    with torch.no_grad():
+        s = bench_samples(lambda: qknorm_rope(qkv[:, :1280].view(16384, 20, 64), qw, cos, sin), repeats=reps)
+    _report("qknorm_rope_fwd/16384x20x64", s, bytes_moved=16384 * 1280 * 2.0 * 2)
+
+
+def case_loss(reps):
+    from kohakuwullm_b200.ops.loss import linear_cross_entropy
+
+    T, D, V = 4096, 1280, 65536
+    h = (torch.randn(T, D, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_()
+    w = (torch.randn(V, D, device="cuda") * 0.02).to(torch.bfloat16).requires_grad_()
+    labels = torch.randint(0, V, (T,), device="cuda")
+    with torch.no_grad():
+        s = bench_samples(lambda: linear_cross_entropy(h, w, labels), repeats=reps)
+    _report(f"linear_ce_fwd/{T}x{D}x{V}", s, flops=2.0 * T * D * V)
+
+    def fb():
+        h.grad = w.grad = None
+        ce, lse = linear_cross_entropy(h, w, labels)
+        (ce.sum() + 1e-4 * (lse ** 2).sum()).backward()
+
+    s = bench_samples(fb, repeats=reps)
+    _report(f"linear_ce_fwd_bwd/{T}x{D}x{V}", s, flops=8.0 * T * D * V)
+
+
+def case_optim(reps):
+    from kohakuwullm_b200.parallel.flat import FlatParameters
+    from kohakuwullm_b200.training.optim.fused_adamw import FlatAdamW
+
+    lin = torch.nn.Linear(8192, 16384, bias=False, device="cuda", dtype=torch.bfloat16)
+    flat = FlatParameters(lin)
+    opt = FlatAdamW(flat)
+    n = lin.weight.numel()
+    s = bench_samples(lambda: opt.step(), repeats=reps)
+    _report(f"adamw_flat/{n}", s, bytes_moved=n * (4 * 4 * 2 + 2.0))   # grad r+zero, master/m/v r+w, bf16 w
+
+
+CASES = {"gemm": case_gemm, "mxfp8": case_mxfp8, "flash": case_flash, "elementwise": case_elementwise, "loss": case_loss,
+         "optim": case_optim}
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default=None, choices=sorted(CASES))
+    ap.add_argument("--reps", type=int, default=10)
+    args = ap.parse_args(argv)
+    for name, fn in CASES.items():
+        if args.only in (None, name):
+            fn(args.reps)
+    from kohakuwullm_b200.ops import native
+
+    torch.cuda.synchronize()
+    native.check_status()
+
+
+if __name__ == "__main__":
+    main()

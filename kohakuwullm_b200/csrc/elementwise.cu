@@ -91,6 +91,15 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
   if (dw_partial)
     for (int i = threadIdx.x; i < cols; i += blockDim.x) s_dw[i] = 0.f;
   __syncthreads();
+  // a lane always owns the same columns (vectors lane, lane+32, ...), so the weight gradient of up to
+  // RMS_REG_VECS vectors per lane is summed over the warp's rows in registers and flushed once
+  constexpr int RMS_REG_VECS = 8;   // covers cols <= 2048; wider rows fall back to shared atomics
+  const bool reg_dw = dw_partial && nvec <= 32 * RMS_REG_VECS;
+  float dw_acc[RMS_REG_VECS][8];
+#pragma unroll
+  for (int j = 0; j < RMS_REG_VECS; ++j)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) dw_acc[j][e] = 0.f;
   for (int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows;
        row += gridDim.x * warps_per_block) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * cols);
@@ -115,7 +124,9 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
     dot = warp_sum(dot) / static_cast<float>(cols);
     const uint4* rr = dres ? reinterpret_cast<const uint4*>(dres + static_cast<size_t>(row) * cols) : nullptr;
     uint4* dxr = reinterpret_cast<uint4*>(dx + static_cast<size_t>(row) * cols);
-    for (int v = lane; v < nvec; v += 32) {
+#pragma unroll
+    for (int jj = 0; jj < RMS_REG_VECS + 1; ++jj) {
+     for (int v = lane + 32 * jj; v < nvec; v += (jj == RMS_REG_VECS ? 32 : nvec)) {
       const uint4 a = xr[v], g = gr[v];
       float xf[8], gf[8], rf[8];
       float2 t;
@@ -138,12 +149,25 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
         if (w) we = one_plus ? 1.f + w[8 * v + e] : w[8 * v + e];
         const float xhat = xf[e] * rstd;
         o[e] = rstd * (gf[e] * we - xhat * dot) + rf[e];
-        if (dw_partial) atomicAdd(&s_dw[8 * v + e], gf[e] * xhat);
+        if (dw_partial) {
+          if (reg_dw && jj < RMS_REG_VECS) dw_acc[jj < RMS_REG_VECS ? jj : 0][e] += gf[e] * xhat;
+          else atomicAdd(&s_dw[8 * v + e], gf[e] * xhat);
+        }
       }
       uint4 ov;
       ov.x = pack_bf16(o[0], o[1]); ov.y = pack_bf16(o[2], o[3]);
       ov.z = pack_bf16(o[4], o[5]); ov.w = pack_bf16(o[6], o[7]);
       dxr[v] = ov;
+     }
+    }
+  }
+  if (reg_dw) {
+#pragma unroll
+    for (int j = 0; j < RMS_REG_VECS; ++j) {
+      const int v = lane + 32 * j;
+      if (v < nvec)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) atomicAdd(&s_dw[8 * v + e], dw_acc[j][e]);
     }
   }
   if (dw_partial) {

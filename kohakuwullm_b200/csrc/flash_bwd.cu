@@ -18,7 +18,7 @@
 namespace kwu {
 
 constexpr int FB_D = 64;
-constexpr int FB_THREADS = 192;
+constexpr int FB_THREADS = 320;  // 8 softmax warps (two per TMEM lane quarter) + TMA warp + MMA warp
 constexpr float FB_LOG2E = 1.4426950408889634f;
 
 // ------------------------------------------------------------------------------------ delta
@@ -107,12 +107,12 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
       mbar_init(&qd_empty[s], 1);
     }
     mbar_init(sdp_full, 1);
-    mbar_init(p_ready, 128);
+    mbar_init(p_ready, 256);
     mbar_init(acc_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(tmem_slot, 256);
     tmem_relinquish();
   }
@@ -122,7 +122,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tS = tmem_base, tDP = tmem_base + 64, tDV = tmem_base + 128, tDK = tmem_base + 192;
 
-  if (warp == 4) {
+  if (warp == 8) {
     if (lane == 0) {
       mbar_expect_tx(kv_full, 32768);
       tma_load_2d(sK, &tmK128, kv_full, hk * FB_D, kv0);
@@ -152,7 +152,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
         tma_load_2d(sDO + s * 8192, &tmDO64, &qd_full[s], h * FB_D, q_lo);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc_f16(128, 64, 1, 0, 0);   // S^T, dP^T: N = 64 queries
       const uint32_t idesc_a = make_idesc_f16(128, 64, 1, 0, 1);   // dV, dK: B is MN-major
@@ -190,9 +190,11 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
       if (ok) tc_commit(acc_done);
     }
   } else {
-    const int row = warp * 32 + lane;
+    // two threads per key row: warp w handles query columns [0,32) of the tile, warp w+4 columns [32,64)
+    const int quarter = warp & 3, half = warp >> 2;
+    const int row = quarter * 32 + lane;
     const int kj = kv0 + row;
-    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const float c_log2 = p.scale * FB_LOG2E;
     bool ok = true;
     for (int it = 0; it < n_it; ++it) {
@@ -210,8 +212,8 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
       int c_hi_q = min(q_end, p.window > 0 ? kj + p.window : q_end) - 1 - q_lo;  // window and document end
       if (kj >= de) c_hi_q = -1;
       const bool need_mask = (c_lo_q > 0) || (c_hi_q < 63);
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      {
+        const int c = half;
         uint32_t sv[32], dp[32], pp[16], dd[16];
         tmem_ld_x32(tS + lane_addr + c * 32, sv);
         tmem_ld_x32(tDP + lane_addr + c * 32, dp);
@@ -244,8 +246,8 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
     }
     if (ok) {
       tc_fence_after();
-#pragma unroll
-      for (int which = 0; which < 2; ++which) {
+      {
+        const int which = half;  // the first thread of a row writes dV, the second dK
         uint32_t o[64];
         const uint32_t src = (which == 0 ? tDV : tDK) + lane_addr;
         tmem_ld_x32(src, o);
@@ -282,7 +284,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
   __syncthreads();
   if (*abort_flag)
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 256);
   }
@@ -334,12 +336,12 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
       mbar_init(&kv_empty[s], 1);
     }
     mbar_init(sdp_full, 1);
-    mbar_init(p_ready, 128);
+    mbar_init(p_ready, 256);
     mbar_init(acc_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(tmem_slot, 256);
     tmem_relinquish();
   }
@@ -349,7 +351,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tS = tmem_base, tDP = tmem_base + 64, tDQ = tmem_base + 128;
 
-  if (warp == 4) {
+  if (warp == 8) {
     if (lane == 0) {
       mbar_expect_tx(q_full, 32768);
       tma_load_2d(sQ, &tmQ128, q_full, h * FB_D, q0);
@@ -363,7 +365,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
         tma_load_2d(sV + s * 8192, &tmV64, &kv_full[s], hk * FB_D, lo + j * 64);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc_f16(128, 64, 1, 0, 0);
       const uint32_t idesc_q = make_idesc_f16(128, 64, 1, 0, 1);
@@ -397,9 +399,10 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
       if (ok) tc_commit(acc_done);
     }
   } else {
-    const int row = warp * 32 + lane;
+    const int quarter = warp & 3, half = warp >> 2;   // two threads per query row, 32 key columns each
+    const int row = quarter * 32 + lane;
     const int qi = q0 + row;
-    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const float c_log2 = p.scale * FB_LOG2E;
     const int qc = min(qi, p.T - 1);
     const float lse_q = p.lse[static_cast<size_t>(h) * p.T + qc] * FB_LOG2E;
@@ -415,8 +418,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
       const int c_hi_k = (qi < q_hi) ? (qi - kv0) : -1;
       const int c_lo_k = (p.window > 0) ? (qi - p.window + 1 - kv0) : 0;
       const bool need_mask = (c_hi_k < 63) || (c_lo_k > 0);
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      {
+        const int c = half;
         uint32_t sv[32], dp[32], dd[16];
         tmem_ld_x32(tS + lane_addr + c * 32, sv);
         tmem_ld_x32(tDP + lane_addr + c * 32, dp);
@@ -445,14 +448,13 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
     }
     if (ok) {
       tc_fence_after();
-      uint32_t o[64];
-      tmem_ld_x32(tDQ + lane_addr, o);
-      tmem_ld_x32(tDQ + lane_addr + 32, o + 32);
+      uint32_t o[32];
+      tmem_ld_x32(tDQ + lane_addr + half * 32, o);
       tmem_ld_wait();
       if (qi < q_hi) {
-        uint4* dst = reinterpret_cast<uint4*>(p.dq + (static_cast<size_t>(qi) * p.Hq + h) * FB_D);
+        uint4* dst = reinterpret_cast<uint4*>(p.dq + (static_cast<size_t>(qi) * p.Hq + h) * FB_D + half * 32);
 #pragma unroll
-        for (int v = 0; v < 8; ++v) {
+        for (int v = 0; v < 4; ++v) {
           uint4 w;
           w.x = pack_bf16(__uint_as_float(o[8 * v + 0]), __uint_as_float(o[8 * v + 1]));
           w.y = pack_bf16(__uint_as_float(o[8 * v + 2]), __uint_as_float(o[8 * v + 3]));
@@ -468,7 +470,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
   __syncthreads();
   if (*abort_flag)
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 256);
   }

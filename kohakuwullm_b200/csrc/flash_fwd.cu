@@ -20,9 +20,9 @@ namespace kwu {
 constexpr int FA_BM = 128;   // query rows per CTA
 constexpr int FA_BN = 128;   // keys per tile
 constexpr int FA_D = 64;
-constexpr int FA_THREADS = 192;
+constexpr int FA_THREADS = 320;  // 8 softmax warps + TMA warp + MMA warp
 constexpr int FA_TILE_BYTES = 128 * 64 * 2;  // 16 KB
-constexpr int FA_SMEM = 5 * FA_TILE_BYTES + 1024 + 1024;
+constexpr int FA_SMEM = 5 * FA_TILE_BYTES + 1024 + 3072 + 1024;  // tiles + barriers + row-max exchange + alignment slack
 constexpr float FA_NEG = -1.0e30f;
 
 struct FlashFwdParams {
@@ -86,6 +86,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* o_done = bars + 11;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* s_rowmax = reinterpret_cast<float*>(smem + 5 * FA_TILE_BYTES + 1024);  // 2 x 256 max + 256 sums
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -105,12 +106,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_init(&v_empty[s], 1);
     }
     mbar_init(s_full, 1);
-    mbar_init(p_full, 128);
+    mbar_init(p_full, 256);
     mbar_init(o_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(tmem_slot, 256);
     tmem_relinquish();
   }
@@ -120,7 +121,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tS = tmem_base, tP = tmem_base + 128, tO = tmem_base + 192;
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
       tma_prefetch_desc(&tmQ);
@@ -140,7 +141,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tma_load_2d(sV + s * FA_TILE_BYTES, &tmV, &v_full[s], hk * FA_D, kv0);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc_f16(128, 128, 1, 0, 0);
@@ -187,33 +188,42 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
     }
   } else {
-    // ---------------------------------------------------------------- softmax (warps 0..3)
-    const int row = warp * 32 + lane;        // query row inside the tile == TMEM lane
+    // ---------------------------------------------------------------- softmax (warps 0..7)
+    // Two threads per query row: warp w and warp w+4 share TMEM lane quarter w%4; the first takes key
+    // columns [0,64) of the tile, the second [64,128). They exchange only the row maximum (through
+    // shared memory, once per tile); each keeps its own partial row sum until the epilogue.
+    const int quarter = warp & 3, half = warp >> 2;
+    const int row = quarter * 32 + lane;     // query row inside the tile == TMEM lane
     const int qi = q0 + row;
-    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t col_base = half * 64;
     float m = FA_NEG, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
       const int kv0 = lo + j * FA_BN;
-      ok = mbar_wait(s_full, j & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_FULL);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+      // after a time-out the loop keeps running (so every warp still meets the named barrier below)
+      // but does no work; the waits return at once because the abort flag is set
+      if (ok) {
+        ok = mbar_wait(s_full, j & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_FULL);
+        ok = __all_sync(0xffffffffu, ok);
+      }
       tc_fence_after();
       const bool need_mask = (kv0 + FA_BN - 1 > q0) || (p.window > 0 && (q0 + FA_BM - 1 - kv0) >= p.window);
       // key columns this row may see inside the tile: [c_lo, c_hi]
-      int c_hi = qi - kv0;
-      int c_lo = (p.window > 0) ? (qi - p.window + 1 - kv0) : -1;
-      // pass 1: row maximum of the raw scores (the positive scale commutes with max)
-      float mx4[4] = {m, m, m, m};   // independent chains keep the max off the critical path
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      const int c_hi = qi - kv0;
+      const int c_lo = (p.window > 0) ? (qi - p.window + 1 - kv0) : -1;
+      // pass 1: maximum of the raw scores of this thread's 64 columns (the positive scale commutes with max)
+      float mx4[4] = {FA_NEG, FA_NEG, FA_NEG, FA_NEG};
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        if (!ok) break;
         uint32_t r[32];
-        tmem_ld_x32(tS + lane_addr + c * 32, r);
+        tmem_ld_x32(tS + lane_addr + col_base + c * 32, r);
         tmem_ld_wait();
         if (need_mask) {
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
-            const int col = c * 32 + e;
+            const int col = col_base + c * 32 + e;
             const float sv = (col <= c_hi && col >= c_lo) ? __uint_as_float(r[e]) : FA_NEG;
             mx4[e & 3] = fmaxf(mx4[e & 3], sv);
           }
@@ -222,24 +232,30 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           for (int e = 0; e < 32; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(r[e]));
         }
       }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      // exchange with the thread that owns the other half of the row (buffers alternate per tile)
+      float* xbuf = s_rowmax + (j & 1) * 256;
+      xbuf[half * 128 + row] = mx;
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      mx = fmaxf(fmaxf(mx, xbuf[(half ^ 1) * 128 + row]), m);
+      if (!ok) continue;
       const float alpha = fast_exp2((m - mx) * p.scale_log2);
       m = mx;
       const float neg_ms = -mx * p.scale_log2;
       // pass 2: probabilities p = 2^(s*c - m*c), packed to bf16
-      uint32_t pk[64];
+      uint32_t pk[32];
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t r[32];
-        tmem_ld_x32(tS + lane_addr + c * 32, r);
+        tmem_ld_x32(tS + lane_addr + col_base + c * 32, r);
         tmem_ld_wait();
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
           float p0 = fast_exp2(fmaf(__uint_as_float(r[e]), p.scale_log2, neg_ms));
           float p1 = fast_exp2(fmaf(__uint_as_float(r[e + 1]), p.scale_log2, neg_ms));
           if (need_mask) {
-            const int col = c * 32 + e;
+            const int col = col_base + c * 32 + e;
             p0 = (col <= c_hi && col >= c_lo) ? p0 : 0.f;
             p1 = (col + 1 <= c_hi && col + 1 >= c_lo) ? p1 : 0.f;
           }
@@ -252,22 +268,19 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (j > 0) {
         ok = mbar_wait(o_done, (j - 1) & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_EMPTY);
         ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
+        if (!ok) continue;
         tc_fence_after();
         if (__any_sync(0xffffffffu, alpha != 1.f)) {
+          // this thread rescales its half of the row's 64 output columns
+          uint32_t o[32];
+          tmem_ld_x32(tO + lane_addr + half * 32, o);
+          tmem_ld_wait();
 #pragma unroll
-          for (int c = 0; c < 2; ++c) {
-            uint32_t o[32];
-            tmem_ld_x32(tO + lane_addr + c * 32, o);
-            tmem_ld_wait();
-#pragma unroll
-            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
-            tmem_st_x32(tO + lane_addr + c * 32, o);
-          }
+          for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+          tmem_st_x32(tO + lane_addr + half * 32, o);
         }
       }
-      tmem_st_x32(tP + lane_addr, pk);
-      tmem_st_x32(tP + lane_addr + 32, pk + 32);
+      tmem_st_x32(tP + lane_addr + half * 32, pk);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(p_full);
@@ -277,6 +290,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       ok = mbar_wait(o_done, (n_kv - 1) & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_FULL);
       ok = __all_sync(0xffffffffu, ok);
     }
+    // total row sum = own partial + the partner's (both are relative to the same final maximum)
+    float* lbuf = s_rowmax + 512;
+    lbuf[half * 128 + row] = l;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    l += lbuf[(half ^ 1) * 128 + row];
     if (ok && n_kv > 0) {
       tc_fence_after();
       float lse = (m * p.scale_log2 + log2f(l)) * 0.6931471805599453f;  // natural log
@@ -287,14 +305,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         inv *= __expf(lse - tot);
         lse = tot;
       }
-      uint32_t o[64];
-      tmem_ld_x32(tO + lane_addr, o);
-      tmem_ld_x32(tO + lane_addr + 32, o + 32);
+      uint32_t o[32];
+      tmem_ld_x32(tO + lane_addr + half * 32, o);
       tmem_ld_wait();
       if (qi < q_hi) {
-        uint4* dst = reinterpret_cast<uint4*>(p.out + (static_cast<size_t>(qi) * p.Hq + h) * FA_D);
+        uint4* dst = reinterpret_cast<uint4*>(p.out + (static_cast<size_t>(qi) * p.Hq + h) * FA_D + half * 32);
 #pragma unroll
-        for (int v = 0; v < 8; ++v) {
+        for (int v = 0; v < 4; ++v) {
           uint4 w;
           w.x = pack_bf16(__uint_as_float(o[8 * v + 0]) * inv, __uint_as_float(o[8 * v + 1]) * inv);
           w.y = pack_bf16(__uint_as_float(o[8 * v + 2]) * inv, __uint_as_float(o[8 * v + 3]) * inv);
@@ -302,7 +319,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           w.w = pack_bf16(__uint_as_float(o[8 * v + 6]) * inv, __uint_as_float(o[8 * v + 7]) * inv);
           dst[v] = w;
         }
-        p.lse[static_cast<size_t>(h) * p.T + qi] = lse;
+        if (half == 0) p.lse[static_cast<size_t>(h) * p.T + qi] = lse;
       }
     }
   }
@@ -311,7 +328,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   __syncthreads();
   if (*abort_flag)
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 256);
   }

@@ -38,6 +38,10 @@ struct GemmParams {
   uint32_t idesc;
   int tiles_m, tiles_n;
   int* status;
+  // split-K (group_mode 0 only): the contraction is cut into `splits` ranges handled by different CTAs,
+  // each adding its partial product into the fp32 output with vector reductions (needs out_fp32 and
+  // C += semantics). Used by weight gradients, whose outputs have too few tiles to fill the GPU.
+  int splits;
   // grouped (mixture-of-experts) modes
   //   1: rows grouped by expert: row tile t reads group_tiles[t] = (m0, expert, valid); the expert picks
   //      a block of `group_b_rows` rows of B (K-major: output rows; MN-major: contraction rows)
@@ -93,6 +97,15 @@ __device__ __forceinline__ bool decode_tile(const GemmParams& p, int tile, int n
     t.c_off = static_cast<long long>(e) * p.c_group_stride;
     return t.nkb > 0;
   }
+  if (p.splits > 1) {
+    const int per = p.tiles_m * p.tiles_n;
+    const int sidx = tile / per;
+    tile = tile % per;
+    const int kb0 = static_cast<int>(static_cast<long long>(num_kb) * sidx / p.splits);
+    const int kb1 = static_cast<int>(static_cast<long long>(num_kb) * (sidx + 1) / p.splits);
+    t.k_begin = kb0 * GEMM_BK;
+    t.nkb = kb1 - kb0;
+  }
   const int tm = tile / p.tiles_n;
   t.n0 = (tile % p.tiles_n) * BN;
   if (p.group_mode == 1) {
@@ -126,7 +139,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_tiles = p.tiles_m * p.tiles_n * (p.group_mode == 2 ? p.num_groups : 1);
+  const int num_tiles = p.tiles_m * p.tiles_n * (p.group_mode == 2 ? p.num_groups : 1) * (p.splits > 1 ? p.splits : 1);
   const int num_kb = (p.K + GEMM_BK - 1) / GEMM_BK;
 
   if (threadIdx.x == 0) {
@@ -330,6 +343,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 v.z = __uint_as_float(r[4 * j + 2]) * p.alpha;
                 v.w = __uint_as_float(r[4 * j + 3]) * p.alpha;
                 float4* d4 = reinterpret_cast<float4*>(dst) + j;
+                if (p.splits > 1) {
+                  red_add_f32x4(dst + 4 * j, v.x, v.y, v.z, v.w);
+                  continue;
+                }
                 if (p.accumulate) {
                   const float4 o = *d4;
                   v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
@@ -341,6 +358,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               for (int j = 0; j < 32; ++j) {
                 if (col0 + j < p.N) {
                   float v = __uint_as_float(r[j]) * p.alpha;
+                  if (p.splits > 1) { atomicAdd(dst + j, v); continue; }
                   if (p.accumulate) v += dst[j];
                   dst[j] = v;
                 }
@@ -446,7 +464,7 @@ template <int BN, bool A_MN, bool B_MN, int EPI = EPI_STORE>
 static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb,
                        int ldc, int out_fp32, int accumulate, float alpha, int max_ctas,
                        cudaStream_t stream, int* status, const EpiArgs& ea = EpiArgs(),
-                       const GroupArgs& ga = GroupArgs(), int b_total_rows = 0) {
+                       const GroupArgs& ga = GroupArgs(), int b_total_rows = 0, int splits = 1) {
   using S = GemmSmem<BN>;
   CUtensorMap tmA, tmB;
   int rc;
@@ -478,6 +496,7 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
   p.tiles_m = ga.mode == 1 ? ga.row_tiles : (M + GEMM_BM - 1) / GEMM_BM;
   p.tiles_n = (N + BN - 1) / BN;
   p.status = status;
+  p.splits = (ga.mode == 0 && out_fp32 && accumulate) ? splits : 1;
   p.group_mode = ga.mode; p.group_tiles = ga.tiles; p.group_offsets = ga.offsets;
   p.group_b_rows = ga.b_rows; p.num_groups = ga.num_groups; p.c_group_stride = ga.c_stride;
   p.labels = ea.labels; p.partial = ea.partial; p.target_logit = ea.target_logit;
@@ -493,7 +512,7 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
     }
     attr_set = true;
   }
-  long grid_l = static_cast<long>(p.tiles_m) * p.tiles_n * (ga.mode == 2 ? ga.num_groups : 1);
+  long grid_l = static_cast<long>(p.tiles_m) * p.tiles_n * (ga.mode == 2 ? ga.num_groups : 1) * (p.splits > 1 ? p.splits : 1);
   int grid = grid_l > (1 << 30) ? (1 << 30) : static_cast<int>(grid_l);
   int cap = num_sms();
   if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;
@@ -529,11 +548,23 @@ KWU_API int kwu_gemm_bf16(const void* A, const void* B, void* C, int M, int N, i
   using namespace kwu;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const int BN = pick_bn(M, N, bn);
+  int BN = pick_bn(M, N, bn);
+  int splits = 1;
+  if (out_fp32 && accumulate && bn == 0 && K >= 2048) {
+    // weight-gradient shape: few output tiles, long contraction. Prefer the wide tile and cut K so
+    // that the work items fill the SMs.
+    const int sms = num_sms();
+    const long t256 = static_cast<long>((M + GEMM_BM - 1) / GEMM_BM) * ((N + 255) / 256);
+    if (t256 <= sms) {
+      BN = 256;
+      while (splits < 4 && t256 * (splits + 1) <= sms && K / (splits + 1) >= 1024) ++splits;
+    }
+  }
 #define KWU_GEMM_CASE(bnv, amn, bmn)                                                              \
   if (BN == bnv && a_mn == amn && b_mn == bmn)                                                    \
     return launch_gemm<bnv, amn != 0, bmn != 0>(A, B, C, M, N, K, lda, ldb, ldc, out_fp32,        \
-                                                accumulate, alpha, max_ctas, st, status);
+                                                accumulate, alpha, max_ctas, st, status, EpiArgs(), \
+                                                GroupArgs(), 0, splits);
   KWU_GEMM_CASE(128, 0, 0) KWU_GEMM_CASE(128, 0, 1) KWU_GEMM_CASE(128, 1, 0) KWU_GEMM_CASE(128, 1, 1)
   KWU_GEMM_CASE(256, 0, 0) KWU_GEMM_CASE(256, 0, 1) KWU_GEMM_CASE(256, 1, 0) KWU_GEMM_CASE(256, 1, 1)
 #undef KWU_GEMM_CASE

@@ -61,3 +61,16 @@ def test_linear_autograd_matches_torch():
     for got, want in ((y, yr), (x.grad, xr.grad), (w.grad, wr.grad)):
         err = (got.float() - want).abs().max().item()
         assert err <= 1e-2 * want.abs().max().item()
+
+
+def test_split_k_weight_gradient_accumulates_exactly_once():
+    """fp32 accumulate with a long contraction takes the split-K path (vector reductions into C)."""
+    from kohakuwullm_b200.ops import native
+    from kohakuwullm_b200.ops.gemm import matmul
+
+    a, b, ref = _operands(1280, 1280, 4096, True, True, seed=5)
+    out = torch.full((1280, 1280), 2.0, device="cuda", dtype=torch.float32)
+    matmul(a, b, a_mn=True, b_mn=True, out=out, accumulate=True)
+    torch.cuda.synchronize()
+    native.check_status()
+    torch.testing.assert_close(out, ref + 2.0, rtol=1e-4, atol=2e-3)
