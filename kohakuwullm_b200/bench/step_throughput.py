@@ -55,6 +55,8 @@ def main(argv=None):
     ap.add_argument("--schedule", default="1f1b")
     ap.add_argument("--no-mxfp8", action="store_true")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--expert-parallel", action="store_true", help="split MoE experts over the ranks (EP + DP)")
+    ap.add_argument("--grad-sync", default=None, choices=["nccl", "fused"])
     ap.add_argument("--set", action="append", default=[], help="config override KEY=VALUE (python literal)")
     args = ap.parse_args(argv)
 
@@ -104,7 +106,8 @@ def main(argv=None):
         with torch.device(dev):
             model = LMBackbone(cfg)
         engine = TrainEngine(model, lr=1e-4, param_dtype=torch.bfloat16,
-                             grad_sync="fused" if world > 1 else "nccl", cuda_graphs=not args.no_graphs)
+                             grad_sync=args.grad_sync or ("fused" if world > 1 else "nccl"),
+                             cuda_graphs=not args.no_graphs, expert_parallel=args.expert_parallel)
         packs = [p.to(dev) for p in make_packs(args.accum, args.micro_tokens, args.len_min, args.len_max,
                                                cfg.vocab_size, seed=17 + rank, log_uniform=args.log_uniform)]
         step = lambda: engine.step(packs)  # noqa: E731
@@ -119,7 +122,7 @@ def main(argv=None):
     native.check_status()
     if rank == 0:
         loss = out["loss"] if isinstance(out, dict) else out.loss
-        print(json.dumps({"preset": args.preset, "n_gpus": world, "mode": "pipeline" if args.pipeline and world > 1 else "dp",
+        print(json.dumps({"preset": args.preset, "n_gpus": world, "mode": "pipeline" if args.pipeline and world > 1 else ("ep+dp" if args.expert_parallel and world > 1 else "dp"),
                           "split": split, "tokens_per_step": tokens_per_step, "ms_per_step": ms / args.steps,
                           "tokens_per_s": tokens_per_step * args.steps / (ms / 1e3), "loss": float(loss),
                           "peak_mem_gib": torch.cuda.max_memory_allocated() / 2 ** 30}))

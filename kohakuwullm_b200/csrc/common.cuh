@@ -29,6 +29,7 @@ enum : int {
   KWU_ERR_TIMEOUT_FLAG = 5,    // a peer / test flag never arrived
   KWU_ERR_TIMEOUT_MISC = 6,
   KWU_ERR_BAD_ARG = 7,
+  KWU_ERR_EP_OVERFLOW = 8,     // an expert-parallel receive buffer was too small for the routed rows
 };
 
 // Wait limit in SM clock cycles (about 2 s at 2 GHz; tests shorten it). The clock is only read once

@@ -14,6 +14,8 @@ Expert evaluation (``MoEMLP``): tokens are counting-sorted by expert, each exper
 segment sum (no atomics). ``expert_path``:
   ``"grouped"``  native grouped tcgen05 GEMMs over the expert-sorted rows (GPU, bf16)
   ``"eager"``    per-expert loop in PyTorch (CPU, tests; the reference calls it ``dense_fallback``)
+After ``parallel.ep.shard_experts`` the layer holds only its rank's experts and tokens travel to the
+owning rank and back over peer memory (or, on CPU, through the collective-based oracle).
 """
 
 from __future__ import annotations
@@ -136,6 +138,8 @@ class MoEMLP(nn.Module):
         self.w_out = nn.Parameter(torch.empty(num_experts, dim, self.hidden))
         self.shared = GLUMLP(dim, hidden=self.hidden * num_shared) if num_shared > 0 else None
         self.expert_path = expert_path  # None: chosen from the input device at call time
+        # expert parallelism (kohakuwullm_b200.parallel.ep.shard_experts fills these in)
+        self.ep, self.ep_group, self.ep_world, self.ep_rank = None, None, 1, 0
 
     def active_parameters(self) -> int:
         per_expert = self.w_in[0].numel() + self.w_out[0].numel()
@@ -148,6 +152,16 @@ class MoEMLP(nn.Module):
         shape = x.shape
         flat = x.reshape(-1, shape[-1])
         idx, w, counts = self.router.route(flat)
+        if self.ep_world > 1:
+            from kohakuwullm_b200.parallel import ep as ep_ops
+
+            if self.ep is not None and moe_ops.native_supported(flat, self.w_in):
+                y = ep_ops.ep_routed_experts(self.ep, flat, idx, w, counts, self.w_in, self.w_out)
+            else:
+                y = ep_ops.reference_ep_forward(flat, idx, w, self.w_in, self.w_out, self.ep_group)
+            if self.shared is not None:
+                y = y + self.shared(flat)
+            return y.reshape(shape)
         path = self.expert_path or ("grouped" if moe_ops.native_supported(flat, self.w_in) else "eager")
         if path == "grouped":
             y = moe_ops.routed_experts(flat, idx, w, counts, self.w_in, self.w_out)

@@ -30,6 +30,7 @@ ERROR_NAMES = {
     5: "timeout waiting for a flag",
     6: "timeout (misc)",
     7: "bad argument",
+    8: "expert-parallel receive buffer overflow (raise the capacity factor)",
 }
 
 

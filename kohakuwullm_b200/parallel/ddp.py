@@ -28,7 +28,8 @@ class GradSync:
         """Sum every gradient buffer over the group (in place)."""
         if self.world <= 1:
             return
-        for buf in self.flat.grad_buffers():
+        for key in self.flat.replicated_keys():
+            buf = self.flat.groups[key].main_grad
             n = buf.numel()
             for s in range(0, n, self.bucket_elems):
                 dist.all_reduce(buf[s:min(n, s + self.bucket_elems)], group=self.group)

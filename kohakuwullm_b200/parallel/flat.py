@@ -1,7 +1,8 @@
 """Flat parameter / gradient storage.
 
 Every parameter of a model becomes a view into one contiguous buffer per dtype group
-(``"lp"``: 16-bit matrices, ``"fp32"``: everything kept in fp32), and gets a ``main_grad`` attribute:
+(``"lp"``: 16-bit matrices, ``"fp32"``: everything kept in fp32; parameters flagged ``ep_local`` go to
+``"lp_ep"`` / ``"fp32_ep"``, which data-parallel reductions skip), and gets a ``main_grad`` attribute:
 a view into an fp32 gradient buffer of the same layout. This is what makes the whole-model fused
 optimizer (one launch), the bucketed gradient collectives (contiguous ranges, no packing) and the
 GEMM-epilogue gradient accumulation possible. Tensors are padded to ``align`` elements so every
@@ -49,6 +50,8 @@ class FlatParameters:
                 continue
             seen.add(id(p))
             key = "fp32" if p.dtype == torch.float32 else "lp"
+            if getattr(p, "ep_local", False):
+                key += "_ep"  # expert-parallel shards: rank-local, never reduced over the data-parallel group
             g = self.groups.setdefault(key, FlatGroup(key, p.dtype))
             if p.dtype != g.dtype:
                 raise ValueError(f"mixed low-precision dtypes: {p.dtype} vs {g.dtype} ({name})")
@@ -97,3 +100,10 @@ class FlatParameters:
 
     def grad_buffers(self) -> list[torch.Tensor]:
         return [g.main_grad for g in self.groups.values()]
+
+    def replicated_keys(self) -> list[str]:
+        return [k for k in self.groups if not k.endswith("_ep")]
+
+    def local_keys(self) -> list[str]:
+        """Groups holding expert-parallel shards (different tensors on every rank)."""
+        return [k for k in self.groups if k.endswith("_ep")]

@@ -56,6 +56,7 @@ class FusedGradSync:
         self.norm = torch.zeros(1, dtype=torch.float32, device=dev)
         self.epoch = 0
         self.limit = wait_limit_cycles
+        self._sq_partial = None
 
     # plain collectives used around the fused step (token counts, logged scalars)
     def all_reduce_scalar(self, t: torch.Tensor) -> torch.Tensor:
@@ -71,9 +72,20 @@ class FusedGradSync:
         self.epoch += 1
         optimizer.step_count += 1
         lr = optimizer.param_groups[0]["lr"]
-        keys = list(self.flat.groups)
+        keys = self.flat.replicated_keys()
+        local_keys = self.flat.local_keys()
         status = native.ptr(native.status_word())
         stream = native.stream_ptr()
+        # expert-parallel shards are not reduced, but their squared norm belongs to the global norm: seed
+        # this rank's partial sum with it before the reduced shards are added
+        for j, key in enumerate(local_keys):
+            buf = self.flat.groups[key].main_grad
+            if self._sq_partial is None:
+                self._sq_partial = torch.empty(L.kwu_sumsq_blocks(), dtype=torch.float32, device=self.device)
+            rc = L.kwu_sumsq_flat(native.ptr(buf), c_ll(buf.numel()), native.ptr(self._sq_partial),
+                                  native.ptr(self._sumsq), c_int(int(j > 0)), stream)
+            native.check(rc, "sumsq_flat")
+        seeded = bool(local_keys)
         for i, key in enumerate(keys):
             g = self.flat.groups[key]
             lo, hi = optimizer._range(g)
@@ -81,7 +93,7 @@ class FusedGradSync:
             rc = L.kwu_ddp_reduce_shard(grad_tab, param_tab, self._flag_tab, self._slot_tab, c_int(self.rank),
                                         c_int(self.world), c_int(self.epoch), c_ll(lo), c_ll(hi - lo),
                                         native.ptr(self._partial), native.ptr(self._counter),
-                                        native.ptr(self._sumsq), c_int(int(i == 0)),
+                                        native.ptr(self._sumsq), c_int(int(i == 0 and not seeded)),
                                         c_int(int(i == len(keys) - 1)), c_int(int(i == 0)), c_ll(self.limit),
                                         stream, status)
             native.check(rc, "ddp_reduce_shard")
@@ -101,3 +113,9 @@ class FusedGradSync:
                 c_int(optimizer.step_count), native.ptr(self._counter), c_int(int(i == len(keys) - 1)), c_int(1),
                 c_ll(self.limit), stream, status)
             native.check(rc, "ddp_adamw_allgather")
+        if local_keys:
+            # same scale as inside the fused kernel: 1/tokens times the clipping coefficient
+            coef = inv_tokens.reshape(1).clone()
+            if max_grad_norm:
+                coef = coef * torch.clamp(max_grad_norm / (self.norm + 1e-6), max=1.0)
+            optimizer.step(grad_scale=coef, zero_grad=True, only=set(local_keys), advance=False)

@@ -113,7 +113,11 @@ class TrainEngine:
                  weight_decay: float = 0.1, max_grad_norm: float = 1.0,
                  param_dtype: torch.dtype | None = None, group=None, grad_sync: str = "nccl",
                  device: torch.device | str | None = None, lr_schedule=None,
-                 cuda_graphs: bool | None = None, graph_max_docs: int | None = None):
+                 cuda_graphs: bool | None = None, graph_max_docs: int | None = None,
+                 expert_parallel: bool | str = False, ep_capacity_factor: float = 2.0):
+        """``expert_parallel``: split every MoE layer's experts over the ranks of ``group`` (tokens travel
+        to the owning rank over peer memory); all other parameters stay data-parallel replicas.
+        ``"reference"`` keeps the sharding but moves tokens with plain collectives (test oracle)."""
         self.model = model
         if device is not None:
             model.to(device)
@@ -124,6 +128,13 @@ class TrainEngine:
         self.world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if self.world > 1 else 0
         self.fused_sync = grad_sync == "fused" and self.world > 1 and self.device.type == "cuda"
+        self.ep = None
+        if expert_parallel and self.world > 1:
+            from kohakuwullm_b200.parallel.ep import ExpertParallel, shard_experts
+
+            if self.device.type == "cuda" and native.available() and expert_parallel != "reference":
+                self.ep = ExpertParallel(group, capacity_factor=ep_capacity_factor)
+            shard_experts(model, self.ep, group if group is not None else dist.group.WORLD)
         if self.fused_sync:
             from kohakuwullm_b200.parallel.fused_ddp import FusedGradSync
             from kohakuwullm_b200.parallel.symm import SymmetricPool
@@ -187,21 +198,40 @@ class TrainEngine:
 
     # ------------------------------------------------------------------
     def _grad_norm_and_coef(self, inv_tokens: torch.Tensor) -> None:
-        bufs = self.flat.grad_buffers()
+        """Global gradient norm and the optimizer's gradient scale, on the device. Replicated buffers hold
+        the same reduced sums on every rank; expert-parallel buffers differ per rank, so their squared
+        norms are summed over the group first."""
+        local = [self.flat.groups[k].main_grad for k in self.flat.local_keys()]
+        shared = [self.flat.groups[k].main_grad for k in self.flat.replicated_keys()]
         if self.device.type == "cuda" and native.available():
             L = native.require()
             if self._partial is None:
                 self._partial = torch.empty(L.kwu_sumsq_blocks(), dtype=torch.float32, device=self.device)
-            for i, b in enumerate(bufs):
-                rc = L.kwu_sumsq_flat(native.ptr(b), ctypes.c_longlong(b.numel()), native.ptr(self._partial),
-                                      native.ptr(self._sumsq), ctypes.c_int(int(i > 0)), native.stream_ptr())
-                native.check(rc, "sumsq_flat")
+
+            def add(bufs, first):
+                for i, b in enumerate(bufs):
+                    rc = L.kwu_sumsq_flat(native.ptr(b), ctypes.c_longlong(b.numel()), native.ptr(self._partial),
+                                          native.ptr(self._sumsq), ctypes.c_int(int(not (first and i == 0))),
+                                          native.stream_ptr())
+                    native.check(rc, "sumsq_flat")
+
+            if local:
+                add(local, True)
+                if self.world > 1:
+                    dist.all_reduce(self._sumsq, group=self.group)
+            add(shared, not local)
             rc = L.kwu_clip_coef(native.ptr(self._sumsq), native.ptr(inv_tokens),
                                  ctypes.c_float(self.max_grad_norm or 0.0), native.ptr(self._coef),
                                  native.ptr(self._norm), native.stream_ptr())
             native.check(rc, "clip_coef")
         else:
-            sq = sum((b.double() ** 2).sum() for b in bufs).float()
+            sq = sum((b.double() ** 2).sum() for b in shared) if shared else torch.zeros((), dtype=torch.float64)
+            if local:
+                sq_local = sum((b.double() ** 2).sum() for b in local)
+                if self.world > 1:
+                    dist.all_reduce(sq_local, group=self.group)
+                sq = sq + sq_local
+            sq = sq.float()
             norm = sq.sqrt() * inv_tokens
             self._norm.copy_(norm.reshape(1))
             coef = inv_tokens.clone().reshape(1)

@@ -61,7 +61,7 @@ class FlatAdamW:
             self.state[key] = st
 
     def _range(self, g: FlatGroup) -> tuple[int, int]:
-        if self.shard is None:
+        if self.shard is None or g.key.endswith("_ep"):  # expert-parallel shards are already rank-local
             return 0, g.total
         rank, world = self.shard
         per = g.total // world
@@ -69,10 +69,16 @@ class FlatAdamW:
 
     # ------------------------------------------------------------------
     @torch.no_grad()
-    def step(self, grad_scale: torch.Tensor | None = None, zero_grad: bool = True) -> None:
-        self.step_count += 1
+    def step(self, grad_scale: torch.Tensor | None = None, zero_grad: bool = True, only=None,
+             advance: bool = True) -> None:
+        """``only``: restrict the update to these group keys; ``advance=False`` keeps the step counter
+        (used when another kernel already updated the remaining groups of the same step)."""
+        if advance:
+            self.step_count += 1
         lr = self.param_groups[0]["lr"]
         for key, g in self.flat.groups.items():
+            if only is not None and key not in only:
+                continue
             st = self.state[key]
             lo, hi = self._range(g)
             master = st.get("master")

@@ -1,0 +1,60 @@
+"""Expert parallelism on CPU (gloo, 2 ranks): the sharded model with the collective-based expert oracle
+takes the same optimizer step as the single-process model holding all experts."""
+
+import os
+import tempfile
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from kohakuwullm_b200.data.packing import collate_packed
+from kohakuwullm_b200.models import LMBackbone, get_preset
+from kohakuwullm_b200.parallel.ep import gather_expert_state
+from kohakuwullm_b200.training.engine import TrainEngine
+
+
+def _model(seed=0):
+    torch.manual_seed(seed)
+    cfg = get_preset("B200-smoke", vocab_size=300, dim=64, depth=2, heads=2, kv_heads=1, head_dim=32,
+                     mlp_hidden=128, moe_every=1, moe_first_dense=1, moe_num_experts=8, moe_top_k=2,
+                     moe_num_shared=1, moe_hidden=64)
+    return LMBackbone(cfg)
+
+
+def _docs(n=8, seed=5):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, 300, (int(torch.randint(5, 40, (1,), generator=g)),), generator=g) for _ in range(n)]
+
+
+def _worker(rank, world, port, path):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    eng = TrainEngine(_model(), lr=1e-2, max_grad_norm=1.0, expert_parallel=True)
+    moe = [m for m in eng.model.modules() if getattr(m, "ep_world", 1) > 1]
+    assert moe and moe[0].w_in.shape[0] == 4 and "fp32_ep" in eng.flat.groups
+    out = eng.step([collate_packed(_docs()[rank::world])])
+    state = gather_expert_state({k: v.detach().clone() for k, v in eng.model.state_dict().items()}, eng.model)
+    if rank == 0:
+        torch.save({"loss": float(out["loss"]), "norm": float(out["grad_norm"]), "state": state}, path)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_expert_parallel_step_matches_single_process():
+    from tests.helpers import free_port
+
+    with tempfile.TemporaryDirectory() as tmp:
+        path = os.path.join(tmp, "r0.pt")
+        mp.spawn(_worker, args=(2, free_port(), path), nprocs=2, join=True)
+        got = torch.load(path)
+    eng = TrainEngine(_model(), lr=1e-2, max_grad_norm=1.0)
+    out = eng.step([collate_packed(_docs())])
+    assert abs(got["loss"] - float(out["loss"])) < 1e-5
+    assert abs(got["norm"] - float(out["grad_norm"])) < 1e-4
+    ref = eng.model.state_dict()
+    for k, v in ref.items():
+        if v.is_floating_point():
+            torch.testing.assert_close(got["state"][k], v, rtol=0, atol=3e-4, msg=lambda m, k=k: f"{k}: {m}")

@@ -1,0 +1,118 @@
+"""Expert-parallel dispatch/combine over NVLink peer memory (csrc/moe_ep.cu) on 2 or more GPUs, against
+the collective-based oracle: one MoE layer forward + backward, and whole training steps through the
+engine (CUDA graphs on, both gradient-sync paths)."""
+
+import os
+import tempfile
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from tests.helpers import free_port
+
+
+def _init(rank, world, port):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+
+
+def _layer_worker(rank, world, port, out_dir):
+    _init(rank, world, port)
+    from kohakuwullm_b200.ops import native
+    from kohakuwullm_b200.parallel.ep import ExpertParallel, ep_routed_experts, reference_ep_forward
+
+    dev = torch.device("cuda", rank)
+    T, D, H, E, k = 1024, 256, 128, 16, 4
+    El = E // world
+    g = torch.Generator(device=dev).manual_seed(11 + rank)
+    x = (torch.randn(T, D, device=dev, generator=g) * 0.5).bfloat16()
+    logits = torch.randn(T, E, device=dev, generator=g)
+    if rank == 0:
+        logits[:, 3] += 1.5          # an unbalanced, but within-capacity, load
+    w, idx = torch.softmax(logits, -1).topk(k, dim=-1)
+    idx = idx.to(torch.int32)
+    counts = torch.bincount(idx.reshape(-1).long(), minlength=E).to(torch.int32)
+    gw = torch.Generator(device=dev).manual_seed(99)  # same full expert tensors on every rank, then sliced
+    w_in = (torch.randn(E, 2 * H, D, device=dev, generator=gw) * 0.05).bfloat16()[rank * El:(rank + 1) * El]
+    w_out = (torch.randn(E, D, H, device=dev, generator=gw) * 0.05).bfloat16()[rank * El:(rank + 1) * El]
+    dy = (torch.randn(T, D, device=dev, generator=g) * 0.1).bfloat16()
+
+    def run(fn):
+        xs = x.clone().requires_grad_()
+        ws = w.clone().requires_grad_()
+        wi = w_in.clone().requires_grad_()
+        wo = w_out.clone().requires_grad_()
+        y = fn(xs, ws, wi, wo)
+        y.backward(dy)
+        return [t.float() for t in (y.detach(), xs.grad, ws.grad, wi.grad, wo.grad)]
+
+    ep = ExpertParallel()
+    for _ in range(2):  # twice: the second pass reuses the workspace and the device-side epochs
+        got = run(lambda xs, ws, wi, wo: ep_routed_experts(ep, xs, idx, ws, counts, wi, wo))
+    ref = run(lambda xs, ws, wi, wo: reference_ep_forward(xs, idx, ws, wi, wo))
+    torch.cuda.synchronize()
+    native.check_status()
+    names = ("y", "dx", "dweight", "dw_in", "dw_out")
+    errs = {}
+    for n, a, b in zip(names, got, ref):
+        errs[n] = ((a - b).abs().max() / b.abs().max().clamp(min=1e-6)).item()
+    torch.save(errs, os.path.join(out_dir, f"layer_{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.multigpu
+@pytest.mark.timeout(600)
+def test_ep_layer_matches_collective_oracle():
+    world = 2 if torch.cuda.device_count() < 4 else 4
+    with tempfile.TemporaryDirectory() as tmp:
+        mp.spawn(_layer_worker, args=(world, free_port(), tmp), nprocs=world, join=True)
+        for r in range(world):
+            errs = torch.load(os.path.join(tmp, f"layer_{r}.pt"))
+            for name, e in errs.items():
+                assert e < 3e-2, f"rank {r} {name}: relative error {e}"
+
+
+def _engine_worker(rank, world, port, mode, out_dir):
+    _init(rank, world, port)
+    from kohakuwullm_b200.data.synthetic import make_packs
+    from kohakuwullm_b200.models import LMBackbone, get_preset
+    from kohakuwullm_b200.ops import native
+    from kohakuwullm_b200.training.engine import TrainEngine
+
+    torch.manual_seed(7)
+    cfg = get_preset("B200-moe-991M", depth=3, vocab_size=4096, mxfp8=False, moe_num_experts=16, moe_top_k=4)
+    with torch.device("cuda", rank):
+        model = LMBackbone(cfg)
+    ep_mode, sync = mode.split("+")
+    eng = TrainEngine(model, lr=1e-3, param_dtype=torch.bfloat16, grad_sync=sync,
+                      expert_parallel=True if ep_mode == "native" else "reference",
+                      cuda_graphs=(ep_mode == "native"))
+    packs = make_packs(2, 2048, 64, 512, cfg.vocab_size, seed=100 + rank)
+    outs = [eng.step(packs) for _ in range(3)]
+    torch.cuda.synchronize()
+    native.check_status()
+    torch.save({"loss": [float(o["loss"]) for o in outs], "norm": [float(o["grad_norm"]) for o in outs]},
+               os.path.join(out_dir, f"{mode}_{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.multigpu
+@pytest.mark.timeout(900)
+def test_ep_engine_steps_match_oracle():
+    world = 2 if torch.cuda.device_count() < 4 else 4
+    with tempfile.TemporaryDirectory() as tmp:
+        for mode in ("reference+nccl", "native+nccl", "native+fused"):
+            mp.spawn(_engine_worker, args=(world, free_port(), mode, tmp), nprocs=world, join=True)
+        ref = torch.load(os.path.join(tmp, "reference+nccl_0.pt"))
+        for mode in ("native+nccl", "native+fused"):
+            got = torch.load(os.path.join(tmp, f"{mode}_0.pt"))
+            for a, b in zip(got["loss"], ref["loss"]):
+                assert abs(a - b) < 5e-3, (mode, got["loss"], ref["loss"])
+            for a, b in zip(got["norm"], ref["norm"]):
+                assert abs(a - b) < 2e-2 * max(b, 1e-6), (mode, got["norm"], ref["norm"])
