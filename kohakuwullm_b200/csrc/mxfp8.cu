@@ -92,7 +92,12 @@ mxfp8_quantize_kernel(const __nv_bfloat16* __restrict__ x, int ldx, uint8_t* __r
 // A block handles a 32 (rows) x 64 (cols) input tile: thread t < 64 owns column c0 + t.
 __global__ void __launch_bounds__(64)
 mxfp8_quantize_t_kernel(const __nv_bfloat16* __restrict__ x, int ldx, uint8_t* __restrict__ qT, int ldq,
-                        uint8_t* __restrict__ sf, int R, int C, int C_pad) {
+                        uint8_t* __restrict__ sf, int R, int C, int C_pad, long long x_batch, long long q_batch,
+                        long long sf_batch) {
+  // blockIdx.z: independent matrices (the experts of a stacked weight) at fixed strides
+  x += static_cast<size_t>(blockIdx.z) * x_batch;
+  qT += static_cast<size_t>(blockIdx.z) * q_batch;
+  sf += static_cast<size_t>(blockIdx.z) * sf_batch;
   const int r0 = blockIdx.y * 32;
   const int c = blockIdx.x * 64 + threadIdx.x;
   if (c >= C_pad) return;
@@ -140,8 +145,28 @@ struct MxGemmParams {
   const uint8_t* sfa;  // scale chunks of A: [ceil(M/128)][K/128][512]
   const uint8_t* sfb;  // scale chunks of B: [ceil(N/128)][K/128][512]
   int tiles_m, tiles_n;
+  // grouped mode (rows of A grouped by expert): tile table entries (m0, expert, valid, 0); B holds the
+  // experts' matrices stacked along its rows, `group_n` rows each (a multiple of 128)
+  const int4* group_tiles;
+  int group_n;
   int* status;
 };
+
+// Tile -> (A row offset, B row offset, output column offset); false: nothing to do for this entry.
+__device__ __forceinline__ bool mx_decode_tile(const MxGemmParams& p, int tile, int BN, int& m0, int& n0, int& b_row0) {
+  const int tm = tile / p.tiles_n, tn = tile % p.tiles_n;
+  n0 = tn * BN;
+  if (p.group_tiles) {
+    const int4 t = p.group_tiles[tm];
+    if (!t.z) return false;
+    m0 = t.x;
+    b_row0 = t.y * p.group_n + n0;
+  } else {
+    m0 = tm * MX_BM;
+    b_row0 = n0;
+  }
+  return true;
+}
 
 template <int BN>
 struct MxSmem {
@@ -218,8 +243,9 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int tm = tile / p.tiles_n, tn = tile % p.tiles_n;
-        const int m0 = tm * MX_BM, n0 = tn * BN;
+        int m0, n0, b_row0;
+        if (!mx_decode_tile(p, tile, BN, m0, n0, b_row0)) continue;
+        const int tm = m0 / MX_BM;
         // scale chunks of this tile's rows: A rows [m0, m0+128) are row tile tm; B rows [n0, n0+BN)
         // start at 128-row tile n0/128 (BN is a multiple of 16, n0 may start mid-chunk only when
         // BN is not a multiple of 128: the chunk pair covering [n0, n0+BN) is loaded and the row
@@ -234,12 +260,12 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           uint8_t* ssf = sb + S::B_BYTES;
           mbar_expect_tx(&full_bar[stage], S::A_BYTES + S::B_BYTES + S::SF_BYTES);
           tma_load_2d(sa, &tmA, &full_bar[stage], kb * MX_BK, m0);
-          tma_load_2d(sb, &tmB, &full_bar[stage], kb * MX_BK, n0);
+          tma_load_2d(sb, &tmB, &full_bar[stage], kb * MX_BK, b_row0);
           bulk_load_1d(ssf, p.sfa + (static_cast<size_t>(tm) * num_kb + kb) * 512, 512, &full_bar[stage]);
 #pragma unroll
           for (int c = 0; c < S::SFB_CHUNKS; ++c)
             bulk_load_1d(ssf + 512 + c * 512,
-                         p.sfb + (static_cast<size_t>(n0 / 128 + c) * num_kb + kb) * 512, 512, &full_bar[stage]);
+                         p.sfb + (static_cast<size_t>(b_row0 / 128 + c) * num_kb + kb) * 512, 512, &full_bar[stage]);
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
@@ -253,9 +279,14 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        {
+          int m0, n0, b_row0;
+          if (!mx_decode_tile(p, tile, BN, m0, n0, b_row0)) continue;
+        }
         const int as = it & 1;
         const uint32_t aphase = (it >> 1) & 1;
+        ++it;
         if (!mbar_wait(&acc_empty[as], aphase ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_EMPTY)) {
           ok = false;
           break;
@@ -296,11 +327,12 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const int quarter = warp & 3;
     int it = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      int m0, n0, b_row0;
+      if (!mx_decode_tile(p, tile, BN, m0, n0, b_row0)) continue;
       const int as = it & 1;
       const uint32_t aphase = (it >> 1) & 1;
-      const int m0 = (tile / p.tiles_n) * MX_BM;
-      const int n0 = (tile % p.tiles_n) * BN;
+      ++it;
       ok = mbar_wait(&acc_full[as], aphase, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_FULL);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -373,17 +405,21 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 template <int BN>
 static int launch_mx(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
                      const uint8_t* sfa, const uint8_t* sfb, int out_fp32, int accumulate, float alpha,
-                     cudaStream_t stream, int* status) {
+                     cudaStream_t stream, int* status, const int4* group_tiles = nullptr, int n_group_tiles = 0,
+                     int n_groups = 1) {
   using S = MxSmem<BN>;
   CUtensorMap tmA, tmB;
   int rc;
   if ((rc = encode_tmap_2d(&tmA, A, ELEM_U8, M, K, lda, MX_BM, MX_BK, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
-  if ((rc = encode_tmap_2d(&tmB, B, ELEM_U8, N, K, ldb, BN, MX_BK, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  if ((rc = encode_tmap_2d(&tmB, B, ELEM_U8, static_cast<long long>(N) * n_groups, K, ldb, BN, MX_BK,
+                           CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   MxGemmParams p;
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.out_fp32 = out_fp32; p.accumulate = accumulate; p.alpha = alpha;
   p.sfa = sfa; p.sfb = sfb;
-  p.tiles_m = (M + MX_BM - 1) / MX_BM;
+  p.tiles_m = group_tiles ? n_group_tiles : (M + MX_BM - 1) / MX_BM;
   p.tiles_n = (N + BN - 1) / BN;
+  p.group_tiles = group_tiles;
+  p.group_n = N;
   p.status = status;
   auto kern = gemm_mxfp8_kernel<BN>;
   static bool attr_set = false;
@@ -441,10 +477,38 @@ KWU_API int kwu_mxfp8_quantize_t(const void* x, int ldx, void* qT, int ldq, void
   const int C_pad = (C + 127) / 128 * 128;
   dim3 grid((C_pad + 63) / 64, R / 32);
   mxfp8_quantize_t_kernel<<<grid, 64, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      (const __nv_bfloat16*)x, ldx, (uint8_t*)qT, ldq, (uint8_t*)sf, R, C, C_pad); kwu::count_launch();
+      (const __nv_bfloat16*)x, ldx, (uint8_t*)qT, ldq, (uint8_t*)sf, R, C, C_pad, 0, 0, 0); kwu::count_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { set_last_error("mxfp8_quantize_t launch: %s", cudaGetErrorString(e)); return 11; }
   return 0;
+}
+
+// `batch` matrices x[b] (R, C) at stride R*ldx -> qT[b] (C, R) at stride C*ldq, scale buffers at stride
+// kwu_mxfp8_sf_bytes(C, R). C must be a multiple of 128 so that the stacked outputs stay chunk-aligned.
+KWU_API int kwu_mxfp8_quantize_t_batched(const void* x, int ldx, void* qT, int ldq, void* sf, int R, int C, int batch,
+                                         void* stream) {
+  if (R % 128 || C % 128) { set_last_error("mxfp8_quantize_t_batched: R and C must be multiples of 128"); return 7; }
+  if (batch <= 0) return 0;
+  dim3 grid(C / 64, R / 32, batch);
+  mxfp8_quantize_t_kernel<<<grid, 64, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      (const __nv_bfloat16*)x, ldx, (uint8_t*)qT, ldq, (uint8_t*)sf, R, C, C, static_cast<long long>(R) * ldx,
+      static_cast<long long>(C) * ldq, kwu_mxfp8_sf_bytes(C, R)); kwu::count_launch();
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { set_last_error("mxfp8_quantize_t_batched launch: %s", cudaGetErrorString(e)); return 11; }
+  return 0;
+}
+
+// Grouped form: rows of A are grouped by expert in 128-row-aligned ranges described by `tiles`
+// ((m0, expert, valid, 0) per 128-row tile); B stacks the experts' (N, K) matrices along its rows.
+// out[rows of expert e] = A[rows] B[e]^T. N must be a multiple of 128.
+KWU_API int kwu_gemm_mxfp8_grouped(const void* A, const void* sfa, const void* B, const void* sfb, void* C,
+                                   int M, int N, int K, int lda, int ldb, int ldc, int n_experts,
+                                   const void* tiles, int n_tiles, void* stream, int* status) {
+  if (M <= 0 || N <= 0 || n_tiles <= 0) return 0;
+  if (K % 128 || N % 128) { set_last_error("gemm_mxfp8_grouped: K and N must be multiples of 128 (got %d, %d)", K, N); return 7; }
+  return launch_mx<128>(A, B, C, M, N, K, lda, ldb, ldc, (const uint8_t*)sfa, (const uint8_t*)sfb, 0, 0, 1.f,
+                        reinterpret_cast<cudaStream_t>(stream), status, reinterpret_cast<const int4*>(tiles),
+                        n_tiles, n_experts);
 }
 
 KWU_API int kwu_gemm_mxfp8(const void* A, const void* sfa, const void* B, const void* sfb, void* C, int M,

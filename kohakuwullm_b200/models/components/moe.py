@@ -140,6 +140,8 @@ class MoEMLP(nn.Module):
         self.expert_path = expert_path  # None: chosen from the input device at call time
         # expert parallelism (kohakuwullm_b200.parallel.ep.shard_experts fills these in)
         self.ep, self.ep_group, self.ep_world, self.ep_rank = None, None, 1, 0
+        self.mxfp8_experts = False
+        self._q_in = self._q_out = None
 
     def active_parameters(self) -> int:
         per_expert = self.w_in[0].numel() + self.w_out[0].numel()
@@ -147,6 +149,39 @@ class MoEMLP(nn.Module):
         if self.shared is not None:
             n += sum(p.numel() for p in self.shared.parameters())
         return n
+
+    # ------------------------------------------------------------------ MXFP8 protocol
+    def mxfp8_matmuls(self) -> list[str]:
+        """Bare-parameter products this module can run in MXFP8 (both expert GEMMs)."""
+        ok = self.dim % 128 == 0 and self.hidden % 128 == 0
+        return ["w_in", "w_out"] if ok else []
+
+    def enable_mxfp8(self) -> None:
+        if self.mxfp8_matmuls():
+            self.mxfp8_experts = True
+            self._q_in = self._q_out = None
+
+    @torch.no_grad()
+    def refresh_mxfp8(self) -> bool:
+        """Rebuild the cached fp8 copies of the expert weights (after every optimizer step)."""
+        if not self.mxfp8_experts or not moe_ops.native.available() or not self.w_in.is_cuda \
+                or self.w_in.dtype != torch.bfloat16:
+            return False
+        from kohakuwullm_b200.ops.mxfp8 import GroupedQuantizedWeight
+
+        if self._q_in is None or self._q_in.shape != tuple(self.w_in.shape):
+            self._q_in, self._q_out = GroupedQuantizedWeight(self.w_in), GroupedQuantizedWeight(self.w_out)
+        else:
+            self._q_in.refresh(self.w_in)
+            self._q_out.refresh(self.w_out)
+        return True
+
+    def _quantized(self, flat):
+        if not self.mxfp8_experts or not moe_ops.native_supported(flat, self.w_in):
+            return None, None
+        if self._q_in is None or self._q_in.shape != tuple(self.w_in.shape):
+            self.refresh_mxfp8()
+        return self._q_in, self._q_out
 
     def forward(self, x):
         shape = x.shape
@@ -156,7 +191,8 @@ class MoEMLP(nn.Module):
             from kohakuwullm_b200.parallel import ep as ep_ops
 
             if self.ep is not None and moe_ops.native_supported(flat, self.w_in):
-                y = ep_ops.ep_routed_experts(self.ep, flat, idx, w, counts, self.w_in, self.w_out)
+                q_in, q_out = self._quantized(flat)
+                y = ep_ops.ep_routed_experts(self.ep, flat, idx, w, counts, self.w_in, self.w_out, q_in, q_out)
             else:
                 y = ep_ops.reference_ep_forward(flat, idx, w, self.w_in, self.w_out, self.ep_group)
             if self.shared is not None:
@@ -164,7 +200,8 @@ class MoEMLP(nn.Module):
             return y.reshape(shape)
         path = self.expert_path or ("grouped" if moe_ops.native_supported(flat, self.w_in) else "eager")
         if path == "grouped":
-            y = moe_ops.routed_experts(flat, idx, w, counts, self.w_in, self.w_out)
+            q_in, q_out = self._quantized(flat)
+            y = moe_ops.routed_experts(flat, idx, w, counts, self.w_in, self.w_out, q_in, q_out)
         else:
             y = moe_ops.routed_experts_reference(flat, idx, w, self.w_in, self.w_out)
         if self.shared is not None:

@@ -252,12 +252,23 @@ class _Combine(torch.autograd.Function):
         return drows, dw.view(ctx.wshape).to(ctx.wdtype), None, None
 
 
-def routed_experts(x, idx, weight, counts, w_in, w_out):
-    """Native routed-expert MLP. ``idx`` (T,k) int32, ``weight`` (T,k), ``counts`` (E,) int32 from the router."""
+def grouped_linear(rows, W, plan, qweight=None):
+    """Expert-grouped linear: bf16 tcgen05 GEMM, or the MXFP8 recipe when ``qweight`` (a
+    ``GroupedQuantizedWeight`` of ``W``) is given."""
+    if qweight is not None:
+        from kohakuwullm_b200.ops.mxfp8 import _MXFP8GroupedLinear
+
+        return _MXFP8GroupedLinear.apply(rows, W, qweight, plan)
+    return _GroupedLinear.apply(rows, W, plan)
+
+
+def routed_experts(x, idx, weight, counts, w_in, w_out, q_in=None, q_out=None):
+    """Native routed-expert MLP. ``idx`` (T,k) int32, ``weight`` (T,k), ``counts`` (E,) int32 from the router.
+    ``q_in`` / ``q_out``: MXFP8 copies of the expert weights (both GEMMs then run block-scaled fp8)."""
     T = x.shape[0]
     plan = make_plan(idx.to(torch.int32).contiguous(), counts.to(torch.int32), w_in.shape[0])
     rows = _Gather.apply(x.contiguous(), plan)
-    h = _GroupedLinear.apply(rows, w_in, plan)
+    h = grouped_linear(rows, w_in, plan, q_in)
     a = swiglu(h)
-    y_rows = _GroupedLinear.apply(a, w_out, plan)
+    y_rows = grouped_linear(a, w_out, plan, q_out)
     return _Combine.apply(y_rows, weight, plan, T)

@@ -176,3 +176,85 @@ def mxfp8_linear_reference(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     wq, we = quantize_reference(w)
     y = dequantize(xq, xe) @ dequantize(wq, we).t()
     return y.to(x.dtype).reshape(*x.shape[:-1], w.shape[0])
+
+
+# ------------------------------------------------------------------------------------ grouped (experts)
+class GroupedQuantizedWeight:
+    """MXFP8 copies of a stacked expert weight (E, N, K): ``W[e]`` along K, stacked as (E*N, K), and
+    ``W[e]^T`` along N, stacked as (E*K, N). N and K are multiples of 128, so every expert's block of
+    rows starts on a scale-chunk boundary."""
+
+    def __init__(self, weight: torch.Tensor):
+        E, N, K = weight.shape
+        dev = weight.device
+        self.shape = (E, N, K)
+        self.q = torch.empty(E * N, K, dtype=torch.uint8, device=dev)
+        self.sf = torch.empty(sf_bytes(E * N, K), dtype=torch.uint8, device=dev)
+        self.qt = torch.empty(E * K, N, dtype=torch.uint8, device=dev)
+        self.sft = torch.empty(E * sf_bytes(K, N), dtype=torch.uint8, device=dev)
+        self.refresh(weight)
+
+    @torch.no_grad()
+    def refresh(self, weight: torch.Tensor) -> None:
+        L = native.require()
+        E, N, K = self.shape
+        w2 = weight.detach().reshape(E * N, K)
+        quantize(w2, self.q, self.sf)
+        rc = L.kwu_mxfp8_quantize_t_batched(native.ptr(w2), c_int(K), native.ptr(self.qt), c_int(N),
+                                            native.ptr(self.sft), c_int(N), c_int(K), c_int(E), native.stream_ptr())
+        native.check(rc, "mxfp8_quantize_t_batched")
+
+
+def grouped_gemm(a_q, a_sf, b_q, b_sf, n_per_expert: int, n_experts: int, tiles: torch.Tensor, out_dtype=torch.bfloat16):
+    """``out[rows of expert e] = A[rows] B[e]^T`` over expert-sorted, 128-row-aligned A rows."""
+    L = native.require()
+    M, K = a_q.shape
+    out = torch.empty(M, n_per_expert, dtype=out_dtype, device=a_q.device)
+    rc = L.kwu_gemm_mxfp8_grouped(native.ptr(a_q), native.ptr(a_sf), native.ptr(b_q), native.ptr(b_sf), native.ptr(out),
+                                  c_int(M), c_int(n_per_expert), c_int(K), c_int(a_q.stride(0)), c_int(b_q.stride(0)),
+                                  c_int(out.stride(0)), c_int(n_experts), native.ptr(tiles), c_int(tiles.shape[0]),
+                                  native.stream_ptr(), native.ptr(native.status_word()))
+    native.check(rc, "gemm_mxfp8_grouped")
+    return out
+
+
+class _MXFP8GroupedLinear(torch.autograd.Function):
+    """Grouped expert linear in the MXFP8 recipe: FPROP and DGRAD block-scaled fp8, WGRAD bf16 into fp32
+    (``main_grad`` when the trainer provides it). ``plan`` carries the tile table and expert offsets."""
+
+    @staticmethod
+    def forward(ctx, rows, W, qw: GroupedQuantizedWeight, plan):
+        E, N, K = W.shape
+        xq, xsf = quantize(rows)
+        out = grouped_gemm(xq, xsf, qw.q, qw.sf, N, E, plan.tiles, out_dtype=rows.dtype)
+        ctx.save_for_backward(rows, W)
+        ctx.qw, ctx.plan = qw, plan
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        L = native.require()
+        rows, W = ctx.saved_tensors
+        qw, plan = ctx.qw, ctx.plan
+        E, N, K = W.shape
+        dout = dout.contiguous()
+        drows = dW = None
+        if ctx.needs_input_grad[0]:
+            dq, dsf = quantize(dout)
+            drows = grouped_gemm(dq, dsf, qw.qt, qw.sft, K, E, plan.tiles, out_dtype=rows.dtype)
+        if ctx.needs_input_grad[1]:
+            main_grad = getattr(W, "main_grad", None)
+            target = main_grad if main_grad is not None else torch.zeros(E, N, K, dtype=torch.float32, device=W.device)
+            rc = L.kwu_gemm_bf16_grouped_wgrad(native.ptr(dout), native.ptr(rows), native.ptr(target),
+                                               c_int(plan.max_rows), c_int(N), c_int(K), c_int(dout.stride(0)),
+                                               c_int(rows.stride(0)), c_int(E), native.ptr(plan.offsets), c_int(1),
+                                               c_int(1), native.stream_ptr(), native.ptr(native.status_word()))
+            native.check(rc, "grouped_gemm_wgrad")
+            if main_grad is None:
+                dW = target.to(W.dtype)
+        return drows, dW, None, None
+
+
+def grouped_supported(W: torch.Tensor) -> bool:
+    return (native.available() and W.is_cuda and W.dtype == torch.bfloat16 and W.dim() == 3
+            and W.shape[1] % 128 == 0 and W.shape[2] % 128 == 0)

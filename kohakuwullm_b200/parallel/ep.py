@@ -225,17 +225,18 @@ class _EPCombine(torch.autograd.Function):
         return d_rows, dw.view(ctx.wshape).to(ctx.wdtype), None, None, None
 
 
-def ep_routed_experts(ep: ExpertParallel, x, idx, weight, counts, w_in_local, w_out_local):
-    """Expert-parallel routed MLP on the native path. ``w_in_local`` (El, 2H, dim), ``w_out_local`` (El, dim, H)."""
+def ep_routed_experts(ep: ExpertParallel, x, idx, weight, counts, w_in_local, w_out_local, q_in=None, q_out=None):
+    """Expert-parallel routed MLP on the native path. ``w_in_local`` (El, 2H, dim), ``w_out_local`` (El, dim, H);
+    ``q_in`` / ``q_out``: their MXFP8 copies (block-scaled fp8 expert GEMMs)."""
     from kohakuwullm_b200.ops.elementwise import swiglu
-    from kohakuwullm_b200.ops.moe import _GroupedLinear
+    from kohakuwullm_b200.ops.moe import grouped_linear
 
     T, D = x.shape
     plan = ep.plan(idx, counts, D)
     rows = ep.dispatch(x, plan)
-    h = _GroupedLinear.apply(rows, w_in_local, plan)
+    h = grouped_linear(rows, w_in_local, plan, q_in)
     a = swiglu(h)
-    y_rows = _GroupedLinear.apply(a, w_out_local, plan)
+    y_rows = grouped_linear(a, w_out_local, plan, q_out)
     return ep.combine(y_rows, weight, plan, T)
 
 

@@ -88,3 +88,61 @@ def test_moe_layer_end_to_end():
     y_eager = m(x)
     err = (y_native.float() - y_eager.float()).abs().max().item()
     assert err <= 3e-2 * y_eager.float().abs().max().item()
+
+
+def test_grouped_mxfp8_gemm_matches_dequantised_product():
+    """Block-scaled grouped GEMM against fp32 products of the dequantised operands, expert by expert."""
+    from kohakuwullm_b200.ops import moe as moe_ops
+    from kohakuwullm_b200.ops import mxfp8
+
+    torch.manual_seed(3)
+    T, K, N, E, k = 2048, 512, 384, 8, 2
+    x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
+    W = (torch.randn(E, N, K, device="cuda") * 0.1).bfloat16()
+    idx = torch.stack([torch.randperm(E, device="cuda")[:k] for _ in range(T)]).to(torch.int32)
+    counts = torch.bincount(idx.reshape(-1).long(), minlength=E).to(torch.int32)
+    plan = moe_ops.make_plan(idx, counts, E)
+    rows = moe_ops._Gather.apply(x, plan)
+    qw = mxfp8.GroupedQuantizedWeight(W)
+    xq, xsf = mxfp8.quantize(rows)
+    out = mxfp8.grouped_gemm(xq, xsf, qw.q, qw.sf, N, E, plan.tiles)
+    torch.cuda.synchronize()
+    off = plan.offsets.tolist()
+    x_deq = mxfp8.dequantize(xq.view(torch.float8_e4m3fn)[: off[E]], mxfp8.sf_to_natural(xsf, plan.max_rows, K)[: off[E]])
+    w_deq = mxfp8.dequantize(qw.q.view(torch.float8_e4m3fn), mxfp8.sf_to_natural(qw.sf, E * N, K)).view(E, N, K)
+    for e in range(E):
+        s, t = off[e], off[e] + int(counts[e])
+        ref = x_deq[s:t] @ w_deq[e].t()
+        torch.testing.assert_close(out[s:t].float(), ref, rtol=2e-2, atol=2e-2)
+    # transposed copies: W[e]^T quantised along N, expert by expert
+    wt_deq = mxfp8.dequantize(qw.qt.view(torch.float8_e4m3fn), torch.cat(
+        [mxfp8.sf_to_natural(c, K, N) for c in qw.sft.view(E, -1)])).view(E, K, N)
+    torch.testing.assert_close(wt_deq, W.float().transpose(1, 2), rtol=0.07, atol=1e-3)
+
+
+def test_routed_experts_mxfp8_close_to_bf16():
+    from kohakuwullm_b200.ops import moe as moe_ops
+    from kohakuwullm_b200.ops import mxfp8
+
+    torch.manual_seed(4)
+    T, dim, E, k, H = 4096, 1024, 16, 4, 384
+    x = torch.randn(T, dim, device="cuda", dtype=torch.bfloat16)
+    w_in = (torch.randn(E, 2 * H, dim, device="cuda") * 0.03).bfloat16()
+    w_out = (torch.randn(E, dim, H, device="cuda") * 0.03).bfloat16()
+    logits = torch.randn(T, E, device="cuda")
+    gate, idx = torch.softmax(logits, -1).topk(k, -1)
+    idx = idx.to(torch.int32)
+    counts = torch.bincount(idx.reshape(-1).long(), minlength=E).to(torch.int32)
+    dy = torch.randn(T, dim, device="cuda", dtype=torch.bfloat16) * 0.1
+
+    def run(q_in, q_out):
+        xs, wi, wo, g = (t.clone().requires_grad_() for t in (x, w_in, w_out, gate))
+        y = moe_ops.routed_experts(xs, idx, g, counts, wi, wo, q_in, q_out)
+        y.backward(dy)
+        return [t.float() for t in (y.detach(), xs.grad, g.grad, wi.grad, wo.grad)]
+
+    ref = run(None, None)
+    got = run(mxfp8.GroupedQuantizedWeight(w_in), mxfp8.GroupedQuantizedWeight(w_out))
+    for name, a, b in zip(("y", "dx", "dgate", "dw_in", "dw_out"), got, ref):
+        rel = ((a - b).norm() / b.norm().clamp(min=1e-9)).item()
+        assert rel < 0.08, f"{name}: relative error {rel}"
