@@ -3,7 +3,8 @@
 ``python -m kohakuwullm_b200.build`` compiles every ``csrc/*.cu`` with nvcc for
 ``compute_100a/sm_100a`` and links ``kohakuwullm_b200/_kwu_native.so``. nvcc cross-compiles,
 so this runs on a machine without a GPU. Objects are rebuilt only when their source (or a
-header) is newer.
+header) is newer. The C++ CPU oracles under ``csrc/cpu`` are built with the host compiler into
+``kohakuwullm_b200/_kwu_cpu.so``.
 """
 
 from __future__ import annotations
@@ -19,6 +20,8 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 OBJ = PKG / "csrc" / "build"
 LIB = PKG / "_kwu_native.so"
+CPU_SRC = CSRC / "cpu"
+CPU_LIB = PKG / "_kwu_cpu.so"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -78,6 +81,20 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIB
 
 
+def build_cpu(force: bool = False) -> Path:
+    """C++ CPU oracles (``csrc/cpu/*.cpp``) -> ``_kwu_cpu.so`` with the host compiler."""
+    sources = sorted(CPU_SRC.glob("*.cpp"))
+    if force or _stale(CPU_LIB, sources):
+        cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
+        cmd = [cxx, "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-o", str(CPU_LIB),
+               *map(str, sources)]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"host compile failed:\n{r.stdout}\n{r.stderr}")
+    return CPU_LIB
+
+
 if __name__ == "__main__":
     path = build(force="--force" in sys.argv, verbose="-v" in sys.argv)
     print(path)
+    print(build_cpu(force="--force" in sys.argv))

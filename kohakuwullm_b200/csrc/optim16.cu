@@ -8,7 +8,7 @@
 //   sr_grouped     the same for a whole model in ONE launch: a table of (param ptr, update ptr, numel,
 //                  running element offset) chunks; element i of tensor t draws random number
 //                  offset[t] + i, so the result is bit-identical to the per-tensor loop.
-// Randomness is Philox4x32-10 keyed by (seed, counter = element index / 4); `draws` (optional) injects the
+// Randomness is Philox4x32-10 keyed by (seed, counter = element index / 8: eight 16-bit draws per block); `draws` (optional) injects the
 // 16-bit draws directly, which is how the PyTorch reference checks the kernels bit for bit.
 // Reference: src/kohakuwullm/kernels/optim/adamw16.py:16-168, stochastic_round.py:44-270,
 // stochastic_round_grouped.py:22-176.

@@ -104,6 +104,11 @@ class Attention(nn.Module):
         q_pos = seq_info.position_ids  # (B, S) absolute positions of the queries
         if cache is not None:
             k, v, k_pos, k_valid = cache.append(layer, k, v, q_pos)
+            if S == 1 and not torch.is_grad_enabled() and attn_ops.decode_supported(q[:, 0], k) \
+                    and q.is_contiguous():
+                # one new token per row: split-KV decode kernel straight over the cache buffers
+                out = attn_ops.decode_attention(q[:, 0], k, v, cache.length + 1, self.window, self.scale, self.sink)
+                return self.o_proj(out.reshape(B, 1, self.q_dim))
         else:
             k_pos = q_pos
             k_valid = torch.ones(B, S, dtype=torch.bool, device=x.device)

@@ -255,3 +255,43 @@ def attention_core(qkv, q_norm, k_norm, cos, sin, cu_seqlens, plan, sink_lse, Hq
         sink_lse = sink_lse.float()
     return _AttentionCore.apply(qkv, q_norm, k_norm, cos, sin, cu_seqlens, plan, sink_lse, Hq, Hkv, window,
                                 float(scale), float(eps), bool(do_norm))
+
+
+# ------------------------------------------------------------------------------------ decode
+def decode_supported(q, k_cache) -> bool:
+    return (native.available() and q.is_cuda and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
+            and q.shape[-1] == 64 and q.shape[-2] % k_cache.shape[-2] == 0 and q.shape[-2] // k_cache.shape[-2] <= 8)
+
+
+_decode_scratch: dict = {}
+
+
+@torch.no_grad()
+def decode_attention(q, k_cache, v_cache, kv_len: int, window: int | None = None, scale: float | None = None,
+                     sink: torch.Tensor | None = None, return_lse: bool = False):
+    """One new token per row against a KV cache: q (B,H,64); caches (B,L_max,Hkv,64); the query sits at
+    position ``kv_len - 1`` and attends keys ``[max(0, kv_len - window), kv_len)``. ``sink`` (H,S) fp32 learned
+    sink logits join the softmax denominator. Split-KV kernel in ``csrc/decode_attn.cu``."""
+    L = native.require()
+    B, H, D = q.shape
+    Hkv = k_cache.shape[2]
+    scale = scale if scale is not None else D ** -0.5
+    out = torch.empty(B, H, D, dtype=q.dtype, device=q.device)
+    lse = torch.empty(B, H, dtype=torch.float32, device=q.device)
+    need = int(L.kwu_decode_scratch_floats(ctypes.c_int(B), ctypes.c_int(H), ctypes.c_int(k_cache.shape[1])))
+    key = (q.device, need)
+    scratch = _decode_scratch.get(key)
+    if scratch is None:
+        scratch = _decode_scratch[key] = torch.empty(need, dtype=torch.float32, device=q.device)
+    sink_f = sink.detach().float().contiguous() if sink is not None else None
+    ll = ctypes.c_longlong
+    rc = L.kwu_decode_attention(
+        native.ptr(q), ll(q.stride(0)), ll(q.stride(1)),
+        native.ptr(k_cache), ll(k_cache.stride(0)), ll(k_cache.stride(1)), ll(k_cache.stride(2)),
+        native.ptr(v_cache), ll(v_cache.stride(0)), ll(v_cache.stride(1)), ll(v_cache.stride(2)),
+        native.ptr(out), ll(out.stride(0)), ll(out.stride(1)), native.ptr(lse), native.ptr(scratch),
+        ctypes.c_int(B), ctypes.c_int(H), ctypes.c_int(Hkv), ctypes.c_int(int(kv_len)), ctypes.c_int(int(window or 0)),
+        ctypes.c_float(scale), native.ptr(sink_f), ctypes.c_int(0 if sink_f is None else sink_f.shape[1]),
+        native.stream_ptr())
+    native.check(rc, "decode_attention")
+    return (out, lse) if return_lse else out

@@ -119,3 +119,59 @@ def test_attention_layer_fused_core_matches_unfused():
         err = (got.float() - want.float()).abs().max().item()
         scale = max(want.float().abs().max().item(), 1e-6)
         assert err <= 4e-2 * scale, f"err {err} scale {scale}"
+
+
+@pytest.mark.parametrize("B,H,Hkv,L,kv_len,window,n_sinks", [
+    (2, 8, 2, 512, 300, None, 0),
+    (3, 20, 4, 2048, 2048, 1024, 4),
+    (1, 16, 16, 1024, 1, None, 1),
+    (4, 24, 8, 4096, 3333, 1024, 0),
+])
+def test_decode_attention_matches_reference(B, H, Hkv, L, kv_len, window, n_sinks):
+    from kohakuwullm_b200.ops.attention import decode_attention
+
+    torch.manual_seed(kv_len)
+    D = 64
+    q = torch.randn(B, H, D, device="cuda", dtype=torch.bfloat16)
+    kc = torch.randn(B, L, Hkv, D, device="cuda", dtype=torch.bfloat16)
+    vc = torch.randn(B, L, Hkv, D, device="cuda", dtype=torch.bfloat16)
+    sink = torch.randn(H, n_sinks, device="cuda") if n_sinks else None
+    out, lse = decode_attention(q, kc, vc, kv_len, window, None, sink, return_lse=True)
+    lo = max(0, kv_len - window) if window else 0
+    g = H // Hkv
+    kf = kc[:, lo:kv_len].float().repeat_interleave(g, 2)            # (B, n, H, D)
+    vf = vc[:, lo:kv_len].float().repeat_interleave(g, 2)
+    s = torch.einsum("bhd,bnhd->bhn", q.float(), kf) * D ** -0.5
+    ref_lse = torch.logsumexp(s, -1)
+    if sink is not None:
+        ref_lse = torch.logaddexp(ref_lse, torch.logsumexp(sink, -1)[None])
+    p = torch.exp(s - ref_lse[..., None])
+    ref = torch.einsum("bhn,bnhd->bhd", p, vf)
+    torch.testing.assert_close(lse, ref_lse, rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=2e-2)
+
+
+def test_cached_decode_step_matches_uncached_forward():
+    """Prefill + one cached decode step (split-KV kernel, window and sinks on) against the full forward."""
+    from kohakuwullm_b200.models import LMBackbone, get_preset
+    from kohakuwullm_b200.models.cache import KVCache
+    from kohakuwullm_b200.models.seqinfo import SeqInfo
+    from kohakuwullm_b200.ops import native
+
+    torch.manual_seed(0)
+    cfg = get_preset("B200-smoke", vocab_size=512, sliding_window=16, global_layer_every=2, attn_sink=True,
+                     attn_num_sinks=2)
+    with torch.device("cuda"):
+        model = LMBackbone(cfg).to(torch.bfloat16).eval()
+    for blk in model.blocks:
+        torch.nn.init.normal_(blk.attn.sink, std=1.0)
+    tokens = torch.randint(0, 512, (3, 41), device="cuda")
+    with torch.no_grad():
+        full = model(tokens, SeqInfo.padded(3, 41, device="cuda"))
+        cache = KVCache.from_config(cfg, 64, static=True)
+        model(tokens[:, :40], cache.seq_info(tokens[:, :40]), cache=cache)
+        before = native.lib().kwu_launch_count()
+        last = model(tokens[:, 40:], cache.seq_info(tokens[:, 40:]), cache=cache)
+        launched = native.lib().kwu_launch_count() - before
+    assert launched >= 2 * cfg.depth, "the decode step did not go through the native decode kernels"
+    torch.testing.assert_close(last[:, 0].float(), full[:, 40].float(), rtol=5e-2, atol=5e-2)

@@ -1,0 +1,89 @@
+"""Optimizer-side kernels on the GPU: stochastic rounding (bit-exact against the reference given the same
+draws; Philox draws equal to the C++ oracle's), fused write-back, grouped write-back, 16-bit AdamW, flat
+AdamW against the C++ oracle."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_sr_cast_bit_exact_with_given_draws_and_with_oracle_philox():
+    from kohakuwullm_b200.ops import cpu_oracle as co
+    from kohakuwullm_b200.ops.optim import sr_cast, stochastic_round_reference
+
+    torch.manual_seed(0)
+    x = torch.randn(5000, device="cuda") * 3
+    draws64 = torch.randint(0, 1 << 16, (5000,))
+    got = sr_cast(x, draws=draws64.to(torch.uint16).cuda())
+    want = stochastic_round_reference(x.cpu(), draws64)
+    assert torch.equal(got.cpu().view(torch.int16), want.view(torch.int16))
+    # device Philox stream == C++ oracle stream
+    seed, offset, n = 20090220, 12345, 257
+    got = sr_cast(x[:n].contiguous(), seed=seed, offset=offset).cpu()
+    bits = torch.tensor([co.draw16(seed, offset + i) for i in range(n)])
+    want = co.sr_round(x[:n].cpu(), bits).to(torch.bfloat16)
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+
+
+def test_sr_update_and_grouped_writeback_agree():
+    from kohakuwullm_b200.ops.optim import GroupedWriteback, sr_update_
+
+    torch.manual_seed(1)
+    shapes = [(300,), (17, 33), (1024,), (5, 7, 11)]
+    ps = [torch.randn(s, device="cuda").bfloat16() for s in shapes]
+    us = [torch.randn(s, device="cuda") for s in shapes]
+    loop = [p.clone() for p in ps]
+    offset = 0
+    for p, u in zip(loop, us):
+        sr_update_(p, u, 0.01, -0.5, seed=99, offset=offset)
+        offset += p.numel()
+    grouped = [p.clone() for p in ps]
+    GroupedWriteback(grouped, us).step([0.01] * 4, [-0.5] * 4, seed=99)
+    torch.cuda.synchronize()
+    for a, b in zip(loop, grouped):
+        assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+    # stochastic rounding is unbiased: the mean of many roundings approaches the fp32 value
+    p = torch.full((1 << 20,), 1.0, device="cuda").bfloat16()
+    u = torch.full((1 << 20,), 0.00123, device="cuda")
+    sr_update_(p, u, 0.0, 1.0, seed=5)
+    assert abs(p.float().mean().item() - 1.00123) < 2e-5
+
+
+def test_adamw16_matches_eager_twin():
+    from kohakuwullm_b200.ops.optim import adamw16_step_
+
+    torch.manual_seed(2)
+    n = 10000
+    p = torch.randn(n, device="cuda").bfloat16()
+    m = torch.zeros(n, device="cuda").bfloat16()
+    sv = torch.zeros(n, device="cuda").bfloat16()
+    pc, mc, svc = p.cpu().clone(), m.cpu().clone(), sv.cpu().clone()
+    for step in (1, 2, 3):
+        g = torch.randn(n, device="cuda")
+        kw = dict(lr=1e-2, betas=(0.9, 0.95), eps=1e-8, wd=0.1, step=step, grad_scale=0.5)
+        adamw16_step_(p, m, sv, g, **kw)
+        adamw16_step_(pc, mc, svc, g.cpu(), **kw)
+    torch.testing.assert_close(p.cpu().float(), pc.float(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(m.cpu().float(), mc.float(), rtol=2e-2, atol=1e-3)
+
+
+def test_flat_adamw_kernel_matches_cpp_oracle():
+    from kohakuwullm_b200.ops import cpu_oracle as co
+    from kohakuwullm_b200.parallel.flat import FlatParameters
+    from kohakuwullm_b200.training.optim.fused_adamw import FlatAdamW
+
+    torch.manual_seed(3)
+    lin = torch.nn.Linear(64, 48, bias=False).cuda()
+    flat = FlatParameters(lin)
+    opt = FlatAdamW(flat, lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    p = lin.weight.detach().cpu().reshape(-1).clone()
+    m, v = torch.zeros_like(p), torch.zeros_like(p)
+    scale = torch.tensor([0.25], device="cuda")
+    for step in (1, 2, 3):
+        g = torch.randn(48, 64, device="cuda")
+        lin.weight.main_grad.copy_(g)
+        opt.step(grad_scale=scale)
+        co.adamw(p, m, v, g.cpu().reshape(-1), 0.25, 1e-2, 0.9, 0.95, 1e-8, 0.1, step)
+    torch.testing.assert_close(lin.weight.detach().cpu().reshape(-1), p, rtol=1e-5, atol=1e-6)
+    assert float(lin.weight.main_grad.abs().sum()) == 0.0
