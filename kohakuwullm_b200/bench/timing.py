@@ -51,6 +51,9 @@ def bench_samples(fn: Callable, *, warmup: int = 3, repeats: int = 20, flush: bo
             flush_l2()
         torch.cuda.synchronize()
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        # keep the GPU busy for ~0.1 ms so that the host enqueues start event, work and end event before
+        # the device reaches them: the interval then holds device time only, not host launch latency
+        torch.cuda._sleep(200_000)
         s.record()
         fn()
         e.record()
