@@ -79,6 +79,103 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 // Optional `dres` is added into dx (gradient arriving on the residual path), which fuses the
 // residual-add backward. Each block accumulates a dW partial over its rows in shared memory and
 // writes it to dw_partial[block, cols]; a second kernel sums the partials.
+// Register-resident variant for rows of at most 32 * NV vectors (8 bf16 each): a lane loads its NV vectors
+// of x and dy once (all loads issued before the first use), forms the row's dot product, and produces dx
+// and the weight-gradient partial from the same registers, so every byte is read exactly once.
+template <int NV>
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
+                       const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dy,
+                       const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
+                       float* __restrict__ dw_partial, int rows, int cols, int one_plus) {
+  extern __shared__ float s_dw[];  // cols floats
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int nvec = cols >> 3;
+  if (dw_partial)
+    for (int i = threadIdx.x; i < cols; i += blockDim.x) s_dw[i] = 0.f;
+  __syncthreads();
+  float dw_acc[NV][8];
+#pragma unroll
+  for (int j = 0; j < NV; ++j)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) dw_acc[j][e] = 0.f;
+  const float inv_cols = 1.f / static_cast<float>(cols);
+  for (int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows;
+       row += gridDim.x * warps_per_block) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * cols);
+    const uint4* gr = reinterpret_cast<const uint4*>(dy + static_cast<size_t>(row) * cols);
+    const uint4* rr = dres ? reinterpret_cast<const uint4*>(dres + static_cast<size_t>(row) * cols) : nullptr;
+    uint4 a[NV], g[NV], r[NV];
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int v = lane + 32 * j;
+      const bool in = v < nvec;
+      a[j] = in ? xr[v] : make_uint4(0, 0, 0, 0);
+      g[j] = in ? gr[v] : make_uint4(0, 0, 0, 0);
+      r[j] = (in && rr) ? rr[v] : make_uint4(0, 0, 0, 0);
+    }
+    const float rstd = rstd_in[row];
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int v = lane + 32 * j;
+      if (v < nvec) {
+        const uint32_t aw[4] = {a[j].x, a[j].y, a[j].z, a[j].w}, gw[4] = {g[j].x, g[j].y, g[j].z, g[j].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 xf = unpack_bf16(aw[e]), gf = unpack_bf16(gw[e]);
+          float w0 = 1.f, w1 = 1.f;
+          if (w) {
+            const float2 wv = *reinterpret_cast<const float2*>(w + 8 * v + 2 * e);
+            w0 = one_plus ? 1.f + wv.x : wv.x;
+            w1 = one_plus ? 1.f + wv.y : wv.y;
+          }
+          dot += gf.x * w0 * xf.x + gf.y * w1 * xf.y;
+        }
+      }
+    }
+    dot = warp_sum(dot) * rstd * inv_cols;
+    uint4* dxr = reinterpret_cast<uint4*>(dx + static_cast<size_t>(row) * cols);
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int v = lane + 32 * j;
+      if (v < nvec) {
+        const uint32_t aw[4] = {a[j].x, a[j].y, a[j].z, a[j].w}, gw[4] = {g[j].x, g[j].y, g[j].z, g[j].w};
+        const uint32_t rw[4] = {r[j].x, r[j].y, r[j].z, r[j].w};
+        uint32_t o[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 xf = unpack_bf16(aw[e]), gf = unpack_bf16(gw[e]), rf = unpack_bf16(rw[e]);
+          float w0 = 1.f, w1 = 1.f;
+          if (w) {
+            const float2 wv = *reinterpret_cast<const float2*>(w + 8 * v + 2 * e);
+            w0 = one_plus ? 1.f + wv.x : wv.x;
+            w1 = one_plus ? 1.f + wv.y : wv.y;
+          }
+          const float xh0 = xf.x * rstd, xh1 = xf.y * rstd;
+          o[e] = pack_bf16(rstd * (gf.x * w0 - xh0 * dot) + rf.x, rstd * (gf.y * w1 - xh1 * dot) + rf.y);
+          dw_acc[j][2 * e] += gf.x * xh0;
+          dw_acc[j][2 * e + 1] += gf.y * xh1;
+        }
+        dxr[v] = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    }
+  }
+  if (dw_partial) {
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int v = lane + 32 * j;
+      if (v < nvec)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) atomicAdd(&s_dw[8 * v + e], dw_acc[j][e]);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < cols; i += blockDim.x)
+      dw_partial[static_cast<size_t>(blockIdx.x) * cols + i] = s_dw[i];
+  }
+}
+
 __global__ void __launch_bounds__(256)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
                    const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dy,
@@ -424,11 +521,21 @@ KWU_API int kwu_rmsnorm_bwd(const void* x, const float* w, const float* rstd, co
   if (cols % 8) { set_last_error("rmsnorm: cols must be a multiple of 8"); return 7; }
   if (rows <= 0) return 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const int grid = grid_for(rows, 8, 296);
+  int grid = grid_for(rows, 8, 296);
   const bool want_dw = (w != nullptr && dw != nullptr && dw_partial != nullptr);
-  rmsnorm_bwd_kernel<<<grid, 256, want_dw ? cols * sizeof(float) : 0, st>>>(
-      (const __nv_bfloat16*)x, w, rstd, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)dres,
-      (__nv_bfloat16*)dx, want_dw ? dw_partial : nullptr, rows, cols, one_plus); kwu::count_launch();
+  const size_t dw_smem = want_dw ? cols * sizeof(float) : 0;
+  const int nv = (cols / 8 + 31) / 32;
+  if (nv <= 8 && grid > 148) grid = 148;  // the register-resident kernels run one CTA per SM
+#define KWU_RMS_BWD_ARGS (const __nv_bfloat16*)x, w, rstd, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)dres, \
+      (__nv_bfloat16*)dx, want_dw ? dw_partial : nullptr, rows, cols, one_plus
+  if (nv <= 2) rmsnorm_bwd_reg_kernel<2><<<grid, 256, dw_smem, st>>>(KWU_RMS_BWD_ARGS);
+  else if (nv <= 4) rmsnorm_bwd_reg_kernel<4><<<grid, 256, dw_smem, st>>>(KWU_RMS_BWD_ARGS);
+  else if (nv <= 5) rmsnorm_bwd_reg_kernel<5><<<grid, 256, dw_smem, st>>>(KWU_RMS_BWD_ARGS);
+  else if (nv <= 6) rmsnorm_bwd_reg_kernel<6><<<grid, 256, dw_smem, st>>>(KWU_RMS_BWD_ARGS);
+  else if (nv <= 8) rmsnorm_bwd_reg_kernel<8><<<grid, 256, dw_smem, st>>>(KWU_RMS_BWD_ARGS);
+  else rmsnorm_bwd_kernel<<<grid, 256, dw_smem, st>>>(KWU_RMS_BWD_ARGS);
+#undef KWU_RMS_BWD_ARGS
+  kwu::count_launch();
   if (int rc = check_launch("rmsnorm_bwd")) return rc;
   if (want_dw) {
     colsum_partials_kernel<<<(cols + 255) / 256, 256, 0, st>>>(dw_partial, dw, grid, cols, accumulate_dw); kwu::count_launch();
