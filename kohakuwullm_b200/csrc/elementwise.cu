@@ -5,6 +5,7 @@
 // src/kohakuwullm/kernels/elementwise/rmsnorm.py:20-128, swiglu.py:49-119 and
 // src/kohakuwullm/kernels/attention/rope.py:27-89.
 #include "common.cuh"
+#include "mx_quant.cuh"
 
 namespace kwu {
 
@@ -16,7 +17,7 @@ __global__ void __launch_bounds__(256)
 rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
                    const float* __restrict__ w, __nv_bfloat16* __restrict__ y,
                    __nv_bfloat16* __restrict__ h_out, float* __restrict__ rstd_out, int rows,
-                   int cols, float eps, int one_plus) {
+                   int cols, float eps, int one_plus, const MxOut mx) {
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
   const int nvec = cols >> 3;  // cols % 8 == 0 (checked on the host)
@@ -49,15 +50,17 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     if (HAS_RES) __syncwarp();
     const uint4* src = HAS_RES ? reinterpret_cast<const uint4*>(hr) : xr;
     uint4* yr = reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * cols);
-    for (int v = lane; v < nvec; v += 32) {
-      const uint4 a = src[v];
+    for (int v0 = 0; v0 < nvec; v0 += 32) {  // uniform trip count: the fp8 emission shuffles inside
+      const int v = v0 + lane;
+      const bool in = v < nvec;
+      const uint4 a = in ? src[v] : make_uint4(0, 0, 0, 0);
       float f[8];
       float2 t;
       t = unpack_bf16(a.x); f[0] = t.x; f[1] = t.y;
       t = unpack_bf16(a.y); f[2] = t.x; f[3] = t.y;
       t = unpack_bf16(a.z); f[4] = t.x; f[5] = t.y;
       t = unpack_bf16(a.w); f[6] = t.x; f[7] = t.y;
-      if (w) {
+      if (w && in) {
         const float4 w0 = reinterpret_cast<const float4*>(w)[2 * v];
         const float4 w1 = reinterpret_cast<const float4*>(w)[2 * v + 1];
         const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
@@ -70,7 +73,12 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
       uint4 o;
       o.x = pack_bf16(f[0], f[1]); o.y = pack_bf16(f[2], f[3]);
       o.z = pack_bf16(f[4], f[5]); o.w = pack_bf16(f[6], f[7]);
-      yr[v] = o;
+      if (in) yr[v] = o;
+      if (mx.q) {  // the fp8 copy is made from the stored (bf16-rounded) values
+        float fr[8];
+        unpack8(o, fr);
+        mx_emit8(fr, in, row, 8 * v, mx.q, mx.ldq, mx.sf, mx.n_kchunks);
+      }
     }
   }
 }
@@ -87,7 +95,7 @@ __global__ void __launch_bounds__(256)
 rmsnorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
                        const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dy,
                        const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
-                       float* __restrict__ dw_partial, int rows, int cols, int one_plus) {
+                       float* __restrict__ dw_partial, int rows, int cols, int one_plus, const MxOut mx) {
   extern __shared__ float s_dw[];  // cols floats
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -140,10 +148,10 @@ rmsnorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ x, const float* __restr
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
       const int v = lane + 32 * j;
+      uint32_t o[4] = {0u, 0u, 0u, 0u};
       if (v < nvec) {
         const uint32_t aw[4] = {a[j].x, a[j].y, a[j].z, a[j].w}, gw[4] = {g[j].x, g[j].y, g[j].z, g[j].w};
         const uint32_t rw[4] = {r[j].x, r[j].y, r[j].z, r[j].w};
-        uint32_t o[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const float2 xf = unpack_bf16(aw[e]), gf = unpack_bf16(gw[e]), rf = unpack_bf16(rw[e]);
@@ -159,6 +167,11 @@ rmsnorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ x, const float* __restr
           dw_acc[j][2 * e + 1] += gf.y * xh1;
         }
         dxr[v] = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+      if (mx.q && 32 * j < nvec) {  // warp-uniform condition: all lanes take part in the block maximum
+        float fr[8];
+        unpack8(make_uint4(o[0], o[1], o[2], o[3]), fr);
+        mx_emit8(fr, v < nvec, row, 8 * v, mx.q, mx.ldq, mx.sf, mx.n_kchunks);
       }
     }
   }
@@ -420,58 +433,79 @@ qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ src, int src_ld,
 // in: (rows, 2H) with the gate in columns [0,H) and the value in [H,2H); out (rows, H).
 __global__ void __launch_bounds__(256)
 swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ in, int in_ld, __nv_bfloat16* __restrict__ out,
-                  int out_ld, int rows, int H) {
+                  int out_ld, int rows, int H, const MxOut mx) {
   const int nvec = H >> 3;
   const long total = static_cast<long>(rows) * nvec;
-  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
-       i += static_cast<long>(gridDim.x) * blockDim.x) {
-    const int r = static_cast<int>(i / nvec);
-    const int v = static_cast<int>(i % nvec);
-    const uint4 g = *reinterpret_cast<const uint4*>(in + static_cast<size_t>(r) * in_ld + 8 * v);
-    const uint4 u = *reinterpret_cast<const uint4*>(in + static_cast<size_t>(r) * in_ld + H + 8 * v);
-    const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
-    uint32_t ow[4];
+  // uniform trip count for the whole block: the optional fp8 emission shuffles inside the loop
+  for (long base = static_cast<long>(blockIdx.x) * blockDim.x; base < total;
+       base += static_cast<long>(gridDim.x) * blockDim.x) {
+    const long i = base + threadIdx.x;
+    const bool in_range = i < total;
+    const int r = in_range ? static_cast<int>(i / nvec) : 0;
+    const int v = in_range ? static_cast<int>(i % nvec) : 0;
+    uint32_t ow[4] = {0u, 0u, 0u, 0u};
+    if (in_range) {
+      const uint4 g = *reinterpret_cast<const uint4*>(in + static_cast<size_t>(r) * in_ld + 8 * v);
+      const uint4 u = *reinterpret_cast<const uint4*>(in + static_cast<size_t>(r) * in_ld + H + 8 * v);
+      const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const float2 gf = unpack_bf16(gw[e]), uf = unpack_bf16(uw[e]);
-      const float s0 = gf.x / (1.f + __expf(-gf.x)), s1 = gf.y / (1.f + __expf(-gf.y));
-      ow[e] = pack_bf16(s0 * uf.x, s1 * uf.y);
+      for (int e = 0; e < 4; ++e) {
+        const float2 gf = unpack_bf16(gw[e]), uf = unpack_bf16(uw[e]);
+        const float s0 = gf.x / (1.f + __expf(-gf.x)), s1 = gf.y / (1.f + __expf(-gf.y));
+        ow[e] = pack_bf16(s0 * uf.x, s1 * uf.y);
+      }
+      *reinterpret_cast<uint4*>(out + static_cast<size_t>(r) * out_ld + 8 * v) =
+          make_uint4(ow[0], ow[1], ow[2], ow[3]);
     }
-    *reinterpret_cast<uint4*>(out + static_cast<size_t>(r) * out_ld + 8 * v) =
-        make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    if (mx.q) {
+      float fr[8];
+      unpack8(make_uint4(ow[0], ow[1], ow[2], ow[3]), fr);
+      mx_emit8(fr, in_range, r, 8 * v, mx.q, mx.ldq, mx.sf, mx.n_kchunks);
+    }
   }
 }
 
 __global__ void __launch_bounds__(256)
 swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ in, int in_ld,
                   const __nv_bfloat16* __restrict__ dout, int dout_ld,
-                  __nv_bfloat16* __restrict__ din, int din_ld, int rows, int H) {
+                  __nv_bfloat16* __restrict__ din, int din_ld, int rows, int H, const MxOut mx) {
   const int nvec = H >> 3;
   const long total = static_cast<long>(rows) * nvec;
-  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
-       i += static_cast<long>(gridDim.x) * blockDim.x) {
-    const int r = static_cast<int>(i / nvec);
-    const int v = static_cast<int>(i % nvec);
-    const uint4 g = *reinterpret_cast<const uint4*>(in + static_cast<size_t>(r) * in_ld + 8 * v);
-    const uint4 u = *reinterpret_cast<const uint4*>(in + static_cast<size_t>(r) * in_ld + H + 8 * v);
-    const uint4 d = *reinterpret_cast<const uint4*>(dout + static_cast<size_t>(r) * dout_ld + 8 * v);
-    const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w},
-                   dw[4] = {d.x, d.y, d.z, d.w};
-    uint32_t og[4], ou[4];
+  for (long base = static_cast<long>(blockIdx.x) * blockDim.x; base < total;
+       base += static_cast<long>(gridDim.x) * blockDim.x) {
+    const long i = base + threadIdx.x;
+    const bool in_range = i < total;
+    const int r = in_range ? static_cast<int>(i / nvec) : 0;
+    const int v = in_range ? static_cast<int>(i % nvec) : 0;
+    uint32_t og[4] = {0u, 0u, 0u, 0u}, ou[4] = {0u, 0u, 0u, 0u};
+    if (in_range) {
+      const uint4 g = *reinterpret_cast<const uint4*>(in + static_cast<size_t>(r) * in_ld + 8 * v);
+      const uint4 u = *reinterpret_cast<const uint4*>(in + static_cast<size_t>(r) * in_ld + H + 8 * v);
+      const uint4 d = *reinterpret_cast<const uint4*>(dout + static_cast<size_t>(r) * dout_ld + 8 * v);
+      const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w},
+                     dw[4] = {d.x, d.y, d.z, d.w};
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const float2 gf = unpack_bf16(gw[e]), uf = unpack_bf16(uw[e]), df = unpack_bf16(dw[e]);
-      const float sg0 = 1.f / (1.f + __expf(-gf.x)), sg1 = 1.f / (1.f + __expf(-gf.y));
-      const float si0 = gf.x * sg0, si1 = gf.y * sg1;
-      const float dg0 = df.x * uf.x * (sg0 * (1.f + gf.x * (1.f - sg0)));
-      const float dg1 = df.y * uf.y * (sg1 * (1.f + gf.y * (1.f - sg1)));
-      og[e] = pack_bf16(dg0, dg1);
-      ou[e] = pack_bf16(df.x * si0, df.y * si1);
+      for (int e = 0; e < 4; ++e) {
+        const float2 gf = unpack_bf16(gw[e]), uf = unpack_bf16(uw[e]), df = unpack_bf16(dw[e]);
+        const float sg0 = 1.f / (1.f + __expf(-gf.x)), sg1 = 1.f / (1.f + __expf(-gf.y));
+        const float si0 = gf.x * sg0, si1 = gf.y * sg1;
+        const float dg0 = df.x * uf.x * (sg0 * (1.f + gf.x * (1.f - sg0)));
+        const float dg1 = df.y * uf.y * (sg1 * (1.f + gf.y * (1.f - sg1)));
+        og[e] = pack_bf16(dg0, dg1);
+        ou[e] = pack_bf16(df.x * si0, df.y * si1);
+      }
+      *reinterpret_cast<uint4*>(din + static_cast<size_t>(r) * din_ld + 8 * v) =
+          make_uint4(og[0], og[1], og[2], og[3]);
+      *reinterpret_cast<uint4*>(din + static_cast<size_t>(r) * din_ld + H + 8 * v) =
+          make_uint4(ou[0], ou[1], ou[2], ou[3]);
     }
-    *reinterpret_cast<uint4*>(din + static_cast<size_t>(r) * din_ld + 8 * v) =
-        make_uint4(og[0], og[1], og[2], og[3]);
-    *reinterpret_cast<uint4*>(din + static_cast<size_t>(r) * din_ld + H + 8 * v) =
-        make_uint4(ou[0], ou[1], ou[2], ou[3]);
+    if (mx.q) {  // din is quantised along its 2H columns: gate half and value half are separate blocks
+      float fr[8];
+      unpack8(make_uint4(og[0], og[1], og[2], og[3]), fr);
+      mx_emit8(fr, in_range, r, 8 * v, mx.q, mx.ldq, mx.sf, mx.n_kchunks);
+      unpack8(make_uint4(ou[0], ou[1], ou[2], ou[3]), fr);
+      mx_emit8(fr, in_range, r, H + 8 * v, mx.q, mx.ldq, mx.sf, mx.n_kchunks);
+    }
   }
 }
 
@@ -495,8 +529,22 @@ static inline int check_launch(const char* what) {
 
 using namespace kwu;
 
-KWU_API int kwu_rmsnorm_fwd(const void* x, const void* res, const float* w, void* y, void* h_out,
-                            float* rstd, int rows, int cols, float eps, int one_plus, void* stream) {
+static MxOut make_mx(void* q, int ldq, void* sf, int cols) {
+  MxOut m;
+  m.q = reinterpret_cast<uint8_t*>(q); m.ldq = ldq; m.sf = reinterpret_cast<uint8_t*>(sf); m.n_kchunks = cols >> 7;
+  return m;
+}
+// The fused fp8 copy needs whole 128-row scale tiles and 128-column chunks.
+static bool mx_shape_ok(const char* what, int rows, int cols) {
+  if (rows % 128 || cols % 128) {
+    set_last_error("%s: fp8 emission needs rows and cols that are multiples of 128 (got %d x %d)", what, rows, cols);
+    return false;
+  }
+  return true;
+}
+
+static int rmsnorm_fwd_impl(const void* x, const void* res, const float* w, void* y, void* h_out,
+                            float* rstd, int rows, int cols, float eps, int one_plus, const MxOut mx, void* stream) {
   if (cols % 8) { set_last_error("rmsnorm: cols must be a multiple of 8"); return 7; }
   if (rows <= 0) return 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
@@ -504,21 +552,35 @@ KWU_API int kwu_rmsnorm_fwd(const void* x, const void* res, const float* w, void
   if (res) {
     rmsnorm_fwd_kernel<true><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)res, w,
                                                   (__nv_bfloat16*)y, (__nv_bfloat16*)h_out, rstd, rows,
-                                                  cols, eps, one_plus); kwu::count_launch();
+                                                  cols, eps, one_plus, mx); kwu::count_launch();
   } else {
     rmsnorm_fwd_kernel<false><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, nullptr, w, (__nv_bfloat16*)y,
-                                                   nullptr, rstd, rows, cols, eps, one_plus); kwu::count_launch();
+                                                   nullptr, rstd, rows, cols, eps, one_plus, mx); kwu::count_launch();
   }
   return check_launch("rmsnorm_fwd");
+}
+
+KWU_API int kwu_rmsnorm_fwd(const void* x, const void* res, const float* w, void* y, void* h_out,
+                            float* rstd, int rows, int cols, float eps, int one_plus, void* stream) {
+  return rmsnorm_fwd_impl(x, res, w, y, h_out, rstd, rows, cols, eps, one_plus, make_mx(nullptr, 0, nullptr, cols), stream);
+}
+
+// Same, and also writes the MXFP8 copy of y (e4m3 bytes `q` with pitch ldq, scale chunks `sf`).
+KWU_API int kwu_rmsnorm_fwd_mx(const void* x, const void* res, const float* w, void* y, void* h_out,
+                               float* rstd, int rows, int cols, float eps, int one_plus, void* q, int ldq, void* sf,
+                               void* stream) {
+  if (!mx_shape_ok("rmsnorm_fwd_mx", rows, cols)) return 7;
+  return rmsnorm_fwd_impl(x, res, w, y, h_out, rstd, rows, cols, eps, one_plus, make_mx(q, ldq, sf, cols), stream);
 }
 
 // dw_partial: scratch of `kwu_rmsnorm_bwd_blocks(rows)` x cols floats (may be null when w is null).
 KWU_API int kwu_rmsnorm_bwd_blocks(int rows) { return grid_for(rows, 8, 296); }
 
-KWU_API int kwu_rmsnorm_bwd(const void* x, const float* w, const float* rstd, const void* dy,
+static int rmsnorm_bwd_impl(const void* x, const float* w, const float* rstd, const void* dy,
                             const void* dres, void* dx, float* dw, float* dw_partial, int rows,
-                            int cols, int one_plus, int accumulate_dw, void* stream) {
+                            int cols, int one_plus, int accumulate_dw, const MxOut mx, void* stream) {
   if (cols % 8) { set_last_error("rmsnorm: cols must be a multiple of 8"); return 7; }
+  if (mx.q && cols > 2048) { set_last_error("rmsnorm_bwd_mx: rows wider than 2048 columns are not supported"); return 7; }
   if (rows <= 0) return 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int grid = grid_for(rows, 8, 296);
@@ -528,11 +590,11 @@ KWU_API int kwu_rmsnorm_bwd(const void* x, const float* w, const float* rstd, co
   if (nv <= 8 && grid > 148) grid = 148;  // the register-resident kernels run one CTA per SM
 #define KWU_RMS_BWD_ARGS (const __nv_bfloat16*)x, w, rstd, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)dres, \
       (__nv_bfloat16*)dx, want_dw ? dw_partial : nullptr, rows, cols, one_plus
-  if (nv <= 2) rmsnorm_bwd_reg_kernel<2><<<grid, 256, dw_smem, st>>>(KWU_RMS_BWD_ARGS);
-  else if (nv <= 4) rmsnorm_bwd_reg_kernel<4><<<grid, 256, dw_smem, st>>>(KWU_RMS_BWD_ARGS);
-  else if (nv <= 5) rmsnorm_bwd_reg_kernel<5><<<grid, 256, dw_smem, st>>>(KWU_RMS_BWD_ARGS);
-  else if (nv <= 6) rmsnorm_bwd_reg_kernel<6><<<grid, 256, dw_smem, st>>>(KWU_RMS_BWD_ARGS);
-  else if (nv <= 8) rmsnorm_bwd_reg_kernel<8><<<grid, 256, dw_smem, st>>>(KWU_RMS_BWD_ARGS);
+  if (nv <= 2) rmsnorm_bwd_reg_kernel<2><<<grid, 256, dw_smem, st>>>(KWU_RMS_BWD_ARGS, mx);
+  else if (nv <= 4) rmsnorm_bwd_reg_kernel<4><<<grid, 256, dw_smem, st>>>(KWU_RMS_BWD_ARGS, mx);
+  else if (nv <= 5) rmsnorm_bwd_reg_kernel<5><<<grid, 256, dw_smem, st>>>(KWU_RMS_BWD_ARGS, mx);
+  else if (nv <= 6) rmsnorm_bwd_reg_kernel<6><<<grid, 256, dw_smem, st>>>(KWU_RMS_BWD_ARGS, mx);
+  else if (nv <= 8) rmsnorm_bwd_reg_kernel<8><<<grid, 256, dw_smem, st>>>(KWU_RMS_BWD_ARGS, mx);
   else rmsnorm_bwd_kernel<<<grid, 256, dw_smem, st>>>(KWU_RMS_BWD_ARGS);
 #undef KWU_RMS_BWD_ARGS
   kwu::count_launch();
@@ -542,6 +604,22 @@ KWU_API int kwu_rmsnorm_bwd(const void* x, const float* w, const float* rstd, co
     return check_launch("rmsnorm_dw");
   }
   return 0;
+}
+
+KWU_API int kwu_rmsnorm_bwd(const void* x, const float* w, const float* rstd, const void* dy,
+                            const void* dres, void* dx, float* dw, float* dw_partial, int rows,
+                            int cols, int one_plus, int accumulate_dw, void* stream) {
+  return rmsnorm_bwd_impl(x, w, rstd, dy, dres, dx, dw, dw_partial, rows, cols, one_plus, accumulate_dw,
+                          make_mx(nullptr, 0, nullptr, cols), stream);
+}
+
+// Same, and also writes the MXFP8 copy of dx (the gradient that the previous projection's dgrad consumes).
+KWU_API int kwu_rmsnorm_bwd_mx(const void* x, const float* w, const float* rstd, const void* dy,
+                               const void* dres, void* dx, float* dw, float* dw_partial, int rows,
+                               int cols, int one_plus, int accumulate_dw, void* q, int ldq, void* sf, void* stream) {
+  if (!mx_shape_ok("rmsnorm_bwd_mx", rows, cols)) return 7;
+  return rmsnorm_bwd_impl(x, w, rstd, dy, dres, dx, dw, dw_partial, rows, cols, one_plus, accumulate_dw,
+                          make_mx(q, ldq, sf, cols), stream);
 }
 
 KWU_API int kwu_qknorm_rope_fwd(const void* src, int src_ld, void* dst, int dst_ld, const float* weight,
@@ -576,26 +654,50 @@ KWU_API int kwu_qknorm_rope_bwd(const void* src, int src_ld, const void* dout, i
   return check_launch("qknorm_rope_bwd");
 }
 
-KWU_API int kwu_swiglu_fwd(const void* in, int in_ld, void* out, int out_ld, int rows, int H,
+static int swiglu_fwd_impl(const void* in, int in_ld, void* out, int out_ld, int rows, int H, const MxOut mx,
                            void* stream) {
   if (H % 8 || in_ld % 8 || out_ld % 8) { set_last_error("swiglu: H and pitches must be multiples of 8"); return 7; }
   if (rows <= 0) return 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int grid = grid_for(static_cast<long>(rows) * (H / 8), 256);
   swiglu_fwd_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)in, in_ld, (__nv_bfloat16*)out, out_ld,
-                                         rows, H); kwu::count_launch();
+                                         rows, H, mx); kwu::count_launch();
   return check_launch("swiglu_fwd");
 }
 
-KWU_API int kwu_swiglu_bwd(const void* in, int in_ld, const void* dout, int dout_ld, void* din,
-                           int din_ld, int rows, int H, void* stream) {
+KWU_API int kwu_swiglu_fwd(const void* in, int in_ld, void* out, int out_ld, int rows, int H,
+                           void* stream) {
+  return swiglu_fwd_impl(in, in_ld, out, out_ld, rows, H, make_mx(nullptr, 0, nullptr, H), stream);
+}
+
+// Same, and also writes the MXFP8 copy of the (rows, H) output.
+KWU_API int kwu_swiglu_fwd_mx(const void* in, int in_ld, void* out, int out_ld, int rows, int H, void* q, int ldq,
+                              void* sf, void* stream) {
+  if (!mx_shape_ok("swiglu_fwd_mx", rows, H)) return 7;
+  return swiglu_fwd_impl(in, in_ld, out, out_ld, rows, H, make_mx(q, ldq, sf, H), stream);
+}
+
+static int swiglu_bwd_impl(const void* in, int in_ld, const void* dout, int dout_ld, void* din,
+                           int din_ld, int rows, int H, const MxOut mx, void* stream) {
   if (H % 8 || in_ld % 8 || dout_ld % 8 || din_ld % 8) { set_last_error("swiglu: H and pitches must be multiples of 8"); return 7; }
   if (rows <= 0) return 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int grid = grid_for(static_cast<long>(rows) * (H / 8), 256);
   swiglu_bwd_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)in, in_ld, (const __nv_bfloat16*)dout,
-                                         dout_ld, (__nv_bfloat16*)din, din_ld, rows, H); kwu::count_launch();
+                                         dout_ld, (__nv_bfloat16*)din, din_ld, rows, H, mx); kwu::count_launch();
   return check_launch("swiglu_bwd");
+}
+
+KWU_API int kwu_swiglu_bwd(const void* in, int in_ld, const void* dout, int dout_ld, void* din,
+                           int din_ld, int rows, int H, void* stream) {
+  return swiglu_bwd_impl(in, in_ld, dout, dout_ld, din, din_ld, rows, H, make_mx(nullptr, 0, nullptr, 2 * H), stream);
+}
+
+// Same, and also writes the MXFP8 copy of the (rows, 2H) input gradient.
+KWU_API int kwu_swiglu_bwd_mx(const void* in, int in_ld, const void* dout, int dout_ld, void* din,
+                              int din_ld, int rows, int H, void* q, int ldq, void* sf, void* stream) {
+  if (!mx_shape_ok("swiglu_bwd_mx", rows, 2 * H) || H % 32) { set_last_error("swiglu_bwd_mx: bad shape"); return 7; }
+  return swiglu_bwd_impl(in, in_ld, dout, dout_ld, din, din_ld, rows, H, make_mx(q, ldq, sf, 2 * H), stream);
 }
 
 // --------------------------------------------------------------------------- allocation-free variant

@@ -15,29 +15,11 @@
 // never inject a NaN scale. Reference: src/kohakuwullm/kernels/mxfp8/quantize.py:39-215 and the
 // cuBLASLt path behind src/kohakuwullm/kernels/mxfp8/linear.py:49-126.
 #include "common.cuh"
+#include "mx_quant.cuh"
 
 namespace kwu {
 
 // ------------------------------------------------------------------------------------ quantise
-__device__ __forceinline__ uint32_t ue8m0_from_amax(float amax) {
-  amax = fmaxf(amax, 1e-30f);
-  const float v = amax * (1.0f / 448.0f);
-  const uint32_t bits = __float_as_uint(v);
-  uint32_t e = (bits >> 23) & 0xffu;
-  if (bits & 0x7fffffu) e += 1;  // ceil(log2(v))
-  return min(e, 254u);
-}
-__device__ __forceinline__ float inv_scale_from_ue8m0(uint32_t e) {
-  // 2^-(e-127) = 2^(127-e): biased exponent 254 - e (e = 254 would be a denormal; clamp)
-  const uint32_t be = (e >= 254u) ? 1u : (254u - e);
-  return __uint_as_float(be << 23);
-}
-__device__ __forceinline__ size_t sf_offset(int row, int kblock, int n_kchunks) {
-  const int rt = row >> 7, r = row & 127;
-  return (static_cast<size_t>(rt) * n_kchunks + (kblock >> 2)) * 512 + (r & 31) * 16 + (r >> 5) * 4 +
-         (kblock & 3);
-}
-
 // One thread = 8 consecutive elements; 4 threads = one 32-block; a warp covers 256 columns of a row.
 __global__ void __launch_bounds__(256)
 mxfp8_quantize_kernel(const __nv_bfloat16* __restrict__ x, int ldx, uint8_t* __restrict__ q, int ldq,

@@ -94,6 +94,9 @@ class LMBackbone(nn.Module):
         report = swap_mxfp8(self)
         if report.blocking:
             raise RuntimeError(f"MXFP8 conversion incomplete: {report.blocking}")
+        from kohakuwullm_b200.models.mxfp8_swap import wire_fused_quantisation
+
+        wire_fused_quantisation(self)
 
     def refresh_mxfp8(self) -> int:
         from kohakuwullm_b200.models.mxfp8_swap import refresh_mxfp8_weights
@@ -131,6 +134,10 @@ class LMBackbone(nn.Module):
 
     def forward(self, tokens: torch.Tensor, seq_info: SeqInfo, cache=None, taps: list | None = None):
         """tokens (T,) packed or (B,S) padded -> final-normed hidden states of the same leading shape."""
+        if self.config.mxfp8:
+            from kohakuwullm_b200.ops.mxfp8 import clear_prequantized
+
+            clear_prequantized()
         x = self.embed_tokens(tokens)
         rope, plan = self.prepare(seq_info, x.device, x.dtype)
         x, pending = self.run_blocks(x, seq_info, rope, plan, cache=cache, taps=taps)

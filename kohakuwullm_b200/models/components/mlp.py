@@ -81,7 +81,8 @@ class GLUMLP(nn.Module):
     def forward(self, x):
         h = self.w_in(x)
         if self.activation == "silu":
-            a = swiglu(h)
+            # with MXFP8 projections the activation kernel also writes the fp8 copies its neighbours consume
+            a = swiglu(h, emit_mx=self.w_out.mxfp8, emit_mx_grad=self.w_in.mxfp8)
         else:
             g, v = h.chunk(2, dim=-1)
             a = torch.nn.functional.gelu(g, approximate="tanh") * v

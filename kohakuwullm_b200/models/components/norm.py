@@ -22,10 +22,14 @@ class RMSNorm(nn.Module):
         self.dim, self.eps = dim, eps
         init = torch.zeros(dim) if self.one_plus else torch.ones(dim)
         self.weight = nn.Parameter(init) if affine else None
+        # set by the MXFP8 wiring: the output / the input gradient feeds an MXFP8 linear, so the kernel
+        # writes the fp8 copy in the same pass
+        self.emit_mx = False
+        self.emit_mx_grad = False
 
     def forward(self, x, residual=None):
         """``norm(x)``, or with ``residual``: ``(norm(x + residual), x + residual)``."""
-        return rmsnorm(x, self.weight, self.eps, self.one_plus, residual)
+        return rmsnorm(x, self.weight, self.eps, self.one_plus, residual, self.emit_mx, self.emit_mx_grad)
 
     def extra_repr(self):
         return f"{self.dim}, eps={self.eps}, affine={self.weight is not None}"

@@ -84,6 +84,39 @@ def swap_mxfp8(model: nn.Module, scope: tuple[str, ...] | None = None, convert_d
     return report
 
 
+def wire_fused_quantisation(backbone: nn.Module) -> int:
+    """Tell every RMSNorm whose output (or whose input gradient) feeds an MXFP8 linear to write the fp8 copy
+    itself: ``norm_attn -> qkv_proj``, ``norm_mlp -> w_in`` in the forward pass; in the backward pass the
+    gradient leaving ``norm_mlp`` is the ``dy`` of ``attn.o_proj`` and the one leaving the NEXT block's
+    ``norm_attn`` (or the final norm) is the ``dy`` of ``mlp.w_out``. Returns the number of flags set."""
+    from kohakuwullm_b200.models.components.norm import RMSNorm
+
+    def is_mx(module, name):
+        lin = getattr(module, name, None)
+        return isinstance(lin, Linear) and lin.mxfp8
+
+    blocks = list(getattr(backbone, "blocks", []))
+    n = 0
+    for i, blk in enumerate(blocks):
+        plain = getattr(blk, "post_attn", None) is None and getattr(blk, "residual_scale", 1.0) == 1.0
+        if isinstance(blk.norm_attn, RMSNorm):
+            blk.norm_attn.emit_mx = is_mx(blk.attn, "qkv_proj")
+            prev_out = i > 0 and plain and is_mx(blocks[i - 1].mlp, "w_out")
+            blk.norm_attn.emit_mx_grad = bool(prev_out)
+            n += int(blk.norm_attn.emit_mx) + int(blk.norm_attn.emit_mx_grad)
+        if isinstance(blk.norm_mlp, RMSNorm):
+            blk.norm_mlp.emit_mx = is_mx(blk.mlp, "w_in")
+            blk.norm_mlp.emit_mx_grad = plain and is_mx(blk.attn, "o_proj")
+            n += int(blk.norm_mlp.emit_mx) + int(blk.norm_mlp.emit_mx_grad)
+    final = getattr(backbone, "final_norm", None)
+    if blocks and isinstance(final, RMSNorm):
+        last = blocks[-1]
+        plain = getattr(last, "post_mlp", None) is None and getattr(last, "residual_scale", 1.0) == 1.0
+        final.emit_mx_grad = plain and is_mx(last.mlp, "w_out")
+        n += int(final.emit_mx_grad)
+    return n
+
+
 def refresh_mxfp8_weights(model: nn.Module) -> int:
     count = 0
     for module in model.modules():

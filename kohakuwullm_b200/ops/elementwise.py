@@ -37,7 +37,7 @@ def rmsnorm_reference(x, weight=None, eps=1e-6, one_plus=False, residual=None):
 
 class _RMSNorm(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weight, residual, eps, one_plus):
+    def forward(ctx, x, weight, residual, eps, one_plus, emit_mx=False, emit_mx_grad=False):
         L = native.require()
         cols = x.shape[-1]
         x2 = x.reshape(-1, cols)
@@ -53,12 +53,23 @@ class _RMSNorm(torch.autograd.Function):
             if not r2.is_contiguous():
                 r2 = r2.contiguous()
             h = torch.empty_like(x2)
-        rc = L.kwu_rmsnorm_fwd(
-            native.ptr(x2), native.ptr(r2), native.ptr(weight), native.ptr(y), native.ptr(h),
-            native.ptr(rstd), c_int(rows), c_int(cols), c_float(eps), c_int(int(one_plus)),
-            native.stream_ptr(),
-        )
+        from kohakuwullm_b200.ops import mxfp8 as mx
+
+        if emit_mx and mx.can_emit(rows, cols):
+            q, sf = mx.alloc_quantized(rows, cols, x.device)
+            rc = L.kwu_rmsnorm_fwd_mx(
+                native.ptr(x2), native.ptr(r2), native.ptr(weight), native.ptr(y), native.ptr(h),
+                native.ptr(rstd), c_int(rows), c_int(cols), c_float(eps), c_int(int(one_plus)),
+                native.ptr(q), c_int(cols), native.ptr(sf), native.stream_ptr())
+            mx.stash_quantized(y, q, sf)
+        else:
+            rc = L.kwu_rmsnorm_fwd(
+                native.ptr(x2), native.ptr(r2), native.ptr(weight), native.ptr(y), native.ptr(h),
+                native.ptr(rstd), c_int(rows), c_int(cols), c_float(eps), c_int(int(one_plus)),
+                native.stream_ptr(),
+            )
         native.check(rc, "rmsnorm_fwd")
+        ctx.emit_mx_grad = emit_mx_grad
         ctx.save_for_backward(h if h is not None else x2, weight, rstd)
         ctx.one_plus = one_plus
         ctx.has_res = residual is not None
@@ -86,26 +97,36 @@ class _RMSNorm(torch.autograd.Function):
             nblocks = L.kwu_rmsnorm_bwd_blocks(c_int(rows))
             partial = torch.empty(nblocks, cols, dtype=torch.float32, device=xin.device)
             dw = torch.empty(cols, dtype=torch.float32, device=xin.device)
-        rc = L.kwu_rmsnorm_bwd(
-            native.ptr(xin), native.ptr(weight), native.ptr(rstd), native.ptr(dy2), native.ptr(dres),
-            native.ptr(dx), native.ptr(dw), native.ptr(partial), c_int(rows), c_int(cols),
-            c_int(int(ctx.one_plus)), c_int(0), native.stream_ptr(),
-        )
+        from kohakuwullm_b200.ops import mxfp8 as mx
+
+        if ctx.emit_mx_grad and mx.can_emit(rows, cols) and cols <= 2048:
+            q, sf = mx.alloc_quantized(rows, cols, xin.device)
+            rc = L.kwu_rmsnorm_bwd_mx(
+                native.ptr(xin), native.ptr(weight), native.ptr(rstd), native.ptr(dy2), native.ptr(dres),
+                native.ptr(dx), native.ptr(dw), native.ptr(partial), c_int(rows), c_int(cols),
+                c_int(int(ctx.one_plus)), c_int(0), native.ptr(q), c_int(cols), native.ptr(sf), native.stream_ptr())
+            mx.stash_quantized(dx, q, sf)
+        else:
+            rc = L.kwu_rmsnorm_bwd(
+                native.ptr(xin), native.ptr(weight), native.ptr(rstd), native.ptr(dy2), native.ptr(dres),
+                native.ptr(dx), native.ptr(dw), native.ptr(partial), c_int(rows), c_int(cols),
+                c_int(int(ctx.one_plus)), c_int(0), native.stream_ptr(),
+            )
         native.check(rc, "rmsnorm_bwd")
         dxv = dx.view(ctx.shape)
         if dw is not None:
             dw = dw.to(weight.dtype)
-        return dxv, dw, (dxv if ctx.has_res else None), None, None
+        return dxv, dw, (dxv if ctx.has_res else None), None, None, None, None
 
 
-def rmsnorm(x, weight=None, eps=1e-6, one_plus=False, residual=None):
+def rmsnorm(x, weight=None, eps=1e-6, one_plus=False, residual=None, emit_mx=False, emit_mx_grad=False):
     """RMSNorm over the last dimension.
 
     With ``residual`` the sum ``h = x + residual`` is formed inside the kernel and the call
     returns ``(norm(h), h)``: the residual add and the pre-norm of a decoder block in one pass.
     """
     if _native_ok(x) and x.shape[-1] % 8 == 0 and (weight is None or weight.dtype == torch.float32):
-        return _RMSNorm.apply(x, weight, residual, eps, one_plus)
+        return _RMSNorm.apply(x, weight, residual, eps, one_plus, emit_mx, emit_mx_grad)
     return rmsnorm_reference(x, weight, eps, one_plus, residual)
 
 
@@ -117,7 +138,7 @@ def swiglu_reference(h):
 
 class _SwiGLU(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, h):
+    def forward(ctx, h, emit_mx=False, emit_mx_grad=False):
         L = native.require()
         H2 = h.shape[-1]
         h2 = h.reshape(-1, H2)
@@ -125,9 +146,18 @@ class _SwiGLU(torch.autograd.Function):
             h2 = h2.contiguous()
         rows, H = h2.shape[0], H2 // 2
         out = torch.empty(rows, H, dtype=h.dtype, device=h.device)
-        rc = L.kwu_swiglu_fwd(native.ptr(h2), c_int(h2.stride(0)), native.ptr(out), c_int(H),
-                              c_int(rows), c_int(H), native.stream_ptr())
+        from kohakuwullm_b200.ops import mxfp8 as mx
+
+        if emit_mx and mx.can_emit(rows, H):
+            q, sf = mx.alloc_quantized(rows, H, h.device)
+            rc = L.kwu_swiglu_fwd_mx(native.ptr(h2), c_int(h2.stride(0)), native.ptr(out), c_int(H),
+                                     c_int(rows), c_int(H), native.ptr(q), c_int(H), native.ptr(sf), native.stream_ptr())
+            mx.stash_quantized(out, q, sf)
+        else:
+            rc = L.kwu_swiglu_fwd(native.ptr(h2), c_int(h2.stride(0)), native.ptr(out), c_int(H),
+                                  c_int(rows), c_int(H), native.stream_ptr())
         native.check(rc, "swiglu_fwd")
+        ctx.emit_mx_grad = emit_mx_grad
         ctx.save_for_backward(h2)
         ctx.shape = h.shape
         return out.view(*h.shape[:-1], H)
@@ -142,16 +172,27 @@ class _SwiGLU(torch.autograd.Function):
         if not d2.is_contiguous():
             d2 = d2.contiguous()
         din = torch.empty(rows, H2, dtype=h2.dtype, device=h2.device)
-        rc = L.kwu_swiglu_bwd(native.ptr(h2), c_int(h2.stride(0)), native.ptr(d2), c_int(H),
-                              native.ptr(din), c_int(H2), c_int(rows), c_int(H), native.stream_ptr())
+        from kohakuwullm_b200.ops import mxfp8 as mx
+
+        if ctx.emit_mx_grad and mx.can_emit(rows, H2) and H % 32 == 0:
+            q, sf = mx.alloc_quantized(rows, H2, h2.device)
+            rc = L.kwu_swiglu_bwd_mx(native.ptr(h2), c_int(h2.stride(0)), native.ptr(d2), c_int(H),
+                                     native.ptr(din), c_int(H2), c_int(rows), c_int(H), native.ptr(q), c_int(H2),
+                                     native.ptr(sf), native.stream_ptr())
+            mx.stash_quantized(din, q, sf)
+        else:
+            rc = L.kwu_swiglu_bwd(native.ptr(h2), c_int(h2.stride(0)), native.ptr(d2), c_int(H),
+                                  native.ptr(din), c_int(H2), c_int(rows), c_int(H), native.stream_ptr())
         native.check(rc, "swiglu_bwd")
-        return din.view(ctx.shape)
+        return din.view(ctx.shape), None, None
 
 
-def swiglu(h):
-    """``silu(h[..., :H]) * h[..., H:]`` for a fused gate|value projection output."""
+def swiglu(h, emit_mx=False, emit_mx_grad=False):
+    """``silu(h[..., :H]) * h[..., H:]`` for a fused gate|value projection output. ``emit_mx`` /
+    ``emit_mx_grad``: also write the MXFP8 copy of the output / of the input gradient for the MXFP8 linear
+    that consumes it (see ``ops.mxfp8.stash_quantized``)."""
     if _native_ok(h) and (h.shape[-1] // 2) % 8 == 0:
-        return _SwiGLU.apply(h)
+        return _SwiGLU.apply(h, emit_mx, emit_mx_grad)
     return swiglu_reference(h)
 
 

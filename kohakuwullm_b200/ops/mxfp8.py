@@ -110,6 +110,42 @@ def gemm(a_q, a_sf, b_q, b_sf, out=None, out_dtype=torch.bfloat16, accumulate=Fa
     return out
 
 
+# ------------------------------------------------------------------------------------ producer-made copies
+# A producer kernel (RMSNorm, SwiGLU, their backward passes) can write the fp8 copy of its output in the same
+# pass. It registers the copy here under the output's address; the MXFP8 linear that consumes the tensor takes
+# it instead of running the quantise kernel. Entries are single-use, are only made when the model wiring says
+# that the consumer is an MXFP8 linear, and are dropped at the start of every model forward.
+_PREQUANTIZED: dict[int, tuple] = {}
+
+
+def alloc_quantized(rows: int, cols: int, device):
+    return (torch.empty(rows, cols, dtype=torch.uint8, device=device),
+            torch.empty(sf_bytes(rows, cols), dtype=torch.uint8, device=device))
+
+
+def can_emit(rows: int, cols: int) -> bool:
+    return rows > 0 and rows % 128 == 0 and cols % 128 == 0
+
+
+def stash_quantized(t: torch.Tensor, q: torch.Tensor, sf: torch.Tensor) -> None:
+    _PREQUANTIZED[t.data_ptr()] = (q, sf, t.numel(), q.shape)
+
+
+def take_quantized(t: torch.Tensor):
+    """The producer-made fp8 copy of ``t`` (2-D, contiguous), or None."""
+    entry = _PREQUANTIZED.pop(t.data_ptr(), None)
+    if entry is None:
+        return None
+    q, sf, numel, shape = entry
+    if numel != t.numel() or tuple(shape) != tuple(t.shape):
+        return None
+    return q, sf
+
+
+def clear_prequantized() -> None:
+    _PREQUANTIZED.clear()
+
+
 # ------------------------------------------------------------------------------------ linear
 class QuantizedWeight:
     """The two MXFP8 copies of one weight matrix (N,K): ``W`` along K and ``W^T`` along N."""
@@ -132,7 +168,7 @@ class QuantizedWeight:
 class _MXFP8Linear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, qw: QuantizedWeight):
-        xq, xsf = quantize(x)
+        xq, xsf = take_quantized(x) or quantize(x)
         y = gemm(xq, xsf, qw.q, qw.sf, out_dtype=x.dtype)
         ctx.save_for_backward(x, w)
         ctx.qw = qw
@@ -145,7 +181,7 @@ class _MXFP8Linear(torch.autograd.Function):
         dy = dy.contiguous()
         dx = dw = None
         if ctx.needs_input_grad[0]:
-            dyq, dysf = quantize(dy)
+            dyq, dysf = take_quantized(dy) or quantize(dy)
             dx = gemm(dyq, dysf, qw.qt, qw.sft, out_dtype=x.dtype)
         if ctx.needs_input_grad[1]:
             main_grad = getattr(w, "main_grad", None)

@@ -77,3 +77,84 @@ def test_mxfp8_linear_fwd_bwd_close_to_bf16():
     for got, want, tol in ((yb, ya, 0.06), (xb.grad, ga, 0.06), (lin.weight.grad, gw, 0.02)):
         rel = (got.float() - want.float()).norm() / want.float().norm()
         assert rel < tol, f"relative error {rel}"
+
+
+def test_producer_made_fp8_copies_equal_the_quantise_kernel():
+    """RMSNorm / SwiGLU (forward and backward) writing the MXFP8 copy in the same pass give the same bytes
+    and scales as quantising their stored bf16 output afterwards."""
+    from kohakuwullm_b200.ops import mxfp8 as mx
+    from kohakuwullm_b200.ops.elementwise import rmsnorm, swiglu
+
+    torch.manual_seed(5)
+    rows, cols, H = 512, 1280, 896
+    mx.clear_prequantized()
+    # RMSNorm with fused residual add
+    x = (torch.randn(rows, cols, device="cuda") * 2).bfloat16().requires_grad_()
+    res = torch.randn(rows, cols, device="cuda").bfloat16().requires_grad_()
+    w = torch.rand(cols, device="cuda").requires_grad_()
+    y, h = rmsnorm(x, w, 1e-6, False, res, emit_mx=True, emit_mx_grad=True)
+    got = mx.take_quantized(y.reshape(rows, cols))
+    assert got is not None
+    q_ref, sf_ref = mx.quantize(y.detach().reshape(rows, cols).contiguous())
+    assert torch.equal(got[0], q_ref) and torch.equal(got[1], sf_ref)
+    dy = torch.randn(rows, cols, device="cuda").bfloat16()
+    dh = torch.randn(rows, cols, device="cuda").bfloat16()
+    torch.autograd.backward([y, h], [dy, dh])
+    got = mx.take_quantized(x.grad.reshape(rows, cols))
+    assert got is not None
+    q_ref, sf_ref = mx.quantize(x.grad.reshape(rows, cols).contiguous())
+    assert torch.equal(got[0], q_ref) and torch.equal(got[1], sf_ref)
+    # the gradients themselves are unchanged by the emission
+    x2, r2, w2 = (t.detach().clone().requires_grad_() for t in (x, res, w))
+    y2, h2 = rmsnorm(x2, w2, 1e-6, False, r2)
+    torch.autograd.backward([y2, h2], [dy, dh])
+    assert torch.equal(x2.grad, x.grad) and torch.equal(w2.grad, w.grad)
+    # SwiGLU
+    hh = torch.randn(rows, 2 * H, device="cuda").bfloat16().requires_grad_()
+    a = swiglu(hh, emit_mx=True, emit_mx_grad=True)
+    got = mx.take_quantized(a)
+    q_ref, sf_ref = mx.quantize(a.detach())
+    assert got is not None and torch.equal(got[0], q_ref) and torch.equal(got[1], sf_ref)
+    a.backward(torch.randn(rows, H, device="cuda").bfloat16())
+    got = mx.take_quantized(hh.grad)
+    q_ref, sf_ref = mx.quantize(hh.grad)
+    assert got is not None and torch.equal(got[0], q_ref) and torch.equal(got[1], sf_ref)
+
+
+def test_training_step_identical_with_and_without_fused_quantisation():
+    from kohakuwullm_b200.data.synthetic import make_packs
+    from kohakuwullm_b200.models import LMBackbone, get_preset
+    from kohakuwullm_b200.models.components.norm import RMSNorm
+    from kohakuwullm_b200.ops import native
+    from kohakuwullm_b200.training.engine import TrainEngine
+
+    def run(fused: bool):
+        torch.manual_seed(0)
+        cfg = get_preset("B200-dense-546M", depth=3, vocab_size=4096)
+        with torch.device("cuda"):
+            model = LMBackbone(cfg)
+        flags = 0
+        for m in model.modules():
+            if isinstance(m, RMSNorm):
+                flags += int(m.emit_mx) + int(m.emit_mx_grad)
+                if not fused:
+                    m.emit_mx = m.emit_mx_grad = False
+        assert flags >= 4 * cfg.depth - 1
+        if not fused:
+            from kohakuwullm_b200.ops.elementwise import swiglu
+
+            def plain_forward(mlp):
+                return lambda x: mlp.w_out(swiglu(mlp.w_in(x)))   # no fp8 emission from the activation kernel
+
+            for blk in model.blocks:
+                blk.mlp.forward = plain_forward(blk.mlp)
+        eng = TrainEngine(model, lr=1e-3, param_dtype=torch.bfloat16, cuda_graphs=False)
+        packs = make_packs(2, 1024, 64, 512, cfg.vocab_size, seed=9)
+        outs = [float(eng.step(packs)["loss"]) for _ in range(2)]
+        torch.cuda.synchronize()
+        native.check_status()
+        return outs, torch.cat([g.data.float().reshape(-1) for g in eng.flat.groups.values()])
+
+    (la, pa), (lb, pb) = run(True), run(False)
+    assert la == lb, (la, lb)
+    assert torch.equal(pa, pb)
