@@ -324,3 +324,223 @@ KWU_API int kwu_moe_combine_bwd(const void* rows, const void* dout, int lddo, co
       offsets, E); kwu::count_launch();
   return moe_check("moe_combine_bwd");
 }
+
+// ------------------------------------------------------------------------------------ router backward
+// Gradient of the gate weights with respect to the logits, then the two gate-matrix products, all fp32:
+//   dlogits[t,e]  from d_weight[t,k] through (normalise over the k picks, scale) and the score function
+//                 (sigmoid / sqrt-softplus touch only the picked experts; softmax is dense over E);
+//                 an incoming dense logit gradient (auxiliary / z-loss terms) is added;
+//   dx[t,:]  = dlogits[t,:] W          (T,E) x (E,D)
+//   dW[e,:] += dlogits[:,e]^T x        reduced over tokens with fp32 atomics
+// The contraction sizes (E <= 128) are far too small for tensor-core tiles to matter; these are SIMT tile
+// loops. Reference: src/kohakuwullm/kernels/moe/router.py:197-280 and the two fp32 matmuls at :415-420.
+namespace kwu {
+
+__global__ void __launch_bounds__(256)
+moe_router_dlogits_kernel(const float* __restrict__ logits, const int* __restrict__ idx,
+                          const float* __restrict__ d_weight, const float* __restrict__ dlogits_in,
+                          float* __restrict__ dlogits, int T, int E, int top_k, int score_fn, int norm_topk,
+                          float scaling) {
+  const int lane = threadIdx.x & 31;
+  const int wpb = blockDim.x >> 5;
+  for (int t = blockIdx.x * wpb + (threadIdx.x >> 5); t < T; t += gridDim.x * wpb) {
+    const float* lg = logits + static_cast<size_t>(t) * E;
+    float* out = dlogits + static_cast<size_t>(t) * E;
+    // scores of this lane's experts (lane, lane+32, ...) and, for softmax, the row statistics
+    float sc[4];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int e = lane + 32 * j;
+      sc[j] = e < E ? lg[e] : -INFINITY;
+      mx = fmaxf(mx, sc[j]);
+    }
+    if (score_fn == SCORE_SOFTMAX) {
+      mx = warp_max(mx);
+      float sum = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        sc[j] = (lane + 32 * j < E) ? __expf(sc[j] - mx) : 0.f;
+        sum += sc[j];
+      }
+      sum = warp_sum(sum);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) sc[j] /= sum;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float l = sc[j];
+        if (lane + 32 * j >= E) { sc[j] = 0.f; continue; }
+        sc[j] = (score_fn == SCORE_SIGMOID) ? 1.f / (1.f + __expf(-l)) : sqrtf(l > 20.f ? l : log1pf(__expf(l)));
+      }
+    }
+    // lane k (< top_k) owns pick k: its expert, unbiased score and incoming gradient
+    int my_e = -1;
+    float my_s = 0.f, my_g = 0.f;
+    if (lane < top_k) {
+      my_e = idx[static_cast<size_t>(t) * top_k + lane];
+      my_g = d_weight[static_cast<size_t>(t) * top_k + lane];
+    }
+    for (int k = 0; k < top_k; ++k) {
+      const int e = __shfl_sync(0xffffffffu, my_e, k);
+      const int owner = e & 31, slot = e >> 5;
+      float s = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (j == slot) s = sc[j];
+      s = __shfl_sync(0xffffffffu, s, owner);
+      if (lane == k) my_s = s;
+    }
+    // d(weight)/d(score) over the picks
+    float ssum = warp_sum(lane < top_k ? my_s : 0.f);
+    float gs = warp_sum(lane < top_k ? my_g * my_s : 0.f);
+    float ds_pick = 0.f;
+    if (lane < top_k) {
+      if (norm_topk) {
+        const float S = ssum + 1e-20f;
+        ds_pick = scaling * (my_g / S - gs / (S * S));
+      } else {
+        ds_pick = scaling * my_g;
+      }
+    }
+    // scatter the pick gradients onto this lane's experts
+    float ds[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int k = 0; k < top_k; ++k) {
+      const int e = __shfl_sync(0xffffffffu, my_e, k);
+      const float d = __shfl_sync(0xffffffffu, ds_pick, k);
+      if ((e & 31) == lane) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (j == (e >> 5)) ds[j] += d;
+      }
+    }
+    float dot = 0.f;
+    if (score_fn == SCORE_SOFTMAX) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) dot += ds[j] * sc[j];
+      dot = warp_sum(dot);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int e = lane + 32 * j;
+      if (e >= E) continue;
+      float dl;
+      if (score_fn == SCORE_SOFTMAX) {
+        dl = sc[j] * (ds[j] - dot);
+      } else if (score_fn == SCORE_SIGMOID) {
+        dl = ds[j] * sc[j] * (1.f - sc[j]);
+      } else {  // s = sqrt(softplus(l)): ds/dl = sigmoid(l) / (2 s)
+        const float sg = 1.f / (1.f + __expf(-lg[e]));
+        dl = sc[j] > 0.f ? ds[j] * sg / (2.f * sc[j]) : 0.f;
+      }
+      if (dlogits_in) dl += dlogits_in[static_cast<size_t>(t) * E + e];
+      out[e] = dl;
+    }
+  }
+}
+
+constexpr int RB_BT = 32, RB_BD = 128, RB_BE = 32;
+
+// dx[t, d] = sum_e dl[t, e] W[e, d]; block = 32 tokens x 128 columns, thread = 1 token-row slice of 16 columns
+__global__ void __launch_bounds__(256)
+moe_router_dx_kernel(const float* __restrict__ dl, const float* __restrict__ W, __nv_bfloat16* __restrict__ dx,
+                     int lddx, int T, int D, int E) {
+  __shared__ float s_dl[RB_BT][RB_BE + 1];
+  __shared__ float s_w[RB_BE][RB_BD + 1];
+  const int t0 = blockIdx.x * RB_BT, d0 = blockIdx.y * RB_BD;
+  const int ty = threadIdx.x >> 3, tx = threadIdx.x & 7;  // 32 token rows x 8 column lanes (16 columns each, stride 8)
+  float acc[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+  for (int e0 = 0; e0 < E; e0 += RB_BE) {
+    for (int i = threadIdx.x; i < RB_BT * RB_BE; i += 256) {
+      const int r = i / RB_BE, c = i % RB_BE;
+      s_dl[r][c] = (t0 + r < T && e0 + c < E) ? dl[static_cast<size_t>(t0 + r) * E + e0 + c] : 0.f;
+    }
+    for (int i = threadIdx.x; i < RB_BE * RB_BD; i += 256) {
+      const int r = i / RB_BD, c = i % RB_BD;
+      s_w[r][c] = (e0 + r < E && d0 + c < D) ? W[static_cast<size_t>(e0 + r) * D + d0 + c] : 0.f;
+    }
+    __syncthreads();
+#pragma unroll 4
+    for (int e = 0; e < RB_BE; ++e) {
+      const float a = s_dl[ty][e];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) acc[j] += a * s_w[e][tx + 8 * j];
+    }
+    __syncthreads();
+  }
+  const int t = t0 + ty;
+  if (t < T)
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const int d = d0 + tx + 8 * j;
+      if (d < D) dx[static_cast<size_t>(t) * lddx + d] = __float2bfloat16(acc[j]);
+    }
+}
+
+constexpr int RW_BT = 64, RW_BD = 64;
+
+// dW[e, d] += sum_{t in chunk} dl[t, e] x[t, d]; block = one 64-column slab and a strided set of 64-token chunks
+__global__ void __launch_bounds__(256)
+moe_router_dw_kernel(const float* __restrict__ dl, const __nv_bfloat16* __restrict__ x, int ldx,
+                     float* __restrict__ dW, int T, int D, int E) {
+  __shared__ float s_dl[RW_BT][RT_MAXE + 1];
+  __shared__ float s_x[RW_BT][RW_BD + 1];
+  const int d0 = blockIdx.x * RW_BD;
+  // thread -> column tx (0..63) and expert lanes ey, ey + 4, ... (E / 4 experts each)
+  const int tx = threadIdx.x & 63, ey = threadIdx.x >> 6;
+  float acc[RT_MAXE / 4];
+#pragma unroll
+  for (int j = 0; j < RT_MAXE / 4; ++j) acc[j] = 0.f;
+  for (int t0 = blockIdx.y * RW_BT; t0 < T; t0 += gridDim.y * RW_BT) {
+    for (int i = threadIdx.x; i < RW_BT * E; i += 256) {
+      const int r = i / E, c = i % E;
+      s_dl[r][c] = (t0 + r < T) ? dl[static_cast<size_t>(t0 + r) * E + c] : 0.f;
+    }
+    for (int i = threadIdx.x; i < RW_BT * RW_BD; i += 256) {
+      const int r = i / RW_BD, c = i % RW_BD;
+      s_x[r][c] = (t0 + r < T && d0 + c < D) ? __bfloat162float(x[static_cast<size_t>(t0 + r) * ldx + d0 + c]) : 0.f;
+    }
+    __syncthreads();
+    for (int r = 0; r < RW_BT; ++r) {
+      const float xv = s_x[r][tx];
+#pragma unroll
+      for (int j = 0; j < RT_MAXE / 4; ++j)
+        if (ey + 4 * j < E) acc[j] += s_dl[r][ey + 4 * j] * xv;
+    }
+    __syncthreads();
+  }
+  if (d0 + tx < D)
+#pragma unroll
+    for (int j = 0; j < RT_MAXE / 4; ++j)
+      if (ey + 4 * j < E) atomicAdd(&dW[static_cast<size_t>(ey + 4 * j) * D + d0 + tx], acc[j]);
+}
+
+}  // namespace kwu
+
+// dlogits: (T,E) fp32 scratch/output. dx (T,D) bf16 or null. dW (E,D) fp32, ACCUMULATED into (zero it first
+// for a plain gradient), or null.
+KWU_API int kwu_moe_router_bwd(const float* logits, const int* idx, const float* d_weight, const float* dlogits_in,
+                               float* dlogits, const void* x, int ldx, const float* W, void* dx, int lddx, float* dW,
+                               int T, int D, int E, int top_k, int score_fn, int norm_topk, float scaling,
+                               void* stream) {
+  if (E > RT_MAXE || top_k > 32) { set_last_error("moe_router_bwd: need E <= 128 and k <= 32"); return 7; }
+  if (T <= 0) return 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  int grid = (T + 7) / 8;
+  if (grid > 148 * 8) grid = 148 * 8;
+  moe_router_dlogits_kernel<<<grid, 256, 0, st>>>(logits, idx, d_weight, dlogits_in, dlogits, T, E, top_k, score_fn,
+                                                 norm_topk, scaling); kwu::count_launch();
+  if (dx) {
+    dim3 g((T + RB_BT - 1) / RB_BT, (D + RB_BD - 1) / RB_BD);
+    moe_router_dx_kernel<<<g, 256, 0, st>>>(dlogits, W, (__nv_bfloat16*)dx, lddx, T, D, E); kwu::count_launch();
+  }
+  if (dW) {
+    int chunks = (T + RW_BT - 1) / RW_BT;
+    if (chunks > 64) chunks = 64;
+    dim3 g((D + RW_BD - 1) / RW_BD, chunks);
+    moe_router_dw_kernel<<<g, 256, 0, st>>>(dlogits, (const __nv_bfloat16*)x, ldx, dW, T, D, E); kwu::count_launch();
+  }
+  return moe_check("moe_router_bwd");
+}

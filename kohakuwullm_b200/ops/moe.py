@@ -63,9 +63,10 @@ def native_supported(x, w_in) -> bool:
 
 # ------------------------------------------------------------------------------------ router
 class _RouterTopK(torch.autograd.Function):
-    """Fused gate GEMM + score + biased top-k + histogram. Backward re-derives the (tiny) score /
-    normalisation gradient from the saved logits with PyTorch ops and forms the two gate-matrix products
-    in fp32."""
+    """Fused gate GEMM + score + biased top-k + histogram. Backward: one kernel turns the gate-weight
+    gradient into logit gradients (normalisation, scaling, score function; dense auxiliary-loss logit
+    gradients are added), two fp32 tile kernels form ``dx = dl W`` and ``dW += dl^T x`` (straight into
+    ``main_grad`` when the trainer provides it)."""
 
     @staticmethod
     def forward(ctx, x, W, bias, load_accum, top_k, score, norm_topk, scaling):
@@ -88,25 +89,30 @@ class _RouterTopK(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, _didx, dweight, _dcounts, dlogits_in):
+        L = native.require()
         x, W, logits, idx = ctx.saved_tensors
         score, norm_topk, scaling = ctx.cfg
-        with torch.enable_grad():
-            lg = logits.detach().requires_grad_()
-            if score == "sigmoid":
-                s = torch.sigmoid(lg)
-            elif score == "softmax":
-                s = torch.softmax(lg, -1)
-            else:
-                s = torch.sqrt(torch.nn.functional.softplus(lg))
-            w = s.gather(1, idx.long())
-            if norm_topk:
-                w = w / (w.sum(-1, keepdim=True) + 1e-20)
-            w = w * scaling
-            (dl,) = torch.autograd.grad(w, lg, dweight)
-        if dlogits_in is not None:
-            dl = dl + dlogits_in
-        dx = (dl @ W.float()).to(x.dtype) if ctx.needs_input_grad[0] else None
-        dW = (dl.t() @ x.float()).to(W.dtype) if ctx.needs_input_grad[1] else None
+        T, D = x.shape
+        E = W.shape[0]
+        k = idx.shape[1]
+        dl = torch.empty(T, E, dtype=torch.float32, device=x.device)
+        dw_in = dweight.float().contiguous() if dweight is not None else torch.zeros(T, k, dtype=torch.float32, device=x.device)
+        dl_in = dlogits_in.float().contiguous() if dlogits_in is not None else None
+        need_dx, need_dW = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        dx = torch.empty(T, D, dtype=x.dtype, device=x.device) if need_dx else None
+        dW32 = None
+        if need_dW:
+            main_grad = getattr(W, "main_grad", None)
+            dW32 = main_grad if (main_grad is not None and main_grad.dtype == torch.float32) else \
+                torch.zeros(E, D, dtype=torch.float32, device=x.device)
+        rc = L.kwu_moe_router_bwd(native.ptr(logits), native.ptr(idx), native.ptr(dw_in), native.ptr(dl_in), native.ptr(dl),
+                                  native.ptr(x), c_int(x.stride(0)), native.ptr(W), native.ptr(dx), c_int(D),
+                                  native.ptr(dW32), c_int(T), c_int(D), c_int(E), c_int(k), c_int(SCORE_IDS[score]),
+                                  c_int(int(norm_topk)), c_float(scaling), native.stream_ptr())
+        native.check(rc, "moe_router_bwd")
+        dW = None
+        if need_dW and dW32 is not getattr(W, "main_grad", None):
+            dW = dW32.to(W.dtype)
         return dx, dW, None, None, None, None, None, None
 
 

@@ -29,6 +29,7 @@ from kohakuwullm_b200.parallel.ddp import GradSync
 from kohakuwullm_b200.parallel.flat import FlatParameters
 from kohakuwullm_b200.training.optim.fused_adamw import FlatAdamW
 from kohakuwullm_b200.training.optim.lowbit import cast_parameters_
+from kohakuwullm_b200.utils import nvtx
 
 
 class GraphedMicroStep:
@@ -252,20 +253,22 @@ class TrainEngine:
         ce_total = torch.zeros((), dtype=torch.float32, device=dev)
         loss_total = torch.zeros((), dtype=torch.float32, device=dev)
         extra: dict[str, torch.Tensor] = {}
-        for mb in micro_batches:
+        for i, mb in enumerate(micro_batches):
             graph = self._graph_for(mb)
             if graph is not None:
-                graph.load(mb)
-                graph.replay()
+                with nvtx.range(f"micro_step_{i}/graph"):
+                    graph.load(mb)
+                    graph.replay()
                 ce_total = ce_total + graph.ce
                 loss_total = loss_total + graph.total
                 for k, v in graph.extra.items():
                     extra[k] = extra.get(k, 0) + v
                 continue
-            mb = mb.to(dev, non_blocking=True)
-            loss, logs = model.loss(mb.tokens, mb.labels, mb.seq_info, reduction="sum",
-                                    router_scale=self._router_scale)
-            loss.backward()
+            with nvtx.range(f"micro_step_{i}/eager"):
+                mb = mb.to(dev, non_blocking=True)
+                loss, logs = model.loss(mb.tokens, mb.labels, mb.seq_info, reduction="sum",
+                                        router_scale=self._router_scale)
+                loss.backward()
             ce_total = ce_total + logs["ce"]
             loss_total = loss_total + loss.detach().float()
             for k in ("z_loss", "router_loss"):
@@ -275,16 +278,21 @@ class TrainEngine:
             self.optimizer.param_groups[0]["lr"] = self.lr_schedule(self.global_step)
         if self.fused_sync:
             # one fused pass: reduce-scatter + scaling + clipping + sharded AdamW + all-gather
-            self.sync.step(self.optimizer, inv_tokens.reshape(1), self.max_grad_norm)
+            with nvtx.range("grad_sync+optimizer/fused"):
+                self.sync.step(self.optimizer, inv_tokens.reshape(1), self.max_grad_norm)
             self._norm = self.sync.norm
             if self.has_mxfp8:
-                model.refresh_mxfp8()
+                with nvtx.range("mxfp8_refresh"):
+                    model.refresh_mxfp8()
         elif local_tokens > 0 or self.world > 1:
-            self.sync.reduce()
-            self._grad_norm_and_coef(inv_tokens)
-            self.optimizer.step(grad_scale=self._coef, zero_grad=True)
+            with nvtx.range("grad_sync"):
+                self.sync.reduce()
+            with nvtx.range("clip+optimizer"):
+                self._grad_norm_and_coef(inv_tokens)
+                self.optimizer.step(grad_scale=self._coef, zero_grad=True)
             if self.has_mxfp8:
-                model.refresh_mxfp8()
+                with nvtx.range("mxfp8_refresh"):
+                    model.refresh_mxfp8()
         else:
             self.flat.zero_grad()  # an all-masked step updates nothing
         if self.has_router:

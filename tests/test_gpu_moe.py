@@ -146,3 +146,33 @@ def test_routed_experts_mxfp8_close_to_bf16():
     for name, a, b in zip(("y", "dx", "dgate", "dw_in", "dw_out"), got, ref):
         rel = ((a - b).norm() / b.norm().clamp(min=1e-9)).item()
         assert rel < 0.08, f"{name}: relative error {rel}"
+
+
+@pytest.mark.parametrize("score", ["sigmoid", "softmax", "sqrtsoftplus"])
+@pytest.mark.parametrize("norm_topk", [True, False])
+def test_router_backward_matches_eager(score, norm_topk):
+    """Gate-weight gradient -> logits -> (dx, dW) through the native backward kernels, against autograd over
+    the eager fp32 router on the same bf16 values; the router z-loss exercises the dense logit-gradient input."""
+    from kohakuwullm_b200.models.components.moe import TopKRouter
+
+    torch.manual_seed(0)
+    T, D, E, k = 777, 256, 64, 6
+    r = TopKRouter(D, E, k, score=score, norm_topk_prob=norm_topk, routed_scaling_factor=1.7, z_loss_weight=1e-2).cuda()
+    torch.nn.init.normal_(r.weight, std=0.3)
+    r.train()
+    x = torch.randn(T, D, device="cuda", dtype=torch.bfloat16)
+    coef = torch.randn(T, k, device="cuda")
+
+    def run(inp):
+        r.weight.grad = None
+        xs = inp.clone().requires_grad_()
+        idx, w, _ = r.route(xs)
+        order = idx.long().argsort(-1)                     # slot order may differ between the two paths
+        loss = (w.gather(1, order) * coef).sum() + r.aux_loss * T
+        loss.backward()
+        return xs.grad.float(), r.weight.grad.float().clone()
+
+    dx_n, dW_n = run(x)
+    dx_e, dW_e = run(x.float())
+    torch.testing.assert_close(dW_n, dW_e, rtol=2e-3, atol=2e-3 * dW_e.abs().max().item())
+    torch.testing.assert_close(dx_n, dx_e, rtol=2e-2, atol=2e-2 * dx_e.abs().max().item())

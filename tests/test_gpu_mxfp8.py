@@ -99,10 +99,16 @@ def test_producer_made_fp8_copies_equal_the_quantise_kernel():
     assert torch.equal(got[0], q_ref) and torch.equal(got[1], sf_ref)
     dy = torch.randn(rows, cols, device="cuda").bfloat16()
     dh = torch.randn(rows, cols, device="cuda").bfloat16()
+    # the consumer (a projection's backward) receives the gradient tensor itself, not a leaf's accumulated copy
+    seen = {}
+    y, h = rmsnorm(x * 1.0, w, 1e-6, False, res, emit_mx=True, emit_mx_grad=True)
+    mx.take_quantized(y.reshape(rows, cols))
+    y.grad_fn.next_functions[0][0].register_prehook(lambda grads: seen.update(g=grads[0]))
     torch.autograd.backward([y, h], [dy, dh])
-    got = mx.take_quantized(x.grad.reshape(rows, cols))
+    g = seen["g"].reshape(rows, cols)
+    got = mx.take_quantized(g)
     assert got is not None
-    q_ref, sf_ref = mx.quantize(x.grad.reshape(rows, cols).contiguous())
+    q_ref, sf_ref = mx.quantize(g.contiguous())
     assert torch.equal(got[0], q_ref) and torch.equal(got[1], sf_ref)
     # the gradients themselves are unchanged by the emission
     x2, r2, w2 = (t.detach().clone().requires_grad_() for t in (x, res, w))
@@ -115,9 +121,12 @@ def test_producer_made_fp8_copies_equal_the_quantise_kernel():
     got = mx.take_quantized(a)
     q_ref, sf_ref = mx.quantize(a.detach())
     assert got is not None and torch.equal(got[0], q_ref) and torch.equal(got[1], sf_ref)
+    a = swiglu(hh * 1.0, emit_mx=True, emit_mx_grad=True)
+    mx.take_quantized(a)
+    a.grad_fn.next_functions[0][0].register_prehook(lambda grads: seen.update(gh=grads[0]))
     a.backward(torch.randn(rows, H, device="cuda").bfloat16())
-    got = mx.take_quantized(hh.grad)
-    q_ref, sf_ref = mx.quantize(hh.grad)
+    got = mx.take_quantized(seen["gh"])
+    q_ref, sf_ref = mx.quantize(seen["gh"].contiguous())
     assert got is not None and torch.equal(got[0], q_ref) and torch.equal(got[1], sf_ref)
 
 
