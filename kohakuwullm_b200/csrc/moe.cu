@@ -479,7 +479,7 @@ moe_router_dx_kernel(const float* __restrict__ dl, const float* __restrict__ W, 
     }
 }
 
-constexpr int RW_BT = 64, RW_BD = 64;
+constexpr int RW_BT = 32, RW_BD = 64;
 
 // dW[e, d] += sum_{t in chunk} dl[t, e] x[t, d]; block = one 64-column slab and a strided set of 64-token chunks
 __global__ void __launch_bounds__(256)

@@ -503,3 +503,103 @@ KWU_API int kwu_gemm_mxfp8(const void* A, const void* sfa, const void* B, const 
   return launch_mx<128>(A, B, C, M, N, K, lda, ldb, ldc, (const uint8_t*)sfa, (const uint8_t*)sfb, out_fp32,
                         accumulate, alpha, reinterpret_cast<cudaStream_t>(stream), status);
 }
+
+// ------------------------------------------------------------------------------------ attention operands
+// Per-head MXFP8 quantisation of q / k for attention (head_dim 64 = two 32-blocks per (token, head) row):
+//   mxfp8_column_mean   mu[h, d] = mean over the T tokens of the pack of x[t, h, d]  (key smoothing: scores
+//                       change by q . mu, a constant along the key axis, which softmax ignores)
+//   mxfp8_quant_heads   x[t, h, :] (- mu[h, :]) -> e4m3 bytes + two UE8M0 scale bytes per row, and the
+//                       dequantised bf16 copy (e4m3 x 2^e is exact in bf16) that the attention kernels read.
+// Reference: src/kohakuwullm/kernels/mxfp8/attention_quant.py:17-78.
+namespace kwu {
+
+__global__ void __launch_bounds__(256)
+mxfp8_column_mean_kernel(const __nv_bfloat16* __restrict__ x, long long ld_t, int T, int H, float* __restrict__ mu) {
+  // block = one head; thread = (channel d = tid % 64, token lane = tid / 64)
+  __shared__ float s_part[4][64];
+  const int h = blockIdx.x, d = threadIdx.x & 63, tl = threadIdx.x >> 6;
+  float acc = 0.f;
+  for (int t = tl; t < T; t += 4) acc += __bfloat162float(x[static_cast<size_t>(t) * ld_t + h * 64 + d]);
+  s_part[tl][d] = acc;
+  __syncthreads();
+  if (tl == 0) mu[h * 64 + d] = (s_part[0][d] + s_part[1][d] + s_part[2][d] + s_part[3][d]) / static_cast<float>(T);
+}
+
+// One lane = 8 channels; 8 lanes = one (token, head) row; a warp covers 4 rows.
+__global__ void __launch_bounds__(256)
+mxfp8_quant_heads_kernel(const __nv_bfloat16* __restrict__ x, long long ld_t, const float* __restrict__ mu,
+                         uint8_t* __restrict__ q8, uint8_t* __restrict__ sf, __nv_bfloat16* __restrict__ deq,
+                         long long rows, int H) {
+  const int lane = threadIdx.x & 31;
+  const long long wid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long r0 = wid * 4; r0 < rows; r0 += nwarps * 4) {
+    const long long row = r0 + (lane >> 3);
+    const int c = (lane & 7) * 8;
+    const bool in = row < rows;
+    const long long t = in ? row / H : 0;
+    const int h = in ? static_cast<int>(row % H) : 0;
+    float f[8];
+    if (in) {
+      const uint4 a = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * ld_t + h * 64 + c);
+      unpack8(a, f);
+      if (mu) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] -= mu[h * 64 + c + e];
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = 0.f;
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    if (!in) continue;
+    const uint32_t e8 = ue8m0_from_amax(amax);
+    const float inv = inv_scale_from_ue8m0(e8);
+    const float scale = __uint_as_float(e8 << 23);  // 2^(e8 - 127); e8 >= 1 here because amax >= 1e-30
+    uint32_t lo = 0, hi = 0;
+    float d[8];
+#pragma unroll
+    for (int e = 0; e < 8; e += 2) {
+      const __nv_fp8x2_storage_t p2 = __nv_cvt_float2_to_fp8x2(make_float2(f[e] * inv, f[e + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+      const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(p2, __NV_E4M3);
+      const float2 back = __half22float2(*reinterpret_cast<const __half2*>(&hr));
+      d[e] = back.x * scale;
+      d[e + 1] = back.y * scale;
+      if (e < 4) lo |= static_cast<uint32_t>(p2) << (8 * e);
+      else hi |= static_cast<uint32_t>(p2) << (8 * (e - 4));
+    }
+    if (q8) *reinterpret_cast<uint2*>(q8 + static_cast<size_t>(row) * 64 + c) = make_uint2(lo, hi);
+    if (sf && (lane & 3) == 0) sf[static_cast<size_t>(row) * 2 + (c >> 5)] = static_cast<uint8_t>(e8);
+    *reinterpret_cast<uint4*>(deq + static_cast<size_t>(row) * 64 + c) =
+        make_uint4(pack_bf16(d[0], d[1]), pack_bf16(d[2], d[3]), pack_bf16(d[4], d[5]), pack_bf16(d[6], d[7]));
+  }
+}
+
+}  // namespace kwu
+
+// x: (T, H, 64) bf16 view with token pitch ld_t elements (heads contiguous). mu: (H, 64) fp32 out.
+KWU_API int kwu_mxfp8_column_mean(const void* x, long long ld_t, int T, int H, float* mu, void* stream) {
+  if (T <= 0 || H <= 0) return 0;
+  mxfp8_column_mean_kernel<<<H, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>((const __nv_bfloat16*)x, ld_t, T, H, mu); kwu::count_launch();
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { set_last_error("mxfp8_column_mean launch: %s", cudaGetErrorString(e)); return 11; }
+  return 0;
+}
+
+// q8 (T,H,64) bytes and sf (T,H,2) bytes are optional; deq (T,H,64) bf16 contiguous is always written.
+KWU_API int kwu_mxfp8_quant_heads(const void* x, long long ld_t, const float* mu, void* q8, void* sf, void* deq, int T,
+                                  int H, void* stream) {
+  if (T <= 0 || H <= 0) return 0;
+  const long long rows = static_cast<long long>(T) * H;
+  long long grid = (rows + 31) / 32;
+  if (grid > 148 * 16) grid = 148 * 16;
+  mxfp8_quant_heads_kernel<<<static_cast<int>(grid), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      (const __nv_bfloat16*)x, ld_t, mu, (uint8_t*)q8, (uint8_t*)sf, (__nv_bfloat16*)deq, rows, H); kwu::count_launch();
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { set_last_error("mxfp8_quant_heads launch: %s", cudaGetErrorString(e)); return 11; }
+  return 0;
+}

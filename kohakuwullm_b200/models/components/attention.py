@@ -152,7 +152,32 @@ class SDPAAttention(Attention):
         return self._forward_padded(x, seq_info, rope, cache, layer)
 
 
+class MXFP8Attention(Attention):
+    """Attention whose score product sees MXFP8 operands: q and k are quantised per head (e4m3, one
+    power-of-two scale per 32 channels; k after subtracting its per-channel mean over the pack, which the
+    softmax cannot see) before ``QK^T``; ``PV`` and every gradient product stay 16-bit, and gradients pass
+    straight through the quantisation. e4m3 values times a power of two are exact in bf16, so the flash
+    kernels read the dequantised operands and produce exactly the block-scaled product (fp32 accumulate);
+    with head_dim 64 these kernels are bound by the softmax arithmetic, not by the tensor pipe, so an fp8
+    MMA for the score tile would not make them faster. Reference:
+    src/kohakuwullm/kernels/mxfp8/attention.py:30-267, attention_quant.py:17-78."""
+
+    backend = "mxfp8"
+
+    def forward(self, x, seq_info, rope=None, cache=None, layer: int = 0, plan=None):
+        if seq_info.packed and cache is None:
+            T = x.shape[0]
+            q, k, v = self._project(x, rope)
+            q = attn_ops.quantize_heads(q, smooth=False)
+            k = attn_ops.quantize_heads(k, smooth=True)
+            out = varlen_attention(q, k, v, seq_info.cu_seqlens, seq_info.max_seqlen, window=self.window,
+                                   sink_lse=self._sink_lse(), scale=self.scale, plan=plan)
+            return self.o_proj(out.reshape(T, self.q_dim))
+        return self._forward_padded(x, seq_info, rope, cache, layer)
+
+
 ATTENTION.register("flash", Attention)
+ATTENTION.register("mxfp8", MXFP8Attention)
 # backend names of the reference resolve to the one native implementation
 for _alias in ("varlen", "triton", "native"):
     ATTENTION.register(_alias, Attention)

@@ -295,3 +295,65 @@ def decode_attention(q, k_cache, v_cache, kv_len: int, window: int | None = None
         native.stream_ptr())
     native.check(rc, "decode_attention")
     return (out, lse) if return_lse else out
+
+
+# ------------------------------------------------------------------------------------ MXFP8 operands
+def quantize_heads_reference(x: torch.Tensor, smooth: bool = False) -> torch.Tensor:
+    """(T,H,64) -> the values an MXFP8 (e4m3, one UE8M0 scale per 32 channels) copy of x holds, as x.dtype.
+    ``smooth`` subtracts the per-(head, channel) mean over the T tokens first."""
+    from kohakuwullm_b200.ops.mxfp8 import dequantize, quantize_reference
+
+    T, H, D = x.shape
+    xf = x.float()
+    if smooth:
+        xf = xf - xf.mean(0, keepdim=True)
+    q, e = quantize_reference(xf.reshape(T * H, D))
+    return dequantize(q, e).view(T, H, D).to(x.dtype)
+
+
+class _QuantizeHeads(torch.autograd.Function):
+    """Per-head MXFP8 quantisation of an attention operand, returned as the exactly representable bf16
+    values (``csrc/mxfp8.cu``: ``mxfp8_quant_heads``). Backward is straight-through; with ``smooth`` the
+    gradient's own token mean is removed, as the mean subtraction requires."""
+
+    @staticmethod
+    def forward(ctx, x, smooth):
+        L = native.require()
+        T, H, D = x.shape
+        if x.stride(2) != 1 or x.stride(1) != D:
+            x = x.contiguous()
+        mu = None
+        if smooth:
+            mu = torch.empty(H, D, dtype=torch.float32, device=x.device)
+            rc = L.kwu_mxfp8_column_mean(native.ptr(x), ctypes.c_longlong(x.stride(0)), ctypes.c_int(T), ctypes.c_int(H),
+                                         native.ptr(mu), native.stream_ptr())
+            native.check(rc, "mxfp8_column_mean")
+        out = torch.empty(T, H, D, dtype=x.dtype, device=x.device)
+        rc = L.kwu_mxfp8_quant_heads(native.ptr(x), ctypes.c_longlong(x.stride(0)), native.ptr(mu), native.ptr(None),
+                                     native.ptr(None), native.ptr(out), ctypes.c_int(T), ctypes.c_int(H),
+                                     native.stream_ptr())
+        native.check(rc, "mxfp8_quant_heads")
+        ctx.smooth = smooth
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        if not ctx.smooth:
+            return dy, None
+        L = native.require()
+        dy = dy.contiguous()
+        T, H, D = dy.shape
+        mu = torch.empty(H, D, dtype=torch.float32, device=dy.device)
+        rc = L.kwu_mxfp8_column_mean(native.ptr(dy), ctypes.c_longlong(dy.stride(0)), ctypes.c_int(T), ctypes.c_int(H),
+                                     native.ptr(mu), native.stream_ptr())
+        native.check(rc, "mxfp8_column_mean")
+        return (dy.float() - mu[None]).to(dy.dtype), None
+
+
+def quantize_heads(x: torch.Tensor, smooth: bool = False) -> torch.Tensor:
+    """MXFP8 round trip of a (T,H,64) attention operand (native on bf16 CUDA input, PyTorch elsewhere)."""
+    if native.available() and x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] == 64:
+        return _QuantizeHeads.apply(x, smooth)
+    return x + (quantize_heads_reference(x, smooth) - x).detach() if not smooth else \
+        (x - x.float().mean(0, keepdim=True).to(x.dtype)) + \
+        (quantize_heads_reference(x, True) - (x - x.float().mean(0, keepdim=True).to(x.dtype))).detach()
