@@ -114,7 +114,8 @@ def test_producer_made_fp8_copies_equal_the_quantise_kernel():
     x2, r2, w2 = (t.detach().clone().requires_grad_() for t in (x, res, w))
     y2, h2 = rmsnorm(x2, w2, 1e-6, False, r2)
     torch.autograd.backward([y2, h2], [dy, dh])
-    assert torch.equal(x2.grad, x.grad) and torch.equal(w2.grad, w.grad)
+    assert torch.equal(x2.grad, x.grad)
+    torch.testing.assert_close(w2.grad, w.grad, rtol=1e-5, atol=1e-4)   # block partials meet in fp32 atomics
     # SwiGLU
     hh = torch.randn(rows, 2 * H, device="cuda").bfloat16().requires_grad_()
     a = swiglu(hh, emit_mx=True, emit_mx_grad=True)
