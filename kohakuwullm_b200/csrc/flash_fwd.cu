@@ -1,10 +1,10 @@
 // Varlen causal / sliding-window flash attention forward for head_dim 64, bf16, on tcgen05.
 //
-// One CTA per (128-row query tile, query head). Roles:
-//   warps 0..3  softmax: thread r owns query row r; reads S from TMEM, online softmax in fp32,
-//               writes P (bf16) back to TMEM, rescales the O accumulator when the row max moves
-//   warp 4      TMA producer: Q once, then K and V tiles through two-stage rings
-//   warp 5      issues tcgen05.mma:  S = Q K^T (smem x smem)  and  O += P V (TMEM x smem)
+// Persistent CTAs (two per SM) walk a heaviest-first list of (128-row query tile, query head) items. Roles:
+//   warps 0..7  softmax: two threads per query row (64 key columns each); read S from TMEM, online
+//               softmax in fp32, write P (bf16) back to TMEM, rescale the O accumulator when the max moves
+//   warp 8      TMA producer: Q per item, K and V tiles through two-stage rings (runs ahead into the next item)
+//   warp 9      issues tcgen05.mma:  S = Q K^T (smem x smem)  and  O += P V (TMEM x smem)
 // TMEM columns: S [0,128) fp32, P [128,192) packed bf16, O [192,256) fp32. Two CTAs fit per SM, so
 // one CTA's softmax overlaps the other's tensor-core work.
 //
@@ -59,16 +59,31 @@ __global__ void attn_plan_kernel(const int* __restrict__ cu, int ndocs, int tile
   for (int i = used + threadIdx.x; i < max_tiles; i += blockDim.x) plan[i] = make_int4(0, 0, 0, 0);
 }
 
+// Work item = (query tile, query head). A CTA walks items blockIdx.x, blockIdx.x + gridDim.x, ... of the
+// heaviest-first list, so TMEM allocation, barrier set-up and the tensor-map fetch are paid once per CTA,
+// and the producer warp is already loading the next item's Q and K while the softmax warps finish the
+// current one. Barrier phases run on counters that continue across items.
+struct FwdItem {
+  int q0, ds, de, h, hk, lo, n_kv, q_hi;
+};
+
+__device__ __forceinline__ bool fwd_decode(const FlashFwdParams& p, int item, FwdItem& it) {
+  const int tile = p.n_tiles - 1 - item / p.Hq;   // later query tiles of a document see more keys: first
+  const int4 job = p.plan[tile];
+  if (!job.w) return false;
+  it.q0 = job.x; it.ds = job.y; it.de = job.z;
+  it.h = item % p.Hq;
+  it.hk = it.h / (p.Hq / p.Hkv);
+  it.q_hi = min(it.q0 + FA_BM, it.de);            // one past the last valid query row
+  it.lo = it.ds;
+  if (p.window > 0) it.lo = max(it.ds, it.q0 - p.window + 1);
+  it.n_kv = (it.q_hi - it.lo + FA_BN - 1) / FA_BN;
+  return it.n_kv > 0;
+}
+
 __global__ void __launch_bounds__(FA_THREADS, 2)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const FlashFwdParams p) {
-  // later query tiles of a document see more keys: schedule them first
-  const int4 job = p.plan[p.n_tiles - 1 - blockIdx.x];
-  if (!job.w) return;
-  const int q0 = job.x, ds = job.y, de = job.z;
-  const int h = blockIdx.y;
-  const int hk = h / (p.Hq / p.Hkv);
-
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -84,18 +99,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* s_full = bars + 9;
   uint64_t* p_full = bars + 10;
   uint64_t* o_done = bars + 11;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* q_empty = bars + 12;  // the item's last S product has read Q
+  uint64_t* o_free = bars + 13;   // the softmax warps have read the item's O accumulator
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* s_rowmax = reinterpret_cast<float*>(smem + 5 * FA_TILE_BYTES + 1024);  // 2 x 256 max + 256 sums
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-
-  // key range of this tile
-  const int q_hi = min(q0 + FA_BM, de);           // one past the last valid query row
-  int lo = ds;
-  if (p.window > 0) lo = max(ds, q0 - p.window + 1);
-  const int n_kv = (q_hi - lo + FA_BN - 1) / FA_BN;
+  const int n_items = p.n_tiles * p.Hq;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -108,6 +120,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     mbar_init(s_full, 1);
     mbar_init(p_full, 256);
     mbar_init(o_done, 1);
+    mbar_init(q_empty, 1);
+    mbar_init(o_free, 256);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -127,18 +141,26 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tma_prefetch_desc(&tmQ);
       tma_prefetch_desc(&tmK);
       tma_prefetch_desc(&tmV);
-      mbar_expect_tx(q_full, FA_TILE_BYTES);
-      tma_load_2d(sQ, &tmQ, q_full, h * FA_D, q0);
-      for (int j = 0; j < n_kv; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        const int kv0 = lo + j * FA_BN;
-        if (!mbar_wait(&k_empty[s], ph ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_EMPTY)) break;
-        mbar_expect_tx(&k_full[s], FA_TILE_BYTES);
-        tma_load_2d(sK + s * FA_TILE_BYTES, &tmK, &k_full[s], hk * FA_D, kv0);
-        if (!mbar_wait(&v_empty[s], ph ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_EMPTY)) break;
-        mbar_expect_tx(&v_full[s], FA_TILE_BYTES);
-        tma_load_2d(sV + s * FA_TILE_BYTES, &tmV, &v_full[s], hk * FA_D, kv0);
+      int g = 0, ic = 0;   // K/V tiles and items issued so far by this CTA
+      bool ok = true;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+        FwdItem it;
+        if (!fwd_decode(p, item, it)) continue;
+        if (!mbar_wait(q_empty, (ic & 1) ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_EMPTY)) break;
+        ++ic;
+        mbar_expect_tx(q_full, FA_TILE_BYTES);
+        tma_load_2d(sQ, &tmQ, q_full, it.h * FA_D, it.q0);
+        for (int j = 0; j < it.n_kv; ++j, ++g) {
+          const int s = g & 1;
+          const uint32_t ph = (g >> 1) & 1;
+          const int kv0 = it.lo + j * FA_BN;
+          if (!mbar_wait(&k_empty[s], ph ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_EMPTY)) { ok = false; break; }
+          mbar_expect_tx(&k_full[s], FA_TILE_BYTES);
+          tma_load_2d(sK + s * FA_TILE_BYTES, &tmK, &k_full[s], it.hk * FA_D, kv0);
+          if (!mbar_wait(&v_empty[s], ph ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_EMPTY)) { ok = false; break; }
+          mbar_expect_tx(&v_full[s], FA_TILE_BYTES);
+          tma_load_2d(sV + s * FA_TILE_BYTES, &tmV, &v_full[s], it.hk * FA_D, kv0);
+        }
       }
     }
   } else if (warp == 9) {
@@ -147,9 +169,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const uint32_t idesc_s = make_idesc_f16(128, 128, 1, 0, 0);
       const uint32_t idesc_o = make_idesc_f16(128, 64, 1, 0, 1);
       const uint32_t aQ = smem_u32(sQ);
-      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
-      auto issue_s = [&](int j) {
-        const int s = j & 1;
+      int g = 0, ic = 0;
+      bool ok = true;
+      auto issue_s = [&](int gj, bool last_of_item) {
+        const int s = gj & 1;
         const uint32_t bK = smem_u32(sK + s * FA_TILE_BYTES);
 #pragma unroll
         for (int k = 0; k < FA_D / 16; ++k)
@@ -157,34 +180,50 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                      make_smem_desc(bK + k * 32, 16, 1024, SWZ_128B), idesc_s, k > 0 ? 1u : 0u);
         tc_commit(s_full);
         tc_commit(&k_empty[s]);
+        if (last_of_item) tc_commit(q_empty);
       };
-      if (ok) ok = mbar_wait(&k_full[0], 0, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
-      if (ok) {
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+        FwdItem it;
+        if (!fwd_decode(p, item, it)) continue;
+        const int n_kv = it.n_kv;
+        ok = mbar_wait(q_full, ic & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
+        if (ok) ok = mbar_wait(&k_full[g & 1], (g >> 1) & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
+        if (!ok) break;
         tc_fence_after();
-        issue_s(0);
-      }
-      for (int j = 0; j < n_kv && ok; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (j + 1 < n_kv) {
-          ok = mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
+        // S of the previous item has been read (its last p_full was waited for below) and P is rewritten
+        // by the softmax warps only after they have waited for the previous item's last o_done
+        issue_s(g, n_kv == 1);
+        for (int j = 0; j < n_kv && ok; ++j) {
+          const int gj = g + j;
+          const int s = gj & 1;
+          const uint32_t ph = (gj >> 1) & 1;
+          if (j + 1 < n_kv) {
+            ok = mbar_wait(&k_full[(gj + 1) & 1], ((gj + 1) >> 1) & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
+            if (!ok) break;
+          }
+          // P_j written (and S_j fully read) by the softmax warps
+          ok = mbar_wait(p_full, gj & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_MISC);
           if (!ok) break;
-        }
-        // P_j written (and S_j fully read) by the softmax warps
-        ok = mbar_wait(p_full, j & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_MISC);
-        if (!ok) break;
-        tc_fence_after();
-        if (j + 1 < n_kv) issue_s(j + 1);
-        ok = mbar_wait(&v_full[s], ph, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t bV = smem_u32(sV + s * FA_TILE_BYTES);
+          tc_fence_after();
+          if (j + 1 < n_kv) issue_s(gj + 1, j + 2 == n_kv);
+          ok = mbar_wait(&v_full[s], ph, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
+          if (!ok) break;
+          if (j == 0) {
+            // the first product of an item overwrites O: the previous item's epilogue must have read it
+            ok = mbar_wait(o_free, (ic & 1) ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_EMPTY);
+            if (!ok) break;
+          }
+          tc_fence_after();
+          const uint32_t bV = smem_u32(sV + s * FA_TILE_BYTES);
 #pragma unroll
-        for (int k = 0; k < FA_BN / 16; ++k)
-          mma_f16_ts(tO, tP + k * 8, make_smem_desc(bV + k * 2048, 8192, 1024, SWZ_128B), idesc_o,
-                     (j > 0 || k > 0) ? 1u : 0u);
-        tc_commit(o_done);
-        tc_commit(&v_empty[s]);
+          for (int k = 0; k < FA_BN / 16; ++k)
+            mma_f16_ts(tO, tP + k * 8, make_smem_desc(bV + k * 2048, 8192, 1024, SWZ_128B), idesc_o,
+                       (j > 0 || k > 0) ? 1u : 0u);
+          tc_commit(o_done);
+          tc_commit(&v_empty[s]);
+        }
+        g += n_kv;
+        ++ic;
       }
     }
   } else {
@@ -194,133 +233,144 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     // shared memory, once per tile); each keeps its own partial row sum until the epilogue.
     const int quarter = warp & 3, half = warp >> 2;
     const int row = quarter * 32 + lane;     // query row inside the tile == TMEM lane
-    const int qi = q0 + row;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t col_base = half * 64;
-    float m = FA_NEG, l = 0.f;
+    int g = 0;
     bool ok = true;
-    for (int j = 0; j < n_kv; ++j) {
-      const int kv0 = lo + j * FA_BN;
-      // after a time-out the loop keeps running (so every warp still meets the named barrier below)
-      // but does no work; the waits return at once because the abort flag is set
-      if (ok) {
-        ok = mbar_wait(s_full, j & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_FULL);
-        ok = __all_sync(0xffffffffu, ok);
-      }
-      tc_fence_after();
-      const bool need_mask = (kv0 + FA_BN - 1 > q0) || (p.window > 0 && (q0 + FA_BM - 1 - kv0) >= p.window);
-      // key columns this row may see inside the tile: [c_lo, c_hi]
-      const int c_hi = qi - kv0;
-      const int c_lo = (p.window > 0) ? (qi - p.window + 1 - kv0) : -1;
-      // pass 1: maximum of the raw scores of this thread's 64 columns (the positive scale commutes with max)
-      float mx4[4] = {FA_NEG, FA_NEG, FA_NEG, FA_NEG};
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        if (!ok) break;
-        uint32_t r[32];
-        tmem_ld_x32(tS + lane_addr + col_base + c * 32, r);
-        tmem_ld_wait();
-        if (need_mask) {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const int col = col_base + c * 32 + e;
-            const float sv = (col <= c_hi && col >= c_lo) ? __uint_as_float(r[e]) : FA_NEG;
-            mx4[e & 3] = fmaxf(mx4[e & 3], sv);
-          }
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(r[e]));
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+      FwdItem it;
+      if (!fwd_decode(p, item, it)) continue;
+      const int q0 = it.q0, n_kv = it.n_kv, h = it.h;
+      const int qi = q0 + row;
+      float m = FA_NEG, l = 0.f;
+      for (int j = 0; j < n_kv; ++j) {
+        const int gj = g + j;
+        const int kv0 = it.lo + j * FA_BN;
+        // after a time-out the loops keep running (so every warp still meets the named barrier below)
+        // but do no work; the waits return at once because the abort flag is set
+        if (ok) {
+          ok = mbar_wait(s_full, gj & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_FULL);
+          ok = __all_sync(0xffffffffu, ok);
         }
-      }
-      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      // exchange with the thread that owns the other half of the row (buffers alternate per tile)
-      float* xbuf = s_rowmax + (j & 1) * 256;
-      xbuf[half * 128 + row] = mx;
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      mx = fmaxf(fmaxf(mx, xbuf[(half ^ 1) * 128 + row]), m);
-      if (!ok) continue;
-      const float alpha = fast_exp2((m - mx) * p.scale_log2);
-      m = mx;
-      const float neg_ms = -mx * p.scale_log2;
-      // pass 2: probabilities p = 2^(s*c - m*c), packed to bf16
-      uint32_t pk[32];
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t r[32];
-        tmem_ld_x32(tS + lane_addr + col_base + c * 32, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float p0 = fast_exp2(fmaf(__uint_as_float(r[e]), p.scale_log2, neg_ms));
-          float p1 = fast_exp2(fmaf(__uint_as_float(r[e + 1]), p.scale_log2, neg_ms));
-          if (need_mask) {
-            const int col = col_base + c * 32 + e;
-            p0 = (col <= c_hi && col >= c_lo) ? p0 : 0.f;
-            p1 = (col + 1 <= c_hi && col + 1 >= c_lo) ? p1 : 0.f;
-          }
-          sum4[(e >> 1) & 3] += p0 + p1;
-          pk[c * 16 + e / 2] = pack_bf16(p0, p1);
-        }
-      }
-      l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
-      // the previous P V product must be complete before P is overwritten and O is touched
-      if (j > 0) {
-        ok = mbar_wait(o_done, (j - 1) & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_EMPTY);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) continue;
         tc_fence_after();
-        if (__any_sync(0xffffffffu, alpha != 1.f)) {
-          // this thread rescales its half of the row's 64 output columns
-          uint32_t o[32];
-          tmem_ld_x32(tO + lane_addr + half * 32, o);
+        const bool need_mask = (kv0 + FA_BN - 1 > q0) || (p.window > 0 && (q0 + FA_BM - 1 - kv0) >= p.window);
+        // key columns this row may see inside the tile: [c_lo, c_hi]
+        const int c_hi = qi - kv0;
+        const int c_lo = (p.window > 0) ? (qi - p.window + 1 - kv0) : -1;
+        // pass 1: maximum of the raw scores of this thread's 64 columns (the positive scale commutes with max)
+        float mx4[4] = {FA_NEG, FA_NEG, FA_NEG, FA_NEG};
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          if (!ok) break;
+          uint32_t r[32];
+          tmem_ld_x32(tS + lane_addr + col_base + c * 32, r);
+          tmem_ld_wait();
+          if (need_mask) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              const int col = col_base + c * 32 + e;
+              const float sv = (col <= c_hi && col >= c_lo) ? __uint_as_float(r[e]) : FA_NEG;
+              mx4[e & 3] = fmaxf(mx4[e & 3], sv);
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(r[e]));
+          }
+        }
+        float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        // exchange with the thread that owns the other half of the row (buffers alternate per tile)
+        float* xbuf = s_rowmax + (gj & 1) * 256;
+        xbuf[half * 128 + row] = mx;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        mx = fmaxf(fmaxf(mx, xbuf[(half ^ 1) * 128 + row]), m);
+        if (!ok) continue;
+        const float alpha = fast_exp2((m - mx) * p.scale_log2);
+        m = mx;
+        const float neg_ms = -mx * p.scale_log2;
+        // pass 2: probabilities p = 2^(s*c - m*c), packed to bf16
+        uint32_t pk[32];
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t r[32];
+          tmem_ld_x32(tS + lane_addr + col_base + c * 32, r);
           tmem_ld_wait();
 #pragma unroll
-          for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
-          tmem_st_x32(tO + lane_addr + half * 32, o);
+          for (int e = 0; e < 32; e += 2) {
+            float p0 = fast_exp2(fmaf(__uint_as_float(r[e]), p.scale_log2, neg_ms));
+            float p1 = fast_exp2(fmaf(__uint_as_float(r[e + 1]), p.scale_log2, neg_ms));
+            if (need_mask) {
+              const int col = col_base + c * 32 + e;
+              p0 = (col <= c_hi && col >= c_lo) ? p0 : 0.f;
+              p1 = (col + 1 <= c_hi && col + 1 >= c_lo) ? p1 : 0.f;
+            }
+            sum4[(e >> 1) & 3] += p0 + p1;
+            pk[c * 16 + e / 2] = pack_bf16(p0, p1);
+          }
         }
-      }
-      tmem_st_x32(tP + lane_addr + half * 32, pk);
-      tmem_st_wait();
-      tc_fence_before();
-      mbar_arrive(p_full);
-    }
-    // ---------------------------------------------------------------- epilogue
-    if (ok && n_kv > 0) {
-      ok = mbar_wait(o_done, (n_kv - 1) & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_FULL);
-      ok = __all_sync(0xffffffffu, ok);
-    }
-    // total row sum = own partial + the partner's (both are relative to the same final maximum)
-    float* lbuf = s_rowmax + 512;
-    lbuf[half * 128 + row] = l;
-    asm volatile("bar.sync 1, 256;" ::: "memory");
-    l += lbuf[(half ^ 1) * 128 + row];
-    if (ok && n_kv > 0) {
-      tc_fence_after();
-      float lse = (m * p.scale_log2 + log2f(l)) * 0.6931471805599453f;  // natural log
-      float inv = 1.f / l;
-      if (p.sink_lse) {
-        const float sl = p.sink_lse[h];
-        const float tot = fmaxf(lse, sl) + log1pf(__expf(-fabsf(lse - sl)));
-        inv *= __expf(lse - tot);
-        lse = tot;
-      }
-      uint32_t o[32];
-      tmem_ld_x32(tO + lane_addr + half * 32, o);
-      tmem_ld_wait();
-      if (qi < q_hi) {
-        uint4* dst = reinterpret_cast<uint4*>(p.out + (static_cast<size_t>(qi) * p.Hq + h) * FA_D + half * 32);
+        l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+        // the previous P V product must be complete before P is overwritten and O is touched; for the
+        // first tile of an item that product belongs to the previous item and was waited for in its epilogue
+        if (j > 0) {
+          ok = mbar_wait(o_done, (gj - 1) & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_EMPTY);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) continue;
+          tc_fence_after();
+          if (__any_sync(0xffffffffu, alpha != 1.f)) {
+            // this thread rescales its half of the row's 64 output columns
+            uint32_t o[32];
+            tmem_ld_x32(tO + lane_addr + half * 32, o);
+            tmem_ld_wait();
 #pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          uint4 w;
-          w.x = pack_bf16(__uint_as_float(o[8 * v + 0]) * inv, __uint_as_float(o[8 * v + 1]) * inv);
-          w.y = pack_bf16(__uint_as_float(o[8 * v + 2]) * inv, __uint_as_float(o[8 * v + 3]) * inv);
-          w.z = pack_bf16(__uint_as_float(o[8 * v + 4]) * inv, __uint_as_float(o[8 * v + 5]) * inv);
-          w.w = pack_bf16(__uint_as_float(o[8 * v + 6]) * inv, __uint_as_float(o[8 * v + 7]) * inv);
-          dst[v] = w;
+            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+            tmem_st_x32(tO + lane_addr + half * 32, o);
+          }
         }
-        if (half == 0) p.lse[static_cast<size_t>(h) * p.T + qi] = lse;
+        tmem_st_x32(tP + lane_addr + half * 32, pk);
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(p_full);
       }
+      // ---------------------------------------------------------------- epilogue of the item
+      if (ok) {
+        ok = mbar_wait(o_done, (g + n_kv - 1) & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_FULL);
+        ok = __all_sync(0xffffffffu, ok);
+      }
+      // total row sum = own partial + the partner's (both are relative to the same final maximum)
+      float* lbuf = s_rowmax + 512;
+      lbuf[half * 128 + row] = l;
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      l += lbuf[(half ^ 1) * 128 + row];
+      if (ok) {
+        tc_fence_after();
+        uint32_t o[32];
+        tmem_ld_x32(tO + lane_addr + half * 32, o);
+        tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(o_free);   // the next item's first product may overwrite O now
+        float lse = (m * p.scale_log2 + log2f(l)) * 0.6931471805599453f;  // natural log
+        float inv = 1.f / l;
+        if (p.sink_lse) {
+          const float sl = p.sink_lse[h];
+          const float tot = fmaxf(lse, sl) + log1pf(__expf(-fabsf(lse - sl)));
+          inv *= __expf(lse - tot);
+          lse = tot;
+        }
+        if (qi < it.q_hi) {
+          uint4* dst = reinterpret_cast<uint4*>(p.out + (static_cast<size_t>(qi) * p.Hq + h) * FA_D + half * 32);
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 w;
+            w.x = pack_bf16(__uint_as_float(o[8 * v + 0]) * inv, __uint_as_float(o[8 * v + 1]) * inv);
+            w.y = pack_bf16(__uint_as_float(o[8 * v + 2]) * inv, __uint_as_float(o[8 * v + 3]) * inv);
+            w.z = pack_bf16(__uint_as_float(o[8 * v + 4]) * inv, __uint_as_float(o[8 * v + 5]) * inv);
+            w.w = pack_bf16(__uint_as_float(o[8 * v + 6]) * inv, __uint_as_float(o[8 * v + 7]) * inv);
+            dst[v] = w;
+          }
+          if (half == 0) p.lse[static_cast<size_t>(h) * p.T + qi] = lse;
+        }
+      }
+      g += n_kv;
     }
   }
 
@@ -383,7 +433,11 @@ KWU_API int kwu_flash_fwd(const void* q, int q_ld, const void* k, int k_ld, cons
   p.sink_lse = sink_lse;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
-  dim3 grid(n_tiles, Hq);
+  int sms = 0, dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  long long items = static_cast<long long>(n_tiles) * Hq;
+  int grid = static_cast<int>(items < 2LL * sms ? items : 2LL * sms);   // two resident CTAs per SM, each walks the item list
   flash_fwd_kernel<<<grid, FA_THREADS, FA_SMEM, reinterpret_cast<cudaStream_t>(stream)>>>(tmQ, tmK, tmV, p); kwu::count_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { set_last_error("flash_fwd launch: %s", cudaGetErrorString(e)); return 11; }
