@@ -2,11 +2,11 @@
 //
 // Three launches, no atomics, deterministic:
 //   1. delta[h,t] = sum_d out[t,h,d] * dout[t,h,d]
-//   2. dK/dV kernel: one CTA per (128-key tile, kv head). Scores are formed TRANSPOSED
+//   2. dK/dV kernel: persistent CTAs over (128-key tile, query head) items. Scores are formed TRANSPOSED
 //      (S^T = K Q^T, dP^T = V dO^T, keys on the TMEM lanes) so that P^T and dS^T are directly the
 //      A operands of dV += P^T dO and dK += dS^T Q. The CTA loops over every query head of its GQA
 //      group and every 64-query tile that can see the key tile, accumulating in TMEM.
-//   3. dQ kernel: one CTA per (128-query tile, query head), loops over 64-key tiles:
+//   3. dQ kernel: persistent CTAs over (128-query tile, query head) items, each looping over 64-key tiles:
 //      S = Q K^T, dP = dO V^T, dS = P o (dP - delta) * scale written to TMEM as bf16,
 //      dQ += dS K accumulated in TMEM.
 // The stored lse already contains the sink term, so P = exp(S*scale - lse) is the sink-aware
@@ -60,18 +60,32 @@ struct FlashBwdParams {
 
 // ------------------------------------------------------------------------------------ dK / dV
 // smem: K tile 16 KB, V tile 16 KB, 2 stages x (Q 8 KB + dO 8 KB).
+// Persistent: a CTA walks items (key tile, query head) blockIdx.x, blockIdx.x + gridDim.x, ...; barrier
+// phases run on counters that continue across items, and the producer warp loads the next item's K / V
+// and first Q / dO tiles while the current item's accumulators are being written out.
 constexpr int FBK_SMEM = 2 * 16384 + 2 * 16384 + 1024 + 1024 + 1024;
+
+struct DkdvItem {
+  int kv0, de, h, hk, q_begin, q_end, n_it;
+};
+
+__device__ __forceinline__ bool dkdv_decode(const FlashBwdParams& p, int item, DkdvItem& it) {
+  const int4 job = p.plan[item / p.Hq];
+  if (!job.w) return false;
+  it.kv0 = job.x; it.de = job.z;
+  it.h = item % p.Hq;                      // one item per query head; GQA partials are summed afterwards
+  it.hk = it.h / (p.Hq / p.Hkv);
+  it.q_begin = it.kv0;
+  it.q_end = it.de;
+  if (p.window > 0) it.q_end = min(it.de, it.kv0 + 127 + p.window);
+  it.n_it = (it.q_end - it.q_begin + 63) / 64;
+  return it.n_it > 0;
+}
 
 __global__ void __launch_bounds__(FB_THREADS, 2)
 flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_constant__ CUtensorMap tmDO64,
                       const __grid_constant__ CUtensorMap tmK128, const __grid_constant__ CUtensorMap tmV128,
                       const FlashBwdParams p) {
-  const int4 job = p.plan[blockIdx.x];
-  if (!job.w) return;
-  const int kv0 = job.x, de = job.z;
-  const int h = blockIdx.y;                 // one CTA per query head; GQA partials are summed afterwards
-  const int hk = h / (p.Hq / p.Hkv);
-
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -88,17 +102,14 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
   uint64_t* sdp_full = bars + 5;
   uint64_t* p_ready = bars + 6;
   uint64_t* acc_done = bars + 7;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* kv_empty = bars + 8;  // the item's last products have read K and V
+  uint64_t* acc_free = bars + 9;  // the item's dK / dV accumulators have been read out
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-
-  const int q_begin = kv0;
-  int q_end = de;
-  if (p.window > 0) q_end = min(de, kv0 + 127 + p.window);
-  const int n_q = (q_end - q_begin + 63) / 64;
-  const int n_it = n_q;
+  const int n_items = p.n_tiles * p.Hq;
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
@@ -109,6 +120,8 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
     mbar_init(sdp_full, 1);
     mbar_init(p_ready, 256);
     mbar_init(acc_done, 1);
+    mbar_init(kv_empty, 1);
+    mbar_init(acc_free, 256);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -123,33 +136,44 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
   const uint32_t tS = tmem_base, tDP = tmem_base + 64, tDV = tmem_base + 128, tDK = tmem_base + 192;
 
   if (warp == 8) {
-    if (lane == 0) {
-      mbar_expect_tx(kv_full, 32768);
-      tma_load_2d(sK, &tmK128, kv_full, hk * FB_D, kv0);
-      tma_load_2d(sV, &tmV128, kv_full, hk * FB_D, kv0);
-    }
-    const float* lse_h = p.lse + static_cast<size_t>(h) * p.T;
-    const float* dl_h = p.delta + static_cast<size_t>(h) * p.T;
-    for (int it = 0; it < n_it; ++it) {
-      const int s = it & 1;
-      const uint32_t ph = (it >> 1) & 1;
-      const int q_lo = q_begin + it * 64;
-      int ok = 1;
-      if (lane == 0) ok = mbar_wait(&qd_empty[s], ph ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_EMPTY) ? 1 : 0;
+    int g = 0, ic = 0;
+    int ok = 1;
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      DkdvItem it;
+      if (!dkdv_decode(p, item, it)) continue;
+      if (lane == 0) {
+        ok = mbar_wait(kv_empty, (ic & 1) ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_EMPTY) ? 1 : 0;
+        if (ok) {
+          mbar_expect_tx(kv_full, 32768);
+          tma_load_2d(sK, &tmK128, kv_full, it.hk * FB_D, it.kv0);
+          tma_load_2d(sV, &tmV128, kv_full, it.hk * FB_D, it.kv0);
+        }
+      }
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
-      // per-query softmax statistics of this tile, staged once for all 128 key rows
+      ++ic;
+      const float* lse_h = p.lse + static_cast<size_t>(it.h) * p.T;
+      const float* dl_h = p.delta + static_cast<size_t>(it.h) * p.T;
+      for (int i = 0; i < it.n_it; ++i, ++g) {
+        const int s = g & 1;
+        const uint32_t ph = (g >> 1) & 1;
+        const int q_lo = it.q_begin + i * 64;
+        if (lane == 0) ok = mbar_wait(&qd_empty[s], ph ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_EMPTY) ? 1 : 0;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+        // per-query softmax statistics of this tile, staged once for all 128 key rows
 #pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        const int qc = min(q_lo + lane + 32 * u, p.T - 1);
-        sLse[s * 64 + lane + 32 * u] = lse_h[qc] * FB_LOG2E;
-        sDelta[s * 64 + lane + 32 * u] = dl_h[qc] * p.scale;
-      }
-      __syncwarp();
-      if (lane == 0) {
-        mbar_expect_tx(&qd_full[s], 16384);
-        tma_load_2d(sQ + s * 8192, &tmQ64, &qd_full[s], h * FB_D, q_lo);
-        tma_load_2d(sDO + s * 8192, &tmDO64, &qd_full[s], h * FB_D, q_lo);
+        for (int u = 0; u < 2; ++u) {
+          const int qc = min(q_lo + lane + 32 * u, p.T - 1);
+          sLse[s * 64 + lane + 32 * u] = lse_h[qc] * FB_LOG2E;
+          sDelta[s * 64 + lane + 32 * u] = dl_h[qc] * p.scale;
+        }
+        __syncwarp();
+        if (lane == 0) {
+          mbar_expect_tx(&qd_full[s], 16384);
+          tma_load_2d(sQ + s * 8192, &tmQ64, &qd_full[s], it.h * FB_D, q_lo);
+          tma_load_2d(sDO + s * 8192, &tmDO64, &qd_full[s], it.h * FB_D, q_lo);
+        }
       }
     }
   } else if (warp == 9) {
@@ -157,94 +181,117 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
       const uint32_t idesc_s = make_idesc_f16(128, 64, 1, 0, 0);   // S^T, dP^T: N = 64 queries
       const uint32_t idesc_a = make_idesc_f16(128, 64, 1, 0, 1);   // dV, dK: B is MN-major
       const uint32_t aK = smem_u32(sK), aV = smem_u32(sV);
-      bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
-      for (int it = 0; it < n_it && ok; ++it) {
-        const int s = it & 1;
-        const uint32_t ph = (it >> 1) & 1;
-        ok = mbar_wait(&qd_full[s], ph, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t bQ = smem_u32(sQ + s * 8192), bDO = smem_u32(sDO + s * 8192);
+      int g = 0, ic = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+        DkdvItem it;
+        if (!dkdv_decode(p, item, it)) continue;
+        ok = mbar_wait(kv_full, ic & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
+        for (int i = 0; i < it.n_it && ok; ++i) {
+          const int gi = g + i;
+          const int s = gi & 1;
+          const uint32_t ph = (gi >> 1) & 1;
+          ok = mbar_wait(&qd_full[s], ph, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t bQ = smem_u32(sQ + s * 8192), bDO = smem_u32(sDO + s * 8192);
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          mma_f16_ss(tS, make_smem_desc(aK + k * 32, 16, 1024, SWZ_128B),
-                     make_smem_desc(bQ + k * 32, 16, 1024, SWZ_128B), idesc_s, k > 0 ? 1u : 0u);
+          for (int k = 0; k < 4; ++k)
+            mma_f16_ss(tS, make_smem_desc(aK + k * 32, 16, 1024, SWZ_128B),
+                       make_smem_desc(bQ + k * 32, 16, 1024, SWZ_128B), idesc_s, k > 0 ? 1u : 0u);
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          mma_f16_ss(tDP, make_smem_desc(aV + k * 32, 16, 1024, SWZ_128B),
-                     make_smem_desc(bDO + k * 32, 16, 1024, SWZ_128B), idesc_s, k > 0 ? 1u : 0u);
-        tc_commit(sdp_full);
-        ok = mbar_wait(p_ready, it & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_MISC);
-        if (!ok) break;
-        tc_fence_after();
+          for (int k = 0; k < 4; ++k)
+            mma_f16_ss(tDP, make_smem_desc(aV + k * 32, 16, 1024, SWZ_128B),
+                       make_smem_desc(bDO + k * 32, 16, 1024, SWZ_128B), idesc_s, k > 0 ? 1u : 0u);
+          tc_commit(sdp_full);
+          ok = mbar_wait(p_ready, gi & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_MISC);
+          if (!ok) break;
+          if (i == 0) {
+            // the first products of an item overwrite dV / dK: the previous item's must have been read out
+            ok = mbar_wait(acc_free, (ic & 1) ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_EMPTY);
+            if (!ok) break;
+          }
+          tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          mma_f16_ts(tDV, tS + k * 8, make_smem_desc(bDO + k * 2048, 8192, 1024, SWZ_128B), idesc_a,
-                     (it > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < 4; ++k)
+            mma_f16_ts(tDV, tS + k * 8, make_smem_desc(bDO + k * 2048, 8192, 1024, SWZ_128B), idesc_a,
+                       (i > 0 || k > 0) ? 1u : 0u);
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          mma_f16_ts(tDK, tDP + k * 8, make_smem_desc(bQ + k * 2048, 8192, 1024, SWZ_128B), idesc_a,
-                     (it > 0 || k > 0) ? 1u : 0u);
-        tc_commit(&qd_empty[s]);
+          for (int k = 0; k < 4; ++k)
+            mma_f16_ts(tDK, tDP + k * 8, make_smem_desc(bQ + k * 2048, 8192, 1024, SWZ_128B), idesc_a,
+                       (i > 0 || k > 0) ? 1u : 0u);
+          tc_commit(&qd_empty[s]);
+        }
+        if (ok) {
+          tc_commit(acc_done);
+          tc_commit(kv_empty);
+        }
+        g += it.n_it;
+        ++ic;
       }
-      if (ok) tc_commit(acc_done);
     }
   } else {
     // two threads per key row: warp w handles query columns [0,32) of the tile, warp w+4 columns [32,64)
     const int quarter = warp & 3, half = warp >> 2;
     const int row = quarter * 32 + lane;
-    const int kj = kv0 + row;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const float c_log2 = p.scale * FB_LOG2E;
+    int g = 0, ic = 0;
     bool ok = true;
-    for (int it = 0; it < n_it; ++it) {
-      const int q_lo = q_begin + it * 64;
-      const float* lse_s = sLse + (it & 1) * 64;
-      const float* dl_s = sDelta + (it & 1) * 64;
-      // observe the producer's barrier directly so its smem writes are visible here
-      ok = mbar_wait(&qd_full[it & 1], (it >> 1) & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
-      if (ok) ok = mbar_wait(sdp_full, it & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_FULL);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
-      // query columns of this tile that key row kj may attend to: [c_lo, c_hi]
-      const int c_lo_q = kj - q_lo;                                           // causal: qi >= kj
-      int c_hi_q = min(q_end, p.window > 0 ? kj + p.window : q_end) - 1 - q_lo;  // window and document end
-      if (kj >= de) c_hi_q = -1;
-      const bool need_mask = (c_lo_q > 0) || (c_hi_q < 63);
-      {
-        const int c = half;
-        uint32_t sv[32], dp[32], pp[16], dd[16];
-        tmem_ld_x32(tS + lane_addr + c * 32, sv);
-        tmem_ld_x32(tDP + lane_addr + c * 32, dp);
-        tmem_ld_wait();
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      DkdvItem it;
+      if (!dkdv_decode(p, item, it)) continue;
+      const int kj = it.kv0 + row;
+      const int de = it.de, q_end = it.q_end, h = it.h, hk = it.hk;
+      for (int i = 0; i < it.n_it; ++i) {
+        const int gi = g + i;
+        const int q_lo = it.q_begin + i * 64;
+        const float* lse_s = sLse + (gi & 1) * 64;
+        const float* dl_s = sDelta + (gi & 1) * 64;
+        // observe the producer's barrier directly so its smem writes are visible here
+        ok = mbar_wait(&qd_full[gi & 1], (gi >> 1) & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
+        if (ok) ok = mbar_wait(sdp_full, gi & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_FULL);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        // query columns of this tile that key row kj may attend to: [c_lo, c_hi]
+        const int c_lo_q = kj - q_lo;                                           // causal: qi >= kj
+        int c_hi_q = min(q_end, p.window > 0 ? kj + p.window : q_end) - 1 - q_lo;  // window and document end
+        if (kj >= de) c_hi_q = -1;
+        const bool need_mask = (c_lo_q > 0) || (c_hi_q < 63);
+        {
+          const int c = half;
+          uint32_t sv[32], dp[32], pp[16], dd[16];
+          tmem_ld_x32(tS + lane_addr + c * 32, sv);
+          tmem_ld_x32(tDP + lane_addr + c * 32, dp);
+          tmem_ld_wait();
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float pr[2], dsv[2];
+          for (int e = 0; e < 32; e += 2) {
+            float pr[2], dsv[2];
 #pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int col = c * 32 + e + u;
-            float pv = fast_exp2(fmaf(__uint_as_float(sv[e + u]), c_log2, -lse_s[col]));
-            if (need_mask) pv = (col >= c_lo_q && col <= c_hi_q) ? pv : 0.f;
-            pr[u] = pv;
-            dsv[u] = pv * fmaf(__uint_as_float(dp[e + u]), p.scale, -dl_s[col]);
+            for (int u = 0; u < 2; ++u) {
+              const int col = c * 32 + e + u;
+              float pv = fast_exp2(fmaf(__uint_as_float(sv[e + u]), c_log2, -lse_s[col]));
+              if (need_mask) pv = (col >= c_lo_q && col <= c_hi_q) ? pv : 0.f;
+              pr[u] = pv;
+              dsv[u] = pv * fmaf(__uint_as_float(dp[e + u]), p.scale, -dl_s[col]);
+            }
+            pp[e / 2] = pack_bf16(pr[0], pr[1]);
+            dd[e / 2] = pack_bf16(dsv[0], dsv[1]);
           }
-          pp[e / 2] = pack_bf16(pr[0], pr[1]);
-          dd[e / 2] = pack_bf16(dsv[0], dsv[1]);
+          // P^T / dS^T as bf16 overwrite the first half of the columns that were just read
+          tmem_st_x16(tS + lane_addr + c * 16, pp);
+          tmem_st_x16(tDP + lane_addr + c * 16, dd);
         }
-        // P^T / dS^T as bf16 overwrite the first half of the columns that were just read
-        tmem_st_x16(tS + lane_addr + c * 16, pp);
-        tmem_st_x16(tDP + lane_addr + c * 16, dd);
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(p_ready);
       }
-      tmem_st_wait();
-      tc_fence_before();
-      mbar_arrive(p_ready);
-    }
-    if (ok) {
-      ok = mbar_wait(acc_done, 0, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_FULL);
-      ok = __all_sync(0xffffffffu, ok);
-    }
-    if (ok) {
+      if (ok) {
+        ok = mbar_wait(acc_done, ic & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_FULL);
+        ok = __all_sync(0xffffffffu, ok);
+      }
+      if (!ok) break;
       tc_fence_after();
       {
         const int which = half;  // the first thread of a row writes dV, the second dK
@@ -253,6 +300,8 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
         tmem_ld_x32(src, o);
         tmem_ld_x32(src + 32, o + 32);
         tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(acc_free);   // the next item's first products may overwrite the accumulators now
         if (kj < de) {
           if (p.dk_part) {
             float4* dst = reinterpret_cast<float4*>((which == 0 ? p.dv_part : p.dk_part) +
@@ -277,6 +326,8 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
           }
         }
       }
+      g += it.n_it;
+      ++ic;
     }
   }
 
@@ -291,20 +342,31 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
 }
 
 // ------------------------------------------------------------------------------------ dQ
-// smem: Q 16 KB, dO 16 KB, 2 stages x (K 8 KB + V 8 KB).
+// smem: Q 16 KB, dO 16 KB, 2 stages x (K 8 KB + V 8 KB). Persistent over (query tile, query head) items,
+// heaviest first, like the forward kernel.
 constexpr int FBQ_SMEM = 2 * 16384 + 2 * 16384 + 1024 + 1024;
+
+struct DqItem {
+  int q0, de, h, hk, q_hi, lo, n_kv;
+};
+
+__device__ __forceinline__ bool dq_decode(const FlashBwdParams& p, int item, DqItem& it) {
+  const int4 job = p.plan[p.n_tiles - 1 - item / p.Hq];   // later query tiles of a document see more keys
+  if (!job.w) return false;
+  it.q0 = job.x; it.de = job.z;
+  it.h = item % p.Hq;
+  it.hk = it.h / (p.Hq / p.Hkv);
+  it.q_hi = min(it.q0 + 128, it.de);
+  it.lo = job.y;
+  if (p.window > 0) it.lo = max(job.y, it.q0 - p.window + 1);
+  it.n_kv = (it.q_hi - it.lo + 63) / 64;
+  return it.n_kv > 0;
+}
 
 __global__ void __launch_bounds__(FB_THREADS, 2)
 flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_constant__ CUtensorMap tmDO128,
                     const __grid_constant__ CUtensorMap tmK64, const __grid_constant__ CUtensorMap tmV64,
                     const FlashBwdParams p) {
-  // later query tiles of a document see more keys: schedule them first
-  const int4 job = p.plan[p.n_tiles - 1 - blockIdx.x];
-  if (!job.w) return;
-  const int q0 = job.x, ds = job.y, de = job.z;
-  const int h = blockIdx.y;
-  const int hk = h / (p.Hq / p.Hkv);
-
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -319,15 +381,14 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
   uint64_t* sdp_full = bars + 5;
   uint64_t* p_ready = bars + 6;
   uint64_t* acc_done = bars + 7;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* q_empty = bars + 8;   // the item's last products have read Q and dO
+  uint64_t* acc_free = bars + 9;  // the item's dQ accumulator has been read out
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int q_hi = min(q0 + 128, de);
-  int lo = ds;
-  if (p.window > 0) lo = max(ds, q0 - p.window + 1);
-  const int n_kv = (q_hi - lo + 63) / 64;
+  const int n_items = p.n_tiles * p.Hq;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -338,6 +399,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
     mbar_init(sdp_full, 1);
     mbar_init(p_ready, 256);
     mbar_init(acc_done, 1);
+    mbar_init(q_empty, 1);
+    mbar_init(acc_free, 256);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -353,16 +416,24 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
 
   if (warp == 8) {
     if (lane == 0) {
-      mbar_expect_tx(q_full, 32768);
-      tma_load_2d(sQ, &tmQ128, q_full, h * FB_D, q0);
-      tma_load_2d(sDO, &tmDO128, q_full, h * FB_D, q0);
-      for (int j = 0; j < n_kv; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(&kv_empty[s], ph ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_EMPTY)) break;
-        mbar_expect_tx(&kv_full[s], 16384);
-        tma_load_2d(sK + s * 8192, &tmK64, &kv_full[s], hk * FB_D, lo + j * 64);
-        tma_load_2d(sV + s * 8192, &tmV64, &kv_full[s], hk * FB_D, lo + j * 64);
+      int g = 0, ic = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+        DqItem it;
+        if (!dq_decode(p, item, it)) continue;
+        if (!mbar_wait(q_empty, (ic & 1) ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_EMPTY)) break;
+        ++ic;
+        mbar_expect_tx(q_full, 32768);
+        tma_load_2d(sQ, &tmQ128, q_full, it.h * FB_D, it.q0);
+        tma_load_2d(sDO, &tmDO128, q_full, it.h * FB_D, it.q0);
+        for (int j = 0; j < it.n_kv; ++j, ++g) {
+          const int s = g & 1;
+          const uint32_t ph = (g >> 1) & 1;
+          if (!mbar_wait(&kv_empty[s], ph ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_EMPTY)) { ok = false; break; }
+          mbar_expect_tx(&kv_full[s], 16384);
+          tma_load_2d(sK + s * 8192, &tmK64, &kv_full[s], it.hk * FB_D, it.lo + j * 64);
+          tma_load_2d(sV + s * 8192, &tmV64, &kv_full[s], it.hk * FB_D, it.lo + j * 64);
+        }
       }
     }
   } else if (warp == 9) {
@@ -370,87 +441,109 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
       const uint32_t idesc_s = make_idesc_f16(128, 64, 1, 0, 0);
       const uint32_t idesc_q = make_idesc_f16(128, 64, 1, 0, 1);
       const uint32_t aQ = smem_u32(sQ), aDO = smem_u32(sDO);
-      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
-      for (int j = 0; j < n_kv && ok; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        ok = mbar_wait(&kv_full[s], ph, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t bK = smem_u32(sK + s * 8192), bV = smem_u32(sV + s * 8192);
+      int g = 0, ic = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+        DqItem it;
+        if (!dq_decode(p, item, it)) continue;
+        ok = mbar_wait(q_full, ic & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
+        for (int j = 0; j < it.n_kv && ok; ++j) {
+          const int gj = g + j;
+          const int s = gj & 1;
+          const uint32_t ph = (gj >> 1) & 1;
+          ok = mbar_wait(&kv_full[s], ph, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t bK = smem_u32(sK + s * 8192), bV = smem_u32(sV + s * 8192);
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          mma_f16_ss(tS, make_smem_desc(aQ + k * 32, 16, 1024, SWZ_128B),
-                     make_smem_desc(bK + k * 32, 16, 1024, SWZ_128B), idesc_s, k > 0 ? 1u : 0u);
+          for (int k = 0; k < 4; ++k)
+            mma_f16_ss(tS, make_smem_desc(aQ + k * 32, 16, 1024, SWZ_128B),
+                       make_smem_desc(bK + k * 32, 16, 1024, SWZ_128B), idesc_s, k > 0 ? 1u : 0u);
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          mma_f16_ss(tDP, make_smem_desc(aDO + k * 32, 16, 1024, SWZ_128B),
-                     make_smem_desc(bV + k * 32, 16, 1024, SWZ_128B), idesc_s, k > 0 ? 1u : 0u);
-        tc_commit(sdp_full);
-        ok = mbar_wait(p_ready, j & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_MISC);
-        if (!ok) break;
-        tc_fence_after();
+          for (int k = 0; k < 4; ++k)
+            mma_f16_ss(tDP, make_smem_desc(aDO + k * 32, 16, 1024, SWZ_128B),
+                       make_smem_desc(bV + k * 32, 16, 1024, SWZ_128B), idesc_s, k > 0 ? 1u : 0u);
+          tc_commit(sdp_full);
+          if (j + 1 == it.n_kv) tc_commit(q_empty);   // Q and dO are free once these products are done
+          ok = mbar_wait(p_ready, gj & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_MISC);
+          if (!ok) break;
+          if (j == 0) {
+            ok = mbar_wait(acc_free, (ic & 1) ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_EMPTY);
+            if (!ok) break;
+          }
+          tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          mma_f16_ts(tDQ, tS + k * 8, make_smem_desc(bK + k * 2048, 8192, 1024, SWZ_128B), idesc_q,
-                     (j > 0 || k > 0) ? 1u : 0u);
-        tc_commit(&kv_empty[s]);
+          for (int k = 0; k < 4; ++k)
+            mma_f16_ts(tDQ, tS + k * 8, make_smem_desc(bK + k * 2048, 8192, 1024, SWZ_128B), idesc_q,
+                       (j > 0 || k > 0) ? 1u : 0u);
+          tc_commit(&kv_empty[s]);
+        }
+        if (ok) tc_commit(acc_done);
+        g += it.n_kv;
+        ++ic;
       }
-      if (ok) tc_commit(acc_done);
     }
   } else {
     const int quarter = warp & 3, half = warp >> 2;   // two threads per query row, 32 key columns each
     const int row = quarter * 32 + lane;
-    const int qi = q0 + row;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const float c_log2 = p.scale * FB_LOG2E;
-    const int qc = min(qi, p.T - 1);
-    const float lse_q = p.lse[static_cast<size_t>(h) * p.T + qc] * FB_LOG2E;
-    const float dl_q = p.delta[static_cast<size_t>(h) * p.T + qc] * p.scale;
+    int g = 0, ic = 0;
     bool ok = true;
-    for (int j = 0; j < n_kv; ++j) {
-      const int kv0 = lo + j * 64;
-      ok = mbar_wait(sdp_full, j & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_FULL);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
-      // key columns of this tile that query row qi may attend to: [c_lo, c_hi]
-      const int c_hi_k = (qi < q_hi) ? (qi - kv0) : -1;
-      const int c_lo_k = (p.window > 0) ? (qi - p.window + 1 - kv0) : 0;
-      const bool need_mask = (c_hi_k < 63) || (c_lo_k > 0);
-      {
-        const int c = half;
-        uint32_t sv[32], dp[32], dd[16];
-        tmem_ld_x32(tS + lane_addr + c * 32, sv);
-        tmem_ld_x32(tDP + lane_addr + c * 32, dp);
-        tmem_ld_wait();
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      DqItem it;
+      if (!dq_decode(p, item, it)) continue;
+      const int qi = it.q0 + row;
+      const int q_hi = it.q_hi, h = it.h;
+      const int qc = min(qi, p.T - 1);
+      const float lse_q = p.lse[static_cast<size_t>(h) * p.T + qc] * FB_LOG2E;
+      const float dl_q = p.delta[static_cast<size_t>(h) * p.T + qc] * p.scale;
+      for (int j = 0; j < it.n_kv; ++j) {
+        const int gj = g + j;
+        const int kv0 = it.lo + j * 64;
+        ok = mbar_wait(sdp_full, gj & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_FULL);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        // key columns of this tile that query row qi may attend to: [c_lo, c_hi]
+        const int c_hi_k = (qi < q_hi) ? (qi - kv0) : -1;
+        const int c_lo_k = (p.window > 0) ? (qi - p.window + 1 - kv0) : 0;
+        const bool need_mask = (c_hi_k < 63) || (c_lo_k > 0);
+        {
+          const int c = half;
+          uint32_t sv[32], dp[32], dd[16];
+          tmem_ld_x32(tS + lane_addr + c * 32, sv);
+          tmem_ld_x32(tDP + lane_addr + c * 32, dp);
+          tmem_ld_wait();
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float dsv[2];
+          for (int e = 0; e < 32; e += 2) {
+            float dsv[2];
 #pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int col = c * 32 + e + u;
-            float pv = fast_exp2(fmaf(__uint_as_float(sv[e + u]), c_log2, -lse_q));
-            if (need_mask) pv = (col >= c_lo_k && col <= c_hi_k) ? pv : 0.f;
-            dsv[u] = pv * fmaf(__uint_as_float(dp[e + u]), p.scale, -dl_q);
+            for (int u = 0; u < 2; ++u) {
+              const int col = c * 32 + e + u;
+              float pv = fast_exp2(fmaf(__uint_as_float(sv[e + u]), c_log2, -lse_q));
+              if (need_mask) pv = (col >= c_lo_k && col <= c_hi_k) ? pv : 0.f;
+              dsv[u] = pv * fmaf(__uint_as_float(dp[e + u]), p.scale, -dl_q);
+            }
+            dd[e / 2] = pack_bf16(dsv[0], dsv[1]);
           }
-          dd[e / 2] = pack_bf16(dsv[0], dsv[1]);
+          tmem_st_x16(tS + lane_addr + c * 16, dd);
         }
-        tmem_st_x16(tS + lane_addr + c * 16, dd);
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(p_ready);
       }
-      tmem_st_wait();
-      tc_fence_before();
-      mbar_arrive(p_ready);
-    }
-    if (ok) {
-      ok = mbar_wait(acc_done, 0, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_FULL);
-      ok = __all_sync(0xffffffffu, ok);
-    }
-    if (ok) {
+      if (ok) {
+        ok = mbar_wait(acc_done, ic & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_FULL);
+        ok = __all_sync(0xffffffffu, ok);
+      }
+      if (!ok) break;
       tc_fence_after();
       uint32_t o[32];
       tmem_ld_x32(tDQ + lane_addr + half * 32, o);
       tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(acc_free);
       if (qi < q_hi) {
         uint4* dst = reinterpret_cast<uint4*>(p.dq + (static_cast<size_t>(qi) * p.Hq + h) * FB_D + half * 32);
 #pragma unroll
@@ -463,6 +556,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
           dst[v] = w;
         }
       }
+      g += it.n_kv;
+      ++ic;
     }
   }
 
@@ -560,13 +655,18 @@ KWU_API int kwu_flash_bwd(const void* q, int q_ld, const void* k, int k_ld, cons
   } else {
     p.dk_part = p.dv_part = nullptr;
   }
-  flash_bwd_dkdv_kernel<<<dim3(n_tiles, Hq), FB_THREADS, FBK_SMEM, st>>>(tmQ64, tmDO64, tmK128, tmV128, p); kwu::count_launch();
+  int sms = 0, dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const long long items = static_cast<long long>(n_tiles) * Hq;
+  const int pgrid = static_cast<int>(items < 2LL * sms ? items : 2LL * sms);   // two resident CTAs per SM walk the items
+  flash_bwd_dkdv_kernel<<<pgrid, FB_THREADS, FBK_SMEM, st>>>(tmQ64, tmDO64, tmK128, tmV128, p); kwu::count_launch();
   if (Hq > Hkv) {
     long g = (static_cast<long>(T) * Hkv * 16 + 255) / 256;
     if (g > 148 * 16) g = 148 * 16;
     flash_group_reduce_kernel<<<static_cast<int>(g), 256, 0, st>>>(p.dk_part, p.dv_part, p.dk, p.dv, dk_ld, dv_ld, T, Hq, Hkv); kwu::count_launch();
   }
-  flash_bwd_dq_kernel<<<dim3(n_tiles, Hq), FB_THREADS, FBQ_SMEM, st>>>(tmQ128, tmDO128, tmK64, tmV64, p); kwu::count_launch();
+  flash_bwd_dq_kernel<<<pgrid, FB_THREADS, FBQ_SMEM, st>>>(tmQ128, tmDO128, tmK64, tmV64, p); kwu::count_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { set_last_error("flash_bwd launch: %s", cudaGetErrorString(e)); return 11; }
   return 0;
