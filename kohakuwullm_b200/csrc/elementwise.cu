@@ -768,3 +768,75 @@ KWU_API int kwu_rmsnorm_bwd_noalloc(const void* x, const float* w, const float* 
   }
   return 0;
 }
+
+// --------------------------------------------------------------------------- embedding
+// Forward: out[t, :] = W[token[t], :] * scale (one warp per token row, 16-byte vectors).
+// Backward: dW[token[t], :] += dout[t, :] * scale with vector fp32 reductions straight into the fp32 gradient
+// buffer: no dense (vocab x dim) temporary and no separate accumulation pass. Takes the place of
+// nn.Embedding's gather and embedding_dense_backward (src/kohakuwullm/models/backbone.py:73-122 uses nn.Embedding).
+namespace kwu {
+
+__global__ void __launch_bounds__(256)
+embedding_fwd_kernel(const long long* __restrict__ tokens, const __nv_bfloat16* __restrict__ W,
+                     __nv_bfloat16* __restrict__ out, int T, int D, int V, float scale) {
+  const int lane = threadIdx.x & 31;
+  const int wpb = blockDim.x >> 5;
+  for (int t = blockIdx.x * wpb + (threadIdx.x >> 5); t < T; t += gridDim.x * wpb) {
+    long long id = tokens[t];
+    id = id < 0 ? 0 : (id >= V ? V - 1 : id);
+    const uint4* src = reinterpret_cast<const uint4*>(W + static_cast<size_t>(id) * D);
+    uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * D);
+    for (int v = lane; v < D / 8; v += 32) {
+      uint4 a = src[v];
+      if (scale != 1.f) {
+        float f[8];
+        float2 x;
+        x = unpack_bf16(a.x); f[0] = x.x; f[1] = x.y; x = unpack_bf16(a.y); f[2] = x.x; f[3] = x.y;
+        x = unpack_bf16(a.z); f[4] = x.x; f[5] = x.y; x = unpack_bf16(a.w); f[6] = x.x; f[7] = x.y;
+        a = make_uint4(pack_bf16(f[0] * scale, f[1] * scale), pack_bf16(f[2] * scale, f[3] * scale),
+                       pack_bf16(f[4] * scale, f[5] * scale), pack_bf16(f[6] * scale, f[7] * scale));
+      }
+      dst[v] = a;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+embedding_bwd_kernel(const long long* __restrict__ tokens, const __nv_bfloat16* __restrict__ dout,
+                     float* __restrict__ dW, int T, int D, int V, float scale) {
+  const int lane = threadIdx.x & 31;
+  const int wpb = blockDim.x >> 5;
+  for (int t = blockIdx.x * wpb + (threadIdx.x >> 5); t < T; t += gridDim.x * wpb) {
+    const long long id = tokens[t];
+    if (id < 0 || id >= V) continue;
+    const uint4* src = reinterpret_cast<const uint4*>(dout + static_cast<size_t>(t) * D);
+    float* dst = dW + static_cast<size_t>(id) * D;
+    for (int v = lane; v < D / 8; v += 32) {
+      const uint4 a = src[v];
+      const float2 f0 = unpack_bf16(a.x), f1 = unpack_bf16(a.y), f2 = unpack_bf16(a.z), f3 = unpack_bf16(a.w);
+      red_add_f32x4(dst + 8 * v, f0.x * scale, f0.y * scale, f1.x * scale, f1.y * scale);
+      red_add_f32x4(dst + 8 * v + 4, f2.x * scale, f2.y * scale, f3.x * scale, f3.y * scale);
+    }
+  }
+}
+
+}  // namespace kwu
+
+KWU_API int kwu_embedding_fwd(const long long* tokens, const void* W, void* out, int T, int D, int V, float scale,
+                              void* stream) {
+  if (D % 8) { set_last_error("embedding: dim must be a multiple of 8"); return 7; }
+  if (T <= 0) return 0;
+  embedding_fwd_kernel<<<grid_for(T, 8), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      tokens, (const __nv_bfloat16*)W, (__nv_bfloat16*)out, T, D, V, scale); kwu::count_launch();
+  return check_launch("embedding_fwd");
+}
+
+// dW: fp32 (V, D), accumulated into.
+KWU_API int kwu_embedding_bwd(const long long* tokens, const void* dout, float* dW, int T, int D, int V, float scale,
+                              void* stream) {
+  if (D % 8) { set_last_error("embedding: dim must be a multiple of 8"); return 7; }
+  if (T <= 0) return 0;
+  embedding_bwd_kernel<<<grid_for(T, 8), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      tokens, (const __nv_bfloat16*)dout, dW, T, D, V, scale); kwu::count_launch();
+  return check_launch("embedding_bwd");
+}

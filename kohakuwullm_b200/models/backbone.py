@@ -105,8 +105,9 @@ class LMBackbone(nn.Module):
 
     # ------------------------------------------------------------------ forward
     def embed_tokens(self, tokens: torch.Tensor) -> torch.Tensor:
-        x = self.embed(tokens)
-        return x * self.embed_scale if self.embed_scale != 1.0 else x
+        from kohakuwullm_b200.ops.elementwise import embedding
+
+        return embedding(tokens, self.embed.weight, self.embed_scale)
 
     def prepare(self, seq_info: SeqInfo, device, dtype):
         """Per-forward constants shared by every layer: rotary tables and the attention work list."""

@@ -198,6 +198,7 @@ class _AttentionCore(torch.autograd.Function):
         native.check(rc, "flash_fwd")
         ctx.save_for_backward(qkv, q, k, out, lse, plan, sink_lse, q_norm, k_norm, cos, sin)
         ctx.cfg = (Hq, Hkv, window, scale, eps, do_norm)
+        ctx.norm_params = (q_norm, k_norm)   # Parameter objects: their ``main_grad`` takes the gradients directly
         return out
 
     @staticmethod
@@ -227,14 +228,17 @@ class _AttentionCore(torch.autograd.Function):
         native.check(rc, "flash_bwd")
         rot_half = 0 if cos is None else cos.shape[-1]
         dws = []
-        for src, g, dst, w, H in ((qkv[:, : Hq * D], dq, dqkv[:, : Hq * D], q_norm, Hq),
-                                  (qkv[:, Hq * D:(Hq + Hkv) * D], dk, dqkv[:, Hq * D:(Hq + Hkv) * D], k_norm, Hkv)):
-            dw = torch.zeros(D, dtype=torch.float32, device=qkv.device) if w is not None else None
+        for src, g, dst, w, H, wp in ((qkv[:, : Hq * D], dq, dqkv[:, : Hq * D], q_norm, Hq, ctx.norm_params[0]),
+                                      (qkv[:, Hq * D:(Hq + Hkv) * D], dk, dqkv[:, Hq * D:(Hq + Hkv) * D], k_norm, Hkv,
+                                       ctx.norm_params[1])):
+            mg = getattr(wp, "main_grad", None)
+            into_main = w is not None and mg is not None and mg.dtype == torch.float32 and mg.is_contiguous()
+            dw = (mg if into_main else torch.zeros(D, dtype=torch.float32, device=qkv.device)) if w is not None else None
             rc = L.kwu_qknorm_rope_bwd(native.ptr(src), ci(ld), native.ptr(g), ci(H * D), native.ptr(dst), ci(dld),
                                        native.ptr(w), native.ptr(dw), native.ptr(cos), native.ptr(sin), ci(T),
                                        ci(H), ci(D), ci(rot_half), cf(eps), ci(int(do_norm)), native.stream_ptr())
             native.check(rc, "qknorm_rope_bwd")
-            dws.append(dw)
+            dws.append(None if into_main else dw)
         dsink = None
         if sink_lse is not None and ctx.needs_input_grad[7]:
             dsink = -(torch.exp(sink_lse.float()[:, None] - lse) * delta).sum(1).to(sink_lse.dtype)

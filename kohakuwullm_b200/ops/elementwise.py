@@ -70,6 +70,7 @@ class _RMSNorm(torch.autograd.Function):
             )
         native.check(rc, "rmsnorm_fwd")
         ctx.emit_mx_grad = emit_mx_grad
+        ctx.weight_param = weight   # the Parameter object: its ``main_grad`` takes the weight gradient directly
         ctx.save_for_backward(h if h is not None else x2, weight, rstd)
         ctx.one_plus = one_plus
         ctx.has_res = residual is not None
@@ -93,10 +94,15 @@ class _RMSNorm(torch.autograd.Function):
                 dres = dres.contiguous()
         dx = torch.empty_like(xin)
         dw = partial = None
+        acc = 0
+        main_grad = getattr(ctx.weight_param, "main_grad", None)
         if weight is not None and ctx.needs_input_grad[1]:
             nblocks = L.kwu_rmsnorm_bwd_blocks(c_int(rows))
             partial = torch.empty(nblocks, cols, dtype=torch.float32, device=xin.device)
-            dw = torch.empty(cols, dtype=torch.float32, device=xin.device)
+            if main_grad is not None and main_grad.dtype == torch.float32 and main_grad.is_contiguous():
+                dw, acc = main_grad, 1      # summed straight into the trainer's fp32 gradient buffer
+            else:
+                dw = torch.empty(cols, dtype=torch.float32, device=xin.device)
         from kohakuwullm_b200.ops import mxfp8 as mx
 
         if ctx.emit_mx_grad and mx.can_emit(rows, cols) and cols <= 2048:
@@ -104,17 +110,19 @@ class _RMSNorm(torch.autograd.Function):
             rc = L.kwu_rmsnorm_bwd_mx(
                 native.ptr(xin), native.ptr(weight), native.ptr(rstd), native.ptr(dy2), native.ptr(dres),
                 native.ptr(dx), native.ptr(dw), native.ptr(partial), c_int(rows), c_int(cols),
-                c_int(int(ctx.one_plus)), c_int(0), native.ptr(q), c_int(cols), native.ptr(sf), native.stream_ptr())
+                c_int(int(ctx.one_plus)), c_int(acc), native.ptr(q), c_int(cols), native.ptr(sf), native.stream_ptr())
             mx.stash_quantized(dx, q, sf)
         else:
             rc = L.kwu_rmsnorm_bwd(
                 native.ptr(xin), native.ptr(weight), native.ptr(rstd), native.ptr(dy2), native.ptr(dres),
                 native.ptr(dx), native.ptr(dw), native.ptr(partial), c_int(rows), c_int(cols),
-                c_int(int(ctx.one_plus)), c_int(0), native.stream_ptr(),
+                c_int(int(ctx.one_plus)), c_int(acc), native.stream_ptr(),
             )
         native.check(rc, "rmsnorm_bwd")
         dxv = dx.view(ctx.shape)
-        if dw is not None:
+        if acc:
+            dw = None
+        elif dw is not None:
             dw = dw.to(weight.dtype)
         return dxv, dw, (dxv if ctx.has_res else None), None, None, None, None
 
@@ -235,6 +243,7 @@ class _QKNormRope(torch.autograd.Function):
         native.check(rc, "qknorm_rope_fwd")
         ctx.save_for_backward(x, weight, cos, sin)
         ctx.eps, ctx.do_norm = eps, do_norm
+        ctx.weight_param = weight
         return out
 
     @staticmethod
@@ -246,8 +255,11 @@ class _QKNormRope(torch.autograd.Function):
             dout = dout.contiguous()
         dx = torch.empty(T, H, D, dtype=x.dtype, device=x.device)
         dw = None
+        main_grad = getattr(ctx.weight_param, "main_grad", None)
+        into_main = main_grad is not None and main_grad.dtype == torch.float32 and main_grad.is_contiguous()
         if weight is not None and ctx.needs_input_grad[1]:
-            dw = torch.zeros(D, dtype=torch.float32, device=x.device)
+            # the kernel accumulates with atomics, so the trainer's fp32 buffer can take the sum directly
+            dw = main_grad if into_main else torch.zeros(D, dtype=torch.float32, device=x.device)
         rot_half = 0 if cos is None else cos.shape[-1]
         rc = L.kwu_qknorm_rope_bwd(
             native.ptr(x), c_int(x.stride(0)), native.ptr(dout), c_int(dout.stride(0)), native.ptr(dx),
@@ -257,7 +269,7 @@ class _QKNormRope(torch.autograd.Function):
         )
         native.check(rc, "qknorm_rope_bwd")
         if dw is not None:
-            dw = dw.to(weight.dtype)
+            dw = None if into_main else dw.to(weight.dtype)
         return dx, dw, None, None, None, None
 
 
@@ -276,3 +288,46 @@ def qknorm_rope(x, weight, cos, sin, eps=1e-6, do_norm=True):
     if ok:
         return _QKNormRope.apply(x, weight, cos, sin, eps, do_norm)
     return qknorm_rope_reference(x, weight, cos, sin, eps, do_norm)
+
+
+# ----------------------------------------------------------------------------- embedding
+class _Embedding(torch.autograd.Function):
+    """Row gather with an optional scale; the backward adds the token gradients straight into the weight's
+    fp32 ``main_grad`` (vector reductions), or into a fresh fp32 buffer when there is none."""
+
+    @staticmethod
+    def forward(ctx, tokens, weight, scale):
+        L = native.require()
+        flat = tokens.reshape(-1).contiguous()
+        V, D = weight.shape
+        out = torch.empty(flat.numel(), D, dtype=weight.dtype, device=weight.device)
+        rc = L.kwu_embedding_fwd(native.ptr(flat), native.ptr(weight), native.ptr(out), c_int(flat.numel()), c_int(D),
+                                 c_int(V), c_float(scale), native.stream_ptr())
+        native.check(rc, "embedding_fwd")
+        ctx.save_for_backward(flat)
+        ctx.weight_param, ctx.scale, ctx.shape = weight, scale, (V, D)
+        return out.view(*tokens.shape, D)
+
+    @staticmethod
+    def backward(ctx, dout):
+        L = native.require()
+        (flat,) = ctx.saved_tensors
+        V, D = ctx.shape
+        w = ctx.weight_param
+        main_grad = getattr(w, "main_grad", None)
+        use_main = main_grad is not None and main_grad.dtype == torch.float32 and main_grad.is_contiguous()
+        target = main_grad if use_main else torch.zeros(V, D, dtype=torch.float32, device=dout.device)
+        d2 = dout.reshape(-1, D).contiguous()
+        rc = L.kwu_embedding_bwd(native.ptr(flat), native.ptr(d2), native.ptr(target), c_int(flat.numel()), c_int(D),
+                                 c_int(V), c_float(ctx.scale), native.stream_ptr())
+        native.check(rc, "embedding_bwd")
+        return None, (None if use_main else target.to(w.dtype)), None
+
+
+def embedding(tokens: torch.Tensor, weight: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """``weight[tokens] * scale``; native gather / scatter-add on bf16 CUDA weights, PyTorch elsewhere."""
+    if native.available() and weight.is_cuda and weight.dtype == torch.bfloat16 and weight.shape[1] % 8 == 0 \
+            and tokens.dtype == torch.long:
+        return _Embedding.apply(tokens, weight, float(scale))
+    x = torch.nn.functional.embedding(tokens, weight)
+    return x * scale if scale != 1.0 else x

@@ -91,3 +91,50 @@ def test_qknorm_rope_fwd_bwd(rot_half, affine):
     _close(src.grad[:, : H * D], srcr.grad[:, : H * D], 3e-2)
     if affine:
         _close(wn.grad, wr.grad, 3e-2)
+
+
+def test_embedding_forward_backward_and_main_grad_accumulation():
+    from kohakuwullm_b200.ops.elementwise import embedding
+
+    torch.manual_seed(0)
+    V, D, T = 1000, 256, 3000
+    w = torch.randn(V, D, device="cuda").bfloat16().requires_grad_()
+    tok = torch.randint(0, V, (T,), device="cuda")
+    dy = torch.randn(T, D, device="cuda").bfloat16()
+    y = embedding(tok, w, 2.0)
+    ref = torch.nn.functional.embedding(tok, w.detach().float()) * 2.0
+    torch.testing.assert_close(y.float(), ref, rtol=1e-2, atol=1e-2)
+    y.backward(dy)
+    gref = torch.zeros(V, D, device="cuda").index_add_(0, tok, dy.float() * 2.0)
+    torch.testing.assert_close(w.grad.float(), gref, rtol=2e-2, atol=2e-2)
+    # with a main_grad buffer the sum lands there (fp32, exact up to addition order) and .grad stays empty
+    w2 = w.detach().clone().requires_grad_()
+    w2.main_grad = torch.ones(V, D, device="cuda")
+    embedding(tok, w2, 2.0).backward(dy)
+    assert w2.grad is None
+    torch.testing.assert_close(w2.main_grad, gref + 1.0, rtol=1e-5, atol=1e-4)
+
+
+def test_norm_weight_gradients_accumulate_into_main_grad():
+    from kohakuwullm_b200.ops.elementwise import qknorm_rope, rmsnorm
+
+    torch.manual_seed(1)
+    x = torch.randn(512, 384, device="cuda").bfloat16().requires_grad_()
+    dy = torch.randn(512, 384, device="cuda").bfloat16()
+    w = torch.rand(384, device="cuda").requires_grad_()
+    rmsnorm(x, w).backward(dy)
+    w2 = w.detach().clone().requires_grad_()
+    w2.main_grad = torch.full((384,), 3.0, device="cuda")
+    rmsnorm(x.detach().requires_grad_(), w2).backward(dy)
+    assert w2.grad is None
+    torch.testing.assert_close(w2.main_grad, w.grad + 3.0, rtol=1e-4, atol=1e-3)
+    q = torch.randn(300, 4, 64, device="cuda").bfloat16().requires_grad_()
+    dq = torch.randn(300, 4, 64, device="cuda").bfloat16()
+    ang = torch.rand(300, 32, device="cuda") * 6.28
+    qw = torch.rand(64, device="cuda").requires_grad_()
+    qknorm_rope(q, qw, ang.cos(), ang.sin()).backward(dq)
+    qw2 = qw.detach().clone().requires_grad_()
+    qw2.main_grad = torch.full((64,), -1.0, device="cuda")
+    qknorm_rope(q.detach().requires_grad_(), qw2, ang.cos(), ang.sin()).backward(dq)
+    assert qw2.grad is None
+    torch.testing.assert_close(qw2.main_grad, qw.grad - 1.0, rtol=1e-4, atol=1e-3)
