@@ -42,6 +42,10 @@ struct GemmParams {
   // each adding its partial product into the fp32 output with vector reductions (needs out_fp32 and
   // C += semantics). Used by weight gradients, whose outputs have too few tiles to fill the GPU.
   int splits;
+  // stream-K (group_mode 0 only, fp32 C += semantics): the (tile, k-block) work units are cut into
+  // `streamk` equal contiguous ranges, one per CTA; a CTA adds the partial product of every tile its range
+  // touches into the output with vector reductions, so all SMs finish together whatever the tile count.
+  int streamk;
   // grouped (mixture-of-experts) modes
   //   1: rows grouped by expert: row tile t reads group_tiles[t] = (m0, expert, valid); the expert picks
   //      a block of `group_b_rows` rows of B (K-major: output rows; MN-major: contraction rows)
@@ -118,6 +122,27 @@ __device__ __forceinline__ bool decode_tile(const GemmParams& p, int tile, int n
   return true;
 }
 
+// Work item number `i` of this CTA. 0: none left; 1: `t` holds work; 2: nothing to do for this index, go on.
+template <int BN>
+__device__ __forceinline__ int next_work(const GemmParams& p, int i, int num_tiles, int num_kb, TileInfo& t) {
+  if (p.streamk > 0) {
+    const long long units = static_cast<long long>(p.tiles_m) * p.tiles_n * num_kb;
+    const long long u0 = units * blockIdx.x / p.streamk, u1 = units * (blockIdx.x + 1) / p.streamk;
+    const long long tile = u0 / num_kb + i;
+    const long long start = max(u0, tile * num_kb), end = min(u1, (tile + 1) * num_kb);
+    if (start >= end) return 0;
+    t.b_row_off = 0; t.c_off = 0;
+    t.m0 = static_cast<int>(tile / p.tiles_n) * GEMM_BM;
+    t.n0 = static_cast<int>(tile % p.tiles_n) * BN;
+    t.k_begin = static_cast<int>(start - tile * num_kb) * GEMM_BK;
+    t.nkb = static_cast<int>(end - start);
+    return 1;
+  }
+  const int tile = blockIdx.x + i * gridDim.x;
+  if (tile >= num_tiles) return 0;
+  return decode_tile<BN>(p, tile, num_kb, t) ? 1 : 2;
+}
+
 template <int BN, bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -171,9 +196,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int wi = 0; ok; ++wi) {
         TileInfo ti;
-        if (!decode_tile<BN>(p, tile, num_kb, ti)) continue;
+        const int got = next_work<BN>(p, wi, num_tiles, num_kb, ti);
+        if (got == 0) break;
+        if (got == 2) continue;
         const int m0 = ti.m0, n0 = ti.n0;
         for (int kb = 0; kb < ti.nkb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_EMPTY)) {
@@ -212,9 +239,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int wi = 0; ok; ++wi) {
         TileInfo ti;
-        if (!decode_tile<BN>(p, tile, num_kb, ti)) continue;
+        const int got = next_work<BN>(p, wi, num_tiles, num_kb, ti);
+        if (got == 0) break;
+        if (got == 2) continue;
         const int as = it & 1;
         const uint32_t aphase = (it >> 1) & 1;
         ++it;
@@ -252,9 +281,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int quarter = warp & 3;  // TMEM lane quarter this warp may read
     int it = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+    for (int wi = 0; ok; ++wi) {
       TileInfo ti;
-      if (!decode_tile<BN>(p, tile, num_kb, ti)) continue;
+      const int got = next_work<BN>(p, wi, num_tiles, num_kb, ti);
+      if (got == 0) break;
+      if (got == 2) continue;
       const int as = it & 1;
       const uint32_t aphase = (it >> 1) & 1;
       ++it;
@@ -343,7 +374,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 v.z = __uint_as_float(r[4 * j + 2]) * p.alpha;
                 v.w = __uint_as_float(r[4 * j + 3]) * p.alpha;
                 float4* d4 = reinterpret_cast<float4*>(dst) + j;
-                if (p.splits > 1) {
+                if (p.splits > 1 || p.streamk > 0) {
                   red_add_f32x4(dst + 4 * j, v.x, v.y, v.z, v.w);
                   continue;
                 }
@@ -358,7 +389,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               for (int j = 0; j < 32; ++j) {
                 if (col0 + j < p.N) {
                   float v = __uint_as_float(r[j]) * p.alpha;
-                  if (p.splits > 1) { atomicAdd(dst + j, v); continue; }
+                  if (p.splits > 1 || p.streamk > 0) { atomicAdd(dst + j, v); continue; }
                   if (p.accumulate) v += dst[j];
                   dst[j] = v;
                 }
@@ -464,7 +495,7 @@ template <int BN, bool A_MN, bool B_MN, int EPI = EPI_STORE>
 static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb,
                        int ldc, int out_fp32, int accumulate, float alpha, int max_ctas,
                        cudaStream_t stream, int* status, const EpiArgs& ea = EpiArgs(),
-                       const GroupArgs& ga = GroupArgs(), int b_total_rows = 0, int splits = 1) {
+                       const GroupArgs& ga = GroupArgs(), int b_total_rows = 0, int splits = 1, bool streamk = false) {
   using S = GemmSmem<BN>;
   CUtensorMap tmA, tmB;
   int rc;
@@ -497,6 +528,7 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
   p.tiles_n = (N + BN - 1) / BN;
   p.status = status;
   p.splits = (ga.mode == 0 && out_fp32 && accumulate) ? splits : 1;
+  p.streamk = 0;
   p.group_mode = ga.mode; p.group_tiles = ga.tiles; p.group_offsets = ga.offsets;
   p.group_b_rows = ga.b_rows; p.num_groups = ga.num_groups; p.c_group_stride = ga.c_stride;
   p.labels = ea.labels; p.partial = ea.partial; p.target_logit = ea.target_logit;
@@ -517,6 +549,12 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
   int cap = num_sms();
   if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;
   if (grid > cap) grid = cap;
+  if (streamk && ga.mode == 0 && out_fp32 && accumulate && EPI == EPI_STORE) {
+    const long long units = static_cast<long long>(p.tiles_m) * p.tiles_n * ((K + GEMM_BK - 1) / GEMM_BK);
+    grid = static_cast<int>(units < cap ? units : cap);
+    p.splits = 1;
+    p.streamk = grid;
+  }
   kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, C, p); kwu::count_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
@@ -550,21 +588,21 @@ KWU_API int kwu_gemm_bf16(const void* A, const void* B, void* C, int M, int N, i
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int BN = pick_bn(M, N, bn);
   int splits = 1;
-  if (out_fp32 && accumulate && bn == 0 && K >= 2048) {
-    // weight-gradient shape: few output tiles, long contraction. Prefer the wide tile and cut K so
-    // that the work items fill the SMs.
+  bool streamk = false;
+  if (out_fp32 && accumulate && bn == 0 && K >= 1024) {
+    // weight-gradient shape: few output tiles, long contraction, C += semantics. Wide tiles, and the
+    // (tile, k-block) units are dealt out evenly over the SMs (stream-K) unless the tiles already fill
+    // whole waves.
     const int sms = num_sms();
     const long t256 = static_cast<long>((M + GEMM_BM - 1) / GEMM_BM) * ((N + 255) / 256);
-    if (t256 <= sms) {
-      BN = 256;
-      while (splits < 4 && t256 * (splits + 1) <= sms && K / (splits + 1) >= 1024) ++splits;
-    }
+    BN = 256;
+    streamk = (t256 % sms) != 0;
   }
 #define KWU_GEMM_CASE(bnv, amn, bmn)                                                              \
   if (BN == bnv && a_mn == amn && b_mn == bmn)                                                    \
     return launch_gemm<bnv, amn != 0, bmn != 0>(A, B, C, M, N, K, lda, ldb, ldc, out_fp32,        \
                                                 accumulate, alpha, max_ctas, st, status, EpiArgs(), \
-                                                GroupArgs(), 0, splits);
+                                                GroupArgs(), 0, splits, streamk);
   KWU_GEMM_CASE(128, 0, 0) KWU_GEMM_CASE(128, 0, 1) KWU_GEMM_CASE(128, 1, 0) KWU_GEMM_CASE(128, 1, 1)
   KWU_GEMM_CASE(256, 0, 0) KWU_GEMM_CASE(256, 0, 1) KWU_GEMM_CASE(256, 1, 0) KWU_GEMM_CASE(256, 1, 1)
 #undef KWU_GEMM_CASE

@@ -63,14 +63,16 @@ def test_linear_autograd_matches_torch():
         assert err <= 1e-2 * want.abs().max().item()
 
 
-def test_split_k_weight_gradient_accumulates_exactly_once():
-    """fp32 accumulate with a long contraction takes the split-K path (vector reductions into C)."""
+@pytest.mark.parametrize("M,N,K", [(1280, 1280, 4096), (7168, 1280, 4096), (1792, 1280, 8192), (384, 1000, 1024 + 64)])
+def test_stream_k_weight_gradient_accumulates_exactly_once(M, N, K):
+    """fp32 C += with a long contraction is scheduled stream-K: every CTA takes an equal run of (tile, k-block)
+    units and adds its partial tiles into C with vector reductions; each unit must be counted exactly once."""
     from kohakuwullm_b200.ops import native
     from kohakuwullm_b200.ops.gemm import matmul
 
-    a, b, ref = _operands(1280, 1280, 4096, True, True, seed=5)
-    out = torch.full((1280, 1280), 2.0, device="cuda", dtype=torch.float32)
+    a, b, ref = _operands(M, N, K, True, True, seed=5)
+    out = torch.full((M, N), 2.0, device="cuda", dtype=torch.float32)
     matmul(a, b, a_mn=True, b_mn=True, out=out, accumulate=True)
     torch.cuda.synchronize()
     native.check_status()
-    torch.testing.assert_close(out, ref + 2.0, rtol=1e-4, atol=2e-3)
+    torch.testing.assert_close(out, ref + 2.0, rtol=1e-4, atol=2e-3 * (K / 4096) ** 0.5 + 1e-3)
