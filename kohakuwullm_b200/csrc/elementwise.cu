@@ -578,12 +578,13 @@ KWU_API int kwu_rmsnorm_bwd_blocks(int rows) { return grid_for(rows, 8, 296); }
 
 static int rmsnorm_bwd_impl(const void* x, const float* w, const float* rstd, const void* dy,
                             const void* dres, void* dx, float* dw, float* dw_partial, int rows,
-                            int cols, int one_plus, int accumulate_dw, const MxOut mx, void* stream) {
+                            int cols, int one_plus, int accumulate_dw, const MxOut mx, void* stream,
+                            int max_blocks = 296) {
   if (cols % 8) { set_last_error("rmsnorm: cols must be a multiple of 8"); return 7; }
   if (mx.q && cols > 2048) { set_last_error("rmsnorm_bwd_mx: rows wider than 2048 columns are not supported"); return 7; }
   if (rows <= 0) return 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  int grid = grid_for(rows, 8, 296);
+  int grid = grid_for(rows, 8, max_blocks);
   const bool want_dw = (w != nullptr && dw != nullptr && dw_partial != nullptr);
   const size_t dw_smem = want_dw ? cols * sizeof(float) : 0;
   const int nv = (cols / 8 + 31) / 32;
@@ -755,18 +756,11 @@ KWU_API int kwu_rmsnorm_bwd_noalloc(const void* x, const float* w, const float* 
     partial = noalloc_scratch_address();
     if (!partial) return 12;
   }
-  const int grid = grid_for(rows, 8, KWU_NOALLOC_MAX_BLOCKS);
-  // every block overwrites its own row of the scratch before the column sum reads it, so nothing in
-  // the array has to start at zero even though it still holds the previous call's partial sums
-  rmsnorm_bwd_kernel<<<grid, 256, want_dw ? cols * sizeof(float) : 0, st>>>(
-      (const __nv_bfloat16*)x, w, rstd, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)dres,
-      (__nv_bfloat16*)dx, partial, rows, cols, one_plus); kwu::count_launch();
-  if (int rc = check_launch("rmsnorm_bwd_noalloc")) return rc;
-  if (want_dw) {
-    colsum_partials_kernel<<<(cols + 255) / 256, 256, 0, st>>>(partial, dw, grid, cols, accumulate_dw); kwu::count_launch();
-    return check_launch("rmsnorm_bwd_noalloc_dw");
-  }
-  return 0;
+  // same kernels and the same choice between them as kwu_rmsnorm_bwd; only the scratch differs. Every block
+  // overwrites its own row of the scratch before the column sum reads it, so nothing in the array has to
+  // start at zero even though it still holds the previous call's partial sums
+  return rmsnorm_bwd_impl(x, w, rstd, dy, dres, dx, want_dw ? dw : nullptr, partial, rows, cols, one_plus,
+                          accumulate_dw, make_mx(nullptr, 0, nullptr, cols), stream, KWU_NOALLOC_MAX_BLOCKS);
 }
 
 // --------------------------------------------------------------------------- embedding
