@@ -57,6 +57,9 @@ def main(argv=None):
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--expert-parallel", action="store_true", help="split MoE experts over the ranks (EP + DP)")
     ap.add_argument("--grad-sync", default=None, choices=["nccl", "fused"])
+    ap.add_argument("--router-bias-std", type=float, default=0.0,
+                    help="seeded N(0, std) selection bias on every router: a skewed expert load")
+    ap.add_argument("--ep-capacity", type=float, default=2.0, help="expert-parallel receive capacity factor")
     ap.add_argument("--set", action="append", default=[], help="config override KEY=VALUE (python literal)")
     args = ap.parse_args(argv)
 
@@ -105,7 +108,13 @@ def main(argv=None):
 
         with torch.device(dev):
             model = LMBackbone(cfg)
-        engine = TrainEngine(model, lr=1e-4, param_dtype=torch.bfloat16,
+        if args.router_bias_std > 0:
+            gen = torch.Generator(device=dev).manual_seed(4242)     # the same skew on every rank
+            for m in model.modules():
+                if hasattr(m, "expert_bias"):
+                    m.expert_bias.copy_(torch.randn(m.expert_bias.shape, generator=gen, device=dev) * args.router_bias_std)
+                    m.bias_update_rate = 0.0                          # keep the skew for the whole measurement
+        engine = TrainEngine(model, lr=1e-4, param_dtype=torch.bfloat16, ep_capacity_factor=args.ep_capacity,
                              grad_sync=args.grad_sync or ("fused" if world > 1 else "nccl"),
                              cuda_graphs=not args.no_graphs, expert_parallel=args.expert_parallel)
         packs = [p.to(dev) for p in make_packs(args.accum, args.micro_tokens, args.len_min, args.len_max,

@@ -143,7 +143,12 @@ class _FusedLinearCE(torch.autograd.Function):
                                     native.ptr(native.status_word()))
             native.check(rc, "gemm_dlogits")
             if ctx.needs_input_grad[0]:
-                matmul(dl, w, b_mn=True, out=dh[s:e])
+                # contraction over the whole vocabulary with few output tiles: accumulate in fp32 so the
+                # (tile, k-block) units can be dealt out evenly over the SMs, then round once
+                dh32 = _scratch_buffer("ce_dh32", (n, D), torch.float32, h.device)
+                dh32.zero_()
+                matmul(dl, w, b_mn=True, out=dh32, accumulate=True)
+                dh[s:e].copy_(dh32)
             if ctx.needs_input_grad[1]:
                 target = main_grad if main_grad is not None else dw
                 matmul(dl, h[s:e], a_mn=True, b_mn=True, out=target, accumulate=True)
