@@ -67,7 +67,7 @@ def _install_shims() -> None:
 
 def run_reference(args, micro_tokens, grad_accum, len_min, len_max, metric, ClockSampler, timed, dist_setup):
     if not (REF / "kohakuwullm").is_dir():
-        _unavailable("baseline/_ref is not installed (pip install --no-index --no-deps --target baseline/_ref /root/reference)")
+        _unavailable("baseline/_ref is not installed (pip install --no-index --no-deps --target baseline/_ref <reference checkout>)")
     sys.path.insert(0, str(REF))
     _install_shims()
     try:

@@ -186,10 +186,14 @@ class _GroupedLinear(torch.autograd.Function):
     """``out[rows of expert e] = rows @ W[e]^T`` with W (E, N, K)."""
 
     @staticmethod
-    def forward(ctx, rows, W, plan: DispatchPlan):
+    def forward(ctx, rows, W, plan: DispatchPlan, out=None, dgrad_out=None):
+        """``out`` / ``dgrad_out``: caller-owned (max_rows, N) / (max_rows, K) buffers for the product and for
+        the input gradient (expert parallelism passes its peer-visible output buffer, saving a copy)."""
         L = native.require()
         E, N, K = W.shape
-        out = torch.empty(plan.max_rows, N, dtype=rows.dtype, device=rows.device)
+        if out is None:
+            out = torch.empty(plan.max_rows, N, dtype=rows.dtype, device=rows.device)
+        ctx.dgrad_out = dgrad_out
         rc = L.kwu_gemm_bf16_grouped_rows(native.ptr(rows), native.ptr(W), native.ptr(out), c_int(plan.max_rows), c_int(N),
                                           c_int(K), c_int(rows.stride(0)), c_int(K), c_int(N), c_int(0), c_int(E),
                                           native.ptr(plan.tiles), c_int(plan.tiles.shape[0]), c_int(0),
@@ -208,7 +212,8 @@ class _GroupedLinear(torch.autograd.Function):
         dout = dout.contiguous()
         drows = dW = None
         if ctx.needs_input_grad[0]:
-            drows = torch.empty(plan.max_rows, K, dtype=rows.dtype, device=rows.device)
+            drows = ctx.dgrad_out if ctx.dgrad_out is not None else \
+                torch.empty(plan.max_rows, K, dtype=rows.dtype, device=rows.device)
             # dx = dy W_e : B = W viewed as (E*N, K) stored [contraction N rows][K cols] per expert
             rc = L.kwu_gemm_bf16_grouped_rows(native.ptr(dout), native.ptr(W), native.ptr(drows), c_int(plan.max_rows),
                                               c_int(K), c_int(N), c_int(dout.stride(0)), c_int(K), c_int(K), c_int(1),
@@ -225,7 +230,7 @@ class _GroupedLinear(torch.autograd.Function):
             native.check(rc, "grouped_gemm_wgrad")
             if main_grad is None:
                 dW = target.to(W.dtype)
-        return drows, dW, None
+        return drows, dW, None, None, None
 
 
 class _Combine(torch.autograd.Function):
@@ -258,14 +263,15 @@ class _Combine(torch.autograd.Function):
         return drows, dw.view(ctx.wshape).to(ctx.wdtype), None, None
 
 
-def grouped_linear(rows, W, plan, qweight=None):
+def grouped_linear(rows, W, plan, qweight=None, out=None, dgrad_out=None):
     """Expert-grouped linear: bf16 tcgen05 GEMM, or the MXFP8 recipe when ``qweight`` (a
-    ``GroupedQuantizedWeight`` of ``W``) is given."""
+    ``GroupedQuantizedWeight`` of ``W``) is given. ``out`` / ``dgrad_out``: optional caller-owned buffers for
+    the product and for the input gradient."""
     if qweight is not None:
         from kohakuwullm_b200.ops.mxfp8 import _MXFP8GroupedLinear
 
-        return _MXFP8GroupedLinear.apply(rows, W, qweight, plan)
-    return _GroupedLinear.apply(rows, W, plan)
+        return _MXFP8GroupedLinear.apply(rows, W, qweight, plan, out, dgrad_out)
+    return _GroupedLinear.apply(rows, W, plan, out, dgrad_out)
 
 
 def routed_experts(x, idx, weight, counts, w_in, w_out, q_in=None, q_out=None):

@@ -155,14 +155,20 @@ class ExpertParallel:
         native.check(rc, "ep_copy_rows")
         return rows
 
+    def output_rows(self) -> torch.Tensor:
+        """The peer-visible (cap, D) output buffer: a GEMM that writes its product (forward) or its input
+        gradient (backward) straight into it saves the copy in ``_publish_rows``."""
+        return self._ws["yout"]
+
     def _publish_rows(self, rows, plan):
-        """private rows -> output buffer, then barrier."""
+        """private rows -> output buffer (skipped when the rows already live there), then barrier."""
         L = native.require()
         ws = self._ws
-        rc = L.kwu_ep_copy_rows(native.ptr(rows), native.ptr(ws["yout"]), native.ptr(plan.offsets),
-                                native.ptr(plan.totals), c_int(ws["El"]), c_int(rows.shape[1]), c_int(0),
-                                native.stream_ptr())
-        native.check(rc, "ep_copy_rows")
+        if rows.data_ptr() != ws["yout"].data_ptr():
+            rc = L.kwu_ep_copy_rows(native.ptr(rows), native.ptr(ws["yout"]), native.ptr(plan.offsets),
+                                    native.ptr(plan.totals), c_int(ws["El"]), c_int(rows.shape[1]), c_int(0),
+                                    native.stream_ptr())
+            native.check(rc, "ep_copy_rows")
         self._barrier(ws, FLAG_OUTPUT)
 
     def _pull(self, plan, w, T, D, keep: bool):
@@ -234,9 +240,10 @@ def ep_routed_experts(ep: ExpertParallel, x, idx, weight, counts, w_in_local, w_
     T, D = x.shape
     plan = ep.plan(idx, counts, D)
     rows = ep.dispatch(x, plan)
-    h = grouped_linear(rows, w_in_local, plan, q_in)
+    stage = ep.output_rows()   # forward: the second GEMM's product; backward: the first GEMM's input gradient
+    h = grouped_linear(rows, w_in_local, plan, q_in, dgrad_out=stage)
     a = swiglu(h)
-    y_rows = grouped_linear(a, w_out_local, plan, q_out)
+    y_rows = grouped_linear(a, w_out_local, plan, q_out, out=stage)
     return ep.combine(y_rows, weight, plan, T)
 
 

@@ -1,5 +1,5 @@
 """The C++ CPU oracles (csrc/cpu/oracle.cpp) against the PyTorch references of the same rules: two
-independent statements of every kernel family's arithmetic must agree before either is used to judge a
+independent statements of every kernel family's arithmetic must agree before either is used to check a
 CUDA kernel."""
 
 import torch
