@@ -361,3 +361,22 @@ def gather_expert_state(state: dict, model: nn.Module, group=None) -> dict:
             dist.all_gather(parts, p.data.contiguous(), group=g)
             out[name] = torch.cat(parts, 0)
     return out
+
+
+@torch.no_grad()
+def scatter_expert_state(state: dict, model: nn.Module, group=None) -> dict:
+    """The inverse of ``gather_expert_state``: from a full-model state dict keep, for every ``ep_local``
+    parameter, this rank's slice of the expert dimension (so a checkpoint written by any layout loads
+    into an expert-parallel model of any group size that divides the expert count)."""
+    g = group if group is not None else dist.group.WORLD
+    world, rank = dist.get_world_size(g), dist.get_rank(g)
+    out = dict(state)
+    for name, p in model.named_parameters():
+        if getattr(p, "ep_local", False) and name in out:
+            full = out[name]
+            if full.shape[0] == p.shape[0]:
+                continue                      # already a local slice
+            if full.shape[0] != p.shape[0] * world:
+                raise ValueError(f"{name}: {full.shape[0]} experts do not split into {world} x {p.shape[0]}")
+            out[name] = full[rank * p.shape[0]:(rank + 1) * p.shape[0]].clone()
+    return out

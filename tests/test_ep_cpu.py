@@ -11,7 +11,7 @@ import torch.multiprocessing as mp
 
 from kohakuwullm_b200.data.packing import collate_packed
 from kohakuwullm_b200.models import LMBackbone, get_preset
-from kohakuwullm_b200.parallel.ep import gather_expert_state
+from kohakuwullm_b200.parallel.ep import gather_expert_state, scatter_expert_state
 from kohakuwullm_b200.training.engine import TrainEngine
 
 
@@ -36,6 +36,12 @@ def _worker(rank, world, port, path):
     assert moe and moe[0].w_in.shape[0] == 4 and "fp32_ep" in eng.flat.groups
     out = eng.step([collate_packed(_docs()[rank::world])])
     state = gather_expert_state({k: v.detach().clone() for k, v in eng.model.state_dict().items()}, eng.model)
+    # a full-model state dict loads back into the sharded model: every rank keeps its own expert slice
+    back = scatter_expert_state(state, eng.model)
+    for name, p in eng.model.named_parameters():
+        if getattr(p, "ep_local", False):
+            assert torch.equal(back[name], p.detach()), name
+    eng.model.load_state_dict(back)
     if rank == 0:
         torch.save({"loss": float(out["loss"]), "norm": float(out["grad_norm"]), "state": state}, path)
     dist.barrier()
