@@ -131,6 +131,7 @@ struct MxGemmParams {
   // experts' matrices stacked along its rows, `group_n` rows each (a multiple of 128)
   const int4* group_tiles;
   int group_n;
+  int sfb_chunk_rows;  // number of 128-row scale chunks B has (chunk indices are clamped to it)
   int* status;
 };
 
@@ -154,9 +155,10 @@ template <int BN>
 struct MxSmem {
   static constexpr int A_BYTES = MX_BM * MX_BK;
   static constexpr int B_BYTES = BN * MX_BK;
-  static constexpr int SFB_CHUNKS = (BN + 127) / 128;
+  // a tile whose width is not a multiple of 128 can start inside a scale chunk and then touches one more
+  static constexpr int SFB_CHUNKS = (BN % 128 == 0) ? BN / 128 : BN / 128 + 1;
   static constexpr int SF_BYTES = 512 + SFB_CHUNKS * 512;
-  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + 1024;  // data + scale area (padded to 1 KB)
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + (SF_BYTES + 1023) / 1024 * 1024;  // data + scale area
   static constexpr int STAGES = (BN > 192) ? 4 : ((BN > 128) ? 5 : 6);
   static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 + 1024;
 };
@@ -245,9 +247,12 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           tma_load_2d(sb, &tmB, &full_bar[stage], kb * MX_BK, b_row0);
           bulk_load_1d(ssf, p.sfa + (static_cast<size_t>(tm) * num_kb + kb) * 512, 512, &full_bar[stage]);
 #pragma unroll
-          for (int c = 0; c < S::SFB_CHUNKS; ++c)
-            bulk_load_1d(ssf + 512 + c * 512,
-                         p.sfb + (static_cast<size_t>(b_row0 / 128 + c) * num_kb + kb) * 512, 512, &full_bar[stage]);
+          for (int c = 0; c < S::SFB_CHUNKS; ++c) {
+            // rows past the end of B belong to masked output columns: any valid chunk will do for them
+            const int chunk = min(b_row0 / 128 + c, p.sfb_chunk_rows - 1);
+            bulk_load_1d(ssf + 512 + c * 512, p.sfb + (static_cast<size_t>(chunk) * num_kb + kb) * 512, 512,
+                         &full_bar[stage]);
+          }
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
@@ -262,10 +267,10 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       int it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        {
-          int m0, n0, b_row0;
-          if (!mx_decode_tile(p, tile, BN, m0, n0, b_row0)) continue;
-        }
+        int m0, n0, b_row0;
+        if (!mx_decode_tile(p, tile, BN, m0, n0, b_row0)) continue;
+        // the tile's first B row sits (b_row0 % 128) / 32 columns into its first scale chunk
+        const uint32_t sfb_off = static_cast<uint32_t>((b_row0 & 127) >> 5);
         const int as = it & 1;
         const uint32_t aphase = (it >> 1) & 1;
         ++it;
@@ -294,7 +299,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             const uint64_t ad = make_smem_desc(sa + k * 32, 16, 1024, SWZ_128B);
             const uint64_t bd = make_smem_desc(sb + k * 32, 16, 1024, SWZ_128B);
             mma_mxf8_ss(d_tmem, ad, bd, make_idesc_mxf8(MX_BM, BN, k, k), tmem_base + SFA_COL,
-                        tmem_base + SFB_COL, (kb > 0 || k > 0) ? 1u : 0u);
+                        tmem_base + SFB_COL + sfb_off, (kb > 0 || k > 0) ? 1u : 0u);
           }
           tc_commit(&empty_bar[stage]);
           if (++stage == STAGES) {
@@ -402,6 +407,7 @@ static int launch_mx(const void* A, const void* B, void* C, int M, int N, int K,
   p.tiles_n = (N + BN - 1) / BN;
   p.group_tiles = group_tiles;
   p.group_n = N;
+  p.sfb_chunk_rows = static_cast<int>((static_cast<long long>(N) * n_groups + 127) / 128);
   p.status = status;
   auto kern = gemm_mxfp8_kernel<BN>;
   static bool attr_set = false;
@@ -421,12 +427,19 @@ static int launch_mx(const void* A, const void* B, void* C, int M, int N, int K,
   return 0;
 }
 
-// B's scale chunks are indexed by 128-row tiles, so a column tile must start on a 128 boundary:
-// BN is restricted to multiples of 128 unless a single tile covers all of N.
+// Tile width: 128, or 160 when that needs fewer (width x rounds) column units on this many SMs. A 160-wide
+// tile may start 32, 64 or 96 rows into a scale chunk; the kernel loads the two chunks it touches and offsets
+// the scale address by whole TMEM columns (32 rows each).
 static int pick_bn_mx(int M, int N, int forced) {
-  if (forced == 128) return 128;
-  // BN = 128 is the only width whose tiles always start on a scale-chunk boundary
-  return 128;
+  if (forced == 128 || forced == 160) return forced;
+  int sms = 0, dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (sms <= 0) sms = 148;
+  const long tm = (M + MX_BM - 1) / MX_BM;
+  const long c128 = ((tm * ((N + 127) / 128) + sms - 1) / sms) * 128;
+  const long c160 = ((tm * ((N + 159) / 160) + sms - 1) / sms) * 160;
+  return c160 < c128 ? 160 : 128;
 }
 
 }  // namespace kwu
@@ -499,7 +512,9 @@ KWU_API int kwu_gemm_mxfp8(const void* A, const void* sfa, const void* B, const 
   if (M <= 0 || N <= 0) return 0;
   if (K % 128) { set_last_error("gemm_mxfp8: K must be a multiple of 128 (got %d)", K); return 7; }
   const int BN = pick_bn_mx(M, N, bn);
-  (void)BN;
+  if (BN == 160)
+    return launch_mx<160>(A, B, C, M, N, K, lda, ldb, ldc, (const uint8_t*)sfa, (const uint8_t*)sfb, out_fp32,
+                          accumulate, alpha, reinterpret_cast<cudaStream_t>(stream), status);
   return launch_mx<128>(A, B, C, M, N, K, lda, ldb, ldc, (const uint8_t*)sfa, (const uint8_t*)sfb, out_fp32,
                         accumulate, alpha, reinterpret_cast<cudaStream_t>(stream), status);
 }

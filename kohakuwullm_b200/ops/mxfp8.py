@@ -95,8 +95,9 @@ def quantize_transposed(x: torch.Tensor, out_q=None, out_sf=None):
     return q, sf
 
 
-def gemm(a_q, a_sf, b_q, b_sf, out=None, out_dtype=torch.bfloat16, accumulate=False, alpha=1.0):
-    """``out (+)= alpha * A B^T`` with A (M,K), B (N,K) both e4m3 with per-32 scales along K."""
+def gemm(a_q, a_sf, b_q, b_sf, out=None, out_dtype=torch.bfloat16, accumulate=False, alpha=1.0, bn: int = 0):
+    """``out (+)= alpha * A B^T`` with A (M,K), B (N,K) both e4m3 with per-32 scales along K. ``bn``: tile
+    width (0: chosen from the shape; 128 or 160)."""
     L = native.require()
     M, K = a_q.shape
     N = b_q.shape[0]
@@ -105,7 +106,7 @@ def gemm(a_q, a_sf, b_q, b_sf, out=None, out_dtype=torch.bfloat16, accumulate=Fa
     rc = L.kwu_gemm_mxfp8(native.ptr(a_q), native.ptr(a_sf), native.ptr(b_q), native.ptr(b_sf), native.ptr(out),
                           c_int(M), c_int(N), c_int(K), c_int(a_q.stride(0)), c_int(b_q.stride(0)),
                           c_int(out.stride(0)), c_int(int(out.dtype == torch.float32)), c_int(int(accumulate)),
-                          c_float(alpha), c_int(0), native.stream_ptr(), native.ptr(native.status_word()))
+                          c_float(alpha), c_int(bn), native.stream_ptr(), native.ptr(native.status_word()))
     native.check(rc, "gemm_mxfp8")
     return out
 
