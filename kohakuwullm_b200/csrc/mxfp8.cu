@@ -427,19 +427,13 @@ static int launch_mx(const void* A, const void* B, void* C, int M, int N, int K,
   return 0;
 }
 
-// Tile width: 128, or 160 when that needs fewer (width x rounds) column units on this many SMs. A 160-wide
-// tile may start 32, 64 or 96 rows into a scale chunk; the kernel loads the two chunks it touches and offsets
-// the scale address by whole TMEM columns (32 rows each).
+// Tile width. Only 128: a tile of that width always starts on a scale-chunk boundary. A 160-wide variant
+// (fewer width x rounds units on 148 SMs for every training shape) was built with the scale address offset
+// by (first row % 128) / 32 TMEM columns; its first run ended in "misaligned address", so scale addresses
+// that are not chunk-aligned (and accumulators at column 160) are not used anywhere in this file.
 static int pick_bn_mx(int M, int N, int forced) {
-  if (forced == 128 || forced == 160) return forced;
-  int sms = 0, dev = 0;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  if (sms <= 0) sms = 148;
-  const long tm = (M + MX_BM - 1) / MX_BM;
-  const long c128 = ((tm * ((N + 127) / 128) + sms - 1) / sms) * 128;
-  const long c160 = ((tm * ((N + 159) / 160) + sms - 1) / sms) * 160;
-  return c160 < c128 ? 160 : 128;
+  (void)M; (void)N; (void)forced;
+  return 128;
 }
 
 }  // namespace kwu
@@ -511,10 +505,7 @@ KWU_API int kwu_gemm_mxfp8(const void* A, const void* sfa, const void* B, const 
                            float alpha, int bn, void* stream, int* status) {
   if (M <= 0 || N <= 0) return 0;
   if (K % 128) { set_last_error("gemm_mxfp8: K must be a multiple of 128 (got %d)", K); return 7; }
-  const int BN = pick_bn_mx(M, N, bn);
-  if (BN == 160)
-    return launch_mx<160>(A, B, C, M, N, K, lda, ldb, ldc, (const uint8_t*)sfa, (const uint8_t*)sfb, out_fp32,
-                          accumulate, alpha, reinterpret_cast<cudaStream_t>(stream), status);
+  (void)pick_bn_mx(M, N, bn);
   return launch_mx<128>(A, B, C, M, N, K, lda, ldb, ldc, (const uint8_t*)sfa, (const uint8_t*)sfb, out_fp32,
                         accumulate, alpha, reinterpret_cast<cudaStream_t>(stream), status);
 }

@@ -96,8 +96,8 @@ def quantize_transposed(x: torch.Tensor, out_q=None, out_sf=None):
 
 
 def gemm(a_q, a_sf, b_q, b_sf, out=None, out_dtype=torch.bfloat16, accumulate=False, alpha=1.0, bn: int = 0):
-    """``out (+)= alpha * A B^T`` with A (M,K), B (N,K) both e4m3 with per-32 scales along K. ``bn``: tile
-    width (0: chosen from the shape; 128 or 160)."""
+    """``out (+)= alpha * A B^T`` with A (M,K), B (N,K) both e4m3 with per-32 scales along K. ``bn`` is
+    reserved (the kernel uses 128-wide tiles)."""
     L = native.require()
     M, K = a_q.shape
     N = b_q.shape[0]
