@@ -266,18 +266,24 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
           tmem_ld_x32(tDP + lane_addr + c * 32, dp);
           tmem_ld_wait();
 #pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            float pr[2], dsv[2];
+          for (int e4 = 0; e4 < 32; e4 += 4) {
+            // the per-query statistics are the same for every key row: one 16-byte shared load covers four columns
+            const float4 l4 = *reinterpret_cast<const float4*>(lse_s + c * 32 + e4);
+            const float4 d4 = *reinterpret_cast<const float4*>(dl_s + c * 32 + e4);
+            const float lq[4] = {l4.x, l4.y, l4.z, l4.w}, dq4[4] = {d4.x, d4.y, d4.z, d4.w};
+            float pr[4], dsv[4];
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
-              const int col = c * 32 + e + u;
-              float pv = fast_exp2(fmaf(__uint_as_float(sv[e + u]), c_log2, -lse_s[col]));
+            for (int u = 0; u < 4; ++u) {
+              const int col = c * 32 + e4 + u;
+              float pv = fast_exp2(fmaf(__uint_as_float(sv[e4 + u]), c_log2, -lq[u]));
               if (need_mask) pv = (col >= c_lo_q && col <= c_hi_q) ? pv : 0.f;
               pr[u] = pv;
-              dsv[u] = pv * fmaf(__uint_as_float(dp[e + u]), p.scale, -dl_s[col]);
+              dsv[u] = pv * fmaf(__uint_as_float(dp[e4 + u]), p.scale, -dq4[u]);
             }
-            pp[e / 2] = pack_bf16(pr[0], pr[1]);
-            dd[e / 2] = pack_bf16(dsv[0], dsv[1]);
+            pp[e4 / 2] = pack_bf16(pr[0], pr[1]);
+            pp[e4 / 2 + 1] = pack_bf16(pr[2], pr[3]);
+            dd[e4 / 2] = pack_bf16(dsv[0], dsv[1]);
+            dd[e4 / 2 + 1] = pack_bf16(dsv[2], dsv[3]);
           }
           // P^T / dS^T as bf16 overwrite the first half of the columns that were just read
           tmem_st_x16(tS + lane_addr + c * 16, pp);

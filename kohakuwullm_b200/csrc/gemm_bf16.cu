@@ -57,6 +57,10 @@ struct GemmParams {
   int group_b_rows;
   int num_groups;
   long long c_group_stride;
+  // scatter epilogue (bf16 EPI_STORE only): output row r goes to the byte address row_ptrs[r] (0: row is
+  // dropped) instead of C + r*ldc. The addresses may be peer-mapped memory of another GPU: the expert-
+  // parallel combine / gradient return is then done by the GEMM's own epilogue stores, tile by tile.
+  const long long* row_ptrs;
   // fused cross-entropy epilogues (EPI_LSE / EPI_DLOGITS)
   const int* labels;     // (M) target column per row, negative = ignored row
   float2* partial;       // EPI_LSE: (tiles_n, M) running (max, sum-exp) per row and column tile
@@ -398,6 +402,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           } else {
             __nv_bfloat16* dst =
                 reinterpret_cast<__nv_bfloat16*>(Cout) + static_cast<size_t>(row) * p.ldc + col0;
+            if (p.row_ptrs) {
+              const long long base = p.row_ptrs[row];
+              if (!base) continue;
+              dst = reinterpret_cast<__nv_bfloat16*>(base) + col0;
+            }
             if (full) {
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
@@ -480,6 +489,7 @@ struct GroupArgs {
   int num_groups = 1;
   long long c_stride = 0;
   int row_tiles = 0;  // mode 1: number of entries in `tiles`
+  const long long* row_ptrs = nullptr;
 };
 
 struct EpiArgs {
@@ -531,6 +541,7 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
   p.streamk = 0;
   p.group_mode = ga.mode; p.group_tiles = ga.tiles; p.group_offsets = ga.offsets;
   p.group_b_rows = ga.b_rows; p.num_groups = ga.num_groups; p.c_group_stride = ga.c_stride;
+  p.row_ptrs = (EPI == EPI_STORE && !out_fp32) ? ga.row_ptrs : nullptr;
   p.labels = ea.labels; p.partial = ea.partial; p.target_logit = ea.target_logit;
   p.lse = ea.lse; p.coef_p = ea.coef_p; p.coef_y = ea.coef_y;
 
@@ -686,13 +697,17 @@ KWU_API int kwu_ce_combine(const void* partial, int tiles_n, int M, float* lse, 
 //   A (M_pad, K) K-major. b_mn = 0: B is (E*N, K), expert e owns rows [e*N, (e+1)*N)  -> y = x W_e^T
 //                         b_mn = 1: B is (E*Kc, N) with Kc = K,  expert e owns rows [e*K, (e+1)*K) -> dx = dy W_e
 //   tiles: (row_tiles, 4) int32 entries (m0, expert, valid, unused) built by kwu_moe_plan.
+//   row_ptrs (optional, bf16 output only): per output row the byte address it is stored at (0 = skip the row);
+//   C is then not written.
 KWU_API int kwu_gemm_bf16_grouped_rows(const void* A, const void* B, void* C, int M_pad, int N, int K, int lda,
                                        int ldb, int ldc, int b_mn, int num_experts, const void* tiles,
-                                       int row_tiles, int out_fp32, void* stream, int* status) {
+                                       int row_tiles, int out_fp32, const long long* row_ptrs, void* stream,
+                                       int* status) {
   using namespace kwu;
   if (M_pad <= 0 || row_tiles <= 0) return 0;
   GroupArgs ga;
   ga.mode = 1;
+  ga.row_ptrs = row_ptrs;
   ga.tiles = reinterpret_cast<const int4*>(tiles);
   ga.row_tiles = row_tiles;
   ga.b_rows = b_mn ? K : N;

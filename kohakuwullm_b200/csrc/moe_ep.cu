@@ -16,6 +16,12 @@
 //                holding a monotonically increasing epoch that lives on the device, so the same launch
 //                sequence can be replayed from a CUDA graph.
 //   ep_copy_rows receive buffer -> private rows (padding rows zeroed), or private rows -> output buffer.
+//   scatter map  ep_copy_rows also turns the (source rank, pair) tag that ep_dispatch left beside every row into
+//                the address of that pair's slot in the SOURCE's per-pair buffer. The expert GEMMs take the map
+//                as their epilogue target (gemm_bf16.cu / mxfp8.cu `row_ptrs`): the second expert GEMM stores
+//                its output rows, and in backward the first GEMM's dgrad its input-gradient rows, straight into
+//                the sources' memory while later tiles are still in the tensor cores. The source then only
+//                sums its own k slots per token (moe_combine on local memory).
 //   ep_combine   out[t] = sum_slot w[t,slot] * yout_owner[pos(t,slot)], read with 16-byte peer loads: a
 //                per-token gather-sum (no atomics, result independent of arrival order). Optionally keeps
 //                the gathered rows for the gate-weight gradient.
@@ -43,6 +49,8 @@ struct EpPeers {
   int* flags[EP_MAX_WORLD];            // [EP_NUM_FLAGS][W] int32 on every rank
   __nv_bfloat16* xrecv[EP_MAX_WORLD];  // [cap][D] rows arriving at the owner
   __nv_bfloat16* yout[EP_MAX_WORLD];   // [cap][D] rows the sources read back
+  int* meta[EP_MAX_WORLD];             // [cap] (source rank << 28 | pair index) of every row at the owner
+  __nv_bfloat16* ypairs[EP_MAX_WORLD]; // [T*k][D] per-pair rows at the SOURCE, written by the owners' GEMM epilogues
 };
 
 __device__ __forceinline__ void ep_st_release(int* p, int v) {
@@ -160,7 +168,7 @@ __global__ void __launch_bounds__(1024) ep_plan_kernel(const EpPlanArgs a) {
 __global__ void __launch_bounds__(256)
 ep_dispatch_kernel(const EpPeers pe, const __nv_bfloat16* __restrict__ x, int ldx, const int* __restrict__ idx,
                    int n_pairs, int top_k, const int* __restrict__ send_base, int* __restrict__ cursors,
-                   int* __restrict__ pos_of, int D, int El, int cap) {
+                   int* __restrict__ pos_of, int D, int El, int cap, int rank) {
   const int lane = threadIdx.x & 31;
   const int wpb = blockDim.x >> 5;
   for (int i = blockIdx.x * wpb + (threadIdx.x >> 5); i < n_pairs; i += gridDim.x * wpb) {
@@ -172,7 +180,10 @@ ep_dispatch_kernel(const EpPeers pe, const __nv_bfloat16* __restrict__ x, int ld
       if (lane == 0) pos_of[i] = -1;
       continue;
     }
-    if (lane == 0) pos_of[i] = pos;
+    if (lane == 0) {
+      pos_of[i] = pos;
+      pe.meta[e / El][pos] = (rank << 28) | i;   // where the owner's GEMM epilogues send this row's results
+    }
     const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(i / top_k) * ldx);
     uint4* dst = reinterpret_cast<uint4*>(pe.xrecv[e / El] + static_cast<size_t>(pos) * D);
     for (int v = lane; v < D / 8; v += 32) dst[v] = src[v];
@@ -187,7 +198,8 @@ __global__ void ep_barrier_kernel(const EpPeers pe, int* epochs, int kind, int r
 // dst[r] = (r is a real row) ? src[r] : 0 for r < offsets[El]. zero_pad = 0 copies everything in use.
 __global__ void __launch_bounds__(256)
 ep_copy_rows_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ dst,
-                    const int* __restrict__ offsets, const int* __restrict__ totals, int El, int D, int zero_pad) {
+                    const int* __restrict__ offsets, const int* __restrict__ totals, int El, int D, int zero_pad,
+                    const EpPeers pe, const int* __restrict__ meta, long long* __restrict__ row_ptrs) {
   __shared__ int s_off[EP_MAX_E + 1], s_tot[EP_MAX_E];
   for (int i = threadIdx.x; i <= El; i += blockDim.x) {
     s_off[i] = offsets[i];
@@ -203,6 +215,15 @@ ep_copy_rows_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __rest
       int le = 0;
       while (le + 1 < El && s_off[le + 1] <= r) ++le;
       real = (r - s_off[le]) < s_tot[le];
+    }
+    if (row_ptrs && lane == 0) {
+      // where this row's results go: the source rank's per-pair buffer, seen through THIS rank's mapping
+      long long addr = 0;
+      if (real) {
+        const int tag = meta[r];
+        addr = reinterpret_cast<long long>(pe.ypairs[tag >> 28] + static_cast<size_t>(tag & 0x0fffffff) * D);
+      }
+      row_ptrs[r] = addr;
     }
     const uint4* s = reinterpret_cast<const uint4*>(src + static_cast<size_t>(r) * D);
     uint4* d = reinterpret_cast<uint4*>(dst + static_cast<size_t>(r) * D);
@@ -282,7 +303,7 @@ static inline int ep_check(const char* what) {
 }
 
 static bool ep_fill(EpPeers& pe, const long long* table, const long long* flags, const long long* xrecv,
-                    const long long* yout, int world) {
+                    const long long* yout, const long long* meta, const long long* ypairs, int world) {
   if (world < 1 || world > EP_MAX_WORLD) { set_last_error("ep: world size %d not in [1, 8]", world); return false; }
   for (int p = 0; p < EP_MAX_WORLD; ++p) {
     const bool in = p < world;
@@ -290,6 +311,8 @@ static bool ep_fill(EpPeers& pe, const long long* table, const long long* flags,
     pe.flags[p] = in ? reinterpret_cast<int*>(flags[p]) : nullptr;
     pe.xrecv[p] = in ? reinterpret_cast<__nv_bfloat16*>(xrecv[p]) : nullptr;
     pe.yout[p] = in ? reinterpret_cast<__nv_bfloat16*>(yout[p]) : nullptr;
+    pe.meta[p] = in ? reinterpret_cast<int*>(meta[p]) : nullptr;
+    pe.ypairs[p] = in ? reinterpret_cast<__nv_bfloat16*>(ypairs[p]) : nullptr;
   }
   return true;
 }
@@ -303,11 +326,11 @@ KWU_API int kwu_ep_table_ints(int world, int E) { return world * E; }
 KWU_API int kwu_ep_flag_ints() { return EP_NUM_FLAGS * EP_MAX_WORLD; }
 
 KWU_API int kwu_ep_plan(const long long* table_ptrs, const long long* flag_ptrs, const long long* xrecv_ptrs,
-                        const long long* yout_ptrs, const int* counts, int* epochs, int rank, int world, int E,
+                        const long long* yout_ptrs, const long long* meta_ptrs, const long long* ypairs_ptrs, const int* counts, int* epochs, int rank, int world, int E,
                         int cap, int* offsets, int* totals, void* tiles, int max_tiles, int* send_base,
                         int* cursors, long long limit_cycles, void* stream, int* status) {
   EpPlanArgs a;
-  if (!ep_fill(a.peers, table_ptrs, flag_ptrs, xrecv_ptrs, yout_ptrs, world)) return 7;
+  if (!ep_fill(a.peers, table_ptrs, flag_ptrs, xrecv_ptrs, yout_ptrs, meta_ptrs, ypairs_ptrs, world)) return 7;
   if (E > EP_MAX_E || E % world) { set_last_error("ep_plan: need E <= 128 and E %% world == 0"); return 7; }
   a.counts = counts; a.epochs = epochs; a.rank = rank; a.world = world; a.E = E; a.El = E / world; a.cap = cap;
   a.offsets = offsets; a.totals = totals; a.tiles = reinterpret_cast<int4*>(tiles); a.max_tiles = max_tiles;
@@ -319,42 +342,49 @@ KWU_API int kwu_ep_plan(const long long* table_ptrs, const long long* flag_ptrs,
 }
 
 KWU_API int kwu_ep_dispatch(const long long* table_ptrs, const long long* flag_ptrs, const long long* xrecv_ptrs,
-                            const long long* yout_ptrs, int world, const void* x, int ldx, const int* idx,
+                            const long long* yout_ptrs, const long long* meta_ptrs, const long long* ypairs_ptrs, int world, const void* x, int ldx, const int* idx,
                             int n_pairs, int top_k, const int* send_base, int* cursors, int* pos_of, int D, int El,
-                            int cap, void* stream) {
+                            int cap, int rank, void* stream) {
   EpPeers pe;
-  if (!ep_fill(pe, table_ptrs, flag_ptrs, xrecv_ptrs, yout_ptrs, world)) return 7;
+  if (!ep_fill(pe, table_ptrs, flag_ptrs, xrecv_ptrs, yout_ptrs, meta_ptrs, ypairs_ptrs, world)) return 7;
   if (D % 8) { set_last_error("ep_dispatch: D must be a multiple of 8"); return 7; }
+  if (n_pairs >= (1 << 28)) { set_last_error("ep_dispatch: too many pairs for the row tags"); return 7; }
   if (n_pairs <= 0) return 0;
   ep_dispatch_kernel<<<148 * 8, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      pe, (const __nv_bfloat16*)x, ldx, idx, n_pairs, top_k, send_base, cursors, pos_of, D, El, cap); kwu::count_launch();
+      pe, (const __nv_bfloat16*)x, ldx, idx, n_pairs, top_k, send_base, cursors, pos_of, D, El, cap, rank); kwu::count_launch();
   return ep_check("ep_dispatch");
 }
 
 KWU_API int kwu_ep_barrier(const long long* table_ptrs, const long long* flag_ptrs, const long long* xrecv_ptrs,
-                           const long long* yout_ptrs, int* epochs, int kind, int rank, int world,
+                           const long long* yout_ptrs, const long long* meta_ptrs, const long long* ypairs_ptrs, int* epochs, int kind, int rank, int world,
                            long long limit_cycles, void* stream, int* status) {
   EpPeers pe;
-  if (!ep_fill(pe, table_ptrs, flag_ptrs, xrecv_ptrs, yout_ptrs, world)) return 7;
+  if (!ep_fill(pe, table_ptrs, flag_ptrs, xrecv_ptrs, yout_ptrs, meta_ptrs, ypairs_ptrs, world)) return 7;
   if (kind < 0 || kind >= EP_NUM_FLAGS) { set_last_error("ep_barrier: unknown flag kind %d", kind); return 7; }
   ep_barrier_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       pe, epochs, kind, rank, world, status, limit_cycles > 0 ? limit_cycles : KWU_WAIT_LIMIT_CYCLES); kwu::count_launch();
   return ep_check("ep_barrier");
 }
 
-KWU_API int kwu_ep_copy_rows(const void* src, void* dst, const int* offsets, const int* totals, int El, int D,
-                             int zero_pad, void* stream) {
+// row_ptrs (optional, with zero_pad = 1 on the receive buffer): for every row the address, in this rank's mapping,
+// of the per-pair slot at the row's source rank (0 for padding rows); the grouped GEMMs take it as their scatter map.
+KWU_API int kwu_ep_copy_rows(const long long* table_ptrs, const long long* flag_ptrs, const long long* xrecv_ptrs,
+                             const long long* yout_ptrs, const long long* meta_ptrs, const long long* ypairs_ptrs,
+                             int world, int rank, const void* src, void* dst, const int* offsets, const int* totals,
+                             int El, int D, int zero_pad, long long* row_ptrs, void* stream) {
+  EpPeers pe;
+  if (!ep_fill(pe, table_ptrs, flag_ptrs, xrecv_ptrs, yout_ptrs, meta_ptrs, ypairs_ptrs, world)) return 7;
   if (D % 8 || El > EP_MAX_E) { set_last_error("ep_copy_rows: D %% 8 != 0 or too many local experts"); return 7; }
   ep_copy_rows_kernel<<<148 * 8, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      (const __nv_bfloat16*)src, (__nv_bfloat16*)dst, offsets, totals, El, D, zero_pad); kwu::count_launch();
+      (const __nv_bfloat16*)src, (__nv_bfloat16*)dst, offsets, totals, El, D, zero_pad, pe, pe.meta[rank], row_ptrs); kwu::count_launch();
   return ep_check("ep_copy_rows");
 }
 
 KWU_API int kwu_ep_combine(const long long* table_ptrs, const long long* flag_ptrs, const long long* xrecv_ptrs,
-                           const long long* yout_ptrs, int world, const int* pos_of, const int* idx, const float* w,
+                           const long long* yout_ptrs, const long long* meta_ptrs, const long long* ypairs_ptrs, int world, const int* pos_of, const int* idx, const float* w,
                            void* out, int ldo, void* keep, int T, int top_k, int D, int El, void* stream) {
   EpPeers pe;
-  if (!ep_fill(pe, table_ptrs, flag_ptrs, xrecv_ptrs, yout_ptrs, world)) return 7;
+  if (!ep_fill(pe, table_ptrs, flag_ptrs, xrecv_ptrs, yout_ptrs, meta_ptrs, ypairs_ptrs, world)) return 7;
   if (D % 8) { set_last_error("ep_combine: D must be a multiple of 8"); return 7; }
   if (T <= 0) return 0;
   int grid = (T + 7) / 8;
@@ -365,11 +395,11 @@ KWU_API int kwu_ep_combine(const long long* table_ptrs, const long long* flag_pt
 }
 
 KWU_API int kwu_ep_combine_bwd(const long long* table_ptrs, const long long* flag_ptrs, const long long* xrecv_ptrs,
-                               const long long* yout_ptrs, int world, const void* dout, int lddo, const void* kept,
+                               const long long* yout_ptrs, const long long* meta_ptrs, const long long* ypairs_ptrs, int world, const void* dout, int lddo, const void* kept,
                                const int* pos_of, const int* idx, const float* w, float* d_w, int n_pairs, int top_k,
                                int D, int El, void* stream) {
   EpPeers pe;
-  if (!ep_fill(pe, table_ptrs, flag_ptrs, xrecv_ptrs, yout_ptrs, world)) return 7;
+  if (!ep_fill(pe, table_ptrs, flag_ptrs, xrecv_ptrs, yout_ptrs, meta_ptrs, ypairs_ptrs, world)) return 7;
   if (D % 8) { set_last_error("ep_combine_bwd: D must be a multiple of 8"); return 7; }
   if (n_pairs <= 0) return 0;
   ep_combine_bwd_kernel<<<148 * 8, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(

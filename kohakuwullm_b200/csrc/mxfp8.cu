@@ -132,6 +132,7 @@ struct MxGemmParams {
   const int4* group_tiles;
   int group_n;
   int sfb_chunk_rows;  // number of 128-row scale chunks B has (chunk indices are clamped to it)
+  const long long* row_ptrs;  // bf16 output: row r is stored at this byte address (0: dropped) instead of C + r*ldc
   int* status;
 };
 
@@ -346,6 +347,11 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             }
           } else {
             __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(Cout) + static_cast<size_t>(row) * p.ldc + col0;
+            if (p.row_ptrs) {
+              const long long base = p.row_ptrs[row];
+              if (!base) continue;
+              dst = reinterpret_cast<__nv_bfloat16*>(base) + col0;
+            }
             if (full) {
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
@@ -393,7 +399,7 @@ template <int BN>
 static int launch_mx(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
                      const uint8_t* sfa, const uint8_t* sfb, int out_fp32, int accumulate, float alpha,
                      cudaStream_t stream, int* status, const int4* group_tiles = nullptr, int n_group_tiles = 0,
-                     int n_groups = 1) {
+                     int n_groups = 1, const long long* row_ptrs = nullptr) {
   using S = MxSmem<BN>;
   CUtensorMap tmA, tmB;
   int rc;
@@ -408,6 +414,7 @@ static int launch_mx(const void* A, const void* B, void* C, int M, int N, int K,
   p.group_tiles = group_tiles;
   p.group_n = N;
   p.sfb_chunk_rows = static_cast<int>((static_cast<long long>(N) * n_groups + 127) / 128);
+  p.row_ptrs = out_fp32 ? nullptr : row_ptrs;
   p.status = status;
   auto kern = gemm_mxfp8_kernel<BN>;
   static bool attr_set = false;
@@ -490,14 +497,16 @@ KWU_API int kwu_mxfp8_quantize_t_batched(const void* x, int ldx, void* qT, int l
 // Grouped form: rows of A are grouped by expert in 128-row-aligned ranges described by `tiles`
 // ((m0, expert, valid, 0) per 128-row tile); B stacks the experts' (N, K) matrices along its rows.
 // out[rows of expert e] = A[rows] B[e]^T. N must be a multiple of 128.
+// row_ptrs (optional): per output row the byte address it is stored at (0 = skip); C is then not written.
 KWU_API int kwu_gemm_mxfp8_grouped(const void* A, const void* sfa, const void* B, const void* sfb, void* C,
                                    int M, int N, int K, int lda, int ldb, int ldc, int n_experts,
-                                   const void* tiles, int n_tiles, void* stream, int* status) {
+                                   const void* tiles, int n_tiles, const long long* row_ptrs, void* stream,
+                                   int* status) {
   if (M <= 0 || N <= 0 || n_tiles <= 0) return 0;
   if (K % 128 || N % 128) { set_last_error("gemm_mxfp8_grouped: K and N must be multiples of 128 (got %d, %d)", K, N); return 7; }
   return launch_mx<128>(A, B, C, M, N, K, lda, ldb, ldc, (const uint8_t*)sfa, (const uint8_t*)sfb, 0, 0, 1.f,
                         reinterpret_cast<cudaStream_t>(stream), status, reinterpret_cast<const int4*>(tiles),
-                        n_tiles, n_experts);
+                        n_tiles, n_experts, row_ptrs);
 }
 
 KWU_API int kwu_gemm_mxfp8(const void* A, const void* sfa, const void* B, const void* sfb, void* C, int M,

@@ -186,18 +186,21 @@ class _GroupedLinear(torch.autograd.Function):
     """``out[rows of expert e] = rows @ W[e]^T`` with W (E, N, K)."""
 
     @staticmethod
-    def forward(ctx, rows, W, plan: DispatchPlan, out=None, dgrad_out=None):
+    def forward(ctx, rows, W, plan: DispatchPlan, out=None, dgrad_out=None, out_row_ptrs=None, dgrad_row_ptrs=None):
         """``out`` / ``dgrad_out``: caller-owned (max_rows, N) / (max_rows, K) buffers for the product and for
-        the input gradient (expert parallelism passes its peer-visible output buffer, saving a copy)."""
+        the input gradient. ``out_row_ptrs`` / ``dgrad_row_ptrs``: (max_rows,) int64 scatter maps; the kernel's
+        epilogue then stores row r at that byte address (0: dropped) instead of into the buffer, which may be
+        another GPU's peer-mapped memory (expert parallelism returns rows to their source ranks this way)."""
         L = native.require()
         E, N, K = W.shape
         if out is None:
             out = torch.empty(plan.max_rows, N, dtype=rows.dtype, device=rows.device)
-        ctx.dgrad_out = dgrad_out
+        ctx.dgrad_out, ctx.dgrad_row_ptrs = dgrad_out, dgrad_row_ptrs
         rc = L.kwu_gemm_bf16_grouped_rows(native.ptr(rows), native.ptr(W), native.ptr(out), c_int(plan.max_rows), c_int(N),
                                           c_int(K), c_int(rows.stride(0)), c_int(K), c_int(N), c_int(0), c_int(E),
                                           native.ptr(plan.tiles), c_int(plan.tiles.shape[0]), c_int(0),
-                                          native.stream_ptr(), native.ptr(native.status_word()))
+                                          native.ptr(out_row_ptrs), native.stream_ptr(),
+                                          native.ptr(native.status_word()))
         native.check(rc, "grouped_gemm_fwd")
         ctx.save_for_backward(rows, W)
         ctx.plan = plan
@@ -218,7 +221,8 @@ class _GroupedLinear(torch.autograd.Function):
             rc = L.kwu_gemm_bf16_grouped_rows(native.ptr(dout), native.ptr(W), native.ptr(drows), c_int(plan.max_rows),
                                               c_int(K), c_int(N), c_int(dout.stride(0)), c_int(K), c_int(K), c_int(1),
                                               c_int(E), native.ptr(plan.tiles), c_int(plan.tiles.shape[0]), c_int(0),
-                                              native.stream_ptr(), native.ptr(native.status_word()))
+                                              native.ptr(ctx.dgrad_row_ptrs), native.stream_ptr(),
+                                              native.ptr(native.status_word()))
             native.check(rc, "grouped_gemm_dgrad")
         if ctx.needs_input_grad[1]:
             main_grad = getattr(W, "main_grad", None)
@@ -230,7 +234,7 @@ class _GroupedLinear(torch.autograd.Function):
             native.check(rc, "grouped_gemm_wgrad")
             if main_grad is None:
                 dW = target.to(W.dtype)
-        return drows, dW, None, None, None
+        return drows, dW, None, None, None, None, None
 
 
 class _Combine(torch.autograd.Function):
@@ -263,15 +267,16 @@ class _Combine(torch.autograd.Function):
         return drows, dw.view(ctx.wshape).to(ctx.wdtype), None, None
 
 
-def grouped_linear(rows, W, plan, qweight=None, out=None, dgrad_out=None):
+def grouped_linear(rows, W, plan, qweight=None, out=None, dgrad_out=None, out_row_ptrs=None, dgrad_row_ptrs=None):
     """Expert-grouped linear: bf16 tcgen05 GEMM, or the MXFP8 recipe when ``qweight`` (a
     ``GroupedQuantizedWeight`` of ``W``) is given. ``out`` / ``dgrad_out``: optional caller-owned buffers for
-    the product and for the input gradient."""
+    the product and for the input gradient; ``out_row_ptrs`` / ``dgrad_row_ptrs``: optional scatter maps for
+    their rows (see ``_GroupedLinear.forward``)."""
     if qweight is not None:
         from kohakuwullm_b200.ops.mxfp8 import _MXFP8GroupedLinear
 
-        return _MXFP8GroupedLinear.apply(rows, W, qweight, plan, out, dgrad_out)
-    return _GroupedLinear.apply(rows, W, plan, out, dgrad_out)
+        return _MXFP8GroupedLinear.apply(rows, W, qweight, plan, out, dgrad_out, out_row_ptrs, dgrad_row_ptrs)
+    return _GroupedLinear.apply(rows, W, plan, out, dgrad_out, out_row_ptrs, dgrad_row_ptrs)
 
 
 def routed_experts(x, idx, weight, counts, w_in, w_out, q_in=None, q_out=None):

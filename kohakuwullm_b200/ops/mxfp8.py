@@ -243,7 +243,7 @@ class GroupedQuantizedWeight:
 
 
 def grouped_gemm(a_q, a_sf, b_q, b_sf, n_per_expert: int, n_experts: int, tiles: torch.Tensor, out_dtype=torch.bfloat16,
-                 out=None):
+                 out=None, row_ptrs=None):
     """``out[rows of expert e] = A[rows] B[e]^T`` over expert-sorted, 128-row-aligned A rows."""
     L = native.require()
     M, K = a_q.shape
@@ -252,7 +252,7 @@ def grouped_gemm(a_q, a_sf, b_q, b_sf, n_per_expert: int, n_experts: int, tiles:
     rc = L.kwu_gemm_mxfp8_grouped(native.ptr(a_q), native.ptr(a_sf), native.ptr(b_q), native.ptr(b_sf), native.ptr(out),
                                   c_int(M), c_int(n_per_expert), c_int(K), c_int(a_q.stride(0)), c_int(b_q.stride(0)),
                                   c_int(out.stride(0)), c_int(n_experts), native.ptr(tiles), c_int(tiles.shape[0]),
-                                  native.stream_ptr(), native.ptr(native.status_word()))
+                                  native.ptr(row_ptrs), native.stream_ptr(), native.ptr(native.status_word()))
     native.check(rc, "gemm_mxfp8_grouped")
     return out
 
@@ -262,12 +262,13 @@ class _MXFP8GroupedLinear(torch.autograd.Function):
     (``main_grad`` when the trainer provides it). ``plan`` carries the tile table and expert offsets."""
 
     @staticmethod
-    def forward(ctx, rows, W, qw: GroupedQuantizedWeight, plan, out=None, dgrad_out=None):
+    def forward(ctx, rows, W, qw: GroupedQuantizedWeight, plan, out=None, dgrad_out=None, out_row_ptrs=None,
+                dgrad_row_ptrs=None):
         E, N, K = W.shape
         xq, xsf = quantize(rows)
-        out = grouped_gemm(xq, xsf, qw.q, qw.sf, N, E, plan.tiles, out_dtype=rows.dtype, out=out)
+        out = grouped_gemm(xq, xsf, qw.q, qw.sf, N, E, plan.tiles, out_dtype=rows.dtype, out=out, row_ptrs=out_row_ptrs)
         ctx.save_for_backward(rows, W)
-        ctx.qw, ctx.plan, ctx.dgrad_out = qw, plan, dgrad_out
+        ctx.qw, ctx.plan, ctx.dgrad_out, ctx.dgrad_row_ptrs = qw, plan, dgrad_out, dgrad_row_ptrs
         return out
 
     @staticmethod
@@ -280,7 +281,8 @@ class _MXFP8GroupedLinear(torch.autograd.Function):
         drows = dW = None
         if ctx.needs_input_grad[0]:
             dq, dsf = quantize(dout)
-            drows = grouped_gemm(dq, dsf, qw.qt, qw.sft, K, E, plan.tiles, out_dtype=rows.dtype, out=ctx.dgrad_out)
+            drows = grouped_gemm(dq, dsf, qw.qt, qw.sft, K, E, plan.tiles, out_dtype=rows.dtype, out=ctx.dgrad_out,
+                                 row_ptrs=ctx.dgrad_row_ptrs)
         if ctx.needs_input_grad[1]:
             main_grad = getattr(W, "main_grad", None)
             target = main_grad if main_grad is not None else torch.zeros(E, N, K, dtype=torch.float32, device=W.device)
@@ -291,7 +293,7 @@ class _MXFP8GroupedLinear(torch.autograd.Function):
             native.check(rc, "grouped_gemm_wgrad")
             if main_grad is None:
                 dW = target.to(W.dtype)
-        return drows, dW, None, None, None, None
+        return drows, dW, None, None, None, None, None, None
 
 
 def grouped_supported(W: torch.Tensor) -> bool:

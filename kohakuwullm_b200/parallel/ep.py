@@ -51,6 +51,7 @@ class EPPlan:
     max_rows: int             # == cap
     top_k: int
     num_experts: int          # LOCAL expert count: what the grouped GEMMs iterate over
+    row_ptrs: torch.Tensor | None = None   # (cap,) int64 scatter map of the received rows (filled by dispatch)
 
 
 class ExpertParallel:
@@ -73,7 +74,7 @@ class ExpertParallel:
         cap = -(-cap // 128) * 128
         if self._ws is not None:
             have_cap, have_D, have_E = self._shape
-            if (D, E) != (have_D, have_E) or cap > have_cap:
+            if (D, E) != (have_D, have_E) or cap > have_cap or n_pairs > self._ws["n_pairs"]:
                 raise ValueError(f"expert-parallel workspace was sized for {self._shape}, got {(cap, D, E)}: all "
                                  "MoE layers of one engine must share dim and E, and no micro-batch may be "
                                  "larger than the first one")
@@ -85,14 +86,19 @@ class ExpertParallel:
         flags = pool.empty(L.kwu_ep_flag_ints(), torch.int32, device)
         xrecv = pool.empty(cap * D, torch.bfloat16, device)
         yout = pool.empty(cap * D, torch.bfloat16, device)
+        meta = pool.empty(cap, torch.int32, device)
+        ypairs = pool.empty(n_pairs * D, torch.bfloat16, device)
         table.zero_()
         flags.zero_()
+        ypairs.zero_()
         pool.rendezvous_all()
         torch.cuda.synchronize(device)
         dist.barrier(group=self.group)
-        tabs = tuple(pool.find(t).ptr_table() for t in (table, flags, xrecv, yout))
+        tabs = tuple(pool.find(t).ptr_table() for t in (table, flags, xrecv, yout, meta, ypairs))
         epochs = torch.zeros(4, dtype=torch.int32, device=device)
         self._ws = dict(pool=pool, table=table, flags=flags, xrecv=xrecv.view(cap, D), yout=yout.view(cap, D),
+                        meta=meta, ypairs=ypairs.view(n_pairs, D), n_pairs=n_pairs,
+                        pair_ids=torch.arange(n_pairs, dtype=torch.int32, device=device),
                         tabs=tabs, epochs=epochs, cap=cap, El=El)
         self._shape = (cap, D, E)
         return self._ws
@@ -141,35 +147,57 @@ class ExpertParallel:
         rc = L.kwu_ep_dispatch(*ws["tabs"], c_int(self.world), native.ptr(x), c_int(x.stride(0)), native.ptr(plan.idx),
                                c_int(plan.idx.numel()), c_int(plan.top_k), native.ptr(plan.send_base),
                                native.ptr(plan.cursors), native.ptr(plan.pos_of), c_int(x.shape[1]), c_int(ws["El"]),
-                               c_int(ws["cap"]), native.stream_ptr())
+                               c_int(ws["cap"]), c_int(self.rank), native.stream_ptr())
         native.check(rc, "ep_dispatch")
 
-    def _take_received(self, plan, D):
-        """barrier, then receive buffer -> private rows with zeroed padding."""
+    def _take_received(self, plan, D, build_scatter_map: bool = False):
+        """barrier, then receive buffer -> private rows with zeroed padding. ``build_scatter_map``: also turn
+        the row tags into the scatter map the expert GEMMs use (``plan.row_ptrs``)."""
         L = native.require()
         ws = self._ws
         self._barrier(ws, FLAG_ARRIVED)
         rows = torch.empty(ws["cap"], D, dtype=torch.bfloat16, device=ws["xrecv"].device)
-        rc = L.kwu_ep_copy_rows(native.ptr(ws["xrecv"]), native.ptr(rows), native.ptr(plan.offsets),
-                                native.ptr(plan.totals), c_int(ws["El"]), c_int(D), c_int(1), native.stream_ptr())
+        if build_scatter_map:
+            plan.row_ptrs = torch.empty(ws["cap"], dtype=torch.int64, device=rows.device)
+        rc = L.kwu_ep_copy_rows(*ws["tabs"], c_int(self.world), c_int(self.rank), native.ptr(ws["xrecv"]),
+                                native.ptr(rows), native.ptr(plan.offsets), native.ptr(plan.totals), c_int(ws["El"]),
+                                c_int(D), c_int(1), native.ptr(plan.row_ptrs if build_scatter_map else None),
+                                native.stream_ptr())
         native.check(rc, "ep_copy_rows")
         return rows
 
     def output_rows(self) -> torch.Tensor:
-        """The peer-visible (cap, D) output buffer: a GEMM that writes its product (forward) or its input
-        gradient (backward) straight into it saves the copy in ``_publish_rows``."""
+        """The peer-visible (cap, D) output buffer. Passed as the nominal output of a GEMM whose epilogue
+        scatters its rows to the sources (``row_ptrs``), it tells ``_publish_rows`` that nothing is left to copy."""
         return self._ws["yout"]
 
     def _publish_rows(self, rows, plan):
-        """private rows -> output buffer (skipped when the rows already live there), then barrier."""
+        """Make the owners' results visible to the sources. Rows that a GEMM epilogue already scattered into the
+        sources' per-pair buffers (``rows`` is then the nominal output buffer) only need the barrier; private
+        rows are first copied into the peer-visible output buffer (pull path)."""
         L = native.require()
         ws = self._ws
-        if rows.data_ptr() != ws["yout"].data_ptr():
-            rc = L.kwu_ep_copy_rows(native.ptr(rows), native.ptr(ws["yout"]), native.ptr(plan.offsets),
-                                    native.ptr(plan.totals), c_int(ws["El"]), c_int(rows.shape[1]), c_int(0),
+        scattered = rows.data_ptr() == ws["yout"].data_ptr()
+        if not scattered:
+            rc = L.kwu_ep_copy_rows(*ws["tabs"], c_int(self.world), c_int(self.rank), native.ptr(rows),
+                                    native.ptr(ws["yout"]), native.ptr(plan.offsets), native.ptr(plan.totals),
+                                    c_int(ws["El"]), c_int(rows.shape[1]), c_int(0), native.ptr(None),
                                     native.stream_ptr())
             native.check(rc, "ep_copy_rows")
         self._barrier(ws, FLAG_OUTPUT)
+        return scattered
+
+    def _sum_pairs(self, plan, w, T, D, keep: bool):
+        """Local tail of the scattered path: out[t] = sum_slot w[t,slot] * ypairs[t*k + slot]."""
+        L = native.require()
+        ws = self._ws
+        n = plan.idx.numel()
+        out = torch.empty(T, D, dtype=torch.bfloat16, device=ws["ypairs"].device)
+        rc = L.kwu_moe_combine(native.ptr(ws["ypairs"]), native.ptr(ws["pair_ids"]), native.ptr(w), native.ptr(out),
+                               c_int(D), c_int(T), c_int(plan.top_k), c_int(D), native.stream_ptr())
+        native.check(rc, "moe_combine")
+        kept = ws["ypairs"][:n].clone() if keep else None
+        return out, kept
 
     def _pull(self, plan, w, T, D, keep: bool):
         L = native.require()
@@ -189,7 +217,7 @@ class _EPDispatch(torch.autograd.Function):
     def forward(ctx, x, ep: ExpertParallel, plan: EPPlan):
         x = x.contiguous()
         ep._push_rows(x, plan)
-        rows = ep._take_received(plan, x.shape[1])
+        rows = ep._take_received(plan, x.shape[1], build_scatter_map=True)
         ctx.ep, ctx.plan, ctx.T = ep, plan, x.shape[0]
         return rows
 
@@ -197,8 +225,10 @@ class _EPDispatch(torch.autograd.Function):
     def backward(ctx, drows):
         ep, plan = ctx.ep, ctx.plan
         drows = drows.contiguous()
-        ep._publish_rows(drows, plan)
-        dx, _ = ep._pull(plan, None, ctx.T, drows.shape[1], keep=False)
+        if ep._publish_rows(drows, plan):
+            dx, _ = ep._sum_pairs(plan, None, ctx.T, drows.shape[1], keep=False)
+        else:
+            dx, _ = ep._pull(plan, None, ctx.T, drows.shape[1], keep=False)
         return dx, None, None
 
 
@@ -207,8 +237,10 @@ class _EPCombine(torch.autograd.Function):
     def forward(ctx, y_rows, weight, ep: ExpertParallel, plan: EPPlan, T):
         y_rows = y_rows.contiguous()
         w = weight.reshape(-1).float().contiguous()
-        ep._publish_rows(y_rows, plan)
-        out, kept = ep._pull(plan, w, T, y_rows.shape[1], keep=True)
+        if ep._publish_rows(y_rows, plan):
+            out, kept = ep._sum_pairs(plan, w, T, y_rows.shape[1], keep=True)
+        else:
+            out, kept = ep._pull(plan, w, T, y_rows.shape[1], keep=True)
         ctx.save_for_backward(kept, w)
         ctx.ep, ctx.plan, ctx.wshape, ctx.wdtype = ep, plan, weight.shape, weight.dtype
         return out
@@ -240,10 +272,13 @@ def ep_routed_experts(ep: ExpertParallel, x, idx, weight, counts, w_in_local, w_
     T, D = x.shape
     plan = ep.plan(idx, counts, D)
     rows = ep.dispatch(x, plan)
-    stage = ep.output_rows()   # forward: the second GEMM's product; backward: the first GEMM's input gradient
-    h = grouped_linear(rows, w_in_local, plan, q_in, dgrad_out=stage)
+    # The second GEMM's epilogue (forward) and the first GEMM's dgrad epilogue (backward) store their rows
+    # straight into the SOURCE ranks' per-pair buffers through the scatter map: the return all-to-all rides on
+    # the GEMM's own stores, tile by tile. `stage` is the nominal output tensor of those two products.
+    stage = ep.output_rows()
+    h = grouped_linear(rows, w_in_local, plan, q_in, dgrad_out=stage, dgrad_row_ptrs=plan.row_ptrs)
     a = swiglu(h)
-    y_rows = grouped_linear(a, w_out_local, plan, q_out, out=stage)
+    y_rows = grouped_linear(a, w_out_local, plan, q_out, out=stage, out_row_ptrs=plan.row_ptrs)
     return ep.combine(y_rows, weight, plan, T)
 
 
