@@ -355,9 +355,9 @@ class _QuantizeHeads(torch.autograd.Function):
 
 
 def quantize_heads(x: torch.Tensor, smooth: bool = False) -> torch.Tensor:
-    """MXFP8 round trip of a (T,H,64) attention operand (native on bf16 CUDA input, PyTorch elsewhere)."""
+    """MXFP8 round trip of a (T,H,64) attention operand (native on bf16 CUDA input, PyTorch elsewhere).
+    Gradients pass straight through the rounding; with ``smooth`` they flow through the mean subtraction."""
     if native.available() and x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] == 64:
         return _QuantizeHeads.apply(x, smooth)
-    return x + (quantize_heads_reference(x, smooth) - x).detach() if not smooth else \
-        (x - x.float().mean(0, keepdim=True).to(x.dtype)) + \
-        (quantize_heads_reference(x, True) - (x - x.float().mean(0, keepdim=True).to(x.dtype))).detach()
+    base = x - x.float().mean(0, keepdim=True).to(x.dtype) if smooth else x
+    return base + (quantize_heads_reference(x, smooth) - base).detach()

@@ -81,3 +81,45 @@ def test_elementwise_cpu_paths():
     out = qknorm_rope(q, None, ang.cos(), ang.sin())
     # rotation preserves the norm of the normalised vector
     torch.testing.assert_close(out.pow(2).mean(-1), torch.ones(5, 2), rtol=1e-3, atol=1e-3)
+
+
+def test_quantize_heads_cpu_fallback_is_straight_through():
+    import torch
+
+    from kohakuwullm_b200.ops.attention import quantize_heads, quantize_heads_reference
+
+    torch.manual_seed(0)
+    x = torch.randn(50, 3, 64, requires_grad=True)
+    y = quantize_heads(x)
+    assert torch.equal(y.detach(), quantize_heads_reference(x.detach()))
+    y.sum().backward()
+    assert torch.equal(x.grad, torch.ones_like(x))
+    k = torch.randn(50, 2, 64, requires_grad=True)
+    ks = quantize_heads(k, smooth=True)
+    (ks * torch.randn_like(ks)).sum().backward()
+    assert k.grad.mean(0).abs().max() < 1e-6          # the mean subtraction removes the gradient's token mean
+    # values are within one e4m3 step of the smoothed input
+    err = (ks.detach() - (k.detach() - k.detach().mean(0, keepdim=True))).abs().max()
+    assert err < 0.07 * k.detach().abs().max()
+
+
+def test_mxfp8_wiring_sets_producer_flags():
+    import torch
+
+    from kohakuwullm_b200.models import LMBackbone, get_preset
+    from kohakuwullm_b200.models.components.norm import RMSNorm
+
+    cfg = get_preset("B200-smoke", vocab_size=512, mxfp8=True, mlp_hidden=768)
+    model = LMBackbone(cfg)
+    blocks = list(model.blocks)
+    assert all(b.norm_attn.emit_mx and b.norm_mlp.emit_mx and b.norm_mlp.emit_mx_grad for b in blocks)
+    assert not blocks[0].norm_attn.emit_mx_grad and all(b.norm_attn.emit_mx_grad for b in blocks[1:])
+    assert model.final_norm.emit_mx_grad
+    plain = LMBackbone(get_preset("B200-smoke", vocab_size=512, mxfp8=False, mlp_hidden=768))
+    assert not any(m.emit_mx or m.emit_mx_grad for m in plain.modules() if isinstance(m, RMSNorm))
+    # the CPU forward ignores the flags (no native kernels): same loss path as without them
+    tok = torch.randint(0, 512, (64,))
+    from kohakuwullm_b200.models.seqinfo import SeqInfo
+
+    out = model(tok, SeqInfo.from_lengths([40, 24]))
+    assert out.shape == (64, cfg.dim)
