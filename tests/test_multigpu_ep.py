@@ -51,15 +51,17 @@ def _layer_worker(rank, world, port, out_dir):
         return [t.float() for t in (y.detach(), xs.grad, ws.grad, wi.grad, wo.grad)]
 
     ep = ExpertParallel()
-    for _ in range(2):  # twice: the second pass reuses the workspace and the device-side epochs
-        got = run(lambda xs, ws, wi, wo: ep_routed_experts(ep, xs, idx, ws, counts, wi, wo))
     ref = run(lambda xs, ws, wi, wo: reference_ep_forward(xs, idx, ws, wi, wo))
-    torch.cuda.synchronize()
-    native.check_status()
     names = ("y", "dx", "dweight", "dw_in", "dw_out")
     errs = {}
-    for n, a, b in zip(names, got, ref):
-        errs[n] = ((a - b).abs().max() / b.abs().max().clamp(min=1e-6)).item()
+    for scatter in (False, True):   # pull path, then the GEMM-epilogue scatter path, on the same workspace
+        ep.scatter_epilogue = scatter
+        for _ in range(2):          # twice: the second pass reuses the workspace and the device-side epochs
+            got = run(lambda xs, ws, wi, wo: ep_routed_experts(ep, xs, idx, ws, counts, wi, wo))
+        torch.cuda.synchronize()
+        native.check_status()
+        for n, a, b in zip(names, got, ref):
+            errs[f"{n}/{'scatter' if scatter else 'pull'}"] = ((a - b).abs().max() / b.abs().max().clamp(min=1e-6)).item()
     torch.save(errs, os.path.join(out_dir, f"layer_{rank}.pt"))
     dist.barrier()
     dist.destroy_process_group()
