@@ -378,7 +378,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 v.z = __uint_as_float(r[4 * j + 2]) * p.alpha;
                 v.w = __uint_as_float(r[4 * j + 3]) * p.alpha;
                 float4* d4 = reinterpret_cast<float4*>(dst) + j;
-                if (p.splits > 1 || p.streamk > 0) {
+                // several CTAs add into the same tile (split-K, stream-K), or the tile is short in K and a
+                // read-modify-write would leave the epilogue waiting on loads (per-expert weight gradients):
+                // fire-and-forget vector reductions
+                if (p.splits > 1 || p.streamk > 0 || (p.group_mode == 2 && p.accumulate)) {
                   red_add_f32x4(dst + 4 * j, v.x, v.y, v.z, v.w);
                   continue;
                 }

@@ -1,6 +1,6 @@
 // Mixture-of-experts routing and dispatch kernels.
 //
-//   moe_router_fwd   gate logits (fp32 SIMT tile GEMM) -> score (sigmoid | softmax | sqrt-softplus) ->
+//   moe_router_fwd   gate logits (fp32 SIMT tile GEMM, or read from a buffer the tensor cores filled) -> score (sigmoid | softmax | sqrt-softplus) ->
 //                    selection over score + bias (bias steers SELECTION only) -> top-k by repeated warp
 //                    arg-max -> gate weight from the UNBIASED score, optionally normalised over the k picks
 //                    and scaled -> per-call histogram `counts` and the running `load_accum`.
@@ -37,7 +37,13 @@ moe_router_fwd_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const float*
   float acc[RT_MAXE / 8];
 #pragma unroll
   for (int j = 0; j < RT_MAXE / 8; ++j) acc[j] = 0.f;
-  for (int d0 = 0; d0 < D; d0 += RT_BD) {
+  if (x == nullptr) {
+    // logits were already formed on the tensor cores (two bf16 GEMMs over a hi/lo split of W): read them
+#pragma unroll
+    for (int j = 0; j < RT_MAXE / 8; ++j)
+      if (tx + 8 * j < E && t0 + ty < T) acc[j] = logits_out[static_cast<size_t>(t0 + ty) * E + tx + 8 * j];
+  }
+  for (int d0 = 0; x != nullptr && d0 < D; d0 += RT_BD) {
     for (int i = tid; i < RT_BT * RT_BD; i += 256) {
       const int r = i / RT_BD, c = i % RT_BD;
       const int t = t0 + r;
@@ -339,8 +345,8 @@ namespace kwu {
 __global__ void __launch_bounds__(256)
 moe_router_dlogits_kernel(const float* __restrict__ logits, const int* __restrict__ idx,
                           const float* __restrict__ d_weight, const float* __restrict__ dlogits_in,
-                          float* __restrict__ dlogits, int T, int E, int top_k, int score_fn, int norm_topk,
-                          float scaling) {
+                          float* __restrict__ dlogits, __nv_bfloat16* __restrict__ dlogits_bf16, int T, int E,
+                          int top_k, int score_fn, int norm_topk, float scaling) {
   const int lane = threadIdx.x & 31;
   const int wpb = blockDim.x >> 5;
   for (int t = blockIdx.x * wpb + (threadIdx.x >> 5); t < T; t += gridDim.x * wpb) {
@@ -435,6 +441,7 @@ moe_router_dlogits_kernel(const float* __restrict__ logits, const int* __restric
       }
       if (dlogits_in) dl += dlogits_in[static_cast<size_t>(t) * E + e];
       out[e] = dl;
+      if (dlogits_bf16) dlogits_bf16[static_cast<size_t>(t) * E + e] = __float2bfloat16(dl);
     }
   }
 }
@@ -521,17 +528,20 @@ moe_router_dw_kernel(const float* __restrict__ dl, const __nv_bfloat16* __restri
 
 // dlogits: (T,E) fp32 scratch/output. dx (T,D) bf16 or null. dW (E,D) fp32, ACCUMULATED into (zero it first
 // for a plain gradient), or null.
+// dlogits_bf16 (optional): a bf16 copy of the logit gradient, the operand of the tensor-core products
+// dx = dl W and dW += dl^T x when the caller forms them with the GEMM kernel instead of passing dx / dW here.
 KWU_API int kwu_moe_router_bwd(const float* logits, const int* idx, const float* d_weight, const float* dlogits_in,
-                               float* dlogits, const void* x, int ldx, const float* W, void* dx, int lddx, float* dW,
-                               int T, int D, int E, int top_k, int score_fn, int norm_topk, float scaling,
-                               void* stream) {
+                               float* dlogits, void* dlogits_bf16, const void* x, int ldx, const float* W, void* dx,
+                               int lddx, float* dW, int T, int D, int E, int top_k, int score_fn, int norm_topk,
+                               float scaling, void* stream) {
   if (E > RT_MAXE || top_k > 32) { set_last_error("moe_router_bwd: need E <= 128 and k <= 32"); return 7; }
   if (T <= 0) return 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int grid = (T + 7) / 8;
   if (grid > 148 * 8) grid = 148 * 8;
-  moe_router_dlogits_kernel<<<grid, 256, 0, st>>>(logits, idx, d_weight, dlogits_in, dlogits, T, E, top_k, score_fn,
-                                                 norm_topk, scaling); kwu::count_launch();
+  moe_router_dlogits_kernel<<<grid, 256, 0, st>>>(logits, idx, d_weight, dlogits_in, dlogits,
+                                                 (__nv_bfloat16*)dlogits_bf16, T, E, top_k, score_fn, norm_topk,
+                                                 scaling); kwu::count_launch();
   if (dx) {
     dim3 g((T + RB_BT - 1) / RB_BT, (D + RB_BD - 1) / RB_BD);
     moe_router_dx_kernel<<<g, 256, 0, st>>>(dlogits, W, (__nv_bfloat16*)dx, lddx, T, D, E); kwu::count_launch();

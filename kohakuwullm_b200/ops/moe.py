@@ -63,13 +63,17 @@ def native_supported(x, w_in) -> bool:
 
 # ------------------------------------------------------------------------------------ router
 class _RouterTopK(torch.autograd.Function):
-    """Fused gate GEMM + score + biased top-k + histogram. Backward: one kernel turns the gate-weight
-    gradient into logit gradients (normalisation, scaling, score function; dense auxiliary-loss logit
-    gradients are added), two fp32 tile kernels form ``dx = dl W`` and ``dW += dl^T x`` (straight into
-    ``main_grad`` when the trainer provides it)."""
+    """Gate logits on the tensor cores (fp32 gate matrix as a bf16 hi/lo pair), then one kernel for score,
+    biased top-k, gate weights and the load histogram. Backward: one kernel turns the gate-weight gradient into
+    logit gradients (normalisation, scaling, score function; dense auxiliary-loss logit gradients are added);
+    ``dx = dl W`` and ``dW += dl^T x`` run on the tensor-core GEMM with bf16 operands and fp32 accumulation,
+    the latter straight into ``main_grad`` when the trainer provides it. The all-fp32 SIMT tile kernels
+    (``kwu_moe_router_fwd`` with ``x``, ``kwu_moe_router_bwd`` with ``dx`` / ``dW``) remain in the library."""
 
     @staticmethod
     def forward(ctx, x, W, bias, load_accum, top_k, score, norm_topk, scaling):
+        from kohakuwullm_b200.ops.gemm import matmul
+
         L = native.require()
         T, D = x.shape
         E = W.shape[0]
@@ -77,18 +81,30 @@ class _RouterTopK(torch.autograd.Function):
         idx = torch.empty(T, top_k, dtype=torch.int32, device=x.device)
         weight = torch.empty(T, top_k, dtype=torch.float32, device=x.device)
         counts = torch.zeros(E, dtype=torch.int32, device=x.device)
-        rc = L.kwu_moe_router_fwd(native.ptr(x), c_int(x.stride(0)), native.ptr(W), native.ptr(bias), native.ptr(logits),
-                                  native.ptr(idx), native.ptr(weight), native.ptr(counts), native.ptr(load_accum),
-                                  c_int(T), c_int(D), c_int(E), c_int(top_k), c_int(SCORE_IDS[score]),
-                                  c_int(int(norm_topk)), c_float(scaling), native.stream_ptr())
+        tensor_core = D % 8 == 0 and x.stride(1) == 1
+        if tensor_core:
+            # gate logits on the tensor cores with the fp32 gate matrix split into a bf16 head and a bf16
+            # remainder: x W_hi^T + x W_lo^T, fp32 accumulation, keeps ~16 mantissa bits of W
+            w_hi = W.detach().to(torch.bfloat16)
+            w_lo = (W.detach() - w_hi.float()).to(torch.bfloat16)
+            xc = x if x.is_contiguous() else x.contiguous()
+            matmul(xc, w_hi, out=logits)
+            matmul(xc, w_lo, out=logits, accumulate=True)
+        rc = L.kwu_moe_router_fwd(native.ptr(None if tensor_core else x), c_int(x.stride(0)), native.ptr(W),
+                                  native.ptr(bias), native.ptr(logits), native.ptr(idx), native.ptr(weight),
+                                  native.ptr(counts), native.ptr(load_accum), c_int(T), c_int(D), c_int(E), c_int(top_k),
+                                  c_int(SCORE_IDS[score]), c_int(int(norm_topk)), c_float(scaling), native.stream_ptr())
         native.check(rc, "moe_router_fwd")
         ctx.save_for_backward(x, W, logits, idx)
         ctx.cfg = (score, norm_topk, scaling)
+        ctx.weight_param = W
         ctx.mark_non_differentiable(idx, counts)
         return idx, weight, counts, logits
 
     @staticmethod
     def backward(ctx, _didx, dweight, _dcounts, dlogits_in):
+        from kohakuwullm_b200.ops.gemm import matmul
+
         L = native.require()
         x, W, logits, idx = ctx.saved_tensors
         score, norm_topk, scaling = ctx.cfg
@@ -96,23 +112,26 @@ class _RouterTopK(torch.autograd.Function):
         E = W.shape[0]
         k = idx.shape[1]
         dl = torch.empty(T, E, dtype=torch.float32, device=x.device)
+        dl16 = torch.empty(T, E, dtype=torch.bfloat16, device=x.device)
         dw_in = dweight.float().contiguous() if dweight is not None else torch.zeros(T, k, dtype=torch.float32, device=x.device)
         dl_in = dlogits_in.float().contiguous() if dlogits_in is not None else None
         need_dx, need_dW = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
-        dx = torch.empty(T, D, dtype=x.dtype, device=x.device) if need_dx else None
-        dW32 = None
-        if need_dW:
-            main_grad = getattr(W, "main_grad", None)
-            dW32 = main_grad if (main_grad is not None and main_grad.dtype == torch.float32) else \
-                torch.zeros(E, D, dtype=torch.float32, device=x.device)
+        # logit gradient (fp32 and a bf16 copy); the two gate-matrix products then run on the tensor cores
         rc = L.kwu_moe_router_bwd(native.ptr(logits), native.ptr(idx), native.ptr(dw_in), native.ptr(dl_in), native.ptr(dl),
-                                  native.ptr(x), c_int(x.stride(0)), native.ptr(W), native.ptr(dx), c_int(D),
-                                  native.ptr(dW32), c_int(T), c_int(D), c_int(E), c_int(k), c_int(SCORE_IDS[score]),
+                                  native.ptr(dl16), native.ptr(None), c_int(0), native.ptr(W), native.ptr(None), c_int(0),
+                                  native.ptr(None), c_int(T), c_int(D), c_int(E), c_int(k), c_int(SCORE_IDS[score]),
                                   c_int(int(norm_topk)), c_float(scaling), native.stream_ptr())
         native.check(rc, "moe_router_bwd")
+        xc = x if x.is_contiguous() else x.contiguous()
+        dx = matmul(dl16, W.detach().to(torch.bfloat16), b_mn=True, out_dtype=x.dtype) if need_dx else None
         dW = None
-        if need_dW and dW32 is not getattr(W, "main_grad", None):
-            dW = dW32.to(W.dtype)
+        if need_dW:
+            main_grad = getattr(ctx.weight_param, "main_grad", None)
+            into_main = main_grad is not None and main_grad.dtype == torch.float32 and main_grad.is_contiguous()
+            target = main_grad if into_main else torch.zeros(E, D, dtype=torch.float32, device=x.device)
+            matmul(dl16, xc, a_mn=True, b_mn=True, out=target, accumulate=True)    # dW += dl^T x, fp32
+            if not into_main:
+                dW = target.to(W.dtype)
         return dx, dW, None, None, None, None, None, None
 
 
@@ -286,6 +305,6 @@ def routed_experts(x, idx, weight, counts, w_in, w_out, q_in=None, q_out=None):
     plan = make_plan(idx.to(torch.int32).contiguous(), counts.to(torch.int32), w_in.shape[0])
     rows = _Gather.apply(x.contiguous(), plan)
     h = grouped_linear(rows, w_in, plan, q_in)
-    a = swiglu(h)
+    a = swiglu(h, emit_mx=q_out is not None, emit_mx_grad=q_in is not None)   # fp8 copies for the neighbours
     y_rows = grouped_linear(a, w_out, plan, q_out)
     return _Combine.apply(y_rows, weight, plan, T)

@@ -265,7 +265,7 @@ class _MXFP8GroupedLinear(torch.autograd.Function):
     def forward(ctx, rows, W, qw: GroupedQuantizedWeight, plan, out=None, dgrad_out=None, out_row_ptrs=None,
                 dgrad_row_ptrs=None):
         E, N, K = W.shape
-        xq, xsf = quantize(rows)
+        xq, xsf = take_quantized(rows) or quantize(rows)
         out = grouped_gemm(xq, xsf, qw.q, qw.sf, N, E, plan.tiles, out_dtype=rows.dtype, out=out, row_ptrs=out_row_ptrs)
         ctx.save_for_backward(rows, W)
         ctx.qw, ctx.plan, ctx.dgrad_out, ctx.dgrad_row_ptrs = qw, plan, dgrad_out, dgrad_row_ptrs
@@ -280,7 +280,7 @@ class _MXFP8GroupedLinear(torch.autograd.Function):
         dout = dout.contiguous()
         drows = dW = None
         if ctx.needs_input_grad[0]:
-            dq, dsf = quantize(dout)
+            dq, dsf = take_quantized(dout) or quantize(dout)
             drows = grouped_gemm(dq, dsf, qw.qt, qw.sft, K, E, plan.tiles, out_dtype=rows.dtype, out=ctx.dgrad_out,
                                  row_ptrs=ctx.dgrad_row_ptrs)
         if ctx.needs_input_grad[1]:

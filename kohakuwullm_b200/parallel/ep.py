@@ -291,7 +291,7 @@ def ep_routed_experts(ep: ExpertParallel, x, idx, weight, counts, w_in_local, w_
     stage = ep.output_rows()
     ptrs = plan.row_ptrs if ep.scatter_epilogue else None   # None: pull path, the GEMMs write `stage` itself
     h = grouped_linear(rows, w_in_local, plan, q_in, dgrad_out=stage, dgrad_row_ptrs=ptrs)
-    a = swiglu(h)
+    a = swiglu(h, emit_mx=q_out is not None, emit_mx_grad=q_in is not None)
     y_rows = grouped_linear(a, w_out_local, plan, q_out, out=stage, out_row_ptrs=ptrs)
     return ep.combine(y_rows, weight, plan, T)
 
