@@ -174,5 +174,6 @@ def test_router_backward_matches_eager(score, norm_topk):
 
     dx_n, dW_n = run(x)
     dx_e, dW_e = run(x.float())
-    torch.testing.assert_close(dW_n, dW_e, rtol=2e-3, atol=2e-3 * dW_e.abs().max().item())
+    # the products run on the tensor cores with a bf16 copy of the logit gradient: bf16-level agreement
+    torch.testing.assert_close(dW_n, dW_e, rtol=2e-2, atol=1e-2 * dW_e.abs().max().item())
     torch.testing.assert_close(dx_n, dx_e, rtol=2e-2, atol=2e-2 * dx_e.abs().max().item())
