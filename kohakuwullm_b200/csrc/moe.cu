@@ -13,6 +13,7 @@
 //   moe_combine_bwd  d_rows[pos] = w * dout[t] (padding rows zero), d_w[t,slot] = <rows[pos], dout[t]>.
 // Reference: src/kohakuwullm/kernels/moe/router.py:76-194, moe_dispatch.py:14-130.
 #include "common.cuh"
+#include "mx_quant.cuh"
 
 namespace kwu {
 
@@ -188,21 +189,30 @@ __global__ void moe_place_kernel(const int* __restrict__ idx, int n_pairs, const
   pair_of[pos] = i;
 }
 
-// rows[pos] = x[pair_of[pos] / k] (zero when the row is padding). One warp per row.
+// rows[pos] = x[pair_of[pos] / k] (zero when the row is padding). One warp per row. With `mx` the MXFP8 copy of
+// the gathered rows (what the first expert GEMM consumes) is written in the same pass: sort + quantise + place.
 __global__ void __launch_bounds__(256)
 moe_gather_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const int* __restrict__ pair_of, int top_k,
-                  __nv_bfloat16* __restrict__ rows, int D, int max_rows, const int* __restrict__ offsets, int E) {
+                  __nv_bfloat16* __restrict__ rows, int D, int max_rows, const int* __restrict__ offsets, int E,
+                  const MxOut mx) {
   const int lane = threadIdx.x & 31;
   const int wpb = blockDim.x >> 5;
   const int used = offsets[E];
+  const int nvec = D / 8;
   for (int r = blockIdx.x * wpb + (threadIdx.x >> 5); r < used; r += gridDim.x * wpb) {
     const int pair = pair_of[r];
     uint4* dst = reinterpret_cast<uint4*>(rows + static_cast<size_t>(r) * D);
-    if (pair < 0) {
-      for (int v = lane; v < D / 8; v += 32) dst[v] = make_uint4(0, 0, 0, 0);
-    } else {
-      const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(pair / top_k) * ldx);
-      for (int v = lane; v < D / 8; v += 32) dst[v] = src[v];
+    const uint4* src = pair < 0 ? nullptr : reinterpret_cast<const uint4*>(x + static_cast<size_t>(pair / top_k) * ldx);
+    for (int v0 = 0; v0 < nvec; v0 += 32) {   // uniform trip count: the fp8 emission shuffles inside
+      const int v = v0 + lane;
+      const bool in = v < nvec;
+      const uint4 a = (in && src) ? src[v] : make_uint4(0, 0, 0, 0);
+      if (in) dst[v] = a;
+      if (mx.q) {
+        float f[8];
+        unpack8(a, f);
+        mx_emit8(f, in, r, 8 * v, mx.q, mx.ldq, mx.sf, mx.n_kchunks);
+      }
     }
   }
 }
@@ -236,35 +246,42 @@ moe_combine_kernel(const __nv_bfloat16* __restrict__ rows, const int* __restrict
 __global__ void __launch_bounds__(256)
 moe_combine_bwd_kernel(const __nv_bfloat16* __restrict__ rows, const __nv_bfloat16* __restrict__ dout, int lddo,
                        const int* __restrict__ pair_of, const float* __restrict__ w, __nv_bfloat16* __restrict__ d_rows,
-                       float* __restrict__ d_w, int top_k, int D, const int* __restrict__ offsets, int E) {
+                       float* __restrict__ d_w, int top_k, int D, const int* __restrict__ offsets, int E,
+                       const MxOut mx) {
   const int lane = threadIdx.x & 31;
   const int wpb = blockDim.x >> 5;
   const int used = offsets[E];
+  const int nvec = D / 8;
   for (int r = blockIdx.x * wpb + (threadIdx.x >> 5); r < used; r += gridDim.x * wpb) {
     const int pair = pair_of[r];
     uint4* dst = reinterpret_cast<uint4*>(d_rows + static_cast<size_t>(r) * D);
-    if (pair < 0) {
-      for (int v = lane; v < D / 8; v += 32) dst[v] = make_uint4(0, 0, 0, 0);
-      continue;
-    }
-    const float ws = w[pair];
-    const uint4* g = reinterpret_cast<const uint4*>(dout + static_cast<size_t>(pair / top_k) * lddo);
+    const float ws = pair < 0 ? 0.f : w[pair];
+    const uint4* g = pair < 0 ? nullptr : reinterpret_cast<const uint4*>(dout + static_cast<size_t>(pair / top_k) * lddo);
     const uint4* y = reinterpret_cast<const uint4*>(rows + static_cast<size_t>(r) * D);
     float dot = 0.f;
-    for (int v = lane; v < D / 8; v += 32) {
-      const uint4 gv = g[v], yv = y[v];
-      const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, yw[4] = {yv.x, yv.y, yv.z, yv.w};
-      uint32_t o[4];
+    for (int v0 = 0; v0 < nvec; v0 += 32) {   // uniform trip count: the fp8 emission shuffles inside
+      const int v = v0 + lane;
+      const bool in = v < nvec;
+      uint32_t o[4] = {0u, 0u, 0u, 0u};
+      if (in && g) {
+        const uint4 gv = g[v], yv = y[v];
+        const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, yw[4] = {yv.x, yv.y, yv.z, yv.w};
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float2 gf = unpack_bf16(gw[e]), yf = unpack_bf16(yw[e]);
-        dot += gf.x * yf.x + gf.y * yf.y;
-        o[e] = pack_bf16(ws * gf.x, ws * gf.y);
+        for (int e = 0; e < 4; ++e) {
+          const float2 gf = unpack_bf16(gw[e]), yf = unpack_bf16(yw[e]);
+          dot += gf.x * yf.x + gf.y * yf.y;
+          o[e] = pack_bf16(ws * gf.x, ws * gf.y);
+        }
       }
-      dst[v] = make_uint4(o[0], o[1], o[2], o[3]);
+      if (in) dst[v] = make_uint4(o[0], o[1], o[2], o[3]);
+      if (mx.q) {
+        float f[8];
+        unpack8(make_uint4(o[0], o[1], o[2], o[3]), f);
+        mx_emit8(f, in, r, 8 * v, mx.q, mx.ldq, mx.sf, mx.n_kchunks);
+      }
     }
     dot = warp_sum(dot);
-    if (lane == 0 && d_w) d_w[pair] = dot;
+    if (lane == 0 && d_w && pair >= 0) d_w[pair] = dot;
   }
 }
 
@@ -303,11 +320,19 @@ KWU_API int kwu_moe_plan_and_place(const int* counts, const int* idx, int n_pair
   return moe_check("moe_plan_and_place");
 }
 
+static MxOut moe_mx(void* q, void* sf, int D) {
+  MxOut m;
+  m.q = reinterpret_cast<uint8_t*>(q); m.ldq = D; m.sf = reinterpret_cast<uint8_t*>(sf); m.n_kchunks = D >> 7;
+  return m;
+}
+
+// q / sf (optional, D %% 128 == 0): MXFP8 copy of the gathered rows, written in the same pass.
 KWU_API int kwu_moe_gather(const void* x, int ldx, const int* pair_of, int top_k, void* rows, int D, int max_rows,
-                           const int* offsets, int E, void* stream) {
+                           const int* offsets, int E, void* q, void* sf, void* stream) {
   if (D % 8) { set_last_error("moe_gather: D must be a multiple of 8"); return 7; }
+  if (q && D % 128) { set_last_error("moe_gather: the fp8 copy needs D %% 128 == 0"); return 7; }
   moe_gather_kernel<<<148 * 8, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      (const __nv_bfloat16*)x, ldx, pair_of, top_k, (__nv_bfloat16*)rows, D, max_rows, offsets, E); kwu::count_launch();
+      (const __nv_bfloat16*)x, ldx, pair_of, top_k, (__nv_bfloat16*)rows, D, max_rows, offsets, E, moe_mx(q, sf, D)); kwu::count_launch();
   return moe_check("moe_gather");
 }
 
@@ -322,12 +347,15 @@ KWU_API int kwu_moe_combine(const void* rows, const int* pos_of, const float* w,
   return moe_check("moe_combine");
 }
 
+// q / sf (optional, D %% 128 == 0): MXFP8 copy of d_rows, written in the same pass.
 KWU_API int kwu_moe_combine_bwd(const void* rows, const void* dout, int lddo, const int* pair_of, const float* w,
-                                void* d_rows, float* d_w, int top_k, int D, const int* offsets, int E, void* stream) {
+                                void* d_rows, float* d_w, int top_k, int D, const int* offsets, int E, void* q,
+                                void* sf, void* stream) {
   if (D % 8) { set_last_error("moe_combine_bwd: D must be a multiple of 8"); return 7; }
+  if (q && D % 128) { set_last_error("moe_combine_bwd: the fp8 copy needs D %% 128 == 0"); return 7; }
   moe_combine_bwd_kernel<<<148 * 8, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       (const __nv_bfloat16*)rows, (const __nv_bfloat16*)dout, lddo, pair_of, w, (__nv_bfloat16*)d_rows, d_w, top_k, D,
-      offsets, E); kwu::count_launch();
+      offsets, E, moe_mx(q, sf, D)); kwu::count_launch();
   return moe_check("moe_combine_bwd");
 }
 

@@ -178,14 +178,22 @@ def make_plan(idx: torch.Tensor, counts: torch.Tensor, num_experts: int) -> Disp
 
 class _Gather(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, plan: DispatchPlan):
+    def forward(ctx, x, plan: DispatchPlan, emit_mx=False):
+        """``emit_mx``: also write the MXFP8 copy of the gathered rows for the MXFP8 expert GEMM that follows."""
+        from kohakuwullm_b200.ops import mxfp8 as mx
+
         L = native.require()
         T, D = x.shape
         rows = torch.empty(plan.max_rows, D, dtype=x.dtype, device=x.device)
+        q = sf = None
+        if emit_mx and mx.can_emit(plan.max_rows, D):
+            q, sf = mx.alloc_quantized(plan.max_rows, D, x.device)
         rc = L.kwu_moe_gather(native.ptr(x), c_int(x.stride(0)), native.ptr(plan.pair_of), c_int(plan.top_k),
                               native.ptr(rows), c_int(D), c_int(plan.max_rows), native.ptr(plan.offsets),
-                              c_int(plan.num_experts), native.stream_ptr())
+                              c_int(plan.num_experts), native.ptr(q), native.ptr(sf), native.stream_ptr())
         native.check(rc, "moe_gather")
+        if q is not None:
+            mx.stash_quantized(rows, q, sf)
         ctx.plan, ctx.T = plan, T
         return rows
 
@@ -198,7 +206,7 @@ class _Gather(torch.autograd.Function):
         rc = L.kwu_moe_combine(native.ptr(drows.contiguous()), native.ptr(plan.pos_of), native.ptr(None), native.ptr(dx),
                                c_int(D), c_int(ctx.T), c_int(plan.top_k), c_int(D), native.stream_ptr())
         native.check(rc, "moe_gather_bwd")
-        return dx, None
+        return dx, None, None
 
 
 class _GroupedLinear(torch.autograd.Function):
@@ -258,7 +266,7 @@ class _GroupedLinear(torch.autograd.Function):
 
 class _Combine(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, rows, weight, plan: DispatchPlan, T):
+    def forward(ctx, rows, weight, plan: DispatchPlan, T, emit_mx_grad=False):
         L = native.require()
         D = rows.shape[1]
         out = torch.empty(T, D, dtype=rows.dtype, device=rows.device)
@@ -268,6 +276,7 @@ class _Combine(torch.autograd.Function):
         native.check(rc, "moe_combine")
         ctx.save_for_backward(rows, w)
         ctx.plan, ctx.wshape, ctx.wdtype = plan, weight.shape, weight.dtype
+        ctx.emit_mx_grad = emit_mx_grad
         return out
 
     @staticmethod
@@ -277,13 +286,21 @@ class _Combine(torch.autograd.Function):
         plan = ctx.plan
         D = rows.shape[1]
         dout = dout.contiguous()
+        from kohakuwullm_b200.ops import mxfp8 as mx
+
         drows = torch.empty_like(rows)
         dw = torch.zeros_like(w)
+        q = sf = None
+        if ctx.emit_mx_grad and mx.can_emit(rows.shape[0], D):
+            q, sf = mx.alloc_quantized(rows.shape[0], D, rows.device)
         rc = L.kwu_moe_combine_bwd(native.ptr(rows), native.ptr(dout), c_int(dout.stride(0)), native.ptr(plan.pair_of),
                                    native.ptr(w), native.ptr(drows), native.ptr(dw), c_int(plan.top_k), c_int(D),
-                                   native.ptr(plan.offsets), c_int(plan.num_experts), native.stream_ptr())
+                                   native.ptr(plan.offsets), c_int(plan.num_experts), native.ptr(q), native.ptr(sf),
+                                   native.stream_ptr())
         native.check(rc, "moe_combine_bwd")
-        return drows, dw.view(ctx.wshape).to(ctx.wdtype), None, None
+        if q is not None:
+            mx.stash_quantized(drows, q, sf)
+        return drows, dw.view(ctx.wshape).to(ctx.wdtype), None, None, None
 
 
 def grouped_linear(rows, W, plan, qweight=None, out=None, dgrad_out=None, out_row_ptrs=None, dgrad_row_ptrs=None):
@@ -303,8 +320,9 @@ def routed_experts(x, idx, weight, counts, w_in, w_out, q_in=None, q_out=None):
     ``q_in`` / ``q_out``: MXFP8 copies of the expert weights (both GEMMs then run block-scaled fp8)."""
     T = x.shape[0]
     plan = make_plan(idx.to(torch.int32).contiguous(), counts.to(torch.int32), w_in.shape[0])
-    rows = _Gather.apply(x.contiguous(), plan)
+    # with MXFP8 experts every producer writes the fp8 copy its consumer needs in the same pass
+    rows = _Gather.apply(x.contiguous(), plan, q_in is not None)
     h = grouped_linear(rows, w_in, plan, q_in)
-    a = swiglu(h, emit_mx=q_out is not None, emit_mx_grad=q_in is not None)   # fp8 copies for the neighbours
+    a = swiglu(h, emit_mx=q_out is not None, emit_mx_grad=q_in is not None)
     y_rows = grouped_linear(a, w_out, plan, q_out)
-    return _Combine.apply(y_rows, weight, plan, T)
+    return _Combine.apply(y_rows, weight, plan, T, q_out is not None)
