@@ -9,6 +9,7 @@ initialisation, device-timed, max over ranks, one JSON line from rank 0) with th
   2  dense 546M, MXFP8 linears, data parallel, 4096-token packs x 4 accumulation (what ``bench.py`` measures too)
   3  MoE 991M under pipeline parallelism: measured stage split, 1F1B, 16 micro-batches of 4096 tokens
   4  MoE 991M, expert parallel + data parallel, 8192-token packs, routers skewed by a seeded N(0, 0.5) bias
+     (receive capacity 5x the mean: with 8 ranks the busiest rank of a layer gets up to ~4x the mean under this skew)
   5  sliding-window 1.1B (window 1024 on 3 of 4 layers, 4 sinks, YaRN x4), 16384-token packs with log-uniform
      documents, MXFP8 attention operands, data parallel
 """
@@ -23,7 +24,7 @@ CONFIGS = {
     3: ["--preset", "B200-moe-991M", "--micro-tokens", "4096", "--accum", "16", "--len-min", "64", "--len-max", "4096",
         "--pipeline", "--schedule", "1f1b"],
     4: ["--preset", "B200-moe-991M", "--micro-tokens", "8192", "--accum", "4", "--len-min", "64", "--len-max", "4096",
-        "--expert-parallel", "--router-bias-std", "0.5", "--ep-capacity", "3.0"],
+        "--expert-parallel", "--router-bias-std", "0.5", "--ep-capacity", "5.0"],
     5: ["--preset", "B200-sliding-1B", "--micro-tokens", "16384", "--accum", "1", "--len-min", "128", "--len-max", "16384",
         "--log-uniform", "--set", "attn='mxfp8'"],
 }
