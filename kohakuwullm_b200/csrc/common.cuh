@@ -75,37 +75,40 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// One probe of the barrier. A thread whose phase is not complete yet is suspended by the hardware until the
+// phase completes or `KWU_WAIT_SUSPEND_NS` have passed, whichever is first, so a waiting warp costs no issue
+// slots and no ALU cycles while it waits (a busy loop of probes took a large share of both from the warps
+// that had work).
+#ifndef KWU_WAIT_SUSPEND_NS
+#define KWU_WAIT_SUSPEND_NS 20000
+#endif
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t"
       ".reg .pred P;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
       "selp.b32 %0, 1, 0, P;\n\t"
       "}\n"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(static_cast<uint32_t>(KWU_WAIT_SUSPEND_NS))
       : "memory");
   return ok != 0;
 }
 
 // Bounded wait. `abort_flag` lives in shared memory and is shared by every role of the CTA.
-// Returns false when the wait was abandoned (own time-out or somebody else's abort).
+// Returns false when the wait was abandoned (own time-out or somebody else's abort). Every failed probe
+// has already slept for up to the suspend time, so the abort flag and the clock are read after each one.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int code) {
-  long long t0 = 0;
-  uint32_t spins = 0;
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
   while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 0x3ff) == 0) {
-      if (*abort_flag) return false;
-      const long long now = clock64();
-      if (t0 == 0) {
-        t0 = now;
-      } else if (now - t0 > KWU_WAIT_LIMIT_CYCLES) {
-        *abort_flag = 1;
-        if (status) atomicCAS(status, 0, code);
-        return false;
-      }
+    if (*abort_flag) return false;
+    if (clock64() - t0 > KWU_WAIT_LIMIT_CYCLES) {
+      *abort_flag = 1;
+      if (status) atomicCAS(status, 0, code);
+      return false;
     }
   }
   return true;

@@ -55,9 +55,17 @@ def gather_state_dict(module: torch.nn.Module, names: Mapping[str, str] | None =
     return merged
 
 
-def gather_optimizer_state(optimizer, names: Mapping[str, str] | None = None, group=None) -> dict:
+def expert_sharded_names(module: torch.nn.Module) -> set[str]:
+    """Names of the parameters of which every rank holds its own slice of the expert dimension."""
+    return {n for n, p in module.named_parameters() if getattr(p, "ep_local", False)}
+
+
+def gather_optimizer_state(optimizer, names: Mapping[str, str] | None = None, group=None,
+                           ep_names: set[str] | frozenset[str] = frozenset()) -> dict:
     """Whole-model-named optimizer state. ``optimizer.state_dict()`` must expose
-    ``named_optimizer_state`` keyed by local parameter names (``FlatAdamW`` does)."""
+    ``named_optimizer_state`` keyed by local parameter names (``FlatAdamW`` does). Entries of ``ep_names``
+    (expert-parallel parameters: every rank owns a different slice under the same name) are concatenated in
+    rank order, which is the order of the expert dimension; all others are merged by their flat ranges."""
     names = names or {}
     sd = optimizer.state_dict()
     mine = {names.get(k, k): {kk: (vv.detach().to("cpu", copy=True) if torch.is_tensor(vv) else vv)
@@ -67,14 +75,41 @@ def gather_optimizer_state(optimizer, names: Mapping[str, str] | None = None, gr
         parts: list = [None] * _world(group)
         dist.all_gather_object(parts, mine, group=group)
         merged: dict = {}
+        ep_global = {names.get(k, k) for k in ep_names}
         for part in parts:
             for k, v in part.items():
                 if k not in merged:
                     merged[k] = v
+                elif k in ep_global:
+                    merged[k] = _concat_expert_slices(merged[k], v)
                 elif "range" in v and "range" in merged[k]:
                     merged[k] = _merge_ranges(merged[k], v)
         mine = merged
     return {"named_optimizer_state": mine, "step": sd.get("step", 0), "hyper": sd.get("hyper", {})}
+
+
+def _concat_expert_slices(a: dict, b: dict) -> dict:
+    """Append rank r+1's state of an expert-parallel parameter to the ranks before it."""
+    out = {}
+    for k in a:
+        if torch.is_tensor(a[k]):
+            out[k] = torch.cat([a[k].reshape(-1), b[k].reshape(-1)])
+    out["range"] = (0, next(iter(out.values())).numel())
+    return out
+
+
+def _local_expert_slice(entry: dict, local_numel: int, rank: int, world: int) -> dict:
+    """This rank's part of a whole-model optimizer entry of an expert-parallel parameter."""
+    lo, hi = entry.get("range", (0, None))
+    n = next(v for v in entry.values() if torch.is_tensor(v)).numel()
+    if lo != 0 or n == local_numel:
+        return entry                                  # already a local slice (same layout as saved)
+    if n != local_numel * world:
+        raise ValueError(f"optimizer state of {n} elements does not split into {world} x {local_numel}")
+    out = {k: (v.reshape(-1)[rank * local_numel:(rank + 1) * local_numel].clone() if torch.is_tensor(v) else v)
+           for k, v in entry.items()}
+    out["range"] = (0, local_numel)
+    return out
 
 
 def _merge_ranges(a: dict, b: dict) -> dict:
@@ -115,10 +150,19 @@ def load(path: str, module: torch.nn.Module, optimizer=None, *, names: Mapping[s
     state = payload["state_dict"]
     local = {}
     missing = []
+    ep_params = {n: p for n, p in module.named_parameters() if getattr(p, "ep_local", False)}
+    world, rank = _world(group), _rank(group)
     for k in module.state_dict().keys():
         g = names.get(k, k)
         if g in state:
-            local[k] = state[g]
+            t = state[g]
+            if k in ep_params and t.shape[0] != ep_params[k].shape[0]:
+                # a whole-model tensor into an expert-parallel module: keep this rank's experts
+                n_local = ep_params[k].shape[0]
+                if t.shape[0] != n_local * world:
+                    raise ValueError(f"{g}: {t.shape[0]} experts do not split into {world} x {n_local}")
+                t = t[rank * n_local:(rank + 1) * n_local]
+            local[k] = t
         else:
             missing.append(g)
     if missing and strict:
@@ -136,5 +180,8 @@ def load(path: str, module: torch.nn.Module, optimizer=None, *, names: Mapping[s
         else:
             inverse = {v: k for k, v in names.items()}
             named = {inverse.get(g, g): v for g, v in opt["named_optimizer_state"].items()}
+            for k, p in ep_params.items():
+                if k in named:
+                    named[k] = _local_expert_slice(named[k], p.numel(), rank, world)
             optimizer.load_state_dict({"named_optimizer_state": named, "step": opt.get("step", 0)})
     return {k: v for k, v in payload.items() if k not in ("state_dict", "optimizer_states")}

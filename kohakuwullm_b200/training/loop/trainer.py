@@ -148,17 +148,23 @@ class LMTrainer:
         loader_state = self.loader.state_dict() if hasattr(self.loader, "state_dict") else None
         state = resume.pack_state(self.snapshot(sync=True), self.loss_ema, loader_state, self.global_step)
         extra = {resume.RESUME_KEY: state, "callbacks": self.callbacks.state_dict()}
-        # weights are replicated under DDP: gather only the (sharded) optimizer state
-        if self.rank == 0 or self.engine.fused_sync:
-            pass
         self._save(path, extra)
 
     def _save(self, path: str, extra: dict) -> None:
-        opt = ckpt.gather_optimizer_state(self.engine.optimizer, None, self.group) if self.engine.fused_sync else \
+        # weights are replicated under DDP, so rank 0's copy is the model; what is spread over the ranks is the
+        # ZeRO-sharded optimizer state and, under expert parallelism, the experts with their optimizer state
+        ep_names = ckpt.expert_sharded_names(self.backbone) if self.world > 1 else set()
+        sharded = self.engine.fused_sync or bool(ep_names)
+        opt = ckpt.gather_optimizer_state(self.engine.optimizer, None, self.group, ep_names=ep_names) if sharded else \
             {"named_optimizer_state": self.engine.optimizer.state_dict()["named_optimizer_state"],
              "step": self.engine.optimizer.step_count}
+        weights = ckpt.local_state_dict(self.backbone)
+        if ep_names:
+            from kohakuwullm_b200.parallel.ep import gather_expert_state
+
+            weights = {k: v.cpu() for k, v in gather_expert_state(weights, self.backbone, self.group).items()}
         if self.rank == 0:
-            payload = {"state_dict": ckpt.local_state_dict(self.backbone), "optimizer_states": [opt],
+            payload = {"state_dict": weights, "optimizer_states": [opt],
                        "global_step": self.global_step, "epoch": 0, "pytorch-lightning_version": ckpt.FORMAT_TAG}
             payload.update(extra)
             os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)

@@ -64,3 +64,58 @@ def test_expert_parallel_step_matches_single_process():
     for k, v in ref.items():
         if v.is_floating_point():
             torch.testing.assert_close(got["state"][k], v, rtol=0, atol=3e-4, msg=lambda m, k=k: f"{k}: {m}")
+
+
+def _ckpt_worker(rank, world, port, tmp):
+    from kohakuwullm_b200.pipe import checkpoint as ckpt
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    eng = TrainEngine(_model(), lr=1e-2, max_grad_norm=1.0, expert_parallel=True)
+    eng.step([collate_packed(_docs()[rank::world])])
+    # whole-model checkpoint written from the expert-parallel layout
+    ep_names = ckpt.expert_sharded_names(eng.model)
+    assert ep_names
+    opt = ckpt.gather_optimizer_state(eng.optimizer, None, None, ep_names=ep_names)
+    weights = gather_expert_state(ckpt.local_state_dict(eng.model), eng.model)
+    path = os.path.join(tmp, "ep.ckpt")
+    if rank == 0:
+        torch.save({"state_dict": weights, "optimizer_states": [opt]}, path)
+    dist.barrier()
+    # a fresh expert-parallel engine (other initial weights) resumes from it and takes the same second step
+    fresh = TrainEngine(_model(seed=11), lr=1e-2, max_grad_norm=1.0, expert_parallel=True)
+    ckpt.load(path, fresh.model, fresh.optimizer)
+    fresh.global_step = eng.global_step
+    batch = [collate_packed(_docs(seed=6)[rank::world])]
+    a, b = eng.step(batch), fresh.step(batch)
+    assert abs(float(a["loss"]) - float(b["loss"])) < 1e-6, (float(a["loss"]), float(b["loss"]))
+    for (n, p), (_, q) in zip(eng.model.named_parameters(), fresh.model.named_parameters()):
+        torch.testing.assert_close(p, q, rtol=0, atol=1e-6, msg=lambda m, n=n: f"{n}: {m}")
+    if rank == 0:
+        torch.save({"loss": float(a["loss"])}, os.path.join(tmp, "second.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_expert_parallel_checkpoint_reshards_weights_and_optimizer_state():
+    """A checkpoint written by 2 expert-parallel ranks holds all experts and their AdamW state; it resumes a
+    2-rank expert-parallel run exactly and a single-process run holding every expert to rounding."""
+    from kohakuwullm_b200.pipe import checkpoint as ckpt
+    from tests.helpers import free_port
+
+    with tempfile.TemporaryDirectory() as tmp:
+        mp.spawn(_ckpt_worker, args=(2, free_port(), tmp), nprocs=2, join=True)
+        payload = torch.load(os.path.join(tmp, "ep.ckpt"), weights_only=False)
+        second = torch.load(os.path.join(tmp, "second.pt"))
+        eng = TrainEngine(_model(seed=3), lr=1e-2, max_grad_norm=1.0)
+        full_experts = {n: p for n, p in eng.model.named_parameters() if n.endswith(("w_in", "w_out")) and p.dim() == 3}
+        assert full_experts
+        for n, p in full_experts.items():
+            assert payload["state_dict"][n].shape == p.shape, n
+            entry = payload["optimizer_states"][0]["named_optimizer_state"][n]
+            assert entry["exp_avg"].numel() == p.numel() and float(entry["exp_avg"].abs().sum()) > 0
+        ckpt.load(os.path.join(tmp, "ep.ckpt"), eng.model, eng.optimizer)
+        eng.global_step = 1
+        out = eng.step([collate_packed(_docs(seed=6))])
+    assert abs(float(out["loss"]) - second["loss"]) < 1e-5
