@@ -20,6 +20,7 @@ namespace kwu {
 constexpr int FB_D = 64;
 constexpr int FB_THREADS = 320;  // 8 softmax warps (two per TMEM lane quarter) + TMA warp + MMA warp
 constexpr float FB_LOG2E = 1.4426950408889634f;
+template <bool V> struct BoolC { static constexpr bool value = V; };   // compile-time switch for the tile bodies
 
 // ------------------------------------------------------------------------------------ delta
 __global__ void __launch_bounds__(256)
@@ -93,8 +94,8 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
   uint8_t* sV = smem + 16384;
   uint8_t* sQ = smem + 32768;           // 2 stages x 8 KB
   uint8_t* sDO = smem + 32768 + 16384;  // 2 stages x 8 KB
-  float* sLse = reinterpret_cast<float*>(smem + 65536);        // 2 stages x 64, pre-scaled by log2(e)
-  float* sDelta = sLse + 128;                                  // 2 stages x 64
+  float* sLse = reinterpret_cast<float*>(smem + 65536);        // 2 stages x 64: -lse * log2(e)
+  float* sDelta = sLse + 128;                                  // 2 stages x 64: -delta * scale
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 65536 + 1024);
   uint64_t* kv_full = bars + 0;
   uint64_t* qd_full = bars + 1;   // [2]
@@ -165,8 +166,8 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
           const int qc = min(q_lo + lane + 32 * u, p.T - 1);
-          sLse[s * 64 + lane + 32 * u] = lse_h[qc] * FB_LOG2E;
-          sDelta[s * 64 + lane + 32 * u] = dl_h[qc] * p.scale;
+          sLse[s * 64 + lane + 32 * u] = -lse_h[qc] * FB_LOG2E;    // negated: they enter as FMA addends
+          sDelta[s * 64 + lane + 32 * u] = -dl_h[qc] * p.scale;
         }
         __syncwarp();
         if (lane == 0) {
@@ -177,58 +178,69 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
       }
     }
   } else if (warp == 9) {
-    if (lane == 0) {
-      const uint32_t idesc_s = make_idesc_f16(128, 64, 1, 0, 0);   // S^T, dP^T: N = 64 queries
-      const uint32_t idesc_a = make_idesc_f16(128, 64, 1, 0, 1);   // dV, dK: B is MN-major
-      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV);
-      int g = 0, ic = 0;
-      bool ok = true;
-      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-        DkdvItem it;
-        if (!dkdv_decode(p, item, it)) continue;
-        ok = mbar_wait(kv_full, ic & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
-        for (int i = 0; i < it.n_it && ok; ++i) {
-          const int gi = g + i;
-          const int s = gi & 1;
-          const uint32_t ph = (gi >> 1) & 1;
-          ok = mbar_wait(&qd_full[s], ph, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
-          if (!ok) break;
-          tc_fence_after();
-          const uint32_t bQ = smem_u32(sQ + s * 8192), bDO = smem_u32(sDO + s * 8192);
+    // The whole warp walks the loop, so that addresses, descriptors and loop counters stay warp-uniform
+    // (a single-lane branch would keep them in per-thread registers and pay a transfer into the uniform
+    // registers for every operand of every tcgen05.mma); one elected lane issues the tensor-core work.
+    const bool leader = elect_one();
+    const uint32_t idesc_s = make_idesc_f16(128, 64, 1, 0, 0);   // S^T, dP^T: N = 64 queries
+    const uint32_t idesc_a = make_idesc_f16(128, 64, 1, 0, 1);   // dV, dK: B is MN-major
+    const uint64_t dK0 = make_smem_desc(smem_u32(sK), 16, 1024, SWZ_128B);
+    const uint64_t dV0 = make_smem_desc(smem_u32(sV), 16, 1024, SWZ_128B);
+    int g = 0, ic = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      DkdvItem it;
+      if (!dkdv_decode(p, item, it)) continue;
+      ok = __all_sync(0xffffffffu, mbar_wait(kv_full, ic & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL));
+      for (int i = 0; i < it.n_it && ok; ++i) {
+        const int gi = g + i;
+        const int s = gi & 1;
+        const uint32_t ph = (gi >> 1) & 1;
+        ok = __all_sync(0xffffffffu, mbar_wait(&qd_full[s], ph, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL));
+        if (!ok) break;
+        tc_fence_after();
+        // K-major operands advance 32 bytes per 16-wide K step (+2 in the descriptor's address field),
+        // MN-major ones 2048 bytes (+128)
+        const uint64_t dQk = make_smem_desc(smem_u32(sQ + s * 8192), 16, 1024, SWZ_128B);
+        const uint64_t dDOk = make_smem_desc(smem_u32(sDO + s * 8192), 16, 1024, SWZ_128B);
+        const uint64_t dQm = make_smem_desc(smem_u32(sQ + s * 8192), 8192, 1024, SWZ_128B);
+        const uint64_t dDOm = make_smem_desc(smem_u32(sDO + s * 8192), 8192, 1024, SWZ_128B);
+        if (leader) {
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            mma_f16_ss(tS, make_smem_desc(aK + k * 32, 16, 1024, SWZ_128B),
-                       make_smem_desc(bQ + k * 32, 16, 1024, SWZ_128B), idesc_s, k > 0 ? 1u : 0u);
+          for (int k = 0; k < 4; ++k) mma_f16_ss(tS, dK0 + 2 * k, dQk + 2 * k, idesc_s, k > 0 ? 1u : 0u);
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            mma_f16_ss(tDP, make_smem_desc(aV + k * 32, 16, 1024, SWZ_128B),
-                       make_smem_desc(bDO + k * 32, 16, 1024, SWZ_128B), idesc_s, k > 0 ? 1u : 0u);
+          for (int k = 0; k < 4; ++k) mma_f16_ss(tDP, dV0 + 2 * k, dDOk + 2 * k, idesc_s, k > 0 ? 1u : 0u);
           tc_commit(sdp_full);
-          ok = mbar_wait(p_ready, gi & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_MISC);
+        }
+        __syncwarp();
+        ok = __all_sync(0xffffffffu, mbar_wait(p_ready, gi & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_MISC));
+        if (!ok) break;
+        if (i == 0) {
+          // the first products of an item overwrite dV / dK: the previous item's must have been read out
+          ok = __all_sync(0xffffffffu,
+                          mbar_wait(acc_free, (ic & 1) ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_EMPTY));
           if (!ok) break;
-          if (i == 0) {
-            // the first products of an item overwrite dV / dK: the previous item's must have been read out
-            ok = mbar_wait(acc_free, (ic & 1) ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_EMPTY);
-            if (!ok) break;
-          }
-          tc_fence_after();
+        }
+        tc_fence_after();
+        const uint32_t acc = i > 0 ? 1u : 0u;
+        if (leader) {
+          mma_f16_ts(tDV, tS, dDOm, idesc_a, acc);
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            mma_f16_ts(tDV, tS + k * 8, make_smem_desc(bDO + k * 2048, 8192, 1024, SWZ_128B), idesc_a,
-                       (i > 0 || k > 0) ? 1u : 0u);
+          for (int k = 1; k < 4; ++k) mma_f16_ts(tDV, tS + k * 8, dDOm + 128 * k, idesc_a, 1u);
+          mma_f16_ts(tDK, tDP, dQm, idesc_a, acc);
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            mma_f16_ts(tDK, tDP + k * 8, make_smem_desc(bQ + k * 2048, 8192, 1024, SWZ_128B), idesc_a,
-                       (i > 0 || k > 0) ? 1u : 0u);
+          for (int k = 1; k < 4; ++k) mma_f16_ts(tDK, tDP + k * 8, dQm + 128 * k, idesc_a, 1u);
           tc_commit(&qd_empty[s]);
         }
-        if (ok) {
-          tc_commit(acc_done);
-          tc_commit(kv_empty);
-        }
-        g += it.n_it;
-        ++ic;
+        __syncwarp();
       }
+      if (ok && leader) {
+        tc_commit(acc_done);
+        tc_commit(kv_empty);
+      }
+      __syncwarp();
+      g += it.n_it;
+      ++ic;
     }
   } else {
     // two threads per key row: warp w handles query columns [0,32) of the tile, warp w+4 columns [32,64)
@@ -258,37 +270,48 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
         const int c_lo_q = kj - q_lo;                                           // causal: qi >= kj
         int c_hi_q = min(q_end, p.window > 0 ? kj + p.window : q_end) - 1 - q_lo;  // window and document end
         if (kj >= de) c_hi_q = -1;
-        const bool need_mask = (c_lo_q > 0) || (c_hi_q < 63);
-        {
+        // Whole warps branch on whether any of their rows needs the mask: off the diagonal and away from the
+        // window / document edges the loop carries no compares or selects at all.
+        const bool need_mask = __any_sync(0xffffffffu, (c_lo_q > 0) || (c_hi_q < 63));
+        auto tile = [&](auto masked) {
+          constexpr bool MASK = decltype(masked)::value;
           const int c = half;
           uint32_t sv[32], dp[32], pp[16], dd[16];
           tmem_ld_x32(tS + lane_addr + c * 32, sv);
           tmem_ld_x32(tDP + lane_addr + c * 32, dp);
           tmem_ld_wait();
+          const uint64_t c2 = pack_f32x2(c_log2, c_log2), sc2 = pack_f32x2(p.scale, p.scale);
 #pragma unroll
           for (int e4 = 0; e4 < 32; e4 += 4) {
-            // the per-query statistics are the same for every key row: one 16-byte shared load covers four columns
-            const float4 l4 = *reinterpret_cast<const float4*>(lse_s + c * 32 + e4);
-            const float4 d4 = *reinterpret_cast<const float4*>(dl_s + c * 32 + e4);
-            const float lq[4] = {l4.x, l4.y, l4.z, l4.w}, dq4[4] = {d4.x, d4.y, d4.z, d4.w};
-            float pr[4], dsv[4];
+            // the per-query statistics are the same for every key row: one 16-byte shared load covers four
+            // columns, already as two fp32 pairs
+            const ulonglong2 nl = *reinterpret_cast<const ulonglong2*>(lse_s + c * 32 + e4);
+            const ulonglong2 nd = *reinterpret_cast<const ulonglong2*>(dl_s + c * 32 + e4);
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const int col = c * 32 + e4 + u;
-              float pv = fast_exp2(fmaf(__uint_as_float(sv[e4 + u]), c_log2, -lq[u]));
-              if (need_mask) pv = (col >= c_lo_q && col <= c_hi_q) ? pv : 0.f;
-              pr[u] = pv;
-              dsv[u] = pv * fmaf(__uint_as_float(dp[e4 + u]), p.scale, -dq4[u]);
+            for (int h2 = 0; h2 < 2; ++h2) {
+              const int e = e4 + 2 * h2;
+              float p0, p1, d0, d1;
+              unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sv[e]), __uint_as_float(sv[e + 1])), c2,
+                                     h2 ? nl.y : nl.x), p0, p1);
+              p0 = fast_exp2(p0);
+              p1 = fast_exp2(p1);
+              if constexpr (MASK) {
+                const int col = c * 32 + e;
+                p0 = (col >= c_lo_q && col <= c_hi_q) ? p0 : 0.f;
+                p1 = (col + 1 >= c_lo_q && col + 1 <= c_hi_q) ? p1 : 0.f;
+              }
+              const uint64_t t2 = fma_f32x2(pack_f32x2(__uint_as_float(dp[e]), __uint_as_float(dp[e + 1])), sc2,
+                                            h2 ? nd.y : nd.x);
+              unpack_f32x2(mul_f32x2(pack_f32x2(p0, p1), t2), d0, d1);
+              pp[e / 2] = pack_bf16(p0, p1);
+              dd[e / 2] = pack_bf16(d0, d1);
             }
-            pp[e4 / 2] = pack_bf16(pr[0], pr[1]);
-            pp[e4 / 2 + 1] = pack_bf16(pr[2], pr[3]);
-            dd[e4 / 2] = pack_bf16(dsv[0], dsv[1]);
-            dd[e4 / 2 + 1] = pack_bf16(dsv[2], dsv[3]);
           }
           // P^T / dS^T as bf16 overwrite the first half of the columns that were just read
           tmem_st_x16(tS + lane_addr + c * 16, pp);
           tmem_st_x16(tDP + lane_addr + c * 16, dd);
-        }
+        };
+        if (need_mask) tile(BoolC<true>{}); else tile(BoolC<false>{});
         tmem_st_wait();
         tc_fence_before();
         mbar_arrive(p_ready);
@@ -443,51 +466,58 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
       }
     }
   } else if (warp == 9) {
-    if (lane == 0) {
-      const uint32_t idesc_s = make_idesc_f16(128, 64, 1, 0, 0);
-      const uint32_t idesc_q = make_idesc_f16(128, 64, 1, 0, 1);
-      const uint32_t aQ = smem_u32(sQ), aDO = smem_u32(sDO);
-      int g = 0, ic = 0;
-      bool ok = true;
-      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-        DqItem it;
-        if (!dq_decode(p, item, it)) continue;
-        ok = mbar_wait(q_full, ic & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
-        for (int j = 0; j < it.n_kv && ok; ++j) {
-          const int gj = g + j;
-          const int s = gj & 1;
-          const uint32_t ph = (gj >> 1) & 1;
-          ok = mbar_wait(&kv_full[s], ph, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
-          if (!ok) break;
-          tc_fence_after();
-          const uint32_t bK = smem_u32(sK + s * 8192), bV = smem_u32(sV + s * 8192);
+    // warp-uniform loop, one elected lane issues (see the dK / dV kernel)
+    const bool leader = elect_one();
+    const uint32_t idesc_s = make_idesc_f16(128, 64, 1, 0, 0);
+    const uint32_t idesc_q = make_idesc_f16(128, 64, 1, 0, 1);
+    const uint64_t dQ0 = make_smem_desc(smem_u32(sQ), 16, 1024, SWZ_128B);
+    const uint64_t dDO0 = make_smem_desc(smem_u32(sDO), 16, 1024, SWZ_128B);
+    int g = 0, ic = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      DqItem it;
+      if (!dq_decode(p, item, it)) continue;
+      ok = __all_sync(0xffffffffu, mbar_wait(q_full, ic & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL));
+      for (int j = 0; j < it.n_kv && ok; ++j) {
+        const int gj = g + j;
+        const int s = gj & 1;
+        const uint32_t ph = (gj >> 1) & 1;
+        ok = __all_sync(0xffffffffu, mbar_wait(&kv_full[s], ph, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL));
+        if (!ok) break;
+        tc_fence_after();
+        const uint64_t dKk = make_smem_desc(smem_u32(sK + s * 8192), 16, 1024, SWZ_128B);
+        const uint64_t dVk = make_smem_desc(smem_u32(sV + s * 8192), 16, 1024, SWZ_128B);
+        const uint64_t dKm = make_smem_desc(smem_u32(sK + s * 8192), 8192, 1024, SWZ_128B);
+        if (leader) {
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            mma_f16_ss(tS, make_smem_desc(aQ + k * 32, 16, 1024, SWZ_128B),
-                       make_smem_desc(bK + k * 32, 16, 1024, SWZ_128B), idesc_s, k > 0 ? 1u : 0u);
+          for (int k = 0; k < 4; ++k) mma_f16_ss(tS, dQ0 + 2 * k, dKk + 2 * k, idesc_s, k > 0 ? 1u : 0u);
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            mma_f16_ss(tDP, make_smem_desc(aDO + k * 32, 16, 1024, SWZ_128B),
-                       make_smem_desc(bV + k * 32, 16, 1024, SWZ_128B), idesc_s, k > 0 ? 1u : 0u);
+          for (int k = 0; k < 4; ++k) mma_f16_ss(tDP, dDO0 + 2 * k, dVk + 2 * k, idesc_s, k > 0 ? 1u : 0u);
           tc_commit(sdp_full);
           if (j + 1 == it.n_kv) tc_commit(q_empty);   // Q and dO are free once these products are done
-          ok = mbar_wait(p_ready, gj & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_MISC);
+        }
+        __syncwarp();
+        ok = __all_sync(0xffffffffu, mbar_wait(p_ready, gj & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_MISC));
+        if (!ok) break;
+        if (j == 0) {
+          ok = __all_sync(0xffffffffu,
+                          mbar_wait(acc_free, (ic & 1) ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_EMPTY));
           if (!ok) break;
-          if (j == 0) {
-            ok = mbar_wait(acc_free, (ic & 1) ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_EMPTY);
-            if (!ok) break;
-          }
-          tc_fence_after();
+        }
+        tc_fence_after();
+        const uint32_t acc = j > 0 ? 1u : 0u;
+        if (leader) {
+          mma_f16_ts(tDQ, tS, dKm, idesc_q, acc);
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            mma_f16_ts(tDQ, tS + k * 8, make_smem_desc(bK + k * 2048, 8192, 1024, SWZ_128B), idesc_q,
-                       (j > 0 || k > 0) ? 1u : 0u);
+          for (int k = 1; k < 4; ++k) mma_f16_ts(tDQ, tS + k * 8, dKm + 128 * k, idesc_q, 1u);
           tc_commit(&kv_empty[s]);
         }
-        if (ok) tc_commit(acc_done);
-        g += it.n_kv;
-        ++ic;
+        __syncwarp();
       }
+      if (ok && leader) tc_commit(acc_done);
+      __syncwarp();
+      g += it.n_kv;
+      ++ic;
     }
   } else {
     const int quarter = warp & 3, half = warp >> 2;   // two threads per query row, 32 key columns each
@@ -514,27 +544,34 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
         // key columns of this tile that query row qi may attend to: [c_lo, c_hi]
         const int c_hi_k = (qi < q_hi) ? (qi - kv0) : -1;
         const int c_lo_k = (p.window > 0) ? (qi - p.window + 1 - kv0) : 0;
-        const bool need_mask = (c_hi_k < 63) || (c_lo_k > 0);
-        {
+        const bool need_mask = __any_sync(0xffffffffu, (c_hi_k < 63) || (c_lo_k > 0));
+        auto tile = [&](auto masked) {
+          constexpr bool MASK = decltype(masked)::value;
           const int c = half;
           uint32_t sv[32], dp[32], dd[16];
           tmem_ld_x32(tS + lane_addr + c * 32, sv);
           tmem_ld_x32(tDP + lane_addr + c * 32, dp);
           tmem_ld_wait();
+          const uint64_t c2 = pack_f32x2(c_log2, c_log2), sc2 = pack_f32x2(p.scale, p.scale);
+          const uint64_t nl2 = pack_f32x2(-lse_q, -lse_q), nd2 = pack_f32x2(-dl_q, -dl_q);
 #pragma unroll
           for (int e = 0; e < 32; e += 2) {
-            float dsv[2];
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-              const int col = c * 32 + e + u;
-              float pv = fast_exp2(fmaf(__uint_as_float(sv[e + u]), c_log2, -lse_q));
-              if (need_mask) pv = (col >= c_lo_k && col <= c_hi_k) ? pv : 0.f;
-              dsv[u] = pv * fmaf(__uint_as_float(dp[e + u]), p.scale, -dl_q);
+            float p0, p1, d0, d1;
+            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sv[e]), __uint_as_float(sv[e + 1])), c2, nl2), p0, p1);
+            p0 = fast_exp2(p0);
+            p1 = fast_exp2(p1);
+            if constexpr (MASK) {
+              const int col = c * 32 + e;
+              p0 = (col >= c_lo_k && col <= c_hi_k) ? p0 : 0.f;
+              p1 = (col + 1 >= c_lo_k && col + 1 <= c_hi_k) ? p1 : 0.f;
             }
-            dd[e / 2] = pack_bf16(dsv[0], dsv[1]);
+            const uint64_t t2 = fma_f32x2(pack_f32x2(__uint_as_float(dp[e]), __uint_as_float(dp[e + 1])), sc2, nd2);
+            unpack_f32x2(mul_f32x2(pack_f32x2(p0, p1), t2), d0, d1);
+            dd[e / 2] = pack_bf16(d0, d1);
           }
           tmem_st_x16(tS + lane_addr + c * 16, dd);
-        }
+        };
+        if (need_mask) tile(BoolC<true>{}); else tile(BoolC<false>{});
         tmem_st_wait();
         tc_fence_before();
         mbar_arrive(p_ready);

@@ -24,6 +24,7 @@ constexpr int FA_THREADS = 320;  // 8 softmax warps + TMA warp + MMA warp
 constexpr int FA_TILE_BYTES = 128 * 64 * 2;  // 16 KB
 constexpr int FA_SMEM = 5 * FA_TILE_BYTES + 1024 + 3072 + 1024;  // tiles + barriers + row-max exchange + alignment slack
 constexpr float FA_NEG = -1.0e30f;
+template <bool V> struct FwdBoolC { static constexpr bool value = V; };
 
 struct FlashFwdParams {
   __nv_bfloat16* out;   // (T, Hq, 64)
@@ -165,66 +166,75 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
   } else if (warp == 9) {
     // ---------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
-      const uint32_t idesc_s = make_idesc_f16(128, 128, 1, 0, 0);
-      const uint32_t idesc_o = make_idesc_f16(128, 64, 1, 0, 1);
-      const uint32_t aQ = smem_u32(sQ);
-      int g = 0, ic = 0;
-      bool ok = true;
-      auto issue_s = [&](int gj, bool last_of_item) {
-        const int s = gj & 1;
-        const uint32_t bK = smem_u32(sK + s * FA_TILE_BYTES);
+    // The whole warp walks the loop, so that descriptors and counters stay warp-uniform (a single-lane
+    // branch keeps them in per-thread registers and pays a transfer into the uniform registers for every
+    // operand of every tcgen05.mma, on the critical path between two softmax tiles); one elected lane issues.
+    const bool leader = elect_one();
+    const uint32_t idesc_s = make_idesc_f16(128, 128, 1, 0, 0);
+    const uint32_t idesc_o = make_idesc_f16(128, 64, 1, 0, 1);
+    const uint64_t dQ0 = make_smem_desc(smem_u32(sQ), 16, 1024, SWZ_128B);
+    int g = 0, ic = 0;
+    bool ok = true;
+    auto issue_s = [&](int gj, bool last_of_item) {
+      const int s = gj & 1;
+      const uint64_t dK = make_smem_desc(smem_u32(sK + s * FA_TILE_BYTES), 16, 1024, SWZ_128B);
+      if (leader) {
 #pragma unroll
-        for (int k = 0; k < FA_D / 16; ++k)
-          mma_f16_ss(tS, make_smem_desc(aQ + k * 32, 16, 1024, SWZ_128B),
-                     make_smem_desc(bK + k * 32, 16, 1024, SWZ_128B), idesc_s, k > 0 ? 1u : 0u);
+        for (int k = 0; k < FA_D / 16; ++k) mma_f16_ss(tS, dQ0 + 2 * k, dK + 2 * k, idesc_s, k > 0 ? 1u : 0u);
         tc_commit(s_full);
         tc_commit(&k_empty[s]);
         if (last_of_item) tc_commit(q_empty);
-      };
-      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-        FwdItem it;
-        if (!fwd_decode(p, item, it)) continue;
-        const int n_kv = it.n_kv;
-        ok = mbar_wait(q_full, ic & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
-        if (ok) ok = mbar_wait(&k_full[g & 1], (g >> 1) & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
+      }
+      __syncwarp();
+    };
+    auto wait_all = [&](uint64_t* bar, uint32_t parity, int code) {
+      return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, p.status, code));
+    };
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      FwdItem it;
+      if (!fwd_decode(p, item, it)) continue;
+      const int n_kv = it.n_kv;
+      ok = wait_all(q_full, ic & 1, KWU_ERR_TIMEOUT_FULL);
+      if (ok) ok = wait_all(&k_full[g & 1], (g >> 1) & 1, KWU_ERR_TIMEOUT_FULL);
+      if (!ok) break;
+      tc_fence_after();
+      // S of the previous item has been read (its last p_full was waited for below) and P is rewritten
+      // by the softmax warps only after they have waited for the previous item's last o_done
+      issue_s(g, n_kv == 1);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int gj = g + j;
+        const int s = gj & 1;
+        const uint32_t ph = (gj >> 1) & 1;
+        if (j + 1 < n_kv) {
+          ok = wait_all(&k_full[(gj + 1) & 1], ((gj + 1) >> 1) & 1, KWU_ERR_TIMEOUT_FULL);
+          if (!ok) break;
+        }
+        // P_j written (and S_j fully read) by the softmax warps
+        ok = wait_all(p_full, gj & 1, KWU_ERR_TIMEOUT_MISC);
         if (!ok) break;
         tc_fence_after();
-        // S of the previous item has been read (its last p_full was waited for below) and P is rewritten
-        // by the softmax warps only after they have waited for the previous item's last o_done
-        issue_s(g, n_kv == 1);
-        for (int j = 0; j < n_kv && ok; ++j) {
-          const int gj = g + j;
-          const int s = gj & 1;
-          const uint32_t ph = (gj >> 1) & 1;
-          if (j + 1 < n_kv) {
-            ok = mbar_wait(&k_full[(gj + 1) & 1], ((gj + 1) >> 1) & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
-            if (!ok) break;
-          }
-          // P_j written (and S_j fully read) by the softmax warps
-          ok = mbar_wait(p_full, gj & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_MISC);
+        if (j + 1 < n_kv) issue_s(gj + 1, j + 2 == n_kv);
+        ok = wait_all(&v_full[s], ph, KWU_ERR_TIMEOUT_FULL);
+        if (!ok) break;
+        if (j == 0) {
+          // the first product of an item overwrites O: the previous item's epilogue must have read it
+          ok = wait_all(o_free, (ic & 1) ^ 1, KWU_ERR_TIMEOUT_ACC_EMPTY);
           if (!ok) break;
-          tc_fence_after();
-          if (j + 1 < n_kv) issue_s(gj + 1, j + 2 == n_kv);
-          ok = mbar_wait(&v_full[s], ph, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
-          if (!ok) break;
-          if (j == 0) {
-            // the first product of an item overwrites O: the previous item's epilogue must have read it
-            ok = mbar_wait(o_free, (ic & 1) ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_EMPTY);
-            if (!ok) break;
-          }
-          tc_fence_after();
-          const uint32_t bV = smem_u32(sV + s * FA_TILE_BYTES);
+        }
+        tc_fence_after();
+        const uint64_t dV = make_smem_desc(smem_u32(sV + s * FA_TILE_BYTES), 8192, 1024, SWZ_128B);
+        const uint32_t acc = j > 0 ? 1u : 0u;
+        if (leader) {
+          mma_f16_ts(tO, tP, dV, idesc_o, acc);
 #pragma unroll
-          for (int k = 0; k < FA_BN / 16; ++k)
-            mma_f16_ts(tO, tP + k * 8, make_smem_desc(bV + k * 2048, 8192, 1024, SWZ_128B), idesc_o,
-                       (j > 0 || k > 0) ? 1u : 0u);
+          for (int k = 1; k < FA_BN / 16; ++k) mma_f16_ts(tO, tP + k * 8, dV + 128 * k, idesc_o, 1u);
           tc_commit(o_done);
           tc_commit(&v_empty[s]);
         }
-        g += n_kv;
-        ++ic;
+        __syncwarp();
       }
+      g += n_kv;
+      ++ic;
     }
   } else {
     // ---------------------------------------------------------------- softmax (warps 0..7)
@@ -290,24 +300,36 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         // pass 2: probabilities p = 2^(s*c - m*c), packed to bf16
         uint32_t pk[32];
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+        // the mask is needed only on diagonal / window-edge tiles (the same for the whole CTA): two copies
+        // of the loop, so that the common one carries no compares or selects
+        auto pass2 = [&](auto masked) {
+          constexpr bool MASK = decltype(masked)::value;
+          const uint64_t sl2 = pack_f32x2(p.scale_log2, p.scale_log2), nm2 = pack_f32x2(neg_ms, neg_ms);
+          uint64_t acc2[2] = {pack_f32x2(0.f, 0.f), pack_f32x2(0.f, 0.f)};
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t r[32];
-          tmem_ld_x32(tS + lane_addr + col_base + c * 32, r);
-          tmem_ld_wait();
+          for (int c = 0; c < 2; ++c) {
+            uint32_t r[32];
+            tmem_ld_x32(tS + lane_addr + col_base + c * 32, r);
+            tmem_ld_wait();
 #pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            float p0 = fast_exp2(fmaf(__uint_as_float(r[e]), p.scale_log2, neg_ms));
-            float p1 = fast_exp2(fmaf(__uint_as_float(r[e + 1]), p.scale_log2, neg_ms));
-            if (need_mask) {
-              const int col = col_base + c * 32 + e;
-              p0 = (col <= c_hi && col >= c_lo) ? p0 : 0.f;
-              p1 = (col + 1 <= c_hi && col + 1 >= c_lo) ? p1 : 0.f;
+            for (int e = 0; e < 32; e += 2) {
+              float p0, p1;
+              unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(r[e]), __uint_as_float(r[e + 1])), sl2, nm2), p0, p1);
+              p0 = fast_exp2(p0);
+              p1 = fast_exp2(p1);
+              if constexpr (MASK) {
+                const int col = col_base + c * 32 + e;
+                p0 = (col <= c_hi && col >= c_lo) ? p0 : 0.f;
+                p1 = (col + 1 <= c_hi && col + 1 >= c_lo) ? p1 : 0.f;
+              }
+              acc2[(e >> 1) & 1] = add_f32x2(acc2[(e >> 1) & 1], pack_f32x2(p0, p1));
+              pk[c * 16 + e / 2] = pack_bf16(p0, p1);
             }
-            sum4[(e >> 1) & 3] += p0 + p1;
-            pk[c * 16 + e / 2] = pack_bf16(p0, p1);
           }
-        }
+          unpack_f32x2(acc2[0], sum4[0], sum4[1]);
+          unpack_f32x2(acc2[1], sum4[2], sum4[3]);
+        };
+        if (need_mask) pass2(FwdBoolC<true>{}); else pass2(FwdBoolC<false>{});
         l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
         // the previous P V product must be complete before P is overwritten and O is touched; for the
         // first tile of an item that product belongs to the previous item and was waited for in its epilogue
