@@ -105,7 +105,9 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
   uint64_t* acc_done = bars + 7;
   uint64_t* kv_empty = bars + 8;  // the item's last products have read K and V
   uint64_t* acc_free = bars + 9;  // the item's dK / dV accumulators have been read out
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* dp_full = bars + 10;   // dP^T is in TMEM (S^T has its own barrier, so the exponentials start earlier)
+  uint64_t* ds_ready = bars + 11;  // dS^T has been written (P^T has its own barrier, so dV starts earlier)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -120,6 +122,8 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
     }
     mbar_init(sdp_full, 1);
     mbar_init(p_ready, 256);
+    mbar_init(dp_full, 1);
+    mbar_init(ds_ready, 256);
     mbar_init(acc_done, 1);
     mbar_init(kv_empty, 1);
     mbar_init(acc_free, 256);
@@ -208,9 +212,10 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
         if (leader) {
 #pragma unroll
           for (int k = 0; k < 4; ++k) mma_f16_ss(tS, dK0 + 2 * k, dQk + 2 * k, idesc_s, k > 0 ? 1u : 0u);
+          tc_commit(sdp_full);   // the softmax warps start on S^T while dP^T is still being issued and computed
 #pragma unroll
           for (int k = 0; k < 4; ++k) mma_f16_ss(tDP, dV0 + 2 * k, dDOk + 2 * k, idesc_s, k > 0 ? 1u : 0u);
-          tc_commit(sdp_full);
+          tc_commit(dp_full);
         }
         __syncwarp();
         ok = __all_sync(0xffffffffu, mbar_wait(p_ready, gi & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_MISC));
@@ -223,13 +228,23 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
         }
         tc_fence_after();
         const uint32_t acc = i > 0 ? 1u : 0u;
+        // dV needs only P^T: it is issued while the softmax warps are still forming dS^T
         if (leader) {
+          // 16 queries per step: steps 0, 1 read columns [0,16) of the score block, steps 2, 3 columns [32,48)
           mma_f16_ts(tDV, tS, dDOm, idesc_a, acc);
 #pragma unroll
-          for (int k = 1; k < 4; ++k) mma_f16_ts(tDV, tS + k * 8, dDOm + 128 * k, idesc_a, 1u);
+          for (int k = 1; k < 4; ++k)
+            mma_f16_ts(tDV, tS + (k >> 1) * 32 + (k & 1) * 8, dDOm + 128 * k, idesc_a, 1u);
+        }
+        __syncwarp();
+        ok = __all_sync(0xffffffffu, mbar_wait(ds_ready, gi & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_MISC));
+        if (!ok) break;
+        tc_fence_after();
+        if (leader) {
           mma_f16_ts(tDK, tDP, dQm, idesc_a, acc);
 #pragma unroll
-          for (int k = 1; k < 4; ++k) mma_f16_ts(tDK, tDP + k * 8, dQm + 128 * k, idesc_a, 1u);
+          for (int k = 1; k < 4; ++k)
+            mma_f16_ts(tDK, tDP + (k >> 1) * 32 + (k & 1) * 8, dQm + 128 * k, idesc_a, 1u);
           tc_commit(&qd_empty[s]);
         }
         __syncwarp();
@@ -273,12 +288,12 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
         // Whole warps branch on whether any of their rows needs the mask: off the diagonal and away from the
         // window / document edges the loop carries no compares or selects at all.
         const bool need_mask = __any_sync(0xffffffffu, (c_lo_q > 0) || (c_hi_q < 63));
-        auto tile = [&](auto masked) {
+        auto tile = [&](auto masked) -> bool {
           constexpr bool MASK = decltype(masked)::value;
           const int c = half;
-          uint32_t sv[32], dp[32], pp[16], dd[16];
+          // phase 1: P^T = exp2(S^T * c - lse), kept in fp32 in place of the scores and stored as bf16
+          uint32_t sv[32], pp[16];
           tmem_ld_x32(tS + lane_addr + c * 32, sv);
-          tmem_ld_x32(tDP + lane_addr + c * 32, dp);
           tmem_ld_wait();
           const uint64_t c2 = pack_f32x2(c_log2, c_log2), sc2 = pack_f32x2(p.scale, p.scale);
 #pragma unroll
@@ -286,11 +301,10 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
             // the per-query statistics are the same for every key row: one 16-byte shared load covers four
             // columns, already as two fp32 pairs
             const ulonglong2 nl = *reinterpret_cast<const ulonglong2*>(lse_s + c * 32 + e4);
-            const ulonglong2 nd = *reinterpret_cast<const ulonglong2*>(dl_s + c * 32 + e4);
 #pragma unroll
             for (int h2 = 0; h2 < 2; ++h2) {
               const int e = e4 + 2 * h2;
-              float p0, p1, d0, d1;
+              float p0, p1;
               unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sv[e]), __uint_as_float(sv[e + 1])), c2,
                                      h2 ? nl.y : nl.x), p0, p1);
               p0 = fast_exp2(p0);
@@ -300,21 +314,46 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
                 p0 = (col >= c_lo_q && col <= c_hi_q) ? p0 : 0.f;
                 p1 = (col + 1 >= c_lo_q && col + 1 <= c_hi_q) ? p1 : 0.f;
               }
+              sv[e] = __float_as_uint(p0);
+              sv[e + 1] = __float_as_uint(p1);
+              pp[e / 2] = pack_bf16(p0, p1);
+            }
+          }
+          // P^T as bf16 overwrites the first half of the 32 score columns that THIS thread read (never columns
+          // that the row's other thread may still have to read): queries [32c, 32c+32) sit in columns [32c, 32c+16)
+          tmem_st_x16(tS + lane_addr + c * 32, pp);
+          tmem_st_wait();
+          tc_fence_before();
+          mbar_arrive(p_ready);
+          // phase 2: dS^T = P^T o (dP^T * scale - delta)
+          bool fine = mbar_wait(dp_full, gi & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_FULL);
+          fine = __all_sync(0xffffffffu, fine);
+          if (!fine) return false;
+          tc_fence_after();
+          uint32_t dp[32], dd[16];
+          tmem_ld_x32(tDP + lane_addr + c * 32, dp);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e4 = 0; e4 < 32; e4 += 4) {
+            const ulonglong2 nd = *reinterpret_cast<const ulonglong2*>(dl_s + c * 32 + e4);
+#pragma unroll
+            for (int h2 = 0; h2 < 2; ++h2) {
+              const int e = e4 + 2 * h2;
+              float d0, d1;
               const uint64_t t2 = fma_f32x2(pack_f32x2(__uint_as_float(dp[e]), __uint_as_float(dp[e + 1])), sc2,
                                             h2 ? nd.y : nd.x);
-              unpack_f32x2(mul_f32x2(pack_f32x2(p0, p1), t2), d0, d1);
-              pp[e / 2] = pack_bf16(p0, p1);
+              unpack_f32x2(mul_f32x2(pack_f32x2(__uint_as_float(sv[e]), __uint_as_float(sv[e + 1])), t2), d0, d1);
               dd[e / 2] = pack_bf16(d0, d1);
             }
           }
-          // P^T / dS^T as bf16 overwrite the first half of the columns that were just read
-          tmem_st_x16(tS + lane_addr + c * 16, pp);
-          tmem_st_x16(tDP + lane_addr + c * 16, dd);
+          tmem_st_x16(tDP + lane_addr + c * 32, dd);
+          tmem_st_wait();
+          tc_fence_before();
+          mbar_arrive(ds_ready);
+          return true;
         };
-        if (need_mask) tile(BoolC<true>{}); else tile(BoolC<false>{});
-        tmem_st_wait();
-        tc_fence_before();
-        mbar_arrive(p_ready);
+        ok = need_mask ? tile(BoolC<true>{}) : tile(BoolC<false>{});
+        if (!ok) break;
       }
       if (ok) {
         ok = mbar_wait(acc_done, ic & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_FULL);
@@ -412,7 +451,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
   uint64_t* acc_done = bars + 7;
   uint64_t* q_empty = bars + 8;   // the item's last products have read Q and dO
   uint64_t* acc_free = bars + 9;  // the item's dQ accumulator has been read out
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* dp_full = bars + 10;  // dP is in TMEM (S has its own barrier, so the exponentials start earlier)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -427,6 +467,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
     }
     mbar_init(sdp_full, 1);
     mbar_init(p_ready, 256);
+    mbar_init(dp_full, 1);
     mbar_init(acc_done, 1);
     mbar_init(q_empty, 1);
     mbar_init(acc_free, 256);
@@ -491,9 +532,10 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
         if (leader) {
 #pragma unroll
           for (int k = 0; k < 4; ++k) mma_f16_ss(tS, dQ0 + 2 * k, dKk + 2 * k, idesc_s, k > 0 ? 1u : 0u);
+          tc_commit(sdp_full);   // the softmax warps start on S while dP is still being issued and computed
 #pragma unroll
           for (int k = 0; k < 4; ++k) mma_f16_ss(tDP, dDO0 + 2 * k, dVk + 2 * k, idesc_s, k > 0 ? 1u : 0u);
-          tc_commit(sdp_full);
+          tc_commit(dp_full);
           if (j + 1 == it.n_kv) tc_commit(q_empty);   // Q and dO are free once these products are done
         }
         __syncwarp();
@@ -509,7 +551,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
         if (leader) {
           mma_f16_ts(tDQ, tS, dKm, idesc_q, acc);
 #pragma unroll
-          for (int k = 1; k < 4; ++k) mma_f16_ts(tDQ, tS + k * 8, dKm + 128 * k, idesc_q, 1u);
+          for (int k = 1; k < 4; ++k)
+            mma_f16_ts(tDQ, tS + (k >> 1) * 32 + (k & 1) * 8, dKm + 128 * k, idesc_q, 1u);
           tc_commit(&kv_empty[s]);
         }
         __syncwarp();
@@ -545,18 +588,18 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
         const int c_hi_k = (qi < q_hi) ? (qi - kv0) : -1;
         const int c_lo_k = (p.window > 0) ? (qi - p.window + 1 - kv0) : 0;
         const bool need_mask = __any_sync(0xffffffffu, (c_hi_k < 63) || (c_lo_k > 0));
-        auto tile = [&](auto masked) {
+        auto tile = [&](auto masked) -> bool {
           constexpr bool MASK = decltype(masked)::value;
           const int c = half;
-          uint32_t sv[32], dp[32], dd[16];
+          // phase 1: P = exp2(S * c - lse) in fp32, in place of the scores
+          uint32_t sv[32];
           tmem_ld_x32(tS + lane_addr + c * 32, sv);
-          tmem_ld_x32(tDP + lane_addr + c * 32, dp);
           tmem_ld_wait();
           const uint64_t c2 = pack_f32x2(c_log2, c_log2), sc2 = pack_f32x2(p.scale, p.scale);
           const uint64_t nl2 = pack_f32x2(-lse_q, -lse_q), nd2 = pack_f32x2(-dl_q, -dl_q);
 #pragma unroll
           for (int e = 0; e < 32; e += 2) {
-            float p0, p1, d0, d1;
+            float p0, p1;
             unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sv[e]), __uint_as_float(sv[e + 1])), c2, nl2), p0, p1);
             p0 = fast_exp2(p0);
             p1 = fast_exp2(p1);
@@ -565,16 +608,32 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
               p0 = (col >= c_lo_k && col <= c_hi_k) ? p0 : 0.f;
               p1 = (col + 1 >= c_lo_k && col + 1 <= c_hi_k) ? p1 : 0.f;
             }
+            sv[e] = __float_as_uint(p0);
+            sv[e + 1] = __float_as_uint(p1);
+          }
+          // phase 2: dS = P o (dP * scale - delta), stored as bf16 over the first half of this thread's score columns
+          bool fine = mbar_wait(dp_full, gj & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_FULL);
+          fine = __all_sync(0xffffffffu, fine);
+          if (!fine) return false;
+          tc_fence_after();
+          uint32_t dp[32], dd[16];
+          tmem_ld_x32(tDP + lane_addr + c * 32, dp);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            float d0, d1;
             const uint64_t t2 = fma_f32x2(pack_f32x2(__uint_as_float(dp[e]), __uint_as_float(dp[e + 1])), sc2, nd2);
-            unpack_f32x2(mul_f32x2(pack_f32x2(p0, p1), t2), d0, d1);
+            unpack_f32x2(mul_f32x2(pack_f32x2(__uint_as_float(sv[e]), __uint_as_float(sv[e + 1])), t2), d0, d1);
             dd[e / 2] = pack_bf16(d0, d1);
           }
-          tmem_st_x16(tS + lane_addr + c * 16, dd);
+          tmem_st_x16(tS + lane_addr + c * 32, dd);
+          tmem_st_wait();
+          tc_fence_before();
+          mbar_arrive(p_ready);
+          return true;
         };
-        if (need_mask) tile(BoolC<true>{}); else tile(BoolC<false>{});
-        tmem_st_wait();
-        tc_fence_before();
-        mbar_arrive(p_ready);
+        ok = need_mask ? tile(BoolC<true>{}) : tile(BoolC<false>{});
+        if (!ok) break;
       }
       if (ok) {
         ok = mbar_wait(acc_done, ic & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_FULL);

@@ -238,47 +238,50 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      int it = 0;
-      bool ok = true;
-      for (int wi = 0; ok; ++wi) {
-        TileInfo ti;
-        const int got = next_work<BN>(p, wi, num_tiles, num_kb, ti);
-        if (got == 0) break;
-        if (got == 2) continue;
-        const int as = it & 1;
-        const uint32_t aphase = (it >> 1) & 1;
-        ++it;
-        if (!mbar_wait(&acc_empty[as], aphase ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_EMPTY)) {
-          ok = false;
-          break;
-        }
+    // The whole warp walks the loop so that stage addresses, descriptors and counters stay warp-uniform
+    // (a single-lane branch keeps them in per-thread registers and pays a move into the uniform registers
+    // for every operand of every tcgen05.mma); one elected lane issues.
+    const bool leader = elect_one();
+    int stage = 0;
+    uint32_t phase = 0;
+    int it = 0;
+    bool ok = true;
+    // the descriptors of one k-block differ only in the address field: +(bytes >> 4) per 16-wide K step
+    const uint32_t a_step = static_cast<uint32_t>(p.a_kadv) >> 4, b_step = static_cast<uint32_t>(p.b_kadv) >> 4;
+    for (int wi = 0; ok; ++wi) {
+      TileInfo ti;
+      const int got = next_work<BN>(p, wi, num_tiles, num_kb, ti);
+      if (got == 0) break;
+      if (got == 2) continue;
+      const int as = it & 1;
+      const uint32_t aphase = (it >> 1) & 1;
+      ++it;
+      ok = __all_sync(0xffffffffu, mbar_wait(&acc_empty[as], aphase ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_EMPTY));
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + as * BN;
+      for (int kb = 0; kb < ti.nkb; ++kb) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&full_bar[stage], phase, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL));
+        if (!ok) break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + as * BN;
-        for (int kb = 0; kb < ti.nkb; ++kb) {
-          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          const uint32_t sa = smem_u32(smem + stage * S::STAGE_BYTES);
-          const uint32_t sb = sa + S::A_BYTES;
+        const uint32_t sa = smem_u32(smem + stage * S::STAGE_BYTES);
+        const uint64_t ad = make_smem_desc(sa, p.a_lbo, p.a_sbo, SWZ_128B);
+        const uint64_t bd = make_smem_desc(sa + S::A_BYTES, p.b_lbo, p.b_sbo, SWZ_128B);
+        const uint32_t acc0 = kb > 0 ? 1u : 0u;
+        if (leader) {
+          mma_f16_ss(d_tmem, ad, bd, p.idesc, acc0);
 #pragma unroll
-          for (int k = 0; k < GEMM_BK / 16; ++k) {
-            const uint64_t ad = make_smem_desc(sa + k * p.a_kadv, p.a_lbo, p.a_sbo, SWZ_128B);
-            const uint64_t bd = make_smem_desc(sb + k * p.b_kadv, p.b_lbo, p.b_sbo, SWZ_128B);
-            mma_f16_ss(d_tmem, ad, bd, p.idesc, (kb > 0 || k > 0) ? 1u : 0u);
-          }
+          for (int k = 1; k < GEMM_BK / 16; ++k) mma_f16_ss(d_tmem, ad + k * a_step, bd + k * b_step, p.idesc, 1u);
           tc_commit(&empty_bar[stage]);
-          if (++stage == STAGES) {
-            stage = 0;
-            phase ^= 1;
-          }
         }
-        if (ok) tc_commit(&acc_full[as]);
+        __syncwarp();
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
       }
+      if (ok && leader) tc_commit(&acc_full[as]);
+      __syncwarp();
     }
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5)

@@ -262,54 +262,61 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      int it = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        int m0, n0, b_row0;
-        if (!mx_decode_tile(p, tile, BN, m0, n0, b_row0)) continue;
-        // the tile's first B row sits (b_row0 % 128) / 32 columns into its first scale chunk
-        const uint32_t sfb_off = static_cast<uint32_t>((b_row0 & 127) >> 5);
-        const int as = it & 1;
-        const uint32_t aphase = (it >> 1) & 1;
-        ++it;
-        if (!mbar_wait(&acc_empty[as], aphase ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_EMPTY)) {
-          ok = false;
-          break;
-        }
+    // The whole warp walks the loop so that stage addresses, descriptors and counters stay warp-uniform (under
+    // a single-lane branch every operand of every tcgen05 instruction is first moved from a per-thread to a
+    // uniform register, and with 128-wide tiles the issue of 2-3 scale copies + 4 MMAs per k-block then takes
+    // longer than their execution); one elected lane issues.
+    const bool leader = elect_one();
+    int stage = 0;
+    uint32_t phase = 0;
+    int it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      int m0, n0, b_row0;
+      if (!mx_decode_tile(p, tile, BN, m0, n0, b_row0)) continue;
+      // the tile's first B row sits (b_row0 % 128) / 32 columns into its first scale chunk
+      const uint32_t sfb_off = static_cast<uint32_t>((b_row0 & 127) >> 5);
+      const int as = it & 1;
+      const uint32_t aphase = (it >> 1) & 1;
+      ++it;
+      ok = __all_sync(0xffffffffu, mbar_wait(&acc_empty[as], aphase ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_EMPTY));
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + as * BN;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&full_bar[stage], phase, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL));
+        if (!ok) break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + as * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          const uint32_t sa = smem_u32(smem + stage * S::STAGE_BYTES);
-          const uint32_t sb = sa + S::A_BYTES;
-          const uint32_t ssf = sb + S::B_BYTES;
-          // scale chunks: shared -> TMEM (32 rows x 16 B each, 8-row groups 128 B apart, no swizzle)
-          tc_cp_32x128b_warpx4(tmem_base + SFA_COL, make_smem_desc(ssf, 16, 128, SWZ_NONE));
+        const uint32_t sa = smem_u32(smem + stage * S::STAGE_BYTES);
+        const uint32_t sb = sa + S::A_BYTES;
+        const uint32_t ssf = sb + S::B_BYTES;
+        const uint64_t ad = make_smem_desc(sa, 16, 1024, SWZ_128B);
+        const uint64_t bd = make_smem_desc(sb, 16, 1024, SWZ_128B);
+        const uint64_t sfd = make_smem_desc(ssf, 16, 128, SWZ_NONE);
+        const uint32_t acc0 = kb > 0 ? 1u : 0u;
+        if (leader) {
+          // scale chunks: shared -> TMEM (32 rows x 16 B each, 8-row groups 128 B apart, no swizzle);
+          // 512 bytes further in shared memory is +32 in the descriptor's address field
+          tc_cp_32x128b_warpx4(tmem_base + SFA_COL, sfd);
 #pragma unroll
-          for (int c = 0; c < S::SFB_CHUNKS; ++c)
-            tc_cp_32x128b_warpx4(tmem_base + SFB_COL + 4 * c, make_smem_desc(ssf + 512 + 512 * c, 16, 128, SWZ_NONE));
+          for (int c = 0; c < S::SFB_CHUNKS; ++c) tc_cp_32x128b_warpx4(tmem_base + SFB_COL + 4 * c, sfd + 32 * (c + 1));
+          // 32 fp8 elements along K per instruction: +32 bytes = +2 in the address field
+          mma_mxf8_ss(d_tmem, ad, bd, make_idesc_mxf8(MX_BM, BN, 0, 0), tmem_base + SFA_COL,
+                      tmem_base + SFB_COL + sfb_off, acc0);
 #pragma unroll
-          for (int k = 0; k < MX_BK / 32; ++k) {
-            const uint64_t ad = make_smem_desc(sa + k * 32, 16, 1024, SWZ_128B);
-            const uint64_t bd = make_smem_desc(sb + k * 32, 16, 1024, SWZ_128B);
-            mma_mxf8_ss(d_tmem, ad, bd, make_idesc_mxf8(MX_BM, BN, k, k), tmem_base + SFA_COL,
-                        tmem_base + SFB_COL + sfb_off, (kb > 0 || k > 0) ? 1u : 0u);
-          }
+          for (int k = 1; k < MX_BK / 32; ++k)
+            mma_mxf8_ss(d_tmem, ad + 2 * k, bd + 2 * k, make_idesc_mxf8(MX_BM, BN, k, k), tmem_base + SFA_COL,
+                        tmem_base + SFB_COL + sfb_off, 1u);
           tc_commit(&empty_bar[stage]);
-          if (++stage == STAGES) {
-            stage = 0;
-            phase ^= 1;
-          }
         }
-        if (ok) tc_commit(&acc_full[as]);
+        __syncwarp();
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
       }
+      if (ok && leader) tc_commit(&acc_full[as]);
+      __syncwarp();
     }
   } else {
     const int quarter = warp & 3;
