@@ -60,6 +60,14 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// Work item of a persistent CTA in round r of a cost-sorted (heaviest first) list: rounds alternate
+// direction, so the CTA that got the heaviest item of one round gets the lightest of the next (static
+// boustrophedon assignment; per-CTA totals come within a few percent of a greedy dynamic queue).
+__device__ __forceinline__ int snake_item(int r) {
+  const int G = static_cast<int>(gridDim.x), b = static_cast<int>(blockIdx.x);
+  return r * G + ((r & 1) ? G - 1 - b : b);
+}
+
 // ------------------------------------------------------------------ mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));

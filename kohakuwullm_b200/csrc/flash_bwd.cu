@@ -71,7 +71,7 @@ struct DkdvItem {
 };
 
 __device__ __forceinline__ bool dkdv_decode(const FlashBwdParams& p, int item, DkdvItem& it) {
-  const int4 job = p.plan[item / p.Hq];
+  const int4 job = p.plan[p.n_tiles + item / p.Hq];   // second list: key tiles seen by the most queries first
   if (!job.w) return false;
   it.kv0 = job.x; it.de = job.z;
   it.h = item % p.Hq;                      // one item per query head; GQA partials are summed afterwards
@@ -143,7 +143,9 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
   if (warp == 8) {
     int g = 0, ic = 0;
     int ok = 1;
-    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+    for (int rnd = 0; rnd * static_cast<int>(gridDim.x) < n_items && ok; ++rnd) {
+      const int item = snake_item(rnd);
+      if (item >= n_items) continue;
       DkdvItem it;
       if (!dkdv_decode(p, item, it)) continue;
       if (lane == 0) {
@@ -192,7 +194,9 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
     const uint64_t dV0 = make_smem_desc(smem_u32(sV), 16, 1024, SWZ_128B);
     int g = 0, ic = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+    for (int rnd = 0; rnd * static_cast<int>(gridDim.x) < n_items && ok; ++rnd) {
+      const int item = snake_item(rnd);
+      if (item >= n_items) continue;
       DkdvItem it;
       if (!dkdv_decode(p, item, it)) continue;
       ok = __all_sync(0xffffffffu, mbar_wait(kv_full, ic & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL));
@@ -265,7 +269,9 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
     const float c_log2 = p.scale * FB_LOG2E;
     int g = 0, ic = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+    for (int rnd = 0; rnd * static_cast<int>(gridDim.x) < n_items && ok; ++rnd) {
+      const int item = snake_item(rnd);
+      if (item >= n_items) continue;
       DkdvItem it;
       if (!dkdv_decode(p, item, it)) continue;
       const int kj = it.kv0 + row;
@@ -419,7 +425,7 @@ struct DqItem {
 };
 
 __device__ __forceinline__ bool dq_decode(const FlashBwdParams& p, int item, DqItem& it) {
-  const int4 job = p.plan[p.n_tiles - 1 - item / p.Hq];   // later query tiles of a document see more keys
+  const int4 job = p.plan[item / p.Hq];   // first list: query tiles that see the most keys first
   if (!job.w) return false;
   it.q0 = job.x; it.de = job.z;
   it.h = item % p.Hq;
@@ -488,7 +494,9 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
     if (lane == 0) {
       int g = 0, ic = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      for (int rnd = 0; rnd * static_cast<int>(gridDim.x) < n_items && ok; ++rnd) {
+        const int item = snake_item(rnd);
+        if (item >= n_items) continue;
         DqItem it;
         if (!dq_decode(p, item, it)) continue;
         if (!mbar_wait(q_empty, (ic & 1) ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_EMPTY)) break;
@@ -515,7 +523,9 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
     const uint64_t dDO0 = make_smem_desc(smem_u32(sDO), 16, 1024, SWZ_128B);
     int g = 0, ic = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+    for (int rnd = 0; rnd * static_cast<int>(gridDim.x) < n_items && ok; ++rnd) {
+      const int item = snake_item(rnd);
+      if (item >= n_items) continue;
       DqItem it;
       if (!dq_decode(p, item, it)) continue;
       ok = __all_sync(0xffffffffu, mbar_wait(q_full, ic & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL));
@@ -569,7 +579,9 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
     const float c_log2 = p.scale * FB_LOG2E;
     int g = 0, ic = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+    for (int rnd = 0; rnd * static_cast<int>(gridDim.x) < n_items && ok; ++rnd) {
+      const int item = snake_item(rnd);
+      if (item >= n_items) continue;
       DqItem it;
       if (!dq_decode(p, item, it)) continue;
       const int qi = it.q0 + row;

@@ -37,11 +37,15 @@ struct FlashFwdParams {
   int* status;
 };
 
-// Tile list for packed batches: for every document, ceil(len/tile) entries.
+// Tile lists for packed batches: for every document, ceil(len/tile) entries (q0, doc_start, doc_end, valid),
+// written twice: plan[0, max_tiles) sorted by the number of keys a QUERY tile sees (descending: the order
+// of the forward and dQ kernels), plan[max_tiles, 2*max_tiles) sorted by the number of queries that see a
+// KEY tile (descending: the dK / dV kernel). Unused entries sort last. One block; a rank sort, since the
+// list has at most a few hundred entries.
 __global__ void attn_plan_kernel(const int* __restrict__ cu, int ndocs, int tile, int4* __restrict__ plan,
                                  int max_tiles) {
-  // one block; thread t handles documents t, t+blockDim, ... after an exclusive scan of tile counts
-  extern __shared__ int s_off[];  // ndocs + 1
+  extern __shared__ int4 s_plan[];                                   // max_tiles entries in token order
+  int* s_off = reinterpret_cast<int*>(s_plan + max_tiles);           // ndocs + 1
   for (int d = threadIdx.x; d < ndocs; d += blockDim.x) {
     const int len = cu[d + 1] - cu[d];
     s_off[d + 1] = (len + tile - 1) / tile;
@@ -55,9 +59,25 @@ __global__ void attn_plan_kernel(const int* __restrict__ cu, int ndocs, int tile
   for (int d = threadIdx.x; d < ndocs; d += blockDim.x) {
     const int s = cu[d], e = cu[d + 1];
     int idx = s_off[d];
-    for (int q0 = s; q0 < e && idx < max_tiles; q0 += tile, ++idx) plan[idx] = make_int4(q0, s, e, 1);
+    for (int q0 = s; q0 < e && idx < max_tiles; q0 += tile, ++idx) s_plan[idx] = make_int4(q0, s, e, 1);
   }
-  for (int i = used + threadIdx.x; i < max_tiles; i += blockDim.x) plan[i] = make_int4(0, 0, 0, 0);
+  for (int i = used + threadIdx.x; i < max_tiles; i += blockDim.x) s_plan[i] = make_int4(0, 0, 0, 0);
+  __syncthreads();
+  for (int i = threadIdx.x; i < max_tiles; i += blockDim.x) {
+    const int4 me = s_plan[i];
+    const int cq = me.w ? min(me.x + tile, me.z) - me.y : -1;   // keys visible to the tile's last query row
+    const int ck = me.w ? me.z - me.x : -1;                     // queries that can see the tile's first key
+    int rq = 0, rk = 0;
+    for (int j = 0; j < max_tiles; ++j) {
+      const int4 o = s_plan[j];
+      const int oq = o.w ? min(o.x + tile, o.z) - o.y : -1;
+      const int ok = o.w ? o.z - o.x : -1;
+      rq += (oq > cq) || (oq == cq && j < i);
+      rk += (ok > ck) || (ok == ck && j < i);
+    }
+    plan[rq] = me;
+    plan[max_tiles + rk] = me;
+  }
 }
 
 // Work item = (query tile, query head). A CTA walks items blockIdx.x, blockIdx.x + gridDim.x, ... of the
@@ -69,8 +89,7 @@ struct FwdItem {
 };
 
 __device__ __forceinline__ bool fwd_decode(const FlashFwdParams& p, int item, FwdItem& it) {
-  const int tile = p.n_tiles - 1 - item / p.Hq;   // later query tiles of a document see more keys: first
-  const int4 job = p.plan[tile];
+  const int4 job = p.plan[item / p.Hq];   // the list is sorted: query tiles that see the most keys first
   if (!job.w) return false;
   it.q0 = job.x; it.ds = job.y; it.de = job.z;
   it.h = item % p.Hq;
@@ -144,7 +163,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tma_prefetch_desc(&tmV);
       int g = 0, ic = 0;   // K/V tiles and items issued so far by this CTA
       bool ok = true;
-      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      for (int rnd = 0; rnd * static_cast<int>(gridDim.x) < n_items && ok; ++rnd) {
+        const int item = snake_item(rnd);
+        if (item >= n_items) continue;
         FwdItem it;
         if (!fwd_decode(p, item, it)) continue;
         if (!mbar_wait(q_empty, (ic & 1) ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_EMPTY)) break;
@@ -190,7 +211,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     auto wait_all = [&](uint64_t* bar, uint32_t parity, int code) {
       return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, p.status, code));
     };
-    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+    for (int rnd = 0; rnd * static_cast<int>(gridDim.x) < n_items && ok; ++rnd) {
+      const int item = snake_item(rnd);
+      if (item >= n_items) continue;
       FwdItem it;
       if (!fwd_decode(p, item, it)) continue;
       const int n_kv = it.n_kv;
@@ -247,7 +270,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const uint32_t col_base = half * 64;
     int g = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+    for (int rnd = 0; rnd * static_cast<int>(gridDim.x) < n_items; ++rnd) {
+      const int item = snake_item(rnd);
+      if (item >= n_items) continue;
       FwdItem it;
       if (!fwd_decode(p, item, it)) continue;
       const int q0 = it.q0, n_kv = it.n_kv, h = it.h;
@@ -413,13 +438,13 @@ using namespace kwu;
 KWU_API int kwu_attn_plan(const int* cu_seqlens, int ndocs, int tile, void* plan, int max_tiles,
                           void* stream) {
   if (ndocs <= 0 || max_tiles <= 0) return 0;
-  if ((ndocs + 1) * sizeof(int) > 96 * 1024) {
-    set_last_error("attn_plan: too many documents (%d)", ndocs);
+  const size_t smem = static_cast<size_t>(max_tiles) * sizeof(int4) + (ndocs + 1) * sizeof(int);
+  if (smem > 96 * 1024) {
+    set_last_error("attn_plan: too many tiles / documents (%d / %d)", max_tiles, ndocs);
     return 7;
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   static bool attr = false;
-  const size_t smem = (ndocs + 1) * sizeof(int);
   if (!attr && smem > 48 * 1024) {
     cudaFuncSetAttribute(attn_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
     attr = true;

@@ -74,15 +74,18 @@ def varlen_attention_reference(q, k, v, cu_seqlens, window=None, sink_lse=None, 
 
 # --------------------------------------------------------------------------------- native path
 def attention_plan(cu_seqlens: torch.Tensor, total_tokens: int, tile: int = 128) -> torch.Tensor:
-    """Device-side work list: one int4 ``(q0, doc_start, doc_end, valid)`` per 128-row query tile.
+    """Device-side work lists: one int4 ``(q0, doc_start, doc_end, valid)`` per 128-row tile, twice.
 
-    The list has the host-known length ``ceil(T/tile) + num_docs`` (an upper bound on the number
-    of tiles), so building and using it needs no host synchronisation and is graph-capturable.
+    Rows ``[0, n)`` hold the tiles sorted by how many keys a query tile sees (heaviest first: the order in
+    which the forward and dQ kernels hand them to their persistent CTAs), rows ``[n, 2n)`` the same tiles
+    sorted by how many queries see a key tile (the dK / dV kernel). ``n = ceil(T/tile) + num_docs`` is a
+    host-known upper bound on the number of tiles (unused entries are marked invalid and sort last), so
+    building and using the lists needs no host synchronisation and is graph-capturable.
     """
     L = native.require()
     ndocs = cu_seqlens.numel() - 1
     max_tiles = (total_tokens + tile - 1) // tile + ndocs
-    plan = torch.empty(max_tiles, 4, dtype=torch.int32, device=cu_seqlens.device)
+    plan = torch.empty(2 * max_tiles, 4, dtype=torch.int32, device=cu_seqlens.device)
     rc = L.kwu_attn_plan(native.ptr(cu_seqlens), c_int(ndocs), c_int(tile), native.ptr(plan),
                          c_int(max_tiles), native.stream_ptr())
     native.check(rc, "attn_plan")
@@ -100,7 +103,7 @@ class _FlashVarlen(torch.autograd.Function):
         rc = L.kwu_flash_fwd(
             native.ptr(q), c_int(q.stride(0)), native.ptr(k), c_int(k.stride(0)), native.ptr(v),
             c_int(v.stride(0)), native.ptr(out), native.ptr(lse), native.ptr(plan),
-            c_int(plan.shape[0]), c_int(T), c_int(Hq), c_int(Hkv), c_int(window or 0),
+            c_int(plan.shape[0] // 2), c_int(T), c_int(Hq), c_int(Hkv), c_int(window or 0),
             native.ptr(sink_lse), c_float(scale), native.stream_ptr(), native.ptr(native.status_word()),
         )
         native.check(rc, "flash_fwd")
@@ -127,7 +130,7 @@ class _FlashVarlen(torch.autograd.Function):
             c_int(v.stride(0)), native.ptr(out), native.ptr(dout), native.ptr(lse), native.ptr(delta),
             native.ptr(dq), native.ptr(dk), c_int(dk.stride(0)), native.ptr(dv), c_int(dv.stride(0)),
             native.ptr(scratch), native.ptr(plan),
-            c_int(plan.shape[0]), c_int(T), c_int(Hq), c_int(Hkv), c_int(ctx.window or 0),
+            c_int(plan.shape[0] // 2), c_int(T), c_int(Hq), c_int(Hkv), c_int(ctx.window or 0),
             c_float(ctx.scale), native.stream_ptr(), native.ptr(native.status_word()),
         )
         native.check(rc, "flash_bwd")
@@ -192,7 +195,7 @@ class _AttentionCore(torch.autograd.Function):
         out = torch.empty(T, Hq, D, dtype=qkv.dtype, device=qkv.device)
         lse = torch.empty(Hq, T, dtype=torch.float32, device=qkv.device)
         rc = L.kwu_flash_fwd(native.ptr(q), ci(Hq * D), native.ptr(k), ci(Hkv * D), native.ptr(v), ci(ld),
-                             native.ptr(out), native.ptr(lse), native.ptr(plan), ci(plan.shape[0]), ci(T),
+                             native.ptr(out), native.ptr(lse), native.ptr(plan), ci(plan.shape[0] // 2), ci(T),
                              ci(Hq), ci(Hkv), ci(window or 0), native.ptr(sink_lse), cf(scale),
                              native.stream_ptr(), native.ptr(native.status_word()))
         native.check(rc, "flash_fwd")
@@ -223,7 +226,7 @@ class _AttentionCore(torch.autograd.Function):
         rc = L.kwu_flash_bwd(native.ptr(q), ci(Hq * D), native.ptr(k), ci(Hkv * D), native.ptr(v), ci(ld),
                              native.ptr(out), native.ptr(dout), native.ptr(lse), native.ptr(delta),
                              native.ptr(dq), native.ptr(dk), ci(Hkv * D), native.ptr(dv), ci(dld),
-                             native.ptr(scratch), native.ptr(plan), ci(plan.shape[0]), ci(T), ci(Hq), ci(Hkv),
+                             native.ptr(scratch), native.ptr(plan), ci(plan.shape[0] // 2), ci(T), ci(Hq), ci(Hkv),
                              ci(window or 0), cf(scale), native.stream_ptr(), native.ptr(native.status_word()))
         native.check(rc, "flash_bwd")
         rot_half = 0 if cos is None else cos.shape[-1]

@@ -70,6 +70,27 @@ def test_flash_fwd_bwd_matches_reference(lengths, Hq, Hkv, window, sinks):
         close(sa.grad, sr.grad, 3e-2, "dsink")
 
 
+def test_attention_plan_lists_are_complete_and_sorted():
+    from kohakuwullm_b200.models.seqinfo import SeqInfo
+    from kohakuwullm_b200.ops.attention import attention_plan
+
+    lengths = [300, 1000, 77, 64, 2655, 128, 1]
+    info = SeqInfo.from_lengths(lengths, device="cuda")
+    plan = attention_plan(info.cu_seqlens, info.total_tokens).cpu()
+    n = plan.shape[0] // 2
+    expect, start = set(), 0
+    for ln in lengths:
+        expect |= {(q0, start, start + ln) for q0 in range(start, start + ln, 128)}
+        start += ln
+    for half, cost in ((plan[:n], lambda r: min(r[0] + 128, r[2]) - r[1]), (plan[n:], lambda r: r[2] - r[0])):
+        rows = half.tolist()
+        valid = [r for r in rows if r[3] == 1]
+        assert {tuple(r[:3]) for r in valid} == expect and len(valid) == len(expect)
+        assert all(r[3] == 1 for r in rows[:len(valid)])          # unused entries come last
+        costs = [cost(r) for r in valid]
+        assert costs == sorted(costs, reverse=True)
+
+
 def test_packed_attention_does_not_cross_documents():
     """Changing one document must leave every other document's output bit-identical."""
     from kohakuwullm_b200.ops.attention import varlen_attention
