@@ -194,27 +194,30 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    // warp-uniform loop, one elected lane issues (coordinates, addresses and the tensor-map pointers stay
+    // in uniform registers; the MN-major operands need up to six loads per k-block)
+    const bool leader = elect_one();
+    if (leader) {
       tma_prefetch_desc(&tmA);
       tma_prefetch_desc(&tmB);
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int wi = 0; ok; ++wi) {
-        TileInfo ti;
-        const int got = next_work<BN>(p, wi, num_tiles, num_kb, ti);
-        if (got == 0) break;
-        if (got == 2) continue;
-        const int m0 = ti.m0, n0 = ti.n0;
-        for (int kb = 0; kb < ti.nkb; ++kb) {
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_EMPTY)) {
-            ok = false;
-            break;
-          }
-          uint8_t* sa = smem + stage * S::STAGE_BYTES;
-          uint8_t* sb = sa + S::A_BYTES;
+    }
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int wi = 0; ok; ++wi) {
+      TileInfo ti;
+      const int got = next_work<BN>(p, wi, num_tiles, num_kb, ti);
+      if (got == 0) break;
+      if (got == 2) continue;
+      const int m0 = ti.m0, n0 = ti.n0;
+      for (int kb = 0; kb < ti.nkb; ++kb) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_EMPTY));
+        if (!ok) break;
+        uint8_t* sa = smem + stage * S::STAGE_BYTES;
+        uint8_t* sb = sa + S::A_BYTES;
+        const int k0 = ti.k_begin + kb * GEMM_BK;
+        if (leader) {
           mbar_expect_tx(&full_bar[stage], S::STAGE_BYTES);
-          const int k0 = ti.k_begin + kb * GEMM_BK;
           if (!A_MN) {
             tma_load_2d(sa, &tmA, &full_bar[stage], k0, m0);
           } else {
@@ -229,10 +232,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             for (int c = 0; c < BN / 64; ++c)
               tma_load_2d(sb + c * 8192, &tmB, &full_bar[stage], n0 + c * 64, k0 + ti.b_row_off);
           }
-          if (++stage == STAGES) {
-            stage = 0;
-            phase ^= 1;
-          }
+        }
+        __syncwarp();
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
         }
       }
     }

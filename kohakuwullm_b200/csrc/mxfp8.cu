@@ -221,28 +221,30 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    if (lane == 0) {
+    // warp-uniform loop, one elected lane issues (see the MMA warp below)
+    const bool leader = elect_one();
+    if (leader) {
       tma_prefetch_desc(&tmA);
       tma_prefetch_desc(&tmB);
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        int m0, n0, b_row0;
-        if (!mx_decode_tile(p, tile, BN, m0, n0, b_row0)) continue;
-        const int tm = m0 / MX_BM;
-        // scale chunks of this tile's rows: A rows [m0, m0+128) are row tile tm; B rows [n0, n0+BN)
-        // start at 128-row tile n0/128 (BN is a multiple of 16, n0 may start mid-chunk only when
-        // BN is not a multiple of 128: the chunk pair covering [n0, n0+BN) is loaded and the row
-        // offset inside it is applied through the TMEM lane/column arithmetic below).
-        for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_EMPTY)) {
-            ok = false;
-            break;
-          }
-          uint8_t* sa = smem + stage * S::STAGE_BYTES;
-          uint8_t* sb = sa + S::A_BYTES;
-          uint8_t* ssf = sb + S::B_BYTES;
+    }
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      int m0, n0, b_row0;
+      if (!mx_decode_tile(p, tile, BN, m0, n0, b_row0)) continue;
+      const int tm = m0 / MX_BM;
+      // scale chunks of this tile's rows: A rows [m0, m0+128) are row tile tm; B rows [n0, n0+BN)
+      // start at 128-row tile n0/128 (BN is a multiple of 16, n0 may start mid-chunk only when
+      // BN is not a multiple of 128: the chunk pair covering [n0, n0+BN) is loaded and the row
+      // offset inside it is applied through the TMEM lane/column arithmetic below).
+      for (int kb = 0; kb < num_kb; ++kb) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_EMPTY));
+        if (!ok) break;
+        uint8_t* sa = smem + stage * S::STAGE_BYTES;
+        uint8_t* sb = sa + S::A_BYTES;
+        uint8_t* ssf = sb + S::B_BYTES;
+        if (leader) {
           mbar_expect_tx(&full_bar[stage], S::A_BYTES + S::B_BYTES + S::SF_BYTES);
           tma_load_2d(sa, &tmA, &full_bar[stage], kb * MX_BK, m0);
           tma_load_2d(sb, &tmB, &full_bar[stage], kb * MX_BK, b_row0);
@@ -254,10 +256,11 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             bulk_load_1d(ssf + 512 + c * 512, p.sfb + (static_cast<size_t>(chunk) * num_kb + kb) * 512, 512,
                          &full_bar[stage]);
           }
-          if (++stage == STAGES) {
-            stage = 0;
-            phase ^= 1;
-          }
+        }
+        __syncwarp();
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
         }
       }
     }
