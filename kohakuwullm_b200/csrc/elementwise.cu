@@ -95,7 +95,8 @@ __global__ void __launch_bounds__(256)
 rmsnorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
                        const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dy,
                        const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
-                       float* __restrict__ dw_partial, int rows, int cols, int one_plus, const MxOut mx) {
+                       float* __restrict__ dw_partial, float* __restrict__ dw_direct, int rows, int cols,
+                       int one_plus, const MxOut mx) {
   extern __shared__ float s_dw[];  // cols floats
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -184,8 +185,13 @@ rmsnorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ x, const float* __restr
         for (int e = 0; e < 8; ++e) atomicAdd(&s_dw[8 * v + e], dw_acc[j][e]);
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < cols; i += blockDim.x)
-      dw_partial[static_cast<size_t>(blockIdx.x) * cols + i] = s_dw[i];
+    if (dw_direct) {
+      // accumulating into an fp32 gradient buffer: the block's column sums go straight there, no second kernel
+      for (int i = threadIdx.x; i < cols; i += blockDim.x) atomicAdd(&dw_direct[i], s_dw[i]);
+    } else {
+      for (int i = threadIdx.x; i < cols; i += blockDim.x)
+        dw_partial[static_cast<size_t>(blockIdx.x) * cols + i] = s_dw[i];
+    }
   }
 }
 
@@ -589,18 +595,22 @@ static int rmsnorm_bwd_impl(const void* x, const float* w, const float* rstd, co
   const size_t dw_smem = want_dw ? cols * sizeof(float) : 0;
   const int nv = (cols / 8 + 31) / 32;
   if (nv <= 8 && grid > 148) grid = 148;  // the register-resident kernels run one CTA per SM
-#define KWU_RMS_BWD_ARGS (const __nv_bfloat16*)x, w, rstd, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)dres, \
-      (__nv_bfloat16*)dx, want_dw ? dw_partial : nullptr, rows, cols, one_plus
-  if (nv <= 2) rmsnorm_bwd_reg_kernel<2><<<grid, 256, dw_smem, st>>>(KWU_RMS_BWD_ARGS, mx);
-  else if (nv <= 4) rmsnorm_bwd_reg_kernel<4><<<grid, 256, dw_smem, st>>>(KWU_RMS_BWD_ARGS, mx);
-  else if (nv <= 5) rmsnorm_bwd_reg_kernel<5><<<grid, 256, dw_smem, st>>>(KWU_RMS_BWD_ARGS, mx);
-  else if (nv <= 6) rmsnorm_bwd_reg_kernel<6><<<grid, 256, dw_smem, st>>>(KWU_RMS_BWD_ARGS, mx);
-  else if (nv <= 8) rmsnorm_bwd_reg_kernel<8><<<grid, 256, dw_smem, st>>>(KWU_RMS_BWD_ARGS, mx);
-  else rmsnorm_bwd_kernel<<<grid, 256, dw_smem, st>>>(KWU_RMS_BWD_ARGS);
-#undef KWU_RMS_BWD_ARGS
+  // dw += ... : the register-resident kernels add their column sums to dw themselves
+  float* direct = (want_dw && accumulate_dw && nv <= 8) ? dw : nullptr;
+#define KWU_RMS_BWD_HEAD (const __nv_bfloat16*)x, w, rstd, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)dres, \
+      (__nv_bfloat16*)dx, want_dw ? dw_partial : nullptr
+#define KWU_RMS_BWD_TAIL rows, cols, one_plus
+  if (nv <= 2) rmsnorm_bwd_reg_kernel<2><<<grid, 256, dw_smem, st>>>(KWU_RMS_BWD_HEAD, direct, KWU_RMS_BWD_TAIL, mx);
+  else if (nv <= 4) rmsnorm_bwd_reg_kernel<4><<<grid, 256, dw_smem, st>>>(KWU_RMS_BWD_HEAD, direct, KWU_RMS_BWD_TAIL, mx);
+  else if (nv <= 5) rmsnorm_bwd_reg_kernel<5><<<grid, 256, dw_smem, st>>>(KWU_RMS_BWD_HEAD, direct, KWU_RMS_BWD_TAIL, mx);
+  else if (nv <= 6) rmsnorm_bwd_reg_kernel<6><<<grid, 256, dw_smem, st>>>(KWU_RMS_BWD_HEAD, direct, KWU_RMS_BWD_TAIL, mx);
+  else if (nv <= 8) rmsnorm_bwd_reg_kernel<8><<<grid, 256, dw_smem, st>>>(KWU_RMS_BWD_HEAD, direct, KWU_RMS_BWD_TAIL, mx);
+  else rmsnorm_bwd_kernel<<<grid, 256, dw_smem, st>>>(KWU_RMS_BWD_HEAD, KWU_RMS_BWD_TAIL);
+#undef KWU_RMS_BWD_HEAD
+#undef KWU_RMS_BWD_TAIL
   kwu::count_launch();
   if (int rc = check_launch("rmsnorm_bwd")) return rc;
-  if (want_dw) {
+  if (want_dw && !direct) {
     colsum_partials_kernel<<<(cols + 255) / 256, 256, 0, st>>>(dw_partial, dw, grid, cols, accumulate_dw); kwu::count_launch();
     return check_launch("rmsnorm_dw");
   }

@@ -91,6 +91,8 @@ struct TileInfo {
   long long c_off;   // added to the output pointer (elements)
 };
 
+constexpr int GEMM_RASTER_M = 16;
+
 // Same decoding in every role of the CTA. Returns false for tiles that carry no work.
 template <int BN>
 __device__ __forceinline__ bool decode_tile(const GemmParams& p, int tile, int num_kb, TileInfo& t) {
@@ -114,15 +116,23 @@ __device__ __forceinline__ bool decode_tile(const GemmParams& p, int tile, int n
     t.k_begin = kb0 * GEMM_BK;
     t.nkb = kb1 - kb0;
   }
-  const int tm = tile / p.tiles_n;
-  t.n0 = (tile % p.tiles_n) * BN;
   if (p.group_mode == 1) {
+    const int tm = tile / p.tiles_n;
+    t.n0 = (tile % p.tiles_n) * BN;
     const int4 g = p.group_tiles[tm];
     t.m0 = g.x;
     t.b_row_off = g.y * p.group_b_rows;
     return g.z != 0;
   }
-  t.m0 = tm * GEMM_BM;
+  // Raster order: panels of GEMM_RASTER_M row tiles, rows fastest inside a panel. The tiles that run at the
+  // same time then share a few B tiles and one A panel, which stays in L2; with columns fastest every wave
+  // of a wide product (a 65536-row vocabulary matrix) streams a different stretch of B from HBM for every
+  // row tile, 32 times the matrix in total.
+  const int span = GEMM_RASTER_M * p.tiles_n;
+  const int panel = tile / span, within = tile - panel * span;
+  const int gm = min(GEMM_RASTER_M, p.tiles_m - panel * GEMM_RASTER_M);
+  t.m0 = (panel * GEMM_RASTER_M + within % gm) * GEMM_BM;
+  t.n0 = (within / gm) * BN;
   return true;
 }
 
@@ -329,19 +339,37 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int col0 = n0 + c * 32;
         if (EPI == EPI_LSE) {
           if (row < p.M && col0 < p.N) {
-            float cmax = -INFINITY;
+            // the column bound and the label only matter in one chunk of a row each: handled outside the
+            // per-element loops, which are a scale, a maximum, and one fused multiply-add + exp2 per logit
+            if (col0 + 32 > p.N) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const float v = (col0 + j < p.N) ? __uint_as_float(r[j]) * p.alpha : -INFINITY;
-              r[j] = __float_as_uint(v);
-              cmax = fmaxf(cmax, v);
-              if (col0 + j == label) { tgt = v; tgt_here = true; }
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j >= p.N) r[j] = __float_as_uint(-INFINITY);
             }
-            const float nm = fmaxf(run_max, cmax);
-            float cs = 0.f;
+            if (label >= col0 && label < col0 + 32) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) cs += exp2f((__uint_as_float(r[j]) - nm) * 1.4426950408889634f);
-            run_sum = run_sum * exp2f((run_max - nm) * 1.4426950408889634f) + cs;
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j == label) { tgt = __uint_as_float(r[j]) * p.alpha; tgt_here = true; }
+            }
+            float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int j = 0; j < 32; ++j) m4[j & 3] = fmaxf(m4[j & 3], __uint_as_float(r[j]));
+            // alpha > 0 commutes with the maximum
+            const float cmax = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * p.alpha;
+            const float nm = fmaxf(run_max, cmax);
+            const float a2 = p.alpha * 1.4426950408889634f, nb = -nm * 1.4426950408889634f;
+            const uint64_t a2p = pack_f32x2(a2, a2), nbp = pack_f32x2(nb, nb);
+            uint64_t acc2[2] = {pack_f32x2(0.f, 0.f), pack_f32x2(0.f, 0.f)};
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+              float e0, e1;
+              unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])), a2p, nbp), e0, e1);
+              acc2[(j >> 1) & 1] = add_f32x2(acc2[(j >> 1) & 1], pack_f32x2(fast_exp2(e0), fast_exp2(e1)));
+            }
+            float c0, c1, c2, c3;
+            unpack_f32x2(acc2[0], c0, c1);
+            unpack_f32x2(acc2[1], c2, c3);
+            run_sum = run_sum * fast_exp2((run_max - nm) * 1.4426950408889634f) + ((c0 + c1) + (c2 + c3));
             run_max = nm;
           }
         } else if (EPI == EPI_DLOGITS) {
@@ -349,12 +377,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             __nv_bfloat16* dst =
                 reinterpret_cast<__nv_bfloat16*>(Cout) + static_cast<size_t>(row) * p.ldc + col0;
             float f[32];
+            {
+              // g = coef_p * exp2(acc * alpha * log2e - lse * log2e); the one-hot term is applied afterwards, in
+              // the one chunk of the row that holds the label
+              const float a2 = p.alpha * 1.4426950408889634f, nb = -row_lse * 1.4426950408889634f;
+              const uint64_t a2p = pack_f32x2(a2, a2), nbp = pack_f32x2(nb, nb), cpp = pack_f32x2(row_cp, row_cp);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const float v = __uint_as_float(r[j]) * p.alpha;
-              float g = row_cp * exp2f((v - row_lse) * 1.4426950408889634f);
-              if (col0 + j == label) g -= row_cy;
-              f[j] = g;
+              for (int j = 0; j < 32; j += 2) {
+                float e0, e1;
+                unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])), a2p, nbp), e0, e1);
+                unpack_f32x2(mul_f32x2(pack_f32x2(fast_exp2(e0), fast_exp2(e1)), cpp), f[j], f[j + 1]);
+              }
+              if (label >= col0 && label < col0 + 32) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (col0 + j == label) f[j] -= row_cy;
+              }
             }
             if (col0 + 32 <= p.N) {
 #pragma unroll
