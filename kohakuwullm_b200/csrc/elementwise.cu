@@ -435,6 +435,161 @@ qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ src, int src_ld,
   }
 }
 
+// Vector form for full rotary (rot_half == 32) or no rotary: eight lanes per 64-element row, 16-byte accesses,
+// four rows per warp pass. Lane sub-index j holds elements [8j, 8j+8); its rotate-half partner is lane j ^ 4.
+__device__ __forceinline__ float row8_sum(float v) {
+  v += __shfl_xor_sync(0xffffffffu, v, 1);
+  v += __shfl_xor_sync(0xffffffffu, v, 2);
+  v += __shfl_xor_sync(0xffffffffu, v, 4);
+  return v;
+}
+
+__global__ void __launch_bounds__(256)
+qknorm_rope_fwd_vec_kernel(const __nv_bfloat16* __restrict__ src, int src_ld,
+                           __nv_bfloat16* __restrict__ dst, int dst_ld,
+                           const float* __restrict__ weight, const float* __restrict__ cos_t,
+                           const float* __restrict__ sin_t, int tokens, int heads, int rot_half,
+                           float eps, int do_norm) {
+  const int lane = threadIdx.x & 31, sub = lane & 7, slot = lane >> 3;
+  const long total = static_cast<long>(tokens) * heads;
+  const int wpb = blockDim.x >> 5;
+  float w[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) w[i] = (do_norm && weight) ? weight[8 * sub + i] : 1.f;
+  for (long r0 = (static_cast<long>(blockIdx.x) * wpb + (threadIdx.x >> 5)) * 4; r0 < total;
+       r0 += static_cast<long>(gridDim.x) * wpb * 4) {
+    const long r = r0 + slot;
+    const bool live = r < total;
+    const int t = live ? static_cast<int>(r / heads) : 0;
+    const int h = live ? static_cast<int>(r % heads) : 0;
+    float x[8];
+    uint4 raw = make_uint4(0, 0, 0, 0);
+    if (live) raw = *reinterpret_cast<const uint4*>(src + static_cast<size_t>(t) * src_ld + h * 64 + 8 * sub);
+    unpack8(raw, x);
+    uint32_t xw[4] = {raw.x, raw.y, raw.z, raw.w};
+    if (do_norm) {
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
+      const float rstd = rsqrtf(row8_sum(ss) * (1.f / 64.f) + eps);
+      // the reference rounds the normalised value to the storage dtype before rotating
+#pragma unroll
+      for (int i = 0; i < 4; ++i) xw[i] = pack_bf16(x[2 * i] * rstd * w[2 * i], x[2 * i + 1] * rstd * w[2 * i + 1]);
+      unpack8(make_uint4(xw[0], xw[1], xw[2], xw[3]), x);
+    }
+    if (rot_half == 32) {
+      float y[8];
+      uint32_t pw[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) pw[i] = __shfl_xor_sync(0xffffffffu, xw[i], 4);
+      unpack8(make_uint4(pw[0], pw[1], pw[2], pw[3]), y);
+      const float sign = (sub < 4) ? -1.f : 1.f;
+      const float4* cp = reinterpret_cast<const float4*>(cos_t + static_cast<size_t>(t) * 32 + 8 * (sub & 3));
+      const float4* sp = reinterpret_cast<const float4*>(sin_t + static_cast<size_t>(t) * 32 + 8 * (sub & 3));
+      const float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
+      const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+      const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[i] = x[i] * c[i] + sign * y[i] * sn[i];
+    }
+    if (live) {
+      uint4 o;
+      o.x = pack_bf16(x[0], x[1]); o.y = pack_bf16(x[2], x[3]);
+      o.z = pack_bf16(x[4], x[5]); o.w = pack_bf16(x[6], x[7]);
+      *reinterpret_cast<uint4*>(dst + static_cast<size_t>(t) * dst_ld + h * 64 + 8 * sub) = o;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+qknorm_rope_bwd_vec_kernel(const __nv_bfloat16* __restrict__ src, int src_ld,
+                           const __nv_bfloat16* __restrict__ dout, int dout_ld,
+                           __nv_bfloat16* __restrict__ dsrc, int dsrc_ld,
+                           const float* __restrict__ weight, float* __restrict__ dweight,
+                           const float* __restrict__ cos_t, const float* __restrict__ sin_t, int tokens,
+                           int heads, int rot_half, float eps, int do_norm) {
+  __shared__ float s_dw[64];
+  if (threadIdx.x < 64) s_dw[threadIdx.x] = 0.f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31, sub = lane & 7, slot = lane >> 3;
+  const long total = static_cast<long>(tokens) * heads;
+  const int wpb = blockDim.x >> 5;
+  float w[8], dw[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    w[i] = (do_norm && weight) ? weight[8 * sub + i] : 1.f;
+    dw[i] = 0.f;
+  }
+  for (long r0 = (static_cast<long>(blockIdx.x) * wpb + (threadIdx.x >> 5)) * 4; r0 < total;
+       r0 += static_cast<long>(gridDim.x) * wpb * 4) {
+    const long r = r0 + slot;
+    const bool live = r < total;
+    const int t = live ? static_cast<int>(r / heads) : 0;
+    const int h = live ? static_cast<int>(r % heads) : 0;
+    uint4 graw = make_uint4(0, 0, 0, 0), xraw = make_uint4(0, 0, 0, 0);
+    if (live) {
+      graw = *reinterpret_cast<const uint4*>(dout + static_cast<size_t>(t) * dout_ld + h * 64 + 8 * sub);
+      if (do_norm) xraw = *reinterpret_cast<const uint4*>(src + static_cast<size_t>(t) * src_ld + h * 64 + 8 * sub);
+    }
+    float d[8];
+    unpack8(graw, d);
+    if (rot_half == 32) {
+      // rotary backward = rotation by the negated angle
+      float y[8];
+      const uint32_t gw[4] = {graw.x, graw.y, graw.z, graw.w};
+      uint32_t pw[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) pw[i] = __shfl_xor_sync(0xffffffffu, gw[i], 4);
+      unpack8(make_uint4(pw[0], pw[1], pw[2], pw[3]), y);
+      const float sign = (sub < 4) ? 1.f : -1.f;
+      const float4* cp = reinterpret_cast<const float4*>(cos_t + static_cast<size_t>(t) * 32 + 8 * (sub & 3));
+      const float4* sp = reinterpret_cast<const float4*>(sin_t + static_cast<size_t>(t) * 32 + 8 * (sub & 3));
+      const float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
+      const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+      const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) d[i] = d[i] * c[i] + sign * y[i] * sn[i];
+    }
+    if (do_norm) {
+      float x[8];
+      unpack8(xraw, x);
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
+      const float rstd = rsqrtf(row8_sum(ss) * (1.f / 64.f) + eps);
+      float dot = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        x[i] *= rstd;                 // normalised input
+        dw[i] += d[i] * x[i];         // dead rows carry zeros
+        d[i] *= w[i];
+        dot += d[i] * x[i];
+      }
+      dot = row8_sum(dot) * (1.f / 64.f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) d[i] = rstd * (d[i] - x[i] * dot);
+    }
+    if (live) {
+      uint4 o;
+      o.x = pack_bf16(d[0], d[1]); o.y = pack_bf16(d[2], d[3]);
+      o.z = pack_bf16(d[4], d[5]); o.w = pack_bf16(d[6], d[7]);
+      *reinterpret_cast<uint4*>(dsrc + static_cast<size_t>(t) * dsrc_ld + h * 64 + 8 * sub) = o;
+    }
+  }
+  if (dweight && do_norm) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      // the four row slots of a warp hold the same columns: fold them before the shared atomics
+      float v = dw[i];
+      v += __shfl_xor_sync(0xffffffffu, v, 8);
+      v += __shfl_xor_sync(0xffffffffu, v, 16);
+      if (slot == 0) atomicAdd(&s_dw[8 * sub + i], v);
+    }
+    __syncthreads();
+    if (threadIdx.x < 64) atomicAdd(&dweight[threadIdx.x], s_dw[threadIdx.x]);
+  }
+}
+
 // --------------------------------------------------------------------------- SwiGLU
 // in: (rows, 2H) with the gate in columns [0,H) and the value in [H,2H); out (rows, H).
 __global__ void __launch_bounds__(256)
@@ -643,6 +798,16 @@ KWU_API int kwu_qknorm_rope_fwd(const void* src, int src_ld, void* dst, int dst_
   }
   if (tokens <= 0) return 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  const bool vec = (rot_half == 32 || rot_half == 0) && src_ld % 8 == 0 && dst_ld % 8 == 0 && al16(src) && al16(dst) &&
+                   (rot_half == 0 || (al16(cos_t) && al16(sin_t))) && (!weight || al16(weight));
+  if (vec) {
+    const int grid = grid_for(static_cast<long>(tokens) * heads, 32, 148 * 8);
+    qknorm_rope_fwd_vec_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)src, src_ld, (__nv_bfloat16*)dst,
+                                                    dst_ld, weight, cos_t, sin_t, tokens, heads, rot_half,
+                                                    eps, do_norm); kwu::count_launch();
+    return check_launch("qknorm_rope_fwd");
+  }
   const int grid = grid_for(static_cast<long>(tokens) * heads, 8, 148 * 16);
   qknorm_rope_fwd_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)src, src_ld, (__nv_bfloat16*)dst,
                                               dst_ld, weight, cos_t, sin_t, tokens, heads, rot_half,
@@ -657,6 +822,17 @@ KWU_API int kwu_qknorm_rope_bwd(const void* src, int src_ld, const void* dout, i
   if (head_dim != 64) { set_last_error("qknorm_rope: head_dim must be 64"); return 7; }
   if (tokens <= 0) return 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  const bool vec = (rot_half == 32 || rot_half == 0) && src_ld % 8 == 0 && dout_ld % 8 == 0 && dsrc_ld % 8 == 0 &&
+                   al16(src) && al16(dout) && al16(dsrc) && (rot_half == 0 || (al16(cos_t) && al16(sin_t)));
+  if (vec) {
+    const int grid = grid_for(static_cast<long>(tokens) * heads, 32, 148 * 4);
+    qknorm_rope_bwd_vec_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)src, src_ld,
+                                                    (const __nv_bfloat16*)dout, dout_ld, (__nv_bfloat16*)dsrc,
+                                                    dsrc_ld, weight, dweight, cos_t, sin_t, tokens, heads,
+                                                    rot_half, eps, do_norm); kwu::count_launch();
+    return check_launch("qknorm_rope_bwd");
+  }
   const int grid = grid_for(static_cast<long>(tokens) * heads, 8, 148 * 4);
   qknorm_rope_bwd_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)src, src_ld,
                                               (const __nv_bfloat16*)dout, dout_ld, (__nv_bfloat16*)dsrc,

@@ -26,17 +26,28 @@ template <bool V> struct BoolC { static constexpr bool value = V; };   // compil
 __global__ void __launch_bounds__(256)
 flash_delta_kernel(const __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ dout,
                    float* __restrict__ delta, int T, int Hq) {
-  // one warp per (t, h) row of 64: two elements per lane
-  const int lane = threadIdx.x & 31;
+  // eight lanes per (t, h) row of 64 (one 16-byte load of each operand per lane), four rows per warp pass
+  const int lane = threadIdx.x & 31, sub = lane & 7, slot = lane >> 3;
   const long total = static_cast<long>(T) * Hq;
   const int wpb = blockDim.x >> 5;
-  for (long r = static_cast<long>(blockIdx.x) * wpb + (threadIdx.x >> 5); r < total;
-       r += static_cast<long>(gridDim.x) * wpb) {
-    const uint32_t a = reinterpret_cast<const uint32_t*>(out + r * 64)[lane];
-    const uint32_t b = reinterpret_cast<const uint32_t*>(dout + r * 64)[lane];
-    const float2 fa = unpack_bf16(a), fb = unpack_bf16(b);
-    const float s = warp_sum(fa.x * fb.x + fa.y * fb.y);
-    if (lane == 0) {
+  for (long r0 = (static_cast<long>(blockIdx.x) * wpb + (threadIdx.x >> 5)) * 4; r0 < total;
+       r0 += static_cast<long>(gridDim.x) * wpb * 4) {
+    const long r = r0 + slot;
+    float s = 0.f;
+    if (r < total) {
+      const uint4 a = reinterpret_cast<const uint4*>(out + r * 64)[sub];
+      const uint4 b = reinterpret_cast<const uint4*>(dout + r * 64)[sub];
+      const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 fa = unpack_bf16(aw[i]), fb = unpack_bf16(bw[i]);
+        s += fa.x * fb.x + fa.y * fb.y;
+      }
+    }
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    s += __shfl_xor_sync(0xffffffffu, s, 4);
+    if (sub == 0 && r < total) {
       const int t = static_cast<int>(r / Hq), h = static_cast<int>(r % Hq);
       delta[static_cast<size_t>(h) * T + t] = s;
     }
@@ -731,7 +742,7 @@ KWU_API int kwu_flash_bwd(const void* q, int q_ld, const void* k, int k_ld, cons
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   {
     long rows = static_cast<long>(T) * Hq;
-    long g = (rows + 7) / 8;
+    long g = (rows + 31) / 32;
     if (g > 148 * 16) g = 148 * 16;
     flash_delta_kernel<<<static_cast<int>(g), 256, 0, st>>>((const __nv_bfloat16*)out,
                                                           (const __nv_bfloat16*)dout, delta, T, Hq); kwu::count_launch();
