@@ -38,6 +38,20 @@ def case_gemm(reps):
         _report(f"gemm_bf16/{tag}_{M}x{N}x{K}", s, flops=2.0 * M * N * K, bytes_moved=2.0 * (M * K + N * K + M * N))
 
 
+def case_wgrad(reps):
+    """Weight-gradient products the way a training step runs them: both operands token-major, fp32 ``C +=``."""
+    from kohakuwullm_b200.ops.gemm import matmul
+
+    K = 4096
+    for (M, N, tag) in [(1792, 1280, "qkv"), (1280, 1280, "wo"), (7168, 1280, "w_in"), (1280, 3584, "w_out")]:
+        a = torch.randn(K, M, device="cuda").to(torch.bfloat16)
+        b = torch.randn(K, N, device="cuda").to(torch.bfloat16)
+        out = torch.zeros(M, N, device="cuda", dtype=torch.float32)
+        s = bench_samples(lambda: matmul(a, b, a_mn=True, b_mn=True, out=out, accumulate=True), repeats=reps)
+        _report(f"wgrad_fp32_accumulate/{tag}_{M}x{N}x{K}", s, flops=2.0 * M * N * K,
+                bytes_moved=2.0 * K * (M + N) + 8.0 * M * N)
+
+
 def case_mxfp8(reps):
     from kohakuwullm_b200.ops import mxfp8 as mx
 
@@ -152,7 +166,7 @@ def case_optim(reps):
     _report(f"adamw_flat/{n}", s, bytes_moved=n * (4 * 4 * 2 + 2.0))   # grad r+zero, master/m/v r+w, bf16 w
 
 
-CASES = {"gemm": case_gemm, "mxfp8": case_mxfp8, "flash": case_flash, "elementwise": case_elementwise, "loss": case_loss,
+CASES = {"gemm": case_gemm, "wgrad": case_wgrad, "mxfp8": case_mxfp8, "flash": case_flash, "elementwise": case_elementwise, "loss": case_loss,
          "optim": case_optim}
 
 
