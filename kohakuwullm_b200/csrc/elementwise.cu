@@ -102,9 +102,6 @@ rmsnorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ x, const float* __restr
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
   const int nvec = cols >> 3;
-  if (dw_partial)
-    for (int i = threadIdx.x; i < cols; i += blockDim.x) s_dw[i] = 0.f;
-  __syncthreads();
   float dw_acc[NV][8];
 #pragma unroll
   for (int j = 0; j < NV; ++j)
@@ -178,20 +175,23 @@ rmsnorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ x, const float* __restr
     }
   }
   if (dw_partial) {
+    // every warp parks its column sums in its own shared-memory row, then each column is summed over the
+    // warps by one thread (shared-memory float atomics from 40 values per lane took 4 us of a 24 us launch)
+    float* mine = s_dw + static_cast<size_t>(threadIdx.x >> 5) * cols;
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
       const int v = lane + 32 * j;
-      if (v < nvec)
-#pragma unroll
-        for (int e = 0; e < 8; ++e) atomicAdd(&s_dw[8 * v + e], dw_acc[j][e]);
+      if (v < nvec) {
+        *reinterpret_cast<float4*>(mine + 8 * v) = make_float4(dw_acc[j][0], dw_acc[j][1], dw_acc[j][2], dw_acc[j][3]);
+        *reinterpret_cast<float4*>(mine + 8 * v + 4) = make_float4(dw_acc[j][4], dw_acc[j][5], dw_acc[j][6], dw_acc[j][7]);
+      }
     }
     __syncthreads();
-    if (dw_direct) {
-      // accumulating into an fp32 gradient buffer: the block's column sums go straight there, no second kernel
-      for (int i = threadIdx.x; i < cols; i += blockDim.x) atomicAdd(&dw_direct[i], s_dw[i]);
-    } else {
-      for (int i = threadIdx.x; i < cols; i += blockDim.x)
-        dw_partial[static_cast<size_t>(blockIdx.x) * cols + i] = s_dw[i];
+    for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+      float t = 0.f;
+      for (int wp = 0; wp < warps_per_block; ++wp) t += s_dw[static_cast<size_t>(wp) * cols + i];
+      if (dw_direct) atomicAdd(&dw_direct[i], t);
+      else dw_partial[static_cast<size_t>(blockIdx.x) * cols + i] = t;
     }
   }
 }
@@ -749,6 +749,10 @@ static int rmsnorm_bwd_impl(const void* x, const float* w, const float* rstd, co
   int grid = grid_for(rows, 8, max_blocks);
   const bool want_dw = (w != nullptr && dw != nullptr && dw_partial != nullptr);
   const size_t dw_smem = want_dw ? cols * sizeof(float) : 0;
+  // 12 warps per CTA keep more rows in flight (8 % faster at 32768 rows) but leave the 4096-row case with an uneven
+  // 2-or-3 rows per warp; there 8 warps are faster
+  const int threads = rows >= 148 * 12 * 6 ? RMS_BWD_THREADS : 256;
+  const size_t dw_smem_reg = want_dw ? static_cast<size_t>(threads / 32) * cols * sizeof(float) : 0;   // one row per warp
   const int nv = (cols / 8 + 31) / 32;
   if (nv <= 8 && grid > 148) grid = 148;  // the register-resident kernels run one CTA per SM
   // dw += ... : the register-resident kernels add their column sums to dw themselves
@@ -756,14 +760,21 @@ static int rmsnorm_bwd_impl(const void* x, const float* w, const float* rstd, co
 #define KWU_RMS_BWD_HEAD (const __nv_bfloat16*)x, w, rstd, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)dres, \
       (__nv_bfloat16*)dx, want_dw ? dw_partial : nullptr
 #define KWU_RMS_BWD_TAIL rows, cols, one_plus
-  // 12 warps per CTA keep more rows in flight (8 % faster at 32768 rows) but leave the 4096-row case with an uneven
-  // 2-or-3 rows per warp; there 8 warps are faster
-  const int threads = rows >= 148 * 12 * 6 ? RMS_BWD_THREADS : 256;
-  if (nv <= 2) rmsnorm_bwd_reg_kernel<2><<<grid, threads, dw_smem, st>>>(KWU_RMS_BWD_HEAD, direct, KWU_RMS_BWD_TAIL, mx);
-  else if (nv <= 4) rmsnorm_bwd_reg_kernel<4><<<grid, threads, dw_smem, st>>>(KWU_RMS_BWD_HEAD, direct, KWU_RMS_BWD_TAIL, mx);
-  else if (nv <= 5) rmsnorm_bwd_reg_kernel<5><<<grid, threads, dw_smem, st>>>(KWU_RMS_BWD_HEAD, direct, KWU_RMS_BWD_TAIL, mx);
-  else if (nv <= 6) rmsnorm_bwd_reg_kernel<6><<<grid, threads, dw_smem, st>>>(KWU_RMS_BWD_HEAD, direct, KWU_RMS_BWD_TAIL, mx);
-  else if (nv <= 8) rmsnorm_bwd_reg_kernel<8><<<grid, threads, dw_smem, st>>>(KWU_RMS_BWD_HEAD, direct, KWU_RMS_BWD_TAIL, mx);
+  static bool reg_attr = false;
+  if (!reg_attr) {
+    const int lim = 12 * 2048 * 4;   // 12 warps x 2048 columns of floats
+    cudaFuncSetAttribute(rmsnorm_bwd_reg_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+    cudaFuncSetAttribute(rmsnorm_bwd_reg_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+    cudaFuncSetAttribute(rmsnorm_bwd_reg_kernel<5>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+    cudaFuncSetAttribute(rmsnorm_bwd_reg_kernel<6>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+    cudaFuncSetAttribute(rmsnorm_bwd_reg_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+    reg_attr = true;
+  }
+  if (nv <= 2) rmsnorm_bwd_reg_kernel<2><<<grid, threads, dw_smem_reg, st>>>(KWU_RMS_BWD_HEAD, direct, KWU_RMS_BWD_TAIL, mx);
+  else if (nv <= 4) rmsnorm_bwd_reg_kernel<4><<<grid, threads, dw_smem_reg, st>>>(KWU_RMS_BWD_HEAD, direct, KWU_RMS_BWD_TAIL, mx);
+  else if (nv <= 5) rmsnorm_bwd_reg_kernel<5><<<grid, threads, dw_smem_reg, st>>>(KWU_RMS_BWD_HEAD, direct, KWU_RMS_BWD_TAIL, mx);
+  else if (nv <= 6) rmsnorm_bwd_reg_kernel<6><<<grid, threads, dw_smem_reg, st>>>(KWU_RMS_BWD_HEAD, direct, KWU_RMS_BWD_TAIL, mx);
+  else if (nv <= 8) rmsnorm_bwd_reg_kernel<8><<<grid, threads, dw_smem_reg, st>>>(KWU_RMS_BWD_HEAD, direct, KWU_RMS_BWD_TAIL, mx);
   else rmsnorm_bwd_kernel<<<grid, 256, dw_smem, st>>>(KWU_RMS_BWD_HEAD, KWU_RMS_BWD_TAIL);
 #undef KWU_RMS_BWD_HEAD
 #undef KWU_RMS_BWD_TAIL
