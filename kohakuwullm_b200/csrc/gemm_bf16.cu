@@ -81,7 +81,10 @@ struct GemmSmem {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN >= 256) ? 4 : ((BN >= 192) ? 5 : 6);
   static constexpr int BAR_BYTES = 1024;
-  static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // +1024 alignment slack
+  // per epilogue warp a 32 x 32 fp32 patch (rows padded to 36 floats) through which the fp32 reductions are
+  // transposed, so that one warp instruction adds to 4 rows x 128 contiguous bytes instead of 32 rows x 16 bytes
+  static constexpr int RED_STAGE_BYTES = 4 * 32 * 36 * 4;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + RED_STAGE_BYTES + 1024;  // +1024 alignment slack
 };
 
 struct TileInfo {
@@ -175,6 +178,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint64_t* acc_empty = acc_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* red_stage = reinterpret_cast<float*>(bar_area + S::BAR_BYTES);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -410,6 +414,38 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (col0 + j < p.N) dst[j] = __float2bfloat16(f[j]);
             }
           }
+        } else if (p.out_fp32 && (p.splits > 1 || p.streamk > 0 || (p.group_mode == 2 && p.accumulate))) {
+          // Several CTAs add into the same tile (split-K, stream-K), or the tile is short in K and a
+          // read-modify-write would leave the epilogue waiting on loads (per-expert weight gradients):
+          // fire-and-forget vector reductions. The accumulator has one row per lane; the patch goes through
+          // shared memory so that the lanes of one reduction instruction cover whole 128-byte row segments.
+          if (col0 < p.N) {   // warp-uniform
+            float* stg = red_stage + (warp - 2) * (32 * 36);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              *reinterpret_cast<float4*>(stg + lane * 36 + 4 * j) =
+                  make_float4(__uint_as_float(r[4 * j]) * p.alpha, __uint_as_float(r[4 * j + 1]) * p.alpha,
+                              __uint_as_float(r[4 * j + 2]) * p.alpha, __uint_as_float(r[4 * j + 3]) * p.alpha);
+            __syncwarp();
+            const int c4 = (lane & 7) * 4;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int rr = i * 4 + (lane >> 3);
+              const int grow = m0 + quarter * 32 + rr;
+              const float4 v = *reinterpret_cast<const float4*>(stg + rr * 36 + c4);
+              if (grow < p.M) {
+                float* dst = reinterpret_cast<float*>(Cout) + static_cast<size_t>(grow) * p.ldc + col0 + c4;
+                if (col0 + c4 + 4 <= p.N) {
+                  red_add_f32x4(dst, v.x, v.y, v.z, v.w);
+                } else {
+                  const float f[4] = {v.x, v.y, v.z, v.w};
+                  for (int e = 0; e < 4; ++e)
+                    if (col0 + c4 + e < p.N) atomicAdd(dst + e, f[e]);
+                }
+              }
+            }
+            __syncwarp();
+          }
         } else if (row < p.M && col0 < p.N) {
           const bool full = (col0 + 32 <= p.N);
           if (p.out_fp32) {
@@ -423,13 +459,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 v.z = __uint_as_float(r[4 * j + 2]) * p.alpha;
                 v.w = __uint_as_float(r[4 * j + 3]) * p.alpha;
                 float4* d4 = reinterpret_cast<float4*>(dst) + j;
-                // several CTAs add into the same tile (split-K, stream-K), or the tile is short in K and a
-                // read-modify-write would leave the epilogue waiting on loads (per-expert weight gradients):
-                // fire-and-forget vector reductions
-                if (p.splits > 1 || p.streamk > 0 || (p.group_mode == 2 && p.accumulate)) {
-                  red_add_f32x4(dst + 4 * j, v.x, v.y, v.z, v.w);
-                  continue;
-                }
                 if (p.accumulate) {
                   const float4 o = *d4;
                   v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
@@ -441,7 +470,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               for (int j = 0; j < 32; ++j) {
                 if (col0 + j < p.N) {
                   float v = __uint_as_float(r[j]) * p.alpha;
-                  if (p.splits > 1 || p.streamk > 0) { atomicAdd(dst + j, v); continue; }
                   if (p.accumulate) v += dst[j];
                   dst[j] = v;
                 }
