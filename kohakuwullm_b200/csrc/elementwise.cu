@@ -131,11 +131,11 @@ rmsnorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ x, const float* __restr
     }
     __syncwarp();
   }
-  float dw_acc[NV][8];
+  uint64_t dw2[NV][4];   // column sums of g * xhat for this lane's columns, as fp32 pairs
 #pragma unroll
   for (int j = 0; j < NV; ++j)
 #pragma unroll
-    for (int e = 0; e < 8; ++e) dw_acc[j][e] = 0.f;
+    for (int e = 0; e < 4; ++e) dw2[j][e] = pack_f32x2(0.f, 0.f);
   const float inv_cols = 1.f / static_cast<float>(cols);
   int pass = 0;
   for (int row = first_row; row < rows; row += row_step, ++pass) {
@@ -173,26 +173,29 @@ rmsnorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ x, const float* __restr
       }
     }
     const float rstd = rstd_in[row];
-    float dot = 0.f;
+    // packed fp32 pairs throughout: a bf16x2 word becomes one 64-bit operand, every multiply / fused
+    // multiply-add works on both halves (the row costs about a third fewer issue slots)
+    auto bf2 = [](uint32_t u) { return pack_f32x2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u)); };
+    const uint64_t one2 = pack_f32x2(1.f, 1.f);
+    auto wpair = [&](int v, int e) -> uint64_t {
+      if (!w) return one2;
+      const uint64_t wv = *reinterpret_cast<const uint64_t*>(w + 8 * v + 2 * e);
+      return one_plus ? add_f32x2(wv, one2) : wv;
+    };
+    uint64_t dot2 = pack_f32x2(0.f, 0.f);
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
       const int v = lane + 32 * j;
       if (v < nvec) {
         const uint32_t aw[4] = {a[j].x, a[j].y, a[j].z, a[j].w}, gw[4] = {g[j].x, g[j].y, g[j].z, g[j].w};
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 xf = unpack_bf16(aw[e]), gf = unpack_bf16(gw[e]);
-          float w0 = 1.f, w1 = 1.f;
-          if (w) {
-            const float2 wv = *reinterpret_cast<const float2*>(w + 8 * v + 2 * e);
-            w0 = one_plus ? 1.f + wv.x : wv.x;
-            w1 = one_plus ? 1.f + wv.y : wv.y;
-          }
-          dot += gf.x * w0 * xf.x + gf.y * w1 * xf.y;
-        }
+        for (int e = 0; e < 4; ++e) dot2 = fma_f32x2(mul_f32x2(bf2(gw[e]), wpair(v, e)), bf2(aw[e]), dot2);
       }
     }
-    dot = warp_sum(dot) * rstd * inv_cols;
+    float dlo, dhi;
+    unpack_f32x2(dot2, dlo, dhi);
+    const float dot = warp_sum(dlo + dhi) * rstd * inv_cols;
+    const uint64_t rstd2 = pack_f32x2(rstd, rstd), ndot2 = pack_f32x2(-dot, -dot);
     uint4* dxr = reinterpret_cast<uint4*>(dx + static_cast<size_t>(row) * cols);
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
@@ -203,17 +206,13 @@ rmsnorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ x, const float* __restr
         const uint32_t rw[4] = {r[j].x, r[j].y, r[j].z, r[j].w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float2 xf = unpack_bf16(aw[e]), gf = unpack_bf16(gw[e]), rf = unpack_bf16(rw[e]);
-          float w0 = 1.f, w1 = 1.f;
-          if (w) {
-            const float2 wv = *reinterpret_cast<const float2*>(w + 8 * v + 2 * e);
-            w0 = one_plus ? 1.f + wv.x : wv.x;
-            w1 = one_plus ? 1.f + wv.y : wv.y;
-          }
-          const float xh0 = xf.x * rstd, xh1 = xf.y * rstd;
-          o[e] = pack_bf16(rstd * (gf.x * w0 - xh0 * dot) + rf.x, rstd * (gf.y * w1 - xh1 * dot) + rf.y);
-          dw_acc[j][2 * e] += gf.x * xh0;
-          dw_acc[j][2 * e + 1] += gf.y * xh1;
+          const uint64_t g2 = bf2(gw[e]);
+          const uint64_t xh2 = mul_f32x2(bf2(aw[e]), rstd2);                          // normalised input
+          const uint64_t t2 = fma_f32x2(xh2, ndot2, mul_f32x2(g2, wpair(v, e)));      // g*w - xhat*dot
+          float o0, o1;
+          unpack_f32x2(fma_f32x2(t2, rstd2, bf2(rw[e])), o0, o1);                     // rstd*(...) + residual grad
+          o[e] = pack_bf16(o0, o1);
+          dw2[j][e] = fma_f32x2(g2, xh2, dw2[j][e]);
         }
         dxr[v] = make_uint4(o[0], o[1], o[2], o[3]);
       }
@@ -233,8 +232,11 @@ rmsnorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ x, const float* __restr
     for (int j = 0; j < NV; ++j) {
       const int v = lane + 32 * j;
       if (v < nvec) {
-        *reinterpret_cast<float4*>(mine + 8 * v) = make_float4(dw_acc[j][0], dw_acc[j][1], dw_acc[j][2], dw_acc[j][3]);
-        *reinterpret_cast<float4*>(mine + 8 * v + 4) = make_float4(dw_acc[j][4], dw_acc[j][5], dw_acc[j][6], dw_acc[j][7]);
+        float d[8];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) unpack_f32x2(dw2[j][e], d[2 * e], d[2 * e + 1]);
+        *reinterpret_cast<float4*>(mine + 8 * v) = make_float4(d[0], d[1], d[2], d[3]);
+        *reinterpret_cast<float4*>(mine + 8 * v + 4) = make_float4(d[4], d[5], d[6], d[7]);
       }
     }
     __syncthreads();
@@ -666,7 +668,7 @@ swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ in, int in_ld, __nv_bfloat16
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const float2 gf = unpack_bf16(gw[e]), uf = unpack_bf16(uw[e]);
-        const float s0 = gf.x / (1.f + __expf(-gf.x)), s1 = gf.y / (1.f + __expf(-gf.y));
+        const float s0 = gf.x * fast_rcp(1.f + __expf(-gf.x)), s1 = gf.y * fast_rcp(1.f + __expf(-gf.y));
         ow[e] = pack_bf16(s0 * uf.x, s1 * uf.y);
       }
       *reinterpret_cast<uint4*>(out + static_cast<size_t>(r) * out_ld + 8 * v) =
@@ -702,7 +704,7 @@ swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ in, int in_ld,
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const float2 gf = unpack_bf16(gw[e]), uf = unpack_bf16(uw[e]), df = unpack_bf16(dw[e]);
-        const float sg0 = 1.f / (1.f + __expf(-gf.x)), sg1 = 1.f / (1.f + __expf(-gf.y));
+        const float sg0 = fast_rcp(1.f + __expf(-gf.x)), sg1 = fast_rcp(1.f + __expf(-gf.y));
         const float si0 = gf.x * sg0, si1 = gf.y * sg1;
         const float dg0 = df.x * uf.x * (sg0 * (1.f + gf.x * (1.f - sg0)));
         const float dg1 = df.y * uf.y * (sg1 * (1.f + gf.y * (1.f - sg1)));
