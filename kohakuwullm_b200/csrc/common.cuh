@@ -388,6 +388,13 @@ __device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
 }
+// 16 bytes from shared memory as two 64-bit words (fp32 pairs), addressed in the shared window: a generic
+// pointer derived from an aligned-up dynamic-shared-memory base makes the compiler emit generic loads
+__device__ __forceinline__ ulonglong2 lds_u64x2(uint32_t saddr) {
+  ulonglong2 v;
+  asm volatile("ld.shared.v2.u64 {%0, %1}, [%2];" : "=l"(v.x), "=l"(v.y) : "r"(saddr));
+  return v;
+}
 // 1/x on the special-function unit (about 1 ulp; the IEEE division of the plain `/` costs ~10 instructions)
 __device__ __forceinline__ float fast_rcp(float x) {
   float y;

@@ -907,7 +907,8 @@ KWU_API int kwu_qknorm_rope_bwd(const void* src, int src_ld, const void* dout, i
   const bool vec = (rot_half == 32 || rot_half == 0) && src_ld % 8 == 0 && dout_ld % 8 == 0 && dsrc_ld % 8 == 0 &&
                    al16(src) && al16(dout) && al16(dsrc) && (rot_half == 0 || (al16(cos_t) && al16(sin_t)));
   if (vec) {
-    const int grid = grid_for(static_cast<long>(tokens) * heads, 32, 148 * 16);
+    // few blocks: each one ends with 64 global atomics for the norm weight gradient (148 x 16 blocks measured 15 % slower)
+    const int grid = grid_for(static_cast<long>(tokens) * heads, 32, 148 * 4);
     qknorm_rope_bwd_vec_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)src, src_ld,
                                                     (const __nv_bfloat16*)dout, dout_ld, (__nv_bfloat16*)dsrc,
                                                     dsrc_ld, weight, dweight, cos_t, sin_t, tokens, heads,

@@ -290,8 +290,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
       for (int i = 0; i < it.n_it; ++i) {
         const int gi = g + i;
         const int q_lo = it.q_begin + i * 64;
-        const float* lse_s = sLse + (gi & 1) * 64;
-        const float* dl_s = sDelta + (gi & 1) * 64;
+        const uint32_t lse_sa = smem_u32(sLse + (gi & 1) * 64), dl_sa = smem_u32(sDelta + (gi & 1) * 64);
         // observe the producer's barrier directly so its smem writes are visible here
         ok = mbar_wait(&qd_full[gi & 1], (gi >> 1) & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
         if (ok) ok = mbar_wait(sdp_full, gi & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_FULL);
@@ -317,7 +316,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
           for (int e4 = 0; e4 < 32; e4 += 4) {
             // the per-query statistics are the same for every key row: one 16-byte shared load covers four
             // columns, already as two fp32 pairs
-            const ulonglong2 nl = *reinterpret_cast<const ulonglong2*>(lse_s + c * 32 + e4);
+            const ulonglong2 nl = lds_u64x2(lse_sa + (c * 32 + e4) * 4);
 #pragma unroll
             for (int h2 = 0; h2 < 2; ++h2) {
               const int e = e4 + 2 * h2;
@@ -352,7 +351,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
           tmem_ld_wait();
 #pragma unroll
           for (int e4 = 0; e4 < 32; e4 += 4) {
-            const ulonglong2 nd = *reinterpret_cast<const ulonglong2*>(dl_s + c * 32 + e4);
+            const ulonglong2 nd = lds_u64x2(dl_sa + (c * 32 + e4) * 4);
 #pragma unroll
             for (int h2 = 0; h2 < 2; ++h2) {
               const int e = e4 + 2 * h2;
