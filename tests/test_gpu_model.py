@@ -1,0 +1,69 @@
+"""Whole-model gradients of the native path (flat buffers, fused weight gradients, every kernel in the
+chain) against the same model evaluated in fp32 on the CPU with the PyTorch fallbacks."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _grads_native(cfg, packs, seed):
+    from kohakuwullm_b200.models import LMBackbone
+    from kohakuwullm_b200.ops import native
+    from kohakuwullm_b200.training.engine import TrainEngine
+
+    torch.manual_seed(seed)
+    with torch.device("cuda"):
+        model = LMBackbone(cfg)
+    eng = TrainEngine(model, lr=1e-3, param_dtype=torch.bfloat16, cuda_graphs=False)
+    model.train()
+    weights = {n: p.detach().float().cpu() for n, p in model.named_parameters()}
+    total = 0.0
+    for mb in packs:
+        mb = mb.to("cuda")
+        loss, _ = model.loss(mb.tokens, mb.labels, mb.seq_info, reduction="sum", router_scale=eng._router_scale)
+        loss.backward()
+        total += float(loss.detach())
+    torch.cuda.synchronize()
+    native.check_status()
+    grads = {n: p.main_grad.detach().float().cpu().clone() for n, p in model.named_parameters()}
+    return weights, grads, total
+
+
+def _grads_cpu(cfg, packs, weights):
+    from kohakuwullm_b200.models import LMBackbone
+
+    model = LMBackbone(cfg).float()
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            p.copy_(weights[n])
+    model.train()
+    total = 0.0
+    for mb in packs:
+        loss, _ = model.loss(mb.tokens, mb.labels, mb.seq_info, reduction="sum")
+        loss.backward()
+        total += float(loss.detach())
+    return {n: p.grad.detach().float().clone() for n, p in model.named_parameters()}, total
+
+
+# MXFP8: every product carries ~5 % relative rounding noise (e4m3 operands), and the gradient of an early
+# parameter has passed through about eight of them: the bound is on noise of that size, and on direction
+@pytest.mark.parametrize("mxfp8,tol", [(False, 0.05), (True, 0.30)])
+def test_whole_model_gradients_match_the_fp32_cpu_model(mxfp8, tol):
+    from kohakuwullm_b200.data.synthetic import make_packs
+    from kohakuwullm_b200.models import get_preset
+
+    cfg = get_preset("B200-dense-546M", depth=2, vocab_size=4096, mxfp8=mxfp8)
+    packs = make_packs(2, 1024, 64, 700, cfg.vocab_size, seed=21)
+    weights, got, loss_gpu = _grads_native(cfg, packs, seed=0)
+    cfg_cpu = get_preset("B200-dense-546M", depth=2, vocab_size=4096, mxfp8=False)
+    want, loss_cpu = _grads_cpu(cfg_cpu, packs, weights)
+    assert abs(loss_gpu - loss_cpu) <= 2e-2 * abs(loss_cpu), (loss_gpu, loss_cpu)
+    worst = {}
+    for n, g in want.items():
+        rel = ((got[n] - g).norm() / g.norm().clamp(min=1e-12)).item()
+        worst[n] = rel
+        cos = torch.nn.functional.cosine_similarity(got[n].flatten(), g.flatten(), dim=0).item()
+        assert cos > 0.95, f"{n}: gradient direction off (cosine {cos})"
+    bad = {n: r for n, r in worst.items() if r > tol}
+    assert not bad, f"gradients off: {sorted(bad.items(), key=lambda kv: -kv[1])[:6]}"
