@@ -425,6 +425,24 @@ int encode_tmap_2d(CUtensorMap* out, const void* base, int elem_kind, uint64_t r
                    uint64_t ld_elems, uint32_t box_rows, uint32_t box_cols, int swizzle);
 enum : int { ELEM_BF16 = 0, ELEM_F16 = 1, ELEM_U8 = 2, ELEM_F32 = 3 };
 const char* last_error();
+// Function attributes (`cudaFuncSetAttribute`) take effect per DEVICE, so "already set" is remembered per
+// device: one bit per device ordinal, read and written atomically. Two threads that race both apply the
+// attribute, which is idempotent.
+struct PerDeviceOnce {
+  unsigned long long done = 0;
+  bool pending() const {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    return !(__atomic_load_n(&done, __ATOMIC_ACQUIRE) & (1ull << (dev & 63)));
+  }
+  void mark() {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    __atomic_fetch_or(&done, 1ull << (dev & 63), __ATOMIC_RELEASE);
+  }
+};
+void set_device_status_word(int* p);
+int* device_status_word();   // the current device's registered status word, or null
 void count_launch(int n = 1);
 long long launch_total();  // bumps the library-wide kernel launch counter
 void set_last_error(const char* fmt, ...);

@@ -102,7 +102,7 @@ rmsnorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ x, const float* __restr
                        const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dy,
                        const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
                        float* __restrict__ dw_partial, float* __restrict__ dw_direct, int rows, int cols,
-                       int one_plus, const MxOut mx) {
+                       int one_plus, const MxOut mx, int* __restrict__ status) {
   extern __shared__ float s_dw[];  // unstaged: one parking row of cols floats per warp
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -143,10 +143,22 @@ rmsnorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ x, const float* __restr
     if (STAGED) {
       const int st = pass & 1;
       if (lane == 0 && row + row_step < rows) fetch(row + row_step, st ^ 1);
-      // bounded wait: a copy that never lands ends the loop instead of hanging the kernel
+      // bounded wait: a copy that never lands ends the loop instead of hanging the kernel, and the host
+      // learns of it through the status word (the rows this warp did not reach stay unwritten)
       bool landed = false;
       for (int tries = 0; tries < 400000 && !landed; ++tries) landed = mbar_try_wait(&bars[warp * 2 + st], (pass >> 1) & 1);
-      if (!__all_sync(0xffffffffu, landed)) break;
+      if (!__all_sync(0xffffffffu, landed)) {
+        if (lane == 0 && status) atomicCAS(status, 0, KWU_ERR_TIMEOUT_MISC);
+        // the next row's copy was issued above into the other stage: give it a bounded time to land before
+        // the stage area is reused as the parking row and the CTA exits
+        if (row + row_step < rows) {
+          bool other = false;
+          for (int tries = 0; tries < 100000 && !other; ++tries)
+            other = mbar_try_wait(&bars[warp * 2 + (st ^ 1)], ((pass + 1) >> 1) & 1);
+        }
+        __syncwarp();
+        break;
+      }
       const uint4* xs = reinterpret_cast<const uint4*>(my_area + static_cast<size_t>(st) * 3 * row_bytes);
       const uint4* gs = reinterpret_cast<const uint4*>(my_area + static_cast<size_t>(st) * 3 * row_bytes + row_bytes);
       const uint4* rs = reinterpret_cast<const uint4*>(my_area + static_cast<size_t>(st) * 3 * row_bytes + 2 * row_bytes);
@@ -646,6 +658,193 @@ qknorm_rope_bwd_vec_kernel(const __nv_bfloat16* __restrict__ src, int src_ld,
   }
 }
 
+// Query and key heads of a fused qkv projection in ONE launch (rows = tokens x (Hq + Hkv); the q and k slices
+// are adjacent in `src`, so head h of token t sits at src + t * src_ld + 64 h for both). At 4096 tokens each
+// of the two separate launches is a few microseconds of work behind a launch; one launch halves that.
+// Vector form only: full rotary (rot_half == 32) or none.
+__global__ void __launch_bounds__(256)
+qknorm_rope_fwd_qk_kernel(const __nv_bfloat16* __restrict__ src, int src_ld, __nv_bfloat16* __restrict__ dst_q,
+                          __nv_bfloat16* __restrict__ dst_k, const float* __restrict__ wq_p,
+                          const float* __restrict__ wk_p, const float* __restrict__ cos_t,
+                          const float* __restrict__ sin_t, int tokens, int Hq, int Hkv, int rot_half, float eps,
+                          int do_norm) {
+  const int lane = threadIdx.x & 31, sub = lane & 7, slot = lane >> 3;
+  const int HT = Hq + Hkv;
+  const long total = static_cast<long>(tokens) * HT;
+  const int wpb = blockDim.x >> 5;
+  float wq[8], wk[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    wq[i] = (do_norm && wq_p) ? wq_p[8 * sub + i] : 1.f;
+    wk[i] = (do_norm && wk_p) ? wk_p[8 * sub + i] : 1.f;
+  }
+  for (long r0 = (static_cast<long>(blockIdx.x) * wpb + (threadIdx.x >> 5)) * 4; r0 < total;
+       r0 += static_cast<long>(gridDim.x) * wpb * 4) {
+    const long r = r0 + slot;
+    const bool live = r < total;
+    const int t = live ? static_cast<int>(r / HT) : 0;
+    const int h = live ? static_cast<int>(r % HT) : 0;
+    const bool is_k = h >= Hq;
+    float x[8];
+    uint4 raw = make_uint4(0, 0, 0, 0);
+    if (live) raw = *reinterpret_cast<const uint4*>(src + static_cast<size_t>(t) * src_ld + h * 64 + 8 * sub);
+    unpack8(raw, x);
+    uint32_t xw[4] = {raw.x, raw.y, raw.z, raw.w};
+    if (do_norm) {
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
+      const float rstd = rsqrtf(row8_sum(ss) * (1.f / 64.f) + eps);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float w0 = is_k ? wk[2 * i] : wq[2 * i], w1 = is_k ? wk[2 * i + 1] : wq[2 * i + 1];
+        xw[i] = pack_bf16(x[2 * i] * rstd * w0, x[2 * i + 1] * rstd * w1);
+      }
+      unpack8(make_uint4(xw[0], xw[1], xw[2], xw[3]), x);
+    }
+    if (rot_half == 32) {
+      float y[8];
+      uint32_t pw[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) pw[i] = __shfl_xor_sync(0xffffffffu, xw[i], 4);
+      unpack8(make_uint4(pw[0], pw[1], pw[2], pw[3]), y);
+      const float sign = (sub < 4) ? -1.f : 1.f;
+      const float4* cp = reinterpret_cast<const float4*>(cos_t + static_cast<size_t>(t) * 32 + 8 * (sub & 3));
+      const float4* sp = reinterpret_cast<const float4*>(sin_t + static_cast<size_t>(t) * 32 + 8 * (sub & 3));
+      const float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
+      const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+      const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[i] = x[i] * c[i] + sign * y[i] * sn[i];
+    }
+    if (live) {
+      uint4 o;
+      o.x = pack_bf16(x[0], x[1]); o.y = pack_bf16(x[2], x[3]);
+      o.z = pack_bf16(x[4], x[5]); o.w = pack_bf16(x[6], x[7]);
+      __nv_bfloat16* d = is_k ? dst_k + (static_cast<size_t>(t) * Hkv + (h - Hq)) * 64
+                              : dst_q + (static_cast<size_t>(t) * Hq + h) * 64;
+      *reinterpret_cast<uint4*>(d + 8 * sub) = o;
+    }
+  }
+}
+
+// Backward of the above for q and k in one launch, writing into the fused gradient buffer `dsrc` (the layout of
+// the qkv projection output). With `mx.q` set it also emits the MXFP8 copy (bytes + scales) of the WHOLE
+// gradient row, v slice included: the v slice was written into `dsrc` by the attention backward before this
+// kernel runs and is only read back here, so the consumer (the qkv projection's dgrad) needs no quantise pass.
+__global__ void __launch_bounds__(256)
+qknorm_rope_bwd_qk_kernel(const __nv_bfloat16* __restrict__ src, int src_ld, const __nv_bfloat16* __restrict__ dq,
+                          const __nv_bfloat16* __restrict__ dk, __nv_bfloat16* __restrict__ dsrc, int dsrc_ld,
+                          const float* __restrict__ wq_p, const float* __restrict__ wk_p,
+                          float* __restrict__ dwq_out, float* __restrict__ dwk_out,
+                          const float* __restrict__ cos_t, const float* __restrict__ sin_t, int tokens, int Hq,
+                          int Hkv, int rot_half, float eps, int do_norm, const MxOut mx) {
+  __shared__ float s_dw[128];
+  if (threadIdx.x < 128) s_dw[threadIdx.x] = 0.f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31, sub = lane & 7, slot = lane >> 3;
+  const int HQK = Hq + Hkv;
+  const int HT = mx.q ? Hq + 2 * Hkv : HQK;   // with emission the v heads are visited too (read-only)
+  const long total = static_cast<long>(tokens) * HT;
+  const int wpb = blockDim.x >> 5;
+  float wq[8], wk[8], dwq[8], dwk[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    wq[i] = (do_norm && wq_p) ? wq_p[8 * sub + i] : 1.f;
+    wk[i] = (do_norm && wk_p) ? wk_p[8 * sub + i] : 1.f;
+    dwq[i] = dwk[i] = 0.f;
+  }
+  // uniform trip count per warp: the emission shuffles inside the loop
+  for (long r0 = (static_cast<long>(blockIdx.x) * wpb + (threadIdx.x >> 5)) * 4; r0 < total;
+       r0 += static_cast<long>(gridDim.x) * wpb * 4) {
+    const long r = r0 + slot;
+    const bool live = r < total;
+    const int t = live ? static_cast<int>(r / HT) : 0;
+    const int h = live ? static_cast<int>(r % HT) : 0;
+    const bool is_v = h >= HQK, is_k = !is_v && h >= Hq;
+    uint4 o = make_uint4(0, 0, 0, 0);
+    if (is_v) {
+      if (live) o = *reinterpret_cast<const uint4*>(dsrc + static_cast<size_t>(t) * dsrc_ld + h * 64 + 8 * sub);
+    }
+    uint4 graw = make_uint4(0, 0, 0, 0), xraw = make_uint4(0, 0, 0, 0);
+    if (live && !is_v) {
+      const __nv_bfloat16* g = is_k ? dk + (static_cast<size_t>(t) * Hkv + (h - Hq)) * 64
+                                    : dq + (static_cast<size_t>(t) * Hq + h) * 64;
+      graw = *reinterpret_cast<const uint4*>(g + 8 * sub);
+      if (do_norm) xraw = *reinterpret_cast<const uint4*>(src + static_cast<size_t>(t) * src_ld + h * 64 + 8 * sub);
+    }
+    float d[8];
+    unpack8(graw, d);
+    if (rot_half == 32) {
+      float y[8];
+      const uint32_t gw[4] = {graw.x, graw.y, graw.z, graw.w};
+      uint32_t pw[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) pw[i] = __shfl_xor_sync(0xffffffffu, gw[i], 4);
+      unpack8(make_uint4(pw[0], pw[1], pw[2], pw[3]), y);
+      const float sign = (sub < 4) ? 1.f : -1.f;
+      const float4* cp = reinterpret_cast<const float4*>(cos_t + static_cast<size_t>(t) * 32 + 8 * (sub & 3));
+      const float4* sp = reinterpret_cast<const float4*>(sin_t + static_cast<size_t>(t) * 32 + 8 * (sub & 3));
+      const float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
+      const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+      const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) d[i] = d[i] * c[i] + sign * y[i] * sn[i];
+    }
+    if (do_norm) {
+      float x[8];
+      unpack8(xraw, x);
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
+      const float rstd = rsqrtf(row8_sum(ss) * (1.f / 64.f) + eps);
+      float dot = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        x[i] *= rstd;
+        const float gx = d[i] * x[i];          // dead and v rows carry zeros
+        dwq[i] += is_k ? 0.f : gx;
+        dwk[i] += is_k ? gx : 0.f;
+        d[i] *= is_k ? wk[i] : wq[i];
+        dot += d[i] * x[i];
+      }
+      dot = row8_sum(dot) * (1.f / 64.f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) d[i] = rstd * (d[i] - x[i] * dot);
+    }
+    if (!is_v) {
+      o.x = pack_bf16(d[0], d[1]); o.y = pack_bf16(d[2], d[3]);
+      o.z = pack_bf16(d[4], d[5]); o.w = pack_bf16(d[6], d[7]);
+      if (live) *reinterpret_cast<uint4*>(dsrc + static_cast<size_t>(t) * dsrc_ld + h * 64 + 8 * sub) = o;
+    }
+    if (mx.q) {
+      float fr[8];
+      unpack8(o, fr);   // the rounded values, as a quantise pass over the stored tensor would see them
+      mx_emit8(fr, live, t, h * 64 + 8 * sub, mx.q, mx.ldq, mx.sf, mx.n_kchunks);
+    }
+  }
+  if (do_norm && (dwq_out || dwk_out)) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float a = dwq[i], b = dwk[i];
+      a += __shfl_xor_sync(0xffffffffu, a, 8);
+      a += __shfl_xor_sync(0xffffffffu, a, 16);
+      b += __shfl_xor_sync(0xffffffffu, b, 8);
+      b += __shfl_xor_sync(0xffffffffu, b, 16);
+      if (slot == 0) {
+        atomicAdd(&s_dw[8 * sub + i], a);
+        atomicAdd(&s_dw[64 + 8 * sub + i], b);
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x < 64) {
+      if (dwq_out) atomicAdd(&dwq_out[threadIdx.x], s_dw[threadIdx.x]);
+    } else if (threadIdx.x < 128) {
+      if (dwk_out) atomicAdd(&dwk_out[threadIdx.x - 64], s_dw[threadIdx.x]);
+    }
+  }
+}
+
 // --------------------------------------------------------------------------- SwiGLU
 // in: (rows, 2H) with the gate in columns [0,H) and the value in [H,2H); out (rows, H).
 __global__ void __launch_bounds__(256)
@@ -818,22 +1017,22 @@ static int rmsnorm_bwd_impl(const void* x, const float* w, const float* rstd, co
   auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
   const size_t stage_smem = 256 + static_cast<size_t>(threads / 32) * 6 * cols * 2;
   const bool staged = al16(x) && al16(dy) && (!dres || al16(dres)) && stage_smem <= 220 * 1024;
-  static bool reg_attr = false;
-  if (!reg_attr) {
+  static PerDeviceOnce reg_attr;
+  if (reg_attr.pending()) {
     const int lim = 220 * 1024;
 #define KWU_RMS_ATTR(NVV)                                                                                      \
     cudaFuncSetAttribute(rmsnorm_bwd_reg_kernel<NVV, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim); \
     cudaFuncSetAttribute(rmsnorm_bwd_reg_kernel<NVV, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim)
     KWU_RMS_ATTR(2); KWU_RMS_ATTR(4); KWU_RMS_ATTR(5); KWU_RMS_ATTR(6); KWU_RMS_ATTR(8);
 #undef KWU_RMS_ATTR
-    reg_attr = true;
+    reg_attr.mark();
   }
 #define KWU_RMS_LAUNCH(NVV)                                                                                         \
   do {                                                                                                              \
     if (staged)                                                                                                     \
-      rmsnorm_bwd_reg_kernel<NVV, true><<<grid, threads, stage_smem, st>>>(KWU_RMS_BWD_HEAD, direct, KWU_RMS_BWD_TAIL, mx); \
+      rmsnorm_bwd_reg_kernel<NVV, true><<<grid, threads, stage_smem, st>>>(KWU_RMS_BWD_HEAD, direct, KWU_RMS_BWD_TAIL, mx, kwu::device_status_word()); \
     else                                                                                                            \
-      rmsnorm_bwd_reg_kernel<NVV, false><<<grid, threads, dw_smem_reg, st>>>(KWU_RMS_BWD_HEAD, direct, KWU_RMS_BWD_TAIL, mx); \
+      rmsnorm_bwd_reg_kernel<NVV, false><<<grid, threads, dw_smem_reg, st>>>(KWU_RMS_BWD_HEAD, direct, KWU_RMS_BWD_TAIL, mx, nullptr); \
   } while (0)
   if (nv <= 2) KWU_RMS_LAUNCH(2);
   else if (nv <= 4) KWU_RMS_LAUNCH(4);
@@ -921,6 +1120,55 @@ KWU_API int kwu_qknorm_rope_bwd(const void* src, int src_ld, const void* dout, i
                                               dsrc_ld, weight, dweight, cos_t, sin_t, tokens, heads,
                                               rot_half, eps, do_norm); kwu::count_launch();
   return check_launch("qknorm_rope_bwd");
+}
+
+// q and k heads of a fused qkv buffer in one launch. dst_q (T, Hq, 64) and dst_k (T, Hkv, 64) are contiguous.
+// Needs rot_half 32 or 0 and 16-byte aligned operands (returns 7 otherwise: use the per-tensor entry points).
+KWU_API int kwu_qknorm_rope_fwd_qk(const void* src, int src_ld, void* dst_q, void* dst_k, const float* wq,
+                                   const float* wk, const float* cos_t, const float* sin_t, int tokens, int Hq,
+                                   int Hkv, int rot_half, float eps, int do_norm, void* stream) {
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if ((rot_half != 32 && rot_half != 0) || src_ld % 8 || !al16(src) || !al16(dst_q) || !al16(dst_k) ||
+      (rot_half && (!al16(cos_t) || !al16(sin_t)))) {
+    set_last_error("qknorm_rope_fwd_qk: needs full or no rotary and 16-byte aligned operands");
+    return 7;
+  }
+  if (tokens <= 0) return 0;
+  const int grid = grid_for(static_cast<long>(tokens) * (Hq + Hkv), 32, 148 * 16);
+  qknorm_rope_fwd_qk_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      (const __nv_bfloat16*)src, src_ld, (__nv_bfloat16*)dst_q, (__nv_bfloat16*)dst_k, wq, wk, cos_t, sin_t, tokens,
+      Hq, Hkv, rot_half, eps, do_norm); kwu::count_launch();
+  return check_launch("qknorm_rope_fwd_qk");
+}
+
+// Backward for q and k in one launch; dq (T, Hq, 64) and dk (T, Hkv, 64) contiguous, results written into the
+// q and k slices of dsrc (T, dsrc_ld). dwq / dwk (64 floats each, optional) are ADDED to. With q8 / sf non-null
+// the MXFP8 copy of all (Hq + 2 Hkv) * 64 columns of dsrc is written too (the v slice must already hold its
+// final values); tokens must then be a multiple of 128 and the column count a multiple of 128.
+KWU_API int kwu_qknorm_rope_bwd_qk(const void* src, int src_ld, const void* dq, const void* dk, void* dsrc,
+                                   int dsrc_ld, const float* wq, const float* wk, float* dwq, float* dwk,
+                                   const float* cos_t, const float* sin_t, int tokens, int Hq, int Hkv,
+                                   int rot_half, float eps, int do_norm, void* q8, int ldq, void* sf,
+                                   void* stream) {
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if ((rot_half != 32 && rot_half != 0) || src_ld % 8 || dsrc_ld % 8 || !al16(src) || !al16(dq) || !al16(dk) ||
+      !al16(dsrc) || (rot_half && (!al16(cos_t) || !al16(sin_t)))) {
+    set_last_error("qknorm_rope_bwd_qk: needs full or no rotary and 16-byte aligned operands");
+    return 7;
+  }
+  if (tokens <= 0) return 0;
+  const int cols = (Hq + 2 * Hkv) * 64;
+  if (q8 && (tokens % 128 || cols % 128 || ldq % 8)) {
+    set_last_error("qknorm_rope_bwd_qk: the fp8 copy needs tokens and columns in multiples of 128");
+    return 7;
+  }
+  const int heads = q8 ? Hq + 2 * Hkv : Hq + Hkv;
+  const int grid = grid_for(static_cast<long>(tokens) * heads, 32, 148 * 4);
+  qknorm_rope_bwd_qk_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      (const __nv_bfloat16*)src, src_ld, (const __nv_bfloat16*)dq, (const __nv_bfloat16*)dk, (__nv_bfloat16*)dsrc,
+      dsrc_ld, wq, wk, dwq, dwk, cos_t, sin_t, tokens, Hq, Hkv, rot_half, eps, do_norm,
+      make_mx(q8, ldq, sf, cols)); kwu::count_launch();
+  return check_launch("qknorm_rope_bwd_qk");
 }
 
 static int swiglu_fwd_impl(const void* in, int in_ld, void* out, int out_ld, int rows, int H, const MxOut mx,

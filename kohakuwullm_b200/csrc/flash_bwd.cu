@@ -758,12 +758,12 @@ KWU_API int kwu_flash_bwd(const void* q, int q_ld, const void* k, int k_ld, cons
   if ((rc = encode_tmap_2d(&tmDO128, dout, ELEM_BF16, T, wq, wq, 128, 64, SW))) return rc;
   if ((rc = encode_tmap_2d(&tmK64, k, ELEM_BF16, T, wk, k_ld, 64, 64, SW))) return rc;
   if ((rc = encode_tmap_2d(&tmV64, v, ELEM_BF16, T, wk, v_ld, 64, 64, SW))) return rc;
-  static bool attr = false;
-  if (!attr) {
+  static PerDeviceOnce attr;
+  if (attr.pending()) {
     cudaError_t e1 = cudaFuncSetAttribute(flash_bwd_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FBK_SMEM);
     cudaError_t e2 = cudaFuncSetAttribute(flash_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FBQ_SMEM);
     if (e1 != cudaSuccess || e2 != cudaSuccess) { set_last_error("flash_bwd attr failed"); return 10; }
-    attr = true;
+    attr.mark();
   }
   FlashBwdParams p;
   p.lse = lse; p.delta = delta;

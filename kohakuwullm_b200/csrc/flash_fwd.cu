@@ -444,10 +444,10 @@ KWU_API int kwu_attn_plan(const int* cu_seqlens, int ndocs, int tile, void* plan
     return 7;
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  static bool attr = false;
-  if (!attr && smem > 48 * 1024) {
+  static PerDeviceOnce attr;
+  if (smem > 48 * 1024 && attr.pending()) {
     cudaFuncSetAttribute(attn_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-    attr = true;
+    attr.mark();
   }
   attn_plan_kernel<<<1, 256, smem, st>>>(cu_seqlens, ndocs, tile, reinterpret_cast<int4*>(plan), max_tiles); kwu::count_launch();
   cudaError_t e = cudaGetLastError();
@@ -465,11 +465,11 @@ KWU_API int kwu_flash_fwd(const void* q, int q_ld, const void* k, int k_ld, cons
   if ((rc = encode_tmap_2d(&tmQ, q, ELEM_BF16, T, (uint64_t)Hq * FA_D, q_ld, FA_BM, FA_D, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if ((rc = encode_tmap_2d(&tmK, k, ELEM_BF16, T, (uint64_t)Hkv * FA_D, k_ld, FA_BN, FA_D, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   if ((rc = encode_tmap_2d(&tmV, v, ELEM_BF16, T, (uint64_t)Hkv * FA_D, v_ld, FA_BN, FA_D, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
-  static bool attr = false;
-  if (!attr) {
+  static PerDeviceOnce attr;
+  if (attr.pending()) {
     cudaError_t e = cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FA_SMEM);
     if (e != cudaSuccess) { set_last_error("flash_fwd attr: %s", cudaGetErrorString(e)); return 10; }
-    attr = true;
+    attr.mark();
   }
   FlashFwdParams p;
   p.out = reinterpret_cast<__nv_bfloat16*>(out);

@@ -20,7 +20,8 @@
 //
 // Flag protocol: flags only ever hold the step's epoch number (monotonically increasing), so nothing
 // is reset between steps. All waits are bounded; on a time-out the kernel records
-// KWU_ERR_TIMEOUT_FLAG in the status word and returns. The division by the global trained-token count
+// KWU_ERR_TIMEOUT_FLAG in the status word and returns, and a reduction that timed out (or that found the
+// status word already set) does not publish its norm, so no rank applies the update of that step. The division by the global trained-token count
 // happens here (inv_tokens is a device scalar), which is what makes gradient accumulation token-exact
 // without a host round trip. Takes the place of torch DDP's bucketed NCCL all-reduce followed by a
 // separate optimizer pass (scripts/train/lm.py:383-398, src/kohakuwullm/training/optim/fused_adamw.py
@@ -130,7 +131,11 @@ ddp_reduce_shard_kernel(const ReduceArgs a) {
     const float total = a.first ? t : (*a.sumsq + t);
     *a.sumsq = total;
     *a.counter = 0;
-    if (a.publish) {
+    // A block whose wait ran out has written the status word before it added itself to the counter. The sum is
+    // then NOT published: every rank's ddp_adamw_allgather runs out of time waiting for it and leaves the
+    // parameters untouched, instead of stepping on gradients that were never reduced.
+    const bool healthy = !a.status || *reinterpret_cast<volatile int*>(a.status) == 0;
+    if (a.publish && healthy) {
       for (int p = 0; p < a.world; ++p) a.peers.slots[p][a.rank] = total;
       __threadfence_system();
       for (int p = 0; p < a.world; ++p) st_release_sys(a.peers.flags[p] + FLAG_SQ * a.world + a.rank, a.epoch);

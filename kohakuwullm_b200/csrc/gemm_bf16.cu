@@ -622,14 +622,14 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
   p.lse = ea.lse; p.coef_p = ea.coef_p; p.coef_y = ea.coef_y;
 
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, EPI>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static PerDeviceOnce attr_set;
+  if (attr_set.pending()) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
     if (e != cudaSuccess) {
       set_last_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e));
       return 10;
     }
-    attr_set = true;
+    attr_set.mark();
   }
   long grid_l = static_cast<long>(p.tiles_m) * p.tiles_n * (ga.mode == 2 ? ga.num_groups : 1) * (p.splits > 1 ? p.splits : 1);
   int grid = grid_l > (1 << 30) ? (1 << 30) : static_cast<int>(grid_l);

@@ -427,11 +427,11 @@ static int launch_mx(const void* A, const void* B, void* C, int M, int N, int K,
   p.row_ptrs = out_fp32 ? nullptr : row_ptrs;
   p.status = status;
   auto kern = gemm_mxfp8_kernel<BN>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static PerDeviceOnce attr_set;
+  if (attr_set.pending()) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
     if (e != cudaSuccess) { set_last_error("gemm_mxfp8 attr: %s", cudaGetErrorString(e)); return 10; }
-    attr_set = true;
+    attr_set.mark();
   }
   int sms = 0, dev = 0;
   cudaGetDevice(&dev);

@@ -20,6 +20,20 @@ void set_last_error(const char* fmt, ...) {
   va_end(ap);
 }
 
+// Status word of each device (set by the host binding), for kernels whose entry point carries no status
+// argument of its own.
+static int* g_status_word[64] = {nullptr};
+void set_device_status_word(int* p) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  __atomic_store_n(&g_status_word[dev & 63], p, __ATOMIC_RELEASE);
+}
+int* device_status_word() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return __atomic_load_n(&g_status_word[dev & 63], __ATOMIC_ACQUIRE);
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -86,6 +100,10 @@ int encode_tmap_2d(CUtensorMap* out, const void* base, int elem_kind, uint64_t r
 }  // namespace kwu
 
 KWU_API const char* kwu_last_error() { return kwu::last_error(); }
+
+// Registers the int32 status word of the CURRENT device (0 = ok; kernels write an error code into it when a
+// bounded wait gives up). Entry points that take a status pointer use that one; the others use this.
+KWU_API void kwu_set_status_word(int* word) { kwu::set_device_status_word(word); }
 
 // Number of kernels this library has launched in this process (for launch accounting in benchmarks).
 KWU_API long long kwu_launch_count() { return kwu::launch_total(); }

@@ -22,22 +22,30 @@ class PackedBatch:
     tokens: torch.Tensor
     labels: torch.Tensor
     seq_info: SeqInfo
+    n_trained: int | None = None   # cached count of positions with a target
 
     @property
     def num_tokens(self) -> int:
         return int(self.tokens.numel())
 
     def trained_tokens(self) -> int:
-        """Host-side count of positions with a target (no device sync if the batch is on the host)."""
-        return int((self.labels != IGNORE).sum())
+        """Count of positions with a target. Counted once (on the host when the labels are there) and
+        carried along by ``to`` / ``pin_memory``, so a batch that already lives on the device costs a
+        device synchronisation only the first time it is asked."""
+        if self.n_trained is None:
+            self.n_trained = int((self.labels != IGNORE).sum())
+        return self.n_trained
 
     def pin_memory(self) -> "PackedBatch":
-        return PackedBatch(self.tokens.pin_memory(), self.labels.pin_memory(), self.seq_info.pin_memory())
+        return PackedBatch(self.tokens.pin_memory(), self.labels.pin_memory(), self.seq_info.pin_memory(),
+                           self.n_trained)
 
     def to(self, device, non_blocking: bool = True) -> "PackedBatch":
+        if self.n_trained is None and not self.labels.is_cuda:
+            self.trained_tokens()
         return PackedBatch(self.tokens.to(device, non_blocking=non_blocking),
                            self.labels.to(device, non_blocking=non_blocking),
-                           self.seq_info.to(device, non_blocking=non_blocking))
+                           self.seq_info.to(device, non_blocking=non_blocking), self.n_trained)
 
     def nbytes(self) -> int:
         n = self.tokens.numel() * self.tokens.element_size() + self.labels.numel() * self.labels.element_size()

@@ -33,10 +33,17 @@ _scratch: dict[tuple, torch.Tensor] = {}
 
 
 def _scratch_buffer(key: str, shape: tuple[int, ...], dtype, device) -> torch.Tensor:
-    """Reused scratch, grown on demand (one per device and purpose)."""
+    """Reused scratch, grown on demand (one per device and purpose).
+
+    While a CUDA graph is being captured the buffer is NOT taken from the shared cache: a graph replays with
+    the addresses it was captured with, and the cached buffer is replaced when a larger request arrives
+    later, which would leave the graph writing into freed memory. An allocation made during capture comes
+    from the graph's private pool and lives as long as the graph does."""
     n = 1
     for s in shape:
         n *= s
+    if torch.device(device).type == "cuda" and torch.cuda.is_current_stream_capturing():
+        return torch.empty(n, dtype=dtype, device=device).view(*shape)
     k = (key, str(device), dtype)
     buf = _scratch.get(k)
     if buf is None or buf.numel() < n:

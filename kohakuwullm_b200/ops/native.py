@@ -93,7 +93,50 @@ def status_word() -> torch.Tensor:
     dev = torch.cuda.current_device()
     if dev not in _status:
         _status[dev] = torch.zeros(1, dtype=torch.int32, device=f"cuda:{dev}")
+        handle = lib()
+        if hasattr(handle, "kwu_set_status_word"):
+            with torch.cuda.device(dev):
+                handle.kwu_set_status_word(ctypes.c_void_p(_status[dev].data_ptr()))
     return _status[dev]
+
+
+class _StatusMirror:
+    """Pinned host copy of one device's status word, refreshed by asynchronous copies."""
+
+    def __init__(self, dev: int):
+        self.host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.event = torch.cuda.Event()
+        self.pending = False
+
+
+_mirrors: dict[int, _StatusMirror] = {}
+
+
+def poll_status() -> None:
+    """Sync-free status check for training loops: raises if a kernel of an EARLIER step reported an error.
+
+    Each call reads the pinned host mirror if the copy started by the previous call has completed, then
+    starts the next 4-byte device->host copy on the current stream. An error is therefore seen one or two
+    calls after the failing kernel ran, without the host ever waiting for the device."""
+    if not torch.cuda.is_available():
+        return
+    dev = torch.cuda.current_device()
+    word = _status.get(dev)
+    if word is None:
+        return
+    mirror = _mirrors.get(dev)
+    if mirror is None:
+        mirror = _mirrors[dev] = _StatusMirror(dev)
+    if mirror.pending and mirror.event.query():
+        mirror.pending = False
+        code = int(mirror.host[0])
+        if code:
+            word.zero_()
+            raise NativeError(f"device {dev}: kernel reported '{ERROR_NAMES.get(code, code)}'")
+    if not mirror.pending:
+        mirror.host.copy_(word, non_blocking=True)
+        mirror.event.record()
+        mirror.pending = True
 
 
 def check_status(sync: bool = True) -> None:

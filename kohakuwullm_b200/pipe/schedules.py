@@ -4,9 +4,9 @@ Two executors share one interface (``step(first_stage_inputs, n_micro) -> list o
 
 * ``NativeSchedule`` — GPipe and 1F1B written directly on ``torch.distributed`` point-to-point ops.
   Activations and their gradients cross a stage boundary as fixed-shape tensors (``boundary`` example
-  tensors give shape and dtype); a send towards one neighbour and the matching receive from it are
-  issued as ONE batched group so neither side can block the other, and on CUDA the transfers run on
-  NCCL's own stream, overlapping the next micro-batch's compute.
+  tensors give shape and dtype). Every transfer is its own asynchronous group, issued by both ends of a
+  link in the same order; sends are never waited for before the next compute, and receives are posted one
+  micro-batch ahead, so on CUDA the transfers run on NCCL's own stream under the compute.
 * ``TorchSchedule`` — adapter over ``torch.distributed.pipelining`` for the multi-chunk schedules
   (interleaved 1F1B, looped BFS, interleaved zero-bubble, ZB-V, DualPipe-V), always built with
   ``scale_grads=False`` because the loss is already normalised by the step's token count.
@@ -58,23 +58,40 @@ class NativeSchedule:
     def _empty(self, spec):
         return [torch.empty(shape, dtype=dtype, device=dev) for shape, dtype, dev, _ in spec]
 
-    def _exchange(self, send_to, send_tensors, recv_from, recv_grad: bool):
-        """One batched group: optional send towards ``send_to`` and optional receive from ``recv_from``."""
-        ops, recv_bufs = [], None
-        if send_tensors is not None:
-            for t in send_tensors:
-                ops.append(dist.P2POp(dist.isend, t.contiguous(), send_to, self.group))
-        if recv_from is not None:
-            # activations arrive from the previous stage, gradients from the next one
-            recv_bufs = self._empty(self.boundary if recv_grad else self.out_boundary)
-            for t in recv_bufs:
-                ops.append(dist.P2POp(dist.irecv, t, recv_from, self.group))
-        if ops:
-            for w in dist.batch_isend_irecv(ops):
+    def _post_send(self, to: int, tensors) -> None:
+        """Start sending ``tensors`` to rank ``to`` and return at once. Nothing waits for a send before the
+        next compute: the work handles (and the tensors, which must stay alive until the transfer is done)
+        are kept until the end of the step."""
+        if not tensors:
+            return
+        bufs = [t.contiguous() for t in tensors]
+        works = dist.batch_isend_irecv([dist.P2POp(dist.isend, t, to, self.group) for t in bufs])
+        self._pending.append((works, bufs))
+
+    def _post_recv(self, frm: int, activations: bool):
+        """Start receiving one boundary (activations from the previous stage, or gradients from the next) and
+        return a handle; ``_take`` waits for it. Posting the receive of the NEXT micro-batch before computing
+        the current one lets the transfer run under that compute."""
+        bufs = self._empty(self.boundary if activations else self.out_boundary)
+        works = dist.batch_isend_irecv([dist.P2POp(dist.irecv, t, frm, self.group) for t in bufs])
+        return bufs, works, activations
+
+    @staticmethod
+    def _take(handle):
+        if handle is None:
+            return None
+        bufs, works, activations = handle
+        for w in works:
+            w.wait()   # NCCL: the compute stream waits for the transfer; the host does not block
+        if activations:
+            bufs = [t.requires_grad_() if t.is_floating_point() else t for t in bufs]
+        return bufs
+
+    def _drain_sends(self) -> None:
+        for works, _bufs in self._pending:
+            for w in works:
                 w.wait()
-        if recv_bufs is not None and recv_grad:
-            recv_bufs = [t.requires_grad_() if t.is_floating_point() else t for t in recv_bufs]
-        return recv_bufs
+        self._pending.clear()
 
     # ------------------------------------------------------------------ compute
     def _forward(self, mb: int, inputs, stash, losses):
@@ -101,38 +118,53 @@ class NativeSchedule:
 
     # ------------------------------------------------------------------ schedules
     def step(self, n_micro: int | None = None) -> list[torch.Tensor]:
+        """One optimizer step's worth of micro-batches.
+
+        Order of the transfers on the link between two neighbouring stages (both sides issue them in this
+        order, each as its own asynchronous group, so the two ends always agree and neither can block the
+        other): the warm-up activations a_0 .. a_w, then alternately a_{w+1+i}, g_i for every steady
+        iteration i, then the remaining gradients. Receives of activations are posted one micro-batch
+        ahead (before the compute they overlap), receives of cool-down gradients likewise; the gradient of
+        a steady iteration can only be asked for after that iteration's activation went out."""
         M = n_micro or self.M
         stash: dict[int, tuple] = {}
         losses: list[torch.Tensor] = []
         warm = M if self.kind == "gpipe" else min(self.S - self.s - 1, M)
         steady = M - warm
+        first, last = self.first, self.last
         f = b = 0
-        inputs = None if self.first else self._exchange(None, None, self.prev, True)
-        # warm-up forwards
-        for _ in range(warm):
-            out = self._forward(f, inputs, stash, losses)
-            f += 1
-            more_f = f < M
-            inputs = self._exchange(None if self.last else self.next, out,
-                                    self.prev if (more_f and not self.first) else None, True)
-        # steady state: one forward, one backward
-        grads = None
-        for i in range(steady):
-            out = self._forward(f, inputs, stash, losses)
-            f += 1
-            grads = self._exchange(None if self.last else self.next, out,
-                                   None if self.last else self.next, False)
-            gin = self._backward(b, grads, stash)
-            b += 1
-            more_f = f < M
-            inputs = self._exchange(None if self.first else self.prev, gin,
-                                    self.prev if (more_f and not self.first) else None, True)
-        # cool-down backwards
-        while b < M:
-            grads = None if self.last else self._exchange(None, None, self.next, False)
-            gin = self._backward(b, grads, stash)
-            b += 1
-            self._exchange(None if self.first else self.prev, gin, None, False)
+        act = None if first else self._post_recv(self.prev, True)
+        try:
+            for _ in range(warm):
+                inputs = self._take(act)
+                act = self._post_recv(self.prev, True) if (not first and f + 1 < M) else None
+                out = self._forward(f, inputs, stash, losses)
+                f += 1
+                if not last:
+                    self._post_send(self.next, out)
+            for _ in range(steady):
+                inputs = self._take(act)
+                act = self._post_recv(self.prev, True) if (not first and f + 1 < M) else None
+                out = self._forward(f, inputs, stash, losses)
+                f += 1
+                grads = None
+                if not last:
+                    self._post_send(self.next, out)
+                    grads = self._take(self._post_recv(self.next, False))
+                gin = self._backward(b, grads, stash)
+                b += 1
+                if not first:
+                    self._post_send(self.prev, gin)
+            grad = self._post_recv(self.next, False) if (not last and b < M) else None
+            while b < M:
+                grads = self._take(grad)
+                grad = self._post_recv(self.next, False) if (not last and b + 1 < M) else None
+                gin = self._backward(b, grads, stash)
+                b += 1
+                if not first:
+                    self._post_send(self.prev, gin)
+        finally:
+            self._drain_sends()
         return losses
 
 

@@ -63,9 +63,7 @@ class PipelineLoop:
         unless ``global_clip`` is off (then it is stage-local, as in the reference)."""
         grads = self._grad_tensors()
         dev = self.module.device
-        sq = torch.zeros(1, dtype=torch.float32, device=dev)
-        for g in grads:
-            sq += g.float().pow(2).sum()
+        sq = self._sumsq(grads, dev)
         if self.global_clip and self.world > 1:
             dist.all_reduce(sq, group=self.group)
         norm = sq.sqrt() * inv_tokens
@@ -74,6 +72,30 @@ class PipelineLoop:
             coef = coef * torch.clamp(self.max_grad_norm / (norm + 1e-6), max=1.0)
         self.last_grad_norm = norm
         return coef
+
+    def _sumsq(self, grads, dev) -> torch.Tensor:
+        """Sum of squares of all gradient tensors as a (1,) fp32 device tensor. Flat fp32 gradient buffers on a
+        GPU go through the deterministic two-level reduction kernel (one launch per buffer); anything else is
+        summed tensor by tensor."""
+        sq = torch.zeros(1, dtype=torch.float32, device=dev)
+        from kohakuwullm_b200.ops import native
+
+        fast = (torch.device(dev).type == "cuda" and native.available()
+                and all(g.dtype == torch.float32 and g.is_contiguous() for g in grads))
+        if fast and grads:
+            import ctypes
+
+            L = native.require()
+            if getattr(self, "_sq_partial", None) is None:
+                self._sq_partial = torch.empty(L.kwu_sumsq_blocks(), dtype=torch.float32, device=dev)
+            for i, g in enumerate(grads):
+                rc = L.kwu_sumsq_flat(native.ptr(g), ctypes.c_longlong(g.numel()), native.ptr(self._sq_partial),
+                                      native.ptr(sq), ctypes.c_int(int(i > 0)), native.stream_ptr())
+                native.check(rc, "sumsq_flat")
+            return sq
+        for g in grads:
+            sq += g.float().pow(2).sum()
+        return sq
 
     def broadcast_loss(self, loss: torch.Tensor | None) -> torch.Tensor:
         dev = self.module.device
@@ -85,6 +107,10 @@ class PipelineLoop:
 
     def step(self, batch: Any) -> StepOutput:
         module, cb = self.module, self.callbacks
+        if torch.device(module.device).type == "cuda":
+            from kohakuwullm_b200.ops import native
+
+            native.poll_status()   # an error a kernel of an earlier step reported (no host synchronisation)
         cb.on_train_batch_start(self, batch, self.global_step)
         self.optimizer.zero_grad(set_to_none=True)
         module.set_batch(batch)

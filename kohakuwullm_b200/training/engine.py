@@ -38,8 +38,11 @@ class GraphedMicroStep:
     A 546M-parameter step is several thousand small launches per micro-batch; replaying them from a
     graph removes the host from the critical path. Shapes are fixed by ``(tokens, max_docs)``:
     ``cu_seqlens`` is padded with zero-length documents up to ``max_docs`` (they produce no attention
-    tiles), so packs with any number of documents replay the same graph. Inputs are copied straight
-    from (pinned) host memory into the graph's static buffers.
+    tiles), so packs with any number of documents replay the same graph. A micro-batch with FEWER tokens
+    than the graph holds is completed by one fully masked filler document (label -100 everywhere, its
+    own positions), the same padding ``collate_packed(pad_to_multiple=...)`` produces, so that
+    document-aligned splits of varying size share a few graphs instead of capturing one each. Inputs are
+    copied straight from (pinned) host memory into the graph's static buffers.
     """
 
     def __init__(self, engine: "TrainEngine", tokens: int, max_docs: int):
@@ -48,6 +51,7 @@ class GraphedMicroStep:
         self.tok = torch.zeros(tokens, dtype=torch.long, device=dev)
         self.lab = torch.full((tokens,), -100, dtype=torch.long, device=dev)
         self.pos = torch.zeros(tokens, dtype=torch.long, device=dev)
+        self._arange = torch.arange(tokens, dtype=torch.long, device=dev)
         self.cu = torch.full((max_docs + 1,), tokens, dtype=torch.int32, device=dev)
         self.cu[0] = 0
         self.ce = torch.zeros((), dtype=torch.float32, device=dev)
@@ -62,14 +66,20 @@ class GraphedMicroStep:
 
     def load(self, mb: PackedBatch) -> None:
         n_docs = mb.seq_info.num_seqs
-        if mb.num_tokens != self.tokens or n_docs > self.max_docs:
+        T = mb.num_tokens
+        pad = self.tokens - T
+        if pad < 0 or n_docs + (1 if pad else 0) > self.max_docs:
             raise ValueError("micro-batch does not fit this graph")
-        self.tok.copy_(mb.tokens, non_blocking=True)
-        self.lab.copy_(mb.labels, non_blocking=True)
-        self.pos.copy_(mb.seq_info.position_ids, non_blocking=True)
+        self.tok[:T].copy_(mb.tokens, non_blocking=True)
+        self.lab[:T].copy_(mb.labels, non_blocking=True)
+        self.pos[:T].copy_(mb.seq_info.position_ids, non_blocking=True)
         self.cu[: n_docs + 1].copy_(mb.seq_info.cu_seqlens, non_blocking=True)
         if n_docs < self.max_docs:
+            # the filler document [T, tokens) followed by empty documents
             self.cu[n_docs + 1:].fill_(self.tokens)
+        if pad:
+            self.lab[T:].fill_(-100)
+            self.pos[T:].copy_(self._arange[:pad])
 
     def _run(self) -> None:
         eng = self.engine
@@ -115,10 +125,14 @@ class TrainEngine:
                  param_dtype: torch.dtype | None = None, group=None, grad_sync: str = "nccl",
                  device: torch.device | str | None = None, lr_schedule=None,
                  cuda_graphs: bool | None = None, graph_max_docs: int | None = None,
+                 graph_token_bucket: int = 512, graph_cache_size: int = 8,
                  expert_parallel: bool | str = False, ep_capacity_factor: float = 2.0):
         """``expert_parallel``: split every MoE layer's experts over the ranks of ``group`` (tokens travel
         to the owning rank over peer memory); all other parameters stay data-parallel replicas.
-        ``"reference"`` keeps the sharding but moves tokens with plain collectives (test oracle)."""
+        ``"reference"`` keeps the sharding but moves tokens with plain collectives (test oracle).
+        ``graph_token_bucket``: captured micro-step graphs hold a multiple of this many tokens; a micro-batch
+        is padded up to the next multiple with a masked filler document. ``graph_cache_size``: at most this
+        many graphs are kept (least recently used goes first); each pins one forward + backward pool."""
         self.model = model
         if device is not None:
             model.to(device)
@@ -162,7 +176,9 @@ class TrainEngine:
         self.last_router_stats: dict = {}
         self.cuda_graphs = (self.device.type == "cuda" and native.available()) if cuda_graphs is None else cuda_graphs
         self.graph_max_docs = graph_max_docs
-        self._graphs: dict[tuple[int, int], GraphedMicroStep] = {}
+        self.graph_token_bucket = max(int(graph_token_bucket), 1)
+        self.graph_cache_size = max(int(graph_cache_size), 1)
+        self._graphs: dict[tuple[int, int], GraphedMicroStep] = {}   # insertion order = recency (LRU first)
         self.replayed_native_launches = 0
         self._router_scale = torch.ones(1, dtype=torch.float32, device=dev)
 
@@ -170,19 +186,23 @@ class TrainEngine:
         """Graph matching this micro-batch's token count (captured on first use), or None."""
         if not self.cuda_graphs:
             return None
-        T = mb.num_tokens
+        b = self.graph_token_bucket
+        T = (mb.num_tokens + b - 1) // b * b
         max_docs = self.graph_max_docs or max(8, T // 32)
-        if mb.seq_info.num_seqs > max_docs:
+        if mb.seq_info.num_seqs + (1 if T != mb.num_tokens else 0) > max_docs:
             return None
         key = (T, max_docs)
-        g = self._graphs.get(key)
+        g = self._graphs.pop(key, None)
         if g is None:
+            while len(self._graphs) >= self.graph_cache_size:
+                old = self._graphs.pop(next(iter(self._graphs)))
+                old.graph = None   # releases the graph and its private memory pool
             g = GraphedMicroStep(self, T, max_docs)
             g.load(mb)
             router_state = self._snapshot_router()
             g.capture()
             self._restore_router(router_state)
-            self._graphs[key] = g
+        self._graphs[key] = g      # most recently used last
         return g
 
     def native_launch_total(self) -> int:
@@ -244,6 +264,10 @@ class TrainEngine:
         model = self.model
         model.train()
         dev = self.device
+        if dev.type == "cuda":
+            # a kernel of an earlier step whose bounded wait ran out (a peer that never arrived, an expert
+            # buffer that overflowed) surfaces here as an exception, without a host synchronisation
+            native.poll_status()
         local_tokens = sum(mb.trained_tokens() for mb in micro_batches)
         tok = torch.tensor([float(local_tokens)], dtype=torch.float32).to(dev, non_blocking=True)
         self.sync.all_reduce_scalar(tok)

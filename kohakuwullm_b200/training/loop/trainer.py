@@ -21,6 +21,7 @@ import torch.distributed as dist
 from kohakuwullm_b200.data.packing import PackedBatch, split_packed
 from kohakuwullm_b200.models import LMBackbone, get_preset
 from kohakuwullm_b200.models.flops import FlopCounter
+from kohakuwullm_b200.ops import native
 from kohakuwullm_b200.pipe import checkpoint as ckpt
 from kohakuwullm_b200.pipe.hooks import CallbackList
 from kohakuwullm_b200.training.engine import TrainEngine
@@ -104,6 +105,8 @@ class LMTrainer:
                 self.global_step += 1
                 if self.global_step % self.log_interval == 0:
                     loss = float(out["loss"])      # the only host read, on the logging interval
+                    if self.device.type == "cuda":
+                        native.check_status()      # the device is idle here anyway: read the status word itself
                     out["loss_host"] = loss
                     if math.isfinite(loss):
                         self.loss_ema = loss if self.loss_ema is None else self.ema_beta * self.loss_ema + (1 - self.ema_beta) * loss
@@ -145,6 +148,8 @@ class LMTrainer:
 
     # ------------------------------------------------------------------ checkpoints
     def save_checkpoint(self, path: str) -> None:
+        if self.device.type == "cuda":
+            native.check_status()   # never write a checkpoint of a run whose kernels reported an error
         loader_state = self.loader.state_dict() if hasattr(self.loader, "state_dict") else None
         state = resume.pack_state(self.snapshot(sync=True), self.loss_ema, loader_state, self.global_step)
         extra = {resume.RESUME_KEY: state, "callbacks": self.callbacks.state_dict()}
