@@ -738,40 +738,49 @@ qknorm_rope_bwd_qk_kernel(const __nv_bfloat16* __restrict__ src, int src_ld, con
                           const float* __restrict__ wq_p, const float* __restrict__ wk_p,
                           float* __restrict__ dwq_out, float* __restrict__ dwk_out,
                           const float* __restrict__ cos_t, const float* __restrict__ sin_t, int tokens, int Hq,
-                          int Hkv, int rot_half, float eps, int do_norm, const MxOut mx) {
-  __shared__ float s_dw[128];
-  if (threadIdx.x < 128) s_dw[threadIdx.x] = 0.f;
+                          int Hkv, int rot_half, float eps, int do_norm, const MxOut mx, int q_blocks) {
+  // Blocks [0, q_blocks) take the query heads, the rest the key heads (and, with emission, the value heads,
+  // which are only read back and quantised): a block then needs ONE weight vector and ONE gradient
+  // accumulator in registers (both roles in every thread cost 99 registers and a third of the occupancy).
+  __shared__ float s_dw[64];
+  if (threadIdx.x < 64) s_dw[threadIdx.x] = 0.f;
   __syncthreads();
+  const bool q_role = static_cast<int>(blockIdx.x) < q_blocks;
+  const int role_block = q_role ? blockIdx.x : blockIdx.x - q_blocks;
+  const int role_blocks = q_role ? q_blocks : gridDim.x - q_blocks;
   const int lane = threadIdx.x & 31, sub = lane & 7, slot = lane >> 3;
-  const int HQK = Hq + Hkv;
-  const int HT = mx.q ? Hq + 2 * Hkv : HQK;   // with emission the v heads are visited too (read-only)
-  const long total = static_cast<long>(tokens) * HT;
+  const int H = q_role ? Hq : (mx.q ? 2 * Hkv : Hkv);   // heads this role walks per token
+  const int h_base = q_role ? 0 : Hq;                   // first head of the role inside a qkv row
+  const int H_norm = q_role ? Hq : Hkv;                 // heads of the role that are normalised / rotated
+  const __nv_bfloat16* gsrc = q_role ? dq : dk;
+  const float* w_p = q_role ? wq_p : wk_p;
+  float* dw_out = q_role ? dwq_out : dwk_out;
+  const long total = static_cast<long>(tokens) * H;
   const int wpb = blockDim.x >> 5;
-  float wq[8], wk[8], dwq[8], dwk[8];
+  float w[8], dw[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    wq[i] = (do_norm && wq_p) ? wq_p[8 * sub + i] : 1.f;
-    wk[i] = (do_norm && wk_p) ? wk_p[8 * sub + i] : 1.f;
-    dwq[i] = dwk[i] = 0.f;
+    w[i] = (do_norm && w_p) ? w_p[8 * sub + i] : 1.f;
+    dw[i] = 0.f;
   }
   // uniform trip count per warp: the emission shuffles inside the loop
-  for (long r0 = (static_cast<long>(blockIdx.x) * wpb + (threadIdx.x >> 5)) * 4; r0 < total;
-       r0 += static_cast<long>(gridDim.x) * wpb * 4) {
+  for (long r0 = (static_cast<long>(role_block) * wpb + (threadIdx.x >> 5)) * 4; r0 < total;
+       r0 += static_cast<long>(role_blocks) * wpb * 4) {
     const long r = r0 + slot;
     const bool live = r < total;
-    const int t = live ? static_cast<int>(r / HT) : 0;
-    const int h = live ? static_cast<int>(r % HT) : 0;
-    const bool is_v = h >= HQK, is_k = !is_v && h >= Hq;
+    const int t = live ? static_cast<int>(r / H) : 0;
+    const int hl = live ? static_cast<int>(r % H) : 0;
+    const bool is_v = hl >= H_norm;
+    const int h = h_base + hl;
     uint4 o = make_uint4(0, 0, 0, 0);
-    if (is_v) {
-      if (live) o = *reinterpret_cast<const uint4*>(dsrc + static_cast<size_t>(t) * dsrc_ld + h * 64 + 8 * sub);
-    }
     uint4 graw = make_uint4(0, 0, 0, 0), xraw = make_uint4(0, 0, 0, 0);
-    if (live && !is_v) {
-      const __nv_bfloat16* g = is_k ? dk + (static_cast<size_t>(t) * Hkv + (h - Hq)) * 64
-                                    : dq + (static_cast<size_t>(t) * Hq + h) * 64;
-      graw = *reinterpret_cast<const uint4*>(g + 8 * sub);
-      if (do_norm) xraw = *reinterpret_cast<const uint4*>(src + static_cast<size_t>(t) * src_ld + h * 64 + 8 * sub);
+    if (live) {
+      if (is_v) {
+        o = *reinterpret_cast<const uint4*>(dsrc + static_cast<size_t>(t) * dsrc_ld + h * 64 + 8 * sub);
+      } else {
+        graw = *reinterpret_cast<const uint4*>(gsrc + (static_cast<size_t>(t) * H_norm + hl) * 64 + 8 * sub);
+        if (do_norm) xraw = *reinterpret_cast<const uint4*>(src + static_cast<size_t>(t) * src_ld + h * 64 + 8 * sub);
+      }
     }
     float d[8];
     unpack8(graw, d);
@@ -802,10 +811,8 @@ qknorm_rope_bwd_qk_kernel(const __nv_bfloat16* __restrict__ src, int src_ld, con
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         x[i] *= rstd;
-        const float gx = d[i] * x[i];          // dead and v rows carry zeros
-        dwq[i] += is_k ? 0.f : gx;
-        dwk[i] += is_k ? gx : 0.f;
-        d[i] *= is_k ? wk[i] : wq[i];
+        dw[i] += d[i] * x[i];         // dead and value rows carry zeros
+        d[i] *= w[i];
         dot += d[i] * x[i];
       }
       dot = row8_sum(dot) * (1.f / 64.f);
@@ -823,25 +830,16 @@ qknorm_rope_bwd_qk_kernel(const __nv_bfloat16* __restrict__ src, int src_ld, con
       mx_emit8(fr, live, t, h * 64 + 8 * sub, mx.q, mx.ldq, mx.sf, mx.n_kchunks);
     }
   }
-  if (do_norm && (dwq_out || dwk_out)) {
+  if (do_norm && dw_out) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      float a = dwq[i], b = dwk[i];
+      float a = dw[i];
       a += __shfl_xor_sync(0xffffffffu, a, 8);
       a += __shfl_xor_sync(0xffffffffu, a, 16);
-      b += __shfl_xor_sync(0xffffffffu, b, 8);
-      b += __shfl_xor_sync(0xffffffffu, b, 16);
-      if (slot == 0) {
-        atomicAdd(&s_dw[8 * sub + i], a);
-        atomicAdd(&s_dw[64 + 8 * sub + i], b);
-      }
+      if (slot == 0) atomicAdd(&s_dw[8 * sub + i], a);
     }
     __syncthreads();
-    if (threadIdx.x < 64) {
-      if (dwq_out) atomicAdd(&dwq_out[threadIdx.x], s_dw[threadIdx.x]);
-    } else if (threadIdx.x < 128) {
-      if (dwk_out) atomicAdd(&dwk_out[threadIdx.x - 64], s_dw[threadIdx.x]);
-    }
+    if (threadIdx.x < 64) atomicAdd(&dw_out[threadIdx.x], s_dw[threadIdx.x]);
   }
 }
 
@@ -1162,12 +1160,16 @@ KWU_API int kwu_qknorm_rope_bwd_qk(const void* src, int src_ld, const void* dq, 
     set_last_error("qknorm_rope_bwd_qk: the fp8 copy needs tokens and columns in multiples of 128");
     return 7;
   }
-  const int heads = q8 ? Hq + 2 * Hkv : Hq + Hkv;
-  const int grid = grid_for(static_cast<long>(tokens) * heads, 32, 148 * 4);
-  qknorm_rope_bwd_qk_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  const int kv_heads = q8 ? 2 * Hkv : Hkv;
+  const int grid = grid_for(static_cast<long>(tokens) * (Hq + kv_heads), 32, 148 * 8);
+  // blocks are dealt to the two roles in proportion to their rows (at least one each)
+  int q_blocks = static_cast<int>(static_cast<long>(grid) * Hq / (Hq + kv_heads));
+  if (q_blocks < 1) q_blocks = 1;
+  const int total_blocks = q_blocks + (grid - q_blocks < 1 ? 1 : grid - q_blocks);
+  qknorm_rope_bwd_qk_kernel<<<total_blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       (const __nv_bfloat16*)src, src_ld, (const __nv_bfloat16*)dq, (const __nv_bfloat16*)dk, (__nv_bfloat16*)dsrc,
       dsrc_ld, wq, wk, dwq, dwk, cos_t, sin_t, tokens, Hq, Hkv, rot_half, eps, do_norm,
-      make_mx(q8, ldq, sf, cols)); kwu::count_launch();
+      make_mx(q8, ldq, sf, cols), q_blocks); kwu::count_launch();
   return check_launch("qknorm_rope_bwd_qk");
 }
 

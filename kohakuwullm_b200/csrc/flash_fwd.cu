@@ -14,6 +14,7 @@
 // Replaces src/kohakuwullm/kernels/attention/flash_attn_fwd.py:35-154 and the vendor FA2 call at
 // src/kohakuwullm/models/components/attention.py:170-188 of the reference.
 #include "common.cuh"
+#include "mx_quant.cuh"
 
 namespace kwu {
 
@@ -35,6 +36,10 @@ struct FlashFwdParams {
   const float* sink_lse;  // (Hq) or null
   float scale_log2;       // softmax scale * log2(e)
   int* status;
+  // optional MXFP8 copy of `out` seen as a (T, Hq * 64) matrix: e4m3 bytes + UE8M0 scale chunks (the layout of
+  // mxfp8.cu), for an MXFP8 output projection. Each epilogue thread holds exactly one 32-element block.
+  uint8_t* q8;
+  uint8_t* sf;
 };
 
 // Tile lists for packed batches: for every document, ceil(len/tile) entries (q0, doc_start, doc_end, valid),
@@ -413,6 +418,32 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             w.z = pack_bf16(__uint_as_float(o[8 * v + 4]) * inv, __uint_as_float(o[8 * v + 5]) * inv);
             w.w = pack_bf16(__uint_as_float(o[8 * v + 6]) * inv, __uint_as_float(o[8 * v + 7]) * inv);
             dst[v] = w;
+            // keep the rounded values (what a quantise pass over the stored tensor would read)
+            o[8 * v + 0] = w.x << 16; o[8 * v + 1] = w.x & 0xffff0000u;
+            o[8 * v + 2] = w.y << 16; o[8 * v + 3] = w.y & 0xffff0000u;
+            o[8 * v + 4] = w.z << 16; o[8 * v + 5] = w.z & 0xffff0000u;
+            o[8 * v + 6] = w.w << 16; o[8 * v + 7] = w.w & 0xffff0000u;
+          }
+          if (p.q8) {
+            float amax = 0.f;
+#pragma unroll
+            for (int e = 0; e < 32; ++e) amax = fmaxf(amax, fabsf(__uint_as_float(o[e])));
+            const uint32_t e8 = ue8m0_from_amax(amax);
+            const float qs = inv_scale_from_ue8m0(e8);
+            uint32_t b[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(
+                  make_float2(__uint_as_float(o[4 * j]) * qs, __uint_as_float(o[4 * j + 1]) * qs), __NV_SATFINITE, __NV_E4M3);
+              const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(
+                  make_float2(__uint_as_float(o[4 * j + 2]) * qs, __uint_as_float(o[4 * j + 3]) * qs), __NV_SATFINITE, __NV_E4M3);
+              b[j] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+            }
+            const int ncols = p.Hq * FA_D;
+            uint4* qd = reinterpret_cast<uint4*>(p.q8 + static_cast<size_t>(qi) * ncols + h * FA_D + half * 32);
+            qd[0] = make_uint4(b[0], b[1], b[2], b[3]);
+            qd[1] = make_uint4(b[4], b[5], b[6], b[7]);
+            p.sf[sf_offset(qi, h * 2 + half, ncols >> 7)] = static_cast<uint8_t>(e8);
           }
           if (half == 0) p.lse[static_cast<size_t>(h) * p.T + qi] = lse;
         }
@@ -455,10 +486,15 @@ KWU_API int kwu_attn_plan(const int* cu_seqlens, int ndocs, int tile, void* plan
   return 0;
 }
 
-KWU_API int kwu_flash_fwd(const void* q, int q_ld, const void* k, int k_ld, const void* v, int v_ld,
+static int flash_fwd_impl(const void* q, int q_ld, const void* k, int k_ld, const void* v, int v_ld,
                           void* out, float* lse, const void* plan, int n_tiles, int T, int Hq, int Hkv,
-                          int window, const float* sink_lse, float scale, void* stream, int* status) {
+                          int window, const float* sink_lse, float scale, void* q8, void* sf, void* stream,
+                          int* status) {
   if (T <= 0 || n_tiles <= 0) return 0;
+  if (q8 && (T % 128 || (Hq * FA_D) % 128 || !sf)) {
+    set_last_error("flash_fwd: the fp8 copy needs tokens and Hq * 64 in multiples of 128");
+    return 7;
+  }
   if (Hq % Hkv) { set_last_error("flash_fwd: Hq must be a multiple of Hkv"); return 7; }
   CUtensorMap tmQ, tmK, tmV;
   int rc;
@@ -480,6 +516,8 @@ KWU_API int kwu_flash_fwd(const void* q, int q_ld, const void* k, int k_ld, cons
   p.sink_lse = sink_lse;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
+  p.q8 = reinterpret_cast<uint8_t*>(q8);
+  p.sf = reinterpret_cast<uint8_t*>(sf);
   int sms = 0, dev = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -489,4 +527,22 @@ KWU_API int kwu_flash_fwd(const void* q, int q_ld, const void* k, int k_ld, cons
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { set_last_error("flash_fwd launch: %s", cudaGetErrorString(e)); return 11; }
   return 0;
+}
+
+KWU_API int kwu_flash_fwd(const void* q, int q_ld, const void* k, int k_ld, const void* v, int v_ld,
+                          void* out, float* lse, const void* plan, int n_tiles, int T, int Hq, int Hkv,
+                          int window, const float* sink_lse, float scale, void* stream, int* status) {
+  return flash_fwd_impl(q, q_ld, k, k_ld, v, v_ld, out, lse, plan, n_tiles, T, Hq, Hkv, window, sink_lse, scale,
+                        nullptr, nullptr, stream, status);
+}
+
+// As kwu_flash_fwd, and also writes the MXFP8 copy of `out` viewed as (T, Hq * 64): q8 (T, Hq * 64) e4m3 bytes and
+// sf, kwu_mxfp8_sf_bytes(T, Hq * 64) bytes of scale chunks. T must be a multiple of 128 (every row of every
+// scale chunk is then written: each token belongs to exactly one query tile).
+KWU_API int kwu_flash_fwd_mx(const void* q, int q_ld, const void* k, int k_ld, const void* v, int v_ld,
+                             void* out, float* lse, const void* plan, int n_tiles, int T, int Hq, int Hkv,
+                             int window, const float* sink_lse, float scale, void* q8, void* sf, void* stream,
+                             int* status) {
+  return flash_fwd_impl(q, q_ld, k, k_ld, v, v_ld, out, lse, plan, n_tiles, T, Hq, Hkv, window, sink_lse, scale,
+                        q8, sf, stream, status);
 }

@@ -24,6 +24,20 @@ __device__ __forceinline__ size_t sf_offset(int row, int kblock, int n_kchunks) 
          (kblock & 3);
 }
 
+// Tile-local scale layout of a B operand (a weight) whose GEMM tiles are `bn` rows wide, bn in (128, 256]: the
+// rows [tile * bn, (tile + 1) * bn) of the matrix own TWO consecutive 512-byte chunks per 128-column k-chunk
+// (rows 0..127 of the tile in the first, rows 128..bn-1 in the second), ordered [tile][k_chunk][2]. A tile's
+// scales then always start at TMEM column 0 of the scale area, whatever bn is (with the plain 128-row chunks
+// a tile that starts inside a chunk needs a column offset, and odd offsets are not addressable).
+__device__ __forceinline__ size_t sf_offset_tiled(int row, int kblock, int n_kchunks, int bn) {
+  const int tile = row / bn, r = row - tile * bn;
+  return ((static_cast<size_t>(tile) * n_kchunks + (kblock >> 2)) * 2 + (r >> 7)) * 512 + (r & 31) * 16 +
+         ((r & 127) >> 5) * 4 + (kblock & 3);
+}
+__device__ __forceinline__ size_t sf_offset_any(int row, int kblock, int n_kchunks, int bn) {
+  return bn > 128 ? sf_offset_tiled(row, kblock, n_kchunks, bn) : sf_offset(row, kblock, n_kchunks);
+}
+
 // Eight consecutive values of one row held by this lane; the aligned group of four lanes holds one
 // 32-element block. Every lane of the warp must call this (the block maximum is formed with shuffles);
 // lanes whose `active` is false contribute zeros and store nothing. `col` is the first of the 8 columns.

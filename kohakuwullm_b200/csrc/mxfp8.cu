@@ -23,7 +23,7 @@ namespace kwu {
 // One thread = 8 consecutive elements; 4 threads = one 32-block; a warp covers 256 columns of a row.
 __global__ void __launch_bounds__(256)
 mxfp8_quantize_kernel(const __nv_bfloat16* __restrict__ x, int ldx, uint8_t* __restrict__ q, int ldq,
-                      uint8_t* __restrict__ sf, int M, int K, int M_pad) {
+                      uint8_t* __restrict__ sf, int M, int K, int M_pad, int sf_bn) {
   const int lane = threadIdx.x & 31;
   const int n_kchunks = K >> 7;
   const int segs = (K + 255) >> 8;  // 256-column segments per row
@@ -65,7 +65,9 @@ mxfp8_quantize_kernel(const __nv_bfloat16* __restrict__ x, int ldx, uint8_t* __r
         }
         *reinterpret_cast<uint2*>(q + static_cast<size_t>(row) * ldq + col) = make_uint2(lo, hi);
       }
-      if ((lane & 3) == 0) sf[sf_offset(row, col >> 5, n_kchunks)] = static_cast<uint8_t>(e8);
+      // tile-local layout (sf_bn > 128): only real rows are written, the buffer's padding keeps its neutral fill
+      if ((lane & 3) == 0 && (sf_bn <= 128 || row < M))
+        sf[sf_offset_any(row, col >> 5, n_kchunks, sf_bn)] = static_cast<uint8_t>(e8);
     }
   }
 }
@@ -75,7 +77,7 @@ mxfp8_quantize_kernel(const __nv_bfloat16* __restrict__ x, int ldx, uint8_t* __r
 __global__ void __launch_bounds__(64)
 mxfp8_quantize_t_kernel(const __nv_bfloat16* __restrict__ x, int ldx, uint8_t* __restrict__ qT, int ldq,
                         uint8_t* __restrict__ sf, int R, int C, int C_pad, long long x_batch, long long q_batch,
-                        long long sf_batch) {
+                        long long sf_batch, int sf_bn) {
   // blockIdx.z: independent matrices (the experts of a stacked weight) at fixed strides
   x += static_cast<size_t>(blockIdx.z) * x_batch;
   qT += static_cast<size_t>(blockIdx.z) * q_batch;
@@ -93,7 +95,7 @@ mxfp8_quantize_t_kernel(const __nv_bfloat16* __restrict__ x, int ldx, uint8_t* _
     amax = fmaxf(amax, fabsf(v[i]));
   }
   const uint32_t e8 = (c < C) ? ue8m0_from_amax(amax) : 127u;
-  if (r0 < R) sf[sf_offset(c, r0 >> 5, n_kchunks)] = static_cast<uint8_t>(e8);
+  if (r0 < R && (sf_bn <= 128 || c < C)) sf[sf_offset_any(c, r0 >> 5, n_kchunks, sf_bn)] = static_cast<uint8_t>(e8);
   if (c < C) {
     const float inv = inv_scale_from_ue8m0(e8);
     uint32_t w[8];
@@ -132,6 +134,7 @@ struct MxGemmParams {
   const int4* group_tiles;
   int group_n;
   int sfb_chunk_rows;  // number of 128-row scale chunks B has (chunk indices are clamped to it)
+  int sfb_tiled;       // B scales are in the tile-local layout of mx_quant.cuh (two chunks per BN-row tile)
   const long long* row_ptrs;  // bf16 output: row r is stored at this byte address (0: dropped) instead of C + r*ldc
   int* status;
 };
@@ -160,7 +163,9 @@ struct MxSmem {
   static constexpr int SFB_CHUNKS = (BN % 128 == 0) ? BN / 128 : BN / 128 + 1;
   static constexpr int SF_BYTES = 512 + SFB_CHUNKS * 512;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + (SF_BYTES + 1023) / 1024 * 1024;  // data + scale area
-  static constexpr int STAGES = (BN > 192) ? 4 : ((BN > 128) ? 5 : 6);
+  // as many stages as fit under 227 KB of shared memory (with 2 KB of barriers and alignment slack), at most 6
+  static constexpr int FIT = (227 * 1024 - 2048) / STAGE_BYTES;
+  static constexpr int STAGES = FIT > 6 ? 6 : FIT;
   static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 + 1024;
 };
 
@@ -249,6 +254,11 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           tma_load_2d(sa, &tmA, &full_bar[stage], kb * MX_BK, m0);
           tma_load_2d(sb, &tmB, &full_bar[stage], kb * MX_BK, b_row0);
           bulk_load_1d(ssf, p.sfa + (static_cast<size_t>(tm) * num_kb + kb) * 512, 512, &full_bar[stage]);
+          if (p.sfb_tiled) {
+            // the tile's own pair of chunks, contiguous in global memory
+            bulk_load_1d(ssf + 512, p.sfb + (static_cast<size_t>(n0 / BN) * num_kb + kb) * 1024, S::SFB_CHUNKS * 512,
+                         &full_bar[stage]);
+          } else
 #pragma unroll
           for (int c = 0; c < S::SFB_CHUNKS; ++c) {
             // rows past the end of B belong to masked output columns: any valid chunk will do for them
@@ -278,7 +288,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       int m0, n0, b_row0;
       if (!mx_decode_tile(p, tile, BN, m0, n0, b_row0)) continue;
       // the tile's first B row sits (b_row0 % 128) / 32 columns into its first scale chunk
-      const uint32_t sfb_off = static_cast<uint32_t>((b_row0 & 127) >> 5);
+      const uint32_t sfb_off = p.sfb_tiled ? 0u : static_cast<uint32_t>((b_row0 & 127) >> 5);
       const int as = it & 1;
       const uint32_t aphase = (it >> 1) & 1;
       ++it;
@@ -338,18 +348,27 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       const int row = m0 + quarter * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + as * BN;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = 0; c < (BN + 31) / 32; ++c) {
         uint32_t r[32];
-        tmem_ld_x32(t_row + c * 32, r);
+        // a tile width that is an odd multiple of 16 ends in a 16-column chunk
+        const int width = (BN % 32 != 0 && c == BN / 32) ? 16 : 32;
+        if (width == 32) {
+          tmem_ld_x32(t_row + c * 32, r);
+        } else {
+          tmem_ld_x16(t_row + c * 32, r);
+#pragma unroll
+          for (int j = 16; j < 32; ++j) r[j] = 0u;
+        }
         tmem_ld_wait();
         const int col0 = n0 + c * 32;
-        if (row < p.M && col0 < p.N) {
-          const bool full = (col0 + 32 <= p.N);
+        const int col_end = min(col0 + width, p.N);   // columns past the tile or the matrix are not stored
+        if (row < p.M && col0 < col_end) {
+          const bool full = (col_end - col0 == 32);
           if (p.out_fp32) {
             float* dst = reinterpret_cast<float*>(Cout) + static_cast<size_t>(row) * p.ldc + col0;
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-              if (full || col0 + j < p.N) {
+              if (full || col0 + j < col_end) {
                 float v = __uint_as_float(r[j]) * p.alpha;
                 if (p.accumulate) v += dst[j];
                 dst[j] = v;
@@ -362,25 +381,28 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
               if (!base) continue;
               dst = reinterpret_cast<__nv_bfloat16*>(base) + col0;
             }
-            if (full) {
+            const int nvec = (col_end - col0) >> 3;   // whole 8-column vectors (N and the tile edges are multiples of 8)
+            if ((col_end - col0) % 8 == 0) {
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
-                float f[8];
+                if (j < nvec) {
+                  float f[8];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[8 * j + e]) * p.alpha;
-                uint4* d4 = reinterpret_cast<uint4*>(dst) + j;
-                if (p.accumulate) {
-                  const uint4 o = *d4;
-                  const float2 o0 = unpack_bf16(o.x), o1 = unpack_bf16(o.y), o2 = unpack_bf16(o.z), o3 = unpack_bf16(o.w);
-                  f[0] += o0.x; f[1] += o0.y; f[2] += o1.x; f[3] += o1.y;
-                  f[4] += o2.x; f[5] += o2.y; f[6] += o3.x; f[7] += o3.y;
+                  for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[8 * j + e]) * p.alpha;
+                  uint4* d4 = reinterpret_cast<uint4*>(dst) + j;
+                  if (p.accumulate) {
+                    const uint4 o = *d4;
+                    const float2 o0 = unpack_bf16(o.x), o1 = unpack_bf16(o.y), o2 = unpack_bf16(o.z), o3 = unpack_bf16(o.w);
+                    f[0] += o0.x; f[1] += o0.y; f[2] += o1.x; f[3] += o1.y;
+                    f[4] += o2.x; f[5] += o2.y; f[6] += o3.x; f[7] += o3.y;
+                  }
+                  *d4 = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
                 }
-                *d4 = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
               }
             } else {
 #pragma unroll
               for (int j = 0; j < 32; ++j) {
-                if (col0 + j < p.N) {
+                if (col0 + j < col_end) {
                   float v = __uint_as_float(r[j]) * p.alpha;
                   if (p.accumulate) v += __bfloat162float(dst[j]);
                   dst[j] = __float2bfloat16(v);
@@ -409,7 +431,7 @@ template <int BN>
 static int launch_mx(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
                      const uint8_t* sfa, const uint8_t* sfb, int out_fp32, int accumulate, float alpha,
                      cudaStream_t stream, int* status, const int4* group_tiles = nullptr, int n_group_tiles = 0,
-                     int n_groups = 1, const long long* row_ptrs = nullptr) {
+                     int n_groups = 1, const long long* row_ptrs = nullptr, int sfb_tiled = 0) {
   using S = MxSmem<BN>;
   CUtensorMap tmA, tmB;
   int rc;
@@ -425,6 +447,7 @@ static int launch_mx(const void* A, const void* B, void* C, int M, int N, int K,
   p.group_n = N;
   p.sfb_chunk_rows = static_cast<int>((static_cast<long long>(N) * n_groups + 127) / 128);
   p.row_ptrs = out_fp32 ? nullptr : row_ptrs;
+  p.sfb_tiled = sfb_tiled;
   p.status = status;
   auto kern = gemm_mxfp8_kernel<BN>;
   static PerDeviceOnce attr_set;
@@ -444,14 +467,17 @@ static int launch_mx(const void* A, const void* B, void* C, int M, int N, int K,
   return 0;
 }
 
-// Tile width. Only 128: a tile of that width always starts on a scale-chunk boundary. A 160-wide variant
-// (fewer width x rounds units on 148 SMs for every training shape) was built with the scale address offset
-// by (first row % 128) / 32 TMEM columns; its first run ended in "misaligned address", so scale addresses
-// that are not chunk-aligned (and accumulators at column 160) are not used anywhere in this file.
-static int pick_bn_mx(int M, int N, int forced) {
-  (void)M; (void)N; (void)forced;
-  return 128;
-}
+// Tile width. 128 works with the plain scale layout (a tile always starts on a chunk boundary). Wider tiles
+// (multiples of 16 up to 240: two accumulators plus the scale columns must fit in 512 TMEM columns) need the B
+// operand's scales in the tile-local layout, which only an operand quantised for that width has (weights).
+// Why wider: per 128-deep k-block a 128 x BN tile moves 16 KB + BN * 128 B through shared memory for
+// 128 * BN * 128 multiply-adds, and the kernel is bound by that traffic, so the cost per output column falls
+// from 0.25 (BN 128) to 0.196 (BN 224); and the width can be chosen so that the tile count fills whole waves
+// of SMs (4096 x 1280: 320 tiles of 128 = 2.16 waves -> 3 rounds; 288 tiles of 144 = 1.95 waves -> 2 rounds).
+// A variant that kept the plain layout and offset the scale address by (first row % 128) / 32 TMEM columns
+// faulted ("misaligned address") at width 160, where that offset is odd; width 192 (offsets 0 and 2) ran
+// correctly, so odd column offsets of the scale address are the cause, and no path here uses an offset.
+static bool bn_supported(int bn) { return bn == 128 || (bn > 128 && bn <= 240 && bn % 16 == 0); }
 
 }  // namespace kwu
 
@@ -470,7 +496,7 @@ KWU_API int kwu_mxfp8_quantize(const void* x, int ldx, void* q, int ldq, void* s
   long grid = (warps + 7) / 8;
   if (grid > 148 * 16) grid = 148 * 16;
   mxfp8_quantize_kernel<<<static_cast<int>(grid), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      (const __nv_bfloat16*)x, ldx, (uint8_t*)q, ldq, (uint8_t*)sf, M, K, M_pad); kwu::count_launch();
+      (const __nv_bfloat16*)x, ldx, (uint8_t*)q, ldq, (uint8_t*)sf, M, K, M_pad, 0); kwu::count_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { set_last_error("mxfp8_quantize launch: %s", cudaGetErrorString(e)); return 11; }
   return 0;
@@ -483,9 +509,47 @@ KWU_API int kwu_mxfp8_quantize_t(const void* x, int ldx, void* qT, int ldq, void
   const int C_pad = (C + 127) / 128 * 128;
   dim3 grid((C_pad + 63) / 64, R / 32);
   mxfp8_quantize_t_kernel<<<grid, 64, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      (const __nv_bfloat16*)x, ldx, (uint8_t*)qT, ldq, (uint8_t*)sf, R, C, C_pad, 0, 0, 0); kwu::count_launch();
+      (const __nv_bfloat16*)x, ldx, (uint8_t*)qT, ldq, (uint8_t*)sf, R, C, C_pad, 0, 0, 0, 0); kwu::count_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { set_last_error("mxfp8_quantize_t launch: %s", cudaGetErrorString(e)); return 11; }
+  return 0;
+}
+
+// Weight forms: as kwu_mxfp8_quantize / kwu_mxfp8_quantize_t, with the scales in the tile-local layout for GEMM
+// tiles `sf_bn` rows wide (sf_bn <= 128: plain layout). The scale buffer has kwu_mxfp8_sf_bytes_tiled bytes and
+// must be pre-filled with the neutral byte 127: only the scales of real rows are written.
+KWU_API long long kwu_mxfp8_sf_bytes_tiled(int rows, int K, int sf_bn) {
+  if (sf_bn <= 128) return kwu_mxfp8_sf_bytes(rows, K);
+  return static_cast<long long>((rows + sf_bn - 1) / sf_bn) * (K / 128) * 1024;
+}
+
+KWU_API int kwu_mxfp8_quantize_w(const void* x, int ldx, void* q, int ldq, void* sf, int M, int K, int sf_bn,
+                                 void* stream) {
+  if (K % 128) { set_last_error("mxfp8_quantize_w: K must be a multiple of 128 (got %d)", K); return 7; }
+  if (!bn_supported(sf_bn)) { set_last_error("mxfp8_quantize_w: unsupported tile width %d", sf_bn); return 7; }
+  if (M <= 0) return 0;
+  const int M_pad = (M + 127) / 128 * 128;
+  long warps = static_cast<long>(M_pad) * ((K + 255) / 256);
+  long grid = (warps + 7) / 8;
+  if (grid > 148 * 16) grid = 148 * 16;
+  mxfp8_quantize_kernel<<<static_cast<int>(grid), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      (const __nv_bfloat16*)x, ldx, (uint8_t*)q, ldq, (uint8_t*)sf, M, K, M_pad, sf_bn); kwu::count_launch();
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { set_last_error("mxfp8_quantize_w launch: %s", cudaGetErrorString(e)); return 11; }
+  return 0;
+}
+
+KWU_API int kwu_mxfp8_quantize_t_w(const void* x, int ldx, void* qT, int ldq, void* sf, int R, int C, int sf_bn,
+                                   void* stream) {
+  if (R % 128) { set_last_error("mxfp8_quantize_t_w: R must be a multiple of 128 (got %d)", R); return 7; }
+  if (!bn_supported(sf_bn)) { set_last_error("mxfp8_quantize_t_w: unsupported tile width %d", sf_bn); return 7; }
+  if (C <= 0) return 0;
+  const int C_pad = (C + 127) / 128 * 128;
+  dim3 grid((C_pad + 63) / 64, R / 32);
+  mxfp8_quantize_t_kernel<<<grid, 64, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      (const __nv_bfloat16*)x, ldx, (uint8_t*)qT, ldq, (uint8_t*)sf, R, C, C_pad, 0, 0, 0, sf_bn); kwu::count_launch();
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { set_last_error("mxfp8_quantize_t_w launch: %s", cudaGetErrorString(e)); return 11; }
   return 0;
 }
 
@@ -498,7 +562,7 @@ KWU_API int kwu_mxfp8_quantize_t_batched(const void* x, int ldx, void* qT, int l
   dim3 grid(C / 64, R / 32, batch);
   mxfp8_quantize_t_kernel<<<grid, 64, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       (const __nv_bfloat16*)x, ldx, (uint8_t*)qT, ldq, (uint8_t*)sf, R, C, C, static_cast<long long>(R) * ldx,
-      static_cast<long long>(C) * ldq, kwu_mxfp8_sf_bytes(C, R)); kwu::count_launch();
+      static_cast<long long>(C) * ldq, kwu_mxfp8_sf_bytes(C, R), 0); kwu::count_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { set_last_error("mxfp8_quantize_t_batched launch: %s", cudaGetErrorString(e)); return 11; }
   return 0;
@@ -524,9 +588,19 @@ KWU_API int kwu_gemm_mxfp8(const void* A, const void* sfa, const void* B, const 
                            float alpha, int bn, void* stream, int* status) {
   if (M <= 0 || N <= 0) return 0;
   if (K % 128) { set_last_error("gemm_mxfp8: K must be a multiple of 128 (got %d)", K); return 7; }
-  (void)pick_bn_mx(M, N, bn);
-  return launch_mx<128>(A, B, C, M, N, K, lda, ldb, ldc, (const uint8_t*)sfa, (const uint8_t*)sfb, out_fp32,
-                        accumulate, alpha, reinterpret_cast<cudaStream_t>(stream), status);
+  if (bn <= 0) bn = 128;
+  if (!bn_supported(bn)) { set_last_error("gemm_mxfp8: tile width %d is not 128 or a multiple of 16 in (128, 240]", bn); return 7; }
+#define KWU_MX_CASE(W)                                                                                              \
+  case W:                                                                                                           \
+    return launch_mx<W>(A, B, C, M, N, K, lda, ldb, ldc, (const uint8_t*)sfa, (const uint8_t*)sfb, out_fp32,        \
+                        accumulate, alpha, reinterpret_cast<cudaStream_t>(stream), status, nullptr, 0, 1, nullptr, \
+                        W > 128 ? 1 : 0)
+  switch (bn) {
+    KWU_MX_CASE(128); KWU_MX_CASE(144); KWU_MX_CASE(160); KWU_MX_CASE(176); KWU_MX_CASE(192);
+    KWU_MX_CASE(208); KWU_MX_CASE(224); KWU_MX_CASE(240);
+  }
+#undef KWU_MX_CASE
+  return 7;
 }
 
 // ------------------------------------------------------------------------------------ attention operands

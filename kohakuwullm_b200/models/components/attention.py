@@ -87,7 +87,9 @@ class Attention(nn.Module):
                 qkv = self.qkv_proj(x)
                 out = attn_ops.attention_core(qkv, self.q_norm, self.k_norm, cos, sin, seq_info.cu_seqlens,
                                               plan, self._sink_lse(), self.heads, self.kv_heads, self.window,
-                                              self.scale, self.norm_eps, self.qk_norm)
+                                              self.scale, self.norm_eps, self.qk_norm,
+                                              emit_mx_grad=bool(getattr(self.qkv_proj, "mxfp8", False)),
+                                              emit_mx_out=bool(getattr(self.o_proj, "mxfp8", False)))
                 return self.o_proj(out.reshape(T, self.q_dim))
             q, k, v = self._project(x, rope)
             out = varlen_attention(q, k, v, seq_info.cu_seqlens, seq_info.max_seqlen, window=self.window,

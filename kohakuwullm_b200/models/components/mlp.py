@@ -41,11 +41,13 @@ class Linear(nn.Module):
         self._qweight = None
         return super()._apply(fn, recurse)
 
-    def quantized_weight(self):
+    def quantized_weight(self, rows_hint: int = 4096):
+        """The MXFP8 copies, built at first use; ``rows_hint`` (the row count of the first input) picks the GEMM
+        tile widths the copies' scales are laid out for."""
         from kohakuwullm_b200.ops.mxfp8 import QuantizedWeight
 
         if self._qweight is None:
-            self._qweight = QuantizedWeight(self.weight.detach())
+            self._qweight = QuantizedWeight(self.weight.detach(), rows_hint)
         return self._qweight
 
     def refresh_quantized_weight(self) -> bool:
@@ -60,7 +62,7 @@ class Linear(nn.Module):
             from kohakuwullm_b200.ops import mxfp8 as mx
 
             if mx.supported(x, self.weight):
-                return mx.mxfp8_linear(x, self.weight, self.quantized_weight())
+                return mx.mxfp8_linear(x, self.weight, self.quantized_weight(x.numel() // x.shape[-1]))
         return linear(x, self.weight, self.bias)
 
     def extra_repr(self):

@@ -17,6 +17,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 
 import torch
 
@@ -164,6 +165,10 @@ def varlen_attention(q, k, v, cu_seqlens, max_seqlen=None, window=None, sink_lse
 
 
 # --------------------------------------------------------------------------------- fused core
+# KWU_FUSED_QK=0 restores one norm+rope launch per tensor and the separate quantise passes (A/B timing only)
+FUSED_QK = os.environ.get("KWU_FUSED_QK", "1") != "0"
+
+
 class _AttentionCore(torch.autograd.Function):
     """QK-norm + RoPE + flash attention over a fused ``qkv`` projection output, as ONE autograd node.
 
@@ -174,7 +179,7 @@ class _AttentionCore(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, qkv, q_norm, k_norm, cos, sin, cu_seqlens, plan, sink_lse, Hq, Hkv, window, scale,
-                eps, do_norm):
+                eps, do_norm, emit_mx_grad=False, emit_mx_out=False):
         from kohakuwullm_b200.ops.elementwise import c_float as cf, c_int as ci
 
         L = native.require()
@@ -187,20 +192,45 @@ class _AttentionCore(torch.autograd.Function):
         q = torch.empty(T, Hq, D, dtype=qkv.dtype, device=qkv.device)
         k = torch.empty(T, Hkv, D, dtype=qkv.dtype, device=qkv.device)
         rot_half = 0 if cos is None else cos.shape[-1]
-        for src, dst, w, H in ((q_src, q, q_norm, Hq), (k_src, k, k_norm, Hkv)):
-            rc = L.kwu_qknorm_rope_fwd(native.ptr(src), ci(ld), native.ptr(dst), ci(H * D), native.ptr(w),
-                                       native.ptr(cos), native.ptr(sin), ci(T), ci(H), ci(D), ci(rot_half),
-                                       cf(eps), ci(int(do_norm)), native.stream_ptr())
-            native.check(rc, "qknorm_rope_fwd")
+        fused_qk = FUSED_QK and rot_half in (0, 32) and ld % 8 == 0 and qkv.data_ptr() % 16 == 0
+        emit_mx_out = emit_mx_out and FUSED_QK
+        if fused_qk:
+            # q and k heads in one launch (they are adjacent in the projection output)
+            rc = L.kwu_qknorm_rope_fwd_qk(native.ptr(qkv), ci(ld), native.ptr(q), native.ptr(k), native.ptr(q_norm),
+                                          native.ptr(k_norm), native.ptr(cos), native.ptr(sin), ci(T), ci(Hq), ci(Hkv),
+                                          ci(rot_half), cf(eps), ci(int(do_norm)), native.stream_ptr())
+            native.check(rc, "qknorm_rope_fwd_qk")
+        else:
+            for src, dst, w, H in ((q_src, q, q_norm, Hq), (k_src, k, k_norm, Hkv)):
+                rc = L.kwu_qknorm_rope_fwd(native.ptr(src), ci(ld), native.ptr(dst), ci(H * D), native.ptr(w),
+                                           native.ptr(cos), native.ptr(sin), ci(T), ci(H), ci(D), ci(rot_half),
+                                           cf(eps), ci(int(do_norm)), native.stream_ptr())
+                native.check(rc, "qknorm_rope_fwd")
         out = torch.empty(T, Hq, D, dtype=qkv.dtype, device=qkv.device)
         lse = torch.empty(Hq, T, dtype=torch.float32, device=qkv.device)
-        rc = L.kwu_flash_fwd(native.ptr(q), ci(Hq * D), native.ptr(k), ci(Hkv * D), native.ptr(v), ci(ld),
-                             native.ptr(out), native.ptr(lse), native.ptr(plan), ci(plan.shape[0] // 2), ci(T),
-                             ci(Hq), ci(Hkv), ci(window or 0), native.ptr(sink_lse), cf(scale),
-                             native.stream_ptr(), native.ptr(native.status_word()))
+        o8 = osf = None
+        if emit_mx_out:
+            from kohakuwullm_b200.ops import mxfp8 as mx
+
+            if mx.can_emit(T, Hq * D):
+                # the epilogue also writes the e4m3 + scale copy of the output for an MXFP8 output projection
+                o8, osf = mx.alloc_quantized(T, Hq * D, qkv.device)
+        if o8 is not None:
+            rc = L.kwu_flash_fwd_mx(native.ptr(q), ci(Hq * D), native.ptr(k), ci(Hkv * D), native.ptr(v), ci(ld),
+                                    native.ptr(out), native.ptr(lse), native.ptr(plan), ci(plan.shape[0] // 2), ci(T),
+                                    ci(Hq), ci(Hkv), ci(window or 0), native.ptr(sink_lse), cf(scale),
+                                    native.ptr(o8), native.ptr(osf), native.stream_ptr(),
+                                    native.ptr(native.status_word()))
+            mx.stash_quantized(out.view(T, Hq * D), o8, osf)
+        else:
+            rc = L.kwu_flash_fwd(native.ptr(q), ci(Hq * D), native.ptr(k), ci(Hkv * D), native.ptr(v), ci(ld),
+                                 native.ptr(out), native.ptr(lse), native.ptr(plan), ci(plan.shape[0] // 2), ci(T),
+                                 ci(Hq), ci(Hkv), ci(window or 0), native.ptr(sink_lse), cf(scale),
+                                 native.stream_ptr(), native.ptr(native.status_word()))
         native.check(rc, "flash_fwd")
         ctx.save_for_backward(qkv, q, k, out, lse, plan, sink_lse, q_norm, k_norm, cos, sin)
         ctx.cfg = (Hq, Hkv, window, scale, eps, do_norm)
+        ctx.fused_qk, ctx.emit_mx_grad = fused_qk, bool(emit_mx_grad)
         ctx.norm_params = (q_norm, k_norm)   # Parameter objects: their ``main_grad`` takes the gradients directly
         return out
 
@@ -231,21 +261,41 @@ class _AttentionCore(torch.autograd.Function):
         native.check(rc, "flash_bwd")
         rot_half = 0 if cos is None else cos.shape[-1]
         dws = []
-        for src, g, dst, w, H, wp in ((qkv[:, : Hq * D], dq, dqkv[:, : Hq * D], q_norm, Hq, ctx.norm_params[0]),
-                                      (qkv[:, Hq * D:(Hq + Hkv) * D], dk, dqkv[:, Hq * D:(Hq + Hkv) * D], k_norm, Hkv,
-                                       ctx.norm_params[1])):
+        targets = []
+        for w, wp in ((q_norm, ctx.norm_params[0]), (k_norm, ctx.norm_params[1])):
             mg = getattr(wp, "main_grad", None)
             into_main = w is not None and mg is not None and mg.dtype == torch.float32 and mg.is_contiguous()
             dw = (mg if into_main else torch.zeros(D, dtype=torch.float32, device=qkv.device)) if w is not None else None
-            rc = L.kwu_qknorm_rope_bwd(native.ptr(src), ci(ld), native.ptr(g), ci(H * D), native.ptr(dst), ci(dld),
-                                       native.ptr(w), native.ptr(dw), native.ptr(cos), native.ptr(sin), ci(T),
-                                       ci(H), ci(D), ci(rot_half), cf(eps), ci(int(do_norm)), native.stream_ptr())
-            native.check(rc, "qknorm_rope_bwd")
-            dws.append(None if into_main else dw)
+            targets.append((w, dw, into_main))
+        if ctx.fused_qk:
+            from kohakuwullm_b200.ops import mxfp8 as mx
+
+            q8 = sf = None
+            if ctx.emit_mx_grad and mx.can_emit(T, dqkv.shape[1]) and dqkv.is_contiguous():
+                # the fp8 copy of the whole gradient row (q, k and the v slice the attention backward wrote)
+                # for the dgrad of an MXFP8 qkv projection
+                q8, sf = mx.alloc_quantized(T, dqkv.shape[1], qkv.device)
+            rc = L.kwu_qknorm_rope_bwd_qk(native.ptr(qkv), ci(ld), native.ptr(dq), native.ptr(dk), native.ptr(dqkv),
+                                          ci(dld), native.ptr(q_norm), native.ptr(k_norm), native.ptr(targets[0][1]),
+                                          native.ptr(targets[1][1]), native.ptr(cos), native.ptr(sin), ci(T), ci(Hq),
+                                          ci(Hkv), ci(rot_half), cf(eps), ci(int(do_norm)), native.ptr(q8),
+                                          ci(dqkv.shape[1]), native.ptr(sf), native.stream_ptr())
+            native.check(rc, "qknorm_rope_bwd_qk")
+            if q8 is not None:
+                mx.stash_quantized(dqkv, q8, sf)
+        else:
+            for (src, g, dst, H), (w, dw, _) in zip(((qkv[:, : Hq * D], dq, dqkv[:, : Hq * D], Hq),
+                                                     (qkv[:, Hq * D:(Hq + Hkv) * D], dk, dqkv[:, Hq * D:(Hq + Hkv) * D], Hkv)),
+                                                    targets):
+                rc = L.kwu_qknorm_rope_bwd(native.ptr(src), ci(ld), native.ptr(g), ci(H * D), native.ptr(dst), ci(dld),
+                                           native.ptr(w), native.ptr(dw), native.ptr(cos), native.ptr(sin), ci(T),
+                                           ci(H), ci(D), ci(rot_half), cf(eps), ci(int(do_norm)), native.stream_ptr())
+                native.check(rc, "qknorm_rope_bwd")
+        dws = [None if into_main else dw for _, dw, into_main in targets]
         dsink = None
         if sink_lse is not None and ctx.needs_input_grad[7]:
             dsink = -(torch.exp(sink_lse.float()[:, None] - lse) * delta).sum(1).to(sink_lse.dtype)
-        return (dqkv, dws[0], dws[1], None, None, None, None, dsink, None, None, None, None, None, None)
+        return (dqkv, dws[0], dws[1], None, None, None, None, dsink, None, None, None, None, None, None, None, None)
 
 
 def attention_core_supported(qkv, head_dim, q_norm, k_norm, cos) -> bool:
@@ -255,13 +305,15 @@ def attention_core_supported(qkv, head_dim, q_norm, k_norm, cos) -> bool:
 
 
 def attention_core(qkv, q_norm, k_norm, cos, sin, cu_seqlens, plan, sink_lse, Hq, Hkv, window, scale, eps,
-                   do_norm):
+                   do_norm, emit_mx_grad=False, emit_mx_out=False):
+    """``emit_mx_grad``: the backward also writes the MXFP8 copy of ``d(qkv)`` for an MXFP8 projection's dgrad.
+    ``emit_mx_out``: the forward also writes the MXFP8 copy of the output for an MXFP8 output projection."""
     if plan is None:
         plan = attention_plan(cu_seqlens, qkv.shape[0])
     if sink_lse is not None:
         sink_lse = sink_lse.float()
     return _AttentionCore.apply(qkv, q_norm, k_norm, cos, sin, cu_seqlens, plan, sink_lse, Hq, Hkv, window,
-                                float(scale), float(eps), bool(do_norm))
+                                float(scale), float(eps), bool(do_norm), bool(emit_mx_grad), bool(emit_mx_out))
 
 
 # ------------------------------------------------------------------------------------ decode

@@ -21,10 +21,60 @@ GPU tests. Replaces the cuBLAS calls behind ``nn.Linear`` in the reference
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
 from kohakuwullm_b200.ops import native
+
+
+# ------------------------------------------------------------------------------------ weight-gradient overlap
+# In the backward pass the chain of activation gradients (dgrad GEMM -> elementwise backward -> attention
+# backward -> ...) is the critical path; a layer's weight gradient only has to be finished before the optimizer
+# reads ``main_grad``. With the overlap switched on, every weight-gradient product that accumulates into
+# ``main_grad`` is launched on a side stream right behind the point where its operands exist, and runs in the
+# shadow of the kernels that follow on the main stream: it fills the SMs a latency-bound attention backward, a
+# memory-bound norm kernel or the last partial wave of a GEMM leave idle. The caller (the training engine)
+# switches it on around a backward pass and joins the side stream afterwards; under CUDA-graph capture the
+# fork and the join are captured as parallel branches of the graph.
+_wgrad_overlap = {"on": False, "streams": {}, "dirty": False}
+
+
+def set_wgrad_overlap(on: bool) -> None:
+    _wgrad_overlap["on"] = bool(on)
+
+
+def wgrad_overlap_enabled() -> bool:
+    return _wgrad_overlap["on"]
+
+
+def launch_wgrad(fn, *operands: torch.Tensor) -> None:
+    """Run ``fn()`` (a weight-gradient product reading ``operands``) on the side stream when the overlap is on,
+    else inline. The operands are marked as used by the side stream so that the caching allocator does not
+    hand their memory out again before the product has read it."""
+    if not _wgrad_overlap["on"] or not operands or not operands[0].is_cuda:
+        fn()
+        return
+    dev = operands[0].device.index
+    side = _wgrad_overlap["streams"].get(dev)
+    if side is None:
+        side = _wgrad_overlap["streams"][dev] = torch.cuda.Stream(device=operands[0].device)
+    main = torch.cuda.current_stream(operands[0].device)
+    side.wait_stream(main)
+    with torch.cuda.stream(side):
+        fn()
+    for t in operands:
+        t.record_stream(side)
+    _wgrad_overlap["dirty"] = True
+
+
+def join_wgrad() -> None:
+    """Make the current stream wait for every weight-gradient product launched on a side stream."""
+    if not _wgrad_overlap["dirty"]:
+        return
+    for dev, side in _wgrad_overlap["streams"].items():
+        torch.cuda.current_stream(torch.device("cuda", dev)).wait_stream(side)
+    _wgrad_overlap["dirty"] = False
 
 
 def _use_native(*tensors: torch.Tensor) -> bool:
@@ -116,7 +166,7 @@ class _Linear(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             main_grad = getattr(w, "main_grad", None)
             if main_grad is not None:
-                matmul(dy, x, a_mn=True, b_mn=True, out=main_grad, accumulate=True)
+                launch_wgrad(lambda: matmul(dy, x, a_mn=True, b_mn=True, out=main_grad, accumulate=True), dy, x)
                 w.grad_in_main = True
             else:
                 dw = matmul(dy, x, a_mn=True, b_mn=True, out_dtype=w.dtype)

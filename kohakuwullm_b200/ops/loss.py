@@ -24,7 +24,7 @@ import ctypes
 import torch
 
 from kohakuwullm_b200.ops import native
-from kohakuwullm_b200.ops.gemm import matmul
+from kohakuwullm_b200.ops.gemm import launch_wgrad, matmul
 
 c_int, c_float = ctypes.c_int, ctypes.c_float
 
@@ -158,7 +158,13 @@ class _FusedLinearCE(torch.autograd.Function):
                 dh[s:e].copy_(dh32)
             if ctx.needs_input_grad[1]:
                 target = main_grad if main_grad is not None else dw
-                matmul(dl, h[s:e], a_mn=True, b_mn=True, out=target, accumulate=True)
+                hs = h[s:e]
+                if main_grad is not None and T <= chunk:
+                    # one chunk: the scratch is not rewritten before the step joins the side stream, so the
+                    # weight gradient may run beside the input-gradient product
+                    launch_wgrad(lambda: matmul(dl, hs, a_mn=True, b_mn=True, out=target, accumulate=True), dl, hs)
+                else:
+                    matmul(dl, hs, a_mn=True, b_mn=True, out=target, accumulate=True)
         if main_grad is not None:
             w.grad_in_main = True
         elif dw is not None:

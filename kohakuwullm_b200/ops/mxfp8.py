@@ -23,11 +23,12 @@ scales are kept in the tensor-core layout described in ``csrc/mxfp8.cu`` and con
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
 from kohakuwullm_b200.ops import native
-from kohakuwullm_b200.ops.gemm import matmul
+from kohakuwullm_b200.ops.gemm import launch_wgrad, matmul
 
 c_int, c_float = ctypes.c_int, ctypes.c_float
 E4M3_MAX = 448.0
@@ -96,8 +97,9 @@ def quantize_transposed(x: torch.Tensor, out_q=None, out_sf=None):
 
 
 def gemm(a_q, a_sf, b_q, b_sf, out=None, out_dtype=torch.bfloat16, accumulate=False, alpha=1.0, bn: int = 0):
-    """``out (+)= alpha * A B^T`` with A (M,K), B (N,K) both e4m3 with per-32 scales along K. ``bn`` is
-    reserved (the kernel uses 128-wide tiles)."""
+    """``out (+)= alpha * A B^T`` with A (M,K), B (N,K) both e4m3 with per-32 scales along K. ``bn``: width of
+    the output tiles; a value above 128 says that ``b_sf`` is in the tile-local layout for that width (made by
+    ``quantize_weight`` / ``quantize_weight_transposed``), 0 or 128 the plain layout."""
     L = native.require()
     M, K = a_q.shape
     N = b_q.shape[0]
@@ -109,6 +111,108 @@ def gemm(a_q, a_sf, b_q, b_sf, out=None, out_dtype=torch.bfloat16, accumulate=Fa
                           c_float(alpha), c_int(bn), native.stream_ptr(), native.ptr(native.status_word()))
     native.check(rc, "gemm_mxfp8")
     return out
+
+
+# ------------------------------------------------------------------------------------ weights: tile width
+TILE_WIDTHS = (128, 144, 160, 176, 192, 208, 224, 240)
+
+
+def pick_tile_width(n_cols: int, m_rows: int = 4096, sms: int = 148) -> int:
+    """Width of the output tiles of ``A (m_rows, K) x W (n_cols, K)^T`` that minimises rounds x cost per round.
+
+    The block-scaled GEMM is bound by shared-memory traffic: per 128-deep k-block a 128 x BN tile moves
+    16 KB + BN * 128 B, so a round of tiles costs ``16 + BN / 8`` units whatever it computes, and a problem
+    takes ``ceil(tiles / SMs)`` rounds. A wider tile is cheaper per column, and the right width fills whole
+    waves (4096 x 1280: 320 tiles of 128 are 3 rounds, 288 tiles of 144 are 2). ``KWU_MX_BN`` forces a width."""
+    forced = os.environ.get("KWU_MX_BN")
+    if forced:
+        return int(forced)
+    tiles_m = max((m_rows + 127) // 128, 1)
+    best, best_bn = None, 128
+    for bn in TILE_WIDTHS:
+        rounds = -(-(tiles_m * -(-n_cols // bn)) // sms)
+        cost = rounds * (16 + bn / 8)
+        if best is None or cost < best - 1e-9:
+            best, best_bn = cost, bn
+    return best_bn
+
+
+_TUNED: dict[tuple[int, int, int, int], int] = {}
+
+
+def tuned_tile_width(m_rows: int, n_cols: int, K: int, device) -> int:
+    """Tile width for ``A (m_rows, K) x W (n_cols, K)^T``, MEASURED once per problem shape on this device: every
+    supported width runs the real kernel on synthetic operands (10 back-to-back launches between two events,
+    best of three) and the fastest wins; the result is cached. The analytic pick above ranks the widths by
+    shared-memory traffic and wave count only and misses the fixed costs of a tile (pipeline fill, epilogue),
+    which decide between near-equal candidates at short contraction lengths. Falls back to the analytic pick
+    under stream capture, without a GPU, and unless ``KWU_MX_AUTOTUNE=1`` asks for the measurement (on the
+    dense training shapes both picks gave the same step time). Every width gives bit-identical results, so
+    ranks that pick differently still agree."""
+    if os.environ.get("KWU_MX_BN"):
+        return int(os.environ["KWU_MX_BN"])
+    dev = torch.device(device)
+    key = (dev.index or 0, m_rows, n_cols, K)
+    if key in _TUNED:
+        return _TUNED[key]
+    if (os.environ.get("KWU_MX_AUTOTUNE", "0") != "1" or dev.type != "cuda" or not native.available()
+            or torch.cuda.is_current_stream_capturing() or m_rows <= 0):
+        return pick_tile_width(n_cols, m_rows)
+    a_q = torch.randint(0, 120, (m_rows, K), dtype=torch.uint8, device=dev)
+    a_sf = torch.full((sf_bytes(m_rows, K),), 127, dtype=torch.uint8, device=dev)
+    b_q = torch.randint(0, 120, (n_cols, K), dtype=torch.uint8, device=dev)
+    out = torch.empty(m_rows, n_cols, dtype=torch.bfloat16, device=dev)
+    best_ms, best_bn = None, 128
+    for bn in TILE_WIDTHS:
+        b_sf = alloc_weight_sf(n_cols, K, bn, dev)
+        run = lambda: gemm(a_q, a_sf, b_q, b_sf, out=out, bn=bn)  # noqa: E731
+        run()
+        run()
+        samples = []
+        for _ in range(3):
+            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s0.record()
+            for _ in range(10):
+                run()
+            s1.record()
+            s1.synchronize()
+            samples.append(s0.elapsed_time(s1) / 10)
+        ms = min(samples)
+        if best_ms is None or ms < best_ms * 0.99:   # a wider tile must win by more than timing noise
+            best_ms, best_bn = ms, bn
+    _TUNED[key] = best_bn
+    return best_bn
+
+
+def sf_bytes_tiled(rows: int, K: int, bn: int) -> int:
+    if bn <= 128:
+        return sf_bytes(rows, K)
+    return -(-rows // bn) * (K // 128) * 1024
+
+
+def alloc_weight_sf(rows: int, K: int, bn: int, device) -> torch.Tensor:
+    """Scale buffer of a weight for tile width ``bn``; padding rows hold the neutral scale 2^0."""
+    return torch.full((sf_bytes_tiled(rows, K, bn),), 127, dtype=torch.uint8, device=device)
+
+
+def quantize_weight(w: torch.Tensor, out_q: torch.Tensor, out_sf: torch.Tensor, bn: int):
+    """bf16 (N,K) -> e4m3 (N,K) + scales along K in the layout for ``bn``-wide tiles."""
+    L = native.require()
+    N, K = w.shape
+    rc = L.kwu_mxfp8_quantize_w(native.ptr(w), c_int(w.stride(0)), native.ptr(out_q), c_int(out_q.stride(0)),
+                                native.ptr(out_sf), c_int(N), c_int(K), c_int(bn), native.stream_ptr())
+    native.check(rc, "mxfp8_quantize_w")
+    return out_q, out_sf
+
+
+def quantize_weight_transposed(w: torch.Tensor, out_q: torch.Tensor, out_sf: torch.Tensor, bn: int):
+    """bf16 (R,C) -> e4m3 (C,R) + scales along R in the layout for ``bn``-wide tiles of the (C,R) operand."""
+    L = native.require()
+    R, C = w.shape
+    rc = L.kwu_mxfp8_quantize_t_w(native.ptr(w), c_int(w.stride(0)), native.ptr(out_q), c_int(out_q.stride(0)),
+                                  native.ptr(out_sf), c_int(R), c_int(C), c_int(bn), native.stream_ptr())
+    native.check(rc, "mxfp8_quantize_t_w")
+    return out_q, out_sf
 
 
 # ------------------------------------------------------------------------------------ producer-made copies
@@ -149,28 +253,32 @@ def clear_prequantized() -> None:
 
 # ------------------------------------------------------------------------------------ linear
 class QuantizedWeight:
-    """The two MXFP8 copies of one weight matrix (N,K): ``W`` along K and ``W^T`` along N."""
+    """The two MXFP8 copies of one weight matrix (N,K): ``W`` along K (the B operand of FPROP, N output
+    columns) and ``W^T`` along N (the B operand of DGRAD, K output columns). Each copy's scales are laid out for
+    the tile width picked for its product (``rows_hint`` = the activation row count the layer runs at)."""
 
-    def __init__(self, weight: torch.Tensor):
+    def __init__(self, weight: torch.Tensor, rows_hint: int = 4096):
         N, K = weight.shape
         dev = weight.device
+        self.bn = tuned_tile_width(rows_hint, N, K, dev)       # FPROP: x (rows, K) x W (N, K)^T
+        self.bn_t = tuned_tile_width(rows_hint, K, N, dev)     # DGRAD: dy (rows, N) x W^T (K, N)^T
         self.q = torch.empty(N, K, dtype=torch.uint8, device=dev)
-        self.sf = torch.empty(sf_bytes(N, K), dtype=torch.uint8, device=dev)
+        self.sf = alloc_weight_sf(N, K, self.bn, dev)
         self.qt = torch.empty(K, N, dtype=torch.uint8, device=dev)
-        self.sft = torch.empty(sf_bytes(K, N), dtype=torch.uint8, device=dev)
+        self.sft = alloc_weight_sf(K, N, self.bn_t, dev)
         self.refresh(weight)
 
     @torch.no_grad()
     def refresh(self, weight: torch.Tensor) -> None:
-        quantize(weight, self.q, self.sf)
-        quantize_transposed(weight, self.qt, self.sft)
+        quantize_weight(weight, self.q, self.sf, self.bn)
+        quantize_weight_transposed(weight, self.qt, self.sft, self.bn_t)
 
 
 class _MXFP8Linear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, qw: QuantizedWeight):
         xq, xsf = take_quantized(x) or quantize(x)
-        y = gemm(xq, xsf, qw.q, qw.sf, out_dtype=x.dtype)
+        y = gemm(xq, xsf, qw.q, qw.sf, out_dtype=x.dtype, bn=qw.bn)
         ctx.save_for_backward(x, w)
         ctx.qw = qw
         return y
@@ -183,11 +291,11 @@ class _MXFP8Linear(torch.autograd.Function):
         dx = dw = None
         if ctx.needs_input_grad[0]:
             dyq, dysf = take_quantized(dy) or quantize(dy)
-            dx = gemm(dyq, dysf, qw.qt, qw.sft, out_dtype=x.dtype)
+            dx = gemm(dyq, dysf, qw.qt, qw.sft, out_dtype=x.dtype, bn=qw.bn_t)
         if ctx.needs_input_grad[1]:
             main_grad = getattr(w, "main_grad", None)
             if main_grad is not None:
-                matmul(dy, x, a_mn=True, b_mn=True, out=main_grad, accumulate=True)
+                launch_wgrad(lambda: matmul(dy, x, a_mn=True, b_mn=True, out=main_grad, accumulate=True), dy, x)
             else:
                 dw = matmul(dy, x, a_mn=True, b_mn=True, out_dtype=w.dtype)
         return dx, dw, None

@@ -17,6 +17,7 @@ into micro-batches and ranks. Reference semantics: src/kohakuwullm/training/loop
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Sequence
 
 import torch
@@ -24,6 +25,7 @@ import torch.distributed as dist
 from torch import nn
 
 from kohakuwullm_b200.data.packing import PackedBatch
+from kohakuwullm_b200.ops import gemm as gemm_ops
 from kohakuwullm_b200.ops import native
 from kohakuwullm_b200.parallel.ddp import GradSync
 from kohakuwullm_b200.parallel.flat import FlatParameters
@@ -85,7 +87,7 @@ class GraphedMicroStep:
         eng = self.engine
         loss, logs = eng.model.loss(self.tok, self.lab, self._info(), reduction="sum",
                                     router_scale=eng._router_scale)
-        loss.backward()
+        eng._backward(loss)
         self.ce.copy_(logs["ce"])
         self.total.copy_(loss.detach())
         for k in ("z_loss", "router_loss"):
@@ -180,6 +182,9 @@ class TrainEngine:
         self.graph_cache_size = max(int(graph_cache_size), 1)
         self._graphs: dict[tuple[int, int], GraphedMicroStep] = {}   # insertion order = recency (LRU first)
         self.replayed_native_launches = 0
+        # weight gradients on a side stream: measured neutral on the dense step (every kernel of the chain
+        # already fills the GPU), so off unless asked for
+        self.wgrad_overlap = os.environ.get("KWU_WGRAD_OVERLAP", "0") == "1"
         self._router_scale = torch.ones(1, dtype=torch.float32, device=dev)
 
     def _graph_for(self, mb: PackedBatch) -> GraphedMicroStep | None:
@@ -204,6 +209,18 @@ class TrainEngine:
             self._restore_router(router_state)
         self._graphs[key] = g      # most recently used last
         return g
+
+    def _backward(self, loss: torch.Tensor) -> None:
+        """Backward of one micro-batch with the weight-gradient products on a side stream (they only have to be
+        done before the optimizer reads ``main_grad``, so they run in the shadow of the activation-gradient
+        chain); the side stream is joined before this returns."""
+        overlap = self.wgrad_overlap and self.device.type == "cuda"
+        gemm_ops.set_wgrad_overlap(overlap)
+        try:
+            loss.backward()
+        finally:
+            gemm_ops.set_wgrad_overlap(False)
+            gemm_ops.join_wgrad()
 
     def native_launch_total(self) -> int:
         """Kernels of the native library launched so far: direct launches plus graph replays."""
@@ -292,7 +309,7 @@ class TrainEngine:
                 mb = mb.to(dev, non_blocking=True)
                 loss, logs = model.loss(mb.tokens, mb.labels, mb.seq_info, reduction="sum",
                                         router_scale=self._router_scale)
-                loss.backward()
+                self._backward(loss)
             ce_total = ce_total + logs["ce"]
             loss_total = loss_total + loss.detach().float()
             for k in ("z_loss", "router_loss"):

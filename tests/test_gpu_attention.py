@@ -237,3 +237,90 @@ def test_mxfp8_attention_backend_trains():
     packs = make_packs(2, 2048, 64, 1024, cfg.vocab_size, seed=3)
     losses = [float(eng.step(packs)["loss"]) for _ in range(6)]
     assert all(l == l for l in losses) and losses[-1] < losses[0]
+
+
+@pytest.mark.parametrize("rotary", [True, False])
+def test_fused_qk_norm_rope_matches_per_tensor_kernels_and_emits_fp8(rotary):
+    """q and k heads handled by one launch give bit-identical outputs to the two per-tensor launches, forward and
+    backward, and the MXFP8 copy of d(qkv) written by the backward equals quantising the stored gradient."""
+    import ctypes
+
+    from kohakuwullm_b200.ops import mxfp8 as mx
+    from kohakuwullm_b200.ops import native
+
+    torch.manual_seed(3)
+    L = native.require()
+    ci, cf = ctypes.c_int, ctypes.c_float
+    T, Hq, Hkv, D = 384, 20, 4, 64
+    cols = (Hq + 2 * Hkv) * D
+    qkv = torch.randn(T, cols, device="cuda").bfloat16()
+    wq = torch.rand(D, device="cuda") + 0.5
+    wk = torch.rand(D, device="cuda") + 0.5
+    ang = torch.rand(T, 32, device="cuda") * 6.28
+    cos, sin = (ang.cos().contiguous(), ang.sin().contiguous()) if rotary else (None, None)
+    rot = 32 if rotary else 0
+    st = native.stream_ptr()
+    # forward
+    q1 = torch.empty(T, Hq, D, device="cuda", dtype=torch.bfloat16)
+    k1 = torch.empty(T, Hkv, D, device="cuda", dtype=torch.bfloat16)
+    q2, k2 = torch.empty_like(q1), torch.empty_like(k1)
+    for src, dst, w, H in ((qkv[:, :Hq * D], q1, wq, Hq), (qkv[:, Hq * D:(Hq + Hkv) * D], k1, wk, Hkv)):
+        native.check(L.kwu_qknorm_rope_fwd(native.ptr(src), ci(cols), native.ptr(dst), ci(H * D), native.ptr(w),
+                                           native.ptr(cos), native.ptr(sin), ci(T), ci(H), ci(D), ci(rot), cf(1e-6),
+                                           ci(1), st), "fwd")
+    native.check(L.kwu_qknorm_rope_fwd_qk(native.ptr(qkv), ci(cols), native.ptr(q2), native.ptr(k2), native.ptr(wq),
+                                          native.ptr(wk), native.ptr(cos), native.ptr(sin), ci(T), ci(Hq), ci(Hkv),
+                                          ci(rot), cf(1e-6), ci(1), st), "fwd_qk")
+    assert torch.equal(q1, q2) and torch.equal(k1, k2)
+    # backward
+    dq = torch.randn(T, Hq, D, device="cuda").bfloat16()
+    dk = torch.randn(T, Hkv, D, device="cuda").bfloat16()
+    dv = torch.randn(T, Hkv * D, device="cuda").bfloat16()
+    d1 = torch.zeros(T, cols, device="cuda", dtype=torch.bfloat16)
+    d1[:, (Hq + Hkv) * D:] = dv
+    d2 = d1.clone()
+    dw1 = [torch.zeros(D, device="cuda"), torch.zeros(D, device="cuda")]
+    dw2 = [torch.zeros(D, device="cuda"), torch.zeros(D, device="cuda")]
+    for src, g, dst, w, H, dw in ((qkv[:, :Hq * D], dq, d1[:, :Hq * D], wq, Hq, dw1[0]),
+                                  (qkv[:, Hq * D:(Hq + Hkv) * D], dk, d1[:, Hq * D:(Hq + Hkv) * D], wk, Hkv, dw1[1])):
+        native.check(L.kwu_qknorm_rope_bwd(native.ptr(src), ci(cols), native.ptr(g), ci(H * D), native.ptr(dst), ci(cols),
+                                           native.ptr(w), native.ptr(dw), native.ptr(cos), native.ptr(sin), ci(T), ci(H),
+                                           ci(D), ci(rot), cf(1e-6), ci(1), st), "bwd")
+    q8, sf = mx.alloc_quantized(T, cols, "cuda")
+    native.check(L.kwu_qknorm_rope_bwd_qk(native.ptr(qkv), ci(cols), native.ptr(dq), native.ptr(dk), native.ptr(d2),
+                                          ci(cols), native.ptr(wq), native.ptr(wk), native.ptr(dw2[0]), native.ptr(dw2[1]),
+                                          native.ptr(cos), native.ptr(sin), ci(T), ci(Hq), ci(Hkv), ci(rot), cf(1e-6),
+                                          ci(1), native.ptr(q8), ci(cols), native.ptr(sf), st), "bwd_qk")
+    assert torch.equal(d1, d2)
+    for a, b in zip(dw1, dw2):
+        torch.testing.assert_close(a, b, rtol=1e-4, atol=1e-3)   # fp32 atomics in a different order
+    q_ref, sf_ref = mx.quantize(d2)
+    assert torch.equal(q8, q_ref) and torch.equal(sf, sf_ref)
+    native.check_status()
+
+
+def test_flash_forward_fp8_copy_of_output_equals_the_quantise_kernel():
+    """The forward epilogue's MXFP8 copy of the attention output (for an MXFP8 output projection) is bit-identical
+    to quantising the stored bf16 output, on a pack with ragged documents (every token lies in one query tile)."""
+    from kohakuwullm_b200.models.seqinfo import SeqInfo
+    from kohakuwullm_b200.ops import mxfp8 as mx
+    from kohakuwullm_b200.ops import native
+    from kohakuwullm_b200.ops.attention import attention_core
+
+    torch.manual_seed(11)
+    Hq, Hkv, D = 20, 4, 64
+    info = SeqInfo.from_lengths([300, 77, 500, 147], device="cuda")   # 1024 tokens
+    T = info.total_tokens
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device="cuda").bfloat16()
+    wq = torch.ones(D, device="cuda")
+    mx.clear_prequantized()
+    out = attention_core(qkv, wq, wq, None, None, info.cu_seqlens, None, None, Hq, Hkv, None, 0.125, 1e-6, True,
+                         emit_mx_out=True)
+    out2d = out.reshape(T, Hq * D)
+    got = mx.take_quantized(out2d)
+    assert got is not None
+    q_ref, sf_ref = mx.quantize(out2d.contiguous())
+    assert torch.equal(got[0], q_ref) and torch.equal(got[1], sf_ref)
+    plain = attention_core(qkv, wq, wq, None, None, info.cu_seqlens, None, None, Hq, Hkv, None, 0.125, 1e-6, True)
+    assert torch.equal(plain, out)
+    native.check_status()

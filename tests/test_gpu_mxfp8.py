@@ -171,3 +171,40 @@ def test_training_step_identical_with_and_without_fused_quantisation():
     assert abs(la[0] - lb[0]) < 1e-6, (la, lb)        # the forward pass has no atomics: identical
     assert abs(la[1] - lb[1]) < 2e-2, (la, lb)
     assert (pa - pb).abs().max().item() < 1e-2
+
+
+@pytest.mark.parametrize("M,N,K,bn", [
+    (256, 1280, 256, 144), (384, 1792, 384, 208), (200, 3584, 128, 224), (128, 1280, 512, 160),
+    (512, 768, 256, 192), (130, 2048, 256, 240), (256, 1296, 128, 176),
+])
+def test_wide_tiles_with_tile_local_weight_scales_equal_the_128_wide_kernel(M, N, K, bn):
+    """A weight quantised with its scales laid out for ``bn``-wide tiles gives, through the ``bn``-wide GEMM, the
+    same bytes as the plain layout through the 128-wide GEMM (same products, same fp32 summation order), also
+    when the last tile hangs over the matrix edge; the transposed (dgrad) copy likewise."""
+    from kohakuwullm_b200.ops import mxfp8 as mx
+    from kohakuwullm_b200.ops import native
+
+    torch.manual_seed(M + N + bn)
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.1).bfloat16()
+    aq, asf = mx.quantize(a)
+    wq, wsf = mx.quantize(w)
+    ref = mx.gemm(aq, asf, wq, wsf)
+    q2 = torch.empty(N, K, dtype=torch.uint8, device="cuda")
+    sf2 = mx.alloc_weight_sf(N, K, bn, "cuda")
+    mx.quantize_weight(w, q2, sf2, bn)
+    assert torch.equal(q2, wq)
+    out = mx.gemm(aq, asf, q2, sf2, bn=bn)
+    assert torch.equal(out, ref)
+    # transposed copy: W^T (K, N) as the B operand of dy (M, N) @ W -> (M, K); needs N % 128 == 0
+    if N % 128 == 0:
+        dy = torch.randn(M, N, device="cuda").bfloat16()
+        dq, dsf = mx.quantize(dy)
+        qt, sft = mx.quantize_transposed(w)
+        ref_t = mx.gemm(dq, dsf, qt, sft)
+        qt2 = torch.empty(K, N, dtype=torch.uint8, device="cuda")
+        sft2 = mx.alloc_weight_sf(K, N, bn, "cuda")
+        mx.quantize_weight_transposed(w, qt2, sft2, bn)
+        assert torch.equal(qt2, qt)
+        assert torch.equal(mx.gemm(dq, dsf, qt2, sft2, bn=bn), ref_t)
+    native.check_status()
