@@ -68,6 +68,20 @@ __device__ __forceinline__ int snake_item(int r) {
   return r * G + ((r & 1) ? G - 1 - b : b);
 }
 
+// ------------------------------------------------------------------ programmatic dependent launch
+// A kernel launched with `launch_k` (host side, below) may START while the kernel before it in the stream is
+// still running: its CTAs become resident as SMs free up and run their set-up (barrier init, TMEM allocation,
+// descriptor prefetch). `pdl_wait` blocks until the preceding kernels have completed and their memory is
+// visible; NOTHING that another kernel produced may be read before it. `pdl_launch_dependents` lets the NEXT
+// kernel in the stream begin its own early start; it is called right after the wait, so at most one successor
+// is resident and waiting at any time. Both are no-ops for a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_sync() {
+  pdl_wait();
+  pdl_launch_dependents();
+}
+
 // ------------------------------------------------------------------ mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
@@ -441,9 +455,30 @@ struct PerDeviceOnce {
     __atomic_fetch_or(&done, 1ull << (dev & 63), __ATOMIC_RELEASE);
   }
 };
+bool pdl_enabled();   // programmatic dependent launch for kernels started through launch_k (KWU_PDL=1 turns it on)
 void set_device_status_word(int* p);
 int* device_status_word();   // the current device's registered status word, or null
 void count_launch(int n = 1);
 long long launch_total();  // bumps the library-wide kernel launch counter
 void set_last_error(const char* fmt, ...);
+}  // namespace kwu
+
+namespace kwu {
+// Launch `kern` with the programmatic-stream-serialization attribute (see pdl_wait above). Only for kernels
+// that call pdl_sync() / pdl_wait() before their first read of another kernel's output.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                            Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
 }  // namespace kwu

@@ -18,6 +18,7 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
                    const float* __restrict__ w, __nv_bfloat16* __restrict__ y,
                    __nv_bfloat16* __restrict__ h_out, float* __restrict__ rstd_out, int rows,
                    int cols, float eps, int one_plus, const MxOut mx) {
+  pdl_sync();   // nothing of the previous kernel is read above this line
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
   const int nvec = cols >> 3;  // cols % 8 == 0 (checked on the host)
@@ -103,6 +104,7 @@ rmsnorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ x, const float* __restr
                        const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
                        float* __restrict__ dw_partial, float* __restrict__ dw_direct, int rows, int cols,
                        int one_plus, const MxOut mx, int* __restrict__ status) {
+  pdl_sync();   // nothing of the previous kernel is read above this line
   extern __shared__ float s_dw[];  // unstaged: one parking row of cols floats per warp
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -268,6 +270,7 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
                    const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dy,
                    const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
                    float* __restrict__ dw_partial, int rows, int cols, int one_plus) {
+  pdl_sync();   // nothing of the previous kernel is read above this line
   extern __shared__ float s_dw[];  // cols floats
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -364,6 +367,7 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
 // dw[c] (+)= sum_b partial[b, c]
 __global__ void colsum_partials_kernel(const float* __restrict__ partial, float* __restrict__ dw,
                                        int nblocks, int cols, int accumulate) {
+  pdl_sync();   // nothing of the previous kernel is read above this line
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= cols) return;
   float s = 0.f;
@@ -384,6 +388,7 @@ qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ src, int src_ld,
                        const float* __restrict__ weight, const float* __restrict__ cos_t,
                        const float* __restrict__ sin_t, int tokens, int heads, int rot_half,
                        float eps, int do_norm) {
+  pdl_sync();   // nothing of the previous kernel is read above this line
   const int lane = threadIdx.x & 31;
   const long total = static_cast<long>(tokens) * heads;
   const int wpb = blockDim.x >> 5;
@@ -440,6 +445,7 @@ qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ src, int src_ld,
                        const float* __restrict__ weight, float* __restrict__ dweight,
                        const float* __restrict__ cos_t, const float* __restrict__ sin_t, int tokens,
                        int heads, int rot_half, float eps, int do_norm) {
+  pdl_sync();   // nothing of the previous kernel is read above this line
   __shared__ float s_dw[64];
   if (threadIdx.x < 64) s_dw[threadIdx.x] = 0.f;
   __syncthreads();
@@ -518,6 +524,7 @@ qknorm_rope_fwd_vec_kernel(const __nv_bfloat16* __restrict__ src, int src_ld,
                            const float* __restrict__ weight, const float* __restrict__ cos_t,
                            const float* __restrict__ sin_t, int tokens, int heads, int rot_half,
                            float eps, int do_norm) {
+  pdl_sync();   // nothing of the previous kernel is read above this line
   const int lane = threadIdx.x & 31, sub = lane & 7, slot = lane >> 3;
   const long total = static_cast<long>(tokens) * heads;
   const int wpb = blockDim.x >> 5;
@@ -576,6 +583,7 @@ qknorm_rope_bwd_vec_kernel(const __nv_bfloat16* __restrict__ src, int src_ld,
                            const float* __restrict__ weight, float* __restrict__ dweight,
                            const float* __restrict__ cos_t, const float* __restrict__ sin_t, int tokens,
                            int heads, int rot_half, float eps, int do_norm) {
+  pdl_sync();   // nothing of the previous kernel is read above this line
   __shared__ float s_dw[64];
   if (threadIdx.x < 64) s_dw[threadIdx.x] = 0.f;
   __syncthreads();
@@ -668,6 +676,7 @@ qknorm_rope_fwd_qk_kernel(const __nv_bfloat16* __restrict__ src, int src_ld, __n
                           const float* __restrict__ wk_p, const float* __restrict__ cos_t,
                           const float* __restrict__ sin_t, int tokens, int Hq, int Hkv, int rot_half, float eps,
                           int do_norm) {
+  pdl_sync();   // nothing of the previous kernel is read above this line
   const int lane = threadIdx.x & 31, sub = lane & 7, slot = lane >> 3;
   const int HT = Hq + Hkv;
   const long total = static_cast<long>(tokens) * HT;
@@ -739,6 +748,7 @@ qknorm_rope_bwd_qk_kernel(const __nv_bfloat16* __restrict__ src, int src_ld, con
                           float* __restrict__ dwq_out, float* __restrict__ dwk_out,
                           const float* __restrict__ cos_t, const float* __restrict__ sin_t, int tokens, int Hq,
                           int Hkv, int rot_half, float eps, int do_norm, const MxOut mx, int q_blocks) {
+  pdl_sync();   // nothing of the previous kernel is read above this line
   // Blocks [0, q_blocks) take the query heads, the rest the key heads (and, with emission, the value heads,
   // which are only read back and quantised): a block then needs ONE weight vector and ONE gradient
   // accumulator in registers (both roles in every thread cost 99 registers and a third of the occupancy).
@@ -848,6 +858,7 @@ qknorm_rope_bwd_qk_kernel(const __nv_bfloat16* __restrict__ src, int src_ld, con
 __global__ void __launch_bounds__(256)
 swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ in, int in_ld, __nv_bfloat16* __restrict__ out,
                   int out_ld, int rows, int H, const MxOut mx) {
+  pdl_sync();   // nothing of the previous kernel is read above this line
   const int nvec = H >> 3;
   const long total = static_cast<long>(rows) * nvec;
   // uniform trip count for the whole block: the optional fp8 emission shuffles inside the loop
@@ -883,6 +894,7 @@ __global__ void __launch_bounds__(256)
 swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ in, int in_ld,
                   const __nv_bfloat16* __restrict__ dout, int dout_ld,
                   __nv_bfloat16* __restrict__ din, int din_ld, int rows, int H, const MxOut mx) {
+  pdl_sync();   // nothing of the previous kernel is read above this line
   const int nvec = H >> 3;
   const long total = static_cast<long>(rows) * nvec;
   for (long base = static_cast<long>(blockIdx.x) * blockDim.x; base < total;
@@ -964,11 +976,11 @@ static int rmsnorm_fwd_impl(const void* x, const void* res, const float* w, void
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int grid = grid_for(rows, 8);
   if (res) {
-    rmsnorm_fwd_kernel<true><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)res, w,
+    launch_k(rmsnorm_fwd_kernel<true>, dim3(grid), dim3(256), 0, st, (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, w,
                                                   (__nv_bfloat16*)y, (__nv_bfloat16*)h_out, rstd, rows,
                                                   cols, eps, one_plus, mx); kwu::count_launch();
   } else {
-    rmsnorm_fwd_kernel<false><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, nullptr, w, (__nv_bfloat16*)y,
+    launch_k(rmsnorm_fwd_kernel<false>, dim3(grid), dim3(256), 0, st, (const __nv_bfloat16*)x, nullptr, w, (__nv_bfloat16*)y,
                                                    nullptr, rstd, rows, cols, eps, one_plus, mx); kwu::count_launch();
   }
   return check_launch("rmsnorm_fwd");
@@ -1028,23 +1040,23 @@ static int rmsnorm_bwd_impl(const void* x, const float* w, const float* rstd, co
 #define KWU_RMS_LAUNCH(NVV)                                                                                         \
   do {                                                                                                              \
     if (staged)                                                                                                     \
-      rmsnorm_bwd_reg_kernel<NVV, true><<<grid, threads, stage_smem, st>>>(KWU_RMS_BWD_HEAD, direct, KWU_RMS_BWD_TAIL, mx, kwu::device_status_word()); \
+      launch_k(rmsnorm_bwd_reg_kernel<NVV, true>, dim3(grid), dim3(threads), stage_smem, st, KWU_RMS_BWD_HEAD, direct, KWU_RMS_BWD_TAIL, mx, kwu::device_status_word()); \
     else                                                                                                            \
-      rmsnorm_bwd_reg_kernel<NVV, false><<<grid, threads, dw_smem_reg, st>>>(KWU_RMS_BWD_HEAD, direct, KWU_RMS_BWD_TAIL, mx, nullptr); \
+      launch_k(rmsnorm_bwd_reg_kernel<NVV, false>, dim3(grid), dim3(threads), dw_smem_reg, st, KWU_RMS_BWD_HEAD, direct, KWU_RMS_BWD_TAIL, mx, nullptr); \
   } while (0)
   if (nv <= 2) KWU_RMS_LAUNCH(2);
   else if (nv <= 4) KWU_RMS_LAUNCH(4);
   else if (nv <= 5) KWU_RMS_LAUNCH(5);
   else if (nv <= 6) KWU_RMS_LAUNCH(6);
   else if (nv <= 8) KWU_RMS_LAUNCH(8);
-  else rmsnorm_bwd_kernel<<<grid, 256, dw_smem, st>>>(KWU_RMS_BWD_HEAD, KWU_RMS_BWD_TAIL);
+  else launch_k(rmsnorm_bwd_kernel, dim3(grid), dim3(256), dw_smem, st, KWU_RMS_BWD_HEAD, KWU_RMS_BWD_TAIL);
 #undef KWU_RMS_LAUNCH
 #undef KWU_RMS_BWD_HEAD
 #undef KWU_RMS_BWD_TAIL
   kwu::count_launch();
   if (int rc = check_launch("rmsnorm_bwd")) return rc;
   if (want_dw && !direct) {
-    colsum_partials_kernel<<<(cols + 255) / 256, 256, 0, st>>>(dw_partial, dw, grid, cols, accumulate_dw); kwu::count_launch();
+    launch_k(colsum_partials_kernel, dim3((cols + 255) / 256), dim3(256), 0, st, dw_partial, dw, grid, cols, accumulate_dw); kwu::count_launch();
     return check_launch("rmsnorm_dw");
   }
   return 0;
@@ -1081,13 +1093,13 @@ KWU_API int kwu_qknorm_rope_fwd(const void* src, int src_ld, void* dst, int dst_
                    (rot_half == 0 || (al16(cos_t) && al16(sin_t))) && (!weight || al16(weight));
   if (vec) {
     const int grid = grid_for(static_cast<long>(tokens) * heads, 32, 148 * 16);
-    qknorm_rope_fwd_vec_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)src, src_ld, (__nv_bfloat16*)dst,
+    launch_k(qknorm_rope_fwd_vec_kernel, dim3(grid), dim3(256), 0, st, (const __nv_bfloat16*)src, src_ld, (__nv_bfloat16*)dst,
                                                     dst_ld, weight, cos_t, sin_t, tokens, heads, rot_half,
                                                     eps, do_norm); kwu::count_launch();
     return check_launch("qknorm_rope_fwd");
   }
   const int grid = grid_for(static_cast<long>(tokens) * heads, 8, 148 * 16);
-  qknorm_rope_fwd_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)src, src_ld, (__nv_bfloat16*)dst,
+  launch_k(qknorm_rope_fwd_kernel, dim3(grid), dim3(256), 0, st, (const __nv_bfloat16*)src, src_ld, (__nv_bfloat16*)dst,
                                               dst_ld, weight, cos_t, sin_t, tokens, heads, rot_half,
                                               eps, do_norm); kwu::count_launch();
   return check_launch("qknorm_rope_fwd");
@@ -1106,14 +1118,14 @@ KWU_API int kwu_qknorm_rope_bwd(const void* src, int src_ld, const void* dout, i
   if (vec) {
     // few blocks: each one ends with 64 global atomics for the norm weight gradient (148 x 16 blocks measured 15 % slower)
     const int grid = grid_for(static_cast<long>(tokens) * heads, 32, 148 * 4);
-    qknorm_rope_bwd_vec_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)src, src_ld,
+    launch_k(qknorm_rope_bwd_vec_kernel, dim3(grid), dim3(256), 0, st, (const __nv_bfloat16*)src, src_ld,
                                                     (const __nv_bfloat16*)dout, dout_ld, (__nv_bfloat16*)dsrc,
                                                     dsrc_ld, weight, dweight, cos_t, sin_t, tokens, heads,
                                                     rot_half, eps, do_norm); kwu::count_launch();
     return check_launch("qknorm_rope_bwd");
   }
   const int grid = grid_for(static_cast<long>(tokens) * heads, 8, 148 * 4);
-  qknorm_rope_bwd_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)src, src_ld,
+  launch_k(qknorm_rope_bwd_kernel, dim3(grid), dim3(256), 0, st, (const __nv_bfloat16*)src, src_ld,
                                               (const __nv_bfloat16*)dout, dout_ld, (__nv_bfloat16*)dsrc,
                                               dsrc_ld, weight, dweight, cos_t, sin_t, tokens, heads,
                                               rot_half, eps, do_norm); kwu::count_launch();
@@ -1133,7 +1145,7 @@ KWU_API int kwu_qknorm_rope_fwd_qk(const void* src, int src_ld, void* dst_q, voi
   }
   if (tokens <= 0) return 0;
   const int grid = grid_for(static_cast<long>(tokens) * (Hq + Hkv), 32, 148 * 16);
-  qknorm_rope_fwd_qk_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  launch_k(qknorm_rope_fwd_qk_kernel, dim3(grid), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream), 
       (const __nv_bfloat16*)src, src_ld, (__nv_bfloat16*)dst_q, (__nv_bfloat16*)dst_k, wq, wk, cos_t, sin_t, tokens,
       Hq, Hkv, rot_half, eps, do_norm); kwu::count_launch();
   return check_launch("qknorm_rope_fwd_qk");
@@ -1166,7 +1178,7 @@ KWU_API int kwu_qknorm_rope_bwd_qk(const void* src, int src_ld, const void* dq, 
   int q_blocks = static_cast<int>(static_cast<long>(grid) * Hq / (Hq + kv_heads));
   if (q_blocks < 1) q_blocks = 1;
   const int total_blocks = q_blocks + (grid - q_blocks < 1 ? 1 : grid - q_blocks);
-  qknorm_rope_bwd_qk_kernel<<<total_blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  launch_k(qknorm_rope_bwd_qk_kernel, dim3(total_blocks), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream), 
       (const __nv_bfloat16*)src, src_ld, (const __nv_bfloat16*)dq, (const __nv_bfloat16*)dk, (__nv_bfloat16*)dsrc,
       dsrc_ld, wq, wk, dwq, dwk, cos_t, sin_t, tokens, Hq, Hkv, rot_half, eps, do_norm,
       make_mx(q8, ldq, sf, cols), q_blocks); kwu::count_launch();
@@ -1179,7 +1191,7 @@ static int swiglu_fwd_impl(const void* in, int in_ld, void* out, int out_ld, int
   if (rows <= 0) return 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int grid = grid_for(static_cast<long>(rows) * (H / 8), 256);
-  swiglu_fwd_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)in, in_ld, (__nv_bfloat16*)out, out_ld,
+  launch_k(swiglu_fwd_kernel, dim3(grid), dim3(256), 0, st, (const __nv_bfloat16*)in, in_ld, (__nv_bfloat16*)out, out_ld,
                                          rows, H, mx); kwu::count_launch();
   return check_launch("swiglu_fwd");
 }
@@ -1202,7 +1214,7 @@ static int swiglu_bwd_impl(const void* in, int in_ld, const void* dout, int dout
   if (rows <= 0) return 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int grid = grid_for(static_cast<long>(rows) * (H / 8), 256);
-  swiglu_bwd_kernel<<<grid, 256, 0, st>>>((const __nv_bfloat16*)in, in_ld, (const __nv_bfloat16*)dout,
+  launch_k(swiglu_bwd_kernel, dim3(grid), dim3(256), 0, st, (const __nv_bfloat16*)in, in_ld, (const __nv_bfloat16*)dout,
                                          dout_ld, (__nv_bfloat16*)din, din_ld, rows, H, mx); kwu::count_launch();
   return check_launch("swiglu_bwd");
 }

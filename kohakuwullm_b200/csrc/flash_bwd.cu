@@ -26,6 +26,7 @@ template <bool V> struct BoolC { static constexpr bool value = V; };   // compil
 __global__ void __launch_bounds__(256)
 flash_delta_kernel(const __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ dout,
                    float* __restrict__ delta, int T, int Hq) {
+  pdl_sync();   // nothing of the previous kernel is read above this line
   // eight lanes per (t, h) row of 64 (one 16-byte load of each operand per lane), four rows per warp pass
   const int lane = threadIdx.x & 31, sub = lane & 7, slot = lane >> 3;
   const long total = static_cast<long>(T) * Hq;
@@ -98,6 +99,7 @@ __global__ void __launch_bounds__(FB_THREADS, 2)
 flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_constant__ CUtensorMap tmDO64,
                       const __grid_constant__ CUtensorMap tmK128, const __grid_constant__ CUtensorMap tmV128,
                       const FlashBwdParams p) {
+  pdl_sync();   // nothing of the previous kernel is read above this line
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -451,6 +453,7 @@ __global__ void __launch_bounds__(FB_THREADS, 2)
 flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_constant__ CUtensorMap tmDO128,
                     const __grid_constant__ CUtensorMap tmK64, const __grid_constant__ CUtensorMap tmV64,
                     const FlashBwdParams p) {
+  pdl_sync();   // nothing of the previous kernel is read above this line
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -700,6 +703,7 @@ __global__ void __launch_bounds__(256)
 flash_group_reduce_kernel(const float* __restrict__ dk_part, const float* __restrict__ dv_part,
                           __nv_bfloat16* __restrict__ dk, __nv_bfloat16* __restrict__ dv, int dk_ld,
                           int dv_ld, int T, int Hq, int Hkv) {
+  pdl_sync();   // nothing of the previous kernel is read above this line
   const int group = Hq / Hkv;
   const long total = static_cast<long>(T) * Hkv * 16;  // float4 lanes
   for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
@@ -743,7 +747,7 @@ KWU_API int kwu_flash_bwd(const void* q, int q_ld, const void* k, int k_ld, cons
     long rows = static_cast<long>(T) * Hq;
     long g = (rows + 31) / 32;
     if (g > 148 * 16) g = 148 * 16;
-    flash_delta_kernel<<<static_cast<int>(g), 256, 0, st>>>((const __nv_bfloat16*)out,
+    launch_k(flash_delta_kernel, dim3(static_cast<int>(g)), dim3(256), 0, st, (const __nv_bfloat16*)out,
                                                           (const __nv_bfloat16*)dout, delta, T, Hq); kwu::count_launch();
   }
   CUtensorMap tmQ64, tmDO64, tmK128, tmV128, tmQ128, tmDO128, tmK64, tmV64;
@@ -784,13 +788,13 @@ KWU_API int kwu_flash_bwd(const void* q, int q_ld, const void* k, int k_ld, cons
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const long long items = static_cast<long long>(n_tiles) * Hq;
   const int pgrid = static_cast<int>(items < 2LL * sms ? items : 2LL * sms);   // two resident CTAs per SM walk the items
-  flash_bwd_dkdv_kernel<<<pgrid, FB_THREADS, FBK_SMEM, st>>>(tmQ64, tmDO64, tmK128, tmV128, p); kwu::count_launch();
+  launch_k(flash_bwd_dkdv_kernel, dim3(pgrid), dim3(FB_THREADS), FBK_SMEM, st, tmQ64, tmDO64, tmK128, tmV128, p); kwu::count_launch();
   if (Hq > Hkv) {
     long g = (static_cast<long>(T) * Hkv * 16 + 255) / 256;
     if (g > 148 * 16) g = 148 * 16;
-    flash_group_reduce_kernel<<<static_cast<int>(g), 256, 0, st>>>(p.dk_part, p.dv_part, p.dk, p.dv, dk_ld, dv_ld, T, Hq, Hkv); kwu::count_launch();
+    launch_k(flash_group_reduce_kernel, dim3(static_cast<int>(g)), dim3(256), 0, st, p.dk_part, p.dv_part, p.dk, p.dv, dk_ld, dv_ld, T, Hq, Hkv); kwu::count_launch();
   }
-  flash_bwd_dq_kernel<<<pgrid, FB_THREADS, FBQ_SMEM, st>>>(tmQ128, tmDO128, tmK64, tmV64, p); kwu::count_launch();
+  launch_k(flash_bwd_dq_kernel, dim3(pgrid), dim3(FB_THREADS), FBQ_SMEM, st, tmQ128, tmDO128, tmK64, tmV64, p); kwu::count_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { set_last_error("flash_bwd launch: %s", cudaGetErrorString(e)); return 11; }
   return 0;

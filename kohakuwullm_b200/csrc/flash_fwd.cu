@@ -109,6 +109,7 @@ __device__ __forceinline__ bool fwd_decode(const FlashFwdParams& p, int item, Fw
 __global__ void __launch_bounds__(FA_THREADS, 2)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const FlashFwdParams p) {
+  pdl_sync();   // nothing of the previous kernel is read above this line
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -523,7 +524,7 @@ static int flash_fwd_impl(const void* q, int q_ld, const void* k, int k_ld, cons
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   long long items = static_cast<long long>(n_tiles) * Hq;
   int grid = static_cast<int>(items < 2LL * sms ? items : 2LL * sms);   // two resident CTAs per SM, each walks the item list
-  flash_fwd_kernel<<<grid, FA_THREADS, FA_SMEM, reinterpret_cast<cudaStream_t>(stream)>>>(tmQ, tmK, tmV, p); kwu::count_launch();
+  launch_k(flash_fwd_kernel, dim3(grid), dim3(FA_THREADS), FA_SMEM, reinterpret_cast<cudaStream_t>(stream), tmQ, tmK, tmV, p); kwu::count_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { set_last_error("flash_fwd launch: %s", cudaGetErrorString(e)); return 11; }
   return 0;

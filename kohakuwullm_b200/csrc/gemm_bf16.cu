@@ -205,6 +205,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_sync();   // set-up above overlapped the previous kernel's tail; operands are read from here on
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -642,7 +643,7 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
     p.splits = 1;
     p.streamk = grid;
   }
-  kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, C, p); kwu::count_launch();
+  launch_k(kern, dim3(grid), dim3(GEMM_THREADS), S::TOTAL, stream, tmA, tmB, C, p); kwu::count_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_error("gemm launch: %s", cudaGetErrorString(e));

@@ -24,6 +24,7 @@ namespace kwu {
 __global__ void __launch_bounds__(256)
 mxfp8_quantize_kernel(const __nv_bfloat16* __restrict__ x, int ldx, uint8_t* __restrict__ q, int ldq,
                       uint8_t* __restrict__ sf, int M, int K, int M_pad, int sf_bn) {
+  pdl_sync();   // nothing of the previous kernel is read above this line
   const int lane = threadIdx.x & 31;
   const int n_kchunks = K >> 7;
   const int segs = (K + 255) >> 8;  // 256-column segments per row
@@ -78,6 +79,7 @@ __global__ void __launch_bounds__(64)
 mxfp8_quantize_t_kernel(const __nv_bfloat16* __restrict__ x, int ldx, uint8_t* __restrict__ qT, int ldq,
                         uint8_t* __restrict__ sf, int R, int C, int C_pad, long long x_batch, long long q_batch,
                         long long sf_batch, int sf_bn) {
+  pdl_sync();   // nothing of the previous kernel is read above this line
   // blockIdx.z: independent matrices (the experts of a stacked weight) at fixed strides
   x += static_cast<size_t>(blockIdx.z) * x_batch;
   qT += static_cast<size_t>(blockIdx.z) * q_batch;
@@ -224,6 +226,7 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_sync();   // set-up above overlapped the previous kernel's tail; operands are read from here on
 
   if (warp == 0) {
     // warp-uniform loop, one elected lane issues (see the MMA warp below)
@@ -461,7 +464,7 @@ static int launch_mx(const void* A, const void* B, void* C, int M, int N, int K,
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   int grid = p.tiles_m * p.tiles_n;
   if (grid > sms) grid = sms;
-  kern<<<grid, MX_THREADS, S::TOTAL, stream>>>(tmA, tmB, C, p); kwu::count_launch();
+  launch_k(kern, dim3(grid), dim3(MX_THREADS), S::TOTAL, stream, tmA, tmB, C, p); kwu::count_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { set_last_error("gemm_mxfp8 launch: %s", cudaGetErrorString(e)); return 11; }
   return 0;
@@ -495,7 +498,7 @@ KWU_API int kwu_mxfp8_quantize(const void* x, int ldx, void* q, int ldq, void* s
   long warps = static_cast<long>(M_pad) * ((K + 255) / 256);
   long grid = (warps + 7) / 8;
   if (grid > 148 * 16) grid = 148 * 16;
-  mxfp8_quantize_kernel<<<static_cast<int>(grid), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  launch_k(mxfp8_quantize_kernel, dim3(static_cast<int>(grid)), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream), 
       (const __nv_bfloat16*)x, ldx, (uint8_t*)q, ldq, (uint8_t*)sf, M, K, M_pad, 0); kwu::count_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { set_last_error("mxfp8_quantize launch: %s", cudaGetErrorString(e)); return 11; }
@@ -508,7 +511,7 @@ KWU_API int kwu_mxfp8_quantize_t(const void* x, int ldx, void* qT, int ldq, void
   if (C <= 0) return 0;
   const int C_pad = (C + 127) / 128 * 128;
   dim3 grid((C_pad + 63) / 64, R / 32);
-  mxfp8_quantize_t_kernel<<<grid, 64, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  launch_k(mxfp8_quantize_t_kernel, dim3(grid), dim3(64), 0, reinterpret_cast<cudaStream_t>(stream), 
       (const __nv_bfloat16*)x, ldx, (uint8_t*)qT, ldq, (uint8_t*)sf, R, C, C_pad, 0, 0, 0, 0); kwu::count_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { set_last_error("mxfp8_quantize_t launch: %s", cudaGetErrorString(e)); return 11; }
@@ -532,7 +535,7 @@ KWU_API int kwu_mxfp8_quantize_w(const void* x, int ldx, void* q, int ldq, void*
   long warps = static_cast<long>(M_pad) * ((K + 255) / 256);
   long grid = (warps + 7) / 8;
   if (grid > 148 * 16) grid = 148 * 16;
-  mxfp8_quantize_kernel<<<static_cast<int>(grid), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  launch_k(mxfp8_quantize_kernel, dim3(static_cast<int>(grid)), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream), 
       (const __nv_bfloat16*)x, ldx, (uint8_t*)q, ldq, (uint8_t*)sf, M, K, M_pad, sf_bn); kwu::count_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { set_last_error("mxfp8_quantize_w launch: %s", cudaGetErrorString(e)); return 11; }
@@ -546,7 +549,7 @@ KWU_API int kwu_mxfp8_quantize_t_w(const void* x, int ldx, void* qT, int ldq, vo
   if (C <= 0) return 0;
   const int C_pad = (C + 127) / 128 * 128;
   dim3 grid((C_pad + 63) / 64, R / 32);
-  mxfp8_quantize_t_kernel<<<grid, 64, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  launch_k(mxfp8_quantize_t_kernel, dim3(grid), dim3(64), 0, reinterpret_cast<cudaStream_t>(stream), 
       (const __nv_bfloat16*)x, ldx, (uint8_t*)qT, ldq, (uint8_t*)sf, R, C, C_pad, 0, 0, 0, sf_bn); kwu::count_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { set_last_error("mxfp8_quantize_t_w launch: %s", cudaGetErrorString(e)); return 11; }
@@ -560,7 +563,7 @@ KWU_API int kwu_mxfp8_quantize_t_batched(const void* x, int ldx, void* qT, int l
   if (R % 128 || C % 128) { set_last_error("mxfp8_quantize_t_batched: R and C must be multiples of 128"); return 7; }
   if (batch <= 0) return 0;
   dim3 grid(C / 64, R / 32, batch);
-  mxfp8_quantize_t_kernel<<<grid, 64, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  launch_k(mxfp8_quantize_t_kernel, dim3(grid), dim3(64), 0, reinterpret_cast<cudaStream_t>(stream), 
       (const __nv_bfloat16*)x, ldx, (uint8_t*)qT, ldq, (uint8_t*)sf, R, C, C, static_cast<long long>(R) * ldx,
       static_cast<long long>(C) * ldq, kwu_mxfp8_sf_bytes(C, R), 0); kwu::count_launch();
   cudaError_t e = cudaGetLastError();
