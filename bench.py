@@ -236,6 +236,10 @@ def main():
                     help="auto: fused NVLink peer-memory kernels when N>1 (NCCL all-reduce if they cannot be set up)")
     ap.add_argument("--ref-attn", default="triton", help="attention backend of the reference arm")
     ap.add_argument("--no-mxfp8", action="store_true", help="bf16 linears instead of MXFP8 (diagnostic only)")
+    ap.add_argument("--ref-dtype", default="fp32", choices=["fp32", "bf16"],
+                    help="reference arm: parameter dtype (fp32 + fused AdamW is its default arm; bf16 = adamw16)")
+    ap.add_argument("--ref-compile", action="store_true",
+                    help="reference arm: per-block torch.compile in reduce-overhead mode (its harness's --compile)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

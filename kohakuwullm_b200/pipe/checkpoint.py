@@ -24,6 +24,10 @@ import torch.distributed as dist
 FORMAT_TAG = "kohakuwupipe"
 
 
+class CheckpointError(RuntimeError):
+    """The checkpoint file cannot be read (truncated, corrupt, or not a checkpoint of this format)."""
+
+
 def _world(group=None) -> int:
     return dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
 
@@ -141,11 +145,30 @@ def save(path: str, module: torch.nn.Module, optimizer=None, *, names: Mapping[s
         dist.barrier(group=group)
 
 
+def read_payload(path: str) -> dict:
+    """``torch.load`` of a checkpoint file, with every way a damaged file can fail turned into one
+    ``CheckpointError`` that names the file (a write that was cut short leaves a zip archive without its
+    central directory; a file of another kind fails in the unpickler)."""
+    import pickle
+    import zipfile
+
+    try:
+        payload = torch.load(path, map_location="cpu", weights_only=False)
+    except FileNotFoundError:
+        raise
+    except (RuntimeError, EOFError, OSError, ValueError, pickle.UnpicklingError, zipfile.BadZipFile) as exc:
+        raise CheckpointError(f"checkpoint {path} is unreadable (truncated or corrupt): "
+                              f"{type(exc).__name__}: {exc}") from exc
+    if not isinstance(payload, dict) or "state_dict" not in payload:
+        raise CheckpointError(f"checkpoint {path} holds no 'state_dict': not a checkpoint of this format")
+    return payload
+
+
 def load(path: str, module: torch.nn.Module, optimizer=None, *, names: Mapping[str, str] | None = None,
          strict: bool = True, group=None) -> dict:
     """Load the slice of a whole-model checkpoint that this module (stage) owns. Returns the payload
     without the big tensors (progress, scheduler state, ...)."""
-    payload = torch.load(path, map_location="cpu", weights_only=False)
+    payload = read_payload(path)
     names = dict(names or {})
     state = payload["state_dict"]
     local = {}

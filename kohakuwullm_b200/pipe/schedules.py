@@ -173,7 +173,10 @@ class TorchSchedule:
 
     def __init__(self, stage_modules: Sequence[torch.nn.Module], stage_indices: Sequence[int], *,
                  num_stages: int, n_micro: int, loss_fn: Callable | None, kind: str, device,
-                 input_args: Sequence[tuple], group=None):
+                 input_args: Sequence[tuple], output_args: Sequence | None = None, group=None):
+        """``input_args`` / ``output_args``: per local stage, example tensors of what it receives and returns
+        (one micro-batch). Both are given so that torch does no shape inference by running the stage: a stage
+        whose forward needs per-step state (sequence layouts) cannot be run at construction time."""
         from torch.distributed import pipelining as pp
 
         classes = {
@@ -184,8 +187,12 @@ class TorchSchedule:
         }
         if kind not in classes:
             raise ValueError(f"unknown schedule {kind!r}; choose from {sorted(classes)}")
-        stages = [pp.PipelineStage(m, i, num_stages, device, input_args=a, group=group)
-                  for m, i, a in zip(stage_modules, stage_indices, input_args)]
+        outs = list(output_args) if output_args is not None else [None] * len(stage_modules)
+        stages = []
+        for m, i, a, o in zip(stage_modules, stage_indices, input_args, outs):
+            if o is not None and isinstance(o, (tuple, list)) and len(o) == 1:
+                o = o[0]          # a stage that returns one tensor
+            stages.append(pp.PipelineStage(m, i, num_stages, device, input_args=a, output_args=o, group=group))
         cls = classes[kind]
         single = kind in ("gpipe", "1f1b")
         self.has_first = 0 in stage_indices

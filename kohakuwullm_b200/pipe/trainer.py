@@ -208,13 +208,17 @@ class PipelineTrainer:
                 out_boundary=() if local[0] == n_stages - 1 else module.boundary_example(self.plans_all[local[0] + 1]),
                 kind=schedule, group=group)
         else:
-            loss_fn = (lambda out, target: module.loss(out, int(target.reshape(-1)[0]))) \
-                if (n_stages - 1) in local else None
+            # torch decides "this schedule trains" from the presence of a loss function, on EVERY rank: a rank
+            # without one runs forward only and returns while its neighbours wait for its gradients
+            loss_fn = lambda out, target: module.loss(out, int(target.reshape(-1)[0]))  # noqa: E731
             self.schedule = TorchSchedule(
                 module.stages, local, num_stages=n_stages, n_micro=n_micro, loss_fn=loss_fn, kind=schedule,
                 device=self.device, group=group,
                 input_args=[module.first_input_example() if i == 0 else module.boundary_example(self.plans_all[i])
-                            for i in local])
+                            for i in local],
+                # what a stage hands on has the shape of what the next one receives; the last stage returns
+                # the same boundary (hidden states [+ the router-loss accumulator]) to the loss function
+                output_args=[module.boundary_example(self.plans_all[min(i + 1, n_stages - 1)]) for i in local])
         self.loop = PipelineLoop(module, self.schedule, self.optimizer, self.scheduler, scaler=scaler,
                                  callbacks=CallbackList(callbacks), max_grad_norm=max_grad_norm,
                                  global_clip=global_clip, group=group)

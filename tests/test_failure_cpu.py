@@ -1,0 +1,143 @@
+"""Failure detection on the host (no GPU involved): an exception on one rank ends the run on every rank and
+reaches every rank's ``on_exception`` hook; ranks that iterate different data are caught on the first step;
+loader state of another world size and damaged checkpoint files are refused with explicit messages."""
+
+import datetime
+import os
+import tempfile
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from kohakuwullm_b200.data.synthetic import make_pack
+from kohakuwullm_b200.models import LMBackbone, get_preset
+from kohakuwullm_b200.pipe import checkpoint as ckpt
+from kohakuwullm_b200.pipe.hooks import Callback
+from kohakuwullm_b200.pipe.trainer import PipelineTrainer
+from kohakuwullm_b200.training.parallel.pipeline import plan_for
+from kohakuwullm_b200.training.parallel.uwupipe import LMPipelineModule, verify_same_batch
+from tests.helpers import free_port
+
+CFG = dict(vocab_size=200, dim=64, depth=4, heads=2, kv_heads=1, head_dim=32, mlp_hidden=128)
+
+
+def _batch(seed=0):
+    return [make_pack(48, 8, 24, 200, seed=seed + s) for s in (1, 2, 3)]
+
+
+class _Record(Callback):
+    def __init__(self, path, rank, fail_at=None):
+        self.path, self.rank, self.fail_at = path, rank, fail_at
+
+    def on_train_batch_end(self, loop, out, batch, step):
+        if self.fail_at is not None and step == self.fail_at:
+            raise RuntimeError(f"injected failure on rank {self.rank}")
+
+    def on_exception(self, loop, exc):
+        with open(self.path, "w") as f:
+            f.write(f"{type(exc).__name__}: {exc}")
+
+
+def _failing_worker(rank, world, port, tmp):
+    import faulthandler
+    faulthandler.dump_traceback_later(120, exit=True)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    # a short collective time-out: the surviving rank's next transfer fails instead of waiting for ever
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    cfg = get_preset("B200-smoke", **CFG)
+    module = LMPipelineModule(cfg, micro_tokens=48, lr=1e-2, param_dtype=None)
+    cb = _Record(os.path.join(tmp, f"exc{rank}.txt"), rank, fail_at=2 if rank == 1 else None)
+    trainer = PipelineTrainer(module, plan_for(cfg, world, layers=[2, 2]), rank=rank, world=world, n_micro=3,
+                              schedule="1f1b", callbacks=[cb])
+    try:
+        trainer.fit((_batch() for _ in range(50)), max_steps=50)
+    except BaseException as exc:  # noqa: BLE001
+        with open(os.path.join(tmp, f"raised{rank}.txt"), "w") as f:
+            f.write(type(exc).__name__)
+    else:
+        with open(os.path.join(tmp, f"finished{rank}.txt"), "w") as f:
+            f.write("ran to the end")
+
+
+@pytest.mark.timeout(300)
+def test_exception_on_one_rank_ends_the_run_and_reaches_every_ranks_hook():
+    with tempfile.TemporaryDirectory() as tmp:
+        ctx = mp.spawn(_failing_worker, args=(2, free_port(), tmp), nprocs=2, join=False)
+        for p in ctx.processes:
+            p.join(timeout=200)
+        alive = [p for p in ctx.processes if p.is_alive()]
+        for p in alive:
+            p.kill()
+        assert not alive, "a rank kept waiting for the one that failed"
+        files = set(os.listdir(tmp))
+        assert {"exc0.txt", "exc1.txt", "raised0.txt", "raised1.txt"} <= files, files
+        assert "injected failure on rank 1" in open(os.path.join(tmp, "exc1.txt")).read()
+        assert not any(f.startswith("finished") for f in files)
+
+
+def _mismatch_worker(rank, world, port, tmp):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=30))
+    verify_same_batch(_batch(0), "cpu")          # identical data: passes
+    try:
+        verify_same_batch(_batch(100 * rank), "cpu")   # rank 1 draws other documents
+    except RuntimeError as exc:
+        with open(os.path.join(tmp, f"mismatch{rank}.txt"), "w") as f:
+            f.write(str(exc))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.timeout(120)
+def test_ranks_that_iterate_different_data_are_caught_on_the_first_step():
+    with tempfile.TemporaryDirectory() as tmp:
+        mp.spawn(_mismatch_worker, args=(2, free_port(), tmp), nprocs=2, join=True)
+        for r in (0, 1):
+            msg = open(os.path.join(tmp, f"mismatch{r}.txt")).read()
+            assert "rank 1 loaded a different batch than rank 0" in msg
+
+
+def test_loader_state_of_another_world_size_is_refused():
+    from kohakuwullm_b200.data.loader.iterative import ResumableLoader
+
+    class _Inner:
+        def state_dict(self):
+            return {"cursor": 3}
+
+        def load_state_dict(self, s):
+            self.loaded = s
+
+        def __iter__(self):
+            return iter(())
+
+    loader = ResumableLoader(_Inner())
+    state = loader.state_dict()
+    assert state["world"] == 1
+    loader.load_state_dict(state)
+    with pytest.raises(ValueError, match="saved with 4 ranks and cannot resume on 1"):
+        loader.load_state_dict({"world": 4, "positions": [{"cursor": 0}] * 4})
+
+
+def test_truncated_or_foreign_checkpoint_file_raises_a_checkpoint_error():
+    torch.manual_seed(0)
+    model = LMBackbone(get_preset("B200-smoke", **CFG))
+    with tempfile.TemporaryDirectory() as tmp:
+        path = os.path.join(tmp, "model.ckpt")
+        ckpt.save(path, model)
+        ckpt.load(path, model)                                   # the intact file loads
+        data = open(path, "rb").read()
+        with open(path, "wb") as f:                              # a write that was cut short
+            f.write(data[: len(data) // 2])
+        with pytest.raises(ckpt.CheckpointError, match="truncated or corrupt"):
+            ckpt.load(path, model)
+        with open(path, "wb") as f:                              # not a checkpoint at all
+            f.write(b"this is a text file")
+        with pytest.raises(ckpt.CheckpointError):
+            ckpt.load(path, model)
+        torch.save({"weights": 1}, path)                         # a torch file of another layout
+        with pytest.raises(ckpt.CheckpointError, match="state_dict"):
+            ckpt.load(path, model)
+        with pytest.raises(FileNotFoundError):
+            ckpt.load(os.path.join(tmp, "missing.ckpt"), model)

@@ -1,0 +1,79 @@
+"""Multi-chunk pipeline schedules (several stages per rank) on CPU / gloo: two optimizer steps through
+interleaved 1F1B and through looped breadth-first leave the same losses and the same weights as the
+single-process model. Not covered here, with the reason: the two V-placed schedules put neighbouring stages on
+one rank, and torch's neighbour handshake then sends from a rank to itself, which gloo cannot do; the
+zero-bubble family splits the backward pass with ``stage_backward_weight``, which in torch 2.11 raises on graphs
+that contain custom ``autograd.Function`` nodes (``_input_metadata`` is a legacy access pattern), and every
+kernel-backed op of this model is such a node."""
+
+import os
+import tempfile
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from kohakuwullm_b200.data.synthetic import make_pack
+from kohakuwullm_b200.models import LMBackbone, get_preset
+from kohakuwullm_b200.pipe.trainer import PipelineTrainer
+from kohakuwullm_b200.training.engine import TrainEngine
+from kohakuwullm_b200.training.parallel.pipeline import plan_for
+from kohakuwullm_b200.training.parallel.uwupipe import LMPipelineModule
+from tests.helpers import free_port
+
+CFG = dict(vocab_size=200, dim=64, depth=4, heads=2, kv_heads=1, head_dim=32, mlp_hidden=128)
+N_MICRO = 4
+
+
+def _batch():
+    return [make_pack(48, 8, 24, 200, seed=s) for s in range(1, N_MICRO + 1)]
+
+
+def _reference(steps=2):
+    torch.manual_seed(1234)
+    model = LMBackbone(get_preset("B200-smoke", **CFG))
+    eng = TrainEngine(model, lr=1e-2, max_grad_norm=1.0)
+    losses = [float(eng.step(_batch())["loss"]) for _ in range(steps)]
+    return losses, {k: v.detach().clone() for k, v in model.state_dict().items()}
+
+
+def _worker(rank, world, port, schedule, out_dir):
+    import faulthandler
+    faulthandler.dump_traceback_later(240, exit=True)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    cfg = get_preset("B200-smoke", **CFG)
+    module = LMPipelineModule(cfg, micro_tokens=48, lr=1e-2, param_dtype=None)
+    plans = plan_for(cfg, 2 * world, layers=[1, 1, 1, 1])          # four stages, two per rank
+    trainer = PipelineTrainer(module, plans, rank=rank, world=world, n_micro=N_MICRO, schedule=schedule,
+                              max_grad_norm=1.0)
+    outs = [trainer.loop.step(_batch()) for _ in range(2)]
+    state = {}
+    for stage in module.stages:
+        names = stage.global_names()
+        for k, v in stage.state_dict().items():
+            state[names.get(k, k)] = v.detach().clone()
+    torch.save({"losses": [float(o.loss) for o in outs], "state": state, "stages": trainer.local_indices},
+               os.path.join(out_dir, f"rank{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.timeout(900)
+@pytest.mark.parametrize("schedule,placement", [("interleaved-1f1b", [[0, 2], [1, 3]]),
+                                                ("looped-bfs", [[0, 2], [1, 3]])])
+def test_multi_chunk_schedule_matches_single_process(schedule, placement):
+    ref_losses, ref_state = _reference()
+    with tempfile.TemporaryDirectory() as tmp:
+        mp.spawn(_worker, args=(2, free_port(), schedule, tmp), nprocs=2, join=True)
+        parts = [torch.load(os.path.join(tmp, f"rank{r}.pt"), weights_only=False) for r in range(2)]
+    assert [p["stages"] for p in parts] == placement
+    for a, b in zip(parts[0]["losses"], ref_losses):
+        assert abs(a - b) < 5e-5, (parts[0]["losses"], ref_losses)
+    merged = {}
+    for p in parts:
+        merged.update(p["state"])
+    assert set(merged) == set(ref_state)
+    for k in ref_state:
+        torch.testing.assert_close(merged[k], ref_state[k], rtol=0, atol=5e-4, msg=k)
