@@ -92,8 +92,14 @@ class LMBackbone(nn.Module):
         from kohakuwullm_b200.models.mxfp8_swap import swap_mxfp8
 
         report = swap_mxfp8(self)
+        self.mxfp8_report = report    # census of per-token matmul work by bucket + unclaimed parameters
         if report.blocking:
             raise RuntimeError(f"MXFP8 conversion incomplete: {report.blocking}")
+        if report.unaccounted:
+            import warnings
+
+            warnings.warn(f"MXFP8 conversion: matmul-shaped parameters that no rule claimed stay 16-bit: "
+                          f"{report.unaccounted}")
         from kohakuwullm_b200.models.mxfp8_swap import wire_fused_quantisation
 
         wire_fused_quantisation(self)

@@ -63,9 +63,12 @@ class FlatAdamW:
     def _range(self, g: FlatGroup) -> tuple[int, int]:
         if self.shard is None or g.key.endswith("_ep"):  # expert-parallel shards are already rank-local
             return 0, g.total
+        # equal shards rounded UP to 8 elements (the fused kernels move 8 at a time), the last one clipped:
+        # every element has exactly one owner for any world size (total is a multiple of 1024, not of 8 * world)
         rank, world = self.shard
-        per = g.total // world
-        return rank * per, (rank + 1) * per
+        per = -(-g.total // world)
+        per = -(-per // 8) * 8
+        return min(rank * per, g.total), min((rank + 1) * per, g.total)
 
     # ------------------------------------------------------------------
     @torch.no_grad()

@@ -87,3 +87,27 @@ def test_flat_adamw_kernel_matches_cpp_oracle():
         co.adamw(p, m, v, g.cpu().reshape(-1), 0.25, 1e-2, 0.9, 0.95, 1e-8, 0.1, step)
     torch.testing.assert_close(lin.weight.detach().cpu().reshape(-1), p, rtol=1e-5, atol=1e-6)
     assert float(lin.weight.main_grad.abs().sum()) == 0.0
+
+
+def test_muon_batched_products_on_the_grouped_gemm_match_bmm():
+    """The Newton-Schulz products of a batch of equal-shape matrices run as ONE grouped tcgen05 launch each; they
+    must equal ``torch.bmm`` in fp32 to bf16 rounding, and the whole iteration must orthogonalise."""
+    from kohakuwullm_b200.ops import native
+    from kohakuwullm_b200.training.optim.muon import PHASES_GRAM, bmm_nt, newton_schulz_cubic
+
+    torch.manual_seed(0)
+    a = torch.randn(5, 256, 640, device="cuda").bfloat16()
+    g = bmm_nt(a, a)                                   # X X^T, both operands K-major
+    want = torch.bmm(a.float(), a.float().transpose(1, 2))
+    assert (g.float() - want).abs().max().item() <= 2e-2 * want.abs().max().item()
+    p = torch.randn(5, 256, 256, device="cuda").bfloat16()
+    y = bmm_nt(p, a, b_mn=True)                        # P X, X MN-major
+    want = torch.bmm(p.float(), a.float())
+    assert (y.float() - want).abs().max().item() <= 2e-2 * want.abs().max().item()
+    grads = torch.randn(6, 256, 768, device="cuda").bfloat16()
+    u = newton_schulz_cubic(grads, torch.bfloat16, phases=PHASES_GRAM)
+    ref = newton_schulz_cubic(grads.float().cpu(), torch.float32, phases=PHASES_GRAM)
+    assert (u.float().cpu() - ref).abs().max().item() < 0.05
+    sv = torch.linalg.svdvals(u.float())
+    assert sv.min() > 0.3 and sv.max() < 1.3
+    native.check_status()

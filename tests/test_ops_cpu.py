@@ -123,3 +123,48 @@ def test_mxfp8_wiring_sets_producer_flags():
 
     out = model(tok, SeqInfo.from_lengths([40, 24]))
     assert out.shape == (64, cfg.dim)
+
+
+def test_mxfp8_swap_census_buckets_and_closing_sweep():
+    """The conversion report accounts for every matmul-shaped parameter: converted work lands in ``fp8``, the
+    vocabulary head and router gates in ``never``, a refused layer in ``skipped``, a declared-but-unconverted
+    expert stack in ``unreached``, and a parameter nobody claims is listed by the closing sweep."""
+    import torch
+    from torch import nn
+
+    from kohakuwullm_b200.models import LMBackbone, get_preset
+    from kohakuwullm_b200.models.mxfp8_swap import swap_mxfp8
+
+    torch.manual_seed(0)
+    dense = LMBackbone(get_preset("B200-smoke", vocab_size=512, dim=256, depth=2, heads=4, kv_heads=2, mlp_hidden=384))
+    rep = swap_mxfp8(dense)
+    assert len(rep.modules) == 2 * 4 and not rep.blocking and not rep.unaccounted and not rep.unreached
+    per_layer = 256 * (256 + 2 * 128) + 256 * 256 + 256 * 768 + 384 * 256
+    assert rep.mac["fp8"] == 2 * per_layer and rep.mac["never"] == 512 * 256
+    assert abs(sum(rep.share(b) for b in ("fp8", "skipped", "unreached", "never")) - 1.0) < 1e-9
+    assert "mxfp8:" in str(rep) and "fp8" in str(rep)
+    # a second pass finds the layers already converted and counts them the same way
+    again = swap_mxfp8(dense)
+    assert again.mac == rep.mac and len(again.modules) == len(rep.modules)
+    # scope: everything outside it is 16-bit by choice
+    dense2 = LMBackbone(get_preset("B200-smoke", vocab_size=512, dim=256, depth=2, heads=4, kv_heads=2, mlp_hidden=384))
+    scoped = swap_mxfp8(dense2, scope=("attn",))
+    assert all(".attn." in m for m in scoped.modules) and scoped.mac["never"] > 512 * 256
+    # a refused layer (width not a multiple of 128) is 'skipped' and blocking
+    odd = LMBackbone(get_preset("B200-smoke", vocab_size=512, dim=256, depth=1, heads=4, kv_heads=2, mlp_hidden=200))
+    r3 = swap_mxfp8(odd)
+    assert r3.blocking and r3.mac["skipped"] > 0
+    # MoE: experts declared and converted at top_k per token; with convert_declared=False they are 'unreached'
+    moe_cfg = dict(vocab_size=512, dim=128, depth=2, heads=2, kv_heads=1, mlp_hidden=256, moe_every=1, moe_first_dense=1,
+                   moe_num_experts=4, moe_top_k=2, moe_num_shared=1, moe_hidden=128)
+    moe = LMBackbone(get_preset("B200-smoke", **moe_cfg))
+    r4 = swap_mxfp8(moe)
+    assert any(d.endswith("w_in") for d in r4.declared) and not r4.unaccounted
+    assert any("router" in b for b in r4.by_design)
+    moe2 = LMBackbone(get_preset("B200-smoke", **moe_cfg))
+    r5 = swap_mxfp8(moe2, convert_declared=False)
+    assert r5.unreached and r5.mac["unreached"] == 2 * (2 * 128 * 128 + 128 * 128)
+    # closing sweep: a bare matrix parameter that no rule knows about
+    dense.blocks[0].extra_matrix = nn.Parameter(torch.zeros(64, 64))
+    r6 = swap_mxfp8(dense)
+    assert r6.unaccounted == ["blocks.0.extra_matrix(64, 64)"]

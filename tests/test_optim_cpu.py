@@ -78,3 +78,106 @@ def test_low_bit_optimizers_step():
         loss.backward()
         opt.step()
         assert not torch.equal(before, model.blocks[0].attn.o_proj.weight.detach().float()), name
+
+
+def test_sharded_flat_adamw_covers_every_element_for_any_world_size():
+    """ZeRO-style shard bounds: for world sizes that do not divide the padded buffer length (3, 5, 6, 7) the
+    shards are still multiples of 8 elements, disjoint, and together cover the whole buffer."""
+    import torch
+
+    from kohakuwullm_b200.parallel.flat import FlatParameters
+    from kohakuwullm_b200.training.optim.fused_adamw import FlatAdamW
+
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(40, 56), torch.nn.Linear(56, 24))
+    for world in (1, 2, 3, 5, 6, 7, 8):
+        flat = FlatParameters(model, install_hooks=False)
+        covered = {k: torch.zeros(g.total, dtype=torch.int32) for k, g in flat.groups.items()}
+        for rank in range(world):
+            opt = FlatAdamW(flat, shard=(rank, world))
+            for k, g in flat.groups.items():
+                lo, hi = opt._range(g)
+                assert lo % 8 == 0 and (hi - lo) % 8 == 0 and 0 <= lo <= hi <= g.total
+                assert opt.state[k]["exp_avg"].numel() == hi - lo
+                covered[k][lo:hi] += 1
+        for k, c in covered.items():
+            assert bool((c == 1).all()), (world, k)
+
+
+def test_muon_newton_schulz_variants_orthogonalise_and_gram_phases_equal_direct_steps():
+    import torch
+
+    from kohakuwullm_b200.training.optim.muon import (PHASES_DIRECT, PHASES_GRAM, newton_schulz,
+                                                      newton_schulz_cubic)
+
+    torch.manual_seed(0)
+    g = torch.randn(3, 48, 160)           # a batch of wide matrices
+    direct = newton_schulz_cubic(g, torch.float32, phases=PHASES_DIRECT)
+    gram = newton_schulz_cubic(g, torch.float32, phases=PHASES_GRAM)
+    torch.testing.assert_close(gram, direct, rtol=1e-3, atol=1e-3)      # the same iteration, regrouped
+    for out in (direct, newton_schulz(g, 5, torch.float32)):
+        sv = torch.linalg.svdvals(out)
+        assert sv.min() > 0.3 and sv.max() < 1.3                       # singular values pulled towards 1
+    tall = torch.randn(160, 48)
+    out = newton_schulz_cubic(tall, torch.float32)
+    assert out.shape == tall.shape
+    torch.testing.assert_close(out, newton_schulz_cubic(tall.t().contiguous(), torch.float32).t(), rtol=1e-4, atol=1e-4)
+    # batched == one matrix at a time
+    single = torch.stack([newton_schulz_cubic(m, torch.float32) for m in g])
+    torch.testing.assert_close(direct, single, rtol=1e-4, atol=1e-4)
+
+
+def test_muonw_batches_by_shape_picks_phases_and_trains():
+    import torch
+
+    from kohakuwullm_b200.training.optim.muon import PHASES_DIRECT, PHASES_GRAM, MuonW
+
+    torch.manual_seed(1)
+    layers = torch.nn.ModuleList([torch.nn.Linear(32, 32, bias=False) for _ in range(3)]
+                                 + [torch.nn.Linear(32, 96, bias=False), torch.nn.Linear(96, 8, bias=True)])
+    hidden = [layers[i].weight for i in range(4)]
+    rest = [{"params": [layers[4].weight], "weight_decay": 0.1}, {"params": [layers[4].bias], "weight_decay": 0.0}]
+    opt = MuonW(hidden, rest, lr=1e-2, muon_lr=0.05, ns_batch_elems=2 * 32 * 32)   # two 32x32 matrices per batch
+    assert opt.phases_for((32, 32)) == PHASES_DIRECT and opt.phases_for((96, 32)) == PHASES_GRAM
+    assert opt._batch_size((32, 32)) == 2
+    x, y = torch.randn(64, 32), torch.randn(64, 8)
+
+    def loss_fn():
+        h = x
+        for i in range(3):
+            h = torch.tanh(layers[i](h))
+        return ((layers[4](torch.tanh(layers[3](h))) - y) ** 2).mean()
+
+    first = float(loss_fn())
+    for _ in range(30):
+        opt.zero_grad()
+        loss = loss_fn()
+        loss.backward()
+        opt.step()
+    assert float(loss_fn()) < 0.7 * first
+    assert "momentum_buffer" in opt.state[hidden[0]] and "exp_avg_rms" in opt.state[layers[4].weight]
+    # the same run with one matrix per batch gives the same weights: batching does not change the result
+    torch.manual_seed(1)
+    layers2 = torch.nn.ModuleList([torch.nn.Linear(32, 32, bias=False) for _ in range(3)]
+                                  + [torch.nn.Linear(32, 96, bias=False), torch.nn.Linear(96, 8, bias=True)])
+    opt2 = MuonW([layers2[i].weight for i in range(4)],
+                 [{"params": [layers2[4].weight], "weight_decay": 0.1}, {"params": [layers2[4].bias]}],
+                 lr=1e-2, muon_lr=0.05, ns_batch_elems=1)
+    h = x
+    for i in range(3):
+        h = torch.tanh(layers2[i](h))
+    ((layers2[4](torch.tanh(layers2[3](h))) - y) ** 2).mean().backward()
+    opt2.step()
+    torch.manual_seed(1)
+    layers3 = torch.nn.ModuleList([torch.nn.Linear(32, 32, bias=False) for _ in range(3)]
+                                  + [torch.nn.Linear(32, 96, bias=False), torch.nn.Linear(96, 8, bias=True)])
+    opt3 = MuonW([layers3[i].weight for i in range(4)],
+                 [{"params": [layers3[4].weight], "weight_decay": 0.1}, {"params": [layers3[4].bias]}],
+                 lr=1e-2, muon_lr=0.05)
+    h = x
+    for i in range(3):
+        h = torch.tanh(layers3[i](h))
+    ((layers3[4](torch.tanh(layers3[3](h))) - y) ** 2).mean().backward()
+    opt3.step()
+    for a, b in zip(layers2.parameters(), layers3.parameters()):
+        torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-6)
