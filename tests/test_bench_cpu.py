@@ -1,0 +1,95 @@
+"""Bench harness arithmetic that needs no GPU: contention statistics, per-step run logs, sweep classification,
+the analytic FLOP budget and the preset ladder."""
+
+import io
+import json
+import os
+import tempfile
+
+import pytest
+import torch
+
+from kohakuwullm_b200.bench import contention, flops_analytic, ladder, runlog, sweep
+
+
+def test_contention_statistics_and_power():
+    quiet = [1.0 + 0.002 * (i % 5) for i in range(200)]
+    v = contention.verdict(quiet)
+    assert v["verdict"] == "clean" and v["certifiable"]
+    shared = quiet[:190] + [1.5] * 10                    # 5 % of the samples ran behind somebody else's kernel
+    assert contention.contended_fraction(shared) == pytest.approx(0.05)
+    assert contention.verdict(shared)["verdict"] == "contended: discard"
+    # 20-microsecond work: the timer floor alone explains a 25 % spread, so no verdict is possible
+    assert not contention.spread_has_power(0.02) and contention.spread_has_power(1.0)
+    assert "too short" in contention.verdict([0.02] * 200)["verdict"]
+    assert "too short" in contention.verdict(quiet[:20])["verdict"]     # too few samples for a 1 % limit
+    assert contention.contended_fraction_min_iters() == 100
+    assert contention.percentile([1.0, 2.0, 3.0], 0.5) == 2.0
+
+
+def test_runlog_round_trip_and_clock_verdict():
+    buf = io.StringIO()
+    buf.write(runlog.HEADER + "\n")
+    elapsed, step = 0.0, 0
+    for flush in range(40):                               # 40 flushes of 10 steps, 0.5 s per step
+        pending = []
+        for _ in range(10):
+            step += 1
+            pending.append((step, step * 1000, 990, torch.tensor(990.0 * 2.5), torch.tensor(1.25), 3e-4, elapsed))
+        elapsed += 5.0
+        last = runlog.write_step_rows(buf, pending, elapsed)
+        assert last[0] == pytest.approx(2.5) and last[2] == elapsed
+    with tempfile.TemporaryDirectory() as tmp:
+        path = os.path.join(tmp, "run.csv")
+        open(path, "w").write(buf.getvalue())
+        run = runlog.load_run(path)
+    assert run["step"][-1] == 400 and isinstance(run["tokens"][0], int)
+    times = runlog.step_times(run)
+    assert len(times) >= runlog.MIN_TIMING_STEPS and all(abs(t - 0.5) < 1e-6 for t in times)
+    v = runlog.clock_verdict(run)
+    assert v["admissible"] and v["tokens_per_s"] == pytest.approx(2000.0)
+    short = {k: vals[:150] for k, vals in run.items()}
+    assert not runlog.clock_verdict(short)["admissible"]
+
+
+def test_sweep_rows_are_clean_contended_or_oom():
+    assert sweep.parse_tag("dp8_bf16_mxfp8_ckpt") == {"strategy": "dp8_ckpt", "dtype": "bf16", "optimizer": None,
+                                                      "flags": ["mxfp8", "ckpt"], "unknown": []}
+    assert sweep.parse_tag("pp4_fp16_muon_weird")["unknown"] == ["weird"]
+    with tempfile.TemporaryDirectory() as tmp:
+        rows = {"a.json": {"preset": "X", "n_gpus": 1, "tokens_per_s": 1000.0},
+                "b.json": {"preset": "X", "n_gpus": 2, "tokens_per_s": 1900.0, "step_spread": 0.4},
+                "c.json": {"preset": "X", "n_gpus": 4, "ok": False},
+                "d.json": {"config": {"model": "Y"}, "n_gpus": 1, "value": 5.0, "clocks": {"reasons": ["hw_slowdown"]}}}
+        for name, payload in rows.items():
+            json.dump(payload, open(os.path.join(tmp, name), "w"))
+        got = {r["file"]: r["status"] for r in sweep.load_rows(tmp)}
+        assert got == {"a.json": "clean", "b.json": "contended", "c.json": "oom", "d.json": "contended"}
+        assert "| c.json | X | 4 | oom | - |" in sweep.table(sweep.load_rows(tmp))
+
+
+def test_analytic_flops_agree_with_the_model_based_counter():
+    from kohakuwullm_b200.models import LMBackbone, get_preset
+    from kohakuwullm_b200.models.flops import FlopCounter
+
+    assert flops_analytic.causal_pairs_per_token(100, 100, None) == pytest.approx(50.5)
+    assert flops_analytic.causal_pairs_per_token(100, 100, 10) == pytest.approx((100 * 10 - 45) / 100)
+    for name, kw in (("B200-smoke", {}), ("Kohaku-MoE-1B", {"depth": 3, "vocab_size": 1024})):
+        cfg = get_preset(name, mxfp8=False, **kw)
+        with torch.device("meta"):
+            model = LMBackbone(cfg)
+        budget = flops_analytic.flop_budget(cfg, len_min=256, len_max=256)
+        model_flops, _ = FlopCounter(model).step_flops([256])
+        # forward + backward of GEMMs and attention (the counter charges attention backward 2x, this budget 2.5x)
+        matrix_3x = budget.gemm_fwd * 3 + budget.attn_fwd * 3
+        assert matrix_3x == pytest.approx(model_flops / 256, rel=0.02), name
+    b = flops_analytic.flop_budget("B200-dense-546M")
+    assert 0.98 < b.matrix_share < 1.0 and 3.0e9 < b.total < 4.5e9
+
+
+def test_ladder_census_counts_active_parameters():
+    rows = ladder.ladder(("Kohaku-200M", "Kohaku-MoE-1B"))
+    dense, moe = rows
+    assert not dense.sparse and dense.total == dense.active
+    assert moe.sparse and moe.active < moe.total / 3 and moe.router > 0
+    assert "Kohaku-MoE-1B" in ladder.render(rows)

@@ -208,3 +208,19 @@ def test_wide_tiles_with_tile_local_weight_scales_equal_the_128_wide_kernel(M, N
         assert torch.equal(qt2, qt)
         assert torch.equal(mx.gemm(dq, dsf, qt2, sft2, bn=bn), ref_t)
     native.check_status()
+
+
+def test_own_mxfp8_gemm_agrees_with_the_vendor_library_on_the_same_bytes():
+    """Verification layer 3: the same e4m3 bytes and the same scale buffers through cuBLASLt's block-scaled
+    product (``F.scaled_mm``, ``BlockWise1x32`` scales, ``SWIZZLE_32_4_4`` layout) and through the tcgen05 kernel.
+    Both accumulate exact products in fp32; they may differ in summation order only, so they agree to one unit
+    in the last place of the bf16 output and both sit within one unit of the fp64 product."""
+    from kohakuwullm_b200.bench import vendor
+
+    if not vendor.vendor_available():
+        pytest.skip("F.scaled_mm with block-wise scaling is not in this torch build")
+    for M, N, K in ((256, 384, 512), (512, 768, 1024)):
+        r = vendor.compare_with_vendor(M, N, K, seed=M)
+        assert r["ours_vs_vendor_max_ulp"] <= 1.0, r
+        assert r["bit_equal_share"] >= 0.99, r
+        assert r["ours_vs_fp64_max_ulp"] <= 1.0 and r["vendor_vs_fp64_max_ulp"] <= 1.0, r
