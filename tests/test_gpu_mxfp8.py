@@ -214,7 +214,8 @@ def test_own_mxfp8_gemm_agrees_with_the_vendor_library_on_the_same_bytes():
     """Verification layer 3: the same e4m3 bytes and the same scale buffers through cuBLASLt's block-scaled
     product (``F.scaled_mm``, ``BlockWise1x32`` scales, ``SWIZZLE_32_4_4`` layout) and through the tcgen05 kernel.
     Both accumulate exact products in fp32; they may differ in summation order only, so they agree to one unit
-    in the last place of the bf16 output and both sit within one unit of the fp64 product."""
+    in the last place of the bf16 output (measured: bit-equal) and both sit within two units of the fp64 product
+    (fp32 accumulation of K products, then one rounding to bf16)."""
     from kohakuwullm_b200.bench import vendor
 
     if not vendor.vendor_available():
@@ -223,4 +224,4 @@ def test_own_mxfp8_gemm_agrees_with_the_vendor_library_on_the_same_bytes():
         r = vendor.compare_with_vendor(M, N, K, seed=M)
         assert r["ours_vs_vendor_max_ulp"] <= 1.0, r
         assert r["bit_equal_share"] >= 0.99, r
-        assert r["ours_vs_fp64_max_ulp"] <= 1.0 and r["vendor_vs_fp64_max_ulp"] <= 1.0, r
+        assert r["ours_vs_fp64_max_ulp"] <= 2.0 and r["vendor_vs_fp64_max_ulp"] <= 2.0, r
