@@ -37,6 +37,10 @@ CKPT_EVERY = 1000
 RESUME = ""
 SEED = 1234
 DEVICE = "auto"
+WANDB_PROJECT = ""          # a Weights & Biases project name turns the W&B sink on (rank 0)
+WANDB_MODE = "offline"      # these machines have no network: sync the run directory later
+RUN_NAME = ""
+METRICS_JSONL = ""          # one JSON object per report
 
 
 def _synthetic_stream(vocab, rank):
@@ -83,7 +87,11 @@ def main():
         loader = build_loader("ddp", records, renderer, lambda s: tok.encode(s), rank=rank, world=world,
                               k=BATCH_TOKENS, m=BATCH_TOKENS // 16, ctx_max=CTX_MAX, seed=SEED,
                               bos=getattr(tok, "bos_token_id", None), eos=getattr(tok, "eos_token_id", None))
-    callbacks = [ThroughputCallback(interval=LOG_INTERVAL * 2)]
+    from kohakuwullm_b200.utils.reporters import build_reporter
+
+    reporter = build_reporter(WANDB_PROJECT or None, RUN_NAME or None, {"preset": PRESET}, METRICS_JSONL or None, 0,
+                              WANDB_MODE, directory=CKPT_DIR or None)
+    callbacks = [ThroughputCallback(interval=LOG_INTERVAL * 2, reporter=reporter)]
     trainer.callbacks.callbacks.extend(callbacks)
     if CKPT_DIR:
         trainer.callbacks.callbacks.append(Checkpoint(trainer, CKPT_DIR, every=CKPT_EVERY))

@@ -33,6 +33,11 @@ CKPT_EVERY = 1000
 RESUME = ""
 SEED = 1234
 BACKEND: str | None = None
+WANDB_PROJECT = ""          # a Weights & Biases project name turns the W&B sink on (rank 0)
+WANDB_MODE = "offline"      # these machines have no network: sync the run directory later
+RUN_NAME = ""
+METRICS_JSONL = ""          # one JSON object per report
+CONSOLE_INTERVAL = 0
 
 
 def main():
@@ -57,10 +62,16 @@ def main():
                      style="v" if SCHEDULE in ("zbv", "dualpipe-v") else "loop")
     log.info("plan", split=[p.num_layers for p in plans])
     log.info("plan_detail", text="\n" + describe(plans))
+    from kohakuwullm_b200.utils.reporters import build_reporter
+
+    reporter = build_reporter(WANDB_PROJECT or None, RUN_NAME or None, {"preset": PRESET, **ARCH_OVERRIDES},
+                              METRICS_JSONL or None, CONSOLE_INTERVAL, WANDB_MODE,
+                              directory=CKPT_DIR or None) if ranks.rank == 0 else None
     module = LMPipelineModule(cfg, micro_tokens=MICRO_TOKENS, lr=LR, weight_decay=WEIGHT_DECAY, seed=SEED)
     trainer = PipelineTrainer(module, plans, rank=ranks.rank, world=ranks.world_size, device=ranks.device,
                               n_micro=NUM_MICROBATCHES, schedule=SCHEDULE, max_grad_norm=MAX_GRAD_NORM,
-                              callbacks=[LossLog(LOG_INTERVAL), Throughput(LOG_INTERVAL)])
+                              callbacks=[LossLog(LOG_INTERVAL, reporter=reporter),
+                                         Throughput(LOG_INTERVAL, reporter=reporter)])
     if CKPT_DIR:
         trainer.loop.callbacks.callbacks.append(Checkpoint(trainer, CKPT_DIR, every=CKPT_EVERY))
     if RESUME:
@@ -75,6 +86,8 @@ def main():
     trainer.fit(stream(), MAX_STEPS)
     if CKPT_DIR:
         trainer.save_checkpoint(os.path.join(CKPT_DIR, "last.ckpt"))
+    if reporter is not None:
+        reporter.finish()
     shutdown()
     return trainer
 

@@ -48,7 +48,16 @@ def build_loader(kind: str, records, renderer, encode: Callable, *, rank: int = 
         return ResumableLoader(IterativePackLoader(records, renderer, encode, shard=rank * workers + worker,
                                                    shards=shards, **kw))
     if kind == "pipeline":
+        if workers > 1:
+            from kohakuwullm_b200.data.loader.workers import WorkerPackLoader
+
+            return ResumableLoader(WorkerPackLoader(records, renderer, encode, workers=workers, kind="pipeline", **kw))
         return ResumableLoader(MicroBatchedLoader(records, renderer, encode, **kw))
+    if kind == "workers":
+        # rendering, tokenisation and packing in ``workers`` child processes, one shard each
+        from kohakuwullm_b200.data.loader.workers import WorkerPackLoader
+
+        return ResumableLoader(WorkerPackLoader(records, renderer, encode, workers=workers, rank=rank, world=world, **kw))
     if kind in ("torch", "map"):
         import torch
         from torch.utils.data import DataLoader, Dataset
@@ -65,8 +74,8 @@ def build_loader(kind: str, records, renderer, encode: Callable, *, rank: int = 
 
         return DataLoader(_Docs(), batch_size=samples, shuffle=kw.pop("shuffle", True), collate_fn=collate_packed,
                           num_workers=kw.pop("num_workers", 0), generator=torch.Generator().manual_seed(kw.pop("seed", 0)))
-    raise KeyError(f"unknown loader kind {kind!r}; choose from iterative, ddp, pipeline, torch, map")
+    raise KeyError(f"unknown loader kind {kind!r}; choose from iterative, ddp, workers, pipeline, torch, map")
 
 
-for _kind in ("iterative", "ddp", "pipeline", "torch", "map"):
+for _kind in ("iterative", "ddp", "workers", "pipeline", "torch", "map"):
     LOADER.register(_kind, (lambda k: (lambda *a, **kw: build_loader(k, *a, **kw)))(_kind))

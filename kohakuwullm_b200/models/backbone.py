@@ -178,10 +178,22 @@ class LMBackbone(nn.Module):
     def update_router_bias(self, rate_scale: float = 1.0) -> dict[str, torch.Tensor]:
         """One balancing step on every router; returns stacked device stats (read them on an interval)."""
         stats: list[dict[str, torch.Tensor]] = []
-        for blk in self.blocks:
-            router = getattr(blk.mlp, "router", None)
-            if router is not None and hasattr(router, "update_bias"):
-                stats.append(router.update_bias(rate_scale))
+        routers = [r for r in (getattr(blk.mlp, "router", None) for blk in self.blocks)
+                   if r is not None and hasattr(r, "update_bias")]
+        # one collective for the whole model: routers that share (expert count, group) have their per-layer
+        # loads stacked into one (layers, experts) tensor and reduced together, instead of one all-reduce each
+        reduced: dict[int, torch.Tensor] = {}
+        pools: dict[tuple, list] = {}
+        for r in routers:
+            if hasattr(r, "wants_load_reduce") and r.wants_load_reduce():
+                pools.setdefault((r.load_accum.numel(), id(r.load_group)), []).append(r)
+        for members in pools.values():
+            stacked = torch.stack([r.load_accum for r in members])
+            torch.distributed.all_reduce(stacked, group=members[0].load_group)
+            for r, row in zip(members, stacked):
+                reduced[id(r)] = row
+        for r in routers:
+            stats.append(r.update_bias(rate_scale, reduced.get(id(r))) if id(r) in reduced else r.update_bias(rate_scale))
         if not stats:
             return {}
         return {

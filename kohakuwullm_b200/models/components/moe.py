@@ -104,12 +104,21 @@ class TopKRouter(nn.Module):
             loss = z if loss is None else loss + z
         return loss
 
+    def wants_load_reduce(self) -> bool:
+        return bool(self.reduce_load and dist.is_available() and dist.is_initialized()
+                    and dist.get_world_size(self.load_group) > 1)
+
     @torch.no_grad()
-    def update_bias(self, rate_scale: float = 1.0) -> dict[str, torch.Tensor]:
-        """Aux-loss-free balancing step; returns device-side stats (no host sync here)."""
-        load = self.load_accum.clone()
-        if self.reduce_load and dist.is_available() and dist.is_initialized() and dist.get_world_size(self.load_group) > 1:
-            dist.all_reduce(load, group=self.load_group)
+    def update_bias(self, rate_scale: float = 1.0, reduced_load: torch.Tensor | None = None) -> dict[str, torch.Tensor]:
+        """Aux-loss-free balancing step; returns device-side stats (no host sync here). ``reduced_load``: this
+        router's load already summed over the data-parallel group (the backbone reduces all routers' loads in
+        ONE collective per step and hands each its row); without it the router reduces its own."""
+        if reduced_load is not None:
+            load = reduced_load
+        else:
+            load = self.load_accum.clone()
+            if self.wants_load_reduce():
+                dist.all_reduce(load, group=self.load_group)
         mean = load.mean()
         self.expert_bias += (self.bias_update_rate * rate_scale) * torch.sign(mean - load)
         denom = mean.clamp(min=1e-9)

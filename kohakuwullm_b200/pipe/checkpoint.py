@@ -64,14 +64,44 @@ def expert_sharded_names(module: torch.nn.Module) -> set[str]:
     return {n for n, p in module.named_parameters() if getattr(p, "ep_local", False)}
 
 
+def named_state_of(optimizer, module: torch.nn.Module) -> dict:
+    """``{"named_optimizer_state": {local parameter name: state}, "step": n}`` for ANY ``torch.optim.Optimizer``:
+    the per-parameter state dicts re-keyed by the parameter's name in ``module`` (a stock optimizer keys its
+    state by position, which does not survive another stage split)."""
+    id2name = {id(p): n for n, p in module.named_parameters()}
+    named, step = {}, 0
+    for grp in optimizer.param_groups:
+        for p in grp["params"]:
+            st = optimizer.state.get(p)
+            if st and id(p) in id2name:
+                named[id2name[id(p)]] = dict(st)
+                s0 = st.get("step", 0)
+                step = max(step, int(s0.item()) if torch.is_tensor(s0) else int(s0))
+    return {"named_optimizer_state": named, "step": step}
+
+
+def load_named_state_into(optimizer, module: torch.nn.Module, named: dict) -> None:
+    """Inverse of ``named_state_of`` for a stock optimizer: state found under a parameter's name is installed."""
+    for n, p in module.named_parameters():
+        entry = named.get(n)
+        if entry is None:
+            continue
+        optimizer.state[p] = {k: (v.to(p.device) if torch.is_tensor(v) else v) for k, v in entry.items()
+                              if k != "range"}
+
+
 def gather_optimizer_state(optimizer, names: Mapping[str, str] | None = None, group=None,
-                           ep_names: set[str] | frozenset[str] = frozenset()) -> dict:
+                           ep_names: set[str] | frozenset[str] = frozenset(), module: torch.nn.Module | None = None) -> dict:
     """Whole-model-named optimizer state. ``optimizer.state_dict()`` must expose
     ``named_optimizer_state`` keyed by local parameter names (``FlatAdamW`` does). Entries of ``ep_names``
     (expert-parallel parameters: every rank owns a different slice under the same name) are concatenated in
     rank order, which is the order of the expert dimension; all others are merged by their flat ranges."""
     names = names or {}
     sd = optimizer.state_dict()
+    if "named_optimizer_state" not in sd:
+        if module is None:
+            raise ValueError("this optimizer keys its state by position; pass the module so that it can be re-keyed by name")
+        sd = named_state_of(optimizer, module)
     mine = {names.get(k, k): {kk: (vv.detach().to("cpu", copy=True) if torch.is_tensor(vv) else vv)
                               for kk, vv in v.items()}
             for k, v in sd["named_optimizer_state"].items()}
@@ -131,7 +161,7 @@ def _merge_ranges(a: dict, b: dict) -> dict:
 def save(path: str, module: torch.nn.Module, optimizer=None, *, names: Mapping[str, str] | None = None,
          global_step: int = 0, epoch: int = 0, extra: dict | None = None, group=None) -> None:
     state = gather_state_dict(module, names, group)
-    opt = gather_optimizer_state(optimizer, names, group) if optimizer is not None else None
+    opt = gather_optimizer_state(optimizer, names, group, module=module) if optimizer is not None else None
     if _rank(group) == 0:
         payload = {"state_dict": state, "optimizer_states": [opt] if opt is not None else [],
                    "global_step": int(global_step), "epoch": int(epoch),
@@ -206,5 +236,8 @@ def load(path: str, module: torch.nn.Module, optimizer=None, *, names: Mapping[s
             for k, p in ep_params.items():
                 if k in named:
                     named[k] = _local_expert_slice(named[k], p.numel(), rank, world)
-            optimizer.load_state_dict({"named_optimizer_state": named, "step": opt.get("step", 0)})
+            if "named_optimizer_state" in optimizer.state_dict():
+                optimizer.load_state_dict({"named_optimizer_state": named, "step": opt.get("step", 0)})
+            else:
+                load_named_state_into(optimizer, module, named)
     return {k: v for k, v in payload.items() if k not in ("state_dict", "optimizer_states")}

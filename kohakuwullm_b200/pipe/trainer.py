@@ -200,10 +200,17 @@ class PipelineTrainer:
         engine = engine or ("native" if schedule in ("gpipe", "1f1b") else "torch")
         if engine == "native":
             stage = module.stages[0]
+            stage_fn = stage.forward_micro if hasattr(stage, "forward_micro") else (lambda mb, *a: stage(*a))
+            loss_fn = module.loss if local[0] == n_stages - 1 else None
+            # a module may hand over a replacement that replays the stage from CUDA graphs
+            fns = module.native_stage_fns(stage, self.plans_all[local[0]], n_stages, n_micro, schedule) \
+                if hasattr(module, "native_stage_fns") else None
+            if fns is not None:
+                stage_fn, loss_fn = fns
             self.schedule = NativeSchedule(
-                stage.forward_micro if hasattr(stage, "forward_micro") else (lambda mb, *a: stage(*a)),
+                stage_fn,
                 stage_index=local[0], num_stages=n_stages, n_micro=n_micro,
-                loss_fn=module.loss if local[0] == n_stages - 1 else None,
+                loss_fn=loss_fn,
                 boundary=() if local[0] == 0 else module.boundary_example(self.plans_all[local[0]]),
                 out_boundary=() if local[0] == n_stages - 1 else module.boundary_example(self.plans_all[local[0] + 1]),
                 kind=schedule, group=group)

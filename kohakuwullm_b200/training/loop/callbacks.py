@@ -91,6 +91,11 @@ class SampleLogCallback(Callback):
             for p, t in zip(self.prompts, texts):
                 log.info("sample", step=step, prompt=p[:40], text=t[:200].replace("\n", "\\n"))
             if self.reporter:
-                self.reporter({"samples": texts}, step)
+                # a reporter with a ``samples`` method gets a table (step, name, prompt, sample, text); a plain
+                # callable gets the texts
+                if hasattr(self.reporter, "samples"):
+                    self.reporter.samples(step, [("preview", p, i, t) for i, (p, t) in enumerate(zip(self.prompts, texts))])
+                else:
+                    self.reporter({"samples": texts}, step)
         except NotImplementedError:
             self.enabled = False  # this parallel layout cannot be driven for previews

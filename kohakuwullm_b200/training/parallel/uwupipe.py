@@ -50,14 +50,18 @@ def verify_same_batch(batch: Sequence[PackedBatch], device, group=None) -> None:
 class LMPipelineModule(PipelineModule):
     def __init__(self, config: LMArchConfig, *, micro_tokens: int, lr: float = 3e-4, betas=(0.9, 0.95),
                  weight_decay: float = 0.1, param_dtype: torch.dtype | None = torch.bfloat16,
-                 seed: int = 1234, lr_schedule=None, group=None):
+                 seed: int = 1234, lr_schedule=None, group=None, cuda_graphs: bool | None = None):
+        """``cuda_graphs``: replay every stage's forward + backward of a micro-batch from CUDA graphs (default: on
+        for CUDA devices with the native kernels, single stage per rank, GPipe / 1F1B)."""
         super().__init__()
         self.config, self.micro_tokens = config, micro_tokens
         self.lr, self.betas, self.weight_decay = lr, betas, weight_decay
         self.param_dtype, self.seed, self.lr_schedule, self.group = param_dtype, seed, lr_schedule, group
         self._labels: list[torch.Tensor] = []
+        self._infos: list = []
         self._checked = False
-        self._router_scale = 1.0
+        self._router_scale = 1.0            # a device scalar once the stage exists (graphs read it in place)
+        self.cuda_graphs = cuda_graphs
 
     # ------------------------------------------------------------------ construction
     def configure_model(self, plan: StagePlan, rank: int, world: int, device) -> LMStage:
@@ -95,6 +99,22 @@ class LMPipelineModule(PipelineModule):
     def first_input_example(self):
         return (torch.zeros(self.micro_tokens, dtype=torch.long, device=self.device),)
 
+    def native_stage_fns(self, stage, plan: StagePlan, n_stages: int, n_micro: int, schedule: str):
+        """``(stage_fn, loss_fn)`` for the native GPipe / 1F1B schedule with the stage replayed from CUDA graphs,
+        or None to run it eagerly. One graph pair per micro-batch in flight on this stage."""
+        from kohakuwullm_b200.ops import native
+
+        on = self.cuda_graphs
+        if on is None:
+            on = self.device.type == "cuda" and native.available()
+        if not on or self.device.type != "cuda":
+            return None
+        from kohakuwullm_b200.training.parallel.graphed_stage import GraphedLMStage
+
+        slots = n_micro if schedule == "gpipe" else min(n_stages - plan.index - 1, n_micro) + 1
+        graphed = GraphedLMStage(self, stage, slots, self.micro_tokens)
+        return graphed, ((lambda out, mb: out) if stage.is_last else None)
+
     def global_names(self) -> dict[str, str]:
         if len(self.stages) == 1:
             return self.stages[0].global_names()
@@ -106,6 +126,7 @@ class LMPipelineModule(PipelineModule):
             verify_same_batch(batch, self.device, self.group)
             self._checked = True
         infos = [b.seq_info.to(self.device, non_blocking=True) for b in batch]
+        self._infos = infos
         for stage in self.stages:
             stage.set_seq_info(infos)
             if stage.is_first:
@@ -113,7 +134,10 @@ class LMPipelineModule(PipelineModule):
             if stage.is_last:
                 self._labels = [b.labels.to(self.device, non_blocking=True) for b in batch]
         tokens = self.step_tokens(batch)
-        self._router_scale = tokens / max(len(batch), 1)
+        scale = tokens / max(len(batch), 1)
+        if not torch.is_tensor(self._router_scale):
+            self._router_scale = torch.ones((), dtype=torch.float32, device=self.device)
+        self._router_scale.fill_(scale)
 
     def num_microbatches(self, batch) -> int:
         return len(batch)
@@ -121,15 +145,20 @@ class LMPipelineModule(PipelineModule):
     def step_tokens(self, batch) -> int:
         return sum(b.trained_tokens() for b in batch)
 
-    def loss(self, output, micro_index: int) -> torch.Tensor:
+    def loss_from(self, output, labels: torch.Tensor):
+        """``(summed loss, summed cross-entropy)`` of one micro-batch's last-stage output."""
         from kohakuwullm_b200.pipe import streams
 
         last = next(s for s in self.stages if s.is_last)
         hidden, aux = (output if isinstance(output, (tuple, list)) else (output, None))
-        loss, logs = last.head.loss(hidden, self._labels[micro_index], reduction="sum")
+        loss, logs = last.head.loss(hidden, labels, reduction="sum")
         if aux is not None:
             loss = loss + streams.reduce_accumulator(aux) * self._router_scale
-        self.log("ce_sum", logs["ce"])
+        return loss, logs["ce"]
+
+    def loss(self, output, micro_index: int) -> torch.Tensor:
+        loss, ce = self.loss_from(output, self._labels[micro_index])
+        self.log("ce_sum", ce)
         return loss
 
     def forward_backward(self, schedule, batch, n_micro: int):

@@ -121,3 +121,50 @@ def test_corpus_records_and_manifest(tmp_path):
 def test_repeat_filter():
     assert ngram_repeat_ratio(list(range(100))) == 0.0
     assert not passes_repeat_filter([1, 2, 3, 4] * 30)
+
+
+@pytest.mark.timeout(120)
+def test_worker_process_loader_matches_in_process_shards_and_resumes():
+    """Packs rendered in worker processes: the stream is the round-robin interleave of the per-worker shards the
+    in-process loader produces, it resumes exactly (consumed position, not produced), and a state written with
+    another worker count is refused."""
+    from kohakuwullm_b200.data.loader.workers import WorkerPackLoader
+
+    tok = ByteTokenizer()
+    records = ListRecords([{"text": "z" * n} for n in random.Random(2).choices(range(3, 50), k=300)])
+    kw = dict(k=64, m=16, seed=3, bos=tok.bos_token_id, eos=tok.eos_token_id)
+
+    def make(workers=2):
+        return ResumableLoader(WorkerPackLoader(records, PlainRenderer(), tok.encode, workers=workers, rank=1, world=2, **kw))
+
+    full_loader = make()
+    it = iter(full_loader)
+    full = [next(it) for _ in range(10)]
+    full_loader.loader.close()
+    # the same shards, in process: worker w of rank 1 of 2 is shard 2 + w of 4
+    shards = [iter(IterativePackLoader(records, PlainRenderer(), tok.encode, shard=2 + w, shards=4, **kw)) for w in range(2)]
+    for i, b in enumerate(full):
+        want, _ = next(shards[i % 2])
+        assert torch.equal(b.tokens, want.tokens) and torch.equal(b.labels, want.labels)
+    # resume after 5 consumed batches (the workers had produced more than that)
+    first = make()
+    it = iter(first)
+    head = [next(it) for _ in range(5)]
+    state = first.state_dict()
+    first.loader.close()
+    second = make()
+    second.load_state_dict(state)
+    it2 = iter(second)
+    tail = [next(it2) for _ in range(5)]
+    second.loader.close()
+    for a, b in zip(head + tail, full):
+        assert torch.equal(a.tokens, b.tokens)
+    with pytest.raises(ValueError, match="worker processes"):
+        make(workers=3).load_state_dict(state)
+    # a failing renderer in a worker surfaces in the trainer process
+    def broken(record, rng):
+        raise KeyError("no such field")
+
+    bad = WorkerPackLoader(records, broken, tok.encode, workers=1, **kw)
+    with pytest.raises(RuntimeError, match="loader worker 0 failed: KeyError"):
+        next(iter(bad))

@@ -54,3 +54,34 @@ def test_schedules():
     assert f(0) < f(9) <= 1.0 and abs(f(10) - 1.0) < 1e-6 and abs(f(110) - 0.1) < 1e-6
     w = build_schedule({"mode": "wsd", "warmup": 0, "end": 100, "decay_start": 80})
     assert w(50) == 1.0 and w(90) == 0.5
+
+
+def test_reporters_write_scalars_perplexity_and_sample_tables(tmp_path, monkeypatch):
+    """The metric sinks: JSONL rows carry the step and a derived perplexity; the W&B sink runs offline (no
+    network here), logs scalars and turns generated samples into a table."""
+    import json
+
+    import torch
+
+    from kohakuwullm_b200.utils.reporters import JsonlReporter, MultiReporter, WandbReporter, build_reporter
+
+    path = tmp_path / "metrics.jsonl"
+    rep = JsonlReporter(str(path))
+    rep({"train/loss": torch.tensor(2.0), "train/lr": 3e-4}, 7)
+    rep.samples(7, [("val", "once upon", 0, "once upon a time")])
+    rows = [json.loads(line) for line in path.read_text().splitlines()]
+    assert rows[0]["step"] == 7 and rows[0]["train/loss"] == 2.0
+    assert abs(rows[0]["train/ppl"] - 7.389056) < 1e-4
+    assert rows[1]["samples"][0][3] == "once upon a time"
+
+    monkeypatch.setenv("WANDB_SILENT", "true")
+    wb = WandbReporter("kwu-test", name="unit", mode="offline", directory=str(tmp_path / "wb"))
+    assert wb.run is not None and wb.run_id
+    both = MultiReporter(wb, JsonlReporter(str(tmp_path / "m2.jsonl")))
+    both({"loss": 1.5, "step": 3})
+    both.samples(3, [("val", "p", 0, "t")])
+    both.finish()
+    assert json.loads((tmp_path / "m2.jsonl").read_text().splitlines()[0])["step"] == 3
+    assert any((tmp_path / "wb").rglob("*.wandb"))            # the offline run directory exists
+    assert build_reporter() is None
+    assert isinstance(build_reporter(jsonl=str(tmp_path / "m3.jsonl"), console_interval=10), MultiReporter)
