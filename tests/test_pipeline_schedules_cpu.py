@@ -113,3 +113,19 @@ def test_pipeline_engine_trains_a_diffusion_model_and_checkpoints_a_stock_optimi
     assert {"inp.weight", "out.weight", "blocks.0.mod.weight", "blocks.3.ff.2.bias"} <= names
     named = payload["optimizer_states"][0]["named_optimizer_state"]
     assert set(named) == names and "exp_avg" in named["blocks.3.ff.2.bias"]
+
+
+@pytest.mark.timeout(300)
+@pytest.mark.parametrize("check", ["checkpoint", "gen-resume"])
+def test_dist_check_harness_passes_on_cpu_ranks(check):
+    """The stand-alone multi-process checks (run on GPUs through torchrun) end in PASS on two gloo ranks."""
+    import subprocess
+    import sys
+
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", str(free_port()), "-m", "kohakuwullm_b200.cli.dist_checks", check,
+           "--backend", "gloo"]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=280,
+                         cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
+    assert out.stdout.strip().splitlines()[-1] == "PASS"
