@@ -189,6 +189,8 @@ def run_ours(args):
     clocks = sampler.stop() if rank == 0 else {}
     native.check_status()
 
+    evidence = _multi_gpu_evidence(engine, cfg, dev, rank, world, host_packs, args) if world > 1 else {}
+
     tokens_per_step = MICRO_TOKENS * GRAD_ACCUM * world
     value = tokens_per_step * args.steps / (ms_dev / 1e3)
     e2e_value = tokens_per_step * args.steps / (max(ms_e2e, wall_e2e) / 1e3)
@@ -209,11 +211,55 @@ def run_ours(args):
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
             "gpu_launches": int(launches),
             "final_loss": losses[-1] if losses else None,
+            **evidence,
         }))
     if world > 1:
         import torch.distributed as dist
 
         dist.destroy_process_group()
+
+
+def _multi_gpu_evidence(engine, cfg, dev, rank, world, host_packs, args) -> dict:
+    """Correctness evidence a multi-GPU run carries with its number (the single-GPU test run cannot):
+
+    ``params_equal_across_ranks``  after all the steps above every rank holds bit-identical parameters (an fp64 sum
+                                   and an XOR-free integer digest of the raw bytes, all-gathered and compared);
+    ``nccl_check``                 two FRESH engines of the same seed, one on the fused peer-memory gradient step and
+                                   one on NCCL all-reduce + unsharded AdamW, run the same packs for a few steps: the
+                                   per-step losses of the two paths side by side and their largest difference.
+    """
+    import torch
+    import torch.distributed as dist
+
+    from kohakuwullm_b200.models import LMBackbone
+    from kohakuwullm_b200.training.engine import TrainEngine
+
+    out: dict = {}
+    digests = []
+    for g in engine.flat.groups.values():
+        raw = g.data.view(torch.uint8).to(torch.int64)
+        weights = torch.arange(1, raw.numel() + 1, device=dev, dtype=torch.int64) % 8191
+        digests.append(torch.stack([(raw * weights).sum(), raw.sum()]))
+    digest = torch.cat(digests)
+    gathered = [torch.empty_like(digest) for _ in range(world)]
+    dist.all_gather(gathered, digest)
+    out["params_equal_across_ranks"] = bool(all(torch.equal(gathered[0], g) for g in gathered))
+    if args.grad_sync != "fused" or args.skip_nccl_check:
+        return out
+    curves = {}
+    for mode in ("fused", "nccl"):
+        torch.manual_seed(1234)
+        with torch.device(dev):
+            model = LMBackbone(cfg)
+        eng = TrainEngine(model, lr=1e-4, param_dtype=torch.bfloat16, grad_sync=mode)
+        curve = [float(eng.step(host_packs)["loss"]) for _ in range(args.check_steps)]
+        curves[mode] = curve
+        del eng, model
+        torch.cuda.empty_cache()
+    diff = max(abs(a - b) for a, b in zip(curves["fused"], curves["nccl"]))
+    out["nccl_check"] = {"steps": args.check_steps, "fused_loss": curves["fused"], "nccl_loss": curves["nccl"],
+                         "max_abs_diff": diff, "agree": bool(diff < 5e-2)}
+    return out
 
 
 def _published_baseline():
@@ -236,6 +282,8 @@ def main():
                     help="auto: fused NVLink peer-memory kernels when N>1 (NCCL all-reduce if they cannot be set up)")
     ap.add_argument("--ref-attn", default="triton", help="attention backend of the reference arm")
     ap.add_argument("--no-mxfp8", action="store_true", help="bf16 linears instead of MXFP8 (diagnostic only)")
+    ap.add_argument("--check-steps", type=int, default=4, help="steps of the fused-vs-NCCL loss comparison (N > 1)")
+    ap.add_argument("--skip-nccl-check", action="store_true", help="N > 1: skip the fused-vs-NCCL loss comparison")
     ap.add_argument("--ref-dtype", default="fp32", choices=["fp32", "bf16"],
                     help="reference arm: parameter dtype (fp32 + fused AdamW is its default arm; bf16 = adamw16)")
     ap.add_argument("--ref-compile", action="store_true",
