@@ -56,7 +56,7 @@ def case_mxfp8(reps):
     from kohakuwullm_b200.ops import mxfp8 as mx
 
     for (M, N, K, tag) in [(8192, 8192, 8192, "square"), (4096, 1792, 1280, "qkv_fwd"), (4096, 7168, 1280, "w_in_fwd"),
-                           (4096, 1280, 3584, "w_out_fwd")]:
+                           (4096, 1280, 3584, "w_out_fwd"), (4096, 1280, 7168, "w_in_dgrad"), (4096, 1280, 1280, "o_fwd")]:
         a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
         b = torch.randn(N, K, device="cuda").to(torch.bfloat16)
         aq, asf = mx.quantize(a)
@@ -64,6 +64,15 @@ def case_mxfp8(reps):
         out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
         s = bench_samples(lambda: mx.gemm(aq, asf, bq, bsf, out=out), repeats=reps)
         _report(f"gemm_mxfp8/{tag}_{M}x{N}x{K}", s, flops=2.0 * M * N * K, bytes_moved=1.0 * (M * K + N * K) + 2.0 * M * N)
+        # the same product as a linear layer runs it: weight scales laid out for the tile width picked for (M, N)
+        bn = mx.pick_tile_width(N, M)
+        if bn != 128:
+            q2 = torch.empty(N, K, dtype=torch.uint8, device="cuda")
+            sf2 = mx.alloc_weight_sf(N, K, bn, "cuda")
+            mx.quantize_weight(b, q2, sf2, bn)
+            s = bench_samples(lambda: mx.gemm(aq, asf, q2, sf2, out=out, bn=bn), repeats=reps)
+            _report(f"gemm_mxfp8_w{bn}/{tag}_{M}x{N}x{K}", s, flops=2.0 * M * N * K,
+                    bytes_moved=1.0 * (M * K + N * K) + 2.0 * M * N)
     x = torch.randn(16384, 3584, device="cuda").to(torch.bfloat16)
     q = torch.empty(16384, 3584, dtype=torch.uint8, device="cuda")
     sf = torch.empty(mx.sf_bytes(16384, 3584), dtype=torch.uint8, device="cuda")
