@@ -60,6 +60,9 @@ def main(argv=None):
     ap.add_argument("--router-bias-std", type=float, default=0.0,
                     help="seeded N(0, std) selection bias on every router: a skewed expert load")
     ap.add_argument("--ep-capacity", type=float, default=2.0, help="expert-parallel receive capacity factor")
+    ap.add_argument("--stage-report", action="store_true",
+                    help="pipeline: per-stage busy time (CUDA events around every stage forward / backward), the "
+                         "bubble share of the step and the cost of one boundary hop")
     ap.add_argument("--set", action="append", default=[], help="config override KEY=VALUE (python literal)")
     args = ap.parse_args(argv)
 
@@ -129,9 +132,29 @@ def main(argv=None):
     from kohakuwullm_b200.ops import native
 
     native.check_status()
+    report = {}
+    if args.stage_report and args.pipeline and world > 1 and hasattr(trainer.schedule, "busy_ms"):
+        from kohakuwullm_b200.pipe.latency import hop_cost
+
+        trainer.schedule.profile = True
+        for _ in range(2):
+            step()
+        busy = trainer.schedule.busy_ms()
+        trainer.schedule.profile = False
+        mine = torch.tensor([busy["forward"] / 2, busy["backward"] / 2], device=dev)
+        every = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(every, mine)
+        hop = hop_cost(args.micro_tokens * cfg.dim * 2, dev)
+        per = ms / args.steps
+        fwd = [round(float(t[0]), 2) for t in every]
+        bwd = [round(float(t[1]), 2) for t in every]
+        report = {"stage_forward_ms": fwd, "stage_backward_ms": bwd,
+                  "stage_busy_share": [round((a + b) / per, 3) for a, b in zip(fwd, bwd)],
+                  "bubble_share_of_slowest_stage": round(1.0 - max(a + b for a, b in zip(fwd, bwd)) / per, 3),
+                  "hop_us": round(hop["seconds"] * 1e6, 1), "hop_gb_per_s": round(hop["gb_per_s"], 1)}
     if rank == 0:
         loss = out["loss"] if isinstance(out, dict) else out.loss
-        print(json.dumps({"preset": args.preset, "n_gpus": world, "mode": "pipeline" if args.pipeline and world > 1 else ("ep+dp" if args.expert_parallel and world > 1 else "dp"),
+        print(json.dumps({**report, "preset": args.preset, "n_gpus": world, "mode": "pipeline" if args.pipeline and world > 1 else ("ep+dp" if args.expert_parallel and world > 1 else "dp"),
                           "split": split, "tokens_per_step": tokens_per_step, "ms_per_step": ms / args.steps,
                           "tokens_per_s": tokens_per_step * args.steps / (ms / 1e3), "loss": float(loss),
                           "peak_mem_gib": torch.cuda.max_memory_allocated() / 2 ** 30}))

@@ -72,11 +72,15 @@ struct FlashBwdParams {
 };
 
 // ------------------------------------------------------------------------------------ dK / dV
-// smem: K tile 16 KB, V tile 16 KB, 2 stages x (Q 8 KB + dO 8 KB).
+// smem: K tile 16 KB, V tile 16 KB, 3 stages x (Q 8 KB + dO 8 KB).
 // Persistent: a CTA walks items (key tile, query head) blockIdx.x, blockIdx.x + gridDim.x, ...; barrier
 // phases run on counters that continue across items, and the producer warp loads the next item's K / V
 // and first Q / dO tiles while the current item's accumulators are being written out.
-constexpr int FBK_SMEM = 2 * 16384 + 2 * 16384 + 1024 + 1024 + 1024;
+// Inside an item the score product of query tile i + 1 is issued right after dV of tile i (the softmax warps
+// keep P in registers for their second phase, so the score columns are free by then): the softmax warps find
+// the next scores ready when they finish a tile instead of waiting for a product that starts only then.
+constexpr int FBK_STAGES = 3;
+constexpr int FBK_SMEM = 2 * 16384 + FBK_STAGES * 16384 + 2048 + 1024 + 1024;
 
 struct DkdvItem {
   int kv0, de, h, hk, q_begin, q_end, n_it;
@@ -105,22 +109,22 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* sK = smem;
   uint8_t* sV = smem + 16384;
-  uint8_t* sQ = smem + 32768;           // 2 stages x 8 KB
-  uint8_t* sDO = smem + 32768 + 16384;  // 2 stages x 8 KB
-  float* sLse = reinterpret_cast<float*>(smem + 65536);        // 2 stages x 64: -lse * log2(e)
-  float* sDelta = sLse + 128;                                  // 2 stages x 64: -delta * scale
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 65536 + 1024);
+  uint8_t* sQ = smem + 32768;                        // FBK_STAGES x 8 KB
+  uint8_t* sDO = smem + 32768 + FBK_STAGES * 8192;   // FBK_STAGES x 8 KB
+  float* sLse = reinterpret_cast<float*>(smem + 32768 + FBK_STAGES * 16384);   // per stage 64: -lse * log2(e)
+  float* sDelta = sLse + FBK_STAGES * 64;                                      // per stage 64: -delta * scale
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 32768 + FBK_STAGES * 16384 + 2048);
   uint64_t* kv_full = bars + 0;
-  uint64_t* qd_full = bars + 1;   // [2]
-  uint64_t* qd_empty = bars + 3;  // [2]
-  uint64_t* sdp_full = bars + 5;
-  uint64_t* p_ready = bars + 6;
-  uint64_t* acc_done = bars + 7;
-  uint64_t* kv_empty = bars + 8;  // the item's last products have read K and V
-  uint64_t* acc_free = bars + 9;  // the item's dK / dV accumulators have been read out
-  uint64_t* dp_full = bars + 10;   // dP^T is in TMEM (S^T has its own barrier, so the exponentials start earlier)
-  uint64_t* ds_ready = bars + 11;  // dS^T has been written (P^T has its own barrier, so dV starts earlier)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* qd_full = bars + 1;   // [3]
+  uint64_t* qd_empty = bars + 4;  // [3]
+  uint64_t* sdp_full = bars + 7;
+  uint64_t* p_ready = bars + 8;
+  uint64_t* acc_done = bars + 9;
+  uint64_t* kv_empty = bars + 10;  // the item's last products have read K and V
+  uint64_t* acc_free = bars + 11;  // the item's dK / dV accumulators have been read out
+  uint64_t* dp_full = bars + 12;   // dP^T is in TMEM (S^T has its own barrier, so the exponentials start earlier)
+  uint64_t* ds_ready = bars + 13;  // dS^T has been written (P^T has its own barrier, so dV starts earlier)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -129,7 +133,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < FBK_STAGES; ++s) {
       mbar_init(&qd_full[s], 1);
       mbar_init(&qd_empty[s], 1);
     }
@@ -175,8 +179,8 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
       const float* lse_h = p.lse + static_cast<size_t>(it.h) * p.T;
       const float* dl_h = p.delta + static_cast<size_t>(it.h) * p.T;
       for (int i = 0; i < it.n_it; ++i, ++g) {
-        const int s = g & 1;
-        const uint32_t ph = (g >> 1) & 1;
+        const int s = g % FBK_STAGES;
+        const uint32_t ph = (g / FBK_STAGES) & 1;
         const int q_lo = it.q_begin + i * 64;
         if (lane == 0) ok = mbar_wait(&qd_empty[s], ph ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_EMPTY) ? 1 : 0;
         ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -213,23 +217,33 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
       DkdvItem it;
       if (!dkdv_decode(p, item, it)) continue;
       ok = __all_sync(0xffffffffu, mbar_wait(kv_full, ic & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL));
-      for (int i = 0; i < it.n_it && ok; ++i) {
-        const int gi = g + i;
-        const int s = gi & 1;
-        const uint32_t ph = (gi >> 1) & 1;
-        ok = __all_sync(0xffffffffu, mbar_wait(&qd_full[s], ph, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL));
-        if (!ok) break;
+      // Order of the products of an item: S(0) | dP(i), [P ready] dV(i), S(i+1), [dS ready] dK(i) | ...
+      // K-major operands advance 32 bytes per 16-wide K step (+2 in the descriptor's address field),
+      // MN-major ones 2048 bytes (+128)
+      auto issue_s = [&](int gi) -> bool {
+        const int s = gi % FBK_STAGES;
+        const uint32_t ph = (gi / FBK_STAGES) & 1;
+        if (!__all_sync(0xffffffffu, mbar_wait(&qd_full[s], ph, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL)))
+          return false;
         tc_fence_after();
-        // K-major operands advance 32 bytes per 16-wide K step (+2 in the descriptor's address field),
-        // MN-major ones 2048 bytes (+128)
         const uint64_t dQk = make_smem_desc(smem_u32(sQ + s * 8192), 16, 1024, SWZ_128B);
-        const uint64_t dDOk = make_smem_desc(smem_u32(sDO + s * 8192), 16, 1024, SWZ_128B);
-        const uint64_t dQm = make_smem_desc(smem_u32(sQ + s * 8192), 8192, 1024, SWZ_128B);
-        const uint64_t dDOm = make_smem_desc(smem_u32(sDO + s * 8192), 8192, 1024, SWZ_128B);
         if (leader) {
 #pragma unroll
           for (int k = 0; k < 4; ++k) mma_f16_ss(tS, dK0 + 2 * k, dQk + 2 * k, idesc_s, k > 0 ? 1u : 0u);
-          tc_commit(sdp_full);   // the softmax warps start on S^T while dP^T is still being issued and computed
+          tc_commit(sdp_full);
+        }
+        __syncwarp();
+        return true;
+      };
+      if (ok) ok = issue_s(g);
+      for (int i = 0; i < it.n_it && ok; ++i) {
+        const int gi = g + i;
+        const int s = gi % FBK_STAGES;
+        const uint64_t dDOk = make_smem_desc(smem_u32(sDO + s * 8192), 16, 1024, SWZ_128B);
+        const uint64_t dQm = make_smem_desc(smem_u32(sQ + s * 8192), 8192, 1024, SWZ_128B);
+        const uint64_t dDOm = make_smem_desc(smem_u32(sDO + s * 8192), 8192, 1024, SWZ_128B);
+        // dP^T of this tile: its columns were last read by dK of the previous tile, issued before this
+        if (leader) {
 #pragma unroll
           for (int k = 0; k < 4; ++k) mma_f16_ss(tDP, dV0 + 2 * k, dDOk + 2 * k, idesc_s, k > 0 ? 1u : 0u);
           tc_commit(dp_full);
@@ -254,6 +268,10 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
             mma_f16_ts(tDV, tS + (k >> 1) * 32 + (k & 1) * 8, dDOm + 128 * k, idesc_a, 1u);
         }
         __syncwarp();
+        if (i + 1 < it.n_it) {
+          ok = issue_s(gi + 1);   // the score columns are free once dV (issued just above) has read P^T
+          if (!ok) break;
+        }
         ok = __all_sync(0xffffffffu, mbar_wait(ds_ready, gi & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_MISC));
         if (!ok) break;
         tc_fence_after();
@@ -292,9 +310,10 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
       for (int i = 0; i < it.n_it; ++i) {
         const int gi = g + i;
         const int q_lo = it.q_begin + i * 64;
-        const uint32_t lse_sa = smem_u32(sLse + (gi & 1) * 64), dl_sa = smem_u32(sDelta + (gi & 1) * 64);
+        const int st = gi % FBK_STAGES;
+        const uint32_t lse_sa = smem_u32(sLse + st * 64), dl_sa = smem_u32(sDelta + st * 64);
         // observe the producer's barrier directly so its smem writes are visible here
-        ok = mbar_wait(&qd_full[gi & 1], (gi >> 1) & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
+        ok = mbar_wait(&qd_full[st], (gi / FBK_STAGES) & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL);
         if (ok) ok = mbar_wait(sdp_full, gi & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_FULL);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
@@ -428,9 +447,12 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
 }
 
 // ------------------------------------------------------------------------------------ dQ
-// smem: Q 16 KB, dO 16 KB, 2 stages x (K 8 KB + V 8 KB). Persistent over (query tile, query head) items,
-// heaviest first, like the forward kernel.
-constexpr int FBQ_SMEM = 2 * 16384 + 2 * 16384 + 1024 + 1024;
+// smem: Q 16 KB, dO 16 KB, 3 stages x (K 8 KB + V 8 KB). Persistent over (query tile, query head) items,
+// heaviest first, like the forward kernel. The score accumulator is double-buffered in TMEM: S of key tile
+// j + 1 is issued while the softmax warps still work on tile j, so inside an item they never wait for a
+// score product (the chain per tile was S -> P -> dS -> dQ, one after the other).
+constexpr int FBQ_STAGES = 3;
+constexpr int FBQ_SMEM = 2 * 16384 + FBQ_STAGES * 16384 + 1024 + 1024;
 
 struct DqItem {
   int q0, de, h, hk, q_hi, lo, n_kv;
@@ -459,19 +481,19 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* sQ = smem;
   uint8_t* sDO = smem + 16384;
-  uint8_t* sK = smem + 32768;           // 2 stages x 8 KB
-  uint8_t* sV = smem + 32768 + 16384;   // 2 stages x 8 KB
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 65536);
+  uint8_t* sK = smem + 32768;                        // FBQ_STAGES x 8 KB
+  uint8_t* sV = smem + 32768 + FBQ_STAGES * 8192;    // FBQ_STAGES x 8 KB
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 32768 + FBQ_STAGES * 16384);
   uint64_t* q_full = bars + 0;
-  uint64_t* kv_full = bars + 1;   // [2]
-  uint64_t* kv_empty = bars + 3;  // [2]
-  uint64_t* sdp_full = bars + 5;
-  uint64_t* p_ready = bars + 6;
-  uint64_t* acc_done = bars + 7;
-  uint64_t* q_empty = bars + 8;   // the item's last products have read Q and dO
-  uint64_t* acc_free = bars + 9;  // the item's dQ accumulator has been read out
-  uint64_t* dp_full = bars + 10;  // dP is in TMEM (S has its own barrier, so the exponentials start earlier)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* kv_full = bars + 1;   // [3]
+  uint64_t* kv_empty = bars + 4;  // [3]
+  uint64_t* sdp_full = bars + 7;  // [2], one per score buffer: S of the next tile may complete early
+  uint64_t* p_ready = bars + 9;
+  uint64_t* acc_done = bars + 10;
+  uint64_t* q_empty = bars + 11;  // the item's last products have read Q and dO
+  uint64_t* acc_free = bars + 12; // the item's dQ accumulator has been read out
+  uint64_t* dp_full = bars + 13;  // dP is in TMEM (S has its own barrier, so the exponentials start earlier)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -480,11 +502,12 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < FBQ_STAGES; ++s) {
       mbar_init(&kv_full[s], 1);
       mbar_init(&kv_empty[s], 1);
     }
-    mbar_init(sdp_full, 1);
+    mbar_init(&sdp_full[0], 1);
+    mbar_init(&sdp_full[1], 1);
     mbar_init(p_ready, 256);
     mbar_init(dp_full, 1);
     mbar_init(acc_done, 1);
@@ -501,7 +524,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS = tmem_base, tDP = tmem_base + 64, tDQ = tmem_base + 128;
+  const uint32_t tS = tmem_base, tDP = tmem_base + 128, tDQ = tmem_base + 192;   // tS: two buffers of 64 columns
 
   if (warp == 8) {
     if (lane == 0) {
@@ -518,8 +541,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
         tma_load_2d(sQ, &tmQ128, q_full, it.h * FB_D, it.q0);
         tma_load_2d(sDO, &tmDO128, q_full, it.h * FB_D, it.q0);
         for (int j = 0; j < it.n_kv; ++j, ++g) {
-          const int s = g & 1;
-          const uint32_t ph = (g >> 1) & 1;
+          const int s = g % FBQ_STAGES;
+          const uint32_t ph = (g / FBQ_STAGES) & 1;
           if (!mbar_wait(&kv_empty[s], ph ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_EMPTY)) { ok = false; break; }
           mbar_expect_tx(&kv_full[s], 16384);
           tma_load_2d(sK + s * 8192, &tmK64, &kv_full[s], it.hk * FB_D, it.lo + j * 64);
@@ -542,24 +565,42 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
       DqItem it;
       if (!dq_decode(p, item, it)) continue;
       ok = __all_sync(0xffffffffu, mbar_wait(q_full, ic & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL));
-      for (int j = 0; j < it.n_kv && ok; ++j) {
-        const int gj = g + j;
-        const int s = gj & 1;
-        const uint32_t ph = (gj >> 1) & 1;
-        ok = __all_sync(0xffffffffu, mbar_wait(&kv_full[s], ph, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL));
-        if (!ok) break;
+      // Order of the products of an item: S(0) | dP(j), S(j+1), [softmax of tile j done] dQ(j) | ...
+      // S(j+1) goes to the other score buffer, whose last reader, dQ(j-1), was issued before it.
+      auto issue_s = [&](int gj) -> bool {
+        const int s = gj % FBQ_STAGES;
+        const uint32_t ph = (gj / FBQ_STAGES) & 1;
+        if (!__all_sync(0xffffffffu, mbar_wait(&kv_full[s], ph, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL)))
+          return false;
         tc_fence_after();
         const uint64_t dKk = make_smem_desc(smem_u32(sK + s * 8192), 16, 1024, SWZ_128B);
-        const uint64_t dVk = make_smem_desc(smem_u32(sV + s * 8192), 16, 1024, SWZ_128B);
-        const uint64_t dKm = make_smem_desc(smem_u32(sK + s * 8192), 8192, 1024, SWZ_128B);
+        const uint32_t dst = tS + (gj & 1) * 64;
         if (leader) {
 #pragma unroll
-          for (int k = 0; k < 4; ++k) mma_f16_ss(tS, dQ0 + 2 * k, dKk + 2 * k, idesc_s, k > 0 ? 1u : 0u);
-          tc_commit(sdp_full);   // the softmax warps start on S while dP is still being issued and computed
+          for (int k = 0; k < 4; ++k) mma_f16_ss(dst, dQ0 + 2 * k, dKk + 2 * k, idesc_s, k > 0 ? 1u : 0u);
+          tc_commit(&sdp_full[gj & 1]);
+        }
+        __syncwarp();
+        return true;
+      };
+      if (ok) ok = issue_s(g);
+      for (int j = 0; j < it.n_kv && ok; ++j) {
+        const int gj = g + j;
+        const int s = gj % FBQ_STAGES;
+        const uint64_t dVk = make_smem_desc(smem_u32(sV + s * 8192), 16, 1024, SWZ_128B);
+        const uint64_t dKm = make_smem_desc(smem_u32(sK + s * 8192), 8192, 1024, SWZ_128B);
+        // the softmax warps have read dP of the previous tile (its p_ready was waited for below)
+        if (leader) {
 #pragma unroll
           for (int k = 0; k < 4; ++k) mma_f16_ss(tDP, dDO0 + 2 * k, dVk + 2 * k, idesc_s, k > 0 ? 1u : 0u);
           tc_commit(dp_full);
-          if (j + 1 == it.n_kv) tc_commit(q_empty);   // Q and dO are free once these products are done
+        }
+        __syncwarp();
+        if (j + 1 < it.n_kv) {
+          ok = issue_s(gj + 1);
+          if (!ok) break;
+        } else if (leader) {
+          tc_commit(q_empty);   // Q and dO are free once the products issued so far are done
         }
         __syncwarp();
         ok = __all_sync(0xffffffffu, mbar_wait(p_ready, gj & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_MISC));
@@ -571,11 +612,12 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
         }
         tc_fence_after();
         const uint32_t acc = j > 0 ? 1u : 0u;
+        const uint32_t tSj = tS + (gj & 1) * 64;
         if (leader) {
-          mma_f16_ts(tDQ, tS, dKm, idesc_q, acc);
+          mma_f16_ts(tDQ, tSj, dKm, idesc_q, acc);
 #pragma unroll
           for (int k = 1; k < 4; ++k)
-            mma_f16_ts(tDQ, tS + (k >> 1) * 32 + (k & 1) * 8, dKm + 128 * k, idesc_q, 1u);
+            mma_f16_ts(tDQ, tSj + (k >> 1) * 32 + (k & 1) * 8, dKm + 128 * k, idesc_q, 1u);
           tc_commit(&kv_empty[s]);
         }
         __syncwarp();
@@ -605,7 +647,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
       for (int j = 0; j < it.n_kv; ++j) {
         const int gj = g + j;
         const int kv0 = it.lo + j * 64;
-        ok = mbar_wait(sdp_full, gj & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_FULL);
+        const uint32_t tSj = tS + (gj & 1) * 64;
+        ok = mbar_wait(&sdp_full[gj & 1], (gj >> 1) & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_ACC_FULL);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
@@ -618,7 +661,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
           const int c = half;
           // phase 1: P = exp2(S * c - lse) in fp32, in place of the scores
           uint32_t sv[32];
-          tmem_ld_x32(tS + lane_addr + c * 32, sv);
+          tmem_ld_x32(tSj + lane_addr + c * 32, sv);
           tmem_ld_wait();
           const uint64_t c2 = pack_f32x2(c_log2, c_log2), sc2 = pack_f32x2(p.scale, p.scale);
           const uint64_t nl2 = pack_f32x2(-lse_q, -lse_q), nd2 = pack_f32x2(-dl_q, -dl_q);
@@ -651,7 +694,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128, const __grid_con
             unpack_f32x2(mul_f32x2(pack_f32x2(__uint_as_float(sv[e]), __uint_as_float(sv[e + 1])), t2), d0, d1);
             dd[e / 2] = pack_bf16(d0, d1);
           }
-          tmem_st_x16(tS + lane_addr + c * 32, dd);
+          tmem_st_x16(tSj + lane_addr + c * 32, dd);
           tmem_st_wait();
           tc_fence_before();
           mbar_arrive(p_ready);

@@ -53,6 +53,32 @@ class NativeSchedule:
         self.next = next_rank if next_rank is not None else rank + 1
         self.first, self.last = stage_index == 0, stage_index == num_stages - 1
         self._pending: list = []
+        self.profile = False          # record a CUDA-event pair around every stage forward / backward
+        self._spans: list = []
+
+    # ------------------------------------------------------------------ stage busy time
+    def _span(self):
+        if not (self.profile and torch.cuda.is_available()):
+            return None
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        return ev
+
+    def _close(self, kind: str, start) -> None:
+        if start is not None:
+            end = torch.cuda.Event(enable_timing=True)
+            end.record()
+            self._spans.append((kind, start, end))
+
+    def busy_ms(self) -> dict:
+        """Device time spent inside stage forwards / backwards since ``profile`` was switched on (or since the
+        last call): what is left of the step time is the pipeline bubble plus exposed transfers."""
+        torch.cuda.synchronize()
+        out = {"forward": 0.0, "backward": 0.0}
+        for kind, a, b in self._spans:
+            out[kind] += a.elapsed_time(b)
+        self._spans.clear()
+        return out
 
     # ------------------------------------------------------------------ communication
     def _empty(self, spec):
@@ -95,23 +121,28 @@ class NativeSchedule:
 
     # ------------------------------------------------------------------ compute
     def _forward(self, mb: int, inputs, stash, losses):
+        t0 = self._span()
         out = self.stage_fn(mb, *inputs) if inputs is not None else self.stage_fn(mb)
         outs = _as_tuple(out)
         if self.last:
             loss = self.loss_fn(outs if len(outs) > 1 else outs[0], mb)
             losses.append(loss.detach())
             stash[mb] = (inputs, (loss,))
+            self._close("forward", t0)
             return None
         stash[mb] = (inputs, outs)
+        self._close("forward", t0)
         return [o.detach() for o in outs]
 
     def _backward(self, mb: int, grads, stash):
         inputs, outs = stash.pop(mb)
+        t0 = self._span()
         if self.last:
             outs[0].backward()
         else:
             pairs = [(o, g) for o, g in zip(outs, grads) if o.requires_grad]
             torch.autograd.backward([o for o, _ in pairs], [g for _, g in pairs])
+        self._close("backward", t0)
         if self.first or inputs is None:
             return None
         return [i.grad if i.grad is not None else torch.zeros_like(i) for i in inputs]
