@@ -31,7 +31,7 @@
 // dispatch after its combine, which follows the owner's "outputs ready" flag, which the owner raises
 // after it has copied its received rows out of the receive buffer.
 // A rank whose receive rows would exceed `cap` records KWU_ERR_EP_OVERFLOW in the status word; pairs
-// beyond the capacity are dropped (pos = -1), never written out of bounds.
+// beyond the capacity are dropped (pos = -1) and counted, never written out of bounds.
 // All waits are bounded (clock64 limit -> KWU_ERR_TIMEOUT_FLAG in the status word, kernel returns).
 // Takes the place of the all-to-all dispatch/combine around the reference's expert GEMMs
 // (src/kohakuwullm/kernels/moe/moe_dispatch.py:14-130; expert parallelism itself has no reference
@@ -104,6 +104,7 @@ struct EpPlanArgs {
   int* send_base;      // [E] first row of this rank's segment in the owner's buffer
   int* cursors;        // [E] zeroed
   long long limit_cycles;
+  int fatal_overflow;  // 1: an owner over capacity sets the overflow code; 0: the excess pairs are dropped and counted
   int* status;
 };
 
@@ -131,7 +132,7 @@ __global__ void __launch_bounds__(1024) ep_plan_kernel(const EpPlanArgs a) {
       acc += (tot + 127) / 128 * 128;
     }
     s_off[E + r] = acc;  // rows in use on owner r
-    if (acc > a.cap && a.status) atomicCAS(a.status, 0, KWU_ERR_EP_OVERFLOW);
+    if (acc > a.cap && a.status && a.fatal_overflow) atomicCAS(a.status, 0, KWU_ERR_EP_OVERFLOW);
   }
   __syncthreads();
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
@@ -168,7 +169,7 @@ __global__ void __launch_bounds__(1024) ep_plan_kernel(const EpPlanArgs a) {
 __global__ void __launch_bounds__(256)
 ep_dispatch_kernel(const EpPeers pe, const __nv_bfloat16* __restrict__ x, int ldx, const int* __restrict__ idx,
                    int n_pairs, int top_k, const int* __restrict__ send_base, int* __restrict__ cursors,
-                   int* __restrict__ pos_of, int D, int El, int cap, int rank) {
+                   int* __restrict__ pos_of, int D, int El, int cap, int rank, int* __restrict__ dropped) {
   const int lane = threadIdx.x & 31;
   const int wpb = blockDim.x >> 5;
   for (int i = blockIdx.x * wpb + (threadIdx.x >> 5); i < n_pairs; i += gridDim.x * wpb) {
@@ -177,7 +178,10 @@ ep_dispatch_kernel(const EpPeers pe, const __nv_bfloat16* __restrict__ x, int ld
     if (lane == 0) pos = send_base[e] + atomicAdd(&cursors[e], 1);
     pos = __shfl_sync(0xffffffffu, pos, 0);
     if (pos >= cap) {
-      if (lane == 0) pos_of[i] = -1;
+      if (lane == 0) {
+        pos_of[i] = -1;
+        if (dropped) atomicAdd(dropped, 1);   // pairs of this rank that found no room at their owner
+      }
       continue;
     }
     if (lane == 0) {
@@ -328,7 +332,7 @@ KWU_API int kwu_ep_flag_ints() { return EP_NUM_FLAGS * EP_MAX_WORLD; }
 KWU_API int kwu_ep_plan(const long long* table_ptrs, const long long* flag_ptrs, const long long* xrecv_ptrs,
                         const long long* yout_ptrs, const long long* meta_ptrs, const long long* ypairs_ptrs, const int* counts, int* epochs, int rank, int world, int E,
                         int cap, int* offsets, int* totals, void* tiles, int max_tiles, int* send_base,
-                        int* cursors, long long limit_cycles, void* stream, int* status) {
+                        int* cursors, long long limit_cycles, int fatal_overflow, void* stream, int* status) {
   EpPlanArgs a;
   if (!ep_fill(a.peers, table_ptrs, flag_ptrs, xrecv_ptrs, yout_ptrs, meta_ptrs, ypairs_ptrs, world)) return 7;
   if (E > EP_MAX_E || E % world) { set_last_error("ep_plan: need E <= 128 and E %% world == 0"); return 7; }
@@ -336,6 +340,7 @@ KWU_API int kwu_ep_plan(const long long* table_ptrs, const long long* flag_ptrs,
   a.offsets = offsets; a.totals = totals; a.tiles = reinterpret_cast<int4*>(tiles); a.max_tiles = max_tiles;
   a.send_base = send_base; a.cursors = cursors;
   a.limit_cycles = limit_cycles > 0 ? limit_cycles : KWU_WAIT_LIMIT_CYCLES;
+  a.fatal_overflow = fatal_overflow;
   a.status = status;
   ep_plan_kernel<<<1, 1024, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a); kwu::count_launch();
   return ep_check("ep_plan");
@@ -344,14 +349,14 @@ KWU_API int kwu_ep_plan(const long long* table_ptrs, const long long* flag_ptrs,
 KWU_API int kwu_ep_dispatch(const long long* table_ptrs, const long long* flag_ptrs, const long long* xrecv_ptrs,
                             const long long* yout_ptrs, const long long* meta_ptrs, const long long* ypairs_ptrs, int world, const void* x, int ldx, const int* idx,
                             int n_pairs, int top_k, const int* send_base, int* cursors, int* pos_of, int D, int El,
-                            int cap, int rank, void* stream) {
+                            int cap, int rank, int* dropped, void* stream) {
   EpPeers pe;
   if (!ep_fill(pe, table_ptrs, flag_ptrs, xrecv_ptrs, yout_ptrs, meta_ptrs, ypairs_ptrs, world)) return 7;
   if (D % 8) { set_last_error("ep_dispatch: D must be a multiple of 8"); return 7; }
   if (n_pairs >= (1 << 28)) { set_last_error("ep_dispatch: too many pairs for the row tags"); return 7; }
   if (n_pairs <= 0) return 0;
   ep_dispatch_kernel<<<148 * 8, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      pe, (const __nv_bfloat16*)x, ldx, idx, n_pairs, top_k, send_base, cursors, pos_of, D, El, cap, rank); kwu::count_launch();
+      pe, (const __nv_bfloat16*)x, ldx, idx, n_pairs, top_k, send_base, cursors, pos_of, D, El, cap, rank, dropped); kwu::count_launch();
   return ep_check("ep_dispatch");
 }
 

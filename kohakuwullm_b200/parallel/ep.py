@@ -56,8 +56,13 @@ class EPPlan:
 
 class ExpertParallel:
     def __init__(self, group=None, capacity_factor: float = 2.0, wait_limit_cycles: int = 0,
-                 scatter_epilogue: bool | None = None):
-        """``scatter_epilogue``: let the expert GEMM epilogues store result rows straight into the source ranks'
+                 scatter_epilogue: bool | None = None, on_overflow: str = "raise"):
+        """``on_overflow``: what a receive buffer that is too small does. ``"raise"``: the overflow code goes
+        into the status word and the next status check ends the run. ``"count"``: the excess (token, expert)
+        pairs are dropped (they contribute zero, like a capacity-limited router) and the run goes on. Either
+        way every rank counts the pairs it could not place; ``dropped_pairs()`` reads the count.
+
+        ``scatter_epilogue``: let the expert GEMM epilogues store result rows straight into the source ranks'
         per-pair buffers (no return kernel) instead of the default pull path (owner writes a peer-visible
         buffer, sources gather with coalesced peer loads). Measured on 2 B200s, MoE 991M with skewed routers:
         pull 263.0k tokens/s, scatter 231.4k: the epilogue's 64-byte row segments use the link worse than the
@@ -67,6 +72,9 @@ class ExpertParallel:
         self.rank = dist.get_rank(self.group)
         if self.world > 8:
             raise ValueError("expert parallelism over peer memory supports up to 8 ranks (one NVSwitch domain)")
+        if on_overflow not in ("raise", "count"):
+            raise ValueError(f"on_overflow must be 'raise' or 'count', not {on_overflow!r}")
+        self.on_overflow = on_overflow
         self.capacity_factor = capacity_factor
         self.limit = wait_limit_cycles
         if scatter_epilogue is None:
@@ -110,9 +118,20 @@ class ExpertParallel:
         self._ws = dict(pool=pool, table=table, flags=flags, xrecv=xrecv.view(cap, D), yout=yout.view(cap, D),
                         meta=meta, ypairs=ypairs.view(n_pairs, D), n_pairs=n_pairs,
                         pair_ids=torch.arange(n_pairs, dtype=torch.int32, device=device),
-                        tabs=tabs, epochs=epochs, cap=cap, El=El)
+                        tabs=tabs, epochs=epochs, cap=cap, El=El,
+                        dropped=torch.zeros(1, dtype=torch.int32, device=device))
         self._shape = (cap, D, E)
         return self._ws
+
+    def dropped_pairs(self, reset: bool = True) -> torch.Tensor:
+        """Device scalar: (token, expert) pairs of THIS rank that found no room at their owner since the last
+        reset, all layers together (the backward reuses the forward's placement). No host sync."""
+        if self._ws is None:
+            return torch.zeros((), dtype=torch.int32)
+        count = self._ws["dropped"].clone().reshape(())
+        if reset:
+            self._ws["dropped"].zero_()
+        return count
 
     def _barrier(self, ws, kind: int) -> None:
         L = native.require()
@@ -139,7 +158,8 @@ class ExpertParallel:
         rc = L.kwu_ep_plan(*ws["tabs"], native.ptr(counts.to(torch.int32)), native.ptr(ws["epochs"]), c_int(self.rank),
                            c_int(self.world), c_int(E), c_int(cap), native.ptr(offsets), native.ptr(totals),
                            native.ptr(tiles), c_int(max_tiles), native.ptr(send_base), native.ptr(cursors),
-                           c_ll(self.limit), native.stream_ptr(), native.ptr(native.status_word()))
+                           c_ll(self.limit), c_int(1 if self.on_overflow == "raise" else 0), native.stream_ptr(),
+                           native.ptr(native.status_word()))
         native.check(rc, "ep_plan")
         return EPPlan(offsets, totals, tiles, send_base, cursors, pos_of, idx32, cap, k, El)
 
@@ -158,7 +178,7 @@ class ExpertParallel:
         rc = L.kwu_ep_dispatch(*ws["tabs"], c_int(self.world), native.ptr(x), c_int(x.stride(0)), native.ptr(plan.idx),
                                c_int(plan.idx.numel()), c_int(plan.top_k), native.ptr(plan.send_base),
                                native.ptr(plan.cursors), native.ptr(plan.pos_of), c_int(x.shape[1]), c_int(ws["El"]),
-                               c_int(ws["cap"]), c_int(self.rank), native.stream_ptr())
+                               c_int(ws["cap"]), c_int(self.rank), native.ptr(ws["dropped"]), native.stream_ptr())
         native.check(rc, "ep_dispatch")
 
     def _take_received(self, plan, D, build_scatter_map: bool = False):

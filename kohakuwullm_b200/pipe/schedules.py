@@ -55,6 +55,34 @@ class NativeSchedule:
         self._pending: list = []
         self.profile = False          # record a CUDA-event pair around every stage forward / backward
         self._spans: list = []
+        self._links = self._make_links()
+
+    def _make_links(self) -> dict:
+        """One 2-rank group per neighbour link AND direction. NCCL runs the operations of one communicator in
+        order on one stream, so on a shared communicator a receive that was posted ahead (and cannot finish
+        before the neighbour has computed) holds back every send this rank posts after it, to either
+        neighbour; with eight stages that chained the whole pipeline together. Built only when the pipeline
+        spans the whole job, because every rank of the job has to take part in creating a group."""
+        if not dist.is_initialized() or self.S < 3:
+            return {}
+        ranks = dist.get_process_group_ranks(self.group) if self.group is not None else None
+        world = dist.get_world_size()
+        if (ranks is not None and len(ranks) != world) or self.S != world:
+            return {}
+        if self.prev != dist.get_rank(self.group) - 1 or self.next != dist.get_rank(self.group) + 1:
+            return {}     # a custom stage placement: keep the caller's group
+        ranks = ranks or list(range(world))
+        mine = {}
+        for link in range(self.S - 1):
+            for direction in ("act", "grad"):
+                g = dist.new_group([ranks[link], ranks[link + 1]])
+                if self.s in (link, link + 1):
+                    mine[(link, direction)] = g
+        return mine
+
+    def _link(self, peer_is_next: bool, direction: str):
+        link = self.s if peer_is_next else self.s - 1
+        return self._links.get((link, direction), self.group)
 
     # ------------------------------------------------------------------ stage busy time
     def _span(self):
@@ -91,7 +119,9 @@ class NativeSchedule:
         if not tensors:
             return
         bufs = [t.contiguous() for t in tensors]
-        works = dist.batch_isend_irecv([dist.P2POp(dist.isend, t, to, self.group) for t in bufs])
+        to_next = to == self.next
+        group = self._link(to_next, "act" if to_next else "grad")
+        works = dist.batch_isend_irecv([dist.P2POp(dist.isend, t, to, group) for t in bufs])
         self._pending.append((works, bufs))
 
     def _post_recv(self, frm: int, activations: bool):
@@ -99,7 +129,8 @@ class NativeSchedule:
         return a handle; ``_take`` waits for it. Posting the receive of the NEXT micro-batch before computing
         the current one lets the transfer run under that compute."""
         bufs = self._empty(self.boundary if activations else self.out_boundary)
-        works = dist.batch_isend_irecv([dist.P2POp(dist.irecv, t, frm, self.group) for t in bufs])
+        group = self._link(not activations, "act" if activations else "grad")
+        works = dist.batch_isend_irecv([dist.P2POp(dist.irecv, t, frm, group) for t in bufs])
         return bufs, works, activations
 
     @staticmethod

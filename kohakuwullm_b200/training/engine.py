@@ -128,7 +128,8 @@ class TrainEngine:
                  device: torch.device | str | None = None, lr_schedule=None,
                  cuda_graphs: bool | None = None, graph_max_docs: int | None = None,
                  graph_token_bucket: int = 512, graph_cache_size: int = 8,
-                 expert_parallel: bool | str = False, ep_capacity_factor: float = 2.0):
+                 expert_parallel: bool | str = False, ep_capacity_factor: float = 2.0,
+                 ep_on_overflow: str = "raise"):
         """``expert_parallel``: split every MoE layer's experts over the ranks of ``group`` (tokens travel
         to the owning rank over peer memory); all other parameters stay data-parallel replicas.
         ``"reference"`` keeps the sharding but moves tokens with plain collectives (test oracle).
@@ -150,7 +151,7 @@ class TrainEngine:
             from kohakuwullm_b200.parallel.ep import ExpertParallel, shard_experts
 
             if self.device.type == "cuda" and native.available() and expert_parallel != "reference":
-                self.ep = ExpertParallel(group, capacity_factor=ep_capacity_factor)
+                self.ep = ExpertParallel(group, capacity_factor=ep_capacity_factor, on_overflow=ep_on_overflow)
             shard_experts(model, self.ep, group if group is not None else dist.group.WORLD)
         if self.fused_sync:
             from kohakuwullm_b200.parallel.fused_ddp import FusedGradSync
@@ -347,4 +348,7 @@ class TrainEngine:
                "grad_norm": self._norm.reshape(()).clone(), "tokens": tok.reshape(())}
         for k, v in extra.items():
             out[k] = v * inv_tokens.reshape(())
+        if self.ep is not None:
+            # pairs this rank's tokens lost to a full receive buffer during the step (0 in a healthy run)
+            out["ep_dropped_pairs"] = self.ep.dropped_pairs(reset=True)
         return out

@@ -118,3 +118,51 @@ def test_ep_engine_steps_match_oracle():
                 assert abs(a - b) < 5e-3, (mode, got["loss"], ref["loss"])
             for a, b in zip(got["norm"], ref["norm"]):
                 assert abs(a - b) < 2e-2 * max(b, 1e-6), (mode, got["norm"], ref["norm"])
+
+
+def _overflow_worker(rank, world, port, out_dir):
+    _init(rank, world, port)
+    from kohakuwullm_b200.ops import native
+    from kohakuwullm_b200.parallel.ep import ExpertParallel, ep_routed_experts
+
+    dev = torch.device("cuda", rank)
+    T, D, H, E, k = 1024, 256, 128, 16, 4
+    El = E // world
+    g = torch.Generator(device=dev).manual_seed(21 + rank)
+    x = (torch.randn(T, D, device=dev, generator=g) * 0.5).bfloat16()
+    logits = torch.randn(T, E, device=dev, generator=g)
+    logits[:, :El] += 8.0            # every token of every rank wants the experts of rank 0
+    w, idx = torch.softmax(logits, -1).topk(k, dim=-1)
+    idx = idx.to(torch.int32)
+    counts = torch.bincount(idx.reshape(-1).long(), minlength=E).to(torch.int32)
+    gw = torch.Generator(device=dev).manual_seed(99)
+    w_in = (torch.randn(E, 2 * H, D, device=dev, generator=gw) * 0.05).bfloat16()[rank * El:(rank + 1) * El]
+    w_out = (torch.randn(E, D, H, device=dev, generator=gw) * 0.05).bfloat16()[rank * El:(rank + 1) * El]
+    out = {}
+    for factor in (0.5, 4.0):        # too small for this routing, then roomy
+        ep = ExpertParallel(capacity_factor=factor, on_overflow="count")
+        xs = x.clone().requires_grad_()
+        y = ep_routed_experts(ep, xs, idx, w, counts, w_in.clone().requires_grad_(), w_out.clone().requires_grad_())
+        y.float().sum().backward()
+        torch.cuda.synchronize()
+        native.check_status()        # counting mode leaves the status word clean
+        dropped = ep.dropped_pairs().to(torch.int64)
+        dist.all_reduce(dropped)
+        out[factor] = (int(dropped), bool(torch.isfinite(y).all()), bool(torch.isfinite(xs.grad).all()))
+    torch.save(out, os.path.join(out_dir, f"overflow_{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.multigpu
+@pytest.mark.timeout(600)
+def test_ep_overflow_is_counted_and_not_fatal_in_count_mode():
+    """A receive buffer that is too small drops the excess pairs (they contribute zero), counts them on the
+    sending ranks and leaves the status word clean; with room for everything the count is zero."""
+    world = 2
+    with tempfile.TemporaryDirectory() as tmp:
+        mp.spawn(_overflow_worker, args=(world, free_port(), tmp), nprocs=world, join=True)
+        got = torch.load(os.path.join(tmp, "overflow_0.pt"))
+    tight, roomy = got[0.5], got[4.0]
+    assert tight[0] > 0 and tight[1] and tight[2], tight
+    assert roomy[0] == 0 and roomy[1] and roomy[2], roomy

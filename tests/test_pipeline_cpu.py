@@ -87,11 +87,13 @@ def _pipe_worker(rank, world, port, schedule, layers, out_dir, load_from):
 
 
 @pytest.mark.timeout(600)
-@pytest.mark.parametrize("schedule,layers", [("1f1b", [3, 1]), ("gpipe", [2, 2])])
+@pytest.mark.parametrize("schedule,layers", [("1f1b", [3, 1]), ("gpipe", [2, 2]), ("1f1b", [1, 1, 1, 1])])
 def test_pipeline_matches_single_process(schedule, layers):
+    # four stages: every inner rank has two neighbours, each link and direction on a group of its own
     ref_losses, ref_state = _reference()
+    world = len(layers)
     with tempfile.TemporaryDirectory() as tmp:
-        mp.spawn(_pipe_worker, args=(2, free_port(), schedule, layers, tmp, None), nprocs=2, join=True)
+        mp.spawn(_pipe_worker, args=(world, free_port(), schedule, layers, tmp, None), nprocs=world, join=True)
         losses = torch.load(os.path.join(tmp, "losses.pt"))
         payload = torch.load(os.path.join(tmp, "pipe.ckpt"), weights_only=False)
     for a, b in zip(losses, ref_losses):
