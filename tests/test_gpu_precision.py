@@ -1,8 +1,10 @@
 """Kernels against FLOAT64 oracles, with bounds in units of the output type's rounding (relative RMS and ULP),
 and attention at the document lengths the benchmarks run (4096 and 16384 tokens, window 1024, sinks, GQA 5:1).
 
-The bounds are about twice what the kernels measure on a B200: an output rounded once from an fp32 accumulator
-has a mean error of a quarter ULP and a relative RMS error of ~2^-9 / sqrt(3) (1.1e-3 for bf16)."""
+An output rounded once from an fp32 accumulator has a mean error of a quarter ULP and, for bf16, a relative RMS
+error of 1.65e-3 (both measured: 0.2504 ULP, 1.655e-3); the GEMM bounds sit 10-20 % above that, so a second
+rounding anywhere in the kernel fails them. The attention bounds are about twice what the kernels measure on
+a B200 (2.0-2.5e-3 for the output and the gradients at 4096 and 16384 tokens)."""
 
 import pytest
 import torch
@@ -11,6 +13,7 @@ pytestmark = pytest.mark.gpu
 
 
 def _rel_rms(got, want):
+    got, want = got.detach(), want.detach()
     return float((got.double() - want.double()).norm() / want.double().norm().clamp(min=1e-30))
 
 
@@ -31,9 +34,10 @@ def test_bf16_gemm_is_one_rounding_from_the_fp64_product(shape):
     torch.cuda.synchronize()
     native.check_status()
     u = ulp_error(out, want)
+    print(shape, u, _rel_rms(out, want), _rel_rms(out32, want))
     assert u["mean_ulp"] < 0.30, u                       # a single round-to-nearest: 0.25
-    assert _rel_rms(out, want) < 1.6e-3, _rel_rms(out, want)
-    assert _rel_rms(out32, want) < 2e-6 * (K ** 0.5), _rel_rms(out32, want)   # fp32 accumulation over K terms
+    assert _rel_rms(out, want) < 1.8e-3, _rel_rms(out, want)
+    assert _rel_rms(out32, want) < 3e-6, _rel_rms(out32, want)                # fp32 accumulation, no output rounding (measured 0.2-1.2e-6)
 
 
 @pytest.mark.parametrize("shape,wide", [((512, 384, 256), False), ((4096, 1792, 1280), True), ((1000, 1280, 3584), True)])
@@ -60,8 +64,9 @@ def test_mxfp8_gemm_is_one_rounding_from_the_fp64_product_of_the_dequantised_ope
     torch.cuda.synchronize()
     native.check_status()
     u = ulp_error(out, want)
+    print(shape, bn, u, _rel_rms(out, want))
     assert u["mean_ulp"] < 0.30, u
-    assert _rel_rms(out, want) < 1.6e-3, _rel_rms(out, want)
+    assert _rel_rms(out, want) < 1.8e-3, _rel_rms(out, want)
 
 
 def _attention_fp64(q, k, v, do, sink, window, scale):
@@ -127,7 +132,8 @@ def test_flash_attention_at_benchmark_lengths_against_fp64(length, window, sinks
         want = _attention_fp64(q.detach(), k.detach(), v.detach(), do, sink.detach() if sinks else None, window, 0.125)
     got = (out, q.grad, k.grad[:, 0], v.grad[:, 0]) + ((sink.grad,) if sinks else ())
     names = ("out", "dq", "dk", "dv", "dsink")
-    bounds = {"out": 4e-3, "dq": 8e-3, "dk": 8e-3, "dv": 6e-3, "dsink": 8e-3}
+    bounds = {"out": 4e-3, "dq": 5e-3, "dk": 5e-3, "dv": 5e-3, "dsink": 6e-3}
     errs = {n: _rel_rms(a, b) for n, a, b in zip(names, got, want)}
+    print(length, window, sinks, errs)
     for n, e in errs.items():
         assert e < bounds[n], errs
