@@ -72,15 +72,20 @@ struct FlashBwdParams {
 };
 
 // ------------------------------------------------------------------------------------ dK / dV
-// smem: K tile 16 KB, V tile 16 KB, 3 stages x (Q 8 KB + dO 8 KB).
+// smem: 2 x K tile 16 KB, V tile 16 KB, 3 stages x (Q 8 KB + dO 8 KB).
 // Persistent: a CTA walks items (key tile, query head) blockIdx.x, blockIdx.x + gridDim.x, ...; barrier
 // phases run on counters that continue across items, and the producer warp loads the next item's K / V
 // and first Q / dO tiles while the current item's accumulators are being written out.
 // Inside an item the score product of query tile i + 1 is issued right after dV of tile i (the softmax warps
 // keep P in registers for their second phase, so the score columns are free by then): the softmax warps find
 // the next scores ready when they finish a tile instead of waiting for a product that starts only then.
+// At an item boundary the chain used to be: last dK done -> K / V of the next item loaded -> first S -> softmax
+// (about 7000 cycles on a CTA that spends 3300 per tile, so short documents paid more for the boundary than
+// for their tiles). K is double-buffered and loaded during the previous item, the item's first Q / dO tile is
+// loaded before its V, so the first S of an item is issued the moment the previous item's products are out,
+// and V (needed only for dP, one softmax phase later) arrives under that first phase.
 constexpr int FBK_STAGES = 3;
-constexpr int FBK_SMEM = 2 * 16384 + FBK_STAGES * 16384 + 2048 + 1024 + 1024;
+constexpr int FBK_SMEM = 3 * 16384 + FBK_STAGES * 16384 + 2048 + 1024 + 1024;
 
 struct DkdvItem {
   int kv0, de, h, hk, q_begin, q_end, n_it;
@@ -107,24 +112,26 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint8_t* sK = smem;
-  uint8_t* sV = smem + 16384;
-  uint8_t* sQ = smem + 32768;                        // FBK_STAGES x 8 KB
-  uint8_t* sDO = smem + 32768 + FBK_STAGES * 8192;   // FBK_STAGES x 8 KB
-  float* sLse = reinterpret_cast<float*>(smem + 32768 + FBK_STAGES * 16384);   // per stage 64: -lse * log2(e)
+  uint8_t* sK = smem;                                // 2 x 16 KB: item n in buffer n & 1
+  uint8_t* sV = smem + 32768;
+  uint8_t* sQ = smem + 49152;                        // FBK_STAGES x 8 KB
+  uint8_t* sDO = smem + 49152 + FBK_STAGES * 8192;   // FBK_STAGES x 8 KB
+  float* sLse = reinterpret_cast<float*>(smem + 49152 + FBK_STAGES * 16384);   // per stage 64: -lse * log2(e)
   float* sDelta = sLse + FBK_STAGES * 64;                                      // per stage 64: -delta * scale
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 32768 + FBK_STAGES * 16384 + 2048);
-  uint64_t* kv_full = bars + 0;
-  uint64_t* qd_full = bars + 1;   // [3]
-  uint64_t* qd_empty = bars + 4;  // [3]
-  uint64_t* sdp_full = bars + 7;
-  uint64_t* p_ready = bars + 8;
-  uint64_t* acc_done = bars + 9;
-  uint64_t* kv_empty = bars + 10;  // the item's last products have read K and V
-  uint64_t* acc_free = bars + 11;  // the item's dK / dV accumulators have been read out
-  uint64_t* dp_full = bars + 12;   // dP^T is in TMEM (S^T has its own barrier, so the exponentials start earlier)
-  uint64_t* ds_ready = bars + 13;  // dS^T has been written (P^T has its own barrier, so dV starts earlier)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 49152 + FBK_STAGES * 16384 + 2048);
+  uint64_t* k_full = bars + 0;    // [2]
+  uint64_t* k_empty = bars + 2;   // [2] the item's last products have read this K buffer
+  uint64_t* qd_full = bars + 4;   // [3]
+  uint64_t* qd_empty = bars + 7;  // [3]
+  uint64_t* sdp_full = bars + 10;
+  uint64_t* p_ready = bars + 11;
+  uint64_t* acc_done = bars + 12;
+  uint64_t* v_full = bars + 13;
+  uint64_t* v_empty = bars + 14;   // the item's last products have read V
+  uint64_t* acc_free = bars + 15;  // the item's dK / dV accumulators have been read out
+  uint64_t* dp_full = bars + 16;   // dP^T is in TMEM (S^T has its own barrier, so the exponentials start earlier)
+  uint64_t* ds_ready = bars + 17;  // dS^T has been written (P^T has its own barrier, so dV starts earlier)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -132,7 +139,12 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
   const int n_items = p.n_tiles * p.Hq;
 
   if (threadIdx.x == 0) {
-    mbar_init(kv_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+    }
+    mbar_init(v_full, 1);
+    mbar_init(v_empty, 1);
     for (int s = 0; s < FBK_STAGES; ++s) {
       mbar_init(&qd_full[s], 1);
       mbar_init(&qd_empty[s], 1);
@@ -142,7 +154,6 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
     mbar_init(dp_full, 1);
     mbar_init(ds_ready, 256);
     mbar_init(acc_done, 1);
-    mbar_init(kv_empty, 1);
     mbar_init(acc_free, 256);
     *abort_flag = 0;
     mbar_fence_init();
@@ -156,49 +167,75 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tS = tmem_base, tDP = tmem_base + 64, tDV = tmem_base + 128, tDK = tmem_base + 192;
+  // the next item of this CTA at or after round `rnd` (rounds whose slot is empty or past the list are skipped)
+  auto next_item = [&](int& rnd, DkdvItem& it) -> bool {
+    for (; rnd * static_cast<int>(gridDim.x) < n_items; ++rnd) {
+      const int item = snake_item(rnd);
+      if (item < n_items && dkdv_decode(p, item, it)) {
+        ++rnd;
+        return true;
+      }
+    }
+    return false;
+  };
 
   if (warp == 8) {
-    int g = 0, ic = 0;
+    int g = 0, ic = 0, rnd = 0;
     int ok = 1;
-    for (int rnd = 0; rnd * static_cast<int>(gridDim.x) < n_items && ok; ++rnd) {
-      const int item = snake_item(rnd);
-      if (item >= n_items) continue;
-      DkdvItem it;
-      if (!dkdv_decode(p, item, it)) continue;
+    DkdvItem it, nx;
+    bool have = next_item(rnd, it);
+    auto load_k = [&](const DkdvItem& d, int n) {   // lane 0: K of the CTA's n-th item into buffer n & 1
+      if (!mbar_wait(&k_empty[n & 1], ((n >> 1) & 1) ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_EMPTY)) return 0;
+      mbar_expect_tx(&k_full[n & 1], 16384);
+      tma_load_2d(sK + (n & 1) * 16384, &tmK128, &k_full[n & 1], d.hk * FB_D, d.kv0);
+      return 1;
+    };
+    auto load_q = [&](const DkdvItem& d, int i) {    // whole warp: the i-th Q / dO tile of item d and its statistics
+      const int s = g % FBK_STAGES;
+      const uint32_t ph = (g / FBK_STAGES) & 1;
+      const int q_lo = d.q_begin + i * 64;
+      if (lane == 0) ok = mbar_wait(&qd_empty[s], ph ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_EMPTY) ? 1 : 0;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) return;
+      const float* lse_h = p.lse + static_cast<size_t>(d.h) * p.T;
+      const float* dl_h = p.delta + static_cast<size_t>(d.h) * p.T;
+      // per-query softmax statistics of this tile, staged once for all 128 key rows
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int qc = min(q_lo + lane + 32 * u, p.T - 1);
+        sLse[s * 64 + lane + 32 * u] = -lse_h[qc] * FB_LOG2E;    // negated: they enter as FMA addends
+        sDelta[s * 64 + lane + 32 * u] = -dl_h[qc] * p.scale;
+      }
+      __syncwarp();
       if (lane == 0) {
-        ok = mbar_wait(kv_empty, (ic & 1) ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_EMPTY) ? 1 : 0;
+        mbar_expect_tx(&qd_full[s], 16384);
+        tma_load_2d(sQ + s * 8192, &tmQ64, &qd_full[s], d.h * FB_D, q_lo);
+        tma_load_2d(sDO + s * 8192, &tmDO64, &qd_full[s], d.h * FB_D, q_lo);
+      }
+      ++g;
+    };
+    if (have) {
+      if (lane == 0) ok = load_k(it, 0);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+    }
+    while (have && ok) {
+      const bool have_next = next_item(rnd, nx);
+      load_q(it, 0);                     // with K (loaded during the previous item) this is all the first S needs
+      if (!ok) break;
+      if (lane == 0) {
+        ok = mbar_wait(v_empty, (ic & 1) ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_EMPTY) ? 1 : 0;
         if (ok) {
-          mbar_expect_tx(kv_full, 32768);
-          tma_load_2d(sK, &tmK128, kv_full, it.hk * FB_D, it.kv0);
-          tma_load_2d(sV, &tmV128, kv_full, it.hk * FB_D, it.kv0);
+          mbar_expect_tx(v_full, 16384);
+          tma_load_2d(sV, &tmV128, v_full, it.hk * FB_D, it.kv0);
         }
+        if (ok && have_next) ok = load_k(nx, ic + 1);
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
+      for (int i = 1; i < it.n_it && ok; ++i) load_q(it, i);
+      it = nx;
+      have = have_next;
       ++ic;
-      const float* lse_h = p.lse + static_cast<size_t>(it.h) * p.T;
-      const float* dl_h = p.delta + static_cast<size_t>(it.h) * p.T;
-      for (int i = 0; i < it.n_it; ++i, ++g) {
-        const int s = g % FBK_STAGES;
-        const uint32_t ph = (g / FBK_STAGES) & 1;
-        const int q_lo = it.q_begin + i * 64;
-        if (lane == 0) ok = mbar_wait(&qd_empty[s], ph ^ 1, abort_flag, p.status, KWU_ERR_TIMEOUT_EMPTY) ? 1 : 0;
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) break;
-        // per-query softmax statistics of this tile, staged once for all 128 key rows
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int qc = min(q_lo + lane + 32 * u, p.T - 1);
-          sLse[s * 64 + lane + 32 * u] = -lse_h[qc] * FB_LOG2E;    // negated: they enter as FMA addends
-          sDelta[s * 64 + lane + 32 * u] = -dl_h[qc] * p.scale;
-        }
-        __syncwarp();
-        if (lane == 0) {
-          mbar_expect_tx(&qd_full[s], 16384);
-          tma_load_2d(sQ + s * 8192, &tmQ64, &qd_full[s], it.h * FB_D, q_lo);
-          tma_load_2d(sDO + s * 8192, &tmDO64, &qd_full[s], it.h * FB_D, q_lo);
-        }
-      }
     }
   } else if (warp == 9) {
     // The whole warp walks the loop, so that addresses, descriptors and loop counters stay warp-uniform
@@ -207,16 +244,13 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
     const bool leader = elect_one();
     const uint32_t idesc_s = make_idesc_f16(128, 64, 1, 0, 0);   // S^T, dP^T: N = 64 queries
     const uint32_t idesc_a = make_idesc_f16(128, 64, 1, 0, 1);   // dV, dK: B is MN-major
-    const uint64_t dK0 = make_smem_desc(smem_u32(sK), 16, 1024, SWZ_128B);
     const uint64_t dV0 = make_smem_desc(smem_u32(sV), 16, 1024, SWZ_128B);
-    int g = 0, ic = 0;
+    int g = 0, ic = 0, rnd = 0;
     bool ok = true;
-    for (int rnd = 0; rnd * static_cast<int>(gridDim.x) < n_items && ok; ++rnd) {
-      const int item = snake_item(rnd);
-      if (item >= n_items) continue;
-      DkdvItem it;
-      if (!dkdv_decode(p, item, it)) continue;
-      ok = __all_sync(0xffffffffu, mbar_wait(kv_full, ic & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL));
+    DkdvItem it;
+    while (ok && next_item(rnd, it)) {
+      const uint64_t dK0 = make_smem_desc(smem_u32(sK + (ic & 1) * 16384), 16, 1024, SWZ_128B);
+      ok = __all_sync(0xffffffffu, mbar_wait(&k_full[ic & 1], (ic >> 1) & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL));
       // Order of the products of an item: S(0) | dP(i), [P ready] dV(i), S(i+1), [dS ready] dK(i) | ...
       // K-major operands advance 32 bytes per 16-wide K step (+2 in the descriptor's address field),
       // MN-major ones 2048 bytes (+128)
@@ -242,6 +276,11 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
         const uint64_t dDOk = make_smem_desc(smem_u32(sDO + s * 8192), 16, 1024, SWZ_128B);
         const uint64_t dQm = make_smem_desc(smem_u32(sQ + s * 8192), 8192, 1024, SWZ_128B);
         const uint64_t dDOm = make_smem_desc(smem_u32(sDO + s * 8192), 8192, 1024, SWZ_128B);
+        if (i == 0) {   // V arrives after the first Q / dO tile; S(0) did not need it
+          ok = __all_sync(0xffffffffu, mbar_wait(v_full, ic & 1, abort_flag, p.status, KWU_ERR_TIMEOUT_FULL));
+          if (!ok) break;
+          tc_fence_after();
+        }
         // dP^T of this tile: its columns were last read by dK of the previous tile, issued before this
         if (leader) {
 #pragma unroll
@@ -286,7 +325,8 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
       }
       if (ok && leader) {
         tc_commit(acc_done);
-        tc_commit(kv_empty);
+        tc_commit(&k_empty[ic & 1]);
+        tc_commit(v_empty);
       }
       __syncwarp();
       g += it.n_it;

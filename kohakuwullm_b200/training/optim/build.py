@@ -18,6 +18,7 @@ from kohakuwullm_b200.registry import OPTIMIZER
 from kohakuwullm_b200.training.optim.adamw16 import AdamW16
 from kohakuwullm_b200.training.optim.lowbit_optim import StochasticAdamW
 from kohakuwullm_b200.training.optim.muon import MuonW
+from kohakuwullm_b200.training.optim.quantized_state import QuantizedStateAdamW
 from kohakuwullm_b200.training.optim.torch_fused import FusedAdamW
 
 
@@ -81,6 +82,9 @@ OPTIMIZER.register("sgd", lambda groups, **kw: torch.optim.SGD(groups, **kw))
 OPTIMIZER.register("fused_adamw", FusedAdamW)
 OPTIMIZER.register("adamw16", AdamW16)
 OPTIMIZER.register("stochastic_adamw", StochasticAdamW)
+# AdamW with quantised moments (the reference takes these three names from an optional package)
+for _name, _fmt in (("adamw8bit", "int8"), ("adamw4bit", "int4"), ("adamwfp8", "fp8")):
+    OPTIMIZER.register(_name, (lambda fmt: lambda groups, **kw: QuantizedStateAdamW(groups, state_format=fmt, **kw))(_fmt))
 
 
 def build_optimizer(model: nn.Module, name: str = "fused_adamw", lr: float = 3e-4, weight_decay: float = 0.1,

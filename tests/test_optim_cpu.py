@@ -1,6 +1,7 @@
 """Optimizers on CPU: grouping rules, FusedAdamW == torch AdamW, stochastic rounding is unbiased and
 matches its injected-draw reference, Newton-Schulz orthogonalises, low-bit casting keeps fp32 names."""
 
+import pytest
 import torch
 
 from kohakuwullm_b200.models import LMBackbone, get_preset
@@ -181,3 +182,44 @@ def test_muonw_batches_by_shape_picks_phases_and_trains():
     opt3.step()
     for a, b in zip(layers2.parameters(), layers3.parameters()):
         torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("name,rel", [("adamw8bit", 0.05), ("adamwfp8", 0.08), ("adamw4bit", 0.35)])
+def test_quantized_state_adamw_tracks_fp32_adamw(name, rel):
+    """The three quantised-moment AdamW variants against torch AdamW on a least-squares problem: the same
+    loss curve within a tolerance that widens with the coarser state, and the moments really are small."""
+    import torch
+    from kohakuwullm_b200.registry import OPTIMIZER
+    from kohakuwullm_b200.training.optim import build  # noqa: F401  registers the names
+    from kohakuwullm_b200.training.optim.quantized_state import dequantize_blocks, quantize_blocks
+
+    torch.manual_seed(0)
+    X, W_true = torch.randn(512, 96), torch.randn(96, 64)
+    Y = X @ W_true
+
+    def run(make):
+        torch.manual_seed(1)
+        w = torch.nn.Parameter(torch.zeros(96, 64))
+        b = torch.nn.Parameter(torch.zeros(64))
+        opt = make([{"params": [w], "weight_decay": 0.01}, {"params": [b], "weight_decay": 0.0}])
+        losses = []
+        for _ in range(200):
+            loss = ((X @ w + b - Y) ** 2).mean()
+            opt.zero_grad()
+            loss.backward()
+            opt.step()
+            losses.append(float(loss))
+        return losses, opt
+
+    ref, _ = run(lambda g: torch.optim.AdamW(g, lr=2e-2, betas=(0.9, 0.95)))
+    got, opt = run(lambda g: OPTIMIZER.get(name)(g, lr=2e-2, betas=(0.9, 0.95)))
+    assert got[-1] < 0.2 * got[0]
+    assert abs(got[-1] - ref[-1]) <= rel * ref[0] * 0.05 + rel * ref[-1], (name, got[-1], ref[-1])
+    full = 2 * 4 * (96 * 64 + 64)
+    assert opt.state_bytes() < (0.32 if name != "adamw4bit" else 0.2) * full + 2 * 4 * 64   # the bias keeps fp32 moments
+    # round trip of the block codecs: relative error bounded by the code spacing
+    x = torch.randn(1000) * torch.logspace(-3, 0, 1000)
+    for fmt, tol in (("int8", 0.03), ("fp8", 0.07), ("int4", 0.4)):
+        block = 128 if fmt == "int4" else 256
+        back = dequantize_blocks(quantize_blocks(x, fmt, block, True), fmt, block, True, x.shape)
+        assert float((back - x).norm() / x.norm()) < tol, fmt
