@@ -6,7 +6,11 @@ perturbs the training RNG stream. Rows that have emitted a stop id keep emitting
 ``LocalGenerator`` decodes with a static KV cache (``use_cache=False`` recomputes the whole prefix each
 step: the reference path used by the equivalence tests). ``PipelineGenerator`` decodes through the stages
 of a pipeline: rank 0 embeds and runs its blocks, every rank forwards the ``(rows, S, dim)`` hidden state
-to the next with NCCL send/recv, the last rank samples and broadcasts the next token.
+to the next with NCCL send/recv, the last rank samples and broadcasts the next token. With
+``microbatches=m`` the rows are cut into m chunks, each with a KV cache of its own on every stage, and one
+decode step runs the chunks through the stages as a forward-only GPipe wave (sends are asynchronous, so stage
+s works on chunk c + 1 while stage s + 1 works on chunk c); the last stage samples all rows at once, so the
+tokens do not depend on m. ``max_new_tokens=None`` decodes until every row has stopped or the context is full.
 Reference: src/kohakuwullm/generation/engine.py:19-385.
 """
 
@@ -62,6 +66,12 @@ def sample(logits: torch.Tensor, temperature: float = 1.0, top_k: int = 0, top_p
     return torch.multinomial(logits.softmax(-1), 1, generator=generator).squeeze(-1)
 
 
+def token_budget(max_new_tokens: int | None, prompt_len: int, max_position: int) -> int:
+    """New tokens to decode: the request, cut to what the model's context still holds (None: all of it)."""
+    room = max(int(max_position) - int(prompt_len), 0)
+    return room if max_new_tokens is None else min(int(max_new_tokens), room) if room else int(max_new_tokens)
+
+
 def advance(tokens: torch.Tensor, nxt: torch.Tensor, finished: torch.Tensor, stop_ids: Sequence[int], eos: int):
     """Append ``nxt``; rows that already finished are held at EOS. Returns (tokens, finished)."""
     nxt = torch.where(finished, torch.full_like(nxt, eos), nxt)
@@ -113,15 +123,18 @@ class LocalGenerator:
 
 
 class PipelineGenerator:
-    """Forward-only pipelined decode over ``LMStage`` slices (one KV cache per stage)."""
+    """Forward-only pipelined decode over ``LMStage`` slices: one KV cache per stage and micro-batch."""
 
-    def __init__(self, stage, rank: int, world: int, eos_id: int = 0, stop_ids: Sequence[int] = (), group=None):
+    def __init__(self, stage, rank: int, world: int, eos_id: int = 0, stop_ids: Sequence[int] = (), group=None,
+                 microbatches: int | None = None):
         self.stage, self.rank, self.world, self.group = stage, rank, world, group
         self.eos = eos_id
         self.stop_ids = tuple(stop_ids) or (eos_id,)
+        self.microbatches = microbatches
         self._gen: torch.Generator | None = None
 
-    def _forward(self, step_in, cache, rows, S, device, dtype):
+    def _forward(self, step_in, cache, rows, S, device, dtype, pending):
+        """One chunk through this rank's blocks. Returns the last stage's logits of the final position."""
         stage = self.stage
         info = cache.seq_info(torch.empty(rows, S, device=device))
         if stage.is_first:
@@ -137,26 +150,38 @@ class PipelineGenerator:
         cache.advance()
         if stage.is_last:
             return stage.head.logits(stage.final_norm(x)[:, -1])
-        dist.send(x.contiguous(), dst=self.rank + 1, group=self.group)
+        x = x.contiguous()
+        # asynchronous: this rank goes on with its next chunk while the next stage takes this one
+        pending.append((dist.isend(x, dst=self.rank + 1, group=self.group), x))
         return None
 
     @torch.no_grad()
-    def generate(self, prompt: torch.Tensor, max_new_tokens: int, **sampling) -> torch.Tensor:
+    def generate(self, prompt: torch.Tensor, max_new_tokens: int | None = 128, **sampling) -> torch.Tensor:
         stage = self.stage
         stage.eval()
         device = prompt.device
         dtype = next(p for p in stage.parameters() if p.dim() >= 2).dtype
         rows, S = prompt.shape
-        cache = KVCache(len(stage.blocks), S + max_new_tokens, static=True)
+        chunks = self.microbatches or 1
+        if rows % chunks:
+            raise ValueError(f"{rows} rows do not split into {chunks} micro-batches")
+        per = rows // chunks
+        budget = token_budget(max_new_tokens, S, getattr(stage.config, "max_position", S + (max_new_tokens or 0)))
+        caches = [KVCache(len(stage.blocks), S + budget, static=True) for _ in range(chunks)]
         if self._gen is None:
             self._gen = torch.Generator(device=device).manual_seed(SAMPLE_SEED)
         tokens = prompt
         finished = torch.zeros(rows, dtype=torch.bool, device=device)
         step_in = prompt
         last = self.world - 1
-        for _ in range(max_new_tokens):
-            logits = self._forward(step_in, cache, rows, step_in.shape[1], device, dtype)
-            nxt = sample(logits, generator=self._gen, **sampling) if self.rank == last else \
+        for _ in range(budget):
+            pending: list = []
+            logits = [self._forward(step_in[c * per:(c + 1) * per], caches[c], per, step_in.shape[1], device, dtype,
+                                    pending) for c in range(chunks)]
+            for work, _buf in pending:
+                work.wait()
+            # all rows are sampled in one call: the random stream is consumed as without micro-batches
+            nxt = sample(torch.cat(logits), generator=self._gen, **sampling) if self.rank == last else \
                 torch.empty(rows, dtype=torch.long, device=device)
             if self.world > 1:
                 dist.broadcast(nxt, src=last, group=self.group)

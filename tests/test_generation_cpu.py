@@ -80,8 +80,11 @@ def _decode_worker(rank, world, port, out_dir):
     tokens = PipelineGenerator(stage, rank, world, eos_id=-1).generate(torch.tensor(PROMPT), 12, temperature=0.0)
     sampled = PipelineGenerator(stage, rank, world, eos_id=-1).generate(torch.tensor(PROMPT), 12, temperature=0.8,
                                                                         top_k=20)
+    # one row per micro-batch: a KV cache per chunk on every stage, chunks sent on asynchronously
+    micro = PipelineGenerator(stage, rank, world, eos_id=-1, microbatches=2).generate(
+        torch.tensor(PROMPT), 12, temperature=0.8, top_k=20)
     if rank == 0:
-        torch.save({"greedy": tokens, "sampled": sampled}, os.path.join(out_dir, "decode.pt"))
+        torch.save({"greedy": tokens, "sampled": sampled, "micro": micro}, os.path.join(out_dir, "decode.pt"))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -106,3 +109,12 @@ def test_pipeline_decode_equals_local_decode_token_for_token():
         got = torch.load(os.path.join(tmp, "decode.pt"))
     assert torch.equal(got["greedy"], want)
     assert torch.equal(got["sampled"], want_sampled)   # same private RNG seed on the sampling rank
+    assert torch.equal(got["micro"], want_sampled)     # all rows are sampled in one call, whatever the chunking
+
+
+def test_token_budget():
+    from kohakuwullm_b200.generation.engine import token_budget
+
+    assert token_budget(16, 10, 8192) == 16
+    assert token_budget(None, 10, 64) == 54            # until the context is full
+    assert token_budget(100, 60, 64) == 4
