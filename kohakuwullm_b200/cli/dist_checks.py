@@ -5,6 +5,8 @@
     torchrun --nproc-per-node 2 -m kohakuwullm_b200.cli.dist_checks generate
     torchrun --nproc-per-node 2 -m kohakuwullm_b200.cli.dist_checks gen-resume
     torchrun --nproc-per-node 4 -m kohakuwullm_b200.cli.dist_checks link-bench
+    torchrun --nproc-per-node 2 -m kohakuwullm_b200.cli.dist_checks trainer-smoke
+    torchrun --nproc-per-node 2 -m kohakuwullm_b200.cli.dist_checks generate-bench --rows 8 --microbatches 4
 
 checkpoint   train under one stage split, save, load under ANOTHER split in a new trainer and compare the next
              step's loss with the uninterrupted run (weights and optimizer state are keyed by whole-model name).
@@ -12,7 +14,13 @@ generate     pipelined greedy decode equals the single-process decode of the sam
              (wide initialisation, so that the comparison can fail).
 gen-resume   a few training steps, decode, checkpoint, reload into a fresh trainer, decode again: same tokens.
 link-bench   cost of one hop between neighbouring ranks for boundary sizes from 4 KB to 128 MB.
-Reference: scripts/dist/{pp_checkpoint_smoke,pp_generate_equivalence,uwupipe_gen_resume,pp_link_bench}.py.
+trainer-smoke  the schedules named in ``--schedules`` (default: GPipe, 1F1B and, through the torch-pipelining
+             adapter, interleaved 1F1B and looped BFS) build, take three steps on one batch and give finite losses
+             that fall; all of them must give the SAME losses.
+generate-bench  milliseconds per decoded token of the pipelined decode, with and without micro-batches
+             (the tokens must be the same either way).
+Reference: scripts/dist/{pp_checkpoint_smoke,pp_generate_equivalence,uwupipe_gen_resume,pp_link_bench,pp_trainer_smoke,
+pp_torch_smoke,pp_generate_smoke,pp_generate_bench}.py.
 """
 
 from __future__ import annotations
@@ -174,7 +182,74 @@ def check_link_bench(args) -> int:
     return _finish(all(r["seconds"] > 0 for r in rows), {"check": "link-bench", "world": ranks.world_size, "hops": rows}, ranks)
 
 
-CHECKS = {"checkpoint": check_checkpoint, "generate": check_generate, "gen-resume": check_gen_resume,
+def check_trainer_smoke(args) -> int:
+    import math
+
+    from kohakuwullm_b200.models import get_preset
+    from kohakuwullm_b200.pipe.trainer import PipelineTrainer
+    from kohakuwullm_b200.training.parallel.pipeline import plan_for
+    from kohakuwullm_b200.training.parallel.uwupipe import LMPipelineModule
+
+    ranks = _setup(args.backend)
+    cfg = get_preset("B200-smoke", **{**CFG, "depth": 2 * max(ranks.world_size, 2)}, mxfp8=False)
+    dtype = torch.bfloat16 if ranks.device.type == "cuda" else None
+    report, ok = {}, True
+    for schedule in args.schedules.split(","):
+        chunks = 1 if schedule in ("gpipe", "1f1b") else 2
+        try:
+            module = LMPipelineModule(cfg, micro_tokens=64, lr=3e-3, param_dtype=dtype)
+            plans = plan_for(cfg, ranks.world_size * chunks, style="v" if schedule in ("zbv", "dualpipe-v") else "loop")
+            tr = PipelineTrainer(module, plans, rank=ranks.rank, world=ranks.world_size, device=ranks.device,
+                                 n_micro=4, schedule=schedule)
+            losses = [float(tr.loop.step(_batch(cfg, 0)).loss) for _ in range(3)]   # the same batch: it must fall
+            fine = all(math.isfinite(x) for x in losses) and min(losses[1:]) < losses[0]
+            report[schedule] = {"losses": losses, "ok": fine}
+            ok = ok and fine
+        except (RuntimeError, NotImplementedError, ValueError, AttributeError) as e:   # what torch's runtime refuses
+            if schedule in ("gpipe", "1f1b", "interleaved-1f1b", "looped-bfs"):
+                report[schedule] = {"ok": False, "error": f"{type(e).__name__}: {e}"[:300]}
+                ok = False
+            else:
+                report[schedule] = {"skipped": f"{type(e).__name__}: {e}"[:300]}
+    firsts = [r["losses"] for r in report.values() if "losses" in r]
+    same = all(max(abs(a - b) for a, b in zip(x, firsts[0])) < 1e-3 for x in firsts) if firsts else False
+    return _finish(ok and same, {"check": "trainer-smoke", "same_losses_across_schedules": same, "schedules": report}, ranks)
+
+
+def check_generate_bench(args) -> int:
+    import time
+
+    from kohakuwullm_b200.generation.engine import PipelineGenerator
+    from kohakuwullm_b200.models import get_preset
+
+    ranks = _setup(args.backend)
+    cfg = get_preset("B200-smoke", **CFG, mxfp8=False, init_std=0.3)
+    first, _ = _splits(cfg.depth, ranks.world_size)
+    tr = _trainer(cfg, ranks, first)
+    stage = tr.module.stages[0]
+    g = torch.Generator().manual_seed(3)
+    prompt = torch.randint(1, cfg.vocab_size, (args.rows, 16), generator=g).to(ranks.device)
+    rows = {}
+    tokens = {}
+    for m in sorted({1, args.microbatches}):
+        gen = PipelineGenerator(stage, ranks.rank, ranks.world_size, eos_id=-1, microbatches=m)
+        gen.generate(prompt, 4, temperature=0.0)                          # warm-up
+        if ranks.device.type == "cuda":
+            torch.cuda.synchronize()
+        if ranks.world_size > 1:
+            dist.barrier()
+        t0 = time.perf_counter()
+        tokens[m] = gen.generate(prompt, args.new_tokens, temperature=0.0).cpu()
+        if ranks.device.type == "cuda":
+            torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        rows[m] = {"ms_per_token": 1e3 * dt / args.new_tokens, "tokens_per_s": args.rows * args.new_tokens / dt}
+    same = all(torch.equal(tokens[m], tokens[1]) for m in tokens)
+    return _finish(same, {"check": "generate-bench", "rows": args.rows, "new_tokens": args.new_tokens,
+                          "by_microbatches": rows, "same_tokens": same}, ranks)
+
+
+CHECKS = {"trainer-smoke": check_trainer_smoke, "generate-bench": check_generate_bench, "checkpoint": check_checkpoint, "generate": check_generate, "gen-resume": check_gen_resume,
           "link-bench": check_link_bench}
 
 
@@ -185,6 +260,13 @@ def main(argv=None) -> int:
     ap.add_argument("--tol", type=float, default=2e-3)
     ap.add_argument("--max-bytes", type=int, default=128 << 20)
     ap.add_argument("--repeats", type=int, default=10)
+    ap.add_argument("--schedules", default="gpipe,1f1b,interleaved-1f1b,looped-bfs",
+                    help="comma list; interleaved-zb / zbv / dualpipe-v can be named, but torch 2.11's runtime fails on them "
+                         "with custom autograd functions (and on gloo a V placement sends to itself): a rank that raises "
+                         "while its neighbour waits ends the check through the watchdog, not with a report")
+    ap.add_argument("--rows", type=int, default=8)
+    ap.add_argument("--microbatches", type=int, default=4)
+    ap.add_argument("--new-tokens", type=int, default=32)
     args = ap.parse_args(argv)
     return CHECKS[args.check](args)
 

@@ -12,13 +12,17 @@ import json
 
 
 def prune_tokenizer_json(data: dict, target: int = 65536, specials: list[str] | None = None,
-                         reserved_prefix: str = "<|reserved_{}|>") -> dict:
+                         reserved_prefix: str = "<|reserved_{}|>", base: int | None = None) -> dict:
+    """``base``: how many ordinary ids to keep (default: all that fit next to the specials). With a smaller
+    ``base`` the ids between the specials and ``target`` become reserved placeholders, so a control token
+    added later is an id assignment, not a re-embedding."""
     specials = list(specials or [])
     model = data["model"]
     vocab = model["vocab"]
-    base = target - len(specials)
-    if base <= 0:
-        raise ValueError("target vocabulary is smaller than the special-token list")
+    if base is None:
+        base = target - len(specials)
+    if base <= 0 or base + len(specials) > target:
+        raise ValueError("target vocabulary is smaller than the ordinary ids plus the special-token list")
     keep = {tok: i for tok, i in vocab.items() if i < base}
     merges = []
     for m in model.get("merges", []):
@@ -48,8 +52,9 @@ def prune_tokenizer_json(data: dict, target: int = 65536, specials: list[str] | 
     return out
 
 
-def prune_file(src: str, dst: str, target: int = 65536, specials: list[str] | None = None) -> None:
+def prune_file(src: str, dst: str, target: int = 65536, specials: list[str] | None = None,
+               base: int | None = None) -> None:
     with open(src) as f:
         data = json.load(f)
     with open(dst, "w") as f:
-        json.dump(prune_tokenizer_json(data, target, specials), f, ensure_ascii=False)
+        json.dump(prune_tokenizer_json(data, target, specials, base=base), f, ensure_ascii=False)

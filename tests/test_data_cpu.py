@@ -168,3 +168,56 @@ def test_worker_process_loader_matches_in_process_shards_and_resumes():
     bad = WorkerPackLoader(records, broken, tok.encode, workers=1, **kw)
     with pytest.raises(RuntimeError, match="loader worker 0 failed: KeyError"):
         next(iter(bad))
+
+
+def test_corpus_tools_census_profile_mixture_and_chat_conversion(tmp_path):
+    import json
+
+    from kohakuwullm_b200.cli import data_tools as dt
+    from kohakuwullm_b200.data import ByteTokenizer
+    from kohakuwullm_b200.data.filters import longest_consecutive_repeat, passes_consecutive_repeat_filter, text_units
+
+    root = tmp_path / "data"
+    a, b = root / "en" / "web", root / "code" / "repo"
+    a.mkdir(parents=True)
+    b.mkdir(parents=True)
+    web = [{"text": f"document number {i} " * 5} for i in range(40)] + [{"text": "document number 3 " * 5}, {"text": " "}]
+    code = [{"text": "```python\nprint(%d)\n```" % i, "lang": "py"} for i in range(10)] + [{"text": "x" * 4000}]
+    (a / "part-0.jsonl").write_text("\n".join(json.dumps(r) for r in web) + "\n")
+    (b / "part-0.jsonl").write_text("\n".join(json.dumps(r) for r in code) + "\nnot json\n")
+    cen = dt.census(str(root))
+    assert set(cen) == {"en/web", "code/repo"}
+    assert cen["en/web"]["rows"] == 42 and abs(cen["en/web"]["dup_frac"] - 1 / 41) < 1e-9
+    assert cen["en/web"]["empty_frac"] == 1 / 42
+    assert cen["code/repo"]["broken_rows"] == 1 and cen["code/repo"]["truncated_frac"] == 1 / 11
+    assert cen["code/repo"]["fields"]["lang"] == 10
+
+    prof = dt.profile(str(root), ByteTokenizer().encode, sample=8)
+    assert prof["code/repo"]["markers"]["code_fence"] == 10 / 12
+    assert abs(prof["en/web"]["chars_per_token"] - 1.0) < 1e-9          # a byte tokenizer on ASCII
+    assert prof["en/web"]["est_tokens"] == prof["en/web"]["chars"]
+
+    stats = {"big": {"rows": 1000, "est_tokens": 1e6}, "small": {"rows": 10, "est_tokens": 1e4}}
+    mix = dt.mixture(stats, {"big": 0.5e6, "small": 0.5e6})
+    assert mix["small"]["repeat"] == 4.0                                  # capped: the rest goes to the big source
+    assert abs(sum(v["tokens"] for v in mix.values()) - 1e6) < 1e-3
+    assert abs(mix["big"]["tokens"] - (1e6 - 4e4)) < 1e-3
+
+    assert longest_consecutive_repeat("a b a b a b c".split(), 5) == (3, 2)
+    assert longest_consecutive_repeat(list("xyz"), 5) == (1, 1)
+    assert text_units("ab " + "Q" * 50)[:2] == ["ab", "Q"] and len(text_units("ab " + "Q" * 50)) == 51
+    assert not passes_consecutive_repeat_filter("spam " * 40) and passes_consecutive_repeat_filter("one two three four")
+    scan = dt.ngram_scan([str(a / "part-0.jsonl")], sample=0, max_n=13, threshold=5, show=1)
+    assert scan["documents"] == 42 and scan["rejected"] >= 41 and scan["worst"][0]["repeats"] >= 5
+
+    chat = tmp_path / "chat.jsonl"
+    chat.write_text("\n".join(json.dumps(r) for r in [
+        {"messages": [{"role": "user", "content": "hi"}, {"role": "assistant", "content": "hello"}]},
+        {"conversations": [{"from": "human", "value": "2+2?"}, {"from": "gpt", "value": "4"}]},
+        {"text": "no conversation here"}]) + "\n")
+    res = dt.to_corpus_chat(str(chat), str(tmp_path / "sft"), rows_per_shard=1)
+    assert res == {"kept": 2, "dropped": 1, "shards": 2}
+    tc = dt.token_census({"name": "corpus", "root": str(tmp_path / "sft")}, "chatml", ByteTokenizer().encode, limit=10)
+    assert tc["records"] == 2 and tc["sampled"] == 2 and tc["mean_tokens"] > 10 and 0 < tc["trained_share"] < 1
+    assert dt.main(["census", "--root", str(root), "--out", str(tmp_path / "out" / "census.json")]) == 0
+    assert json.loads((tmp_path / "out" / "census.json").read_text())["en/web"]["rows"] == 42

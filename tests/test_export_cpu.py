@@ -53,3 +53,37 @@ def test_gguf_writer(tmp_path):
     raw = open(path, "rb").read()
     magic, version, n_tensors, n_kv = struct.unpack("<IIQQ", raw[:24])
     assert (magic, version, n_tensors, n_kv) == (GGUF_MAGIC, 3, 2, 2)
+
+
+def test_build_tokenizer_cli(tmp_path, capsys):
+    """Train a small byte-level BPE, prune it through the CLI: exact vocabulary size, named specials then reserved
+    slots, BOS prepended by the post-processor, and the measured growth in tokens per sample."""
+    import json
+
+    from tokenizers import Tokenizer, decoders, models, pre_tokenizers, trainers
+
+    from kohakuwullm_b200.cli import build_tokenizer as bt
+
+    corpus = ["the quick brown fox jumps over the lazy dog %d times" % i for i in range(200)]
+    tok = Tokenizer(models.BPE())
+    tok.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False)
+    tok.decoder = decoders.ByteLevel()
+    tok.train_from_iterator(corpus, trainers.BpeTrainer(vocab_size=400, initial_alphabet=pre_tokenizers.ByteLevel.alphabet(),
+                                                        show_progress=False))
+    src = tmp_path / "src"
+    src.mkdir()
+    tok.save(str(src / "tokenizer.json"))
+    shard = tmp_path / "part.jsonl"
+    shard.write_text("\n".join(json.dumps({"text": t}) for t in corpus) + "\n")
+    n_named = len(bt.CORE_SPECIALS + bt.CHAT_SPECIALS + bt.tipo_specials())
+    target = 320 + n_named + 10
+    assert bt.main(["--source", str(src), "--out", str(tmp_path / "out"), "--base", "320", "--target", str(target),
+                    "--check-corpus", str(shard), "--check-samples", "50"]) == 0
+    report = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert report["vocab"] == target and report["named_specials"] == n_named and report["reserved"] == 10
+    assert report["length_ratio"] >= 1.0 and report["samples"] == 50
+    built = Tokenizer.from_file(str(tmp_path / "out" / "tokenizer.json"))
+    vocab = built.get_vocab()
+    assert vocab["<|bos|>"] == 320 and vocab["<|reserved_9|>"] == target - 1
+    ids = built.encode("the quick fox").ids
+    assert ids[0] == vocab["<|bos|>"] and built.decode(ids[1:]) == "the quick fox"

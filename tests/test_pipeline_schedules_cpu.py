@@ -129,3 +129,13 @@ def test_dist_check_harness_passes_on_cpu_ranks(check):
                          cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
     assert out.stdout.strip().splitlines()[-1] == "PASS"
+
+
+@pytest.mark.timeout(300)
+def test_multi_stream_boundaries_give_every_stage_its_gradient():
+    """Accumulator, shared-context and skip streams across four stages (so the inner ranks use one group per
+    link and direction): gradients equal the single-process model on every stage."""
+    from kohakuwullm_b200.cli import pipe_streams
+    from tests.helpers import free_port
+
+    assert pipe_streams.main(["--case", "all", "--stages", "4", "--port", str(free_port())]) == 0
