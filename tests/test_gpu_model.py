@@ -129,4 +129,4 @@ def test_graph_replay_with_varying_micro_batch_sizes_matches_eager():
     den = sum(float((pe[n] - start[n]).double().pow(2).sum()) for n in pe)
     rel = (num / max(den, 1e-30)) ** 0.5
     print("relative distance of the updates:", rel)
-    assert rel < 0.35, rel
+    assert rel < 0.1, rel    # measured 0.02
