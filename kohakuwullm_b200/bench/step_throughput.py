@@ -60,6 +60,8 @@ def main(argv=None):
     ap.add_argument("--router-bias-std", type=float, default=0.0,
                     help="seeded N(0, std) selection bias on every router: a skewed expert load")
     ap.add_argument("--ep-capacity", type=float, default=2.0, help="expert-parallel receive capacity factor")
+    ap.add_argument("--no-head-only-stage", action="store_true",
+                    help="pipeline: every stage must hold at least one block (default: the last may hold the head only)")
     ap.add_argument("--stage-report", action="store_true",
                     help="pipeline: per-stage busy time (CUDA events around every stage forward / backward), the "
                          "bubble share of the step and the cost of one boundary hop")
@@ -97,7 +99,8 @@ def main(argv=None):
 
         costs = measure_costs(cfg, args.micro_tokens, dev) if rank == 0 else None
         costs = broadcast_costs(costs, cfg.depth, dev)
-        plans = plan_for(cfg, world, args.micro_tokens, costs=costs)
+        # a head as wide as this vocabulary costs more than two blocks: the planner may give it a stage of its own
+        plans = plan_for(cfg, world, args.micro_tokens, costs=costs, allow_empty_last=not args.no_head_only_stage)
         module = LMPipelineModule(cfg, micro_tokens=args.micro_tokens, lr=1e-4)
         trainer = PipelineTrainer(module, plans, rank=rank, world=world, device=dev, n_micro=args.accum,
                                   schedule=args.schedule)

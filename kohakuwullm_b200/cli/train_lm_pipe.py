@@ -22,6 +22,7 @@ NUM_MICROBATCHES = 16
 SCHEDULE = "1f1b"
 LAYERS: list | None = None
 AUTOTUNE = True
+HEAD_ONLY_STAGE = True     # the measured split may leave the last stage with the final norm and the head only
 LEN_MIN, LEN_MAX = 64, 4096
 LR = 3e-4
 WEIGHT_DECAY = 0.1
@@ -59,7 +60,8 @@ def main():
         costs = broadcast_costs(measured, cfg.depth, ranks.device)
     chunks = 2 if SCHEDULE in ("zbv", "dualpipe-v", "interleaved-1f1b", "looped-bfs", "interleaved-zb") else 1
     plans = plan_for(cfg, ranks.world_size * chunks, MICRO_TOKENS, layers=LAYERS, costs=costs,
-                     style="v" if SCHEDULE in ("zbv", "dualpipe-v") else "loop")
+                     style="v" if SCHEDULE in ("zbv", "dualpipe-v") else "loop",
+                     allow_empty_last=HEAD_ONLY_STAGE and costs is not None)
     log.info("plan", split=[p.num_layers for p in plans])
     log.info("plan_detail", text="\n" + describe(plans))
     from kohakuwullm_b200.utils.reporters import build_reporter

@@ -87,9 +87,10 @@ def _pipe_worker(rank, world, port, schedule, layers, out_dir, load_from):
 
 
 @pytest.mark.timeout(600)
-@pytest.mark.parametrize("schedule,layers", [("1f1b", [3, 1]), ("gpipe", [2, 2]), ("1f1b", [1, 1, 1, 1])])
+@pytest.mark.parametrize("schedule,layers", [("1f1b", [3, 1]), ("gpipe", [2, 2]), ("1f1b", [1, 1, 1, 1]), ("1f1b", [2, 2, 0])])
 def test_pipeline_matches_single_process(schedule, layers):
-    # four stages: every inner rank has two neighbours, each link and direction on a group of its own
+    # four stages: every inner rank has two neighbours, each link and direction on a group of its own;
+    # [2, 2, 0]: a last stage that holds the final norm and the head only (what the planner may pick for a wide head)
     ref_losses, ref_state = _reference()
     world = len(layers)
     with tempfile.TemporaryDirectory() as tmp:
