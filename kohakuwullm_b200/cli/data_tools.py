@@ -7,6 +7,7 @@
     python -m kohakuwullm_b200.cli.data_tools token-census --records '{"name":"corpus","root":"DATA/en/source"}' \\
                                                            --renderer plain --limit 20000
     python -m kohakuwullm_b200.cli.data_tools to-corpus-chat --src chat.jsonl --dst DATA/sft/chat
+    python -m kohakuwullm_b200.cli.data_tools to-vault-chat  --src chat.jsonl --root VAULT --corpus sft/chat
 
 A corpus is laid out as ``<root>/<category>/<source>/*.jsonl`` (one JSON object per line). Everything streams:
 memory is the counters, the duplicate table and one tokenizer batch. ``to-corpus-chat`` writes conversation
@@ -237,6 +238,34 @@ def to_corpus_chat(src: str, dst: str, rows_per_shard: int = 200_000) -> dict:
     return {"kept": kept, "dropped": dropped, "shards": shard}
 
 
+def to_vault_chat(src: str, root: str, corpus: str, rows_per_shard: int = 200_000) -> dict:
+    """The same conversion into key-value shards ``root/corpus/part-NNNNN.kv`` with sequential int64 keys; read them
+    with ``{"name": "vault_corpus", "corpus": corpus, "root": root, "schema": "json"}``."""
+    from kohakuwullm_b200.data.sources.kvstore import KVWriter
+
+    d = os.path.join(root, corpus)
+    os.makedirs(d, exist_ok=True)
+    paths = [src] if os.path.isfile(src) else sorted(os.path.join(src, f) for f in os.listdir(src) if f.endswith(".jsonl"))
+    shard, rows, kept, dropped, out = 0, 0, 0, 0, None
+    for row in iter_rows(paths):
+        msgs = row.get("messages") or row.get("conversations")
+        if not isinstance(msgs, list) or not msgs:
+            dropped += 1
+            continue
+        if out is None or rows >= rows_per_shard:
+            if out:
+                out.close()
+            out = KVWriter(os.path.join(d, f"part-{shard:05d}.kv"))
+            shard, rows = shard + 1, 0
+        out.put(kept, {"messages": [{"role": str(m.get("role") or m.get("from") or "user"),
+                                     "content": str(m.get("content") or m.get("value") or "")} for m in msgs if isinstance(m, dict)]})
+        rows += 1
+        kept += 1
+    if out:
+        out.close()
+    return {"kept": kept, "dropped": dropped, "shards": shard}
+
+
 def _encoder(path: str | None):
     if not path:
         from kohakuwullm_b200.data import ByteTokenizer
@@ -261,6 +290,8 @@ def main(argv=None) -> int:
     p.add_argument("--tokenizer"); p.add_argument("--limit", type=int, default=20000); p.add_argument("--max-length", type=int)
     p = sub.add_parser("to-corpus-chat"); p.add_argument("--src", required=True); p.add_argument("--dst", required=True)
     p.add_argument("--rows-per-shard", type=int, default=200_000)
+    p = sub.add_parser("to-vault-chat"); p.add_argument("--src", required=True); p.add_argument("--root", required=True)
+    p.add_argument("--corpus", required=True); p.add_argument("--rows-per-shard", type=int, default=200_000)
     for sp in sub.choices.values():
         sp.add_argument("--out", help="write the JSON result here instead of stdout")
     a = ap.parse_args(argv)
@@ -277,6 +308,8 @@ def main(argv=None) -> int:
         spec = json.loads(a.records) if a.records.lstrip().startswith("{") else a.records
         rend = json.loads(a.renderer) if a.renderer.lstrip().startswith("{") else a.renderer
         res = token_census(spec, rend, _encoder(a.tokenizer), a.limit, a.max_length)
+    elif a.cmd == "to-vault-chat":
+        res = to_vault_chat(a.src, a.root, a.corpus, a.rows_per_shard)
     else:
         res = to_corpus_chat(a.src, a.dst, a.rows_per_shard)
     text = json.dumps(res, indent=1, ensure_ascii=False)

@@ -12,6 +12,7 @@ from kohakuwullm_b200.data.loader.padded import PaddedBatch, collate_padded, spl
 from kohakuwullm_b200.data.loader.permute import FeistelPermutation, ShardIndices, is_validation  # noqa: F401
 from kohakuwullm_b200.data.packing import PackedBatch, collate_packed, split_packed  # noqa: F401
 from kohakuwullm_b200.data.renderers import base as _renderers  # noqa: F401  (registrations)
+from kohakuwullm_b200.data.sources import kvstore as _kvstore  # noqa: F401  (registrations)
 from kohakuwullm_b200.data.sources import records as _records  # noqa: F401  (registrations)
 from kohakuwullm_b200.data.synthetic import make_pack, make_packs  # noqa: F401
 from kohakuwullm_b200.registry import DATASET, LOADER, RENDERER, build

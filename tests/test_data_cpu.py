@@ -219,5 +219,76 @@ def test_corpus_tools_census_profile_mixture_and_chat_conversion(tmp_path):
     assert res == {"kept": 2, "dropped": 1, "shards": 2}
     tc = dt.token_census({"name": "corpus", "root": str(tmp_path / "sft")}, "chatml", ByteTokenizer().encode, limit=10)
     assert tc["records"] == 2 and tc["sampled"] == 2 and tc["mean_tokens"] > 10 and 0 < tc["trained_share"] < 1
+    assert dt.to_vault_chat(str(chat), str(tmp_path / "vault"), "sft/chat", rows_per_shard=1) == {"kept": 2, "dropped": 1, "shards": 2}
+    tv = dt.token_census({"name": "vault_corpus", "corpus": "sft/chat", "root": str(tmp_path / "vault"), "schema": "json"},
+                         "chatml", ByteTokenizer().encode, limit=10)
+    assert tv["records"] == 2 and tv["mean_tokens"] == tc["mean_tokens"]      # the same rows through the other store
     assert dt.main(["census", "--root", str(root), "--out", str(tmp_path / "out" / "census.json")]) == 0
     assert json.loads((tmp_path / "out" / "census.json").read_text())["en/web"]["rows"] == 42
+
+
+def _kv_child(path, q):
+    from kohakuwullm_b200.data.sources.kvstore import KVFile
+
+    q.put(KVFile(path).get(3))
+
+
+def test_kv_store_and_vault_style_sources(tmp_path):
+    import multiprocessing as mp
+    import random
+
+    from kohakuwullm_b200.data import build_dataset
+    from kohakuwullm_b200.data.sources.kvstore import KVFile, KVWriter, TagRecords, VaultCorpusRecords, quality_of
+
+    # the store: any key order, three value kinds, last write wins, integer keys sort numerically
+    path = str(tmp_path / "a.kv")
+    with KVWriter(path) as w:
+        for i in (5, 3, 300, 4):
+            w.put(i, f"doc {i}")
+        w.put("blob", b"\x00\x01")
+        w.put("meta", {"n": 1})
+        w.put("meta", {"n": 2})
+    kv = KVFile(path)
+    assert len(kv) == 6 and kv.get(300) == "doc 300" and kv.get("blob") == b"\x00\x01" and kv.get("meta") == {"n": 2}
+    assert kv.get(7) is None and [k for k in kv.keys() if len(k) == 8] == sorted(k for k in kv.keys() if len(k) == 8)
+    q = mp.get_context("fork").Queue()
+    p = mp.get_context("fork").Process(target=_kv_child, args=(path, q))
+    p.start()
+    assert q.get(timeout=30) == "doc 3"
+    p.join()
+    (tmp_path / "cut.kv").write_bytes(open(path, "rb").read()[:-10])
+    with pytest.raises(ValueError):
+        KVFile(str(tmp_path / "cut.kv"))
+
+    # corpus shards with sequential ids, text and conversation schemas, snapshot check
+    d = tmp_path / "vault" / "en" / "web"
+    d.mkdir(parents=True)
+    for s in range(2):
+        with KVWriter(str(d / f"part-{s}.kv")) as w:
+            for i in range(3):
+                w.put(s * 3 + i, f"text {s * 3 + i}")
+    corpus = VaultCorpusRecords("en/web", str(tmp_path / "vault"))
+    assert len(corpus) == 6 and corpus[4] == {"text": "text 4", "source": "en/web"} and corpus.snapshot() == [3, 3]
+    with pytest.raises(ValueError):
+        VaultCorpusRecords("en/web", str(tmp_path / "vault"), snapshot=[3, 2])
+    records, renderer = build_dataset({"name": "vault_corpus", "corpus": "en/web", "root": str(tmp_path / "vault")}, "plain")
+    assert len(records) == 6 and renderer(records[0], None)[0][0].startswith("text 0")
+
+    # tag records joined with captions, rendered by the TIPO renderer
+    with KVWriter(str(tmp_path / "meta.kv")) as w:
+        w.put("00000012", {"id": 12, "general": ["1girl", "smile"], "artist": ["someone"], "character": ["alice"],
+                           "copyright": [], "meta": ["highres"], "rating": "g", "score": 120, "width": 800, "height": 1200,
+                           "year": 2021, "has_image": True})
+        w.put("00000013", {"id": 13, "general": ["tree"], "score": -3})
+    with KVWriter(str(tmp_path / "cap.kv")) as w:
+        w.put("/img/12.webp", {"brief": "a girl", "description": "a smiling girl under a tree", "title": "t"})
+    tags = TagRecords(str(tmp_path / "meta.kv"), str(tmp_path / "cap.kv"), caption_key="/img/{id}.webp")
+    assert len(tags) == 2 and quality_of(120) == "best quality" and quality_of(-3) == "worst quality"
+    r = tags[0]
+    assert r["quality"] == "best quality" and r["long"].startswith("a smiling") and r["aspect_ratio"] == 0.67
+    assert tags[1]["long"] is None and tags[1]["tags"] == ["tree"]                      # tag-only post
+    assert len(TagRecords(str(tmp_path / "meta.kv"), image_only=True)) == 1
+    from kohakuwullm_b200.data.renderers.base import TIPORenderer
+
+    segs = TIPORenderer()(r, random.Random(0))
+    assert len(segs) == 2 and segs[1][1] is True and "<|" in segs[0][0]
