@@ -167,12 +167,14 @@ def case_optim(reps):
     from kohakuwullm_b200.parallel.flat import FlatParameters
     from kohakuwullm_b200.training.optim.fused_adamw import FlatAdamW
 
-    lin = torch.nn.Linear(8192, 16384, bias=False, device="cuda", dtype=torch.bfloat16)
-    flat = FlatParameters(lin)
-    opt = FlatAdamW(flat)
-    n = lin.weight.numel()
-    s = bench_samples(lambda: opt.step(), repeats=reps)
-    _report(f"adamw_flat/{n}", s, bytes_moved=n * (4 * 4 * 2 + 2.0))   # grad r+zero, master/m/v r+w, bf16 w
+    for rows in (8192, 57344):     # 134M elements, and 940M: the size of a whole 1B-parameter model's buffers (17 GB)
+        lin = torch.nn.Linear(16384, rows, bias=False, device="cuda", dtype=torch.bfloat16)
+        flat = FlatParameters(lin)
+        opt = FlatAdamW(flat)
+        n = lin.weight.numel()
+        s = bench_samples(lambda: opt.step(), repeats=reps)
+        _report(f"adamw_flat/{n}", s, bytes_moved=n * (4 * 4 * 2 + 2.0))   # grad r+zero, master/m/v r+w, bf16 w
+        del opt, flat, lin
 
 
 CASES = {"gemm": case_gemm, "wgrad": case_wgrad, "mxfp8": case_mxfp8, "flash": case_flash, "elementwise": case_elementwise, "loss": case_loss,

@@ -38,8 +38,14 @@ adamw_flat_kernel(float* __restrict__ master, float* __restrict__ m, float* __re
                   const float* __restrict__ seg_lr_mult, int nseg, long long n,
                   const float* __restrict__ grad_scale, AdamHyper hp, int zero_grad) {
   const float gs = grad_scale ? *grad_scale : 1.f;
-  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x * 4;
-  for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4; i < n; i += stride) {
+  // Each block walks ONE contiguous range of the buffers (not a grid-wide stride): with five streams of several
+  // gigabytes each, a grid-stride loop has every block on a new 2 MB page of every stream at every iteration.
+  const long long vecs = n >> 2;
+  const long long per_block = ((vecs + gridDim.x - 1) / gridDim.x + 31) & ~31LL;   // whole 512-byte lines of fp32
+  const long long v_begin = static_cast<long long>(blockIdx.x) * per_block;
+  const long long v_end = v_begin + per_block < vecs ? v_begin + per_block : vecs;
+  for (long long vi = v_begin + threadIdx.x; vi < v_end; vi += blockDim.x) {
+    const long long i = vi << 2;
     // segments start on multiples of 4 elements, so one lookup serves the whole vector
     const int s = find_segment(seg_start, nseg, i);
     const float wd = seg_wd[s];
