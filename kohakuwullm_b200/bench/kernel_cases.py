@@ -174,7 +174,17 @@ def case_optim(reps):
         n = lin.weight.numel()
         s = bench_samples(lambda: opt.step(), repeats=reps)
         _report(f"adamw_flat/{n}", s, bytes_moved=n * (4 * 4 * 2 + 2.0))   # grad r+zero, master/m/v r+w, bf16 w
-        del opt, flat, lin
+        import ctypes
+
+        from kohakuwullm_b200.ops import native
+
+        L = native.require()
+        grad = flat.grad_buffers()[0] if hasattr(flat, "grad_buffers") else torch.zeros(n, device="cuda")
+        partial, out = torch.empty(L.kwu_sumsq_blocks(), device="cuda"), torch.zeros(1, device="cuda")
+        s = bench_samples(lambda: L.kwu_sumsq_flat(native.ptr(grad), ctypes.c_longlong(grad.numel()), native.ptr(partial),
+                                                   native.ptr(out), ctypes.c_int(0), native.stream_ptr()), repeats=reps)
+        _report(f"sumsq_flat/{grad.numel()}", s, bytes_moved=grad.numel() * 4.0)
+        del opt, flat, lin, grad
 
 
 CASES = {"gemm": case_gemm, "wgrad": case_wgrad, "mxfp8": case_mxfp8, "flash": case_flash, "elementwise": case_elementwise, "loss": case_loss,

@@ -83,15 +83,25 @@ __global__ void __launch_bounds__(256)
 sumsq_partial_kernel(const float* __restrict__ x, long long n, float* __restrict__ partial) {
   __shared__ float s_red[8];
   float acc = 0.f;
-  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x * 4;
-  for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4; i < n; i += stride) {
-    if (i + 4 <= n) {
-      const float4 a = *reinterpret_cast<const float4*>(x + i);
-      acc += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
-    } else {
-      for (long long j = i; j < n; ++j) acc += x[j] * x[j];
+  // one contiguous range per block, four independent 16-byte loads in flight per thread: a single load per
+  // thread and iteration left the kernel at half of the copy bandwidth (bound by latency, not by bytes)
+  const long long vecs = n >> 2;
+  const long long per_block = ((vecs + gridDim.x - 1) / gridDim.x + 31) & ~31LL;
+  const long long v_begin = static_cast<long long>(blockIdx.x) * per_block;
+  const long long v_end = v_begin + per_block < vecs ? v_begin + per_block : vecs;
+  const float4* x4 = reinterpret_cast<const float4*>(x);
+  for (long long vi = v_begin + threadIdx.x; vi < v_end; vi += 4LL * blockDim.x) {
+    float4 a[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long idx = vi + static_cast<long long>(u) * blockDim.x;
+      a[u] = idx < v_end ? x4[idx] : make_float4(0.f, 0.f, 0.f, 0.f);
     }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) acc += a[u].x * a[u].x + a[u].y * a[u].y + a[u].z * a[u].z + a[u].w * a[u].w;
   }
+  if (blockIdx.x == 0 && threadIdx.x == 0)
+    for (long long j = vecs << 2; j < n; ++j) acc += x[j] * x[j];   // up to three trailing elements
   acc = warp_sum(acc);
   if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = acc;
   __syncthreads();

@@ -111,3 +111,29 @@ def test_muon_batched_products_on_the_grouped_gemm_match_bmm():
     sv = torch.linalg.svdvals(u.float())
     assert sv.min() > 0.3 and sv.max() < 1.3
     native.check_status()
+
+
+@pytest.mark.parametrize("n", [1, 3, 1000, 4099, 1 << 20, (1 << 22) + 7])
+def test_sumsq_flat_matches_float64_sum(n):
+    """Sum of squares for global-norm clipping: ranges per block, tail elements, the accumulate flag; run twice,
+    same bits (fixed reduction order)."""
+    import ctypes
+
+    from kohakuwullm_b200.ops import native
+
+    L = native.require()
+    g = torch.Generator(device="cuda").manual_seed(n)
+    x = torch.randn(n, device="cuda", generator=g)
+    partial = torch.empty(L.kwu_sumsq_blocks(), device="cuda")
+    out = torch.full((1,), 5.0, device="cuda")
+
+    def run(acc):
+        native.check(L.kwu_sumsq_flat(native.ptr(x), ctypes.c_longlong(n), native.ptr(partial), native.ptr(out),
+                                      ctypes.c_int(acc), native.stream_ptr()), "sumsq")
+        return float(out)
+
+    first = run(0)
+    want = float(x.double().pow(2).sum())
+    assert abs(first - want) <= 2e-6 * want + 1e-12
+    assert run(0) == first
+    assert abs(run(1) - 2 * want) <= 4e-6 * want + 1e-12
