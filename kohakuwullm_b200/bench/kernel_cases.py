@@ -143,6 +143,46 @@ def case_elementwise(reps):
     _report("qknorm_rope_fwd/16384x20x64", s, bytes_moved=16384 * 1280 * 2.0 * 2)
 
 
+def case_qk(reps):
+    """QK-norm + rotary for the q and k heads of a fused qkv buffer in one launch, forward and backward (the
+    backward also writes the MXFP8 copy of the whole d(qkv) row), at the training shape."""
+    import ctypes
+
+    from kohakuwullm_b200.ops import mxfp8 as mx
+    from kohakuwullm_b200.ops import native
+
+    L = native.require()
+    ci, cf = ctypes.c_int, ctypes.c_float
+    T, Hq, Hkv, D = 4096, 20, 4, 64
+    cols = (Hq + 2 * Hkv) * D
+    qkv = torch.randn(T, cols, device="cuda").bfloat16()
+    wq, wk = torch.ones(D, device="cuda"), torch.ones(D, device="cuda")
+    ang = torch.rand(T, 32, device="cuda") * 6.28
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    q, k = torch.empty(T, Hq, D, device="cuda", dtype=torch.bfloat16), torch.empty(T, Hkv, D, device="cuda", dtype=torch.bfloat16)
+    dq, dk = torch.randn_like(q), torch.randn_like(k)
+    dqkv = torch.zeros(T, cols, device="cuda", dtype=torch.bfloat16)
+    dwq, dwk = torch.zeros(D, device="cuda"), torch.zeros(D, device="cuda")
+    q8, sf = mx.alloc_quantized(T, cols, "cuda")
+    st = native.stream_ptr()
+
+    def fwd():
+        L.kwu_qknorm_rope_fwd_qk(native.ptr(qkv), ci(cols), native.ptr(q), native.ptr(k), native.ptr(wq), native.ptr(wk),
+                                 native.ptr(cos), native.ptr(sin), ci(T), ci(Hq), ci(Hkv), ci(32), cf(1e-6), ci(1), st)
+
+    def bwd():
+        L.kwu_qknorm_rope_bwd_qk(native.ptr(qkv), ci(cols), native.ptr(dq), native.ptr(dk), native.ptr(dqkv), ci(cols),
+                                 native.ptr(wq), native.ptr(wk), native.ptr(dwq), native.ptr(dwk), native.ptr(cos),
+                                 native.ptr(sin), ci(T), ci(Hq), ci(Hkv), ci(32), cf(1e-6), ci(1), native.ptr(q8), ci(cols),
+                                 native.ptr(sf), st)
+
+    qk_bytes = T * (Hq + Hkv) * D * 2.0
+    s = bench_samples(fwd, repeats=reps)
+    _report(f"qknorm_rope_fwd_qk/{T}x{Hq}+{Hkv}x{D}", s, bytes_moved=2 * qk_bytes)
+    s = bench_samples(bwd, repeats=reps)
+    _report(f"qknorm_rope_bwd_qk_mx/{T}x{Hq}+{Hkv}x{D}", s, bytes_moved=3 * qk_bytes + T * cols * 1.0 + T * Hkv * D * 2.0)
+
+
 def case_loss(reps):
     from kohakuwullm_b200.ops.loss import linear_cross_entropy
 
@@ -187,7 +227,7 @@ def case_optim(reps):
         del opt, flat, lin, grad
 
 
-CASES = {"gemm": case_gemm, "wgrad": case_wgrad, "mxfp8": case_mxfp8, "flash": case_flash, "elementwise": case_elementwise, "loss": case_loss,
+CASES = {"gemm": case_gemm, "wgrad": case_wgrad, "mxfp8": case_mxfp8, "flash": case_flash, "elementwise": case_elementwise, "qk": case_qk, "loss": case_loss,
          "optim": case_optim}
 
 

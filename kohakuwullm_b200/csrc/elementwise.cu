@@ -687,52 +687,68 @@ qknorm_rope_fwd_qk_kernel(const __nv_bfloat16* __restrict__ src, int src_ld, __n
     wq[i] = (do_norm && wq_p) ? wq_p[8 * sub + i] : 1.f;
     wk[i] = (do_norm && wk_p) ? wk_p[8 * sub + i] : 1.f;
   }
-  for (long r0 = (static_cast<long>(blockIdx.x) * wpb + (threadIdx.x >> 5)) * 4; r0 < total;
-       r0 += static_cast<long>(gridDim.x) * wpb * 4) {
-    const long r = r0 + slot;
-    const bool live = r < total;
-    const int t = live ? static_cast<int>(r / HT) : 0;
-    const int h = live ? static_cast<int>(r % HT) : 0;
-    const bool is_k = h >= Hq;
-    float x[8];
-    uint4 raw = make_uint4(0, 0, 0, 0);
-    if (live) raw = *reinterpret_cast<const uint4*>(src + static_cast<size_t>(t) * src_ld + h * 64 + 8 * sub);
-    unpack8(raw, x);
-    uint32_t xw[4] = {raw.x, raw.y, raw.z, raw.w};
-    if (do_norm) {
-      float ss = 0.f;
+  // Two rows per 8-lane group and iteration (8 rows per warp): both rows' loads (data and rotary tables) are
+  // issued before either row's arithmetic, so a lane has ten 16-byte loads in flight instead of five. At 4096
+  // tokens a warp runs the loop once or twice only, and the kernel's time is that chain's latency.
+  for (long r0 = (static_cast<long>(blockIdx.x) * wpb + (threadIdx.x >> 5)) * 8; r0 < total;
+       r0 += static_cast<long>(gridDim.x) * wpb * 8) {
+    long rr[2];
+    bool live[2], is_k[2];
+    int tt[2], hh[2];
+    uint4 raw[2];
+    float4 c0[2], c1[2], s0[2], s1[2];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
-      const float rstd = rsqrtf(row8_sum(ss) * (1.f / 64.f) + eps);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float w0 = is_k ? wk[2 * i] : wq[2 * i], w1 = is_k ? wk[2 * i + 1] : wq[2 * i + 1];
-        xw[i] = pack_bf16(x[2 * i] * rstd * w0, x[2 * i + 1] * rstd * w1);
+    for (int u = 0; u < 2; ++u) {
+      rr[u] = r0 + slot + 4 * u;
+      live[u] = rr[u] < total;
+      tt[u] = live[u] ? static_cast<int>(rr[u] / HT) : 0;
+      hh[u] = live[u] ? static_cast<int>(rr[u] % HT) : 0;
+      is_k[u] = hh[u] >= Hq;
+      raw[u] = make_uint4(0, 0, 0, 0);
+      if (live[u]) raw[u] = *reinterpret_cast<const uint4*>(src + static_cast<size_t>(tt[u]) * src_ld + hh[u] * 64 + 8 * sub);
+      if (rot_half == 32) {
+        const float4* cp = reinterpret_cast<const float4*>(cos_t + static_cast<size_t>(tt[u]) * 32 + 8 * (sub & 3));
+        const float4* sp = reinterpret_cast<const float4*>(sin_t + static_cast<size_t>(tt[u]) * 32 + 8 * (sub & 3));
+        c0[u] = cp[0]; c1[u] = cp[1]; s0[u] = sp[0]; s1[u] = sp[1];
       }
-      unpack8(make_uint4(xw[0], xw[1], xw[2], xw[3]), x);
     }
-    if (rot_half == 32) {
-      float y[8];
-      uint32_t pw[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) pw[i] = __shfl_xor_sync(0xffffffffu, xw[i], 4);
-      unpack8(make_uint4(pw[0], pw[1], pw[2], pw[3]), y);
-      const float sign = (sub < 4) ? -1.f : 1.f;
-      const float4* cp = reinterpret_cast<const float4*>(cos_t + static_cast<size_t>(t) * 32 + 8 * (sub & 3));
-      const float4* sp = reinterpret_cast<const float4*>(sin_t + static_cast<size_t>(t) * 32 + 8 * (sub & 3));
-      const float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
-      const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-      const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    for (int u = 0; u < 2; ++u) {
+      float x[8];
+      unpack8(raw[u], x);
+      uint32_t xw[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+      if (do_norm) {
+        float ss = 0.f;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) x[i] = x[i] * c[i] + sign * y[i] * sn[i];
-    }
-    if (live) {
-      uint4 o;
-      o.x = pack_bf16(x[0], x[1]); o.y = pack_bf16(x[2], x[3]);
-      o.z = pack_bf16(x[4], x[5]); o.w = pack_bf16(x[6], x[7]);
-      __nv_bfloat16* d = is_k ? dst_k + (static_cast<size_t>(t) * Hkv + (h - Hq)) * 64
-                              : dst_q + (static_cast<size_t>(t) * Hq + h) * 64;
-      *reinterpret_cast<uint4*>(d + 8 * sub) = o;
+        for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
+        const float rstd = rsqrtf(row8_sum(ss) * (1.f / 64.f) + eps);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float w0 = is_k[u] ? wk[2 * i] : wq[2 * i], w1 = is_k[u] ? wk[2 * i + 1] : wq[2 * i + 1];
+          xw[i] = pack_bf16(x[2 * i] * rstd * w0, x[2 * i + 1] * rstd * w1);
+        }
+        unpack8(make_uint4(xw[0], xw[1], xw[2], xw[3]), x);
+      }
+      if (rot_half == 32) {
+        float y[8];
+        uint32_t pw[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) pw[i] = __shfl_xor_sync(0xffffffffu, xw[i], 4);
+        unpack8(make_uint4(pw[0], pw[1], pw[2], pw[3]), y);
+        const float sign = (sub < 4) ? -1.f : 1.f;
+        const float c[8] = {c0[u].x, c0[u].y, c0[u].z, c0[u].w, c1[u].x, c1[u].y, c1[u].z, c1[u].w};
+        const float sn[8] = {s0[u].x, s0[u].y, s0[u].z, s0[u].w, s1[u].x, s1[u].y, s1[u].z, s1[u].w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = x[i] * c[i] + sign * y[i] * sn[i];
+      }
+      if (live[u]) {
+        uint4 o;
+        o.x = pack_bf16(x[0], x[1]); o.y = pack_bf16(x[2], x[3]);
+        o.z = pack_bf16(x[4], x[5]); o.w = pack_bf16(x[6], x[7]);
+        __nv_bfloat16* d = is_k[u] ? dst_k + (static_cast<size_t>(tt[u]) * Hkv + (hh[u] - Hq)) * 64
+                                   : dst_q + (static_cast<size_t>(tt[u]) * Hq + hh[u]) * 64;
+        *reinterpret_cast<uint4*>(d + 8 * sub) = o;
+      }
     }
   }
 }
@@ -1144,7 +1160,7 @@ KWU_API int kwu_qknorm_rope_fwd_qk(const void* src, int src_ld, void* dst_q, voi
     return 7;
   }
   if (tokens <= 0) return 0;
-  const int grid = grid_for(static_cast<long>(tokens) * (Hq + Hkv), 32, 148 * 16);
+  const int grid = grid_for(static_cast<long>(tokens) * (Hq + Hkv), 64, 148 * 8);
   launch_k(qknorm_rope_fwd_qk_kernel, dim3(grid), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream), 
       (const __nv_bfloat16*)src, src_ld, (__nv_bfloat16*)dst_q, (__nv_bfloat16*)dst_k, wq, wk, cos_t, sin_t, tokens,
       Hq, Hkv, rot_half, eps, do_norm); kwu::count_launch();
