@@ -24,6 +24,12 @@ BATCH_TOKENS = 16384            # tokens per rank per optimizer step
 GRAD_ACCUM = 4
 CTX_MAX = 4096
 LEN_MIN, LEN_MAX = 64, 4096
+OPTIMIZER = "fused_adamw"      # or muon, adamw16, stochastic_adamw, adamw8bit, adamw4bit, adamwfp8, adamw, adam, sgd
+OPTIMIZER_KWARGS: dict = {}     # e.g. {"muon_lr": 0.02}
+GRAD_SYNC = "auto"             # fused (reduce-scatter + AdamW + all-gather over peer memory) with fused_adamw on GPUs, else nccl
+EXPERT_PARALLEL = False        # split the experts of every MoE layer over the ranks (the rest stays data parallel)
+EP_CAPACITY = 2.0
+EP_ON_OVERFLOW = "raise"       # or "count": drop pairs that find no room and report ep_dropped_pairs
 LR = 3e-4
 WEIGHT_DECAY = 0.1
 BETAS = (0.9, 0.95)
@@ -71,7 +77,9 @@ def main():
     sched = autofill_schedule_steps(dict(LR_SCHEDULE), MAX_STEPS, WARMUP_STEPS)
     trainer = LMTrainer(PRESET, dict(ARCH_OVERRIDES), lr=LR, betas=BETAS, weight_decay=WEIGHT_DECAY,
                         max_grad_norm=MAX_GRAD_NORM, grad_accum=GRAD_ACCUM, lr_schedule=sched, device=device,
-                        log_interval=LOG_INTERVAL, seed=SEED)
+                        log_interval=LOG_INTERVAL, seed=SEED, optimizer=OPTIMIZER, optimizer_kwargs=dict(OPTIMIZER_KWARGS),
+                        grad_sync=GRAD_SYNC, expert_parallel=EXPERT_PARALLEL, ep_capacity_factor=EP_CAPACITY,
+                        ep_on_overflow=EP_ON_OVERFLOW)
     if DATA == "synthetic":
         loader = _synthetic_stream(trainer.config.vocab_size, rank)
     else:

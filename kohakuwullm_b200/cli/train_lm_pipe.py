@@ -24,6 +24,8 @@ LAYERS: list | None = None
 AUTOTUNE = True
 HEAD_ONLY_STAGE = True     # the measured split may leave the last stage with the final norm and the head only
 LEN_MIN, LEN_MAX = 64, 4096
+OPTIMIZER = "fused_adamw"      # or muon, adamw16, stochastic_adamw, adamw8bit, adamw4bit, adamwfp8, adamw, adam, sgd
+OPTIMIZER_KWARGS: dict = {}
 LR = 3e-4
 WEIGHT_DECAY = 0.1
 MAX_GRAD_NORM = 1.0
@@ -69,7 +71,8 @@ def main():
     reporter = build_reporter(WANDB_PROJECT or None, RUN_NAME or None, {"preset": PRESET, **ARCH_OVERRIDES},
                               METRICS_JSONL or None, CONSOLE_INTERVAL, WANDB_MODE,
                               directory=CKPT_DIR or None) if ranks.rank == 0 else None
-    module = LMPipelineModule(cfg, micro_tokens=MICRO_TOKENS, lr=LR, weight_decay=WEIGHT_DECAY, seed=SEED)
+    module = LMPipelineModule(cfg, micro_tokens=MICRO_TOKENS, lr=LR, weight_decay=WEIGHT_DECAY, seed=SEED,
+                              optimizer=OPTIMIZER, optimizer_kwargs=dict(OPTIMIZER_KWARGS))
     trainer = PipelineTrainer(module, plans, rank=ranks.rank, world=ranks.world_size, device=ranks.device,
                               n_micro=NUM_MICROBATCHES, schedule=SCHEDULE, max_grad_norm=MAX_GRAD_NORM,
                               callbacks=[LossLog(LOG_INTERVAL, reporter=reporter),

@@ -129,13 +129,17 @@ class TrainEngine:
                  cuda_graphs: bool | None = None, graph_max_docs: int | None = None,
                  graph_token_bucket: int = 512, graph_cache_size: int = 8,
                  expert_parallel: bool | str = False, ep_capacity_factor: float = 2.0,
-                 ep_on_overflow: str = "raise"):
+                 ep_on_overflow: str = "raise", optimizer: str = "fused_adamw", optimizer_kwargs: dict | None = None):
         """``expert_parallel``: split every MoE layer's experts over the ranks of ``group`` (tokens travel
         to the owning rank over peer memory); all other parameters stay data-parallel replicas.
         ``"reference"`` keeps the sharding but moves tokens with plain collectives (test oracle).
         ``graph_token_bucket``: captured micro-step graphs hold a multiple of this many tokens; a micro-batch
         is padded up to the next multiple with a masked filler document. ``graph_cache_size``: at most this
-        many graphs are kept (least recently used goes first); each pins one forward + backward pool."""
+        many graphs are kept (least recently used goes first); each pins one forward + backward pool.
+        ``optimizer``: ``"fused_adamw"`` is the flat one-launch AdamW (the only one the fused gradient step can
+        carry); any other registered name (``muon``, ``adamw16``, ``stochastic_adamw``, ``adamw8bit``, ``adamw``,
+        ...) is built by ``build_optimizer`` with the same grouping rules and stepped from the reduced, clipped
+        gradients (NCCL gradient sync)."""
         self.model = model
         if device is not None:
             model.to(device)
@@ -145,7 +149,9 @@ class TrainEngine:
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if self.world > 1 else 0
-        self.fused_sync = grad_sync == "fused" and self.world > 1 and self.device.type == "cuda"
+        self.generic_optimizer = optimizer != "fused_adamw"
+        self.fused_sync = (grad_sync == "fused" and self.world > 1 and self.device.type == "cuda"
+                           and not self.generic_optimizer)
         self.ep = None
         if expert_parallel and self.world > 1:
             from kohakuwullm_b200.parallel.ep import ExpertParallel, shard_experts
@@ -165,7 +171,18 @@ class TrainEngine:
             self.flat = FlatParameters(model)
             self.sync = GradSync(self.flat, group)
             shard = None
-        self.optimizer = FlatAdamW(self.flat, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, shard=shard)
+        if self.generic_optimizer:
+            from kohakuwullm_b200.training.optim.build import build_optimizer
+
+            kw = dict(optimizer_kwargs or {})
+            if optimizer not in ("sgd", "muon"):
+                kw.setdefault("eps", eps)
+            self.optimizer = build_optimizer(model, optimizer, lr=lr, weight_decay=weight_decay, betas=betas, **kw)
+            for g in self.optimizer.param_groups:
+                g.setdefault("initial_lr", g["lr"])
+            self._base_lr = lr
+        else:
+            self.optimizer = FlatAdamW(self.flat, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, shard=shard)
         self.max_grad_norm = max_grad_norm
         self.lr_schedule = lr_schedule
         self.global_step = 0
@@ -210,6 +227,22 @@ class TrainEngine:
             self._restore_router(router_state)
         self._graphs[key] = g      # most recently used last
         return g
+
+    @torch.no_grad()
+    def _generic_step(self) -> None:
+        """Step an optimizer that reads ``p.grad``: the flat fp32 gradient buffers are scaled in place by the
+        token-count / clipping coefficient, handed over as ``.grad`` (in the parameter's dtype for 16-bit
+        parameters), and cleared afterwards."""
+        for buf in self.flat.grad_buffers():
+            buf.mul_(self._coef)
+        params = [p for p in self.model.parameters() if p.requires_grad and hasattr(p, "main_grad")]
+        for p in params:
+            g = p.main_grad
+            p.grad = g if g.dtype == p.dtype else g.to(p.dtype)
+        self.optimizer.step()
+        for p in params:
+            p.grad = None
+        self.flat.zero_grad()
 
     def _backward(self, loss: torch.Tensor) -> None:
         """Backward of one micro-batch with the weight-gradient products on a side stream (they only have to be
@@ -317,7 +350,12 @@ class TrainEngine:
                 if k in logs:
                     extra[k] = extra.get(k, 0) + logs[k]
         if self.lr_schedule is not None:
-            self.optimizer.param_groups[0]["lr"] = self.lr_schedule(self.global_step)
+            now = self.lr_schedule(self.global_step)
+            if self.generic_optimizer:      # every group keeps its ratio to the base rate (Muon, embedding, muP groups)
+                for g in self.optimizer.param_groups:
+                    g["lr"] = g["initial_lr"] * (now / self._base_lr)
+            else:
+                self.optimizer.param_groups[0]["lr"] = now
         if self.fused_sync:
             # one fused pass: reduce-scatter + scaling + clipping + sharded AdamW + all-gather
             with nvtx.range("grad_sync+optimizer/fused"):
@@ -331,7 +369,10 @@ class TrainEngine:
                 self.sync.reduce()
             with nvtx.range("clip+optimizer"):
                 self._grad_norm_and_coef(inv_tokens)
-                self.optimizer.step(grad_scale=self._coef, zero_grad=True)
+                if self.generic_optimizer:
+                    self._generic_step()
+                else:
+                    self.optimizer.step(grad_scale=self._coef, zero_grad=True)
             if self.has_mxfp8:
                 with nvtx.range("mxfp8_refresh"):
                     model.refresh_mxfp8()

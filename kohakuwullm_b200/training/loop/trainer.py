@@ -38,7 +38,9 @@ class LMTrainer:
                  betas=(0.9, 0.95), weight_decay: float = 0.1, max_grad_norm: float = 1.0, grad_accum: int = 1,
                  lr_schedule: dict | None = None, param_dtype: torch.dtype | None = torch.bfloat16,
                  device=None, group=None, grad_sync: str = "auto", callbacks=(), log_interval: int = 10,
-                 ema: float = 0.98, seed: int = 1234, head_kwargs: dict | None = None):
+                 ema: float = 0.98, seed: int = 1234, head_kwargs: dict | None = None,
+                 optimizer: str = "fused_adamw", optimizer_kwargs: dict | None = None, expert_parallel: bool = False,
+                 ep_capacity_factor: float = 2.0, ep_on_overflow: str = "raise"):
         self.rank = dist.get_rank(group) if dist.is_available() and dist.is_initialized() else 0
         self.world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
         self.group = group
@@ -51,11 +53,13 @@ class LMTrainer:
             self.backbone = LMBackbone(self.config, head_kwargs=head_kwargs)
         sched = build_schedule(lr_schedule)
         if grad_sync == "auto":
-            grad_sync = "fused" if (self.world > 1 and self.device.type == "cuda") else "nccl"
+            grad_sync = "fused" if (self.world > 1 and self.device.type == "cuda" and optimizer == "fused_adamw") else "nccl"
         dtype = param_dtype if self.device.type == "cuda" else None
         self.engine = TrainEngine(self.backbone, lr=lr, betas=betas, weight_decay=weight_decay, max_grad_norm=max_grad_norm,
                                   param_dtype=dtype, group=group, grad_sync=grad_sync,
-                                  lr_schedule=(lambda step: lr * sched(step)))
+                                  lr_schedule=(lambda step: lr * sched(step)), optimizer=optimizer,
+                                  optimizer_kwargs=optimizer_kwargs, expert_parallel=expert_parallel,
+                                  ep_capacity_factor=ep_capacity_factor, ep_on_overflow=ep_on_overflow)
         self.flops = FlopCounter(self.backbone)
         self.grad_accum, self.log_interval, self.ema_beta = grad_accum, log_interval, ema
         self.callbacks = CallbackList(callbacks)
@@ -160,9 +164,18 @@ class LMTrainer:
         # ZeRO-sharded optimizer state and, under expert parallelism, the experts with their optimizer state
         ep_names = ckpt.expert_sharded_names(self.backbone) if self.world > 1 else set()
         sharded = self.engine.fused_sync or bool(ep_names)
-        opt = ckpt.gather_optimizer_state(self.engine.optimizer, None, self.group, ep_names=ep_names) if sharded else \
-            {"named_optimizer_state": self.engine.optimizer.state_dict()["named_optimizer_state"],
-             "step": self.engine.optimizer.step_count}
+        if sharded:
+            opt = ckpt.gather_optimizer_state(self.engine.optimizer, None, self.group, ep_names=ep_names,
+                                              module=self.backbone)
+        elif self.engine.generic_optimizer:
+            # an optimizer that keys its state by position: re-keyed by parameter name (replicas are identical)
+            sd = ckpt.named_state_of(self.engine.optimizer, self.backbone)
+            opt = {"named_optimizer_state": {k: {kk: (vv.detach().to("cpu", copy=True) if torch.is_tensor(vv) else vv)
+                                                 for kk, vv in v.items()} for k, v in sd["named_optimizer_state"].items()},
+                   "step": sd["step"]}
+        else:
+            opt = {"named_optimizer_state": self.engine.optimizer.state_dict()["named_optimizer_state"],
+                   "step": self.engine.optimizer.step_count}
         weights = ckpt.local_state_dict(self.backbone)
         if ep_names:
             from kohakuwullm_b200.parallel.ep import gather_expert_state

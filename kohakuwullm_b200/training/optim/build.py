@@ -98,3 +98,42 @@ def build_optimizer(model: nn.Module, name: str = "fused_adamw", lr: float = 3e-
     if name == "sgd":
         return OPTIMIZER.get(name)(groups, lr=lr, **kw)
     return OPTIMIZER.get(name)(groups, lr=lr, betas=betas, **kw)
+
+
+class MainGradOptimizer:
+    """Drives an optimizer that reads ``p.grad`` from parameters whose gradients live in flat fp32 ``main_grad``
+    buffers (``parallel/flat.py``): ``step`` hands every parameter its gradient (cast to the parameter's dtype for
+    16-bit parameters), steps, and clears the flat buffers. ``flat`` is exposed so that the training loops find the
+    gradient buffers for the global norm and scale them in place before the step."""
+
+    def __init__(self, optimizer: torch.optim.Optimizer, flat, module: nn.Module):
+        self.inner, self.flat, self.module = optimizer, flat, module
+
+    @property
+    def param_groups(self):
+        return self.inner.param_groups
+
+    @property
+    def state(self):
+        return self.inner.state
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        params = [p for p in self.module.parameters() if p.requires_grad and hasattr(p, "main_grad")]
+        for p in params:
+            g = p.main_grad
+            p.grad = g if g.dtype == p.dtype else g.to(p.dtype)
+        out = self.inner.step(closure)
+        for p in params:
+            p.grad = None
+        self.flat.zero_grad()
+        return out
+
+    def zero_grad(self, set_to_none: bool = True) -> None:
+        self.flat.zero_grad()
+
+    def state_dict(self):
+        return self.inner.state_dict()
+
+    def load_state_dict(self, sd):
+        return self.inner.load_state_dict(sd)

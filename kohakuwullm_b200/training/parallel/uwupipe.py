@@ -50,9 +50,12 @@ def verify_same_batch(batch: Sequence[PackedBatch], device, group=None) -> None:
 class LMPipelineModule(PipelineModule):
     def __init__(self, config: LMArchConfig, *, micro_tokens: int, lr: float = 3e-4, betas=(0.9, 0.95),
                  weight_decay: float = 0.1, param_dtype: torch.dtype | None = torch.bfloat16,
-                 seed: int = 1234, lr_schedule=None, group=None, cuda_graphs: bool | None = None):
+                 seed: int = 1234, lr_schedule=None, group=None, cuda_graphs: bool | None = None,
+                 optimizer: str = "fused_adamw", optimizer_kwargs: dict | None = None):
         """``cuda_graphs``: replay every stage's forward + backward of a micro-batch from CUDA graphs (default: on
-        for CUDA devices with the native kernels, single stage per rank, GPipe / 1F1B)."""
+        for CUDA devices with the native kernels, single stage per rank, GPipe / 1F1B). ``optimizer``: the flat
+        one-launch AdamW, or any registered name (``muon``, ``adamw16``, ``adamw8bit``, ...), built over this rank's
+        stage with the usual grouping rules."""
         super().__init__()
         self.config, self.micro_tokens = config, micro_tokens
         self.lr, self.betas, self.weight_decay = lr, betas, weight_decay
@@ -62,6 +65,7 @@ class LMPipelineModule(PipelineModule):
         self._checked = False
         self._router_scale = 1.0            # a device scalar once the stage exists (graphs read it in place)
         self.cuda_graphs = cuda_graphs
+        self.optimizer_name, self.optimizer_kwargs = optimizer, dict(optimizer_kwargs or {})
 
     # ------------------------------------------------------------------ construction
     def configure_model(self, plan: StagePlan, rank: int, world: int, device) -> LMStage:
@@ -86,8 +90,13 @@ class LMPipelineModule(PipelineModule):
         params = self.stages[0] if len(self.stages) == 1 else torch.nn.ModuleList(self.stages)
         self.flat = FlatParameters(params)
         self._flat_names = {f"{i}.{k}": v for i, st in enumerate(self.stages) for k, v in st.global_names().items()}
-        opt = FlatAdamW(self.flat, lr=self.lr, betas=self.betas, weight_decay=self.weight_decay)
-        return opt
+        if self.optimizer_name == "fused_adamw":
+            return FlatAdamW(self.flat, lr=self.lr, betas=self.betas, weight_decay=self.weight_decay)
+        from kohakuwullm_b200.training.optim.build import MainGradOptimizer, build_optimizer
+
+        inner = build_optimizer(params, self.optimizer_name, lr=self.lr, weight_decay=self.weight_decay,
+                                betas=self.betas, **self.optimizer_kwargs)
+        return MainGradOptimizer(inner, self.flat, params)
 
     def boundary_example(self, plan: StagePlan):
         dtype = next(p for p in self.stages[0].parameters() if p.dim() >= 2).dtype

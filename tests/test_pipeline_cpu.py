@@ -57,21 +57,21 @@ def _batch():
     return [make_pack(48, 8, 24, 200, seed=s) for s in (1, 2, 3)]
 
 
-def _reference(steps=2):
+def _reference(steps=2, optimizer="fused_adamw"):
     torch.manual_seed(1234)
     model = LMBackbone(get_preset("B200-smoke", **CFG))
-    eng = TrainEngine(model, lr=1e-2, max_grad_norm=1.0)
+    eng = TrainEngine(model, lr=1e-2, max_grad_norm=1.0, optimizer=optimizer)
     losses = [float(eng.step(_batch())["loss"]) for _ in range(steps)]
     return losses, {k: v.detach().clone() for k, v in model.state_dict().items()}
 
 
-def _pipe_worker(rank, world, port, schedule, layers, out_dir, load_from):
+def _pipe_worker(rank, world, port, schedule, layers, out_dir, load_from, optimizer="fused_adamw"):
     import faulthandler
     faulthandler.dump_traceback_later(30, exit=True)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     cfg = get_preset("B200-smoke", **CFG)
-    module = LMPipelineModule(cfg, micro_tokens=48, lr=1e-2, param_dtype=None)
+    module = LMPipelineModule(cfg, micro_tokens=48, lr=1e-2, param_dtype=None, optimizer=optimizer)
     plans = plan_for(cfg, world, layers=layers)
     trainer = PipelineTrainer(module, plans, rank=rank, world=world, n_micro=3, schedule=schedule, max_grad_norm=1.0)
     steps = 2
@@ -105,6 +105,25 @@ def test_pipeline_matches_single_process(schedule, layers):
         torch.testing.assert_close(state[k], ref_state[k], rtol=0, atol=5e-4, msg=k)
     named = payload["optimizer_states"][0]["named_optimizer_state"]
     assert set(named) == {k for k in ref_state if "expert_bias" not in k and "load_accum" not in k}
+
+
+@pytest.mark.timeout(600)
+def test_pipeline_with_a_registered_optimizer_matches_single_process():
+    """Muon on the pipeline engine: every stage builds it over its own slice (hidden matrices of one shape are
+    orthogonalised as a batch per stage); losses and weights equal the single-process engine with the same
+    optimizer, and its position-keyed state is checkpointed by whole-model names."""
+    ref_losses, ref_state = _reference(optimizer="muon")
+    with tempfile.TemporaryDirectory() as tmp:
+        mp.spawn(_pipe_worker, args=(2, free_port(), "1f1b", [3, 1], tmp, None, "muon"), nprocs=2, join=True)
+        losses = torch.load(os.path.join(tmp, "losses.pt"))
+        payload = torch.load(os.path.join(tmp, "pipe.ckpt"), weights_only=False)
+    for a, b in zip(losses, ref_losses):
+        assert abs(a - b) < 2e-5, (losses, ref_losses)
+    for k in ref_state:
+        torch.testing.assert_close(payload["state_dict"][k], ref_state[k], rtol=0, atol=5e-4, msg=k)
+    named = payload["optimizer_states"][0]["named_optimizer_state"]
+    assert any("momentum" in "".join(v.keys()) or "buf" in "".join(v.keys()) for v in named.values())
+    assert all(k in ref_state for k in named)
 
 
 @pytest.mark.timeout(600)

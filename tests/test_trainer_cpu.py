@@ -3,6 +3,8 @@
 import os
 import random
 
+import pytest
+
 import torch
 
 from kohakuwullm_b200.data import ByteTokenizer, IterativePackLoader, ResumableLoader
@@ -85,3 +87,33 @@ def test_reporters_write_scalars_perplexity_and_sample_tables(tmp_path, monkeypa
     assert any((tmp_path / "wb").rglob("*.wandb"))            # the offline run directory exists
     assert build_reporter() is None
     assert isinstance(build_reporter(jsonl=str(tmp_path / "m3.jsonl"), console_interval=10), MultiReporter)
+
+
+@pytest.mark.parametrize("name,kwargs", [("muon", {"muon_lr": 0.02}), ("adamw", {}), ("adamw8bit", {"min_quantized_size": 256})])
+def test_trainer_with_a_registered_optimizer_trains_checkpoints_and_resumes(tmp_path, name, kwargs):
+    """Any registered optimizer can drive the trainer (it steps from the reduced, clipped flat gradients); its state is
+    checkpointed by parameter name and an interrupted run continues exactly."""
+    def make():
+        return LMTrainer("B200-smoke", dict(ARCH), lr=5e-3, grad_accum=2, log_interval=100, device="cpu",
+                         lr_schedule={"mode": "cosine", "warmup": 2, "end": 20}, optimizer=name, optimizer_kwargs=dict(kwargs))
+
+    full = make()
+    assert full.engine.generic_optimizer and not full.engine.fused_sync
+    full.fit(_loader(), 6)
+    ref = torch.cat([p.detach().reshape(-1) for p in full.backbone.parameters()])
+    start = torch.cat([p.detach().reshape(-1) for p in make().backbone.parameters()])
+    assert float((ref - start).abs().max()) > 1e-4          # it trained
+    lrs = {round(g["lr"] / g["initial_lr"], 6) for g in full.engine.optimizer.param_groups}
+    assert len(lrs) == 1                                      # every group follows the schedule with its own base rate
+
+    first = make()
+    loader = _loader()
+    first.fit(loader, 3)
+    path = os.path.join(tmp_path, "run.ckpt")
+    first.save_checkpoint(path)
+    second = make()
+    loader2 = _loader()
+    second.load_checkpoint(path, loader2)
+    second.fit(loader2, 6)
+    got = torch.cat([p.detach().reshape(-1) for p in second.backbone.parameters()])
+    torch.testing.assert_close(got, ref, rtol=0, atol=5e-5)
