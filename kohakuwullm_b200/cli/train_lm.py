@@ -18,7 +18,24 @@ import torch.distributed as dist
 PRESET = "Kohaku-500M"
 ARCH_OVERRIDES: dict = {}
 DATA = "synthetic"              # "synthetic" or a corpus directory (jsonl / txt shards)
-RENDERER = "plain"
+SOURCES: list = []              # a mixture instead of DATA: [{"records": <record spec>, "repeat": 1.0, "source": "tag"}, ...]
+RENDERER = "plain"              # a renderer name or spec ("plain", "chatml", "qa", "tipo", {"name": "per_source", ...})
+NUM_WORKERS = 0                 # > 0: render + tokenise + pack in that many worker processes
+VAL_FRACTION = 0.0              # hold this share of the records out (hash split) and validate on it
+VAL_INTERVAL = 500
+VAL_BATCHES = 8
+CHECKPOINT_PATH = ""            # load weights only from this checkpoint (RESUME also restores optimizer, counters, loader)
+HEAD_KWARGS: dict = {}          # e.g. {"chunk": 4096}
+GRAD_CKPT = False               # recompute every block in backward
+USE_MUP = False                 # muP learning-rate / weight-decay groups relative to BASE_DIM
+BASE_DIM = 256
+SAMPLE_INTERVAL = 0             # > 0: decode SAMPLE_PROMPTS every N steps and log the text (and a W&B table)
+SAMPLE_PROMPTS: list = []
+SAMPLE_TOKENS = 64
+SAMPLE_TEMPERATURE = 0.8
+SAMPLE_TOP_P = 0.95
+SAMPLE_TOP_K = 0
+SAMPLE_MIN_P = 0.0
 TOKENIZER = "byte"              # "byte" or a Hugging Face tokenizer path
 BATCH_TOKENS = 16384            # tokens per rank per optimizer step
 GRAD_ACCUM = 4
@@ -75,36 +92,71 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl" if use_cuda else "gloo", **({"device_id": device} if use_cuda else {}))
     sched = autofill_schedule_steps(dict(LR_SCHEDULE), MAX_STEPS, WARMUP_STEPS)
-    trainer = LMTrainer(PRESET, dict(ARCH_OVERRIDES), lr=LR, betas=BETAS, weight_decay=WEIGHT_DECAY,
+    arch = dict(ARCH_OVERRIDES)
+    if GRAD_CKPT:
+        arch["grad_ckpt"] = True
+    opt_kwargs = dict(OPTIMIZER_KWARGS)
+    if USE_MUP:
+        opt_kwargs["mup_base_dim"] = BASE_DIM
+    trainer = LMTrainer(PRESET, arch, lr=LR, betas=BETAS, weight_decay=WEIGHT_DECAY, head_kwargs=dict(HEAD_KWARGS) or None,
                         max_grad_norm=MAX_GRAD_NORM, grad_accum=GRAD_ACCUM, lr_schedule=sched, device=device,
-                        log_interval=LOG_INTERVAL, seed=SEED, optimizer=OPTIMIZER, optimizer_kwargs=dict(OPTIMIZER_KWARGS),
+                        log_interval=LOG_INTERVAL, seed=SEED, optimizer=("adamw" if USE_MUP and OPTIMIZER == "fused_adamw" else OPTIMIZER),
+                        optimizer_kwargs=opt_kwargs,
                         grad_sync=GRAD_SYNC, expert_parallel=EXPERT_PARALLEL, ep_capacity_factor=EP_CAPACITY,
                         ep_on_overflow=EP_ON_OVERFLOW)
-    if DATA == "synthetic":
+    tok, val_loader = None, None
+    if DATA == "synthetic" and not SOURCES:
         loader = _synthetic_stream(trainer.config.vocab_size, rank)
     else:
         from kohakuwullm_b200.data import ByteTokenizer, build_dataset, build_loader
 
-        records, renderer = build_dataset({"name": "corpus", "root": DATA}, RENDERER)
+        spec = {"name": "mixture", "sources": SOURCES, "seed": SEED} if SOURCES else {"name": "corpus", "root": DATA}
+        records, renderer = build_dataset(spec, RENDERER)
         if TOKENIZER == "byte":
             tok = ByteTokenizer()
         else:
             from transformers import AutoTokenizer
 
             tok = AutoTokenizer.from_pretrained(TOKENIZER)
-        loader = build_loader("ddp", records, renderer, lambda s: tok.encode(s), rank=rank, world=world,
-                              k=BATCH_TOKENS, m=BATCH_TOKENS // 16, ctx_max=CTX_MAX, seed=SEED,
-                              bos=getattr(tok, "bos_token_id", None), eos=getattr(tok, "eos_token_id", None))
+        encode = lambda s: tok.encode(s)  # noqa: E731
+        common = dict(k=BATCH_TOKENS, m=BATCH_TOKENS // 16, ctx_max=CTX_MAX, seed=SEED,
+                      bos=getattr(tok, "bos_token_id", None), eos=getattr(tok, "eos_token_id", None))
+        if VAL_FRACTION > 0:
+            from kohakuwullm_b200.data.sources.records import SplitRecords
+
+            held_out = SplitRecords(records, VAL_FRACTION, "val", SEED)
+            records = SplitRecords(records, VAL_FRACTION, "train", SEED)
+            val_loader = lambda: build_loader("ddp", held_out, renderer, encode, rank=rank, world=world, **common)  # noqa: E731
+        if NUM_WORKERS > 0:
+            loader = build_loader("workers", records, renderer, encode, rank=rank, world=world, workers=NUM_WORKERS, **common)
+        else:
+            loader = build_loader("ddp", records, renderer, encode, rank=rank, world=world, **common)
     from kohakuwullm_b200.utils.reporters import build_reporter
 
     reporter = build_reporter(WANDB_PROJECT or None, RUN_NAME or None, {"preset": PRESET}, METRICS_JSONL or None, 0,
                               WANDB_MODE, directory=CKPT_DIR or None)
     callbacks = [ThroughputCallback(interval=LOG_INTERVAL * 2, reporter=reporter)]
+    if SAMPLE_INTERVAL > 0 and SAMPLE_PROMPTS and tok is not None:
+        from kohakuwullm_b200.training.loop.callbacks import SampleLogCallback
+
+        callbacks.append(SampleLogCallback(list(SAMPLE_PROMPTS), tok, SAMPLE_INTERVAL, SAMPLE_TOKENS, reporter,
+                                           temperature=SAMPLE_TEMPERATURE, top_p=SAMPLE_TOP_P, top_k=SAMPLE_TOP_K,
+                                           min_p=SAMPLE_MIN_P))
+    if val_loader is not None:
+        from kohakuwullm_b200.training.loop.callbacks import ValidationCallback
+
+        callbacks.append(ValidationCallback(val_loader, VAL_INTERVAL, VAL_BATCHES, reporter))
     trainer.callbacks.callbacks.extend(callbacks)
     if CKPT_DIR:
         trainer.callbacks.callbacks.append(Checkpoint(trainer, CKPT_DIR, every=CKPT_EVERY))
     if RESUME:
         trainer.load_checkpoint(RESUME, loader if hasattr(loader, "load_state_dict") else None)
+    elif CHECKPOINT_PATH:
+        from kohakuwullm_b200.pipe import checkpoint as ckpt
+
+        ckpt.load(CHECKPOINT_PATH, trainer.backbone, None, strict=False)      # weights only: a fresh optimizer and step count
+        if trainer.engine.has_mxfp8:
+            trainer.backbone.refresh_mxfp8()
     trainer.fit(loader, MAX_STEPS)
     if CKPT_DIR:
         trainer.save_checkpoint(os.path.join(CKPT_DIR, "last.ckpt"))

@@ -110,3 +110,73 @@ class PathKeyedRecords:
             rec = json.load(f)
         rec.setdefault("key", key)
         return rec
+
+
+@DATASET.register("mixture")
+class MixtureRecords:
+    """Several sources as one random-access sequence, each repeated ``repeat`` times (the mixture weights of a
+    run). ``sources``: a list of ``{"records": <spec or instance>, "repeat": 1.0, "source": "tag"}``. An integer
+    part of ``repeat`` gives whole copies; a fractional part gives a fixed pseudo-random subset of that share
+    (a Feistel permutation of the source, seeded, so the subset does not depend on the epoch or the rank).
+    Dict records get a ``"source"`` field (kept if they already have one): the per-source renderer keys on it."""
+
+    def __init__(self, sources, seed: int = 0, **_unused):
+        from kohakuwullm_b200.data.loader.permute import FeistelPermutation, splitmix64
+        from kohakuwullm_b200.registry import build
+
+        self.parts = []
+        self._starts = [0]
+        for i, spec in enumerate(sources):
+            spec = dict(spec)
+            recs = spec.pop("records")
+            if isinstance(recs, (str, dict)):
+                recs = build(recs, DATASET)
+            repeat = float(spec.pop("repeat", 1.0))
+            tag = spec.pop("source", None) or getattr(recs, "name", None) or f"source{i}"
+            n = len(recs)
+            total = int(n * repeat + 1e-9)
+            perm = FeistelPermutation(n, splitmix64(seed * 1000003 + i)) if (total % n and n > 1) else None
+            self.parts.append((recs, n, total, perm, tag))
+            self._starts.append(self._starts[-1] + total)
+
+    def __len__(self) -> int:
+        return self._starts[-1]
+
+    def __getitem__(self, i: int):
+        if not 0 <= i < len(self):
+            raise IndexError(i)
+        s = bisect_right(self._starts, i) - 1
+        recs, n, total, perm, tag = self.parts[s]
+        j = i - self._starts[s]
+        whole = (total // n) * n
+        local = j % n if j < whole else perm(j - whole)       # the fractional tail: a fixed subset
+        rec = recs[local]
+        if isinstance(rec, dict) and "source" not in rec:
+            rec = dict(rec, source=tag)
+        return rec
+
+    def composition(self) -> dict:
+        """Records per source after repetition (what the mixture really is)."""
+        return {tag: total for _, _, total, _, tag in self.parts}
+
+
+@DATASET.register("split")
+class SplitRecords:
+    """The training or the validation part of a source: record ``i`` is validation when a hash of ``(seed, i)``
+    falls under ``fraction`` (the split does not depend on epoch, rank or world size)."""
+
+    def __init__(self, records, fraction: float, part: str = "train", seed: int = 0, **_unused):
+        from kohakuwullm_b200.data.loader.permute import is_validation
+        from kohakuwullm_b200.registry import build
+
+        if part not in ("train", "val"):
+            raise ValueError(f"part must be 'train' or 'val', not {part!r}")
+        self.records = build(records, DATASET) if isinstance(records, (str, dict)) else records
+        want_val = part == "val"
+        self.index = [i for i in range(len(self.records)) if is_validation(i, fraction, seed) == want_val]
+
+    def __len__(self) -> int:
+        return len(self.index)
+
+    def __getitem__(self, i: int):
+        return self.records[self.index[i]]

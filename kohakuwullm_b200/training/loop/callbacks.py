@@ -99,3 +99,21 @@ class SampleLogCallback(Callback):
                     self.reporter({"samples": texts}, step)
         except NotImplementedError:
             self.enabled = False  # this parallel layout cannot be driven for previews
+
+
+class ValidationCallback(Callback):
+    """Every ``interval`` steps run ``trainer.validate`` over ``max_batches`` batches of a freshly built loader (so every
+    validation sees the same held-out batches) and log / report ``val/loss``, ``val/ppl``, ``val/tokens``."""
+
+    def __init__(self, make_loader, interval: int = 500, max_batches: int = 8, reporter=None):
+        self.make_loader, self.interval, self.max_batches, self.reporter = make_loader, interval, max_batches, reporter
+        self.last: dict = {}
+
+    def on_train_batch_end(self, trainer, out, batch, step):
+        if self.interval <= 0 or step % self.interval:
+            return
+        self.last = trainer.validate(self.make_loader(), self.max_batches)
+        if trainer.rank == 0:
+            log.info("validation", step=step, **self.last)
+            if self.reporter:
+                self.reporter(dict(self.last), step)

@@ -292,3 +292,25 @@ def test_kv_store_and_vault_style_sources(tmp_path):
 
     segs = TIPORenderer()(r, random.Random(0))
     assert len(segs) == 2 and segs[1][1] is True and "<|" in segs[0][0]
+
+
+def test_mixture_and_split_records():
+    from kohakuwullm_b200.data import build_dataset
+    from kohakuwullm_b200.data.sources.records import ListRecords, MixtureRecords, SplitRecords
+
+    a = ListRecords([{"text": f"a{i}"} for i in range(10)])
+    b = ListRecords([{"text": f"b{i}", "source": "given"} for i in range(4)])
+    mix = MixtureRecords([{"records": a, "repeat": 1.5, "source": "web"}, {"records": b, "repeat": 3}])
+    assert len(mix) == 15 + 12 and mix.composition() == {"web": 15, "source1": 12}
+    texts = [mix[i]["text"] for i in range(len(mix))]
+    assert texts[:10] == [f"a{i}" for i in range(10)]
+    tail = texts[10:15]
+    assert len(set(tail)) == 5 and set(tail) <= {f"a{i}" for i in range(10)}         # half of the source, no repeats
+    assert [mix[i]["text"] for i in range(10, 15)] == tail                           # and always the same half
+    assert texts[15:] == [f"b{i % 4}" for i in range(12)]
+    assert mix[0]["source"] == "web" and mix[20]["source"] == "given"
+    train, val = SplitRecords(a, 0.3, "train", seed=1), SplitRecords(a, 0.3, "val", seed=1)
+    assert len(train) + len(val) == 10 and not ({r["text"] for r in train} & {r["text"] for r in val})
+    records, _ = build_dataset({"name": "mixture", "sources": [{"records": {"name": "list", "records": [{"text": "x"}]},
+                                                                "repeat": 2}]}, "plain")
+    assert len(records) == 2

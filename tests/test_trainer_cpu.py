@@ -117,3 +117,42 @@ def test_trainer_with_a_registered_optimizer_trains_checkpoints_and_resumes(tmp_
     second.fit(loader2, 6)
     got = torch.cat([p.detach().reshape(-1) for p in second.backbone.parameters()])
     torch.testing.assert_close(got, ref, rtol=0, atol=5e-5)
+
+
+def test_train_lm_cli_with_a_mixture_validation_sampling_and_weight_only_load(tmp_path, capsys):
+    """The training entry point end to end on CPU: two jsonl corpora mixed with repeat weights, a held-out validation
+    split, preview sampling, metrics as JSONL, a checkpoint, and a second run that starts from its weights only."""
+    import importlib
+    import json
+
+    from kohakuwullm_b200.utils.config import configure
+
+    rng = random.Random(1)
+    for name, n in (("web", 60), ("code", 30)):
+        d = tmp_path / name
+        d.mkdir()
+        (d / "part-0.jsonl").write_text("\n".join(json.dumps({"text": "".join(rng.choice("abcdef ") for _ in range(rng.randint(10, 80)))})
+                                                  for _ in range(n)) + "\n")
+    common = ["--set", "DEVICE='cpu'", "--set", "PRESET='B200-smoke'", "--set", f"ARCH_OVERRIDES={ARCH!r}", "--set", "BATCH_TOKENS=192",
+              "--set", "CTX_MAX=96", "--set", "GRAD_ACCUM=2", "--set", "LOG_INTERVAL=2", "--set", "WARMUP_STEPS=1",
+              "--set", f"SOURCES=[{{'records': {{'name': 'corpus', 'root': {str(tmp_path / 'web')!r}}}, 'repeat': 1.5, 'source': 'web'}}, "
+                       f"{{'records': {{'name': 'corpus', 'root': {str(tmp_path / 'code')!r}}}, 'repeat': 2, 'source': 'code'}}]",
+              "--set", "VAL_FRACTION=0.2", "--set", "VAL_INTERVAL=2", "--set", "VAL_BATCHES=2",
+              "--set", "SAMPLE_INTERVAL=2", "--set", "SAMPLE_PROMPTS=['abc']", "--set", "SAMPLE_TOKENS=4",
+              "--set", f"METRICS_JSONL={str(tmp_path / 'metrics.jsonl')!r}"]
+    mod = importlib.import_module("kohakuwullm_b200.cli.train_lm")
+    mod = importlib.reload(mod)
+    configure(mod, common + ["--set", "MAX_STEPS=4", "--set", f"CKPT_DIR={str(tmp_path / 'ckpt')!r}"])
+    first = mod.main()
+    assert first.global_step == 4 and os.path.exists(tmp_path / "ckpt" / "last.ckpt")
+    rows = [json.loads(l) for l in open(tmp_path / "metrics.jsonl")]
+    assert any("val/loss" in r for r in rows)
+    mod = importlib.reload(mod)
+    configure(mod, common + ["--set", "MAX_STEPS=1", "--set", f"CHECKPOINT_PATH={str(tmp_path / 'ckpt' / 'last.ckpt')!r}",
+                             "--set", "OPTIMIZER='adamw'", "--set", "USE_MUP=True", "--set", "BASE_DIM=16"])
+    second = mod.main()
+    assert second.global_step == 1                       # weights only: counters start again
+    a = torch.cat([p.detach().reshape(-1) for p in first.backbone.parameters()])
+    b = torch.cat([p.detach().reshape(-1) for p in second.backbone.parameters()])
+    assert float((a - b).abs().max()) < 0.1              # one small step away from the loaded weights, not a fresh init
+    assert len({g["lr"] for g in second.engine.optimizer.param_groups}) > 1      # muP groups
