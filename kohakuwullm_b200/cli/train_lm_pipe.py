@@ -24,6 +24,24 @@ LAYERS: list | None = None
 AUTOTUNE = True
 HEAD_ONLY_STAGE = True     # the measured split may leave the last stage with the final norm and the head only
 LEN_MIN, LEN_MAX = 64, 4096
+DATA = "synthetic"          # "synthetic", a corpus directory, or use SOURCES
+SOURCES: list = []          # [{"records": <record spec>, "repeat": 1.0, "source": "tag"}, ...]
+RENDERER = "plain"
+TOKENIZER = "byte"          # "byte" or a Hugging Face tokenizer path
+CTX_MAX = 4096
+LR_SCHEDULE: dict = {"mode": "cosine", "warmup": None, "end": None, "min_value": 0.1}
+WARMUP_STEPS = 100
+AUX_LOSS_WEIGHT: float | None = None        # overrides the preset's router auxiliary-loss weight
+ROUTER_Z_LOSS_WEIGHT: float | None = None
+BIAS_SCHEDULE: dict | None = None           # schedule of the routers' bias update rate, e.g. {"mode": "linear", "end": 2000}
+GRAD_SCALER = "auto"                        # loss scaling for fp16 parameters ("auto": on for fp16 only), "on", "off"
+GRAD_SCALER_INIT = 65536.0
+CHECKPOINT_PATH = ""                        # weights only (RESUME restores optimizer, scheduler and counters too)
+SAMPLE_INTERVAL = 0                         # > 0: collective preview decode every N steps
+SAMPLE_PROMPTS: list = []                   # [(name, prompt), ...]
+SAMPLE_TOKENS = 64
+SAMPLE_TEMPERATURE = 0.35
+SAMPLE_TOP_P = 0.95
 OPTIMIZER = "fused_adamw"      # or muon, adamw16, stochastic_adamw, adamw8bit, adamw4bit, adamwfp8, adamw, adam, sgd
 OPTIMIZER_KWARGS: dict = {}
 LR = 3e-4
@@ -55,7 +73,15 @@ def main():
 
     log = get_logger("lm_pipe")
     ranks = init_pipeline(BACKEND)
-    cfg = get_preset(PRESET, **ARCH_OVERRIDES)
+    arch = dict(ARCH_OVERRIDES)
+    router_kw = dict(arch.get("moe_router_kwargs") or get_preset(PRESET).moe_router_kwargs or {})
+    if AUX_LOSS_WEIGHT is not None:
+        router_kw["aux_loss_weight"] = AUX_LOSS_WEIGHT
+    if ROUTER_Z_LOSS_WEIGHT is not None:
+        router_kw["z_loss_weight"] = ROUTER_Z_LOSS_WEIGHT
+    if router_kw:
+        arch["moe_router_kwargs"] = router_kw
+    cfg = get_preset(PRESET, **arch)
     costs = None
     if AUTOTUNE and LAYERS is None:
         measured = measure_costs(cfg, MICRO_TOKENS, ranks.device) if ranks.rank == 0 else None
@@ -71,16 +97,49 @@ def main():
     reporter = build_reporter(WANDB_PROJECT or None, RUN_NAME or None, {"preset": PRESET, **ARCH_OVERRIDES},
                               METRICS_JSONL or None, CONSOLE_INTERVAL, WANDB_MODE,
                               directory=CKPT_DIR or None) if ranks.rank == 0 else None
+    from kohakuwullm_b200.utils.misc import autofill_schedule_steps
+
+    sched = autofill_schedule_steps(dict(LR_SCHEDULE), MAX_STEPS, WARMUP_STEPS) if LR_SCHEDULE else None
     module = LMPipelineModule(cfg, micro_tokens=MICRO_TOKENS, lr=LR, weight_decay=WEIGHT_DECAY, seed=SEED,
-                              optimizer=OPTIMIZER, optimizer_kwargs=dict(OPTIMIZER_KWARGS))
+                              optimizer=OPTIMIZER, optimizer_kwargs=dict(OPTIMIZER_KWARGS), lr_schedule=sched)
+    scaler = None
+    if GRAD_SCALER == "on":
+        from kohakuwullm_b200.pipe.scaler import PipelineGradScaler
+
+        scaler = PipelineGradScaler(init_scale=GRAD_SCALER_INIT)
     trainer = PipelineTrainer(module, plans, rank=ranks.rank, world=ranks.world_size, device=ranks.device,
-                              n_micro=NUM_MICROBATCHES, schedule=SCHEDULE, max_grad_norm=MAX_GRAD_NORM,
+                              n_micro=NUM_MICROBATCHES, schedule=SCHEDULE, max_grad_norm=MAX_GRAD_NORM, scaler=scaler,
                               callbacks=[LossLog(LOG_INTERVAL, reporter=reporter),
                                          Throughput(LOG_INTERVAL, reporter=reporter)])
+    tok = None
+    if DATA != "synthetic" or SOURCES:
+        from kohakuwullm_b200.data import ByteTokenizer
+
+        if TOKENIZER == "byte":
+            tok = ByteTokenizer()
+        else:
+            from transformers import AutoTokenizer
+
+            tok = AutoTokenizer.from_pretrained(TOKENIZER)
+    if BIAS_SCHEDULE:
+        from kohakuwullm_b200.training.parallel.uwupipe_callbacks import RouterBiasSchedule
+
+        trainer.loop.callbacks.callbacks.append(RouterBiasSchedule(module, dict(BIAS_SCHEDULE)))
+    if SAMPLE_INTERVAL > 0 and SAMPLE_PROMPTS and tok is not None:
+        from kohakuwullm_b200.training.parallel.uwupipe_callbacks import SamplePreview
+
+        trainer.loop.callbacks.callbacks.append(SamplePreview(
+            module, tok, [tuple(p) for p in SAMPLE_PROMPTS], every_n_steps=SAMPLE_INTERVAL, max_new_tokens=SAMPLE_TOKENS,
+            temperature=SAMPLE_TEMPERATURE, top_p=SAMPLE_TOP_P, report=getattr(reporter, "samples", None)))
     if CKPT_DIR:
         trainer.loop.callbacks.callbacks.append(Checkpoint(trainer, CKPT_DIR, every=CKPT_EVERY))
     if RESUME:
         trainer.load_checkpoint(RESUME)
+    elif CHECKPOINT_PATH:
+        from kohakuwullm_b200.pipe import checkpoint as ckpt
+
+        for stage in module.stages:            # weights only: this rank's slice of the whole-model checkpoint
+            ckpt.load(CHECKPOINT_PATH, stage, None, names=module.global_names(), strict=False)
 
     def stream():
         step = trainer.loop.global_step
@@ -88,7 +147,18 @@ def main():
             yield make_packs(NUM_MICROBATCHES, MICRO_TOKENS, LEN_MIN, LEN_MAX, cfg.vocab_size, seed=SEED + step)
             step += 1
 
-    trainer.fit(stream(), MAX_STEPS)
+    if tok is None:
+        batches = stream()
+    else:
+        # every rank iterates the SAME micro-batched loader (stage 0 uses the tokens, the last stage the labels)
+        from kohakuwullm_b200.data import build_dataset, build_loader
+
+        spec = {"name": "mixture", "sources": SOURCES, "seed": SEED} if SOURCES else {"name": "corpus", "root": DATA}
+        records, renderer = build_dataset(spec, RENDERER)
+        batches = build_loader("pipeline", records, renderer, lambda s: tok.encode(s), k=MICRO_TOKENS, m=MICRO_TOKENS // 16,
+                               num_microbatches=NUM_MICROBATCHES, ctx_max=CTX_MAX, seed=SEED,
+                               bos=getattr(tok, "bos_token_id", None), eos=getattr(tok, "eos_token_id", None))
+    trainer.fit(batches, MAX_STEPS)
     if CKPT_DIR:
         trainer.save_checkpoint(os.path.join(CKPT_DIR, "last.ckpt"))
     if reporter is not None:

@@ -91,12 +91,19 @@ class LMPipelineModule(PipelineModule):
         self.flat = FlatParameters(params)
         self._flat_names = {f"{i}.{k}": v for i, st in enumerate(self.stages) for k, v in st.global_names().items()}
         if self.optimizer_name == "fused_adamw":
-            return FlatAdamW(self.flat, lr=self.lr, betas=self.betas, weight_decay=self.weight_decay)
-        from kohakuwullm_b200.training.optim.build import MainGradOptimizer, build_optimizer
+            opt = FlatAdamW(self.flat, lr=self.lr, betas=self.betas, weight_decay=self.weight_decay)
+        else:
+            from kohakuwullm_b200.training.optim.build import MainGradOptimizer, build_optimizer
 
-        inner = build_optimizer(params, self.optimizer_name, lr=self.lr, weight_decay=self.weight_decay,
-                                betas=self.betas, **self.optimizer_kwargs)
-        return MainGradOptimizer(inner, self.flat, params)
+            inner = build_optimizer(params, self.optimizer_name, lr=self.lr, weight_decay=self.weight_decay,
+                                    betas=self.betas, **self.optimizer_kwargs)
+            opt = MainGradOptimizer(inner, self.flat, params)
+        if self.lr_schedule is None:
+            return opt
+        from kohakuwullm_b200.utils.schedule import GroupLRSchedule, build_schedule
+
+        fn = self.lr_schedule if callable(self.lr_schedule) else build_schedule(dict(self.lr_schedule))
+        return opt, GroupLRSchedule(opt, fn)
 
     def boundary_example(self, plan: StagePlan):
         dtype = next(p for p in self.stages[0].parameters() if p.dim() >= 2).dtype

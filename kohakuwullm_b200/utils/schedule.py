@@ -52,3 +52,32 @@ def build_schedule(spec: dict | None) -> Callable[[int], float]:
 
         return f
     return _single(spec)
+
+
+class GroupLRSchedule:
+    """A scheduler object for the training loops (``step`` / ``state_dict`` / ``load_state_dict``): after every
+    optimizer step each parameter group's rate becomes its OWN base rate times ``fn(step)``, so groups with
+    different base rates (Muon, embedding, muP groups) keep their ratios. Works on anything with ``param_groups``."""
+
+    def __init__(self, optimizer, fn: Callable[[int], float]):
+        self.optimizer, self.fn, self.step_count = optimizer, fn, 0
+        self.base = [g["lr"] for g in optimizer.param_groups]
+        self._apply()
+
+    def _apply(self) -> None:
+        f = float(self.fn(self.step_count))
+        for g, base in zip(self.optimizer.param_groups, self.base):
+            g["lr"] = base * f
+
+    def step(self) -> None:
+        self.step_count += 1
+        self._apply()
+
+    def state_dict(self) -> dict:
+        return {"step": self.step_count, "base": list(self.base)}
+
+    def load_state_dict(self, state: dict) -> None:
+        self.step_count = int(state.get("step", 0))
+        if state.get("base") and len(state["base"]) == len(self.base):
+            self.base = list(state["base"])
+        self._apply()

@@ -139,3 +139,52 @@ def test_multi_stream_boundaries_give_every_stage_its_gradient():
     from tests.helpers import free_port
 
     assert pipe_streams.main(["--case", "all", "--stages", "4", "--port", str(free_port())]) == 0
+
+
+def _pipe_cli_worker(rank, world, port, tmp):
+    import importlib
+    import json
+
+    from kohakuwullm_b200.utils.config import configure
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank))
+    mod = importlib.import_module("kohakuwullm_b200.cli.train_lm_pipe")
+    arch = dict(vocab_size=258, dim=32, depth=4, heads=2, kv_heads=1, head_dim=16, mlp_hidden=64, moe_every=1, moe_first_dense=1,
+                moe_num_experts=4, moe_top_k=2, moe_hidden=32, mxfp8=False)
+    common = ["--set", "BACKEND='gloo'", "--set", "PRESET='B200-smoke'", "--set", f"ARCH_OVERRIDES={arch!r}", "--set", "MICRO_TOKENS=64",
+              "--set", "NUM_MICROBATCHES=3", "--set", "CTX_MAX=48", "--set", "AUTOTUNE=False", "--set", f"DATA={os.path.join(tmp, 'web')!r}",
+              "--set", "OPTIMIZER='muon'", "--set", "OPTIMIZER_KWARGS={'muon_lr': 0.01}", "--set", "WARMUP_STEPS=2",
+              "--set", "AUX_LOSS_WEIGHT=0.01", "--set", "BIAS_SCHEDULE={'mode': 'linear', 'end': 10}", "--set", "LOG_INTERVAL=1",
+              "--set", f"METRICS_JSONL={os.path.join(tmp, 'm.jsonl')!r}"]
+    configure(mod, common + ["--set", "MAX_STEPS=3", "--set", f"CKPT_DIR={os.path.join(tmp, 'ck')!r}"])
+    tr = mod.main()
+    lrs = [g["lr"] for g in tr.optimizer.param_groups]
+    mod = importlib.reload(mod)
+    configure(mod, common + ["--set", "MAX_STEPS=1", "--set", f"CHECKPOINT_PATH={os.path.join(tmp, 'ck', 'last.ckpt')!r}"])
+    tr2 = mod.main()
+    if rank == 0:
+        with open(os.path.join(tmp, "result.json"), "w") as f:
+            json.dump({"steps": tr.loop.global_step, "lrs": lrs, "steps2": tr2.loop.global_step}, f)
+
+
+@pytest.mark.timeout(600)
+def test_pipeline_training_cli_on_a_corpus_with_muon_schedule_and_weight_only_restart(tmp_path):
+    """The pipeline entry point on two gloo ranks: jsonl corpus through the micro-batched loader (identical on both
+    ranks), a small MoE, Muon with a warm-up / cosine schedule that scales every group, the router-bias schedule, JSONL
+    metrics, a whole-model checkpoint, and a second run that starts from its weights."""
+    import json
+    import random
+
+    from tests.helpers import free_port
+
+    rng = random.Random(2)
+    d = tmp_path / "web"
+    d.mkdir()
+    (d / "part-0.jsonl").write_text("\n".join(json.dumps({"text": "".join(rng.choice("abcdef ") for _ in range(rng.randint(10, 60)))})
+                                              for _ in range(200)) + "\n")
+    mp.spawn(_pipe_cli_worker, args=(2, free_port(), str(tmp_path)), nprocs=2, join=True)
+    res = json.load(open(tmp_path / "result.json"))
+    assert res["steps"] == 3 and res["steps2"] == 1
+    assert len(set(round(x, 9) for x in res["lrs"])) > 1           # Muon and AdamW groups keep their own rates
+    rows = [json.loads(l) for l in open(tmp_path / "m.jsonl")]
+    assert rows and all(r["train/loss"] == r["train/loss"] for r in rows if "train/loss" in r)
