@@ -15,6 +15,7 @@ microbatch.py:20-261, resume.py:20-274.
 
 from __future__ import annotations
 
+import io
 import multiprocessing as mp
 import queue
 from typing import Callable
@@ -34,9 +35,15 @@ def _worker_main(make_loader: Callable, state: dict | None, out: "mp.Queue", sto
         if state is not None:
             loader.load_state_dict(state)
         for batch, pos in loader:
+            # as BYTES: a tensor put on a multiprocessing queue travels as a shared-memory file descriptor that the
+            # receiver has to fetch from a helper thread of the sender, which fails (EOFError) when the sender is a
+            # forked child that is exiting or busy; a byte string goes through the pipe itself
+            buf = io.BytesIO()
+            torch.save(batch, buf)
+            payload = buf.getvalue()
             while not stop.is_set():
                 try:
-                    out.put((batch, pos), timeout=0.2)
+                    out.put((payload, pos), timeout=0.2)
                     break
                 except queue.Full:
                     continue
@@ -119,7 +126,7 @@ class WorkerPackLoader:
             try:
                 while True:
                     q.get_nowait()
-            except (queue.Empty, OSError, ValueError):
+            except (queue.Empty, OSError, ValueError, EOFError):
                 pass
         for p in self._procs:
             p.join(timeout=2.0)
@@ -150,6 +157,9 @@ class WorkerPackLoader:
                 batch, pos = item
                 if isinstance(batch, str) and batch == _STOP:
                     raise RuntimeError(f"loader worker {w} failed: {pos}")
+                import torch
+
+                batch = torch.load(io.BytesIO(batch), weights_only=False)
                 if self.pin_memory and hasattr(batch, "pin_memory"):
                     batch = batch.pin_memory()
                 self._positions[w] = pos
