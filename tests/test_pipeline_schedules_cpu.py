@@ -141,7 +141,7 @@ def test_multi_stream_boundaries_give_every_stage_its_gradient():
     assert pipe_streams.main(["--case", "all", "--stages", "4", "--port", str(free_port())]) == 0
 
 
-def _pipe_cli_worker(rank, world, port, tmp):
+def _pipe_cli_worker(rank, world, port, port2, tmp):
     import importlib
     import json
 
@@ -159,6 +159,7 @@ def _pipe_cli_worker(rank, world, port, tmp):
     configure(mod, common + ["--set", "MAX_STEPS=3", "--set", f"CKPT_DIR={os.path.join(tmp, 'ck')!r}"])
     tr = mod.main()
     lrs = [g["lr"] for g in tr.optimizer.param_groups]
+    os.environ["MASTER_PORT"] = str(port2)      # a second rendezvous in the same processes: never on the port just closed
     mod = importlib.reload(mod)
     configure(mod, common + ["--set", "MAX_STEPS=1", "--set", f"CHECKPOINT_PATH={os.path.join(tmp, 'ck', 'last.ckpt')!r}"])
     tr2 = mod.main()
@@ -182,7 +183,7 @@ def test_pipeline_training_cli_on_a_corpus_with_muon_schedule_and_weight_only_re
     d.mkdir()
     (d / "part-0.jsonl").write_text("\n".join(json.dumps({"text": "".join(rng.choice("abcdef ") for _ in range(rng.randint(10, 60)))})
                                               for _ in range(200)) + "\n")
-    mp.spawn(_pipe_cli_worker, args=(2, free_port(), str(tmp_path)), nprocs=2, join=True)
+    mp.spawn(_pipe_cli_worker, args=(2, free_port(), free_port(), str(tmp_path)), nprocs=2, join=True)
     res = json.load(open(tmp_path / "result.json"))
     assert res["steps"] == 3 and res["steps2"] == 1
     assert len(set(round(x, 9) for x in res["lrs"])) > 1           # Muon and AdamW groups keep their own rates
