@@ -130,3 +130,25 @@ def test_graph_replay_with_varying_micro_batch_sizes_matches_eager():
     rel = (num / max(den, 1e-30)) ** 0.5
     print("relative distance of the updates:", rel)
     assert rel < 0.1, rel    # measured 0.02
+
+
+@pytest.mark.parametrize("name,kwargs", [("muon", {"muon_lr": 0.02}), ("adamw16", {}), ("adamw8bit", {})])
+def test_engine_steps_with_other_registered_optimizers_on_the_native_path(name, kwargs):
+    """The graphed native forward / backward with an optimizer that reads ``p.grad``: bf16 parameters, flat fp32
+    gradients handed over per step; the loss on one repeated batch must fall and stay finite."""
+    from kohakuwullm_b200.data.synthetic import make_packs
+    from kohakuwullm_b200.models import LMBackbone, get_preset
+    from kohakuwullm_b200.ops import native
+    from kohakuwullm_b200.training.engine import TrainEngine
+
+    cfg = get_preset("B200-smoke", depth=2, vocab_size=2048)
+    torch.manual_seed(5)
+    with torch.device("cuda"):
+        model = LMBackbone(cfg)
+    eng = TrainEngine(model, lr=2e-3, param_dtype=torch.bfloat16, optimizer=name, optimizer_kwargs=dict(kwargs))
+    packs = [p.to("cuda") for p in make_packs(2, 1024, 32, 512, cfg.vocab_size, seed=9)]
+    losses = [float(eng.step(packs)["loss"]) for _ in range(6)]
+    torch.cuda.synchronize()
+    native.check_status()
+    assert all(l == l and l < 1e4 for l in losses), losses
+    assert losses[-1] < losses[0] - 0.05, losses
