@@ -150,6 +150,54 @@ def native_supported(q, k, v) -> bool:
     )
 
 
+def _block_attention(qb, kf, vf, q0: int, window, sink, scale: float):
+    """Rows [q0, q0 + len(qb)) of ONE document against its keys [lo, q0 + len(qb)): (out, lse) in fp32."""
+    Lq = qb.shape[1]
+    hi = q0 + Lq
+    lo = max(0, q0 - window + 1) if window is not None else 0
+    scores = torch.matmul(qb, kf[:, lo:hi].transpose(1, 2)) * scale            # (Hq, Lq, hi - lo)
+    qi = torch.arange(q0, hi, device=qb.device)[:, None]
+    kj = torch.arange(lo, hi, device=qb.device)[None, :]
+    ok = kj <= qi
+    if window is not None:
+        ok &= (qi - kj) < window
+    scores = scores.masked_fill(~ok, float("-inf"))
+    lse = torch.logsumexp(scores, dim=-1)
+    if sink is not None:
+        lse = torch.logaddexp(lse, sink[:, None])
+    return torch.matmul(torch.exp(scores - lse[..., None]), vf[:, lo:hi]), lse
+
+
+def varlen_attention_blockwise(q, k, v, cu_seqlens, window=None, sink_lse=None, scale=None, return_lse=False,
+                               block: int = 1024):
+    """PyTorch path for head sizes the native kernels do not cover (they are written for 64): the same
+    semantics as the oracle above, but a document is processed ``block`` query rows at a time, each block under
+    activation recomputation, so the peak is (heads x block x keys) instead of (heads x L x L) in forward AND
+    backward, and a sliding window also bounds the keys a block touches."""
+    from torch.utils.checkpoint import checkpoint
+
+    T, Hq, D = q.shape
+    group = Hq // k.shape[1]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    sink = sink_lse.float() if sink_lse is not None else None
+    bounds = cu_seqlens.tolist()
+    outs, lses = [], []
+    for s, e in zip(bounds[:-1], bounds[1:]):
+        qf = q[s:e].float().transpose(0, 1)
+        kf = k[s:e].float().transpose(0, 1).repeat_interleave(group, 0)
+        vf = v[s:e].float().transpose(0, 1).repeat_interleave(group, 0)
+        for q0 in range(0, e - s, block):
+            qb = qf[:, q0:q0 + block]
+            if torch.is_grad_enabled() and (qb.requires_grad or kf.requires_grad or vf.requires_grad):
+                o, l = checkpoint(_block_attention, qb, kf, vf, q0, window, sink, float(scale), use_reentrant=False)
+            else:
+                o, l = _block_attention(qb, kf, vf, q0, window, sink, float(scale))
+            outs.append(o.transpose(0, 1))
+            lses.append(l)
+    out = torch.cat(outs, 0).to(q.dtype) if outs else q.new_zeros(q.shape)
+    return (out, torch.cat(lses, 1)) if return_lse else out
+
+
 def varlen_attention(q, k, v, cu_seqlens, max_seqlen=None, window=None, sink_lse=None, scale=None,
                      plan=None, return_lse=False):
     """Packed causal attention; see the module docstring for the semantics."""
@@ -161,7 +209,7 @@ def varlen_attention(q, k, v, cu_seqlens, max_seqlen=None, window=None, sink_lse
             sink_lse = sink_lse.float()
         out, lse = _FlashVarlen.apply(q, k, v, cu_seqlens, plan, window, sink_lse, float(scale))
         return (out, lse) if return_lse else out
-    return varlen_attention_reference(q, k, v, cu_seqlens, window, sink_lse, scale, return_lse)
+    return varlen_attention_blockwise(q, k, v, cu_seqlens, window, sink_lse, scale, return_lse)
 
 
 # --------------------------------------------------------------------------------- fused core

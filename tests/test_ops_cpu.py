@@ -168,3 +168,30 @@ def test_mxfp8_swap_census_buckets_and_closing_sweep():
     dense.blocks[0].extra_matrix = nn.Parameter(torch.zeros(64, 64))
     r6 = swap_mxfp8(dense)
     assert r6.unaccounted == ["blocks.0.extra_matrix(64, 64)"]
+
+
+def test_blockwise_attention_fallback_matches_the_oracle_for_other_head_sizes():
+    """Head sizes without a native kernel take a blockwise PyTorch path with recomputation: same outputs, lse and
+    gradients as the full-matrix oracle, with windows and sinks, for blocks that do not divide the documents."""
+    import torch
+
+    from kohakuwullm_b200.models.seqinfo import SeqInfo
+    from kohakuwullm_b200.ops.attention import varlen_attention, varlen_attention_blockwise, varlen_attention_reference
+
+    torch.manual_seed(0)
+    info = SeqInfo.from_lengths([70, 33, 129])
+    T, Hq, Hkv, D = info.total_tokens, 4, 2, 128
+    for window, sinks in ((None, False), (40, True)):
+        q, k, v = (torch.randn(T, h, D, requires_grad=True) for h in (Hq, Hkv, Hkv))
+        sink = torch.randn(Hq, requires_grad=True) if sinks else None
+        ref, lse_r = varlen_attention_reference(q, k, v, info.cu_seqlens, window, sink, return_lse=True)
+        g = torch.randn_like(ref)
+        grads_r = torch.autograd.grad(ref, [q, k, v] + ([sink] if sinks else []), g)
+        out, lse = varlen_attention_blockwise(q, k, v, info.cu_seqlens, window, sink, return_lse=True, block=48)
+        grads = torch.autograd.grad(out, [q, k, v] + ([sink] if sinks else []), g)
+        torch.testing.assert_close(out, ref, rtol=1e-5, atol=1e-5)
+        torch.testing.assert_close(lse, lse_r, rtol=1e-5, atol=1e-5)
+        for a, b in zip(grads, grads_r):
+            torch.testing.assert_close(a, b, rtol=1e-4, atol=1e-5)
+    assert torch.equal(varlen_attention(q, k, v, info.cu_seqlens, window=40, sink_lse=sink),
+                       varlen_attention_blockwise(q, k, v, info.cu_seqlens, 40, sink))      # the public entry point uses it
