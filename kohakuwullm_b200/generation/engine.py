@@ -96,9 +96,11 @@ class LocalGenerator:
         return self._rng[key]
 
     @torch.no_grad()
-    def generate(self, prompt: torch.Tensor, max_new_tokens: int, **sampling) -> torch.Tensor:
-        """prompt (rows, S) of equal-length rows -> (rows, S + new)."""
+    def generate(self, prompt: torch.Tensor, max_new_tokens: int | None = 128, **sampling) -> torch.Tensor:
+        """prompt (rows, S) of equal-length rows -> (rows, S + new). ``max_new_tokens=None``: until every row has
+        stopped or the context is full."""
         bb = self.backbone
+        max_new_tokens = token_budget(max_new_tokens, prompt.shape[1], getattr(bb.config, "max_position", 1 << 30))
         was_training = bb.training
         bb.eval()
         tokens = prompt

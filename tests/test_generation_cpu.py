@@ -118,3 +118,28 @@ def test_token_budget():
     assert token_budget(16, 10, 8192) == 16
     assert token_budget(None, 10, 64) == 54            # until the context is full
     assert token_budget(100, 60, 64) == 4
+
+
+def test_sample_cli_from_a_checkpoint(tmp_path, capsys):
+    from kohakuwullm_b200.cli import sample
+    from kohakuwullm_b200.pipe import checkpoint as ckpt
+
+    from kohakuwullm_b200.models import LMBackbone, get_preset
+
+    cfg = dict(GEN_CFG, vocab_size=258)                   # the byte tokenizer's ids plus BOS / EOS
+    torch.manual_seed(7)
+    model = LMBackbone(get_preset("B200-smoke", **cfg))
+    path = str(tmp_path / "m.ckpt")
+    ckpt.save(path, model)
+    sets = [x for k, v in cfg.items() for x in ("--set", f"{k}={v}")]
+    rc = sample.main(["--ckpt", path, "--preset", "B200-smoke", *sets, "--prompt", "ab", "--prompt", "hello", "--count", "2",
+                      "--max-new-tokens", "6", "--temperature", "0.7", "--top-k", "20", "--device", "cpu", "--bench-steps", "1"])
+    out = capsys.readouterr().out
+    assert rc == 0 and out.count("--- prompt") == 4 and out.count("--- decode:") == 2
+    # greedy decoding from the CLI equals the generator on the same weights
+    sample.main(["--ckpt", path, "--preset", "B200-smoke", *sets, "--prompt", "ab", "--max-new-tokens", "5", "--temperature", "0",
+                 "--device", "cpu"])
+    first = capsys.readouterr().out
+    sample.main(["--ckpt", path, "--preset", "B200-smoke", *sets, "--prompt", "ab", "--max-new-tokens", "5", "--temperature", "0",
+                 "--device", "cpu", "--no-cache"])
+    assert capsys.readouterr().out == first
