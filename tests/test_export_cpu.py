@@ -87,3 +87,114 @@ def test_build_tokenizer_cli(tmp_path, capsys):
     assert vocab["<|bos|>"] == 320 and vocab["<|reserved_9|>"] == target - 1
     ids = built.encode("the quick fox").ids
     assert ids[0] == vocab["<|bos|>"] and built.decode(ids[1:]) == "the quick fox"
+
+
+def _read_gguf(path):
+    """A minimal GGUF v3 reader: metadata (scalars, strings, arrays) and tensors as float32 arrays."""
+    import numpy as np
+
+    raw = open(path, "rb").read()
+    pos = 0
+
+    def take(fmt):
+        nonlocal pos
+        out = struct.unpack_from("<" + fmt, raw, pos)
+        pos += struct.calcsize("<" + fmt)
+        return out if len(out) > 1 else out[0]
+
+    def string():
+        nonlocal pos
+        n = take("Q")
+        s = raw[pos:pos + n].decode("utf-8")
+        pos += n
+        return s
+
+    def value(t):
+        if t == 8:
+            return string()
+        if t == 9:
+            et, n = take("I"), take("Q")
+            return [value(et) for _ in range(n)]
+        return take({4: "I", 5: "i", 6: "f", 7: "B", 10: "Q"}[t])
+
+    magic, version, n_tensors, n_kv = take("I"), take("I"), take("Q"), take("Q")
+    meta = {}
+    for _ in range(n_kv):
+        k = string()
+        meta[k] = value(take("I"))
+    infos = []
+    for _ in range(n_tensors):
+        name = string()
+        nd = take("I")
+        dims = [take("Q") for _ in range(nd)]
+        infos.append((name, list(reversed(dims)), take("I"), take("Q")))
+    base = (pos + 31) // 32 * 32
+    tensors = {}
+    for name, shape, code, off in infos:
+        n = int(np.prod(shape))
+        if code == 0:
+            arr = np.frombuffer(raw, np.float32, n, base + off)
+        elif code == 1:
+            arr = np.frombuffer(raw, np.float16, n, base + off).astype(np.float32)
+        else:
+            arr = (np.frombuffer(raw, np.uint16, n, base + off).astype(np.uint32) << 16).view(np.float32)
+        tensors[name] = torch.from_numpy(arr.reshape(shape).copy())
+    return (magic, version), meta, tensors
+
+
+def test_gguf_export_in_llama_cpp_layouts(tmp_path):
+    """dots1 for a sparse model, qwen3 for a dense one: hyper-parameters, tensor names, the q/k/v and gate/up splits,
+    GQA expansion, dtype choice, and the tokenizer block."""
+    import json
+
+    from kohakuwullm_b200.cli import to_gguf
+
+    common = dict(vocab_size=101, dim=64, depth=2, heads=4, kv_heads=2, head_dim=16, mlp_hidden=96, mxfp8=False)
+    sparse = get_preset("B200-moe-991M", **common, moe_first_dense=1, moe_num_experts=4, moe_top_k=2, moe_hidden=48, moe_num_shared=1)
+    torch.manual_seed(0)
+    model = LMBackbone(sparse)
+    state = model.state_dict()
+    tokdir = tmp_path / "tok"
+    tokdir.mkdir()
+    vocab = {f"t{i}": i for i in range(99)}
+    (tokdir / "tokenizer.json").write_text(json.dumps({
+        "model": {"vocab": vocab, "merges": [["t0", "t1"], "t2 t3"]},
+        "added_tokens": [{"id": 99, "content": "<|bos|>", "special": True}, {"id": 100, "content": "<|im_end|>", "special": True}]}))
+    (tokdir / "tokenizer_config.json").write_text(json.dumps({"bos_token": "<|bos|>", "eos_token": {"content": "<|im_end|>"},
+                                                              "chat_template": "{{ messages }}"}))
+    out = str(tmp_path / "moe.gguf")
+    info = to_gguf.convert(state, sparse, out, name="tiny-moe", out_dtype="bf16", tokenizer=str(tokdir))
+    assert info["arch"] == "dots1"
+    (magic, version), meta, tensors = _read_gguf(out)
+    assert (magic, version) == (to_gguf.GGUF_MAGIC, 3)
+    assert meta["general.architecture"] == "dots1" and meta["general.file_type"] == 32
+    assert meta["dots1.block_count"] == 2 and meta["dots1.attention.head_count_kv"] == 4        # expanded to one per query head
+    assert meta["dots1.expert_count"] == 4 and meta["dots1.expert_used_count"] == 2 and meta["dots1.leading_dense_block_count"] == 1
+    assert meta["dots1.feed_forward_length"] == 96 and meta["dots1.expert_feed_forward_length"] == 48
+    assert meta["tokenizer.ggml.model"] == "gpt2" and len(meta["tokenizer.ggml.tokens"]) == 101
+    assert meta["tokenizer.ggml.merges"] == ["t0 t1", "t2 t3"] and meta["tokenizer.ggml.token_type"][99] == 3
+    assert meta["tokenizer.ggml.bos_token_id"] == 99 and meta["tokenizer.ggml.eos_token_id"] == 100
+    assert meta["tokenizer.ggml.eot_token_id"] == 100 and meta["tokenizer.chat_template"] == "{{ messages }}"
+    qkv = state["blocks.0.attn.qkv_proj.weight"].float()
+    bf = lambda t: t.to(torch.bfloat16).float()  # noqa: E731
+    assert torch.equal(tensors["blk.0.attn_q.weight"], bf(qkv[:64]))
+    k = qkv[64:96].reshape(2, 16, 64).repeat_interleave(2, 0).reshape(64, 64)
+    assert torch.equal(tensors["blk.0.attn_k.weight"], bf(k)) and tensors["blk.0.attn_v.weight"].shape == (64, 64)
+    gate, up = state["blocks.0.mlp.w_in.weight"].float().chunk(2, 0)
+    assert torch.equal(tensors["blk.0.ffn_gate.weight"], bf(gate)) and torch.equal(tensors["blk.0.ffn_up.weight"], bf(up))
+    assert tensors["blk.1.ffn_gate_exps.weight"].shape == (4, 48, 64) and tensors["blk.1.ffn_down_exps.weight"].shape == (4, 64, 48)
+    assert tensors["blk.1.ffn_gate_shexp.weight"].shape[1] == 64 and "blk.1.exp_probs_b.bias" in tensors
+    assert torch.equal(tensors["blk.0.attn_q_norm.weight"], state["blocks.0.attn.q_norm"].float())   # vectors stay fp32
+    assert not any("load_accum" in n for n in tensors)
+
+    dense = get_preset("B200-smoke", **common)
+    dmodel = LMBackbone(dense)
+    ckpt_path = str(tmp_path / "d.ckpt")
+    torch.save({"state_dict": dmodel.state_dict()}, ckpt_path)
+    sets = [x for k, v in common.items() for x in ("--set", f"{k}={v}")]
+    assert to_gguf.main(["--ckpt", ckpt_path, "--preset", "B200-smoke", *sets, "--out", str(tmp_path / "d.gguf"),
+                         "--no-expand-kv", "--out-dtype", "f32"]) == 0
+    _, dmeta, dtensors = _read_gguf(str(tmp_path / "d.gguf"))
+    assert dmeta["general.architecture"] == "qwen3" and dmeta["qwen3.attention.head_count_kv"] == 2 and "qwen3.expert_count" not in dmeta
+    assert dtensors["blk.1.attn_k.weight"].shape == (32, 64)
+    assert torch.equal(dtensors["output.weight"], dmodel.state_dict()["head.proj.weight"].float())
