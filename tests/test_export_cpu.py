@@ -198,3 +198,28 @@ def test_gguf_export_in_llama_cpp_layouts(tmp_path):
     assert dmeta["general.architecture"] == "qwen3" and dmeta["qwen3.attention.head_count_kv"] == 2 and "qwen3.expert_count" not in dmeta
     assert dtensors["blk.1.attn_k.weight"].shape == (32, 64)
     assert torch.equal(dtensors["output.weight"], dmodel.state_dict()["head.proj.weight"].float())
+
+
+def test_to_hf_cli_copies_the_tokenizer_and_checks_logits(tmp_path, capsys):
+    import json
+    import os
+
+    from kohakuwullm_b200.cli import to_hf
+
+    common = dict(vocab_size=101, dim=64, depth=2, heads=2, kv_heads=1, head_dim=32, mlp_hidden=128, init_std=0.2, mxfp8=False)
+    torch.manual_seed(1)
+    model = LMBackbone(get_preset("B200-smoke", **common))
+    ckpt_path = str(tmp_path / "m.ckpt")
+    torch.save({"state_dict": model.state_dict()}, ckpt_path)
+    tokdir = tmp_path / "tok"
+    tokdir.mkdir()
+    (tokdir / "tokenizer.json").write_text(json.dumps({"model": {"vocab": {}, "merges": []}}))
+    (tokdir / "tokenizer_config.json").write_text("{}")
+    sets = [x for k, v in common.items() for x in ("--set", f"{k}={v}")]
+    out = tmp_path / "hf"
+    assert to_hf.main(["--ckpt", ckpt_path, "--preset", "B200-smoke", *sets, "--out", str(out), "--out-dtype", "fp32",
+                       "--tokenizer", str(tokdir), "--check"]) == 0
+    text = capsys.readouterr().out
+    assert "check: largest relative logit difference" in text and "tokenizer.json" in text
+    for name in ("config.json", "modeling_kohaku.py", "configuration_kohaku.py", "tokenizer.json", "tokenizer_config.json"):
+        assert os.path.exists(out / name), name
