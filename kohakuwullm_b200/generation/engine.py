@@ -69,7 +69,11 @@ def sample(logits: torch.Tensor, temperature: float = 1.0, top_k: int = 0, top_p
 def token_budget(max_new_tokens: int | None, prompt_len: int, max_position: int) -> int:
     """New tokens to decode: the request, cut to what the model's context still holds (None: all of it)."""
     room = max(int(max_position) - int(prompt_len), 0)
-    return room if max_new_tokens is None else min(int(max_new_tokens), room) if room else int(max_new_tokens)
+    if max_new_tokens is None:
+        return room
+    # an explicit request is honoured up to the context; a prompt that already fills the context keeps the request
+    # (rotary positions extrapolate; the caller asked for it)
+    return min(int(max_new_tokens), room) if room else int(max_new_tokens)
 
 
 def advance(tokens: torch.Tensor, nxt: torch.Tensor, finished: torch.Tensor, stop_ids: Sequence[int], eos: int):
