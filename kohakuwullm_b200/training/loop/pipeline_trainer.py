@@ -23,7 +23,9 @@ class PipelinedLMTrainer:
                  micro_tokens: int = 4096, num_microbatches: int = 16, schedule: str = "1f1b",
                  layers: Sequence[int] | None = None, autotune: bool = False, lr: float = 3e-4,
                  weight_decay: float = 0.1, max_grad_norm: float | None = 1.0, seed: int = 1234,
-                 param_dtype: torch.dtype | None = None, callbacks=(), device=None, group=None):
+                 param_dtype: torch.dtype | None = None, callbacks=(), device=None, group=None,
+                 optimizer: str = "fused_adamw", optimizer_kwargs: dict | None = None, lr_schedule: dict | None = None,
+                 head_only_stage: bool = False):
         from kohakuwullm_b200.models import get_preset
         from kohakuwullm_b200.models.presets import LMArchConfig
         from kohakuwullm_b200.pipe.trainer import PipelineTrainer
@@ -45,10 +47,12 @@ class PipelinedLMTrainer:
             measured = measure_costs(self.config, micro_tokens, self.device) if self.rank == 0 else None
             costs = broadcast_costs(measured, self.config.depth, self.device)
         self.plans = plan_for(self.config, self.world * chunks, micro_tokens, layers=layers, costs=costs,
-                              style="v" if schedule in ("zbv", "dualpipe-v") else "loop")
+                              style="v" if schedule in ("zbv", "dualpipe-v") else "loop",
+                              allow_empty_last=head_only_stage and costs is not None)
         kw = {} if param_dtype is None else {"param_dtype": param_dtype}
         self.module = LMPipelineModule(self.config, micro_tokens=micro_tokens, lr=lr, weight_decay=weight_decay,
-                                       seed=seed, group=group, **kw)
+                                       seed=seed, group=group, optimizer=optimizer, optimizer_kwargs=optimizer_kwargs,
+                                       lr_schedule=lr_schedule, **kw)
         self.trainer = PipelineTrainer(self.module, self.plans, rank=self.rank, world=self.world, device=self.device,
                                        n_micro=num_microbatches, schedule=schedule, max_grad_norm=max_grad_norm,
                                        callbacks=list(callbacks), group=group)
