@@ -59,6 +59,7 @@ CKPT_DIR = ""
 CKPT_EVERY = 1000
 RESUME = ""
 SEED = 1234
+GPUS = 0                    # > 1 and not under a launcher: spawn that many ranks on this machine (no restarts)
 DEVICE = "auto"
 WANDB_PROJECT = ""          # a Weights & Biases project name turns the W&B sink on (rank 0)
 WANDB_MODE = "offline"      # these machines have no network: sync the run directory later
@@ -169,4 +170,7 @@ if __name__ == "__main__":
     from kohakuwullm_b200.utils.config import configure
 
     configure(sys.modules[__name__], sys.argv[1:])
-    main()
+    from kohakuwullm_b200.utils.launch import maybe_self_launch
+
+    if not maybe_self_launch("kohakuwullm_b200.cli.train_lm", GPUS):
+        main()

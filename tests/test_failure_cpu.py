@@ -141,3 +141,72 @@ def test_truncated_or_foreign_checkpoint_file_raises_a_checkpoint_error():
             ckpt.load(path, model)
         with pytest.raises(FileNotFoundError):
             ckpt.load(os.path.join(tmp, "missing.ckpt"), model)
+
+
+def test_spike_score_flags_a_loss_spike_and_ignores_noise():
+    import random
+
+    from kohakuwullm_b200.training.loop.health import SpikeScore
+
+    rng = random.Random(0)
+    s = SpikeScore(window=200, threshold=7.0, min_history=20)
+    flagged = [s.is_spike(s.update(2.0 + 0.01 * rng.gauss(0, 1))) for _ in range(150)]
+    assert not any(flagged)
+    assert s.is_spike(s.update(2.5))                      # fifty sigma above the running median
+    assert not s.is_spike(s.update(2.01))                 # and the detector recovers at once (median / MAD are robust)
+
+
+def test_killed_loader_worker_is_reported_not_waited_for():
+    """A worker process that dies (killed from outside, out of memory) must surface as an error in the trainer process
+    within a second or two, not as a stalled input pipeline."""
+    import os
+    import random
+    import signal
+    import time
+
+    import pytest
+
+    from kohakuwullm_b200.data import ByteTokenizer
+    from kohakuwullm_b200.data.loader.workers import WorkerPackLoader
+    from kohakuwullm_b200.data.renderers.base import PlainRenderer
+    from kohakuwullm_b200.data.sources.records import ListRecords
+
+    tok = ByteTokenizer()
+    records = ListRecords([{"text": "z" * n} for n in random.Random(2).choices(range(3, 50), k=400)])
+    loader = WorkerPackLoader(records, PlainRenderer(), tok.encode, workers=1, prefetch=1, k=64, m=16, seed=3)
+    it = iter(loader)
+    next(it)
+    os.kill(loader._procs[0].pid, signal.SIGKILL)
+    t0 = time.time()
+    with pytest.raises(RuntimeError, match="loader worker 0 exited"):
+        for _ in range(20):                                # what the worker had already queued may still arrive
+            next(it)
+    assert time.time() - t0 < 30
+
+
+def test_training_script_launches_its_own_ranks(tmp_path):
+    """``GPUS=2`` without a launcher: the script spawns two ranks (gloo here), trains and writes one checkpoint; a rank
+    that raises ends the whole run with an error instead of leaving its peer waiting."""
+    import json
+    import os
+    import random
+    import subprocess
+    import sys
+
+    rng = random.Random(3)
+    d = tmp_path / "web"
+    d.mkdir()
+    (d / "part-0.jsonl").write_text("\n".join(json.dumps({"text": "".join(rng.choice("abcdef ") for _ in range(rng.randint(10, 60)))})
+                                              for _ in range(200)) + "\n")
+    arch = dict(vocab_size=258, dim=32, depth=2, heads=2, kv_heads=1, head_dim=16, mlp_hidden=64, mxfp8=False)
+    base = [sys.executable, "-m", "kohakuwullm_b200.cli.train_lm_pipe", "--set", "GPUS=2", "--set", "BACKEND='gloo'",
+            "--set", "PRESET='B200-smoke'", "--set", f"ARCH_OVERRIDES={arch!r}", "--set", "MICRO_TOKENS=64", "--set", "NUM_MICROBATCHES=2",
+            "--set", "CTX_MAX=48", "--set", "AUTOTUNE=False", "--set", f"DATA={str(d)!r}", "--set", "MAX_STEPS=2", "--set", "WARMUP_STEPS=1"]
+    env = dict(os.environ, PYTHONPATH=os.getcwd())
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT"):
+        env.pop(k, None)
+    ok = subprocess.run(base + ["--set", f"CKPT_DIR={str(tmp_path / 'ck')!r}"], env=env, capture_output=True, text=True, timeout=300)
+    assert ok.returncode == 0, ok.stderr[-2000:]
+    assert os.path.exists(tmp_path / "ck" / "last.ckpt")
+    bad = subprocess.run(base + ["--set", "SCHEDULE='no-such-schedule'"], env=env, capture_output=True, text=True, timeout=300)
+    assert bad.returncode != 0 and "no-such-schedule" in (bad.stderr + bad.stdout)
