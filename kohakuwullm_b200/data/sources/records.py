@@ -41,9 +41,13 @@ class CorpusRecords:
         self.root, self.text_field = root, text_field
         path = os.path.join(root, self.MANIFEST)
         if rebuild_manifest or not os.path.exists(path):
+            # several ranks may get here at once: each builds the (identical) manifest for itself and publishes it
+            # with an atomic rename, so no reader ever sees a half-written file
             self.manifest = self.build_manifest(root)
-            with open(path, "w") as f:
+            tmp = f"{path}.{os.getpid()}.tmp"
+            with open(tmp, "w") as f:
                 json.dump(self.manifest, f)
+            os.replace(tmp, path)
         else:
             with open(path) as f:
                 self.manifest = json.load(f)
