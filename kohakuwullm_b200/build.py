@@ -56,6 +56,21 @@ def _compile(nvcc: str, src: Path, obj: Path, verbose: bool) -> str:
 
 
 def build(force: bool = False, verbose: bool = False) -> Path:
+    """Compile what is stale and link. Safe to call from several processes at once (the ranks of a job that start on
+    a machine where the library has not been built yet): one holds an exclusive file lock and builds, the others wait
+    for it and then find everything up to date."""
+    import fcntl
+
+    OBJ.mkdir(parents=True, exist_ok=True)
+    with open(OBJ / ".lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            return _build_locked(force, verbose)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+def _build_locked(force: bool, verbose: bool) -> Path:
     nvcc = _nvcc()
     OBJ.mkdir(parents=True, exist_ok=True)
     headers = sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h"))
@@ -74,23 +89,32 @@ def build(force: bool = False, verbose: bool = False) -> Path:
                     print(f"--- {futs[f].name}\n{out}")
     objs = [OBJ / (s.stem + ".o") for s in sources]
     if force or jobs or _stale(LIB, objs):
-        cmd = [nvcc, "-shared", "-o", str(LIB), *map(str, objs), "-lcudart_static", "-lpthread", "-ldl", "-lrt"]
+        # link next to the target and rename: a process that loads the library meanwhile sees the old or the new file
+        tmp = LIB.with_suffix(".so.tmp")
+        cmd = [nvcc, "-shared", "-o", str(tmp), *map(str, objs), "-lcudart_static", "-lpthread", "-ldl", "-lrt"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+        os.replace(tmp, LIB)
     return LIB
 
 
 def build_cpu(force: bool = False) -> Path:
     """C++ CPU oracles (``csrc/cpu/*.cpp``) -> ``_kwu_cpu.so`` with the host compiler."""
+    import fcntl
+
     sources = sorted(CPU_SRC.glob("*.cpp"))
-    if force or _stale(CPU_LIB, sources):
-        cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
-        cmd = [cxx, "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-o", str(CPU_LIB),
-               *map(str, sources)]
-        r = subprocess.run(cmd, capture_output=True, text=True)
-        if r.returncode != 0:
-            raise RuntimeError(f"host compile failed:\n{r.stdout}\n{r.stderr}")
+    OBJ.mkdir(parents=True, exist_ok=True)
+    with open(OBJ / ".lock_cpu", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)        # as for the device library: one builder at a time, atomic publish
+        if force or _stale(CPU_LIB, sources):
+            cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
+            tmp = CPU_LIB.with_suffix(".so.tmp")
+            cmd = [cxx, "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-o", str(tmp), *map(str, sources)]
+            r = subprocess.run(cmd, capture_output=True, text=True)
+            if r.returncode != 0:
+                raise RuntimeError(f"host compile failed:\n{r.stdout}\n{r.stderr}")
+            os.replace(tmp, CPU_LIB)
     return CPU_LIB
 
 
