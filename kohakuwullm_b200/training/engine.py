@@ -153,6 +153,7 @@ class TrainEngine:
         self.fused_sync = (grad_sync == "fused" and self.world > 1 and self.device.type == "cuda"
                            and not self.generic_optimizer)
         self.ep = None
+        self.ep_sharded = bool(expert_parallel) and self.world > 1
         if expert_parallel and self.world > 1:
             from kohakuwullm_b200.parallel.ep import ExpertParallel, shard_experts
 
@@ -227,6 +228,22 @@ class TrainEngine:
             self._restore_router(router_state)
         self._graphs[key] = g      # most recently used last
         return g
+
+    def _same_micro_batch_count(self, micro_batches: Sequence[PackedBatch]) -> list[PackedBatch]:
+        """Under expert parallelism every MoE layer of every micro-batch is a collective exchange, so all ranks
+        have to run the same number of micro-batches. A document-aligned split can give one rank fewer pieces than
+        another (few long documents); the ranks agree on the largest count and the others append fully masked
+        filler micro-batches (no loss, no gradient, but they take part in the exchanges)."""
+        from kohakuwullm_b200.models.seqinfo import SeqInfo
+
+        n = torch.tensor([len(micro_batches)], dtype=torch.int32, device=self.device)
+        dist.all_reduce(n, op=dist.ReduceOp.MAX, group=self.group)
+        missing = int(n) - len(micro_batches)
+        out = list(micro_batches)
+        for _ in range(missing):
+            out.append(PackedBatch(torch.zeros(16, dtype=torch.long), torch.full((16,), -100, dtype=torch.long),
+                                   SeqInfo.from_lengths([16]), 0))
+        return out
 
     @torch.no_grad()
     def _generic_step(self) -> None:
@@ -319,6 +336,8 @@ class TrainEngine:
             # a kernel of an earlier step whose bounded wait ran out (a peer that never arrived, an expert
             # buffer that overflowed) surfaces here as an exception, without a host synchronisation
             native.poll_status()
+        if self.ep_sharded:
+            micro_batches = self._same_micro_batch_count(micro_batches)
         local_tokens = sum(mb.trained_tokens() for mb in micro_batches)
         tok = torch.tensor([float(local_tokens)], dtype=torch.float32).to(dev, non_blocking=True)
         self.sync.all_reduce_scalar(tok)

@@ -119,3 +119,36 @@ def test_expert_parallel_checkpoint_reshards_weights_and_optimizer_state():
         eng.global_step = 1
         out = eng.step([collate_packed(_docs(seed=6))])
     assert abs(float(out["loss"]) - second["loss"]) < 1e-5
+
+
+def _uneven_worker(rank, world, port, path):
+    import faulthandler
+
+    faulthandler.dump_traceback_later(120, exit=True)      # a hang here ends with every thread's stack, not a stalled suite
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    eng = TrainEngine(_model(), lr=1e-2, max_grad_norm=1.0, expert_parallel=True)
+    docs = _docs(12)
+    mine = [collate_packed(docs[i:i + 3]) for i in range(0, 9, 3)] if rank == 0 else [collate_packed(docs[9:])]
+    out = eng.step(mine)                                    # three micro-batches on rank 0, one on rank 1
+    if rank == 0:
+        torch.save({"loss": float(out["loss"]), "tokens": float(out["tokens"])}, path)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_expert_parallel_ranks_with_different_micro_batch_counts_do_not_hang():
+    """Every MoE layer of every micro-batch is a collective exchange: the ranks agree on the largest micro-batch count
+    and the others add masked filler micro-batches. The loss equals the single-process step over all twelve documents."""
+    from tests.helpers import free_port
+
+    with tempfile.TemporaryDirectory() as tmp:
+        path = os.path.join(tmp, "out.pt")
+        mp.spawn(_uneven_worker, args=(2, free_port(), path), nprocs=2, join=True)
+        got = torch.load(path)
+    docs = _docs(12)
+    ref = TrainEngine(_model(), lr=1e-2, max_grad_norm=1.0)
+    want = ref.step([collate_packed(docs[i:i + 3]) for i in range(0, 12, 3)])
+    assert got["tokens"] == float(want["tokens"])
+    assert abs(got["loss"] - float(want["loss"])) < 2e-3, (got, float(want["loss"]))
