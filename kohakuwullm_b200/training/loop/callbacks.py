@@ -80,7 +80,9 @@ class SampleLogCallback(Callback):
         self.enabled = True
 
     def on_train_batch_end(self, trainer, out, batch, step):
-        if not self.enabled or step % self.interval or trainer.rank != 0:
+        # with the experts split over the ranks a forward is a collective: every rank decodes, rank 0 reports
+        collective = bool(getattr(getattr(trainer, "engine", None), "ep_sharded", False))
+        if not self.enabled or step % self.interval or (trainer.rank != 0 and not collective):
             return
         try:
             texts = []
@@ -88,6 +90,8 @@ class SampleLogCallback(Callback):
                 ids = torch.tensor([self.tok.encode(prompt)], device=trainer.device)
                 gen = trainer.generate(ids, self.max_new, **self.sampling)
                 texts.append(self.tok.decode(gen[0].tolist()))
+            if trainer.rank != 0:
+                return
             for p, t in zip(self.prompts, texts):
                 log.info("sample", step=step, prompt=p[:40], text=t[:200].replace("\n", "\\n"))
             if self.reporter:

@@ -11,6 +11,7 @@ import sys
 import time
 
 _configured = False
+_muted = False     # this rank prints nothing (every rank but 0, unless all ranks are asked for)
 
 
 def _rank() -> int:
@@ -18,7 +19,7 @@ def _rank() -> int:
 
 
 def configure(level: str | int = "INFO", stream=None, all_ranks: bool | None = None) -> None:
-    global _configured
+    global _configured, _muted
     root = logging.getLogger("kohakuwullm_b200")
     root.handlers.clear()
     handler = logging.StreamHandler(stream or sys.stderr)
@@ -28,7 +29,8 @@ def configure(level: str | int = "INFO", stream=None, all_ranks: bool | None = N
     root.propagate = False
     if all_ranks is None:
         all_ranks = os.environ.get("KWP_LOG_ALL_RANKS", "0") == "1"
-    root.disabled = (not all_ranks) and _rank() != 0
+    # a flag of our own: ``Logger.disabled`` on the parent does not stop records that child loggers hand up
+    _muted = (not all_ranks) and _rank() != 0
     _configured = True
 
 
@@ -39,6 +41,8 @@ class StructuredLogger:
     def _emit(self, level: int, event: str, fields: dict) -> None:
         if not _configured:
             configure()
+        if _muted and level < logging.ERROR:      # errors are worth seeing from any rank
+            return
         stamp = time.strftime("%H:%M:%S")
         body = " ".join(f"{k}={_fmt(v)}" for k, v in fields.items())
         self._log.log(level, f"{stamp} [r{_rank()}] {event} {body}".rstrip())

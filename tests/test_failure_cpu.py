@@ -210,3 +210,20 @@ def test_training_script_launches_its_own_ranks(tmp_path):
     assert os.path.exists(tmp_path / "ck" / "last.ckpt")
     bad = subprocess.run(base + ["--set", "SCHEDULE='no-such-schedule'"], env=env, capture_output=True, text=True, timeout=300)
     assert bad.returncode != 0 and "no-such-schedule" in (bad.stderr + bad.stdout)
+
+
+def test_only_rank_zero_logs_unless_asked(monkeypatch):
+    import io
+
+    from kohakuwullm_b200.utils import logging as klog
+
+    for rank, all_ranks, expect in (("0", None, True), ("1", None, False), ("1", True, True)):
+        monkeypatch.setenv("RANK", rank)
+        buf = io.StringIO()
+        klog.configure(stream=buf, all_ranks=all_ranks)
+        klog.get_logger("t").info("event", x=1)
+        assert ("event x=1" in buf.getvalue()) == expect, (rank, all_ranks, buf.getvalue())
+        klog.get_logger("t").error("bad")
+        assert "bad" in buf.getvalue()                      # errors from any rank
+    monkeypatch.setenv("RANK", "0")
+    klog.configure()
