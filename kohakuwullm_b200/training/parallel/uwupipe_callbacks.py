@@ -34,6 +34,11 @@ def _routers(module) -> list:
     return found
 
 
+from kohakuwullm_b200.utils.logging import get_logger  # noqa: E402
+
+_log = get_logger("preview")
+
+
 class RouterBiasSchedule(Callback):
     def __init__(self, module, schedule: dict | Callable[[int], float]):
         self.module = module
@@ -152,6 +157,9 @@ class SamplePreview(Callback):
                         rows.append((name, "", i, self.tokenizer.decode(out[i, ids.numel():].tolist())))
         if self._rank() == 0 and not silent:
             self.history.append((step, rows))
+            for name, prompt_text, i, text in rows:
+                _log.info("sample", step=step, name=name, n=i, prompt=prompt_text[:40].replace("\n", "\\n"),
+                          text=text[:200].replace("\n", "\\n"))
             if self.report is not None:
                 self.report(step, rows)
         return rows
