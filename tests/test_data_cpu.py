@@ -308,3 +308,54 @@ def test_mixture_and_split_records():
     records, _ = build_dataset({"name": "mixture", "sources": [{"records": {"name": "list", "records": [{"text": "x"}]},
                                                                 "repeat": 2}]}, "plain")
     assert len(records) == 2
+
+
+def test_kv_store_and_mixture_properties():
+    """Property tests: any set of keys / values written in any order reads back exactly; a mixture's length and
+    per-source counts follow the repeat weights, and its fractional part never repeats a record."""
+    import tempfile
+
+    from hypothesis import given, settings
+    from hypothesis import strategies as st
+
+    from kohakuwullm_b200.data.sources.kvstore import KVFile, KVWriter, encode_key
+    from kohakuwullm_b200.data.sources.records import ListRecords, MixtureRecords
+
+    values = st.one_of(st.binary(max_size=40), st.text(max_size=20), st.dictionaries(st.text(max_size=5), st.integers(), max_size=3))
+    keys = st.one_of(st.integers(min_value=0, max_value=2 ** 40), st.text(min_size=1, max_size=12))
+
+    @settings(max_examples=40, deadline=None)
+    @given(st.lists(st.tuples(keys, values), min_size=1, max_size=30))
+    def store(pairs):
+        with tempfile.TemporaryDirectory() as tmp:
+            path = f"{tmp}/x.kv"
+            with KVWriter(path) as w:
+                for k, v in pairs:
+                    w.put(k, v)
+            kv = KVFile(path)
+            want = {}
+            for k, v in pairs:
+                want[encode_key(k)] = (k, v)                       # the last write of a key wins
+            assert len(kv) == len(want)
+            for k, v in want.values():
+                assert kv.get(k) == v
+            assert kv.keys() == sorted(kv.keys())
+
+    @settings(max_examples=40, deadline=None)
+    @given(st.lists(st.tuples(st.integers(1, 30), st.floats(0.1, 3.0)), min_size=1, max_size=4), st.integers(0, 100))
+    def mix(parts, seed):
+        sources = [{"records": ListRecords([{"text": f"{i}:{j}"} for j in range(n)]), "repeat": r, "source": f"s{i}"}
+                   for i, (n, r) in enumerate(parts)]
+        m = MixtureRecords(sources, seed=seed)
+        assert len(m) == sum(int(n * r + 1e-9) for n, r in parts)
+        start = 0
+        for i, (n, r) in enumerate(parts):
+            total = int(n * r + 1e-9)
+            got = [m[start + j]["text"] for j in range(total)]
+            assert all(t.startswith(f"{i}:") for t in got)
+            whole = (total // n) * n
+            assert len(set(got[whole:])) == total - whole          # the fractional tail is a subset without repeats
+            start += total
+
+    store()
+    mix()
