@@ -146,9 +146,11 @@ class LMTrainer:
         return {"val/loss": loss, "val/ppl": math.exp(min(loss, 20.0)), "val/tokens": int(n)}
 
     def generate(self, prompt: torch.Tensor, max_new_tokens: int, **sampling) -> torch.Tensor:
-        from kohakuwullm_b200.generation.engine import LocalGenerator
+        from kohakuwullm_b200.training.loop.sampling import PreviewSampler
 
-        return LocalGenerator(self.backbone).generate(prompt, max_new_tokens, **sampling)
+        if getattr(self, "_preview_sampler", None) is None:
+            self._preview_sampler = PreviewSampler()
+        return self._preview_sampler.generate(self.backbone, prompt, max_new_tokens, **sampling)
 
     # ------------------------------------------------------------------ checkpoints
     def save_checkpoint(self, path: str) -> None:

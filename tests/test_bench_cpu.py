@@ -93,3 +93,48 @@ def test_ladder_census_counts_active_parameters():
     assert not dense.sparse and dense.total == dense.active
     assert moe.sparse and moe.active < moe.total / 3 and moe.router > 0
     assert "Kohaku-MoE-1B" in ladder.render(rows)
+
+
+def test_plotting_svg_is_well_formed_and_complete(tmp_path):
+    """The dependency-free plotter: stable colours, SI labels, round ticks, and an SVG that parses as XML and holds
+    one shape per data point; a configuration that was not run leaves a gap, not a zero-height bar."""
+    import xml.etree.ElementTree as ET
+
+    from kohakuwullm_b200.bench import plotting as pl
+
+    pal = pl.Palette()
+    assert pal.color("ours") == pal.color("ours") != pal.color("reference")
+    assert [pl.si_format(v) for v in (1536, 2e6, 0.25, 7, 1.4e12)] == ["1.5k", "2M", "0.25", "7", "1.4T"]
+    ticks = pl.nice_ticks(0.0, 181_000.0)
+    assert ticks[0] == 0.0 and ticks[-1] >= 181_000 and len(set(round(b - a, 6) for a, b in zip(ticks, ticks[1:]))) == 1
+    assert pl.log_ticks(1, 8, 2.0) == [1, 2, 4, 8]
+
+    rows = []
+    for impl, scale in (("ours", 180e3), ("reference", 44e3)):
+        for n in (1, 2, 8):
+            if impl == "reference" and n == 8:
+                continue                                            # never run: must not be drawn as a zero
+            rows.append({"impl": impl, "n_gpus": n, "value": scale * n * (0.97 if n > 1 else 1.0), "status": "clean",
+                         "file": f"{impl}_{n}.json", "config": {"model": "Kohaku-500M"}})
+    rows.append({"impl": "ours", "n_gpus": 4, "value": 1.0, "status": "contended", "file": "bad.json"})
+    fig = pl.scaling_figure(rows)
+    root = ET.fromstring(fig.svg())
+    ns = "{http://www.w3.org/2000/svg}"
+    assert len(root.findall(f"{ns}circle")) == 2 * (3 + 2)          # value and efficiency panels, solid lines only
+    assert len(root.findall(f"{ns}polyline")) == 3 * 2              # value + ideal + efficiency per series
+    bars = pl.throughput_figure(rows)
+    root = ET.fromstring(bars.svg())
+    drawn = [r for r in root.iter(f"{ns}rect") if r.find(f"{ns}title") is not None]
+    assert len(drawn) == 5 and all(float(r.get("height")) > 0 for r in drawn)
+    out = pl.save_figure(bars, str(tmp_path / "plots" / "throughput.png"))
+    assert out.endswith("throughput.svg") and os.path.getsize(out) > 500
+
+    # the command line reads result files the way the sweep reader does
+    import json as _json
+    for r in rows:
+        with open(tmp_path / r["file"], "w") as fh:
+            fh.write(_json.dumps({k: v for k, v in r.items() if k not in ("status", "file")}) + "\n")
+    assert pl.main([str(tmp_path), "--scaling", "--out", str(tmp_path / "scaling.svg")]) == 0
+    ET.parse(tmp_path / "scaling.svg")
+    empty = pl.Figure()
+    assert "no data" in empty.svg()

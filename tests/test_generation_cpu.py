@@ -25,6 +25,23 @@ def test_cached_decode_matches_cache_free(wide_model):
     assert len(set(a[0, 5:].tolist())) > 1, "degenerate decode: the comparison proves nothing"
 
 
+def test_preview_sampler_has_its_own_random_stream(wide_model):
+    """Previews draw from the sampler's stream: the training stream is left where it was, two previews in a row do
+    not repeat each other, and a fresh sampler reproduces the first one."""
+    from kohakuwullm_b200.training.loop.sampling import PreviewSampler
+
+    prompt = torch.randint(0, 97, (2, 4))
+    before = torch.get_rng_state()
+    sampler = PreviewSampler(eos_id=96)
+    first = sampler.generate(wide_model, prompt, 10, temperature=1.0)
+    second = sampler.generate(wide_model, prompt, 10, temperature=1.0)
+    assert torch.equal(torch.get_rng_state(), before)
+    assert sampler.backbone is None and wide_model.training
+    assert first.shape == second.shape == (2, 14) and not torch.equal(first, second)
+    again = PreviewSampler(eos_id=96).generate(wide_model, prompt, 10, temperature=1.0)
+    assert torch.equal(first, again)
+
+
 def test_filters():
     logits = torch.tensor([[1.0, 2.0, 3.0, 4.0]])
     assert torch.isinf(filter_top_k(logits, 2)[0, :2]).all() and torch.isfinite(filter_top_k(logits, 2)[0, 2:]).all()
