@@ -35,17 +35,26 @@ E4M3_MAX = 448.0
 
 
 # ------------------------------------------------------------------------------------ reference
-def quantize_reference(x: torch.Tensor):
-    """(M,K) -> (q float8_e4m3fn (M,K), exp uint8 (M,K/32)) with the exponent rule above."""
+SQRT2_MANTISSA = 0x3504F3   # fraction bits of sqrt(2): a float at or above 2^E * sqrt(2) has log2 >= E + 0.5
+
+
+def quantize_reference(x: torch.Tensor, exponent: str = "ceil"):
+    """(M,K) -> (q float8_e4m3fn (M,K), exp uint8 (M,K/32)).
+
+    ``exponent="ceil"`` is the rule above (the kernels' rule: the scaled block never exceeds 448, nothing
+    saturates). ``"nearest"`` rounds ``log2(amax/448)`` to the nearest integer instead: half of the blocks get a
+    scale one binade smaller (finer steps) and their largest elements saturate at 448. It exists for A/B runs of
+    the two conventions (src/kohakuwullm/bench/vendor/mxfp8_rounding.py); no kernel uses it."""
+    if exponent not in ("ceil", "nearest"):
+        raise ValueError(f"unknown exponent rule {exponent!r}")
     M, K = x.shape
     xb = x.float().view(M, K // 32, 32)
     amax = xb.abs().amax(-1).clamp(min=1e-30)
-    exp = torch.ceil(torch.log2(amax / E4M3_MAX)).clamp(min=-127, max=127)
-    # exact ceil(log2) from the float bits (log2 of a float can be off by one ulp near powers of two)
+    # exact from the float bits (log2 of a float can be off by one ulp near powers of two)
     bits = (amax / E4M3_MAX).view(torch.int32)
-    e = ((bits >> 23) & 0xFF) + ((bits & 0x7FFFFF) != 0).to(torch.int32)
-    e = e.clamp(max=254)
-    del exp
+    frac = bits & 0x7FFFFF
+    up = (frac != 0) if exponent == "ceil" else (frac >= SQRT2_MANTISSA)
+    e = (((bits >> 23) & 0xFF) + up.to(torch.int32)).clamp(max=254)
     inv = torch.where(e >= 254, torch.full_like(e, 1), 254 - e)
     inv_scale = (inv << 23).view(torch.float32)
     q = (xb * inv_scale[..., None]).clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn).view(M, K)

@@ -138,3 +138,127 @@ def test_plotting_svg_is_well_formed_and_complete(tmp_path):
     ET.parse(tmp_path / "scaling.svg")
     empty = pl.Figure()
     assert "no data" in empty.svg()
+
+
+def test_mxfp8_exponent_rules_and_emulated_linear():
+    """Round-up never saturates; round-to-nearest picks the same scale or one binade smaller and clips the block's
+    largest elements. The emulated linear under the round-up rule is the MXFP8 reference forward, and its gradients
+    stay close to the unquantised ones."""
+    from kohakuwullm_b200.bench import mxfp8_rounding as rd
+    from kohakuwullm_b200.ops import mxfp8 as mx
+
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(48, 256, generator=g) * torch.logspace(-3, 3, 48)[:, None]
+    q_up, e_up = mx.quantize_reference(x, "ceil")
+    q_nr, e_nr = mx.quantize_reference(x, "nearest")
+    d = e_up.int() - e_nr.int()
+    assert set(d.unique().tolist()) == {0, 1}
+    # round-up: the scaled block maximum is in (224, 448]; the 448 code appears only where the maximum is exact
+    assert float(q_up.float().abs().max()) <= 448.0
+    scaled_max = (x.view(48, 8, 32).abs().amax(-1) / torch.pow(2.0, e_up.float() - 127.0))
+    assert bool(((scaled_max > 224.0 - 1e-3) & (scaled_max <= 448.0)).all())
+    stats = rd.block_statistics(x)
+    assert 0.3 < stats["blocks_with_smaller_scale"] < 0.7
+    assert stats["saturated_share_nearest"] > stats["saturated_share_ceil"]
+    with pytest.raises(ValueError):
+        mx.quantize_reference(x, "floor")
+
+    w = torch.randn(64, 256, generator=g) * 0.05
+    xs = torch.randn(3, 5, 256, generator=g)
+    assert torch.equal(rd.emulated_mxfp8_linear(xs, w, "ceil"), mx.mxfp8_linear_reference(xs, w))
+    for rule in rd.RULES:
+        a, b = xs.clone().requires_grad_(), w.clone().requires_grad_()
+        rd.emulated_mxfp8_linear(a, b, rule).square().sum().backward()
+        a2, b2 = xs.clone().requires_grad_(), w.clone().requires_grad_()
+        (a2 @ b2.t()).square().sum().backward()
+        rel = lambda u, v: float((u - v).norm() / v.norm())
+        bound = 0.08 if rule == "ceil" else 0.2      # clipping the block maxima costs more than a coarser step
+        assert rel(a.grad, a2.grad) < bound and rel(b.grad, b2.grad) < bound, rule
+
+
+def test_mxfp8_emulation_swaps_in_place_and_restores():
+    from kohakuwullm_b200.bench import mxfp8_rounding as rd
+    from kohakuwullm_b200.models import LMBackbone, get_preset
+    from kohakuwullm_b200.models.seqinfo import SeqInfo
+
+    torch.manual_seed(0)
+    cfg = get_preset("B200-smoke", vocab_size=128, dim=64, depth=2, heads=2, kv_heads=2, head_dim=32, mlp_hidden=128,
+                     mxfp8=False)
+    model = LMBackbone(cfg).eval()
+    ids = torch.randint(0, 128, (2, 9))
+    info = SeqInfo.padded(2, 9)
+    with torch.no_grad():
+        plain = model(ids, info)
+        n_all = rd.emulate_mxfp8_(model, "ceil")
+        up = model(ids, info)
+        rd.restore_(model)
+        n_attn = rd.emulate_mxfp8_(model, "nearest", scope=("attn.",))
+        near = model(ids, info)
+        rd.restore_(model)
+        again = model(ids, info)
+    assert n_all > n_attn > 0
+    assert torch.equal(plain, again)
+    assert not torch.equal(plain, up) and not torch.equal(up, near)
+    assert float((up - plain).norm() / plain.norm()) < 0.1
+    args = type("A", (), dict(vocab=64, dim=64, depth=1, lr=2e-3, steps=6, window=3, device="cpu"))()
+    data = rd.chain_data(2, 4, 17, 64, 0)
+    first = rd.train_arm("ceil", 0, args, data)
+    assert first == rd.train_arm("ceil", 0, args, data)            # an arm is a function of its seed
+    assert first != rd.train_arm("nearest", 0, args, data)
+
+
+def test_lost_update_nearest_freezes_where_stochastic_moves(tmp_path):
+    """At a learning rate far below half an ulp per step, round-to-nearest leaves nearly every bf16 weight
+    bit-identical while stochastic rounding moves a visible share; at the peak rate both move."""
+    from kohakuwullm_b200.bench import lost_update as lu
+
+    p = torch.tensor([1.0, 0.5, 3.0], dtype=torch.bfloat16)
+    assert torch.allclose(lu.half_ulp(p), torch.tensor([2.0 ** -8, 2.0 ** -9, 2.0 ** -7]))
+    assert torch.allclose(lu.half_ulp(p.to(torch.float16)), torch.tensor([2.0 ** -11, 2.0 ** -12, 2.0 ** -10]))
+    assert not lu.decay_survives(3e-4, 0.1, torch.bfloat16) and lu.decay_survives(3e-2, 0.5, torch.bfloat16)
+    rc = lu.main(["--steps", "6", "--dim", "64", "--depth", "1", "--vocab", "64", "--rows", "4", "--length", "17",
+                  "--batches", "4", "--lrs", "3e-3", "3e-7", "--arms", "nearest", "stochastic", "--device", "cpu",
+                  "--out", str(tmp_path)])
+    assert rc == 0
+    rows = {(r["arm"], r["lr"]): r for r in json.load(open(tmp_path / "lost_update.json"))}
+    assert rows[("nearest", 3e-7)]["never_moved"] > 0.97
+    assert rows[("stochastic", 3e-7)]["never_moved"] < rows[("nearest", 3e-7)]["never_moved"] - 0.01
+    assert rows[("nearest", 3e-3)]["never_moved"] < 0.2 and rows[("nearest", 3e-3)]["updates_above_half_ulp"] > 0.5
+    assert os.path.getsize(tmp_path / "lost_update.svg") > 500
+
+
+def test_stage_memory_accounts_every_parameter_once():
+    """The per-stage estimate is built on the meta device: stage parameter counts add up to the whole model, the
+    flat fused AdamW costs 12 bytes per parameter (divided by the data-parallel size), the quantised-state optimizers
+    cost what the optimizer itself reports, and a card that is too small is reported as not fitting."""
+    from kohakuwullm_b200.bench import stage_memory as sm
+    from kohakuwullm_b200.models import LMBackbone, get_preset
+
+    kw = dict(vocab_size=1024, dim=256, depth=6, heads=4, kv_heads=2, head_dim=64, mlp_hidden=512)
+    cfg = get_preset("B200-smoke", **kw)
+    with torch.device("meta"):
+        whole = sum(p.numel() for p in LMBackbone(cfg, init=False).parameters())
+    rows = sm.stage_rows("B200-smoke", 3, overrides=kw, optimizer="fused_adamw", mxfp8=True)
+    assert len(rows) == 3 and abs(sum(r["params_m"] for r in rows) * 1e6 - whole) < 1
+    for r in rows:
+        n = r["params_m"] * 1e6
+        assert abs(r["optimizer_gib"] * 2 ** 30 - 12 * n) < 1 and abs(r["grads_gib"] * 2 ** 30 - 4 * n) < 1
+        assert 2 * n <= r["weights_gib"] * 2 ** 30 < 2.1 * n          # bf16 except the few fp32 gains
+        assert r["mxfp8_gib"] > 0 and r["fits"]
+    sharded = sm.stage_rows("B200-smoke", 3, overrides=kw, optimizer="fused_adamw", dp=8)
+    assert abs(sharded[0]["optimizer_gib"] * 8 - rows[0]["optimizer_gib"]) < 1e-6
+    small = sm.stage_rows("B200-smoke", 1, overrides=kw, card_gib=0.001)
+    assert not small[0]["fits"] and small[0]["left_gib"] < 0
+    assert sm.main(["--preset", "B200-smoke", "--set", "depth=2", "--card-gib", "0.0001"]) == 1
+
+    # the state model of the quantised optimizers against the optimizer's own accounting
+    from kohakuwullm_b200.training.optim.quantized_state import QuantizedStateAdamW
+
+    p = torch.nn.Parameter(torch.randn(300, 256))
+    p.grad = torch.randn_like(p)
+    for name, fmt in (("adamw8bit", "int8"), ("adamw4bit", "int4"), ("adamwfp8", "fp8")):
+        opt = QuantizedStateAdamW([p], state_format=fmt)
+        opt.step()
+        assert opt.state_bytes() == sm.optimizer_state_bytes([("w", p)], name), name
+    with pytest.raises(ValueError):
+        sm.optimizer_state_bytes([("w", p)], "lion")
