@@ -66,14 +66,17 @@ def autofill_schedule_steps(schedule: dict | None, total_steps: int, warmup_step
     def _open(v):
         return v is None or v == -1
 
-    if "phases" in out:
-        phases = [dict(p) for p in out["phases"]]
+    key = "phases" if "phases" in out else ("schedules" if out.get("mode") == "composer" and "schedules" in out else None)
+    if key:
+        phases = [dict(p) for p in out[key]]
+        if _open(out.get("end")):
+            out["end"] = total_steps            # what fractional phase ends refer to
         if phases:
-            if warmup_steps is not None and _open(phases[0].get("warmup", 0) if "warmup" in phases[0] else 0) and "warmup" in phases[0]:
+            if warmup_steps is not None and "warmup" in phases[0] and _open(phases[0]["warmup"]):
                 phases[0]["warmup"] = warmup_steps
             if _open(phases[-1].get("end")):
                 phases[-1]["end"] = total_steps
-        out["phases"] = phases
+        out[key] = phases
         return out
     if _open(out.get("end")):
         out["end"] = total_steps

@@ -1,26 +1,55 @@
 """Learning-rate schedules as plain functions of the step (the role AnySchedule plays in the reference).
 
-A spec is ``{"mode": "cosine"|"linear"|"constant"|"wsd", "warmup": n, "end": total, "min_value": f, ...}`` or a
-composition ``{"phases": [spec, ...]}`` where each phase runs until its own ``end``. ``build_schedule``
-returns ``f(step) -> multiplier``; ``LambdaLR``-style use: ``lr = base_lr * f(step)``."""
+A spec is a dict; ``build_schedule(spec)`` returns ``f(step) -> multiplier`` (``lr = base_lr * f(step)``).
+
+Single schedules, ``{"mode": ..., "warmup": n, "end": total, "value": 1.0, "min_value": 0.0, ...}``: the first
+``warmup`` steps ramp linearly up to ``value``, then the mode takes over until ``end`` and holds its last value:
+
+=============  =========================================================================================
+``constant``   ``value``
+``linear``     straight line from ``value`` to ``min_value`` at ``end``
+``cosine``     half cosine from ``value`` to ``min_value`` at ``end``
+``wsd``        ``value`` until ``decay_start``, then a straight line to ``min_value`` at ``end``
+``power``      ``value * (max(step, s0) / s0) ** b``: flat for ``s0`` steps, then a power law (``b = -0.5`` is the
+               inverse-square-root decay); never below ``min_value``
+``exponential`` ``value * 0.5 ** (step / half_life)``, never below ``min_value``
+=============  =========================================================================================
+
+Compositions, ``{"phases": [spec, ...]}`` (``{"mode": "composer", "schedules": [...], "end": total}`` is read the
+same way): phase i runs from the previous phase's ``end`` to its own. A phase's ``end`` is an absolute step, or a
+fraction of the composition's ``end`` when it is a float in (0, 1]. Inside a phase the step counts from the phase's
+start, and the phase's output is multiplied by the value the previous phase ended on, so the curve is continuous
+(a power-law phase followed by a cosine tail starts the tail where the power law stopped).
+"""
 
 from __future__ import annotations
 
 import math
 from typing import Callable
 
+MODES = ("constant", "linear", "cosine", "wsd", "power", "exponential")
+
 
 def _single(spec: dict) -> Callable[[int], float]:
     mode = spec.get("mode", "cosine")
+    if mode not in MODES:
+        raise ValueError(f"unknown schedule mode {mode!r}; known: {', '.join(MODES)}")
     warmup = int(spec.get("warmup", 0) or 0)
     end = int(spec.get("end", 0) or 0)
     lo = float(spec.get("min_value", 0.0))
     hi = float(spec.get("value", 1.0))
     decay_start = int(spec.get("decay_start", end))  # wsd: constant until here, then decay to end
+    s0 = max(float(spec.get("s0", 1.0)), 1.0)
+    b = float(spec.get("b", -0.5))
+    half_life = max(float(spec.get("half_life", 1.0)), 1e-9)
 
     def f(step: int) -> float:
         if warmup and step < warmup:
             return hi * (step + 1) / warmup
+        if mode == "power":
+            return max(lo, hi * (max(float(min(step, end) if end else step), s0) / s0) ** b)
+        if mode == "exponential":
+            return max(lo, hi * 0.5 ** ((min(step, end) if end else step) / half_life))
         if mode == "constant" or end <= warmup:
             return hi
         if mode == "wsd":
@@ -36,22 +65,44 @@ def _single(spec: dict) -> Callable[[int], float]:
     return f
 
 
+def _phase_ends(phases: list[dict], total: int | None) -> list[int]:
+    ends = []
+    for p in phases:
+        e = p.get("end")
+        if isinstance(e, float) and 0.0 < e <= 1.0:
+            if not total or total <= 0:
+                raise ValueError("a fractional phase end needs the composition's own 'end'")
+            e = int(round(e * total))
+        if e is None or int(e) <= (ends[-1] if ends else 0):
+            raise ValueError(f"phase ends must be given and increase, got {[q.get('end') for q in phases]}")
+        ends.append(int(e))
+    return ends
+
+
 def build_schedule(spec: dict | None) -> Callable[[int], float]:
     if not spec:
         return lambda step: 1.0
-    if "phases" in spec:
-        phases = [(int(p["end"]), _single(p)) for p in spec["phases"]]
+    phases = spec.get("phases", spec.get("schedules") if spec.get("mode") == "composer" else None)
+    if phases is None:
+        return _single(spec)
+    phases = [dict(p) for p in phases]
+    if not phases:
+        return lambda step: 1.0
+    total = spec.get("end")
+    ends = _phase_ends(phases, int(total) if isinstance(total, (int, float)) and total and total > 0 else None)
+    starts = [0] + ends[:-1]
+    fns = [_single({**p, "end": e - s}) for p, s, e in zip(phases, starts, ends)]
+    carry = [1.0]                       # value the previous phases ended on
+    for fn, s, e in zip(fns[:-1], starts, ends):
+        carry.append(carry[-1] * fn(e - s))
 
-        def f(step: int) -> float:
-            start = 0
-            for end, fn in phases:
-                if step < end or end == phases[-1][0]:
-                    return fn(step - start) if start else fn(step)
-                start = end
-            return phases[-1][1](step)
+    def f(step: int) -> float:
+        for i, e in enumerate(ends):
+            if step < e or i == len(ends) - 1:
+                return carry[i] * fns[i](step - starts[i])
+        raise AssertionError("unreachable")
 
-        return f
-    return _single(spec)
+    return f
 
 
 class GroupLRSchedule:

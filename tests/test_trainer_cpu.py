@@ -56,6 +56,37 @@ def test_schedules():
     assert f(0) < f(9) <= 1.0 and abs(f(10) - 1.0) < 1e-6 and abs(f(110) - 0.1) < 1e-6
     w = build_schedule({"mode": "wsd", "warmup": 0, "end": 100, "decay_start": 80})
     assert w(50) == 1.0 and w(90) == 0.5
+    p = build_schedule({"mode": "power", "s0": 100, "b": -0.5, "warmup": 10, "end": 10_000, "min_value": 0.05})
+    assert p(50) == 1.0 and abs(p(400) - 0.5) < 1e-9 and abs(p(10_000) - 0.1) < 1e-9 and p(10 ** 9) == p(10_000)
+    e = build_schedule({"mode": "exponential", "half_life": 100, "min_value": 0.2})
+    assert abs(e(100) - 0.5) < 1e-9 and e(1000) == 0.2
+    with pytest.raises(ValueError):
+        build_schedule({"mode": "triangle"})
+
+
+def test_composed_schedules_are_continuous_and_count_from_each_phase_start():
+    from kohakuwullm_b200.utils.misc import autofill_schedule_steps
+
+    # constant, then a cosine that must reach its floor exactly at the composition's end
+    f = build_schedule({"phases": [{"mode": "constant", "end": 100}, {"mode": "cosine", "end": 200, "min_value": 0.1}]})
+    assert f(0) == f(99) == 1.0 and abs(f(100) - 1.0) < 1e-9
+    assert abs(f(150) - 0.55) < 1e-9 and abs(f(200) - 0.1) < 1e-9 and abs(f(5000) - 0.1) < 1e-9
+    # the reference's long-run recipe: warm-up, inverse-square-root decay for 90 % of the run, cosine tail that
+    # starts where the power law stopped (fractional ends refer to the composition's end, left open in the config)
+    spec = {"mode": "composer", "end": -1, "schedules": [
+        {"mode": "power", "end": 0.9, "s0": 2500, "b": -0.5, "warmup": None},
+        {"mode": "cosine", "end": 1.0, "min_value": 0.01}]}
+    g = build_schedule(autofill_schedule_steps(spec, 400_000, 2000))
+    assert abs(g(1999) - 1.0) < 1e-9 and g(2500) == 1.0
+    at_switch = (360_000 / 2500) ** -0.5
+    assert abs(g(359_999) - at_switch) < 1e-4 and abs(g(360_000) - at_switch) < 1e-9
+    assert abs(g(400_000) - 0.01 * at_switch) < 1e-9
+    values = [g(s) for s in range(0, 400_001, 997)]
+    assert all(b <= a + 1e-12 for a, b in zip(values[3:], values[4:]))       # monotone after the warm-up
+    with pytest.raises(ValueError):
+        build_schedule({"phases": [{"mode": "constant", "end": 0.5}, {"mode": "cosine", "end": 1.0}]})   # no total
+    with pytest.raises(ValueError):
+        build_schedule({"phases": [{"mode": "constant", "end": 100}, {"mode": "cosine", "end": 100}]})
 
 
 def test_reporters_write_scalars_perplexity_and_sample_tables(tmp_path, monkeypatch):
