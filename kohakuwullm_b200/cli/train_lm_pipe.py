@@ -113,7 +113,8 @@ def main():
                               callbacks=[LossLog(LOG_INTERVAL, reporter=reporter),
                                          Throughput(LOG_INTERVAL, reporter=reporter)])
     tok = None
-    if DATA != "synthetic" or SOURCES:
+    use_corpus = DATA != "synthetic" or bool(SOURCES)
+    if use_corpus or (SAMPLE_INTERVAL > 0 and SAMPLE_PROMPTS):      # previews need a tokenizer on synthetic packs too
         from kohakuwullm_b200.data import ByteTokenizer
 
         if TOKENIZER == "byte":
@@ -148,7 +149,7 @@ def main():
             yield make_packs(NUM_MICROBATCHES, MICRO_TOKENS, LEN_MIN, LEN_MAX, cfg.vocab_size, seed=SEED + step)
             step += 1
 
-    if tok is None:
+    if not use_corpus:
         batches = stream()
     else:
         # every rank iterates the SAME micro-batched loader (stage 0 uses the tokens, the last stage the labels)

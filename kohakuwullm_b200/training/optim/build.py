@@ -62,18 +62,25 @@ def group_parameters(model: nn.Module, weight_decay: float = 0.1, decay_embeddin
     return groups
 
 
-def muon_groups(model: nn.Module, lr: float, muon_lr: float, weight_decay: float):
-    hidden, rest_decay, rest_plain = [], [], []
+def muon_groups(model: nn.Module, lr: float, muon_lr: float, weight_decay: float, embed_lr: float | None = None):
+    """Hidden matrices for the orthogonalised step; the rest for the internal AdamW in up to three groups: decayed,
+    undecayed, and (with ``embed_lr``) the token-indexed tables (embedding, head) at a rate of their own."""
+    hidden, rest_decay, rest_plain, tables = [], [], [], []
     for name, p in model.named_parameters():
         if not p.requires_grad:
             continue
         if is_hidden_matrix(name, p):
             hidden.append(p)
+        elif embed_lr is not None and p.dim() >= 2 and (is_embedding(name) or "head" in name.split(".")):
+            tables.append(p)
         elif is_decay_param(name, p) and not is_embedding(name):
             rest_decay.append(p)
         else:
             rest_plain.append(p)
-    return hidden, [{"params": rest_decay, "weight_decay": weight_decay}, {"params": rest_plain, "weight_decay": 0.0}]
+    groups = [{"params": rest_decay, "weight_decay": weight_decay}, {"params": rest_plain, "weight_decay": 0.0}]
+    if tables:
+        groups.append({"params": tables, "weight_decay": 0.0, "lr": embed_lr})
+    return hidden, groups
 
 
 OPTIMIZER.register("adamw", lambda groups, **kw: torch.optim.AdamW(groups, foreach=True, **kw))
@@ -92,7 +99,7 @@ def build_optimizer(model: nn.Module, name: str = "fused_adamw", lr: float = 3e-
                     mup_base_dim: int | None = None, muon_lr: float | None = None, **kw):
     if name == "muon":
         muon_lr = muon_lr or 0.02
-        hidden, rest = muon_groups(model, lr, muon_lr, weight_decay)
+        hidden, rest = muon_groups(model, lr, muon_lr, weight_decay, embed_lr)
         return MuonW(hidden, rest, lr=lr, muon_lr=muon_lr, weight_decay=weight_decay, betas=betas, **kw)
     groups = group_parameters(model, weight_decay, decay_embeddings, embed_lr, lr, mup_base_dim)
     if name == "sgd":

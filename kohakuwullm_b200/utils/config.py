@@ -2,7 +2,7 @@
 
 A training script declares its knobs as UPPER_CASE module globals. A config is a Python file whose
 UPPER_CASE globals (or the dict returned by its ``config_gen()``) overwrite the script's same-named
-globals; ``--set KEY=VALUE`` (a Python literal) overwrites one more. Unknown keys are an error, so a typo
+globals (names with a leading underscore are the config's own helpers and are ignored); ``--set KEY=VALUE`` (a Python literal) overwrites one more. Unknown keys are an error, so a typo
 never silently trains the default. Reference: configs/lm/README.md:1-25, docs/guides/writing-configs.md.
 """
 
@@ -16,14 +16,19 @@ from types import ModuleType
 from typing import Any
 
 
+def _is_knob(name: str) -> bool:
+    """UPPER_CASE and not private: a config may keep helpers of its own under a leading underscore."""
+    return name.isupper() and not name.startswith("_")
+
+
 def load_config_file(path: str) -> dict[str, Any]:
     ns = runpy.run_path(path)
     if callable(ns.get("config_gen")):
         out = ns["config_gen"]()
         if not isinstance(out, dict):
             raise TypeError(f"{path}: config_gen() must return a dict")
-        return {k: v for k, v in out.items() if k.isupper()}
-    return {k: v for k, v in ns.items() if k.isupper()}
+        return {k: v for k, v in out.items() if _is_knob(k)}
+    return {k: v for k, v in ns.items() if _is_knob(k)}
 
 
 def parse_value(text: str) -> Any:

@@ -223,3 +223,20 @@ def test_quantized_state_adamw_tracks_fp32_adamw(name, rel):
         block = 128 if fmt == "int4" else 256
         back = dequantize_blocks(quantize_blocks(x, fmt, block, True), fmt, block, True, x.shape)
         assert float((back - x).norm() / x.norm()) < tol, fmt
+
+
+def test_muon_embed_lr_puts_the_token_tables_in_their_own_group():
+    from kohakuwullm_b200.models import LMBackbone, get_preset
+    from kohakuwullm_b200.training.optim.build import build_optimizer
+
+    cfg = get_preset("B200-smoke", vocab_size=64, dim=64, depth=1, heads=2, kv_heads=2, head_dim=32, mlp_hidden=128)
+    model = LMBackbone(cfg)
+    names = {id(p): n for n, p in model.named_parameters()}
+    opt = build_optimizer(model, "muon", lr=5e-4, muon_lr=2e-3, embed_lr=1e-3)
+    tables = [g for g in opt.param_groups if not g["use_muon"] and g["lr"] == 1e-3]
+    assert len(tables) == 1 and sorted(names[id(p)] for p in tables[0]["params"]) == ["embed.weight", "head.proj.weight"]
+    assert tables[0]["weight_decay"] == 0.0
+    seen = [id(p) for g in opt.param_groups for p in g["params"]]
+    assert len(seen) == len(set(seen)) == len(list(model.parameters()))       # every parameter in exactly one group
+    plain = build_optimizer(model, "muon", lr=5e-4, muon_lr=2e-3)
+    assert all(g["lr"] in (5e-4, 2e-3) for g in plain.param_groups)

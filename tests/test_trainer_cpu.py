@@ -187,3 +187,48 @@ def test_train_lm_cli_with_a_mixture_validation_sampling_and_weight_only_load(tm
     b = torch.cat([p.detach().reshape(-1) for p in second.backbone.parameters()])
     assert float((a - b).abs().max()) < 0.1              # one small step away from the loaded weights, not a fresh init
     assert len({g["lr"] for g in second.engine.optimizer.param_groups}) > 1      # muP groups
+
+
+def test_every_shipped_config_names_only_knobs_of_its_entry_point(monkeypatch):
+    """A config is applied with unknown keys refused, so loading each shipped file against the entry point its
+    docstring names proves that no recipe carries a stale or misspelt knob; model presets must exist, schedules must
+    build, source and renderer specs must name registered kinds."""
+    import glob
+    import importlib
+
+    from kohakuwullm_b200.models import get_preset
+    from kohakuwullm_b200.registry import DATASET, RENDERER
+    from kohakuwullm_b200.utils.config import apply_overrides, load_config_file
+    from kohakuwullm_b200.utils.misc import autofill_schedule_steps
+
+    import kohakuwullm_b200.data  # noqa: F401  (registrations)
+
+    monkeypatch.setenv("KWU_SWEEP", "12288x21_mxfp8_ckpt")
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "configs", "lm")
+    files = [f for f in sorted(glob.glob(os.path.join(root, "**", "*.py"), recursive=True))
+             if not os.path.basename(f).startswith("_")]
+    assert len(files) >= 15
+    for path in files:
+        text = open(path).read()
+        entry = "train_lm_pipe" if "cli.train_lm_pipe" in text else "train_lm"
+        module = importlib.import_module(f"kohakuwullm_b200.cli.{entry}")
+        knobs = {k: v for k, v in vars(module).items() if k.isupper()}
+        apply_overrides(knobs, load_config_file(path), path)          # raises on an unknown knob
+        get_preset(knobs["PRESET"], **knobs["ARCH_OVERRIDES"])
+        if knobs.get("LR_SCHEDULE"):
+            f = build_schedule(autofill_schedule_steps(dict(knobs["LR_SCHEDULE"]), knobs["MAX_STEPS"], knobs["WARMUP_STEPS"]))
+            assert 0.0 < f(knobs["MAX_STEPS"] - 1) <= 1.0 and f(knobs["WARMUP_STEPS"]) > 0.5, path
+        for src in knobs.get("SOURCES") or []:
+            assert src["records"]["name"] in DATASET and src["repeat"] > 0, path
+        r = knobs.get("RENDERER")
+        names = [r] if isinstance(r, str) else [r["name"], *r.get("renderers", {}).values()]
+        assert all(n in RENDERER for n in names), path
+        if knobs.get("SCHEDULE"):
+            from kohakuwullm_b200.pipe.schedules import SCHEDULES
+            assert knobs["SCHEDULE"] in SCHEDULES, path
+    sweep = load_config_file(os.path.join(root, "sweep", "microbatch.py"))
+    assert (sweep["MICRO_TOKENS"], sweep["NUM_MICROBATCHES"]) == (12288, 21)
+    assert sweep["ARCH_OVERRIDES"]["mxfp8"] and sweep["ARCH_OVERRIDES"]["grad_ckpt"] and sweep["SCHEDULE"] == "1f1b"
+    monkeypatch.setenv("KWU_SWEEP", "8192x32_fp7")
+    with pytest.raises(ValueError):
+        load_config_file(os.path.join(root, "sweep", "microbatch.py"))
