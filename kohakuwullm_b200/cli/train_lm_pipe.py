@@ -42,6 +42,13 @@ SAMPLE_PROMPTS: list = []                   # [(name, prompt), ...]
 SAMPLE_TOKENS = 64
 SAMPLE_TEMPERATURE = 0.35
 SAMPLE_TOP_P = 0.95
+SAMPLE_TOP_K = 0
+SAMPLE_MIN_P = 0.0
+SAMPLE_COUNT = 4                            # completions per prompt
+SAMPLE_FROM_BATCH = 0                       # > 0: also continue that many documents cut out of the batch just trained on
+SAMPLE_PREFIX_TOKENS = 768                  # longest prefix kept of such a document
+SAMPLE_TURNS_ONLY = True                    # cut chat documents at a turn boundary (the assistant answers)
+SAMPLE_LOCAL = True                         # True: gather the weights and decode on rank 0; False: pipelined decode
 OPTIMIZER = "fused_adamw"      # or muon, adamw16, stochastic_adamw, adamw8bit, adamw4bit, adamwfp8, adamw, adam, sgd
 OPTIMIZER_KWARGS: dict = {}
 LR = 3e-4
@@ -114,7 +121,7 @@ def main():
                                          Throughput(LOG_INTERVAL, reporter=reporter)])
     tok = None
     use_corpus = DATA != "synthetic" or bool(SOURCES)
-    if use_corpus or (SAMPLE_INTERVAL > 0 and SAMPLE_PROMPTS):      # previews need a tokenizer on synthetic packs too
+    if use_corpus or (SAMPLE_INTERVAL > 0 and (SAMPLE_PROMPTS or SAMPLE_FROM_BATCH)):      # previews need a tokenizer on synthetic packs too
         from kohakuwullm_b200.data import ByteTokenizer
 
         if TOKENIZER == "byte":
@@ -127,12 +134,14 @@ def main():
         from kohakuwullm_b200.training.parallel.uwupipe_callbacks import RouterBiasSchedule
 
         trainer.loop.callbacks.callbacks.append(RouterBiasSchedule(module, dict(BIAS_SCHEDULE)))
-    if SAMPLE_INTERVAL > 0 and SAMPLE_PROMPTS and tok is not None:
+    if SAMPLE_INTERVAL > 0 and (SAMPLE_PROMPTS or SAMPLE_FROM_BATCH) and tok is not None:
         from kohakuwullm_b200.training.parallel.uwupipe_callbacks import SamplePreview
 
         trainer.loop.callbacks.callbacks.append(SamplePreview(
             module, tok, [tuple(p) for p in SAMPLE_PROMPTS], every_n_steps=SAMPLE_INTERVAL, max_new_tokens=SAMPLE_TOKENS,
-            temperature=SAMPLE_TEMPERATURE, top_p=SAMPLE_TOP_P, report=getattr(reporter, "samples", None)))
+            temperature=SAMPLE_TEMPERATURE, top_p=SAMPLE_TOP_P, top_k=SAMPLE_TOP_K, min_p=SAMPLE_MIN_P,
+            samples=SAMPLE_COUNT, from_batch=SAMPLE_FROM_BATCH, prefix_tokens=SAMPLE_PREFIX_TOKENS,
+            turns_only=SAMPLE_TURNS_ONLY, local=SAMPLE_LOCAL, report=getattr(reporter, "samples", None)))
     if CKPT_DIR:
         trainer.loop.callbacks.callbacks.append(Checkpoint(trainer, CKPT_DIR, every=CKPT_EVERY))
     if RESUME:

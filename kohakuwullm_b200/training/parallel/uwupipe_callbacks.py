@@ -9,7 +9,7 @@ the restored step.
 on rank 0. It is collective: by default the stages' weights are gathered under whole-model names, rank 0
 rebuilds the full model and decodes locally (one gather per preview, no per-token pipeline traffic); with
 ``local=False`` every rank drives a pipelined forward-only decode instead. Prompts are fixed
-``(name, text)`` pairs or documents cut out of the batch that was just trained on.
+``(name, text)`` pairs and, with ``from_batch``, documents cut out of the batch that was just trained on.
 Reference behaviour: src/kohakuwullm/training/parallel/uwupipe_callbacks.py:32-337.
 """
 
@@ -136,8 +136,9 @@ class SamplePreview(Callback):
     def preview(self, step: int, batch=None, silent: bool = False):
         named = [(n, self._encode(t)) for n, t in self.prompts]
         if self.from_batch and batch is not None:
-            named = prompts_from_batch(batch, self.from_batch, seed=step, prefix_frac=self.prefix_frac,
-                                       prefix_tokens=self.prefix_tokens, turns_only=self.turns_only) or named
+            # the fixed prompts stay comparable from preview to preview; the batch prompts show the current data
+            named = named + prompts_from_batch(batch, self.from_batch, seed=step, prefix_frac=self.prefix_frac,
+                                               prefix_tokens=self.prefix_tokens, turns_only=self.turns_only)
         if not named:
             return []
         if self.local:
