@@ -44,6 +44,7 @@ LEN_MIN, LEN_MAX = 64, 4096
 OPTIMIZER = "fused_adamw"      # or muon, adamw16, stochastic_adamw, adamw8bit, adamw4bit, adamwfp8, adamw, adam, sgd
 OPTIMIZER_KWARGS: dict = {}     # e.g. {"muon_lr": 0.02}
 GRAD_SYNC = "auto"             # fused (reduce-scatter + AdamW + all-gather over peer memory) with fused_adamw on GPUs, else nccl
+GRAD_COMPRESS = ""             # "bf16" / "fp16": NCCL gradient buckets cross the wire in that dtype (nccl sync only)
 EXPERT_PARALLEL = False        # split the experts of every MoE layer over the ranks (the rest stays data parallel)
 EP_CAPACITY = 2.0
 EP_ON_OVERFLOW = "raise"       # or "count": drop pairs that find no room and report ep_dropped_pairs
@@ -104,7 +105,7 @@ def main():
                         log_interval=LOG_INTERVAL, seed=SEED, optimizer=("adamw" if USE_MUP and OPTIMIZER == "fused_adamw" else OPTIMIZER),
                         optimizer_kwargs=opt_kwargs,
                         grad_sync=GRAD_SYNC, expert_parallel=EXPERT_PARALLEL, ep_capacity_factor=EP_CAPACITY,
-                        ep_on_overflow=EP_ON_OVERFLOW)
+                        ep_on_overflow=EP_ON_OVERFLOW, grad_compress=GRAD_COMPRESS or None)
     tok, val_loader = None, None
     if DATA == "synthetic" and not SOURCES:
         loader = _synthetic_stream(trainer.config.vocab_size, rank)

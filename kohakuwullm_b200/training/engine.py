@@ -129,8 +129,11 @@ class TrainEngine:
                  cuda_graphs: bool | None = None, graph_max_docs: int | None = None,
                  graph_token_bucket: int = 512, graph_cache_size: int = 8,
                  expert_parallel: bool | str = False, ep_capacity_factor: float = 2.0,
-                 ep_on_overflow: str = "raise", optimizer: str = "fused_adamw", optimizer_kwargs: dict | None = None):
-        """``expert_parallel``: split every MoE layer's experts over the ranks of ``group`` (tokens travel
+                 ep_on_overflow: str = "raise", optimizer: str = "fused_adamw", optimizer_kwargs: dict | None = None,
+                 grad_compress: str | None = None):
+        """``grad_compress``: ``"bf16"`` / ``"fp16"`` sends the NCCL gradient buckets in that dtype (ignored by the
+        fused peer-memory step, which reduces fp32).
+        ``expert_parallel``: split every MoE layer's experts over the ranks of ``group`` (tokens travel
         to the owning rank over peer memory); all other parameters stay data-parallel replicas.
         ``"reference"`` keeps the sharding but moves tokens with plain collectives (test oracle).
         ``graph_token_bucket``: captured micro-step graphs hold a multiple of this many tokens; a micro-batch
@@ -170,7 +173,7 @@ class TrainEngine:
             shard = (self.rank, self.world)
         else:
             self.flat = FlatParameters(model)
-            self.sync = GradSync(self.flat, group)
+            self.sync = GradSync(self.flat, group, compress=grad_compress)
             shard = None
         if self.generic_optimizer:
             from kohakuwullm_b200.training.optim.build import build_optimizer

@@ -40,7 +40,7 @@ class LMTrainer:
                  device=None, group=None, grad_sync: str = "auto", callbacks=(), log_interval: int = 10,
                  ema: float = 0.98, seed: int = 1234, head_kwargs: dict | None = None,
                  optimizer: str = "fused_adamw", optimizer_kwargs: dict | None = None, expert_parallel: bool = False,
-                 ep_capacity_factor: float = 2.0, ep_on_overflow: str = "raise"):
+                 ep_capacity_factor: float = 2.0, ep_on_overflow: str = "raise", grad_compress: str | None = None):
         self.rank = dist.get_rank(group) if dist.is_available() and dist.is_initialized() else 0
         self.world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
         self.group = group
@@ -59,7 +59,8 @@ class LMTrainer:
                                   param_dtype=dtype, group=group, grad_sync=grad_sync,
                                   lr_schedule=(lambda step: lr * sched(step)), optimizer=optimizer,
                                   optimizer_kwargs=optimizer_kwargs, expert_parallel=expert_parallel,
-                                  ep_capacity_factor=ep_capacity_factor, ep_on_overflow=ep_on_overflow)
+                                  ep_capacity_factor=ep_capacity_factor, ep_on_overflow=ep_on_overflow,
+                                  grad_compress=grad_compress)
         self.flops = FlopCounter(self.backbone)
         self.grad_accum, self.log_interval, self.ema_beta = grad_accum, log_interval, ema
         self.callbacks = CallbackList(callbacks)

@@ -55,12 +55,12 @@ def test_all_masked_step_changes_nothing():
     assert eng.optimizer.step_count == 0
 
 
-def _ddp_worker(rank, world, port, path):
+def _ddp_worker(rank, world, port, path, compress=None):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     docs = _docs(8)
     mine = docs[rank::world]
-    eng = TrainEngine(_model(), lr=1e-2, max_grad_norm=1.0)
+    eng = TrainEngine(_model(), lr=1e-2, max_grad_norm=1.0, grad_compress=compress)
     out = eng.step([collate_packed(mine)])
     flat = torch.cat([p.detach().reshape(-1) for p in eng.model.parameters()])
     if rank == 0:
@@ -83,6 +83,26 @@ def test_world_two_matches_world_one():
     assert abs(got["loss"] - float(out["loss"])) < 1e-5
     assert abs(got["norm"] - float(out["grad_norm"])) < 1e-4
     torch.testing.assert_close(got["flat"], flat, rtol=0, atol=3e-4)
+
+
+@pytest.mark.timeout(300)
+@pytest.mark.parametrize("compress", ["bf16", "fp16"])
+def test_compressed_gradient_buckets_stay_close_to_the_exact_sum(compress):
+    """Gradient buckets sent in a 16-bit dtype: the loss is untouched (it is reduced separately), the gradient norm
+    agrees to the wire format's precision, and the result is still a SUM (the fp16 pre-division is undone)."""
+    from tests.helpers import free_port
+
+    with tempfile.TemporaryDirectory() as tmp:
+        path = os.path.join(tmp, "r0.pt")
+        mp.spawn(_ddp_worker, args=(2, free_port(), path, compress), nprocs=2, join=True)
+        got = torch.load(path)
+    eng = TrainEngine(_model(), lr=1e-2, max_grad_norm=1.0)
+    out = eng.step([collate_packed(_docs(8))])
+    assert abs(got["loss"] - float(out["loss"])) < 1e-5
+    rel = abs(got["norm"] - float(out["grad_norm"])) / float(out["grad_norm"])
+    assert rel < (1e-2 if compress == "bf16" else 2e-3), rel
+    with pytest.raises(ValueError):
+        TrainEngine(_model(), grad_compress="int3")
 
 
 def test_smoke_config_trains():
