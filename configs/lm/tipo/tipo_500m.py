@@ -30,6 +30,7 @@ GPUS = 8
 OPTIMIZER = "muon"
 OPTIMIZER_KWARGS = {"muon_lr": 0.02}
 GRAD_SYNC = "nccl"              # the fused peer-memory step shards the flat AdamW only
+GRAD_COMPRESS = "bf16"          # gradient buckets cross NVLink in bf16
 LR = 3e-4
 BETAS = (0.9, 0.95)
 WEIGHT_DECAY = 0.1

@@ -10,6 +10,7 @@ Given AFTER ``tipo_500m.py`` it overrides only the optimizer section.
 OPTIMIZER = "fused_adamw"
 OPTIMIZER_KWARGS = {}
 GRAD_SYNC = "auto"
+GRAD_COMPRESS = ""
 LR = 6e-4
 RUN_NAME = "tipo-500m-adamw"
 CKPT_DIR = "out/ckpt/tipo-500m-adamw"
