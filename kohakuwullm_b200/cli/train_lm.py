@@ -53,6 +53,7 @@ WEIGHT_DECAY = 0.1
 BETAS = (0.9, 0.95)
 MAX_GRAD_NORM = 1.0
 WARMUP_STEPS = 100
+WARMUP_RATIO = 0.0              # > 0: the warm-up is this share of MAX_STEPS (overrides WARMUP_STEPS)
 MAX_STEPS = 1000
 LR_SCHEDULE = {"mode": "cosine", "warmup": None, "end": None, "min_value": 0.1}
 LOG_INTERVAL = 10
@@ -93,7 +94,8 @@ def main():
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl" if use_cuda else "gloo", **({"device_id": device} if use_cuda else {}))
-    sched = autofill_schedule_steps(dict(LR_SCHEDULE), MAX_STEPS, WARMUP_STEPS)
+    warmup = max(1, round(WARMUP_RATIO * MAX_STEPS)) if WARMUP_RATIO > 0 else WARMUP_STEPS
+    sched = autofill_schedule_steps(dict(LR_SCHEDULE), MAX_STEPS, warmup)
     arch = dict(ARCH_OVERRIDES)
     if GRAD_CKPT:
         arch["grad_ckpt"] = True

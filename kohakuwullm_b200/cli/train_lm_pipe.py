@@ -31,6 +31,8 @@ TOKENIZER = "byte"          # "byte" or a Hugging Face tokenizer path
 CTX_MAX = 4096
 LR_SCHEDULE: dict = {"mode": "cosine", "warmup": None, "end": None, "min_value": 0.1}
 WARMUP_STEPS = 100
+WARMUP_RATIO = 0.0                          # > 0: the warm-up is this share of MAX_STEPS (overrides WARMUP_STEPS)
+PARAM_DTYPE = "bf16"                        # "bf16" (the native kernels), "fp32", or "fp16" (PyTorch paths + loss scaler)
 AUX_LOSS_WEIGHT: float | None = None        # overrides the preset's router auxiliary-loss weight
 ROUTER_Z_LOSS_WEIGHT: float | None = None
 BIAS_SCHEDULE: dict | None = None           # schedule of the routers' bias update rate, e.g. {"mode": "linear", "end": 2000}
@@ -107,11 +109,16 @@ def main():
                               directory=CKPT_DIR or None) if ranks.rank == 0 else None
     from kohakuwullm_b200.utils.misc import autofill_schedule_steps
 
-    sched = autofill_schedule_steps(dict(LR_SCHEDULE), MAX_STEPS, WARMUP_STEPS) if LR_SCHEDULE else None
+    warmup = max(1, round(WARMUP_RATIO * MAX_STEPS)) if WARMUP_RATIO > 0 else WARMUP_STEPS
+    sched = autofill_schedule_steps(dict(LR_SCHEDULE), MAX_STEPS, warmup) if LR_SCHEDULE else None
+    dtypes = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": None}
+    if PARAM_DTYPE not in dtypes:
+        raise ValueError(f"PARAM_DTYPE must be one of {sorted(dtypes)}, not {PARAM_DTYPE!r}")
     module = LMPipelineModule(cfg, micro_tokens=MICRO_TOKENS, lr=LR, weight_decay=WEIGHT_DECAY, seed=SEED,
-                              optimizer=OPTIMIZER, optimizer_kwargs=dict(OPTIMIZER_KWARGS), lr_schedule=sched)
+                              param_dtype=dtypes[PARAM_DTYPE], optimizer=OPTIMIZER,
+                              optimizer_kwargs=dict(OPTIMIZER_KWARGS), lr_schedule=sched)
     scaler = None
-    if GRAD_SCALER == "on":
+    if GRAD_SCALER == "on" or (GRAD_SCALER == "auto" and PARAM_DTYPE == "fp16" and ranks.device.type == "cuda"):
         from kohakuwullm_b200.pipe.scaler import PipelineGradScaler
 
         scaler = PipelineGradScaler(init_scale=GRAD_SCALER_INIT)
