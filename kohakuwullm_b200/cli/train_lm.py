@@ -37,6 +37,10 @@ SAMPLE_TOP_P = 0.95
 SAMPLE_TOP_K = 0
 SAMPLE_MIN_P = 0.0
 TOKENIZER = "byte"              # "byte" or a Hugging Face tokenizer path
+BATCH_LAYOUT = "packed"         # "padded": one row per document (SAMPLES_PER_BATCH rows cut to CTX_MAX), eager launches and
+                                # explicit-mask attention; same loss per token, for ablations and readable debugging
+SAMPLES_PER_BATCH = 8
+PAD_TOKEN_ID = 0
 BATCH_TOKENS = 16384            # tokens per rank per optimizer step
 GRAD_ACCUM = 4
 CTX_MAX = 4096
@@ -131,7 +135,23 @@ def main():
             held_out = SplitRecords(records, VAL_FRACTION, "val", SEED)
             records = SplitRecords(records, VAL_FRACTION, "train", SEED)
             val_loader = lambda: build_loader("ddp", held_out, renderer, encode, rank=rank, world=world, **common)  # noqa: E731
-        if NUM_WORKERS > 0:
+        if BATCH_LAYOUT not in ("packed", "padded"):
+            raise ValueError(f"BATCH_LAYOUT must be 'packed' or 'padded', not {BATCH_LAYOUT!r}")
+        if BATCH_LAYOUT == "padded":
+            # whole documents, one per row; every rank reads its own stride of the records, epoch after epoch
+            mine = [i for i in range(len(records)) if i % world == rank]
+            view = type("RankShard", (), {"__len__": lambda self: len(mine),
+                                          "__getitem__": lambda self, i: records[mine[i]]})()
+            per_epoch = build_loader("map", view, renderer, encode, layout="padded", samples_per_batch=SAMPLES_PER_BATCH,
+                                     ctx_max=CTX_MAX, pad_id=PAD_TOKEN_ID, seed=SEED + rank, num_workers=NUM_WORKERS,
+                                     bos=common["bos"], eos=common["eos"])
+
+            def _epochs():
+                while True:
+                    yield from per_epoch
+
+            loader = _epochs()
+        elif NUM_WORKERS > 0:
             loader = build_loader("workers", records, renderer, encode, rank=rank, world=world, workers=NUM_WORKERS, **common)
         else:
             loader = build_loader("ddp", records, renderer, encode, rank=rank, world=world, **common)

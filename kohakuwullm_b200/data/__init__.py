@@ -41,7 +41,8 @@ def build_dataset(records_spec: Any, renderer_spec: Any = "plain"):
 def build_loader(kind: str, records, renderer, encode: Callable, *, rank: int = 0, world: int = 1,
                  worker: int = 0, workers: int = 1, **kw):
     """``iterative`` one shard; ``ddp`` one shard per (rank, worker); ``pipeline`` identical exact-k
-    micro-batched steps on every rank; ``torch`` / ``map`` map-style loaders of whole documents."""
+    micro-batched steps on every rank; ``torch`` / ``map`` map-style loaders of whole documents, ``samples_per_batch``
+    per batch, ``layout="packed"`` (one row) or ``"padded"`` (one row per document)."""
     if kind == "iterative":
         return ResumableLoader(IterativePackLoader(records, renderer, encode, **kw))
     if kind == "ddp":
@@ -65,6 +66,15 @@ def build_loader(kind: str, records, renderer, encode: Callable, *, rank: int = 
 
         bos, eos = kw.pop("bos", None), kw.pop("eos", None)
         samples = kw.pop("samples_per_batch", 8)
+        layout, ctx_max, pad_id = kw.pop("layout", "packed"), kw.pop("ctx_max", None), kw.pop("pad_id", 0)
+        if layout not in ("packed", "padded"):
+            raise ValueError(f"layout must be 'packed' or 'padded', not {layout!r}")
+
+        def collate(rows):
+            if layout == "padded":
+                return collate_padded(rows, pad_id=pad_id, pad_to_multiple=8, max_length=ctx_max)
+            return collate_packed([(i[:ctx_max], None if m is None else m[:ctx_max]) if ctx_max else (i, m)
+                                   for i, m in rows])
 
         class _Docs(Dataset):
             def __len__(self):
@@ -73,7 +83,7 @@ def build_loader(kind: str, records, renderer, encode: Callable, *, rank: int = 
             def __getitem__(self, i):
                 return tokenize_segments(renderer(records[i], None), encode, bos, eos)
 
-        return DataLoader(_Docs(), batch_size=samples, shuffle=kw.pop("shuffle", True), collate_fn=collate_packed,
+        return DataLoader(_Docs(), batch_size=samples, shuffle=kw.pop("shuffle", True), collate_fn=collate,
                           num_workers=kw.pop("num_workers", 0), generator=torch.Generator().manual_seed(kw.pop("seed", 0)))
     raise KeyError(f"unknown loader kind {kind!r}; choose from iterative, ddp, workers, pipeline, torch, map")
 

@@ -1,4 +1,6 @@
-"""Padded (B,S) batches: the layout used by evaluation and by the KV-cache generation path.
+"""Padded (B,S) batches: the layout used by evaluation and by the KV-cache generation path; the training engine
+takes them as well (eager launches, explicit-mask attention: for ablations and readable debugging, the loss per token
+is the same as for the packed layout).
 Reference: src/kohakuwullm/data/loader/padded.py:14-102."""
 
 from __future__ import annotations
@@ -18,17 +20,30 @@ class PaddedBatch:
     lengths: torch.Tensor     # (B,)
     seq_info: SeqInfo
 
+    @property
+    def num_tokens(self) -> int:
+        return int(self.tokens.numel())
+
+    def trained_tokens(self) -> int:
+        """Positions with a target (padding and masked spans carry -100)."""
+        return int((self.labels != IGNORE).sum())
+
     def to(self, device, non_blocking=True):
         return PaddedBatch(self.tokens.to(device, non_blocking=non_blocking),
                            self.labels.to(device, non_blocking=non_blocking),
                            self.lengths.to(device, non_blocking=non_blocking), self.seq_info.to(device, non_blocking))
 
 
-def collate_padded(samples, pad_id: int = 0, pad_to_multiple: int | None = None) -> PaddedBatch:
+def collate_padded(samples, pad_id: int = 0, pad_to_multiple: int | None = None,
+                   max_length: int | None = None) -> PaddedBatch:
+    """Rows are documents (``ids`` or ``(ids, trained_mask)``), cut to ``max_length`` tokens, padded on the right."""
     docs = []
     for s in samples:
         ids, mask = s if isinstance(s, tuple) else (s, None)
         ids = torch.as_tensor(ids, dtype=torch.long)
+        if max_length and ids.numel() > max_length:
+            ids = ids[:max_length]
+            mask = None if mask is None else torch.as_tensor(mask)[:max_length]
         if ids.numel() > 1:
             docs.append((ids, shift_labels(ids, None if mask is None else torch.as_tensor(mask, dtype=torch.bool))))
     if not docs:

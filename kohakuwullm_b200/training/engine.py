@@ -211,8 +211,8 @@ class TrainEngine:
 
     def _graph_for(self, mb: PackedBatch) -> GraphedMicroStep | None:
         """Graph matching this micro-batch's token count (captured on first use), or None."""
-        if not self.cuda_graphs:
-            return None
+        if not self.cuda_graphs or not getattr(mb.seq_info, "packed", True):
+            return None        # padded (rows, S) batches run eagerly
         b = self.graph_token_bucket
         T = (mb.num_tokens + b - 1) // b * b
         max_docs = self.graph_max_docs or max(8, T // 32)

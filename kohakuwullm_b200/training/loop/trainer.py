@@ -83,9 +83,15 @@ class LMTrainer:
 
     # ------------------------------------------------------------------ step
     def training_step(self, batch: PackedBatch) -> dict:
-        micro = split_packed(batch, self.grad_accum) if self.grad_accum > 1 else [batch]
+        if batch.seq_info.packed:
+            micro = split_packed(batch, self.grad_accum) if self.grad_accum > 1 else [batch]
+            lengths = batch.seq_info.lengths or tuple(batch.seq_info.seqlens.tolist())
+        else:       # padded rows: split along the batch axis; FLOPs count the documents' own lengths, not the padding
+            from kohakuwullm_b200.data.loader.padded import split_padded
+
+            micro = split_padded(batch, self.grad_accum) if self.grad_accum > 1 else [batch]
+            lengths = tuple(int(n) for n in batch.lengths.tolist())
         out = self.engine.step(micro)
-        lengths = batch.seq_info.lengths or tuple(batch.seq_info.seqlens.tolist())
         mf, hf = self.flops.step_flops(lengths)
         self._local = self._local + TokenSnapshot(batch.num_tokens, batch.trained_tokens(), mf, hf, 0.0)
         return out

@@ -187,6 +187,40 @@ def test_train_lm_cli_with_a_mixture_validation_sampling_and_weight_only_load(tm
     b = torch.cat([p.detach().reshape(-1) for p in second.backbone.parameters()])
     assert float((a - b).abs().max()) < 0.1              # one small step away from the loaded weights, not a fresh init
     assert len({g["lr"] for g in second.engine.optimizer.param_groups}) > 1      # muP groups
+    # the padded layout: one row per document, same entry point, loss finite and falling into the same range
+    mod = importlib.reload(mod)
+    configure(mod, common + ["--set", "MAX_STEPS=3", "--set", "BATCH_LAYOUT='padded'", "--set", "SAMPLES_PER_BATCH=4",
+                             "--set", "WARMUP_RATIO=0.34", "--set", "VAL_FRACTION=0.0", "--set", "SAMPLE_INTERVAL=0"])
+    third = mod.main()
+    assert third.global_step == 3 and third.loss_ema is not None and 3.0 < third.loss_ema < 7.0
+
+
+def test_padded_and_packed_layouts_give_the_same_step():
+    """The same documents as one packed row, as one padded batch and as a padded batch split into micro-batches:
+    identical loss, gradient norm, token count and (up to summation order) parameters after the step."""
+    from kohakuwullm_b200.data.loader.padded import collate_padded, split_padded
+    from kohakuwullm_b200.data.packing import collate_packed
+    from kohakuwullm_b200.models import LMBackbone, get_preset
+    from kohakuwullm_b200.training.engine import TrainEngine
+
+    def model():
+        torch.manual_seed(0)
+        return LMBackbone(get_preset("B200-smoke", vocab_size=300, dim=64, depth=2, heads=2, kv_heads=1, head_dim=32,
+                                     mlp_hidden=128, sliding_window=8, global_layer_every=2, attn_sink=True))
+
+    g = torch.Generator().manual_seed(3)
+    docs = [torch.randint(0, 300, (int(torch.randint(5, 40, (1,), generator=g)),), generator=g) for _ in range(6)]
+    results = []
+    for batches in ([collate_packed(docs)], [collate_padded(docs)], split_padded(collate_padded(docs, pad_to_multiple=8), 3)):
+        eng = TrainEngine(model(), lr=1e-2, max_grad_norm=1.0)
+        out = eng.step(batches)
+        flat = torch.cat([p.detach().reshape(-1) for p in eng.model.parameters()])
+        results.append((float(out["loss"]), float(out["grad_norm"]), float(out["tokens"]), flat))
+    for loss, norm, tokens, flat in results[1:]:
+        assert abs(loss - results[0][0]) < 1e-5 and abs(norm - results[0][1]) < 1e-4 and tokens == results[0][2]
+        torch.testing.assert_close(flat, results[0][3], rtol=0, atol=3e-4)
+    cut = collate_padded(docs, max_length=16)
+    assert cut.tokens.shape[1] == 16 and int(cut.lengths.max()) == 16
 
 
 def test_every_shipped_config_names_only_knobs_of_its_entry_point(monkeypatch):
