@@ -55,6 +55,7 @@ EP_ON_OVERFLOW = "raise"       # or "count": drop pairs that find no room and re
 LR = 3e-4
 WEIGHT_DECAY = 0.1
 BETAS = (0.9, 0.95)
+EPS = 1e-8
 MAX_GRAD_NORM = 1.0
 WARMUP_STEPS = 100
 WARMUP_RATIO = 0.0              # > 0: the warm-up is this share of MAX_STEPS (overrides WARMUP_STEPS)
@@ -111,7 +112,7 @@ def main():
                         log_interval=LOG_INTERVAL, seed=SEED, optimizer=("adamw" if USE_MUP and OPTIMIZER == "fused_adamw" else OPTIMIZER),
                         optimizer_kwargs=opt_kwargs,
                         grad_sync=GRAD_SYNC, expert_parallel=EXPERT_PARALLEL, ep_capacity_factor=EP_CAPACITY,
-                        ep_on_overflow=EP_ON_OVERFLOW, grad_compress=GRAD_COMPRESS or None)
+                        ep_on_overflow=EP_ON_OVERFLOW, grad_compress=GRAD_COMPRESS or None, eps=EPS)
     tok, val_loader = None, None
     if DATA == "synthetic" and not SOURCES:
         loader = _synthetic_stream(trainer.config.vocab_size, rank)

@@ -20,6 +20,7 @@ ARCH_OVERRIDES: dict = {}
 MICRO_TOKENS = 4096
 NUM_MICROBATCHES = 16
 SCHEDULE = "1f1b"
+VIRTUAL_STAGES = 2          # model chunks per rank under the looped multi-chunk schedules (the V-shaped ones use 2)
 LAYERS: list | None = None
 AUTOTUNE = True
 HEAD_ONLY_STAGE = True     # the measured split may leave the last stage with the final norm and the head only
@@ -96,7 +97,8 @@ def main():
     if AUTOTUNE and LAYERS is None:
         measured = measure_costs(cfg, MICRO_TOKENS, ranks.device) if ranks.rank == 0 else None
         costs = broadcast_costs(measured, cfg.depth, ranks.device)
-    chunks = 2 if SCHEDULE in ("zbv", "dualpipe-v", "interleaved-1f1b", "looped-bfs", "interleaved-zb") else 1
+    chunks = 2 if SCHEDULE in ("zbv", "dualpipe-v") else \
+        max(int(VIRTUAL_STAGES), 2) if SCHEDULE in ("interleaved-1f1b", "looped-bfs", "interleaved-zb") else 1
     plans = plan_for(cfg, ranks.world_size * chunks, MICRO_TOKENS, layers=LAYERS, costs=costs,
                      style="v" if SCHEDULE in ("zbv", "dualpipe-v") else "loop",
                      allow_empty_last=HEAD_ONLY_STAGE and costs is not None)

@@ -40,7 +40,8 @@ class LMTrainer:
                  device=None, group=None, grad_sync: str = "auto", callbacks=(), log_interval: int = 10,
                  ema: float = 0.98, seed: int = 1234, head_kwargs: dict | None = None,
                  optimizer: str = "fused_adamw", optimizer_kwargs: dict | None = None, expert_parallel: bool = False,
-                 ep_capacity_factor: float = 2.0, ep_on_overflow: str = "raise", grad_compress: str | None = None):
+                 ep_capacity_factor: float = 2.0, ep_on_overflow: str = "raise", grad_compress: str | None = None,
+                 eps: float = 1e-8):
         self.rank = dist.get_rank(group) if dist.is_available() and dist.is_initialized() else 0
         self.world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
         self.group = group
@@ -55,7 +56,7 @@ class LMTrainer:
         if grad_sync == "auto":
             grad_sync = "fused" if (self.world > 1 and self.device.type == "cuda" and optimizer == "fused_adamw") else "nccl"
         dtype = param_dtype if self.device.type == "cuda" else None
-        self.engine = TrainEngine(self.backbone, lr=lr, betas=betas, weight_decay=weight_decay, max_grad_norm=max_grad_norm,
+        self.engine = TrainEngine(self.backbone, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, max_grad_norm=max_grad_norm,
                                   param_dtype=dtype, group=group, grad_sync=grad_sync,
                                   lr_schedule=(lambda step: lr * sched(step)), optimizer=optimizer,
                                   optimizer_kwargs=optimizer_kwargs, expert_parallel=expert_parallel,
