@@ -71,6 +71,8 @@ DEVICE = "auto"
 WANDB_PROJECT = ""          # a Weights & Biases project name turns the W&B sink on (rank 0)
 WANDB_MODE = "offline"      # these machines have no network: sync the run directory later
 RUN_NAME = ""
+RUN_ID = ""                 # continue this Weights & Biases run (a resumed training keeps one curve)
+PROGRESS_BAR = False        # a step-driven progress bar on rank 0
 METRICS_JSONL = ""          # one JSON object per report
 
 
@@ -159,8 +161,12 @@ def main():
     from kohakuwullm_b200.utils.reporters import build_reporter
 
     reporter = build_reporter(WANDB_PROJECT or None, RUN_NAME or None, {"preset": PRESET}, METRICS_JSONL or None, 0,
-                              WANDB_MODE, directory=CKPT_DIR or None)
+                              WANDB_MODE, run_id=RUN_ID or None, directory=CKPT_DIR or None)
     callbacks = [ThroughputCallback(interval=LOG_INTERVAL * 2, reporter=reporter)]
+    if PROGRESS_BAR:
+        from kohakuwullm_b200.training.loop.callbacks import StepProgressBar
+
+        callbacks.append(StepProgressBar(MAX_STEPS))
     if SAMPLE_INTERVAL > 0 and SAMPLE_PROMPTS and tok is not None:
         from kohakuwullm_b200.training.loop.callbacks import SampleLogCallback
 

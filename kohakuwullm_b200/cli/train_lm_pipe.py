@@ -23,6 +23,7 @@ SCHEDULE = "1f1b"
 VIRTUAL_STAGES = 2          # model chunks per rank under the looped multi-chunk schedules (the V-shaped ones use 2)
 LAYERS: list | None = None
 AUTOTUNE = True
+AUTOTUNE_DOC_LEN = 2048     # document length of the probe batch the layer costs are measured on
 HEAD_ONLY_STAGE = True     # the measured split may leave the last stage with the final norm and the head only
 LEN_MIN, LEN_MAX = 64, 4096
 DATA = "synthetic"          # "synthetic", a corpus directory, or use SOURCES
@@ -50,6 +51,7 @@ SAMPLE_MIN_P = 0.0
 SAMPLE_COUNT = 4                            # completions per prompt
 SAMPLE_FROM_BATCH = 0                       # > 0: also continue that many documents cut out of the batch just trained on
 SAMPLE_PREFIX_TOKENS = 768                  # longest prefix kept of such a document
+SAMPLE_PREFIX_FRAC = 0.25                   # where a document without turn structure is cut
 SAMPLE_TURNS_ONLY = True                    # cut chat documents at a turn boundary (the assistant answers)
 SAMPLE_LOCAL = True                         # True: gather the weights and decode on rank 0; False: pipelined decode
 OPTIMIZER = "fused_adamw"      # or muon, adamw16, stochastic_adamw, adamw8bit, adamw4bit, adamwfp8, adamw, adam, sgd
@@ -68,6 +70,8 @@ BACKEND: str | None = None
 WANDB_PROJECT = ""          # a Weights & Biases project name turns the W&B sink on (rank 0)
 WANDB_MODE = "offline"      # these machines have no network: sync the run directory later
 RUN_NAME = ""
+RUN_ID = ""                 # continue this Weights & Biases run (a resumed training keeps one curve)
+PROGRESS_BAR = False        # a step-driven progress bar on rank 0
 METRICS_JSONL = ""          # one JSON object per report
 CONSOLE_INTERVAL = 0
 
@@ -95,7 +99,7 @@ def main():
     cfg = get_preset(PRESET, **arch)
     costs = None
     if AUTOTUNE and LAYERS is None:
-        measured = measure_costs(cfg, MICRO_TOKENS, ranks.device) if ranks.rank == 0 else None
+        measured = measure_costs(cfg, MICRO_TOKENS, ranks.device, doc_len=AUTOTUNE_DOC_LEN) if ranks.rank == 0 else None
         costs = broadcast_costs(measured, cfg.depth, ranks.device)
     chunks = 2 if SCHEDULE in ("zbv", "dualpipe-v") else \
         max(int(VIRTUAL_STAGES), 2) if SCHEDULE in ("interleaved-1f1b", "looped-bfs", "interleaved-zb") else 1
@@ -107,7 +111,7 @@ def main():
     from kohakuwullm_b200.utils.reporters import build_reporter
 
     reporter = build_reporter(WANDB_PROJECT or None, RUN_NAME or None, {"preset": PRESET, **ARCH_OVERRIDES},
-                              METRICS_JSONL or None, CONSOLE_INTERVAL, WANDB_MODE,
+                              METRICS_JSONL or None, CONSOLE_INTERVAL, WANDB_MODE, run_id=RUN_ID or None,
                               directory=CKPT_DIR or None) if ranks.rank == 0 else None
     from kohakuwullm_b200.utils.misc import autofill_schedule_steps
 
@@ -139,6 +143,10 @@ def main():
             from transformers import AutoTokenizer
 
             tok = AutoTokenizer.from_pretrained(TOKENIZER)
+    if PROGRESS_BAR:
+        from kohakuwullm_b200.pipe.callbacks import ProgressBar
+
+        trainer.loop.callbacks.callbacks.append(ProgressBar(MAX_STEPS))
     if BIAS_SCHEDULE:
         from kohakuwullm_b200.training.parallel.uwupipe_callbacks import RouterBiasSchedule
 
@@ -150,6 +158,7 @@ def main():
             module, tok, [tuple(p) for p in SAMPLE_PROMPTS], every_n_steps=SAMPLE_INTERVAL, max_new_tokens=SAMPLE_TOKENS,
             temperature=SAMPLE_TEMPERATURE, top_p=SAMPLE_TOP_P, top_k=SAMPLE_TOP_K, min_p=SAMPLE_MIN_P,
             samples=SAMPLE_COUNT, from_batch=SAMPLE_FROM_BATCH, prefix_tokens=SAMPLE_PREFIX_TOKENS,
+            prefix_frac=SAMPLE_PREFIX_FRAC,
             turns_only=SAMPLE_TURNS_ONLY, local=SAMPLE_LOCAL, report=getattr(reporter, "samples", None)))
     if CKPT_DIR:
         trainer.loop.callbacks.callbacks.append(Checkpoint(trainer, CKPT_DIR, every=CKPT_EVERY))
