@@ -73,6 +73,8 @@ WANDB_MODE = "offline"      # these machines have no network: sync the run direc
 RUN_NAME = ""
 RUN_ID = ""                 # continue this Weights & Biases run (a resumed training keeps one curve)
 PROGRESS_BAR = False        # a step-driven progress bar on rank 0
+HEARTBEAT = 0.0             # > 0: ranks beat into a store of their own; a peer silent for this many seconds (or one that
+                            # announced its exit) ends the run between two steps, before the next collective is launched
 METRICS_JSONL = ""          # one JSON object per report
 
 
@@ -163,6 +165,10 @@ def main():
     reporter = build_reporter(WANDB_PROJECT or None, RUN_NAME or None, {"preset": PRESET}, METRICS_JSONL or None, 0,
                               WANDB_MODE, run_id=RUN_ID or None, directory=CKPT_DIR or None)
     callbacks = [ThroughputCallback(interval=LOG_INTERVAL * 2, reporter=reporter)]
+    if HEARTBEAT > 0 and world > 1:
+        from kohakuwullm_b200.utils.heartbeat import HeartbeatCallback, RankHeartbeat
+
+        callbacks.append(HeartbeatCallback(RankHeartbeat.from_env(interval=max(HEARTBEAT / 10.0, 0.05), timeout=HEARTBEAT)))
     if PROGRESS_BAR:
         from kohakuwullm_b200.training.loop.callbacks import StepProgressBar
 

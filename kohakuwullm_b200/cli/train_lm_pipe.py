@@ -72,6 +72,8 @@ WANDB_MODE = "offline"      # these machines have no network: sync the run direc
 RUN_NAME = ""
 RUN_ID = ""                 # continue this Weights & Biases run (a resumed training keeps one curve)
 PROGRESS_BAR = False        # a step-driven progress bar on rank 0
+HEARTBEAT = 0.0             # > 0: ranks beat into a store of their own; a peer silent for this many seconds (or one that
+                            # announced its exit) ends the run between two steps, before the next collective is launched
 METRICS_JSONL = ""          # one JSON object per report
 CONSOLE_INTERVAL = 0
 
@@ -143,6 +145,11 @@ def main():
             from transformers import AutoTokenizer
 
             tok = AutoTokenizer.from_pretrained(TOKENIZER)
+    if HEARTBEAT > 0 and ranks.world_size > 1:
+        from kohakuwullm_b200.utils.heartbeat import HeartbeatCallback, RankHeartbeat
+
+        hb = RankHeartbeat.from_env(interval=max(HEARTBEAT / 10.0, 0.05), timeout=HEARTBEAT)
+        trainer.loop.callbacks.callbacks.append(HeartbeatCallback(hb))
     if PROGRESS_BAR:
         from kohakuwullm_b200.pipe.callbacks import ProgressBar
 

@@ -227,3 +227,156 @@ def test_only_rank_zero_logs_unless_asked(monkeypatch):
         assert "bad" in buf.getvalue()                      # errors from any rank
     monkeypatch.setenv("RANK", "0")
     klog.configure()
+
+
+class _DictStore:
+    """In-process stand-in for the job's key-value store."""
+
+    def __init__(self):
+        self.data = {}
+
+    def set(self, key, value):
+        self.data[key] = value.encode() if isinstance(value, str) else bytes(value)
+
+    def get(self, key):
+        return self.data[key]
+
+    def check(self, keys):
+        return all(k in self.data for k in keys)
+
+
+def test_heartbeat_notices_a_silent_peer_and_an_announced_exit():
+    """Three ranks on one store. A peer that stops beating is reported after the timeout (judged on the reader's own
+    clock), one that says it leaves is reported at once, and a peer that never appeared is tolerated only for the
+    timeout."""
+    import time
+
+    from kohakuwullm_b200.utils.heartbeat import HeartbeatCallback, PeerLost, RankHeartbeat
+
+    store = _DictStore()
+    hbs = [RankHeartbeat(store, r, 3, interval=0.05, timeout=0.4) for r in range(3)]
+    time.sleep(0.15)
+    for hb in hbs:
+        hb.check(force=True)
+        assert hb.alive() == [0, 1, 2]
+    hbs[2].close()                                   # dies silently: no more beats, no announcement
+    t0 = time.monotonic()
+    with pytest.raises(PeerLost) as err:
+        while time.monotonic() - t0 < 3.0:
+            hbs[0].check()
+            time.sleep(0.02)
+    assert err.value.rank == 2 and 0.3 < time.monotonic() - t0 < 1.5 and "no heartbeat" in str(err.value)
+    assert hbs[1].alive() == [0, 1]
+    # an exception in a rank's own step announces the exit through the callback; the others stop at their next check
+    HeartbeatCallback(hbs[1]).on_exception(None, ValueError("loss is nan"))
+    with pytest.raises(PeerLost) as err:
+        hbs[0].check(force=True)
+    assert err.value.rank == 1 and "loss is nan" in str(err.value)
+    hbs[0].close()
+    late = RankHeartbeat(_DictStore(), 0, 2, interval=0.05, timeout=0.3)      # rank 1 never shows up
+    late.check(force=True)
+    time.sleep(0.4)
+    with pytest.raises(PeerLost) as err:
+        late.check(force=True)
+    assert err.value.rank == 1 and "never" in str(err.value)
+    late.close()
+    with pytest.raises(ValueError):
+        RankHeartbeat(_DictStore(), 0, 2, interval=1.0, timeout=1.5)
+
+
+def _heartbeat_rank(rank, world, port, out_dir):
+    import time
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    from kohakuwullm_b200.utils.heartbeat import PeerLost, RankHeartbeat
+
+    hb = RankHeartbeat.from_env(interval=0.1, timeout=1.0, port_offset=0)
+    result = "finished"
+    try:
+        for step in range(60):
+            hb.check()
+            if rank == world - 1 and step == 5:
+                os._exit(0)                          # the process is gone between two steps, without a word
+            time.sleep(0.05)
+    except PeerLost as exc:
+        result = f"lost {exc.rank}"
+    with open(os.path.join(out_dir, f"r{rank}.txt"), "w") as fh:
+        fh.write(result)
+    if rank == 0:
+        time.sleep(1.0)                              # the store's server outlives the other readers
+    hb.close()
+
+
+@pytest.mark.timeout(120)
+def test_heartbeat_over_a_tcp_store_between_processes(tmp_path):
+    """Real processes and a real TCP store: the last rank exits between steps; the survivors learn of it on the host
+    within the timeout and name the rank, with no collective involved."""
+    import multiprocessing as mp
+
+    from tests.helpers import free_port
+
+    ctx = mp.get_context("spawn")
+    port = free_port()
+    procs = [ctx.Process(target=_heartbeat_rank, args=(r, 3, port, str(tmp_path))) for r in range(3)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(60)
+        assert not p.is_alive()
+    assert (tmp_path / "r0.txt").read_text() == "lost 2" and (tmp_path / "r1.txt").read_text() == "lost 2"
+    assert not (tmp_path / "r2.txt").exists()
+
+
+def _hb_trainer_rank(rank, world, port, out_dir):
+    import time
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=120))
+    from kohakuwullm_b200.training.loop.trainer import LMTrainer
+    from kohakuwullm_b200.utils.heartbeat import HeartbeatCallback, PeerLost, RankHeartbeat
+
+    class Trip(Callback):
+        def on_train_batch_end(self, trainer, out, batch, step):
+            if rank == 1 and step == 2:
+                raise RuntimeError("injected failure")
+            if rank == 0 and step == 2:
+                time.sleep(1.0)               # the survivor reaches its next step after the failing rank said goodbye
+
+    hb = RankHeartbeat.from_env(interval=0.1, timeout=5.0)
+    trainer = LMTrainer("B200-smoke", dict(CFG), device="cpu", param_dtype=None, callbacks=[HeartbeatCallback(hb), Trip()])
+    t0 = time.monotonic()
+    try:
+        trainer.fit((make_pack(48, 8, 24, 200, seed=s) for s in range(50)), max_steps=50)
+        result = "finished"
+    except PeerLost as exc:
+        result = f"PeerLost {exc.rank} at step {trainer.global_step} after {time.monotonic() - t0:.1f}s: {exc}"
+    except RuntimeError as exc:
+        result = f"RuntimeError: {exc}"
+    with open(os.path.join(out_dir, f"r{rank}.txt"), "w") as fh:
+        fh.write(result)
+    if rank == 0:
+        time.sleep(0.5)
+    os._exit(0)        # skip the process-group teardown: the peer is gone
+
+
+@pytest.mark.timeout(180)
+def test_trainer_with_heartbeat_stops_before_the_next_collective(tmp_path):
+    """Data-parallel trainer on two gloo ranks with a 120 s collective time-out: rank 1 raises after step 2. Rank 0
+    must not enter step 3's all-reduce (it would wait two minutes): the heartbeat check at the start of the step
+    raises PeerLost with the failing rank's own message."""
+    import multiprocessing as mp_std
+
+    ctx = mp_std.get_context("spawn")
+    port = free_port()
+    procs = [ctx.Process(target=_hb_trainer_rank, args=(r, 2, port, str(tmp_path))) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(100)
+    alive = [p for p in procs if p.is_alive()]
+    for p in alive:
+        p.kill()
+    assert not alive, "the surviving rank went into a collective with a dead peer"
+    r0, r1 = (tmp_path / "r0.txt").read_text(), (tmp_path / "r1.txt").read_text()
+    assert r1 == "RuntimeError: injected failure"
+    assert r0.startswith("PeerLost 1 at step 2") and "injected failure" in r0, r0
