@@ -44,6 +44,7 @@ PAD_TOKEN_ID = 0
 BATCH_TOKENS = 16384            # tokens per rank per optimizer step
 GRAD_ACCUM = 4
 CTX_MAX = 4096
+DOC_FILTER: str | dict = ""     # "ngram" (share of repeated 4-grams), "consecutive" (back-to-back n-gram runs), or {"name": .., **args}
 LEN_MIN, LEN_MAX = 64, 4096
 OPTIMIZER = "fused_adamw"      # or muon, adamw16, stochastic_adamw, adamw8bit, adamw4bit, adamwfp8, adamw, adam, sgd
 OPTIMIZER_KWARGS: dict = {}     # e.g. {"muon_lr": 0.02}
@@ -132,7 +133,9 @@ def main():
 
             tok = AutoTokenizer.from_pretrained(TOKENIZER)
         encode = lambda s: tok.encode(s)  # noqa: E731
-        common = dict(k=BATCH_TOKENS, m=BATCH_TOKENS // 16, ctx_max=CTX_MAX, seed=SEED,
+        from kohakuwullm_b200.data.filters import build_doc_filter
+
+        common = dict(k=BATCH_TOKENS, m=BATCH_TOKENS // 16, ctx_max=CTX_MAX, seed=SEED, doc_filter=build_doc_filter(DOC_FILTER),
                       bos=getattr(tok, "bos_token_id", None), eos=getattr(tok, "eos_token_id", None))
         if VAL_FRACTION > 0:
             from kohakuwullm_b200.data.sources.records import SplitRecords

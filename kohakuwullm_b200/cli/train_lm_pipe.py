@@ -31,6 +31,7 @@ SOURCES: list = []          # [{"records": <record spec>, "repeat": 1.0, "source
 RENDERER = "plain"
 TOKENIZER = "byte"          # "byte" or a Hugging Face tokenizer path
 CTX_MAX = 4096
+DOC_FILTER: str | dict = ""  # "ngram" (share of repeated 4-grams), "consecutive" (back-to-back n-gram runs), or {"name": .., **args}
 LR_SCHEDULE: dict = {"mode": "cosine", "warmup": None, "end": None, "min_value": 0.1}
 WARMUP_STEPS = 100
 WARMUP_RATIO = 0.0                          # > 0: the warm-up is this share of MAX_STEPS (overrides WARMUP_STEPS)
@@ -188,11 +189,13 @@ def main():
     else:
         # every rank iterates the SAME micro-batched loader (stage 0 uses the tokens, the last stage the labels)
         from kohakuwullm_b200.data import build_dataset, build_loader
+        from kohakuwullm_b200.data.filters import build_doc_filter
 
         spec = {"name": "mixture", "sources": SOURCES, "seed": SEED} if SOURCES else {"name": "corpus", "root": DATA}
         records, renderer = build_dataset(spec, RENDERER)
         batches = build_loader("pipeline", records, renderer, lambda s: tok.encode(s), k=MICRO_TOKENS, m=MICRO_TOKENS // 16,
                                num_microbatches=NUM_MICROBATCHES, ctx_max=CTX_MAX, seed=SEED,
+                               doc_filter=build_doc_filter(DOC_FILTER),
                                bos=getattr(tok, "bos_token_id", None), eos=getattr(tok, "eos_token_id", None))
     trainer.fit(batches, MAX_STEPS)
     if CKPT_DIR:

@@ -62,3 +62,28 @@ def longest_consecutive_repeat(units: Sequence, max_n: int = 13) -> tuple[int, i
 
 def passes_consecutive_repeat_filter(text: str, max_n: int = 13, threshold: int = 32) -> bool:
     return longest_consecutive_repeat(text_units(text), max_n)[0] < threshold
+
+
+def passes_consecutive_token_repeat(tokens: Sequence, max_n: int = 13, threshold: int = 32) -> bool:
+    """The consecutive-repeat rule on token ids (what a loader filter sees)."""
+    return longest_consecutive_repeat(tokens, max_n)[0] < threshold
+
+
+DOC_FILTERS = {"ngram": passes_repeat_filter, "consecutive": passes_consecutive_token_repeat}
+
+
+def build_doc_filter(spec):
+    """A loader's ``doc_filter`` (token ids -> keep?) from a name, ``{"name": ..., **arguments}`` or a callable;
+    ``None`` / ``""`` is no filter. The result is a ``functools.partial`` of a module-level function, so it pickles
+    into loader worker processes."""
+    import functools
+
+    if not spec:
+        return None
+    if callable(spec):
+        return spec
+    cfg = {"name": spec} if isinstance(spec, str) else dict(spec)
+    name = cfg.pop("name")
+    if name not in DOC_FILTERS:
+        raise KeyError(f"unknown document filter {name!r}; known: {', '.join(sorted(DOC_FILTERS))}")
+    return functools.partial(DOC_FILTERS[name], **cfg)

@@ -89,12 +89,13 @@ class IterativePackLoader:
     def __init__(self, records, renderer, encode, *, k: int, m: int = 0, ctx_max: int | None = None,
                  shard: int = 0, shards: int = 1, seed: int = 0, bos: int | None = None, eos: int | None = None,
                  shuffle: bool = True, exact: bool = False, pad_id: int = 0, min_tokens: int = 2,
-                 doc_filter: Callable | None = None, max_retries: int = 64):
+                 doc_filter: Callable | None = None, max_retries: int = 64, max_deferred: int = 16):
         self.records, self.renderer, self.encode = records, renderer, encode
         self.k, self.m, self.ctx_max = k, m, ctx_max or k
         self.order = ShardIndices(len(records), shard, shards, seed, shuffle)
         self.seed, self.bos, self.eos, self.exact, self.pad_id = seed, bos, eos, exact, pad_id
         self.min_tokens, self.doc_filter, self.max_retries = min_tokens, doc_filter, max_retries
+        self.max_deferred = max_deferred
         self.pos = LoaderPosition(shard, shards)
 
     # ------------------------------------------------------------------ resume
@@ -130,7 +131,7 @@ class IterativePackLoader:
                 raise RuntimeError(f"{self.max_retries} consecutive records were rejected; check the filter / renderer")
 
     def _next_pack(self) -> PackedBatch:
-        docs, used = [], 0
+        docs, used, deferred = [], 0, 0
         carry, self.pos.carry = self.pos.carry, []
         queue = list(carry)
         while True:
@@ -157,7 +158,10 @@ class IterativePackLoader:
                     self.pos.carry.append((ids, mask))
                 break
             self.pos.carry.append((ids, mask))
-            if used >= self.k - self.m or not docs:
+            deferred += 1
+            # a pack that no upcoming document fits into (the room is smaller than every document but larger than
+            # the slack) must still close: after a few deferrals it is emitted as it is
+            if used >= self.k - self.m or not docs or deferred >= self.max_deferred:
                 break
         self.pos.carry = queue + self.pos.carry
         self.pos.emitted += 1

@@ -359,3 +359,50 @@ def test_kv_store_and_mixture_properties():
 
     store()
     mix()
+
+
+def test_doc_filter_builder_names_arguments_and_pickling():
+    import pickle
+
+    from kohakuwullm_b200.data.filters import build_doc_filter
+
+    assert build_doc_filter("") is None and build_doc_filter(None) is None
+    looping = [1, 2, 3, 4] * 40
+    varied = list(range(160))
+    ngram = build_doc_filter("ngram")
+    assert ngram(varied) and not ngram(looping)
+    strict = build_doc_filter({"name": "consecutive", "threshold": 8})
+    assert strict(varied) and not strict(looping) and build_doc_filter("consecutive")(looping[:100])   # 25 runs < 32
+    again = pickle.loads(pickle.dumps(strict))                  # travels into loader worker processes
+    assert not again(looping)
+    keep_all = lambda ids: True                                  # noqa: E731
+    assert build_doc_filter(keep_all) is keep_all
+    with pytest.raises(KeyError):
+        build_doc_filter("perplexity")
+
+
+def test_pack_closes_when_no_document_fits_the_remaining_room():
+    """Every document is 30 tokens, the budget 100 and the slack 4: after three documents the room (10) is larger
+    than the slack and smaller than any document, so nothing upcoming ever fits. The pack must close anyway (the
+    packer looks a bounded number of documents ahead), nothing may be lost or doubled, and the documents it looked at
+    open the following packs."""
+    from kohakuwullm_b200.data import build_loader
+    from kohakuwullm_b200.registry import DATASET, build
+
+    texts = [f"{i:04d}" + chr(65 + i % 26) * 24 for i in range(400)]   # 28 bytes + BOS + EOS = 30 tokens, all distinct
+    records = build({"name": "list", "records": [{"text": t} for t in texts]}, DATASET)
+    loader = build_loader("iterative", records, lambda r, rng=None: [(r["text"], True)], lambda s: list(s.encode()),
+                          k=100, m=4, ctx_max=64, seed=3, bos=256, eos=257, shuffle=False)
+    emitted = []
+    it = iter(loader)
+    for _ in range(40):
+        batch = next(it)
+        assert batch.num_tokens == 90 and batch.seq_info.num_seqs == 3
+        cu = batch.seq_info.cu_seqlens.tolist()
+        emitted += [bytes(t for t in batch.tokens[a:b].tolist() if t < 256).decode() for a, b in zip(cu, cu[1:])]
+    state = loader.state_dict()["positions"][0]
+    assert len(emitted) == len(set(emitted)) == 120
+    assert len(state["carry"]) <= 16                                  # the look-ahead queue stays bounded
+    # what was read is what was emitted plus what waits in the queue: nothing lost
+    assert state["pass"] == 0 and state["cursor"] == 120 + len(state["carry"])
+    assert set(emitted) <= set(texts[: state["cursor"]])

@@ -67,7 +67,7 @@ def _reference(steps=2, optimizer="fused_adamw"):
 
 def _pipe_worker(rank, world, port, schedule, layers, out_dir, load_from, optimizer="fused_adamw"):
     import faulthandler
-    faulthandler.dump_traceback_later(30, exit=True)
+    faulthandler.dump_traceback_later(120, exit=True)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     cfg = get_preset("B200-smoke", **CFG)
@@ -153,7 +153,7 @@ def test_checkpoint_loads_under_another_split_and_on_one_process():
 
 def _plm_worker(rank, world, port, out_dir):
     import faulthandler
-    faulthandler.dump_traceback_later(60, exit=True)
+    faulthandler.dump_traceback_later(120, exit=True)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     from kohakuwullm_b200.training.loop.pipeline_trainer import PipelinedLMTrainer
