@@ -406,3 +406,39 @@ def test_pack_closes_when_no_document_fits_the_remaining_room():
     # what was read is what was emitted plus what waits in the queue: nothing lost
     assert state["pass"] == 0 and state["cursor"] == 120 + len(state["carry"])
     assert set(emitted) <= set(texts[: state["cursor"]])
+
+
+@pytest.mark.timeout(120)
+def test_packing_properties_over_random_lengths_budgets_and_slack():
+    """For arbitrary document lengths, budgets and slack, in both packing modes: the loader always yields, a pack never
+    exceeds its budget, exact packs are exactly full, and over the packs of one epoch the documents come out once each
+    (whole in the non-exact mode, as the concatenation of their pieces in the exact mode)."""
+    from hypothesis import given, settings
+    from hypothesis import strategies as st
+
+    from kohakuwullm_b200.data import build_loader
+    from kohakuwullm_b200.registry import DATASET, build
+
+    @settings(max_examples=40, deadline=None)
+    @given(lengths=st.lists(st.integers(1, 60), min_size=3, max_size=40), k=st.integers(16, 96),
+           slack=st.integers(0, 15), exact=st.booleans(), seed=st.integers(0, 5))
+    def check(lengths, k, slack, exact, seed):
+        texts = [f"{i:03d}" + "x" * (n - 1) if n > 3 else "y" * n for i, n in enumerate(lengths)]
+        records = build({"name": "list", "records": [{"text": t} for t in texts]}, DATASET)
+        ctx = min(k, 48)
+        loader = build_loader("iterative", records, lambda r, rng=None: [(r["text"], True)], lambda s: list(s.encode()),
+                              k=k, m=min(slack, k // 2), ctx_max=ctx, seed=seed, bos=256, eos=257, exact=exact)
+        total = sum(min(len(t) + 2, ctx) for t in texts)                  # tokens of one epoch after the cut to ctx
+        seen_tokens, packs = 0, 0
+        it = iter(loader)
+        while seen_tokens < total and packs < 4 * len(texts) + 8:
+            batch = next(it)
+            packs += 1
+            real = int((batch.tokens != 0).sum()) if exact else batch.num_tokens    # exact packs pad the very last one
+            assert batch.num_tokens <= k
+            if exact:
+                assert batch.num_tokens == k
+            seen_tokens += real
+        assert seen_tokens >= total, (seen_tokens, total, packs)          # the epoch was delivered, the loader never stalled
+
+    check()
