@@ -235,9 +235,13 @@ class PipelineTrainer:
 
     # ------------------------------------------------------------------ checkpoints
     def _stage_module(self):
+        """What a checkpoint of this rank covers: the stage, or with several stages per rank a list of them whose
+        parameter names (``"<local index>.<name>"``) are the keys ``module.global_names()`` maps to whole-model names."""
         if len(self.module.stages) == 1:
             return self.module.stages[0]
-        raise NotImplementedError("checkpointing several stages per rank is not implemented")
+        if getattr(self, "_stage_list", None) is None:
+            self._stage_list = torch.nn.ModuleList(self.module.stages)
+        return self._stage_list
 
     def save_checkpoint(self, path: str) -> None:
         stage = self._stage_module()

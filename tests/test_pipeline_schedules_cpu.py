@@ -56,6 +56,18 @@ def _worker(rank, world, port, schedule, out_dir):
             state[names.get(k, k)] = v.detach().clone()
     torch.save({"losses": [float(o.loss) for o in outs], "state": state, "stages": trainer.local_indices},
                os.path.join(out_dir, f"rank{rank}.pt"))
+    # several stages per rank in ONE whole-model checkpoint, and back: zero the weights, load, compare
+    path = os.path.join(out_dir, "multi.ckpt")
+    trainer.save_checkpoint(path)
+    kept = {k: v.detach().clone() for st in module.stages for k, v in st.state_dict().items()}
+    with torch.no_grad():
+        for st in module.stages:
+            for prm in st.parameters():
+                prm.zero_()
+    rest = trainer.load_checkpoint(path)
+    again = {k: v for st in module.stages for k, v in st.state_dict().items()}
+    ok = all(torch.equal(kept[k], again[k]) for k in kept) and rest.get("global_step", 2) == 2 and trainer.loop.global_step == 2
+    torch.save({"roundtrip": bool(ok)}, os.path.join(out_dir, f"roundtrip{rank}.pt"))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -77,6 +89,26 @@ def test_multi_chunk_schedule_matches_single_process(schedule, placement):
     assert set(merged) == set(ref_state)
     for k in ref_state:
         torch.testing.assert_close(merged[k], ref_state[k], rtol=0, atol=5e-4, msg=k)
+
+
+@pytest.mark.timeout(900)
+def test_checkpoint_with_two_stages_per_rank_is_a_whole_model_file():
+    """Interleaved 1F1B, two ranks, four stages: the checkpoint is one file keyed by whole-model names (it loads into
+    a single-process model and equals the reference run), and loading it back restores every stage and the step."""
+    from kohakuwullm_b200.pipe import checkpoint as ckpt
+
+    _, ref_state = _reference()
+    with tempfile.TemporaryDirectory() as tmp:
+        mp.spawn(_worker, args=(2, free_port(), "interleaved-1f1b", tmp), nprocs=2, join=True)
+        assert all(torch.load(os.path.join(tmp, f"roundtrip{r}.pt"))["roundtrip"] for r in range(2))
+        whole = LMBackbone(get_preset("B200-smoke", **CFG))
+        rest = ckpt.load(os.path.join(tmp, "multi.ckpt"), whole)
+        payload = ckpt.read_payload(os.path.join(tmp, "multi.ckpt"))
+    assert set(payload["state_dict"]) == set(ref_state) and rest["global_step"] == 2
+    for k, v in whole.state_dict().items():
+        torch.testing.assert_close(v, ref_state[k], rtol=0, atol=5e-4, msg=k)
+    named = payload["optimizer_states"][0]["named_optimizer_state"]
+    assert set(named) == {n for n, _ in whole.named_parameters()}        # optimizer state under whole-model names too
 
 
 # ------------------------------------------------------------------ a non-LM user of the engine
