@@ -41,6 +41,18 @@ def test_preview_sampler_has_its_own_random_stream(wide_model):
     again = PreviewSampler(eos_id=96).generate(wide_model, prompt, 10, temperature=1.0)
     assert torch.equal(first, again)
 
+    class Tok:
+        bos_token_id = 95
+
+        def encode(self, text):
+            return [ord(c) % 90 for c in text]
+
+        def decode(self, ids):
+            return " ".join(str(i) for i in ids)
+
+    texts = PreviewSampler(eos_id=96).texts(wide_model, Tok(), ["ab", "xyz"], 5, count=2, temperature=0.7)
+    assert len(texts) == 2 and all(len(t) == 2 and all(len(x.split()) == 5 for x in t) for t in texts)
+
 
 def test_filters():
     logits = torch.tensor([[1.0, 2.0, 3.0, 4.0]])
