@@ -11,17 +11,23 @@ import torch
 def to_hf_config(cfg):
     from kohakuwullm_b200.export.hf.configuration_kohaku import KohakuConfig
 
+    from kohakuwullm_b200.models.components.mlp import resolve_hidden
+
     rk = cfg.moe_router_kwargs or {}
+    # the widths the model itself resolves (an explicit value, else ratio * dim * 2/3 rounded up to the multiple)
+    dense_hidden = resolve_hidden(cfg.dim, cfg.mlp_ratio, cfg.mlp_hidden, cfg.mlp_multiple_of, glu=True)
+    expert_hidden = resolve_hidden(cfg.dim, cfg.moe_ratio, cfg.moe_hidden, cfg.mlp_multiple_of, glu=True) \
+        if any(cfg.moe_layers) else 0
     return KohakuConfig(
         vocab_size=cfg.vocab_size, hidden_size=cfg.dim, num_hidden_layers=cfg.depth, num_attention_heads=cfg.heads,
         num_key_value_heads=cfg.kv_heads, head_dim=cfg.head_dim,
-        intermediate_size=cfg.mlp_hidden or int(-(-cfg.dim * cfg.mlp_ratio * 2 / 3 // cfg.mlp_multiple_of) * cfg.mlp_multiple_of),
+        intermediate_size=dense_hidden,
         rms_norm_eps=cfg.norm_eps, kohaku_rope_theta=cfg.rope_theta, kohaku_rope_scaling=cfg.rope_scaling,
         kohaku_rope_factor=cfg.rope_factor,
         max_position_embeddings=cfg.max_position, qk_norm=cfg.qk_norm, windows=cfg.windows,
         num_sinks=cfg.attn_num_sinks if cfg.attn_sink else 0, moe_layers=cfg.moe_layers,
         moe_num_experts=cfg.moe_num_experts if any(cfg.moe_layers) else 0, moe_top_k=cfg.moe_top_k,
-        moe_num_shared=cfg.moe_num_shared, moe_intermediate_size=cfg.moe_hidden or 0, moe_score=rk.get("score", "sigmoid"),
+        moe_num_shared=cfg.moe_num_shared, moe_intermediate_size=expert_hidden, moe_score=rk.get("score", "sigmoid"),
         moe_norm_topk_prob=rk.get("norm_topk_prob", True), moe_scaling=rk.get("routed_scaling_factor", 1.0),
         tie_word_embeddings=cfg.tie_embeddings, embedding_scale=cfg.embedding_scale, logit_soft_cap=cfg.logit_soft_cap)
 

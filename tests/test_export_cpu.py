@@ -33,6 +33,14 @@ def test_hf_export_moe(tmp_path):
                       moe_num_experts=4, moe_top_k=2, moe_hidden=64, mxfp8=False, init_std=0.2), tmp_path)
 
 
+def test_hf_export_widths_derived_from_ratios(tmp_path):
+    """No explicit hidden sizes: the dense and the expert widths come from ``ratio * dim * 2/3`` rounded up to the
+    multiple, exactly as the model resolves them (an export that wrote 0 for a derived expert width failed to load)."""
+    _check(get_preset("B200-smoke", vocab_size=101, dim=96, depth=3, heads=2, kv_heads=1, head_dim=32, mlp_hidden=None,
+                      mlp_ratio=3.0, mlp_multiple_of=32, moe_every=1, moe_first_dense=1, moe_num_experts=4, moe_top_k=2,
+                      moe_hidden=None, moe_ratio=1.5, moe_num_shared=2, mxfp8=False, init_std=0.2), tmp_path)
+
+
 def test_prune_tokenizer():
     vocab = {chr(97 + i): i for i in range(6)}
     vocab.update({"ab": 6, "cd": 7, "abcd": 8, "ef": 9})
