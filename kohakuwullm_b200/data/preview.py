@@ -20,8 +20,11 @@ MIN_FILLER_TOKENS = 32
 
 
 def batch_documents(batch) -> list[tuple[torch.Tensor, torch.Tensor]]:
-    """``[(tokens, labels)]`` per document of a packed batch, a list of packed micro-batches, or an object
+    """``[(tokens, labels)]`` per document of a packed batch, a list of packed micro-batches, a pipeline step
+    (``micro``: its packs), or an object
     with ``tokens`` / ``labels`` and ``seq_infos`` (one layout per equally sized micro-batch)."""
+    if hasattr(batch, "micro"):                      # a pipeline step: its packs, in order
+        batch = list(batch.micro)
     if isinstance(batch, (list, tuple)):
         out = []
         for b in batch:

@@ -23,6 +23,12 @@ def test_turn_cut_comes_from_the_loss_mask():
     assert trained_spans(got[0][1]) == [(7, 12)]
     prompts = prompts_from_batch(batch, 5, seed=1)
     assert len(prompts) == 2 and all(name.startswith("batch/turn/") for name, _ in prompts)
+    # what the pipeline loaders hand out (a step of several packs) is read the same way as a list of packs
+    from kohakuwullm_b200.data.loader.iterative import MicroBatchedStep
+
+    step = MicroBatchedStep([batch, collate_packed([_chat_doc(4, 4, 400)])])
+    assert [d[0].numel() for d in batch_documents(step)] == [12, 12, 40, 8]
+    assert len(prompts_from_batch(step, 5, seed=1)) == 3
     by_first = {int(p[0]): p for _, p in prompts}
     assert by_first[100].tolist() == list(range(100, 107))
     assert by_first[200].tolist() == list(range(200, 203))
