@@ -8,7 +8,7 @@
 The points the reference publishes are 4096x64, 8192x32, 12288x21, 14336x18, 16384x16 and 32768x8, with MXFP8 experts,
 activation checkpointing or the V-shaped schedule as variants; any other ``AxB`` works the same way. Every point runs
 60 steps on synthetic packs and writes its per-step metrics to ``out/sweep/<point>.jsonl``; read them with
-``kohakuwullm_b200.bench.sweep`` / ``bench.plotting``.
+``python -m kohakuwullm_b200.bench.plotting out/sweep --metrics train/loss throughput/tokens_per_s --out out/sweep/curves.svg``.
 """
 
 import os

@@ -6,9 +6,12 @@ the scaling plot and in the kernel plot.
     python -m kohakuwullm_b200.bench.plotting results/ --out results/throughput.svg
     python -m kohakuwullm_b200.bench.plotting results/ --scaling --out results/scaling.svg
 
+    python -m kohakuwullm_b200.bench.plotting out/sweep --metrics train/loss throughput/tokens_per_s --out out/sweep/curves.svg
+
 The command reads the result files ``bench.sweep.load_rows`` reads (one JSON line per run) and draws either bars of
 the metric per file or, with ``--scaling``, the metric over the number of GPUs with the ideal line of the smallest
-run. Reference: src/kohakuwullm/bench/core/plotting.py:1-134 (matplotlib styling helpers for its bench scripts).
+run; with ``--metrics`` it reads the per-step ``*.jsonl`` files of the trainers' JSONL sink instead and draws one panel
+per metric with one line per run. Reference: src/kohakuwullm/bench/core/plotting.py:1-134 (matplotlib styling helpers for its bench scripts).
 """
 
 from __future__ import annotations
@@ -45,9 +48,7 @@ def si_format(value: float) -> str:
     for unit, scale in (("T", 1e12), ("G", 1e9), ("M", 1e6), ("k", 1e3)):
         if abs(value) >= scale:
             return f"{value / scale:.1f}".rstrip("0").rstrip(".") + unit
-    if value != 0 and abs(value) < 1:
-        return f"{value:g}"
-    return f"{value:.0f}"
+    return f"{value:.4g}"      # 7 -> "7", 0.25 -> "0.25", 11.145 -> "11.14" (tick labels of a flat curve must differ)
 
 
 def nice_ticks(lo: float, hi: float, count: int = 5) -> list[float]:
@@ -278,6 +279,46 @@ def scaling_figure(rows: list[dict], key: str = "value", palette: Palette | None
     return fig
 
 
+def load_metric_curves(directory: str, pattern: str = "*.jsonl") -> dict[str, dict[str, tuple[list, list]]]:
+    """``{file stem: {metric: (steps, values)}}`` from the per-step metric files a ``JsonlReporter`` writes (one JSON
+    object per report with a ``step`` and any number of scalar metrics)."""
+    import glob
+    import json
+
+    runs: dict[str, dict[str, tuple[list, list]]] = {}
+    for path in sorted(glob.glob(os.path.join(directory, pattern))):
+        curves: dict[str, tuple[list, list]] = {}
+        with open(path) as fh:
+            for line in fh:
+                try:
+                    row = json.loads(line)
+                except ValueError:
+                    continue                      # a line cut short by a killed run
+                step = row.get("step")
+                if not isinstance(step, int):
+                    continue
+                for k, v in row.items():
+                    if k not in ("step", "t") and isinstance(v, (int, float)) and math.isfinite(v):
+                        xs, ys = curves.setdefault(k, ([], []))
+                        xs.append(step)
+                        ys.append(float(v))
+        if curves:
+            runs[os.path.splitext(os.path.basename(path))[0]] = curves
+    return runs
+
+
+def curves_figure(runs: dict, metrics: list[str], palette: Palette | None = None, logy: bool = False) -> Figure:
+    """One panel per metric, one line per run: loss and throughput of the points of a sweep side by side."""
+    palette = palette or Palette()
+    fig = Figure(1, max(len(metrics), 1))
+    for panel, metric in zip(fig.panels, metrics):
+        panel.title, panel.xlabel, panel.ylabel, panel.logy = metric, "step", metric.split("/")[-1], logy
+        for run, curves in runs.items():
+            if metric in curves:
+                panel.line(run, curves[metric][0], curves[metric][1], palette.color(run))
+    return fig
+
+
 def main(argv=None) -> int:
     from kohakuwullm_b200.bench.sweep import load_rows
 
@@ -286,8 +327,14 @@ def main(argv=None) -> int:
     ap.add_argument("--pattern", default="*.json")
     ap.add_argument("--key", default="value")
     ap.add_argument("--scaling", action="store_true")
+    ap.add_argument("--metrics", nargs="+", help="plot these per-step metrics of *.jsonl metric files, one panel each")
+    ap.add_argument("--logy", action="store_true")
     ap.add_argument("--out", required=True)
     args = ap.parse_args(argv)
+    if args.metrics:
+        runs = load_metric_curves(args.directory, args.pattern if args.pattern != "*.json" else "*.jsonl")
+        print(f"wrote {save_figure(curves_figure(runs, args.metrics, logy=args.logy), args.out)} from {len(runs)} runs")
+        return 0
     rows = load_rows(args.directory, args.pattern)
     fig = (scaling_figure if args.scaling else throughput_figure)(rows, args.key)
     print(f"wrote {save_figure(fig, args.out)} from {len(rows)} rows")

@@ -138,6 +138,20 @@ def test_plotting_svg_is_well_formed_and_complete(tmp_path):
     ET.parse(tmp_path / "scaling.svg")
     empty = pl.Figure()
     assert "no data" in empty.svg()
+    # per-step metric files of the trainers' JSONL sink: one panel per metric, one line per run, cut lines skipped
+    for name, shift in (("a", 0.0), ("b", 0.01)):
+        with open(tmp_path / f"{name}.jsonl", "w") as fh:
+            for step in range(2, 12, 2):
+                fh.write(_json.dumps({"step": step, "t": 0.1 * step, "train/loss": 11.15 - 0.001 * step + shift}) + "\n")
+                fh.write(_json.dumps({"step": step, "t": 0.1 * step, "throughput/tokens_per_s": 1000.0 + step}) + "\n")
+            fh.write('{"step": 12, "train/lo')
+    runs = pl.load_metric_curves(str(tmp_path))
+    assert sorted(runs) == ["a", "b"] and runs["a"]["train/loss"][0] == [2, 4, 6, 8, 10]
+    assert pl.main([str(tmp_path), "--metrics", "train/loss", "throughput/tokens_per_s", "--out", str(tmp_path / "curves.svg")]) == 0
+    root = ET.parse(tmp_path / "curves.svg").getroot()
+    assert len(root.findall(f"{ns}polyline")) == 4
+    labels = [t.text for t in root.iter(f"{ns}text")]
+    assert len({x for x in labels if x and x.startswith("11.")}) >= 3        # distinct tick labels on a flat curve
 
 
 def test_mxfp8_exponent_rules_and_emulated_linear():
