@@ -23,6 +23,7 @@ from kohakuwullm_b200.registry import NORM, POSENC, build
 
 # imported for their registrations
 from kohakuwullm_b200.models.components import attention as _a, mlp as _m, moe as _e, norm as _n, posenc as _p  # noqa: F401,E501
+from kohakuwullm_b200.models.components import moe_variants as _v, ndrope as _r  # noqa: F401,E402  (registrations)
 
 
 def build_block(config: LMArchConfig, layer: int) -> DecoderBlock:

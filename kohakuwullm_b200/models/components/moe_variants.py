@@ -32,10 +32,12 @@ class SinkhornRouter(TopKRouter):
     def route(self, x):
         logits = torch.nn.functional.linear(x.float(), self.weight.float())
         with torch.no_grad():
-            cost = torch.exp((logits - logits.max()) / self.temperature) + 1e-12
+            # in the log domain: dividing logits by a small temperature spans hundreds of e-folds, which underflows
+            # a plain exp() to a matrix of floor values and collapses the assignment onto one expert
+            cost = logits / self.temperature
             for _ in range(self.iterations):
-                cost = cost / cost.sum(0, keepdim=True)      # balance experts
-                cost = cost / cost.sum(1, keepdim=True)      # normalise tokens
+                cost = cost - torch.logsumexp(cost, dim=0, keepdim=True)      # balance experts
+                cost = cost - torch.logsumexp(cost, dim=1, keepdim=True)      # normalise tokens
             idx = cost.topk(self.top_k, dim=-1).indices
         s = torch.softmax(logits, -1)
         w = s.gather(1, idx)
