@@ -21,6 +21,7 @@ DATA = "synthetic"              # "synthetic" or a corpus directory (jsonl / txt
 SOURCES: list = []              # a mixture instead of DATA: [{"records": <record spec>, "repeat": 1.0, "source": "tag"}, ...]
 RENDERER = "plain"              # a renderer name or spec ("plain", "chatml", "qa", "tipo", {"name": "per_source", ...})
 NUM_WORKERS = 0                 # > 0: render + tokenise + pack in that many worker processes
+PREFETCH_FACTOR = 4             # packs each worker process keeps ready ahead of the trainer
 VAL_FRACTION = 0.0              # hold this share of the records out (hash split) and validate on it
 VAL_INTERVAL = 500
 VAL_BATCHES = 8
@@ -160,7 +161,8 @@ def main():
 
             loader = _epochs()
         elif NUM_WORKERS > 0:
-            loader = build_loader("workers", records, renderer, encode, rank=rank, world=world, workers=NUM_WORKERS, **common)
+            loader = build_loader("workers", records, renderer, encode, rank=rank, world=world, workers=NUM_WORKERS,
+                                  prefetch=PREFETCH_FACTOR, **common)
         else:
             loader = build_loader("ddp", records, renderer, encode, rank=rank, world=world, **common)
     from kohakuwullm_b200.utils.reporters import build_reporter
