@@ -183,8 +183,52 @@ def tensor_map(state: dict, cfg, expand_kv: bool) -> dict[str, torch.Tensor]:
     return out
 
 
+def unrepresentable(cfg) -> list[str]:
+    """Options of the model that the ``qwen3`` / ``dots1`` graphs of llama.cpp have no place for. A file written
+    anyway loads and runs, and computes a different function."""
+    def name(spec):
+        return spec if isinstance(spec, str) else (spec.get("name") if isinstance(spec, dict) else str(spec))
+
+    bad = []
+    if name(cfg.norm) not in ("rmsnorm", "rmsnorm_native", "rmsnorm_triton"):
+        bad.append(f"norm={name(cfg.norm)!r}")
+    if name(cfg.mlp) not in ("swiglu", "swiglu_native", "swiglu_triton"):
+        bad.append(f"mlp={name(cfg.mlp)!r}")
+    if name(cfg.posenc) != "rope":
+        bad.append(f"posenc={name(cfg.posenc)!r}")
+    if any(w is not None for w in cfg.windows):
+        bad.append("sliding windows")
+    if cfg.attn_sink:
+        bad.append("attention sinks")
+    if cfg.rope_scaling not in (None, "none"):
+        bad.append(f"rope_scaling={cfg.rope_scaling!r}")
+    if not cfg.qk_norm:
+        bad.append("qk_norm=False (the graphs expect per-head q/k norm weights)")
+    elif not cfg.qk_norm_affine:
+        bad.append("qk_norm_affine=False (the graphs expect per-head q/k norm weights)")
+    for flag in ("attn_bias", "post_norm", "scale_residual_by_depth", "embedding_scale"):
+        if getattr(cfg, flag):
+            bad.append(flag)
+    if cfg.logit_soft_cap:
+        bad.append("logit_soft_cap")
+    if any(cfg.moe_layers):
+        kw = cfg.moe_router_kwargs or {}
+        if name(cfg.moe_router) != "topk":
+            bad.append(f"moe_router={name(cfg.moe_router)!r}")
+        if kw.get("score", kw.get("score_func", "sigmoid")) not in GATING:
+            bad.append(f"router score {kw.get('score')!r}")
+        if cfg.moe_mlp not in (None, "moe"):
+            bad.append(f"moe_mlp={cfg.moe_mlp!r}")
+    return bad
+
+
 def convert(state: dict, cfg, out: str, *, name: str = "kohaku", arch: str = "auto", out_dtype: str = "f16", expand_kv: bool = True,
-            tokenizer: str | None = None, turn_end: str = "<|im_end|>", chat_template: bool = True) -> dict:
+            tokenizer: str | None = None, turn_end: str = "<|im_end|>", chat_template: bool = True,
+            allow_lossy: bool = False) -> dict:
+    lossy = unrepresentable(cfg)
+    if lossy and not allow_lossy:
+        raise ValueError("llama.cpp's " + ("dots1" if any(cfg.moe_layers) else "qwen3") + " graph cannot express: "
+                         + ", ".join(lossy) + " (pass allow_lossy / --allow-lossy to write the file anyway)")
     state = {k.removeprefix("module."): v for k, v in state.items()}
     sparse = any(k.endswith("mlp.router.weight") for k in state)
     if arch == "auto":
@@ -196,7 +240,7 @@ def convert(state: dict, cfg, out: str, *, name: str = "kohaku", arch: str = "au
         meta.update(tokenizer_meta(tokenizer, turn_end, chat_template))
     tensors = tensor_map(state, cfg, expand_kv)
     write_gguf(out, tensors, meta, out_dtype=out_dtype)
-    return {"arch": arch, "tensors": len(tensors), "dtype": out_dtype, "metadata_keys": len(meta)}
+    return {"arch": arch, "tensors": len(tensors), "dtype": out_dtype, "metadata_keys": len(meta), "lossy": lossy}
 
 
 def main(argv=None) -> int:
@@ -214,13 +258,16 @@ def main(argv=None) -> int:
     ap.add_argument("--tokenizer", default=None, help="directory with tokenizer.json (+ tokenizer_config.json)")
     ap.add_argument("--turn-end-token", default="<|im_end|>")
     ap.add_argument("--no-chat-template", action="store_true")
+    ap.add_argument("--allow-lossy", action="store_true", help="write the file although the target graph lacks some of the model's options")
     a = ap.parse_args(argv)
     cfg = get_preset(a.preset, **{k: parse_value(v) for k, v in (kv.split("=", 1) for kv in a.set)})
     state = torch.load(a.ckpt, map_location="cpu", weights_only=False)
     state = state.get("state_dict", state)
     info = convert(state, cfg, a.out, name=a.preset, arch=a.arch, out_dtype=a.out_dtype, expand_kv=not a.no_expand_kv,
-                   tokenizer=a.tokenizer, turn_end=a.turn_end_token, chat_template=not a.no_chat_template)
-    print(f"wrote {a.out}: {info['tensors']} tensors, arch={info['arch']}, {info['dtype']}")
+                   tokenizer=a.tokenizer, turn_end=a.turn_end_token, chat_template=not a.no_chat_template,
+                   allow_lossy=a.allow_lossy)
+    print(f"wrote {a.out}: {info['tensors']} tensors, arch={info['arch']}, {info['dtype']}"
+          + (f" (NOT expressed in the file: {', '.join(info['lossy'])})" if info["lossy"] else ""))
     return 0
 
 

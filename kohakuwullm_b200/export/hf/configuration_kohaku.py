@@ -12,7 +12,8 @@ class KohakuConfig(PretrainedConfig):
                  kohaku_rope_scaling=None, kohaku_rope_factor=1.0, max_position_embeddings=8192, qk_norm=True, windows=None,
                  num_sinks=0, moe_layers=None, moe_num_experts=0, moe_top_k=0, moe_num_shared=0,
                  moe_intermediate_size=0, moe_score="sigmoid", moe_norm_topk_prob=True, moe_scaling=1.0,
-                 tie_word_embeddings=False, embedding_scale=False, logit_soft_cap=None, **kwargs):
+                 tie_word_embeddings=False, embedding_scale=False, logit_soft_cap=None, hidden_act="silu",
+                 residual_scale=1.0, rope_partial=1.0, **kwargs):
         self.vocab_size, self.hidden_size, self.num_hidden_layers = vocab_size, hidden_size, num_hidden_layers
         self.num_attention_heads, self.num_key_value_heads, self.head_dim = num_attention_heads, num_key_value_heads, head_dim
         self.intermediate_size, self.rms_norm_eps = intermediate_size, rms_norm_eps
@@ -26,4 +27,6 @@ class KohakuConfig(PretrainedConfig):
         self.moe_intermediate_size, self.moe_score = moe_intermediate_size, moe_score
         self.moe_norm_topk_prob, self.moe_scaling = moe_norm_topk_prob, moe_scaling
         self.embedding_scale, self.logit_soft_cap = embedding_scale, logit_soft_cap
+        # gate activation of the dense MLPs ("silu" or "gelu_tanh"), multiplier of every branch output, rotated share of a head
+        self.hidden_act, self.residual_scale, self.rope_partial = hidden_act, residual_scale, rope_partial
         super().__init__(tie_word_embeddings=tie_word_embeddings, **kwargs)

@@ -8,6 +8,39 @@ import shutil
 import torch
 
 
+def _name(spec) -> str:
+    return spec if isinstance(spec, str) else (spec.get("name") if isinstance(spec, dict) else getattr(spec, "__name__", str(spec)))
+
+
+NORMS = {"rmsnorm": False, "rmsnorm_native": False, "rmsnorm_triton": False, "gemma_rmsnorm": True}     # name -> scale is 1 + weight
+MLPS = {"swiglu": "silu", "swiglu_native": "silu", "swiglu_triton": "silu", "geglu": "gelu_tanh"}
+
+
+def unsupported_options(cfg) -> list[str]:
+    """Architecture options the exported modelling code does not implement. Some of them keep every parameter name
+    (a routing variant, a residual rule), so loading the weights would succeed and the exported model would silently
+    compute something else: the export refuses them instead."""
+    bad = []
+    if _name(cfg.norm) not in NORMS:
+        bad.append(f"norm={_name(cfg.norm)!r}")
+    if _name(cfg.mlp) not in MLPS:
+        bad.append(f"mlp={_name(cfg.mlp)!r}")
+    if _name(cfg.posenc) != "rope":
+        bad.append(f"posenc={_name(cfg.posenc)!r}")
+    if cfg.post_norm:
+        bad.append("post_norm")
+    if cfg.attn_bias:
+        bad.append("attn_bias")
+    if cfg.qk_norm and not cfg.qk_norm_affine:
+        bad.append("qk_norm_affine=False")
+    if any(cfg.moe_layers):
+        if _name(cfg.moe_router) != "topk":
+            bad.append(f"moe_router={_name(cfg.moe_router)!r}")
+        if cfg.moe_mlp not in (None, "moe"):
+            bad.append(f"moe_mlp={cfg.moe_mlp!r}")
+    return bad
+
+
 def to_hf_config(cfg):
     from kohakuwullm_b200.export.hf.configuration_kohaku import KohakuConfig
 
@@ -29,7 +62,8 @@ def to_hf_config(cfg):
         moe_num_experts=cfg.moe_num_experts if any(cfg.moe_layers) else 0, moe_top_k=cfg.moe_top_k,
         moe_num_shared=cfg.moe_num_shared, moe_intermediate_size=expert_hidden, moe_score=rk.get("score", "sigmoid"),
         moe_norm_topk_prob=rk.get("norm_topk_prob", True), moe_scaling=rk.get("routed_scaling_factor", 1.0),
-        tie_word_embeddings=cfg.tie_embeddings, embedding_scale=cfg.embedding_scale, logit_soft_cap=cfg.logit_soft_cap)
+        tie_word_embeddings=cfg.tie_embeddings, embedding_scale=cfg.embedding_scale, logit_soft_cap=cfg.logit_soft_cap,
+        hidden_act=MLPS.get(_name(cfg.mlp), "silu"), residual_scale=cfg.residual_scale, rope_partial=cfg.rope_partial)
 
 
 def convert_state_dict(state: dict, cfg) -> dict:
@@ -43,6 +77,11 @@ def convert_state_dict(state: dict, cfg) -> dict:
         out[k] = v
     if cfg.tie_embeddings:
         out["lm_head.weight"] = out["embed.weight"]
+    if NORMS.get(_name(cfg.norm), False):
+        # the model scales by 1 + weight (zero-initialised weight); the exported norm scales by its weight
+        for k in list(out):
+            if k.endswith(("norm_attn.weight", "norm_mlp.weight", "final_norm.weight")):
+                out[k] = out[k].float() + 1.0
     return out
 
 
@@ -50,6 +89,9 @@ def export_hf(backbone_or_state, cfg, out_dir: str, dtype=torch.bfloat16):
     from kohakuwullm_b200.export.hf.modeling_kohaku import KohakuForCausalLM
 
     state = backbone_or_state.state_dict() if hasattr(backbone_or_state, "state_dict") else backbone_or_state
+    bad = unsupported_options(cfg)
+    if bad:
+        raise ValueError("the exported modelling code does not implement: " + ", ".join(bad))
     hf_cfg = to_hf_config(cfg)
     hf_cfg.auto_map = {"AutoConfig": "configuration_kohaku.KohakuConfig",
                        "AutoModelForCausalLM": "modeling_kohaku.KohakuForCausalLM"}

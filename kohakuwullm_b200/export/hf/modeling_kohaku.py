@@ -30,7 +30,8 @@ class KohakuRMSNorm(nn.Module):
 
 
 def _inv_freq(cfg: KohakuConfig):
-    d, theta, f = cfg.head_dim, cfg.kohaku_rope_theta, cfg.kohaku_rope_factor
+    d = int(cfg.head_dim * getattr(cfg, "rope_partial", 1.0)) // 2 * 2      # only the first d channels of a head rotate
+    theta, f = cfg.kohaku_rope_theta, cfg.kohaku_rope_factor
     idx = torch.arange(0, d, 2, dtype=torch.float64)
     scale = 1.0
     if cfg.kohaku_rope_scaling in (None, "none", "linear"):
@@ -75,9 +76,11 @@ class KohakuAttention(nn.Module):
             q, k = _rms(q, self.q_norm, cfg.rms_norm_eps), _rms(k, self.k_norm, cfg.rms_norm_eps)
 
         def rot(t):
-            a, b = t.float()[..., : D // 2], t.float()[..., D // 2:]
+            half = cos.shape[-1]
+            tf = t.float()
+            a, b, tail = tf[..., :half], tf[..., half:2 * half], tf[..., 2 * half:]
             c, s = cos[:, :, None, :], sin[:, :, None, :]
-            return torch.cat([a * c - b * s, b * c + a * s], -1).to(t.dtype)
+            return torch.cat([a * c - b * s, b * c + a * s, tail], -1).to(t.dtype)
 
         q, k = rot(q), rot(k)
         if past is not None:
@@ -104,14 +107,16 @@ class KohakuAttention(nn.Module):
 
 
 class KohakuMLP(nn.Module):
-    def __init__(self, dim, hidden):
+    def __init__(self, dim, hidden, act="silu"):
         super().__init__()
         self.w_in = nn.Linear(dim, 2 * hidden, bias=False)
         self.w_out = nn.Linear(hidden, dim, bias=False)
+        self.act = act
 
     def forward(self, x):
         g, v = self.w_in(x).chunk(2, -1)
-        return self.w_out(torch.nn.functional.silu(g) * v)
+        g = torch.nn.functional.gelu(g, approximate="tanh") if self.act == "gelu_tanh" else torch.nn.functional.silu(g)
+        return self.w_out(g * v)
 
 
 class KohakuMoE(nn.Module):
@@ -155,12 +160,14 @@ class KohakuBlock(nn.Module):
         self.norm_attn = KohakuRMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
         self.attn = KohakuAttention(cfg, layer)
         self.norm_mlp = KohakuRMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
-        self.mlp = KohakuMoE(cfg) if cfg.moe_layers[layer] else KohakuMLP(cfg.hidden_size, cfg.intermediate_size)
+        self.mlp = KohakuMoE(cfg) if cfg.moe_layers[layer] else \
+            KohakuMLP(cfg.hidden_size, cfg.intermediate_size, getattr(cfg, "hidden_act", "silu"))
+        self.scale = float(getattr(cfg, "residual_scale", 1.0))
 
     def forward(self, x, cos, sin, pos, past):
         a, past = self.attn(self.norm_attn(x), cos, sin, pos, past)
-        x = x + a
-        return x + self.mlp(self.norm_mlp(x)), past
+        x = x + a * self.scale
+        return x + self.mlp(self.norm_mlp(x)) * self.scale, past
 
 
 class KohakuForCausalLM(PreTrainedModel):

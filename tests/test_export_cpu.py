@@ -2,6 +2,8 @@
 
 import struct
 
+import pytest
+
 import torch
 
 from kohakuwullm_b200.export.hf.convert import export_hf
@@ -39,6 +41,71 @@ def test_hf_export_widths_derived_from_ratios(tmp_path):
     _check(get_preset("B200-smoke", vocab_size=101, dim=96, depth=3, heads=2, kv_heads=1, head_dim=32, mlp_hidden=None,
                       mlp_ratio=3.0, mlp_multiple_of=32, moe_every=1, moe_first_dense=1, moe_num_experts=4, moe_top_k=2,
                       moe_hidden=None, moe_ratio=1.5, moe_num_shared=2, mxfp8=False, init_std=0.2), tmp_path)
+
+
+BASE = dict(vocab_size=101, dim=64, depth=3, heads=2, kv_heads=1, head_dim=32, mlp_hidden=128, init_std=0.2, mxfp8=False)
+MOE4 = dict(moe_every=1, moe_num_experts=4, moe_top_k=2, moe_hidden=64)
+
+
+@pytest.mark.parametrize("overrides", [
+    dict(tie_embeddings=True, embedding_scale=True, logit_soft_cap=20.0),
+    dict(rope_scaling="ntk", rope_factor=2.0, rope_partial=0.5),
+    dict(rope_scaling="yarn", rope_factor=4.0, rope_partial=0.75),
+    dict(rope_scaling="linear", rope_factor=4.0),
+    dict(norm="gemma_rmsnorm"),
+    dict(mlp="geglu"),
+    dict(scale_residual_by_depth=True, qk_norm=False),
+    dict(**MOE4, moe_router_kwargs={"score": "sqrtsoftplus", "norm_topk_prob": False, "routed_scaling_factor": 2.5}),
+])
+def test_hf_export_reproduces_every_supported_option(tmp_path, overrides):
+    cfg = get_preset("B200-smoke", **{**BASE, **overrides})
+    torch.manual_seed(0)
+    model = LMBackbone(cfg).eval()
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            if "norm" in n:
+                p.add_(torch.randn_like(p) * 0.2)          # a gain of exactly 1 (or 0) would hide a wrong scaling rule
+    hf = export_hf(model.state_dict(), cfg, str(tmp_path), dtype=torch.float32).eval()
+    tokens = torch.randint(0, cfg.vocab_size, (2, 11))
+    with torch.no_grad():
+        ours = model.head.logits(model(tokens, SeqInfo.padded(2, 11)))
+        theirs = hf(tokens).logits
+    torch.testing.assert_close(ours, theirs, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("overrides,word", [
+    (dict(attn_bias=True), "attn_bias"), (dict(post_norm=True), "post_norm"), (dict(qk_norm_affine=False), "qk_norm_affine"),
+    (dict(norm="layernorm"), "layernorm"), (dict(mlp="gelu"), "gelu"), (dict(posenc="none"), "posenc"),
+    (dict(**MOE4, moe_router="sinkhorn"), "sinkhorn"), (dict(**MOE4, moe_mlp="latent_moe"), "latent_moe"),
+])
+def test_exports_refuse_what_their_target_cannot_express(tmp_path, overrides, word):
+    """An option that keeps every parameter name (a routing variant, a residual rule) would load into the exported
+    model and silently compute something else: both exporters name the option and refuse."""
+    from kohakuwullm_b200.cli.to_gguf import convert, unrepresentable
+
+    cfg = get_preset("B200-smoke", **{**BASE, **overrides})
+    state = LMBackbone(cfg).state_dict()
+    with pytest.raises(ValueError, match=word):
+        export_hf(state, cfg, str(tmp_path / "hf"))
+    with pytest.raises(ValueError, match=word):
+        convert(state, cfg, str(tmp_path / "m.gguf"))
+    assert any(word in item for item in unrepresentable(cfg))
+
+
+def test_gguf_refuses_windows_sinks_and_scaling_unless_told_to_write_anyway(tmp_path):
+    from kohakuwullm_b200.cli.to_gguf import convert, unrepresentable
+
+    plain = get_preset("B200-smoke", **BASE)
+    assert unrepresentable(plain) == []
+    fancy = get_preset("B200-smoke", **BASE, sliding_window=4, global_layer_every=2, attn_sink=True, rope_scaling="yarn",
+                       rope_factor=4.0, logit_soft_cap=30.0)
+    lossy = unrepresentable(fancy)
+    assert {"sliding windows", "attention sinks", "logit_soft_cap"} <= set(lossy) and any("yarn" in x for x in lossy)
+    state = LMBackbone(fancy).state_dict()
+    with pytest.raises(ValueError, match="sliding windows"):
+        convert(state, fancy, str(tmp_path / "m.gguf"))
+    info = convert(state, fancy, str(tmp_path / "m.gguf"), allow_lossy=True)
+    assert info["lossy"] == lossy and (tmp_path / "m.gguf").stat().st_size > 1000
 
 
 def test_prune_tokenizer():
