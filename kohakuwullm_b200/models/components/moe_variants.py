@@ -1,7 +1,7 @@
 """Routing and expert-layer variants next to the DeepSeekMoE default.
 
-``sinkhorn``       assignment from a Sinkhorn-balanced matrix (3 iterations, temperature 0.05), gate weight
-                   from the raw softmax;
+``sinkhorn``       while training: assignment from a Sinkhorn-balanced matrix (3 iterations, temperature 0.05,
+                   log domain), gate weight from the raw softmax; in evaluation: each token's own top-k;
 ``expert_choice``  every expert takes its ``capacity`` best tokens (kept for experiments; it has no
                    token-choice ``route`` and raises if wired into ``MoEMLP``);
 ``relu``           ReMoE: ``relu(logits)`` gates, sparsity steered by an L1 coefficient that is multiplied by
@@ -31,6 +31,17 @@ class SinkhornRouter(TopKRouter):
 
     def route(self, x):
         logits = torch.nn.functional.linear(x.float(), self.weight.float())
+        if not self.training:
+            # the balanced assignment depends on which tokens share the batch, which is not causal: decoding one
+            # token at a time and recomputing the whole prefix would pick different experts. Evaluation and
+            # generation therefore take the plain top-k of each token's own scores.
+            s = torch.softmax(logits, -1)
+            w, idx = s.topk(self.top_k, dim=-1)
+            if self.norm_topk_prob:
+                w = w / (w.sum(-1, keepdim=True) + 1e-20)
+            self.aux_loss = None
+            counts = torch.bincount(idx.reshape(-1), minlength=self.num_experts).to(torch.int32)
+            return idx, w * self.routed_scaling_factor, counts
         with torch.no_grad():
             # in the log domain: dividing logits by a small temperature spans hundreds of e-folds, which underflows
             # a plain exp() to a matrix of floor values and collapses the assignment onto one expert

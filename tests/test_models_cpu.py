@@ -93,6 +93,20 @@ def test_sinkhorn_assignment_is_more_balanced_than_plain_topk():
     assert float(c.max()) < 2.5 * float(c.float().mean()), c
 
 
+def test_sinkhorn_model_decodes_the_same_with_and_without_a_cache():
+    """Balancing over the batch is a training-time rule; in evaluation each token routes on its own scores, so a
+    cached decode (one token per step) and a recompute of the whole prefix agree token for token."""
+    from kohakuwullm_b200.generation.engine import LocalGenerator
+
+    torch.manual_seed(0)
+    cfg = get_preset("B200-smoke", **{**BASE, **MOE, "moe_router": "sinkhorn", "vocab_size": 97, "init_std": 0.3})
+    model = LMBackbone(cfg)
+    prompt = torch.randint(0, 97, (3, 5))
+    cached = LocalGenerator(model, eos_id=96, use_cache=True).generate(prompt, 10, temperature=0.0)
+    plain = LocalGenerator(model, eos_id=96, use_cache=False).generate(prompt, 10, temperature=0.0)
+    assert torch.equal(cached, plain) and len(set(cached[0, 5:].tolist())) > 1
+
+
 def test_relu_router_steers_its_sparsity_coefficient_towards_the_target():
     torch.manual_seed(0)
     router = ROUTER.get("relu")(64, 8, 2, l1_init=1e-3, alpha=1.5)
