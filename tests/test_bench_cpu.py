@@ -276,3 +276,22 @@ def test_stage_memory_accounts_every_parameter_once():
         assert opt.state_bytes() == sm.optimizer_state_bytes([("w", p)], name), name
     with pytest.raises(ValueError):
         sm.optimizer_state_bytes([("w", p)], "lion")
+
+
+@pytest.mark.timeout(120)
+def test_loader_throughput_bench_counts_tokens_in_process_and_with_workers(capsys):
+    """The data-path benchmark on a small synthetic corpus: one row per worker count with a positive rate and packs
+    filled close to the budget, for the byte tokenizer and for a BPE trained on the corpus itself."""
+    from kohakuwullm_b200.bench import loader_throughput as lt
+
+    assert lt.main(["--documents", "300", "--doc-chars", "400", "--workers", "0", "2", "--seconds", "0.4",
+                    "--pack-tokens", "2048", "--ctx-max", "1024"]) == 0
+    rows = [json.loads(line) for line in capsys.readouterr().out.splitlines() if line.startswith("{")]
+    runs = [r for r in rows if "workers" in r]
+    assert [r["workers"] for r in runs] == [0, 2]
+    assert all(r["tokens_per_s"] > 1e4 and 0.8 < r["fill"] <= 1.0 for r in runs)
+    assert rows[-1]["best_tokens_per_s"] == max(r["tokens_per_s"] for r in runs)
+    assert lt.main(["--documents", "200", "--doc-chars", "400", "--workers", "0", "--seconds", "0.3", "--pack-tokens", "1024",
+                    "--ctx-max", "512", "--tokenizer", "bpe:600"]) == 0
+    bpe = [json.loads(line) for line in capsys.readouterr().out.splitlines() if '"workers"' in line][0]
+    assert bpe["tokenizer"] == "bpe:600" and bpe["tokens_per_s"] > 1e3
