@@ -34,7 +34,7 @@ _TEXT = [            # (corpus, repeat, renderer)
 ]
 
 SOURCES = [{"records": {"name": "vault_corpus", "root": _text_root, "corpus": name,
-                        "schema": "json" if kind == "chat" else "text"}, "repeat": repeat, "source": name}
+                        "schema": "json" if kind in ("chat", "qa_chatml") else "text"}, "repeat": repeat, "source": name}
            for name, repeat, kind in _TEXT] + _cap["caption_sources"](("danbooru", "coyo11m", "laion_coco"))
 RENDERER = {"name": "per_source", "default": "plain",
             "renderers": {**{name: kind for name, _, kind in _TEXT},

@@ -85,6 +85,10 @@ class LoaderPosition:
         return cls(d["shard"], d["shards"], d.get("pass", 0), d.get("cursor", 0), carry, d.get("emitted", 0))
 
 
+class EmptyShard(LookupError):
+    """This loader's shard holds no records."""
+
+
 class IterativePackLoader:
     def __init__(self, records, renderer, encode, *, k: int, m: int = 0, ctx_max: int | None = None,
                  shard: int = 0, shards: int = 1, seed: int = 0, bos: int | None = None, eos: int | None = None,
@@ -116,7 +120,7 @@ class IterativePackLoader:
                 self.pos.epoch += 1
                 self.pos.cursor = 0
                 if self.order.length() == 0:
-                    raise StopIteration
+                    raise EmptyShard(f"shard {self.order.shard}/{self.order.shards} of {len(self.records)} records is empty")
             idx = self.order.index(self.pos.epoch, self.pos.cursor)
             self.pos.cursor += 1
             rng = random.Random((self.seed * 1000003 + idx) ^ (self.pos.epoch << 32))
@@ -169,7 +173,10 @@ class IterativePackLoader:
 
     def __iter__(self) -> Iterator[tuple[PackedBatch, dict]]:
         while True:
-            batch = self._next_pack()
+            try:
+                batch = self._next_pack()
+            except EmptyShard:
+                return                 # nothing to read (a hold-out split of a tiny corpus): an empty iteration, not an error
             yield batch, self.pos.as_dict()
 
 

@@ -181,6 +181,8 @@ class VaultCorpusRecords:
         value = self.shards[s].value_at(i - self._starts[s])
         if self.schema == "text":
             return {"text": value if isinstance(value, str) else bytes(value).decode("utf-8", "replace"), "source": self.name}
+        if isinstance(value, (str, bytes, bytearray)):
+            value = json.loads(value)          # a store whose writer kept the documents as JSON text
         return value
 
 

@@ -117,6 +117,11 @@ class ValidationCallback(Callback):
         if self.interval <= 0 or step % self.interval:
             return
         self.last = trainer.validate(self.make_loader(), self.max_batches)
+        if not self.last.get("val/tokens"):
+            if trainer.rank == 0 and not getattr(self, "_warned_empty", False):
+                log.warning("validation", step=step, message="the held-out split is empty: nothing to validate on")
+                self._warned_empty = True
+            return
         if trainer.rank == 0:
             log.info("validation", step=step, **self.last)
             if self.reporter:

@@ -73,9 +73,11 @@ def _phase_ends(phases: list[dict], total: int | None) -> list[int]:
             if not total or total <= 0:
                 raise ValueError("a fractional phase end needs the composition's own 'end'")
             e = int(round(e * total))
-        if e is None or int(e) <= (ends[-1] if ends else 0):
+        frac = isinstance(p.get("end"), float) and 0.0 < p["end"] <= 1.0
+        last = ends[-1] if ends else 0
+        if e is None or int(e) < last or (int(e) == last and not frac):
             raise ValueError(f"phase ends must be given and increase, got {[q.get('end') for q in phases]}")
-        ends.append(int(e))
+        ends.append(int(e))        # a fractional end may round onto the previous one in a very short run: an empty phase
     return ends
 
 
@@ -91,6 +93,8 @@ def build_schedule(spec: dict | None) -> Callable[[int], float]:
     total = spec.get("end")
     ends = _phase_ends(phases, int(total) if isinstance(total, (int, float)) and total and total > 0 else None)
     starts = [0] + ends[:-1]
+    keep = [i for i, (a, b) in enumerate(zip(starts, ends)) if b > a]          # phases that rounding left empty drop out
+    phases, starts, ends = [phases[i] for i in keep], [starts[i] for i in keep], [ends[i] for i in keep]
     fns = [_single({**p, "end": e - s}) for p, s, e in zip(phases, starts, ends)]
     carry = [1.0]                       # value the previous phases ended on
     for fn, s, e in zip(fns[:-1], starts, ends):

@@ -442,3 +442,35 @@ def test_packing_properties_over_random_lengths_budgets_and_slack():
         assert seen_tokens >= total, (seen_tokens, total, packs)          # the epoch was delivered, the loader never stalled
 
     check()
+
+
+def test_a_loader_without_records_is_an_empty_iteration():
+    """A hold-out split of a tiny corpus can be empty: iterating it yields nothing (it used to escape as a
+    ``StopIteration`` inside a generator, which Python turns into a RuntimeError)."""
+    from kohakuwullm_b200.data import build_loader
+    from kohakuwullm_b200.data.sources.records import SplitRecords
+    from kohakuwullm_b200.registry import DATASET, build
+
+    records = build({"name": "list", "records": [{"text": "abc def"} for _ in range(3)]}, DATASET)
+    held_out = SplitRecords(records, 0.0001, "val", 0)
+    assert len(held_out) == 0
+    loader = build_loader("ddp", held_out, lambda r, rng=None: [(r["text"], True)], lambda s: list(s.encode()), k=64, m=4)
+    assert list(loader) == []
+    # more shards than records: the shards beyond the records are empty iterations too
+    extra = build_loader("ddp", records, lambda r, rng=None: [(r["text"], True)], lambda s: list(s.encode()), k=64, m=4,
+                         rank=5, world=8)
+    assert list(extra) == []
+
+
+def test_vault_corpus_json_schema_reads_dict_values_and_json_text(tmp_path):
+    import json
+
+    from kohakuwullm_b200.data.sources.kvstore import KVWriter, VaultCorpusRecords
+
+    d = tmp_path / "sft" / "chat"
+    d.mkdir(parents=True)
+    with KVWriter(str(d / "shard-0.kv")) as w:
+        w.put("00000000", {"messages": [{"role": "user", "content": "hi"}]})          # stored as JSON by the writer
+        w.put("00000001", json.dumps({"messages": [{"role": "user", "content": "yo"}]}))   # JSON kept as text by another tool
+    recs = VaultCorpusRecords("sft/chat", str(tmp_path), schema="json")
+    assert [r["messages"][0]["content"] for r in (recs[0], recs[1])] == ["hi", "yo"]

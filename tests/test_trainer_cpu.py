@@ -83,6 +83,9 @@ def test_composed_schedules_are_continuous_and_count_from_each_phase_start():
     assert abs(g(400_000) - 0.01 * at_switch) < 1e-9
     values = [g(s) for s in range(0, 400_001, 997)]
     assert all(b <= a + 1e-12 for a, b in zip(values[3:], values[4:]))       # monotone after the warm-up
+    # a ten-step smoke run of the same recipe: 0.9 x 4 rounds onto 4, the tail phase is empty and drops out
+    short = build_schedule(autofill_schedule_steps(spec, 4, 1))
+    assert all(0.0 < short(s) <= 1.0 for s in range(6))
     with pytest.raises(ValueError):
         build_schedule({"phases": [{"mode": "constant", "end": 0.5}, {"mode": "cosine", "end": 1.0}]})   # no total
     with pytest.raises(ValueError):
