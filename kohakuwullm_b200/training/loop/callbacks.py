@@ -93,7 +93,7 @@ class SampleLogCallback(Callback):
             if trainer.rank != 0:
                 return
             for p, t in zip(self.prompts, texts):
-                log.info("sample", step=step, prompt=p[:40], text=t[:200].replace("\n", "\\n"))
+                log.info("sample", step=step, prompt=p[:40].replace("\n", "\\n"), text=t[:200].replace("\n", "\\n"))
             if self.reporter:
                 # a reporter with a ``samples`` method gets a table (step, name, prompt, sample, text); a plain
                 # callable gets the texts
