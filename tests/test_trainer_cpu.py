@@ -269,3 +269,15 @@ def test_every_shipped_config_names_only_knobs_of_its_entry_point(monkeypatch):
     monkeypatch.setenv("KWU_SWEEP", "8192x32_fp7")
     with pytest.raises(ValueError):
         load_config_file(os.path.join(root, "sweep", "microbatch.py"))
+
+
+def test_every_entry_point_knob_is_named_in_the_configuration_guide():
+    import importlib
+    import re
+
+    doc = open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "docs", "configs.md")).read()
+    for entry in ("train_lm", "train_lm_pipe"):
+        mod = importlib.import_module(f"kohakuwullm_b200.cli.{entry}")
+        knobs = [k for k in vars(mod) if k.isupper() and not k.startswith("_")]
+        missing = [k for k in knobs if not re.search(rf"\b{k}\b", doc)]
+        assert not missing, f"{entry}: knobs without a mention in docs/configs.md: {missing}"
