@@ -66,6 +66,11 @@ class WorkerPackLoader:
             raise ValueError("workers must be at least 1")
         if kind not in ("iterative", "pipeline"):
             raise ValueError(f"unknown worker loader kind {kind!r}")
+        total_shards = workers if kind == "pipeline" else world * workers
+        if len(records) < total_shards:
+            # a worker whose shard is empty would exit without a batch; say what is wrong instead
+            raise ValueError(f"{len(records)} records cannot feed {total_shards} loader shards "
+                             f"({workers} workers x {1 if kind == 'pipeline' else world} ranks): use fewer workers")
         self.records, self.renderer, self.encode = records, renderer, encode
         self.workers, self.rank, self.world, self.kind = workers, rank, world, kind
         self.prefetch, self.pin_memory, self.kw = prefetch, pin_memory, loader_kwargs

@@ -474,3 +474,12 @@ def test_vault_corpus_json_schema_reads_dict_values_and_json_text(tmp_path):
         w.put("00000001", json.dumps({"messages": [{"role": "user", "content": "yo"}]}))   # JSON kept as text by another tool
     recs = VaultCorpusRecords("sft/chat", str(tmp_path), schema="json")
     assert [r["messages"][0]["content"] for r in (recs[0], recs[1])] == ["hi", "yo"]
+
+
+def test_worker_loader_refuses_more_shards_than_records():
+    from kohakuwullm_b200.data import build_loader
+    from kohakuwullm_b200.registry import DATASET, build
+
+    records = build({"name": "list", "records": [{"text": "abc"} for _ in range(3)]}, DATASET)
+    with pytest.raises(ValueError, match="use fewer workers"):
+        build_loader("workers", records, lambda r, rng=None: [(r["text"], True)], lambda s: list(s.encode()), workers=4, k=64)
